@@ -1,0 +1,405 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-weight decode hot path on B200.
+
+A step is one pass of the decode FFN projections of a dense 27B-class layer at batch 1:
+quantize_q8(x[5120]) -> Q4_K gate matvec and Q4_K up matvec (5120 -> 17408, sharing the
+quantized x), quantize_q8(h[17408]) -> Q6_K down matvec (17408 -> 5120).  The metric is the
+reference's: repacked weight bytes streamed per second (GB/s).  Steps rotate over several
+distinct copies of the layer's weights so that no launch finds its weights in L2.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+With N > 1 (launched by torch.distributed.run, one rank per GPU) every matrix is split by
+output rows, each rank streams its shard, and the shards' outputs are all-gathered.
+`--impl reference` times the reference's CPU path (dequantize to f32 + sequential-f32 row
+dots, row-parallel over the host cores) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+Q4_K, Q6_K = 12, 14
+HIDDEN, FFN = 5120, 17408
+LAYER = [("gate", Q4_K, HIDDEN, FFN), ("up", Q4_K, HIDDEN, FFN), ("down", Q6_K, FFN, HIDDEN)]
+
+
+def measured_peaks() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.lines: list[str] = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [s.strip() for s in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------- CPU arm
+
+
+def cpu_layer_sample(seconds: float, threads: int):
+    """Times the reference's CPU path (oracle port) on the layer's three matrices; returns
+    (GB/s by the same byte count the GPU arm uses, description, seconds per layer)."""
+    sys.path.insert(0, str(ROOT / "tests"))
+    import oracle as ro
+    from reinstinct_b200 import synth
+
+    total_bytes, mats = 0, []
+    for i, (_, t, in_dim, out_dim) in enumerate(LAYER):
+        raw = synth.synth_blocks(t, in_dim, out_dim, seed=10 + i)
+        x = synth.synth_activations(1, in_dim, seed=20 + i)
+        mats.append((t, raw, x, in_dim, out_dim, np.empty(in_dim * out_dim, dtype=np.float32)))
+        total_bytes += ro.repacked_len(t, in_dim, out_dim)
+    times = []
+    t_end = time.perf_counter() + seconds
+    while not times or (time.perf_counter() < t_end and len(times) < 50):
+        t0 = time.perf_counter()
+        for t, raw, x, in_dim, out_dim, wf in mats:
+            ro.cpu_path(t, raw, x, in_dim, out_dim, n_threads=threads, w_f32=wf, dequant=True)
+        times.append(time.perf_counter() - t0)
+    best = min(times)
+    sample = (f"{len(times)} passes of the full layer (gate, up: Q4_K 5120->17408; down: Q6_K 17408->5120), "
+              f"dequantize-to-f32 + sequential-f32 row dots, best pass {best * 1e3:.1f} ms")
+    return total_bytes / best / 1e9, sample, best
+
+
+def run_reference_arm(args):
+    """The reference's CPU implementation of the path, all host threads, on rank 0 only.
+    A step is one layer pass over the first `rows` output rows of each matrix, with `rows`
+    chosen from a probe so that the whole run stays within a couple of minutes."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    sys.path.insert(0, str(ROOT / "tests"))
+    import oracle as ro
+    from reinstinct_b200 import synth
+
+    def build(frac: float):
+        total_bytes, mats = 0, []
+        for i, (_, t, in_dim, out_dim) in enumerate(LAYER):
+            rows = min(out_dim, max(32, int(out_dim * frac) // 32 * 32))
+            raw = synth.synth_blocks(t, in_dim, rows, seed=10 + i)
+            x = synth.synth_activations(1, in_dim, seed=20 + i)
+            mats.append((t, raw, x, in_dim, rows, np.empty(in_dim * rows, dtype=np.float32)))
+            total_bytes += ro.repacked_len(t, in_dim, rows)
+        return total_bytes, mats
+
+    def one_pass(mats):
+        t0 = time.perf_counter()
+        for t, raw, x, in_dim, rows, wf in mats:
+            ro.cpu_path(t, raw, x, in_dim, rows, n_threads=threads, w_f32=wf, dequant=True)
+        return time.perf_counter() - t0
+
+    _, probe = build(1.0 / 16)
+    one_pass(probe)
+    t_probe = one_pass(probe) * 16  # estimate of a full layer pass
+    budget_s = 100.0
+    frac = min(1.0, budget_s / max(t_probe * (args.steps + args.warmup), 1e-9))
+    total_bytes, mats = build(frac)
+    times = []
+    for it in range(args.warmup + args.steps):
+        dt = one_pass(mats)
+        if it >= args.warmup:
+            times.append(dt)
+    per_step_s = sum(times) / len(times)
+    value = total_bytes / per_step_s / 1e9
+    sample = (f"each step: dequantize-to-f32 + sequential-f32 row dots over the first {frac:.3f} of the output "
+              f"rows of gate, up (Q4_K) and down (Q6_K), {total_bytes / 1e6:.1f} MB repacked, {threads} threads")
+    full_layer_s = per_step_s * 176168960 / total_bytes
+    line = {
+        "impl": "reference", "metric": "q4k_decode_matvec_hbm_gbs", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step_s * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "tok_per_s_per_layer": 1.0 / full_layer_s,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int) -> dict:
+    return {
+        "workload": "config 2: dense-27B decode FFN projections, batch 1 (Q4_K gate+up 5120->17408, Q6_K down 17408->5120)",
+        "bytes_per_step": 176168960,
+        "l2": "weights rotate over 3 distinct layer copies (528 MB > 4x L2); every launch reads cold HBM",
+        "parallelism": f"row-shard x{n_gpus} + all-gather" if n_gpus > 1 else "single GPU",
+    }
+
+
+# ------------------------------------------------------------------------------------- GPU arm
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    from reinstinct_b200 import runtime as rt
+    from reinstinct_b200 import synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    rt.init(local)
+
+    n_copies = 3
+    # Row shards: rank r owns rows [r*out/world, (r+1)*out/world) of every matrix; shard sizes
+    # are multiples of 32 so quantize-then-gather equals gather-then-quantize.
+    shards = []
+    for name, t, in_dim, out_dim in LAYER:
+        assert out_dim % (32 * world) == 0
+        shards.append((name, t, in_dim, out_dim // world))
+    copies = []
+    layer_bytes_local = 0
+    for c in range(n_copies):
+        ws = []
+        for i, (name, t, in_dim, out_local) in enumerate(shards):
+            # seeds differ by copy, matrix and rank: every shard is distinct data
+            raw = synth.synth_blocks(t, in_dim, out_local, seed=1000 * c + 10 * i + rank + 1)
+            ws.append(rt.GpuMatvecTensor.from_bytes_matvec(raw, t, in_dim, out_local, device=dev))
+        copies.append(ws)
+    layer_bytes_local = sum(w.data.numel() for w in copies[0])
+    layer_bytes_total = layer_bytes_local * world
+
+    x_host = torch.from_numpy(synth.synth_activations(1, HIDDEN, 5)).pin_memory()
+    h_host = torch.from_numpy(synth.synth_activations(1, FFN, 6)).pin_memory()
+    x_dev = torch.empty_like(x_host, device=dev)
+    h_dev = torch.empty_like(h_host, device=dev)
+    x_dev.copy_(x_host)
+    h_dev.copy_(h_host)
+    xq = torch.empty((HIDDEN // 32) * 40, dtype=torch.uint8, device=dev)
+    hq = torch.empty((FFN // 32) * 40, dtype=torch.uint8, device=dev)
+    y_gate = torch.empty(FFN // world, device=dev)
+    y_up = torch.empty(FFN // world, device=dev)
+    y_down = torch.empty(HIDDEN // world, device=dev)
+    g_gate = torch.empty(FFN, device=dev) if world > 1 else y_gate
+    g_up = torch.empty(FFN, device=dev) if world > 1 else y_up
+    g_down = torch.empty(HIDDEN, device=dev) if world > 1 else y_down
+    yg_host = torch.empty(FFN, dtype=torch.float32).pin_memory()
+    yu_host = torch.empty(FFN, dtype=torch.float32).pin_memory()
+    yd_host = torch.empty(HIDDEN, dtype=torch.float32).pin_memory()
+    launches_per_step = 5
+
+    def step(c: int):
+        ws = copies[c % n_copies]
+        rt.launch_quantize_q8(x_dev, xq, HIDDEN, 1)
+        rt.launch_matvec_xq8(ws[0], xq, y_gate)
+        rt.launch_matvec_xq8(ws[1], xq, y_up)
+        rt.launch_quantize_q8(h_dev, hq, FFN, 1)
+        rt.launch_matvec_xq8(ws[2], hq, y_down)
+        if world > 1:
+            dist.all_gather_into_tensor(g_gate, y_gate)
+            dist.all_gather_into_tensor(g_up, y_up)
+            dist.all_gather_into_tensor(g_down, y_down)
+
+    def step_e2e(c: int):
+        x_dev.copy_(x_host, non_blocking=True)
+        h_dev.copy_(h_host, non_blocking=True)
+        step(c)
+        yg_host.copy_(g_gate, non_blocking=True)
+        yu_host.copy_(g_up, non_blocking=True)
+        yd_host.copy_(g_down, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps: int, warmup: int) -> float:
+        """Device time in ms of `steps` calls, max over ranks."""
+        for i in range(warmup):
+            fn(i)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    # The decode loop is launch-bound from Python (8 us kernels), so the steps are replayed
+    # from a CUDA graph, as the reference's engine replays its forward (graph of n_copies steps).
+    use_graph = world == 1 and not args.no_graph
+    if use_graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(3):
+                step(i)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for c in range(n_copies):
+                step(c)
+
+        def run_steps(i):
+            graph.replay()
+        steps_per_call = n_copies
+    else:
+        run_steps = step
+        steps_per_call = 1
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    calls = max(1, (args.steps + steps_per_call - 1) // steps_per_call)
+    steps_timed = calls * steps_per_call
+    ms = timed(run_steps, calls, max(3, (args.warmup + steps_per_call - 1) // steps_per_call))
+    ms_per_step = ms / steps_timed
+    value = layer_bytes_total / (ms_per_step * 1e-3) / 1e9
+
+    # end to end: host buffers in, host buffers out, copies inside the timed region
+    ms_e2e = timed(step_e2e, args.steps, max(3, args.warmup))
+    e2e_value = layer_bytes_total / (ms_e2e / args.steps * 1e-3) / 1e9
+
+    # dominant kernel alone: the Q4_K matvec over rotating copies, CUDA events on its stream
+    q4k_bytes = copies[0][0].data.numel()
+    mats = [copies[c][i] for c in range(n_copies) for i in (0, 1)]
+
+    def q4k_only(i):
+        for w in mats:
+            rt.launch_matvec_xq8(w, xq, y_gate)
+    if use_graph:
+        gq = torch.cuda.CUDAGraph()
+        q4k_only(0)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(gq):
+            q4k_only(0)
+
+        def q4k_call(i):
+            gq.replay()
+    else:
+        q4k_call = q4k_only
+    reps = max(20, args.steps // 2)
+    ms_q = timed(q4k_call, reps, 5)
+    q4k_us = ms_q * 1e3 / (reps * len(mats))
+    clocks = sampler.stop() if rank == 0 else None
+
+    # Q6_K down alone, for the per-format report
+    q6_bytes = copies[0][2].data.numel()
+    downs = [copies[c][2] for c in range(n_copies)]
+
+    def q6_only(i):
+        for w in downs:
+            rt.launch_matvec_xq8(w, hq, y_down)
+    ms_6 = timed(q6_only, reps, 5)
+    q6_us = ms_6 * 1e3 / (reps * len(downs))
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        achieved = q4k_bytes / (q4k_us * 1e-6) / 1e9
+        line = {
+            "metric": "q4k_decode_matvec_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": steps_timed, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 dp4a, f32 accumulate",
+            "data": "synthetic", "config": workload_config(world),
+            "e2e": {"value": e2e_value, "unit": "GB/s",
+                    "h2d_bytes_per_step": (HIDDEN + FFN) * 4, "d2h_bytes_per_step": (2 * FFN + HIDDEN) * 4,
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": launches_per_step * steps_timed,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": "matvec_kernel<Q4_K> 5120->%d" % (FFN // world),
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": peak_kind, "us_per_launch": q4k_us, "bytes_per_launch": q4k_bytes,
+                         "traffic": None},
+            "per_kernel": {"q4k_gate_up_gbs": achieved, "q6k_down_gbs": q6_bytes / (q6_us * 1e-6) / 1e9,
+                           "q6k_us": q6_us},
+            "tok_per_s_per_layer": 1e3 / ms_per_step,
+            "graph_replay": use_graph,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            v, sample, _ = cpu_layer_sample(seconds=12.0, threads=os.cpu_count() or 1)
+            line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port",
+                                    "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=30)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

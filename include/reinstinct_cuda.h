@@ -1,0 +1,224 @@
+/*
+ * reinstinct_cuda.h — C ABI of libreinstinct_cuda.so, the sm_100a (B200) backend for
+ * the quantized-weight hot path of the reinstinct engine.
+ *
+ * This is the surface a `src/cuda` module binds in place of `src/hip`: one entry point
+ * per launch wrapper of the reference's runtime, so launch geometry lives behind the
+ * ABI instead of in the caller.  Plain pointers and sizes only.  Every pointer named
+ * `*_dev` / w / xq / y / x is a DEVICE pointer unless the comment says host.
+ *
+ * Conventions (src/hip/mod.rs:19-22, src/runtime/qwen35.rs:4282-4292):
+ *   - every call returns an int: 0 on success, a positive cudaError_t value, or a
+ *     negative RC_ERR_* code; nothing aborts and nothing throws across the boundary;
+ *   - launches are asynchronous on `stream` (a cudaStream_t / CUstream passed as
+ *     void*, NULL = the default stream); no entry point allocates, frees,
+ *     synchronises or reads back, so all of them are legal under stream capture;
+ *   - the caller owns every buffer; inputs and outputs never alias;
+ *   - weights are in the repacked-v2 layout of src/quant/<fmt>.rs::repack_for_matvec,
+ *     read unchanged; activations cross the boundary as 40-byte BlockQ8 blocks
+ *     (kernels/quantize_q8.cpp:16-21) that need only 8-byte alignment;
+ *   - `ggml_type` is the GGUF discriminant (src/gguf/types.rs:16-35).
+ */
+#ifndef REINSTINCT_CUDA_H
+#define REINSTINCT_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RC_ABI_VERSION 1
+
+/* src/gguf/types.rs:16-35 */
+enum rc_ggml_type {
+    RC_TYPE_Q4_0 = 2,
+    RC_TYPE_Q8_0 = 8,
+    RC_TYPE_Q4_K = 12,
+    RC_TYPE_Q5_K = 13,
+    RC_TYPE_Q6_K = 14,
+    RC_TYPE_IQ4_XS = 23
+};
+
+enum rc_error {
+    RC_OK = 0,
+    RC_ERR_BAD_TYPE = -1,      /* ggml_type not one of the six above                  */
+    RC_ERR_BAD_SHAPE = -2,     /* in_dim not a multiple of the block size, zero dims  */
+    RC_ERR_NULL_POINTER = -3,
+    RC_ERR_MISALIGNED = -4,    /* weight base not 16-byte, BlockQ8 base not 8-byte    */
+    RC_ERR_TOO_MANY_ROWS = -5, /* n_rows beyond what the entry point accepts          */
+    RC_ERR_SCRATCH_TOO_SMALL = -6,
+    RC_ERR_NO_DEVICE = -7,     /* no sm_100 device / kernels not loadable             */
+    RC_ERR_BAD_ARGUMENT = -8
+};
+
+#define RC_BLOCKQ8_BYTES 40          /* kernels/quantize_q8.cpp:16-21 */
+#define RC_MATVEC_MAX_ROWS 16        /* src/runtime/prefill.rs:42 MAX_BATCHED_ROWS */
+
+/* ---- library ---------------------------------------------------------------- */
+
+/* Selects `device`, checks it is compute capability 10.x and sets the kernels'
+ * shared-memory attributes.  Call once per device before stream capture; the
+ * launch entry points call it lazily for the current device otherwise.
+ * Replaces KernelCache::compile + Module::load (src/runtime/mod.rs:195-245). */
+int rc_init(int device);
+int rc_abi_version(void);
+/* Static string for any code returned by this library
+ * (hip::Hip::err_str, src/hip/sys.rs:107-119). */
+const char *rc_error_string(int code);
+
+/* ---- layout helpers (host arithmetic only) ------------------------------------ */
+
+/* src/quant/q4_k.rs:92-95 (same rule in q4_0.rs:60-63, q8_0.rs:68-71, iq4_xs.rs:79-82) */
+size_t rc_repacked_n_sub_padded(size_t in_dim);
+/* src/quant/<fmt>.rs::repacked_len; 0 for an unsupported type or shape */
+size_t rc_repacked_len(int ggml_type, size_t in_dim, size_t out_dim);
+/* bytes of the on-disk GGUF rows for the same shape; 0 if unsupported */
+size_t rc_ondisk_len(int ggml_type, size_t in_dim, size_t out_dim);
+
+/* On-disk GGUF rows (device) -> repacked-v2 planes (device), done on the GPU.
+ * Produces byte-for-byte what src/quant/<fmt>.rs::repack_for_matvec produces on the
+ * host (q4_0.rs:86-104, q4_k.rs:126-176, q5_k.rs:97-151, q6_k.rs:86-148,
+ * q8_0.rs:93-119, iq4_xs.rs:106-136); the step GpuMatvecTensor::from_bytes_matvec
+ * (src/runtime/qwen35.rs:251-331) performs at load.  `blocks_dev` needs 2-byte
+ * alignment, `out_dev` 16-byte. */
+int rc_repack_for_matvec(void *stream, int ggml_type, const void *blocks_dev,
+                         size_t in_dim, size_t out_dim, void *out_dev);
+
+/* ---- activation quantizer --------------------------------------------------------- */
+
+/* launch_quantize_q8 (src/runtime/gemma4.rs:1495-1506),
+ * launch_quantize_q8_into (src/runtime/qwen35.rs:3202-3211);
+ * kernel quantize_q8_f32 (kernels/quantize_q8.cpp:23-54).
+ * x f32 [n_vec][in_dim] -> xq BlockQ8 [n_vec][in_dim/32]; in_dim % 32 == 0. */
+int rc_quantize_q8(void *stream, const float *x, void *xq, uint32_t in_dim, uint32_t n_vec);
+
+/* ---- decode matvec ------------------------------------------------------------------- */
+
+/* launch_matvec_xq8 (src/runtime/gemma4.rs:1526-1564),
+ * launch_matvec_repacked_xq8 (src/runtime/qwen35.rs:2232-2280); kernels
+ * matvec_{q4_0,q4k,q5k,q6k,q8_0,iq4xs}_repacked_f32.
+ * y f32 [out_dim] = W[out_dim][in_dim] . xq[in_dim/32]. */
+int rc_matvec(void *stream, int ggml_type, const void *w, const void *xq, float *y,
+              uint32_t in_dim, uint32_t out_dim);
+
+/* matmul_kquant_batched_into's kernel launch (src/runtime/prefill.rs:448-508),
+ * bmm_batched_kquant (src/runtime/qwen35.rs:4085-4111); kernels
+ * matvec_<fmt>_repacked_batched{,16}_f32.  1 <= n_rows <= RC_MATVEC_MAX_ROWS; Q8_0 is
+ * accepted too (the reference has no batched Q8_0 kernel, prefill.rs:350-354).
+ * xq [n_rows][in_dim/32], y f32 [n_rows][out_dim]. */
+int rc_matvec_batched(void *stream, int ggml_type, const void *w, const void *xq, float *y,
+                      uint32_t in_dim, uint32_t out_dim, uint32_t n_rows);
+
+/* launch_matvec (src/runtime/gemma4.rs:1508-1520), launch_matvec_dispatch
+ * (src/runtime/qwen35.rs:2179-2229): quantize x into the caller's xq scratch
+ * ((in_dim/32)*40 bytes), then rc_matvec. */
+int rc_matvec_f32(void *stream, int ggml_type, const void *w, const float *x, float *y,
+                  uint32_t in_dim, uint32_t out_dim, void *xq_scratch, size_t scratch_bytes);
+
+/* Test and debug aid: the per-(activation row, weight row, sub-block) integers the
+ * matvec forms before scaling.  idots int32 [n_rows][out_dim][in_dim/32][2]; slot 1 is
+ * used by Q6_K only (the second 16-weight half, kernels/matvec_q6k_repacked.cpp:83-109). */
+int rc_matvec_block_dots(void *stream, int ggml_type, const void *w, const void *xq,
+                         int32_t *idots, uint32_t in_dim, uint32_t out_dim, uint32_t n_rows);
+
+/* ---- int8 MMQ GEMM --------------------------------------------------------------------- */
+
+/* matmul_mmq_into's kernel launch (src/runtime/prefill.rs:512-567), bmm_mmq
+ * (src/runtime/qwen35.rs:4116-4148); kernels mmq_gemm_<fmt>_repacked{,_narrow}_f32.
+ * Y f32 [p_rows][out_dim] = Xq[p_rows][in_dim/32] . W^T, any p_rows >= 1. */
+int rc_mmq_gemm(void *stream, int ggml_type, const void *w, const void *xq, float *y,
+                uint32_t in_dim, uint32_t out_dim, uint32_t p_rows);
+
+/* PrefillGemm::matmul_into_raw (src/runtime/prefill.rs:343-437): quantize X into the
+ * caller's scratch (n_rows*(in_dim/32)*40 bytes), then the batched matvec for
+ * n_rows <= RC_MATVEC_MAX_ROWS, else the MMQ GEMM.  x f32 [n_rows][in_dim]. */
+int rc_matmul(void *stream, int ggml_type, const void *w, const float *x, float *y,
+              uint32_t in_dim, uint32_t out_dim, uint32_t n_rows, void *xq_scratch,
+              size_t scratch_bytes);
+/* bytes rc_matmul / rc_matvec_f32 need in xq_scratch */
+size_t rc_matmul_scratch_bytes(uint32_t in_dim, uint32_t n_rows);
+
+/* ---- MoE: expert sort, gather, scatter, grouped GEMM --------------------------------------- */
+
+/* launch_moe_sort (src/runtime/qwen35.rs:2892-2938, src/runtime/gemma4.rs:1825-1870);
+ * kernels moe_sort_{zero,histogram,scan,scatter} (kernels/moe_expert_sort.cpp:27-76).
+ * ids int32 [n_entries] (entry = tok*n_used + slot); outputs count[n_expert],
+ * cursor[n_expert] (scratch), expert_off[n_expert+1], tile_off[n_expert+1] (prefix of
+ * ceil(count/bn)), perm[n_entries].  Ids outside [0,n_expert) are dropped.  Order
+ * inside one expert is ascending entry index (the reference leaves it unspecified). */
+int rc_moe_sort(void *stream, const int32_t *ids, uint32_t n_entries, uint32_t n_expert,
+                uint32_t bn, int32_t *count, int32_t *cursor, int32_t *expert_off,
+                int32_t *tile_off, int32_t *perm);
+/* tile width the grouped GEMM assumes for tile_off (MOE_GEMM_BN, qwen35.rs:127) */
+uint32_t rc_moe_tile_bn(void);
+
+/* launch_moe_gather_xq (src/runtime/qwen35.rs:2999-3013); kernel moe_gather_xq
+ * (kernels/moe_expert_sort.cpp:82-96): xq_dst[p] = xq_src[perm[p] / n_used]. */
+int rc_moe_gather_xq(void *stream, const void *xq_src, const int32_t *perm, void *xq_dst,
+                     uint32_t n_sub, uint32_t n_used, uint32_t n_entries);
+
+/* launch_moe_scatter_rows (src/runtime/qwen35.rs:3016-3030); kernel moe_scatter_rows
+ * (kernels/moe_expert_sort.cpp:100-110): dst[perm[p]] = src[p], `dim` floats a row. */
+int rc_moe_scatter_rows(void *stream, const float *src, const int32_t *perm, float *dst,
+                        uint32_t dim, uint32_t n_entries);
+
+/* launch_moe_grouped_gemm (src/runtime/qwen35.rs:3036-3064,
+ * src/runtime/gemma4.rs:1909-1936); kernels mmq_gemm_{q4k,q5k,q6k,q8_0}_grouped_f32
+ * (kernels/mmq_gemm_q4k_grouped.cpp:38-165).  All six types are accepted.  xq and y
+ * are in expert-sorted order; expert e uses slab + e*bytes_per_expert. */
+int rc_mmq_gemm_grouped(void *stream, int ggml_type, const void *slab,
+                        size_t bytes_per_expert, const int32_t *expert_off,
+                        const int32_t *tile_off, uint32_t n_expert, const void *xq, float *y,
+                        uint32_t in_dim, uint32_t out_dim, uint32_t n_entries);
+
+/* ---- device API mirror (src/hip/sys.rs:57-101, src/hip/mod.rs) --------------------------- */
+
+enum rc_memcpy_kind { /* src/hip/sys.rs:45-53 */
+    RC_MEMCPY_H2H = 0, RC_MEMCPY_H2D = 1, RC_MEMCPY_D2H = 2, RC_MEMCPY_D2D = 3,
+    RC_MEMCPY_DEFAULT = 4
+};
+enum rc_capture_mode { RC_CAPTURE_GLOBAL = 0, RC_CAPTURE_THREAD_LOCAL = 1, RC_CAPTURE_RELAXED = 2 };
+
+int rc_get_device_count(int *count);
+int rc_set_device(int device);
+int rc_get_device(int *device);
+int rc_device_get_name(char *name, int len, int device);
+int rc_device_total_mem(size_t *bytes, int device);
+int rc_mem_get_info(size_t *free_bytes, size_t *total_bytes);
+int rc_device_can_access_peer(int *can, int device, int peer);
+/* "already enabled" is reported as success (src/hip/mod.rs:125-131) */
+int rc_device_enable_peer_access(int peer);
+int rc_device_synchronize(void);
+
+int rc_malloc(void **ptr, size_t bytes);
+int rc_free(void *ptr);
+int rc_memcpy(void *dst, const void *src, size_t bytes, int kind);
+int rc_memcpy_async(void *dst, const void *src, size_t bytes, int kind, void *stream);
+int rc_memcpy_peer_async(void *dst, int dst_device, const void *src, int src_device,
+                         size_t bytes, void *stream);
+int rc_memset_async(void *dst, int value, size_t bytes, void *stream);
+
+int rc_stream_create(void **stream);
+int rc_stream_destroy(void *stream);
+int rc_stream_synchronize(void *stream);
+int rc_stream_wait_event(void *stream, void *event);
+
+int rc_event_create(void **event);
+int rc_event_record(void *event, void *stream);
+int rc_event_synchronize(void *event);
+int rc_event_elapsed_time(float *ms, void *start, void *stop);
+int rc_event_destroy(void *event);
+
+int rc_stream_begin_capture(void *stream, int mode);
+int rc_stream_end_capture(void *stream, void **graph);
+int rc_graph_instantiate(void **graph_exec, void *graph);
+int rc_graph_launch(void *graph_exec, void *stream);
+int rc_graph_destroy(void *graph);
+int rc_graph_exec_destroy(void *graph_exec);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* REINSTINCT_CUDA_H */

@@ -1,0 +1,404 @@
+// C ABI of libreinstinct_cuda.so: argument checks, dispatch and the device-API mirror.
+// The declarations and the reference interfaces they stand in for are in
+// include/reinstinct_cuda.h.
+#include <cstdio>
+#include <cstring>
+
+#include "rc_common.cuh"
+#include "rc_internal.h"
+
+namespace rc {
+
+namespace {
+constexpr int kMaxDevices = 64;
+int g_sm_count[kMaxDevices];
+bool g_ready[kMaxDevices];
+} // namespace
+
+
+
+int sm_count()
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+    return g_sm_count[dev] > 0 ? g_sm_count[dev] : 148;
+}
+
+int ensure_device_ready()
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return RC_ERR_NO_DEVICE;
+    if (g_ready[dev]) return RC_OK;
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, dev);
+    if (e != cudaSuccess) return (int)e;
+    // The kernels are sm_100a only; there is no other code path to fall back to.
+    if (prop.major != 10) return RC_ERR_NO_DEVICE;
+    g_sm_count[dev] = prop.multiProcessorCount;
+    int rc = matvec_set_attributes();
+    if (rc) return rc;
+    rc = mmq_set_attributes();
+    if (rc) return rc;
+    rc = moe_set_attributes();
+    if (rc) return rc;
+    g_ready[dev] = true;
+    return RC_OK;
+}
+
+namespace {
+
+inline cudaStream_t S(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+int check_weight_args(int type, const void *w, const void *xq, const void *y, uint32_t in_dim,
+                      uint32_t out_dim)
+{
+    if (!fmt_known(type)) return RC_ERR_BAD_TYPE;
+    if (in_dim == 0 || out_dim == 0 || in_dim % fmt_block_weights(type)) return RC_ERR_BAD_SHAPE;
+    if (!w || !xq || !y) return RC_ERR_NULL_POINTER;
+    if (((uintptr_t)w & 15u) || ((uintptr_t)xq & 7u) || ((uintptr_t)y & 3u)) return RC_ERR_MISALIGNED;
+    return RC_OK;
+}
+
+} // namespace
+} // namespace rc
+
+using namespace rc;
+
+extern "C" {
+
+int rc_abi_version(void) { return RC_ABI_VERSION; }
+
+int rc_init(int device)
+{
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return (int)e;
+    return ensure_device_ready();
+}
+
+const char *rc_error_string(int code)
+{
+    switch (code) {
+    case RC_OK: return "success";
+    case RC_ERR_BAD_TYPE: return "unsupported ggml type (expected Q4_0, Q8_0, Q4_K, Q5_K, Q6_K or IQ4_XS)";
+    case RC_ERR_BAD_SHAPE: return "bad shape (zero dimension, or in_dim not a multiple of the format's block size)";
+    case RC_ERR_NULL_POINTER: return "null pointer argument";
+    case RC_ERR_MISALIGNED: return "misaligned pointer (weights need 16 bytes, BlockQ8 8 bytes, f32 4 bytes)";
+    case RC_ERR_TOO_MANY_ROWS: return "too many activation rows for this entry point";
+    case RC_ERR_SCRATCH_TOO_SMALL: return "scratch buffer too small";
+    case RC_ERR_NO_DEVICE: return "no usable sm_100 device";
+    case RC_ERR_BAD_ARGUMENT: return "bad argument";
+    }
+    if (code > 0) return cudaGetErrorString((cudaError_t)code);
+    return "unknown reinstinct_cuda error";
+}
+
+size_t rc_repacked_n_sub_padded(size_t in_dim) { return nsp_of((uint32_t)(in_dim / 32)); }
+
+size_t rc_repacked_len(int type, size_t in_dim, size_t out_dim)
+{
+    return repacked_len_of(type, in_dim, out_dim);
+}
+
+size_t rc_ondisk_len(int type, size_t in_dim, size_t out_dim)
+{
+    if (!fmt_known(type) || in_dim == 0 || in_dim % fmt_block_weights(type)) return 0;
+    return out_dim * (in_dim / fmt_block_weights(type)) * fmt_block_bytes(type);
+}
+
+int rc_repack_for_matvec(void *stream, int type, const void *blocks_dev, size_t in_dim,
+                         size_t out_dim, void *out_dev)
+{
+    if (!fmt_known(type)) return RC_ERR_BAD_TYPE;
+    if (in_dim == 0 || in_dim % fmt_block_weights(type) || in_dim > 0xFFFFFFE0ull ||
+        out_dim > 0xFFFFFFFFull)
+        return RC_ERR_BAD_SHAPE;
+    if (out_dim == 0) return RC_OK;
+    if (!blocks_dev || !out_dev) return RC_ERR_NULL_POINTER;
+    if (((uintptr_t)out_dev & 15u) || ((uintptr_t)blocks_dev & 1u)) return RC_ERR_MISALIGNED;
+    int rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_repack(S(stream), type, blocks_dev, in_dim, out_dim, out_dev);
+}
+
+int rc_quantize_q8(void *stream, const float *x, void *xq, uint32_t in_dim, uint32_t n_vec)
+{
+    if (in_dim == 0 || in_dim % 32) return RC_ERR_BAD_SHAPE;
+    if (n_vec == 0) return RC_OK;
+    if (!x || !xq) return RC_ERR_NULL_POINTER;
+    if (((uintptr_t)x & 3u) || ((uintptr_t)xq & 7u)) return RC_ERR_MISALIGNED;
+    int rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_quantize_q8(S(stream), x, xq, in_dim, n_vec);
+}
+
+int rc_matvec(void *stream, int type, const void *w, const void *xq, float *y, uint32_t in_dim,
+              uint32_t out_dim)
+{
+    int rc = check_weight_args(type, w, xq, y, in_dim, out_dim);
+    if (rc) return rc;
+    rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_matvec(S(stream), type, w, xq, y, in_dim, out_dim, 1, nullptr);
+}
+
+int rc_matvec_batched(void *stream, int type, const void *w, const void *xq, float *y,
+                      uint32_t in_dim, uint32_t out_dim, uint32_t n_rows)
+{
+    if (n_rows == 0) return RC_OK;
+    if (n_rows > RC_MATVEC_MAX_ROWS) return RC_ERR_TOO_MANY_ROWS;
+    int rc = check_weight_args(type, w, xq, y, in_dim, out_dim);
+    if (rc) return rc;
+    rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_matvec(S(stream), type, w, xq, y, in_dim, out_dim, n_rows, nullptr);
+}
+
+int rc_matvec_block_dots(void *stream, int type, const void *w, const void *xq, int32_t *idots,
+                         uint32_t in_dim, uint32_t out_dim, uint32_t n_rows)
+{
+    if (n_rows == 0) return RC_OK;
+    if (n_rows > RC_MATVEC_MAX_ROWS) return RC_ERR_TOO_MANY_ROWS;
+    int rc = check_weight_args(type, w, xq, idots, in_dim, out_dim);
+    if (rc) return rc;
+    rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_matvec(S(stream), type, w, xq, nullptr, in_dim, out_dim, n_rows, idots);
+}
+
+size_t rc_matmul_scratch_bytes(uint32_t in_dim, uint32_t n_rows)
+{
+    return (size_t)n_rows * (in_dim / 32) * RC_BLOCKQ8_BYTES;
+}
+
+int rc_matvec_f32(void *stream, int type, const void *w, const float *x, float *y, uint32_t in_dim,
+                  uint32_t out_dim, void *xq_scratch, size_t scratch_bytes)
+{
+    return rc_matmul(stream, type, w, x, y, in_dim, out_dim, 1, xq_scratch, scratch_bytes);
+}
+
+int rc_mmq_gemm(void *stream, int type, const void *w, const void *xq, float *y, uint32_t in_dim,
+                uint32_t out_dim, uint32_t p_rows)
+{
+    if (p_rows == 0) return RC_OK;
+    int rc = check_weight_args(type, w, xq, y, in_dim, out_dim);
+    if (rc) return rc;
+    rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_mmq_gemm(S(stream), type, w, xq, y, in_dim, out_dim, p_rows);
+}
+
+int rc_matmul(void *stream, int type, const void *w, const float *x, float *y, uint32_t in_dim,
+              uint32_t out_dim, uint32_t n_rows, void *xq_scratch, size_t scratch_bytes)
+{
+    if (n_rows == 0) return RC_OK;
+    if (!x) return RC_ERR_NULL_POINTER;
+    int rc = check_weight_args(type, w, xq_scratch, y, in_dim, out_dim);
+    if (rc) return rc;
+    if (scratch_bytes < rc_matmul_scratch_bytes(in_dim, n_rows)) return RC_ERR_SCRATCH_TOO_SMALL;
+    rc = ensure_device_ready();
+    if (rc) return rc;
+    rc = launch_quantize_q8(S(stream), x, xq_scratch, in_dim, n_rows);
+    if (rc) return rc;
+    // Row-count dispatch of PrefillGemm::matmul_into_raw (src/runtime/prefill.rs:343-437):
+    // few rows stream the weights once through the matvec, more rows go to the tensor cores.
+    if (n_rows <= RC_MATVEC_MAX_ROWS)
+        return launch_matvec(S(stream), type, w, xq_scratch, y, in_dim, out_dim, n_rows, nullptr);
+    return launch_mmq_gemm(S(stream), type, w, xq_scratch, y, in_dim, out_dim, n_rows);
+}
+
+uint32_t rc_moe_tile_bn(void) { return mmq_grouped_bn(); }
+
+int rc_moe_sort(void *stream, const int32_t *ids, uint32_t n_entries, uint32_t n_expert,
+                uint32_t bn, int32_t *count, int32_t *cursor, int32_t *expert_off,
+                int32_t *tile_off, int32_t *perm)
+{
+    if (n_expert == 0 || bn == 0) return RC_ERR_BAD_ARGUMENT;
+    if (!count || !cursor || !expert_off || !tile_off) return RC_ERR_NULL_POINTER;
+    if (n_entries && (!ids || !perm)) return RC_ERR_NULL_POINTER;
+    int rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_moe_sort(S(stream), ids, n_entries, n_expert, bn, count, cursor, expert_off,
+                           tile_off, perm);
+}
+
+int rc_moe_gather_xq(void *stream, const void *xq_src, const int32_t *perm, void *xq_dst,
+                     uint32_t n_sub, uint32_t n_used, uint32_t n_entries)
+{
+    if (n_entries == 0 || n_sub == 0) return RC_OK;
+    if (n_used == 0) return RC_ERR_BAD_ARGUMENT;
+    if (!xq_src || !perm || !xq_dst) return RC_ERR_NULL_POINTER;
+    if (((uintptr_t)xq_src & 7u) || ((uintptr_t)xq_dst & 7u)) return RC_ERR_MISALIGNED;
+    int rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_moe_gather_xq(S(stream), xq_src, perm, xq_dst, n_sub, n_used, n_entries);
+}
+
+int rc_moe_scatter_rows(void *stream, const float *src, const int32_t *perm, float *dst,
+                        uint32_t dim, uint32_t n_entries)
+{
+    if (n_entries == 0 || dim == 0) return RC_OK;
+    if (!src || !perm || !dst) return RC_ERR_NULL_POINTER;
+    int rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_moe_scatter_rows(S(stream), src, perm, dst, dim, n_entries);
+}
+
+int rc_mmq_gemm_grouped(void *stream, int type, const void *slab, size_t bytes_per_expert,
+                        const int32_t *expert_off, const int32_t *tile_off, uint32_t n_expert,
+                        const void *xq, float *y, uint32_t in_dim, uint32_t out_dim,
+                        uint32_t n_entries)
+{
+    if (n_entries == 0) return RC_OK;
+    if (n_expert == 0) return RC_ERR_BAD_ARGUMENT;
+    int rc = check_weight_args(type, slab, xq, y, in_dim, out_dim);
+    if (rc) return rc;
+    if (!expert_off || !tile_off) return RC_ERR_NULL_POINTER;
+    if (bytes_per_expert < repacked_len_of(type, in_dim, out_dim)) return RC_ERR_BAD_ARGUMENT;
+    // every expert's planes are read with 16-byte loads
+    if (n_expert > 1 && (bytes_per_expert & 15u)) return RC_ERR_MISALIGNED;
+    rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_mmq_grouped(S(stream), type, slab, bytes_per_expert, expert_off, tile_off,
+                              n_expert, xq, y, in_dim, out_dim, n_entries);
+}
+
+/* ---- device API mirror ------------------------------------------------------------------- */
+
+int rc_get_device_count(int *count) { return count ? (int)cudaGetDeviceCount(count) : RC_ERR_NULL_POINTER; }
+int rc_set_device(int device) { return (int)cudaSetDevice(device); }
+int rc_get_device(int *device) { return device ? (int)cudaGetDevice(device) : RC_ERR_NULL_POINTER; }
+
+int rc_device_get_name(char *name, int len, int device)
+{
+    if (!name || len <= 0) return RC_ERR_NULL_POINTER;
+    cudaDeviceProp prop;
+    cudaError_t e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) return (int)e;
+    std::snprintf(name, (size_t)len, "%s", prop.name);
+    return RC_OK;
+}
+
+int rc_device_total_mem(size_t *bytes, int device)
+{
+    if (!bytes) return RC_ERR_NULL_POINTER;
+    cudaDeviceProp prop;
+    cudaError_t e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) return (int)e;
+    *bytes = prop.totalGlobalMem;
+    return RC_OK;
+}
+
+int rc_mem_get_info(size_t *free_bytes, size_t *total_bytes)
+{
+    if (!free_bytes || !total_bytes) return RC_ERR_NULL_POINTER;
+    return (int)cudaMemGetInfo(free_bytes, total_bytes);
+}
+
+int rc_device_can_access_peer(int *can, int device, int peer)
+{
+    return can ? (int)cudaDeviceCanAccessPeer(can, device, peer) : RC_ERR_NULL_POINTER;
+}
+
+int rc_device_enable_peer_access(int peer)
+{
+    cudaError_t e = cudaDeviceEnablePeerAccess(peer, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        cudaGetLastError(); // clear the sticky-less error state
+        return RC_OK;
+    }
+    return (int)e;
+}
+
+int rc_device_synchronize(void) { return (int)cudaDeviceSynchronize(); }
+
+int rc_malloc(void **ptr, size_t bytes) { return ptr ? (int)cudaMalloc(ptr, bytes) : RC_ERR_NULL_POINTER; }
+int rc_free(void *ptr) { return (int)cudaFree(ptr); }
+
+int rc_memcpy(void *dst, const void *src, size_t bytes, int kind)
+{
+    return (int)cudaMemcpy(dst, src, bytes, (cudaMemcpyKind)kind);
+}
+int rc_memcpy_async(void *dst, const void *src, size_t bytes, int kind, void *stream)
+{
+    return (int)cudaMemcpyAsync(dst, src, bytes, (cudaMemcpyKind)kind, S(stream));
+}
+int rc_memcpy_peer_async(void *dst, int dst_device, const void *src, int src_device, size_t bytes,
+                         void *stream)
+{
+    return (int)cudaMemcpyPeerAsync(dst, dst_device, src, src_device, bytes, S(stream));
+}
+int rc_memset_async(void *dst, int value, size_t bytes, void *stream)
+{
+    return (int)cudaMemsetAsync(dst, value, bytes, S(stream));
+}
+
+int rc_stream_create(void **stream)
+{
+    if (!stream) return RC_ERR_NULL_POINTER;
+    cudaStream_t s;
+    cudaError_t e = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
+    *stream = (void *)s;
+    return (int)e;
+}
+int rc_stream_destroy(void *stream) { return (int)cudaStreamDestroy(S(stream)); }
+int rc_stream_synchronize(void *stream) { return (int)cudaStreamSynchronize(S(stream)); }
+int rc_stream_wait_event(void *stream, void *event)
+{
+    return (int)cudaStreamWaitEvent(S(stream), (cudaEvent_t)event, 0);
+}
+
+int rc_event_create(void **event)
+{
+    if (!event) return RC_ERR_NULL_POINTER;
+    cudaEvent_t ev;
+    cudaError_t e = cudaEventCreate(&ev);
+    *event = (void *)ev;
+    return (int)e;
+}
+int rc_event_record(void *event, void *stream) { return (int)cudaEventRecord((cudaEvent_t)event, S(stream)); }
+int rc_event_synchronize(void *event) { return (int)cudaEventSynchronize((cudaEvent_t)event); }
+int rc_event_elapsed_time(float *ms, void *start, void *stop)
+{
+    return ms ? (int)cudaEventElapsedTime(ms, (cudaEvent_t)start, (cudaEvent_t)stop) : RC_ERR_NULL_POINTER;
+}
+int rc_event_destroy(void *event) { return (int)cudaEventDestroy((cudaEvent_t)event); }
+
+int rc_stream_begin_capture(void *stream, int mode)
+{
+    return (int)cudaStreamBeginCapture(S(stream), (cudaStreamCaptureMode)mode);
+}
+int rc_stream_end_capture(void *stream, void **graph)
+{
+    if (!graph) return RC_ERR_NULL_POINTER;
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(S(stream), &g);
+    *graph = (void *)g;
+    return (int)e;
+}
+int rc_graph_instantiate(void **graph_exec, void *graph)
+{
+    if (!graph_exec) return RC_ERR_NULL_POINTER;
+    cudaGraphExec_t ge = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&ge, (cudaGraph_t)graph, 0);
+    *graph_exec = (void *)ge;
+    return (int)e;
+}
+int rc_graph_launch(void *graph_exec, void *stream)
+{
+    return (int)cudaGraphLaunch((cudaGraphExec_t)graph_exec, S(stream));
+}
+int rc_graph_destroy(void *graph) { return (int)cudaGraphDestroy((cudaGraph_t)graph); }
+int rc_graph_exec_destroy(void *graph_exec) { return (int)cudaGraphExecDestroy((cudaGraphExec_t)graph_exec); }
+
+/* tuning hook for sweeps: 0 restores the built-in heuristic for that knob */
+void rc_tune_matvec(int rows, int threads, int ctas_per_sm);
+
+} // extern "C"
+
+namespace rc { void matvec_set_tuning(int rows, int threads, int ctas_per_sm); }
+extern "C" void rc_tune_matvec(int rows, int threads, int ctas_per_sm)
+{
+    rc::matvec_set_tuning(rows, threads, ctas_per_sm);
+}

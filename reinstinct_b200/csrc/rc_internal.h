@@ -1,0 +1,48 @@
+// Internal launch functions behind the C ABI (one per kernel family).  All return RC_OK,
+// a negative rc_error or a positive cudaError_t; arguments are validated by the callers in
+// rc_api.cu.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace rc {
+
+int launch_quantize_q8(cudaStream_t s, const float *x, void *xq, uint32_t in_dim, uint32_t n_vec);
+
+int launch_repack(cudaStream_t s, int type, const void *blocks, size_t in_dim, size_t out_dim,
+                  void *out);
+
+// Decode and small-batch matvec (1 <= n_rows <= 16).  idots != nullptr selects the debug
+// variant that also writes the per-block integers.
+int launch_matvec(cudaStream_t s, int type, const void *w, const void *xq, float *y,
+                  uint32_t in_dim, uint32_t out_dim, uint32_t n_rows, int32_t *idots);
+int matvec_set_attributes();
+int launch_matvec_grouped(cudaStream_t s, int type, const void *slab, size_t bytes_per_expert,
+                          const int32_t *expert_off, const int32_t *tile_off, uint32_t n_expert,
+                          const void *xq, float *y, uint32_t in_dim, uint32_t out_dim,
+                          uint32_t n_entries);
+int moe_set_attributes();
+
+int launch_mmq_gemm(cudaStream_t s, int type, const void *w, const void *xq, float *y,
+                    uint32_t in_dim, uint32_t out_dim, uint32_t p_rows);
+int launch_mmq_grouped(cudaStream_t s, int type, const void *slab, size_t bytes_per_expert,
+                       const int32_t *expert_off, const int32_t *tile_off, uint32_t n_expert,
+                       const void *xq, float *y, uint32_t in_dim, uint32_t out_dim,
+                       uint32_t n_entries);
+int mmq_set_attributes();
+uint32_t mmq_grouped_bn();
+
+int launch_moe_sort(cudaStream_t s, const int32_t *ids, uint32_t n_entries, uint32_t n_expert,
+                    uint32_t bn, int32_t *count, int32_t *cursor, int32_t *expert_off,
+                    int32_t *tile_off, int32_t *perm);
+int launch_moe_gather_xq(cudaStream_t s, const void *xq_src, const int32_t *perm, void *xq_dst,
+                         uint32_t n_sub, uint32_t n_used, uint32_t n_entries);
+int launch_moe_scatter_rows(cudaStream_t s, const float *src, const int32_t *perm, float *dst,
+                            uint32_t dim, uint32_t n_entries);
+
+// Per-device one-time setup (kernel attributes); returns RC_OK or an error.
+int ensure_device_ready();
+int sm_count();
+
+} // namespace rc

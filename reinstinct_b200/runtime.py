@@ -1,0 +1,252 @@
+"""Host-side mirror of the reference's launch wrappers for the quantized-weight hot path.
+
+Same names, argument meaning and error behaviour as the Rust runtime of the reference
+(src/runtime/{gemma4,qwen35,prefill}.rs); every launch goes through the C ABI of
+libreinstinct_cuda.so on the current torch CUDA stream.  torch supplies device memory and
+streams only.  Errors from the library are raised as `RcError` carrying the code and the
+message, like the reference's `Err("<ctx>: <message> (code N)")` (src/hip/mod.rs:19-22).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import ALL_TYPES, BLOCKQ8_BYTES, MATVEC_MAX_ROWS, RcError, check
+
+__all__ = [
+    "GpuMatvecTensor", "GpuExpertTensor", "PrefillGemm", "MoeGroupedScratch",
+    "launch_quantize_q8", "launch_matvec", "launch_matvec_xq8", "launch_matvec_batched",
+    "matvec_block_dots", "launch_mmq_gemm", "launch_moe_sort", "launch_moe_gather_xq",
+    "launch_moe_grouped_gemm", "launch_moe_scatter_rows", "repacked_len", "init",
+]
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def init(device: int | None = None) -> None:
+    """Loads the library and prepares `device` (rc_init); call before graph capture."""
+    lib = _lib.load()
+    dev = torch.cuda.current_device() if device is None else device
+    check(lib.rc_init(dev), "rc_init")
+
+
+def repacked_len(dtype: int, in_dim: int, out_dim: int) -> int:
+    """quant::<fmt>::repacked_len (e.g. src/quant/q4_k.rs:98-102)."""
+    n = _lib.load().rc_repacked_len(dtype, in_dim, out_dim)
+    if n == 0:
+        raise ValueError(f"unsupported dtype/shape: {dtype} in_dim={in_dim} out_dim={out_dim}")
+    return n
+
+
+@dataclass
+class GpuMatvecTensor:
+    """GpuMatvecTensor { data, dtype, in_dim, out_dim, repacked } (src/runtime/qwen35.rs:182-191)."""
+    data: torch.Tensor  # uint8, device
+    dtype: int
+    in_dim: int
+    out_dim: int
+    repacked: bool = True
+
+    @staticmethod
+    def from_bytes_matvec(raw, dtype: int, in_dim: int, out_dim: int,
+                          device: torch.device | str = "cuda") -> "GpuMatvecTensor":
+        """from_bytes_matvec (src/runtime/qwen35.rs:251-331): on-disk GGUF rows -> repacked-v2
+        planes.  The raw blocks are uploaded and repacked on the GPU (rc_repack_for_matvec)."""
+        lib = _lib.load()
+        need = lib.rc_ondisk_len(dtype, in_dim, out_dim)
+        if need == 0:
+            raise ValueError(f"from_bytes_matvec: unsupported dtype {dtype} or in_dim {in_dim}")
+        raw_t = torch.as_tensor(np.frombuffer(raw, dtype=np.uint8) if not isinstance(raw, (np.ndarray, torch.Tensor)) else raw)
+        raw_t = raw_t.reshape(-1)
+        if raw_t.numel() < need:
+            raise ValueError(f"from_bytes_matvec: {raw_t.numel()} bytes < {need} needed")
+        raw_d = raw_t[:need].to(device, non_blocking=False).contiguous()
+        out = torch.empty(repacked_len(dtype, in_dim, out_dim), dtype=torch.uint8, device=device)
+        with torch.cuda.device(out.device):
+            check(lib.rc_repack_for_matvec(_stream(), dtype, raw_d.data_ptr(), in_dim, out_dim,
+                                           out.data_ptr()), "rc_repack_for_matvec")
+            torch.cuda.current_stream().synchronize()
+        return GpuMatvecTensor(out, dtype, in_dim, out_dim, True)
+
+
+@dataclass
+class GpuExpertTensor:
+    """GpuExpertTensor { data, dtype, in_dim, out_dim, bytes_per_expert, repacked }
+    (src/runtime/qwen35.rs:387-436): every expert repacked separately into one slab."""
+    data: torch.Tensor
+    dtype: int
+    in_dim: int
+    out_dim: int
+    bytes_per_expert: int
+    n_expert: int
+    repacked: bool = True
+
+    @staticmethod
+    def from_bytes(raw, dtype: int, in_dim: int, out_dim: int, n_expert: int,
+                   device: torch.device | str = "cuda") -> "GpuExpertTensor":
+        lib = _lib.load()
+        per_src = lib.rc_ondisk_len(dtype, in_dim, out_dim)
+        per_dst = repacked_len(dtype, in_dim, out_dim)
+        raw_t = torch.as_tensor(raw).reshape(-1)
+        if raw_t.numel() < per_src * n_expert:
+            raise ValueError("GpuExpertTensor.from_bytes: raw buffer too small")
+        raw_d = raw_t.to(device).contiguous()
+        out = torch.empty(per_dst * n_expert, dtype=torch.uint8, device=device)
+        with torch.cuda.device(out.device):
+            for e in range(n_expert):
+                check(lib.rc_repack_for_matvec(_stream(), dtype, raw_d.data_ptr() + e * per_src,
+                                               in_dim, out_dim, out.data_ptr() + e * per_dst),
+                      "rc_repack_for_matvec")
+            torch.cuda.current_stream().synchronize()
+        return GpuExpertTensor(out, dtype, in_dim, out_dim, per_dst, n_expert, True)
+
+
+def launch_quantize_q8(x: torch.Tensor, out: torch.Tensor, in_dim: int, n_vec: int) -> None:
+    """launch_quantize_q8(x, out, in_dim, n_vec) (src/runtime/gemma4.rs:1495-1506)."""
+    assert x.dtype == torch.float32 and out.dtype == torch.uint8
+    assert x.numel() >= in_dim * n_vec, "launch_quantize_q8: x too short"
+    assert out.numel() >= (in_dim // 32) * BLOCKQ8_BYTES * n_vec, "launch_quantize_q8: out too short"
+    check(_lib.load().rc_quantize_q8(_stream(), _ptr(x), _ptr(out), in_dim, n_vec), "rc_quantize_q8")
+
+
+def launch_matvec_xq8(w: GpuMatvecTensor, xq8: torch.Tensor, y: torch.Tensor) -> None:
+    """launch_matvec_xq8(w, xq8, y) (src/runtime/gemma4.rs:1526-1564)."""
+    assert w.repacked, "launch_matvec_xq8 requires a repacked weight"
+    assert y.dtype == torch.float32 and y.numel() >= w.out_dim
+    check(_lib.load().rc_matvec(_stream(), w.dtype, _ptr(w.data), _ptr(xq8), _ptr(y), w.in_dim,
+                                w.out_dim), "rc_matvec")
+
+
+def launch_matvec(w: GpuMatvecTensor, x: torch.Tensor, y: torch.Tensor, xq8: torch.Tensor) -> None:
+    """launch_matvec(w, x, y) (src/runtime/gemma4.rs:1508-1520): quantize into the engine's
+    xq8 scratch, then the matvec."""
+    assert w.repacked
+    check(_lib.load().rc_matvec_f32(_stream(), w.dtype, _ptr(w.data), _ptr(x), _ptr(y), w.in_dim,
+                                    w.out_dim, _ptr(xq8), xq8.numel()), "rc_matvec_f32")
+
+
+def launch_matvec_batched(w: GpuMatvecTensor, xq8: torch.Tensor, y: torch.Tensor, n_rows: int) -> None:
+    """The batched matvec launch of matmul_kquant_batched_into (src/runtime/prefill.rs:448-508)."""
+    assert w.repacked
+    check(_lib.load().rc_matvec_batched(_stream(), w.dtype, _ptr(w.data), _ptr(xq8), _ptr(y),
+                                        w.in_dim, w.out_dim, n_rows), "rc_matvec_batched")
+
+
+def matvec_block_dots(w: GpuMatvecTensor, xq8: torch.Tensor, n_rows: int) -> torch.Tensor:
+    """Per-(activation row, weight row, sub-block) integers, int32 [n_rows][out][n_sub][2]."""
+    out = torch.zeros((n_rows, w.out_dim, w.in_dim // 32, 2), dtype=torch.int32, device=w.data.device)
+    check(_lib.load().rc_matvec_block_dots(_stream(), w.dtype, _ptr(w.data), _ptr(xq8), _ptr(out),
+                                           w.in_dim, w.out_dim, n_rows), "rc_matvec_block_dots")
+    return out
+
+
+def launch_mmq_gemm(w: GpuMatvecTensor, xq8: torch.Tensor, y: torch.Tensor, p_rows: int) -> None:
+    """The MMQ launch of matmul_mmq_into (src/runtime/prefill.rs:512-567)."""
+    assert w.repacked
+    check(_lib.load().rc_mmq_gemm(_stream(), w.dtype, _ptr(w.data), _ptr(xq8), _ptr(y), w.in_dim,
+                                  w.out_dim, p_rows), "rc_mmq_gemm")
+
+
+class PrefillGemm:
+    """PrefillGemm (src/runtime/prefill.rs:215-567): Y = X . W^T for any row count, owning the
+    int8 activation scratch.  The scratch grows on demand after a stream synchronize, which is
+    only legal outside graph capture — pre-size with `max_x` as the reference does."""
+
+    def __init__(self, max_x: int = 32, device: torch.device | str = "cuda"):
+        self.device = torch.device(device)
+        self.xq8 = torch.empty(max(max_x, 32) // 32 * BLOCKQ8_BYTES, dtype=torch.uint8, device=self.device)
+
+    def _grow(self, n_bytes: int) -> None:
+        if self.xq8.numel() < n_bytes:
+            torch.cuda.current_stream().synchronize()  # the old buffer may still be in flight
+            self.xq8 = torch.empty(n_bytes, dtype=torch.uint8, device=self.device)
+
+    def matmul(self, w: GpuMatvecTensor, x: torch.Tensor, n_rows: int) -> torch.Tensor:
+        dst = torch.empty((n_rows, w.out_dim), dtype=torch.float32, device=self.device)
+        self.matmul_into(dst, w, x, n_rows)
+        return dst
+
+    def matmul_into(self, dst: torch.Tensor, w: GpuMatvecTensor, x: torch.Tensor, n_rows: int) -> None:
+        if dst.numel() < n_rows * w.out_dim:
+            raise ValueError(f"matmul_into: dst.len={dst.numel()} < n_rows*out_dim={n_rows * w.out_dim}")
+        self.matmul_into_raw(dst.data_ptr(), w, x.data_ptr(), n_rows)
+
+    def matmul_into_raw(self, dst_ptr: int, w: GpuMatvecTensor, x_ptr: int, n_rows: int) -> None:
+        """matmul_into_raw (src/runtime/prefill.rs:343-437); the caller owns the bounds."""
+        assert w.repacked, "only repacked weights are supported (no dequant->fp16 fallback)"
+        lib = _lib.load()
+        self._grow(lib.rc_matmul_scratch_bytes(w.in_dim, n_rows))
+        check(lib.rc_matmul(_stream(), w.dtype, _ptr(w.data), x_ptr, dst_ptr, w.in_dim, w.out_dim,
+                            n_rows, _ptr(self.xq8), self.xq8.numel()), "rc_matmul")
+
+    def matmul_host(self, w: GpuMatvecTensor, x_host: torch.Tensor, y_host: torch.Tensor,
+                    x_dev: torch.Tensor, y_dev: torch.Tensor, n_rows: int) -> None:
+        """End-to-end call with HOST buffers (pinned): upload x, run, download y, all on the
+        current stream; returns after the download is enqueued."""
+        x_dev.copy_(x_host, non_blocking=True)
+        self.matmul_into(y_dev, w, x_dev, n_rows)
+        y_host.copy_(y_dev, non_blocking=True)
+
+
+@dataclass
+class MoeGroupedScratch:
+    """MoeGroupedScratch (src/runtime/gemma4.rs:279-288): the sort outputs."""
+    count: torch.Tensor
+    cursor: torch.Tensor
+    expert_off: torch.Tensor
+    tile_off: torch.Tensor
+    perm: torch.Tensor
+    n_expert: int
+
+    @staticmethod
+    def new(n_expert: int, max_entries: int, device="cuda") -> "MoeGroupedScratch":
+        i32 = dict(dtype=torch.int32, device=device)
+        return MoeGroupedScratch(torch.zeros(n_expert, **i32), torch.zeros(n_expert, **i32),
+                                 torch.zeros(n_expert + 1, **i32), torch.zeros(n_expert + 1, **i32),
+                                 torch.zeros(max(max_entries, 1), **i32), n_expert)
+
+
+def moe_tile_bn() -> int:
+    return int(_lib.load().rc_moe_tile_bn())
+
+
+def launch_moe_sort(moe: MoeGroupedScratch, ids: torch.Tensor, n_entries: int, bn: int | None = None) -> None:
+    """launch_moe_sort (src/runtime/qwen35.rs:2892-2938)."""
+    assert ids.dtype == torch.int32
+    bn = moe_tile_bn() if bn is None else bn
+    check(_lib.load().rc_moe_sort(_stream(), _ptr(ids), n_entries, moe.n_expert, bn, _ptr(moe.count),
+                                  _ptr(moe.cursor), _ptr(moe.expert_off), _ptr(moe.tile_off),
+                                  _ptr(moe.perm)), "rc_moe_sort")
+
+
+def launch_moe_gather_xq(moe: MoeGroupedScratch, xq_src: torch.Tensor, xq_dst: torch.Tensor,
+                         n_sub: int, n_used: int, n_entries: int) -> None:
+    """launch_moe_gather_xq (src/runtime/qwen35.rs:2999-3013)."""
+    check(_lib.load().rc_moe_gather_xq(_stream(), _ptr(xq_src), _ptr(moe.perm), _ptr(xq_dst), n_sub,
+                                       n_used, n_entries), "rc_moe_gather_xq")
+
+
+def launch_moe_scatter_rows(moe: MoeGroupedScratch, src: torch.Tensor, dst: torch.Tensor, dim: int,
+                            n_entries: int) -> None:
+    """launch_moe_scatter_rows (src/runtime/qwen35.rs:3016-3030)."""
+    check(_lib.load().rc_moe_scatter_rows(_stream(), _ptr(src), _ptr(moe.perm), _ptr(dst), dim,
+                                          n_entries), "rc_moe_scatter_rows")
+
+
+def launch_moe_grouped_gemm(moe: MoeGroupedScratch, et: GpuExpertTensor, xq: torch.Tensor,
+                            y: torch.Tensor, in_dim: int, out_dim: int, n_entries: int) -> None:
+    """launch_moe_grouped_gemm (src/runtime/qwen35.rs:3036-3064)."""
+    check(_lib.load().rc_mmq_gemm_grouped(_stream(), et.dtype, _ptr(et.data), et.bytes_per_expert,
+                                          _ptr(moe.expert_off), _ptr(moe.tile_off), moe.n_expert,
+                                          _ptr(xq), _ptr(y), in_dim, out_dim, n_entries),
+          "rc_mmq_gemm_grouped")

@@ -1,0 +1,201 @@
+"""ctypes wrapper of the CPU oracle (oracle/libro_oracle.so).  Test infrastructure only."""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+ORACLE_DIR = Path(__file__).resolve().parent.parent / "oracle"
+LIB_PATH = ORACLE_DIR / "libro_oracle.so"
+
+Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS = 2, 8, 12, 13, 14, 23
+ALL_TYPES = (Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS)
+NAMES = {Q4_0: "q4_0", Q8_0: "q8_0", Q4_K: "q4_k", Q5_K: "q5_k", Q6_K: "q6_k", IQ4_XS: "iq4_xs"}
+
+_lib = None
+
+
+def build() -> Path:
+    src = [ORACLE_DIR / "ro_oracle.c", ORACLE_DIR / "ro_oracle.h"]
+    if not LIB_PATH.exists() or any(s.stat().st_mtime > LIB_PATH.stat().st_mtime for s in src):
+        subprocess.run(["make", "-C", str(ORACLE_DIR)], check=True, capture_output=True)
+    return LIB_PATH
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        build()
+        L = C.CDLL(str(LIB_PATH))
+        sz, vp, i = C.c_size_t, C.c_void_p, C.c_int
+        L.ro_f16_to_f32.restype = C.c_float
+        L.ro_f16_to_f32.argtypes = [C.c_uint16]
+        L.ro_f32_to_f16.restype = C.c_uint16
+        L.ro_f32_to_f16.argtypes = [C.c_float]
+        L.ro_bf16_to_f32.restype = C.c_float
+        L.ro_bf16_to_f32.argtypes = [C.c_uint16]
+        for name in ("ro_block_bytes", "ro_block_weights"):
+            getattr(L, name).restype = sz
+            getattr(L, name).argtypes = [i]
+        L.ro_nsp.restype = sz
+        L.ro_nsp.argtypes = [sz]
+        L.ro_repacked_len.restype = sz
+        L.ro_repacked_len.argtypes = [i, sz, sz]
+        L.ro_dequantize.restype = i
+        L.ro_dequantize.argtypes = [i, vp, vp, sz]
+        L.ro_repack.restype = i
+        L.ro_repack.argtypes = [i, vp, sz, sz, vp]
+        L.ro_quantize_q8.restype = None
+        L.ro_quantize_q8.argtypes = [vp, vp, sz, sz]
+        L.ro_dequantize_q8.restype = None
+        L.ro_dequantize_q8.argtypes = [vp, vp, sz, sz]
+        L.ro_matvec_q8.restype = i
+        L.ro_matvec_q8.argtypes = [i, vp, vp, sz, sz, sz, sz, sz, vp, vp, vp]
+        L.ro_matvec_f32.restype = None
+        L.ro_matvec_f32.argtypes = [vp, vp, sz, sz, vp, i]
+        L.ro_cpu_path.restype = i
+        L.ro_cpu_path.argtypes = [i, vp, vp, sz, sz, sz, vp, vp, i, i]
+        L.ro_moe_sort.restype = None
+        L.ro_moe_sort.argtypes = [vp, sz, sz, sz, vp, vp, vp, vp]
+        L.ro_router_topk.restype = None
+        L.ro_router_topk.argtypes = [vp, sz, sz, sz, vp, vp]
+        L.ro_grouped_q8.restype = i
+        L.ro_grouped_q8.argtypes = [i, vp, sz, vp, sz, vp, sz, sz, vp, vp]
+        _lib = L
+    return _lib
+
+
+def _p(a: np.ndarray | None):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def f16_to_f32(bits: int) -> float:
+    return float(lib().ro_f16_to_f32(bits))
+
+
+def f32_to_f16(v: float) -> int:
+    return int(lib().ro_f32_to_f16(C.c_float(v)))
+
+
+def block_bytes(t: int) -> int:
+    return lib().ro_block_bytes(t)
+
+
+def block_weights(t: int) -> int:
+    return lib().ro_block_weights(t)
+
+
+def nsp(in_dim: int) -> int:
+    return lib().ro_nsp(in_dim)
+
+
+def repacked_len(t: int, in_dim: int, out_dim: int) -> int:
+    return lib().ro_repacked_len(t, in_dim, out_dim)
+
+
+def dequantize(t: int, blocks: np.ndarray, n_weights: int) -> np.ndarray:
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+    out = np.empty(n_weights, dtype=np.float32)
+    assert lib().ro_dequantize(t, _p(blocks), _p(out), n_weights) == 0
+    return out
+
+
+def repack(t: int, blocks: np.ndarray, in_dim: int, out_dim: int) -> np.ndarray:
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+    n = repacked_len(t, in_dim, out_dim)
+    assert n > 0, "unsupported shape"
+    out = np.empty(n, dtype=np.uint8)
+    assert lib().ro_repack(t, _p(blocks), in_dim, out_dim, _p(out)) == 0
+    return out
+
+
+def quantize_q8(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    x2 = x.reshape(-1, x.shape[-1])
+    n_vec, in_dim = x2.shape
+    out = np.empty(n_vec * (in_dim // 32) * 40, dtype=np.uint8)
+    lib().ro_quantize_q8(_p(x2), _p(out), in_dim, n_vec)
+    return out
+
+
+def dequantize_q8(xq: np.ndarray, in_dim: int, n_vec: int) -> np.ndarray:
+    out = np.empty((n_vec, in_dim), dtype=np.float32)
+    lib().ro_dequantize_q8(_p(np.ascontiguousarray(xq)), _p(out), in_dim, n_vec)
+    return out
+
+
+def matvec_q8(t: int, w: np.ndarray, xq: np.ndarray, in_dim: int, out_dim: int, n_rows: int = 1,
+              want_idots: bool = False):
+    """Returns (y32 [n_rows,out], y64 [n_rows,out], idots [n_rows,out,n_sub,2] or None)."""
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    xq = np.ascontiguousarray(xq, dtype=np.uint8)
+    y32 = np.empty((n_rows, out_dim), dtype=np.float32)
+    y64 = np.empty((n_rows, out_dim), dtype=np.float64)
+    idots = np.empty((n_rows, out_dim, in_dim // 32, 2), dtype=np.int32) if want_idots else None
+    rc = lib().ro_matvec_q8(t, _p(w), _p(xq), in_dim, out_dim, n_rows, 0, out_dim, _p(y32), _p(y64), _p(idots))
+    assert rc == 0
+    return y32, y64, idots
+
+
+def matvec_f32(x: np.ndarray, w: np.ndarray, in_dim: int, out_dim: int, n_threads: int = 1) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    y = np.empty(out_dim, dtype=np.float32)
+    lib().ro_matvec_f32(_p(x), _p(w), in_dim, out_dim, _p(y), n_threads)
+    return y
+
+
+def cpu_path(t: int, blocks: np.ndarray, x: np.ndarray, in_dim: int, out_dim: int, n_threads: int = 1,
+             w_f32: np.ndarray | None = None, dequant: bool = True) -> np.ndarray:
+    """The reference's CPU path: dequantize to f32, then sequential-f32 row dots."""
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, in_dim)
+    n_rows = x.shape[0]
+    if w_f32 is None:
+        w_f32 = np.empty(out_dim * in_dim, dtype=np.float32)
+    y = np.empty((n_rows, out_dim), dtype=np.float32)
+    rc = lib().ro_cpu_path(t, _p(np.ascontiguousarray(blocks)), _p(x), in_dim, out_dim, n_rows, _p(w_f32),
+                           _p(y), n_threads, 1 if dequant else 0)
+    assert rc == 0
+    return y
+
+
+def moe_sort(ids: np.ndarray, n_expert: int, bn: int):
+    ids = np.ascontiguousarray(ids, dtype=np.int32).reshape(-1)
+    n = ids.size
+    count = np.zeros(n_expert, dtype=np.int32)
+    eoff = np.zeros(n_expert + 1, dtype=np.int32)
+    toff = np.zeros(n_expert + 1, dtype=np.int32)
+    perm = np.full(max(n, 1), -1, dtype=np.int32)
+    lib().ro_moe_sort(_p(ids), n, n_expert, bn, _p(count), _p(eoff), _p(toff), _p(perm))
+    return count, eoff, toff, perm[:n]
+
+
+def router_topk(logits: np.ndarray, n_used: int):
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    n_tok, n_expert = logits.shape
+    ids = np.empty((n_tok, n_used), dtype=np.int32)
+    wts = np.empty((n_tok, n_used), dtype=np.float32)
+    lib().ro_router_topk(_p(logits), n_tok, n_expert, n_used, _p(ids), _p(wts))
+    return ids, wts
+
+
+def grouped_q8(t: int, slab: np.ndarray, bytes_per_expert: int, expert_off: np.ndarray, xq: np.ndarray,
+               in_dim: int, out_dim: int):
+    n_expert = expert_off.size - 1
+    n_entries = int(expert_off[-1])
+    y32 = np.zeros((n_entries, out_dim), dtype=np.float32)
+    y64 = np.zeros((n_entries, out_dim), dtype=np.float64)
+    rc = lib().ro_grouped_q8(t, _p(np.ascontiguousarray(slab)), bytes_per_expert,
+                             _p(np.ascontiguousarray(expert_off, dtype=np.int32)), n_expert,
+                             _p(np.ascontiguousarray(xq)), in_dim, out_dim, _p(y32), _p(y64))
+    assert rc == 0
+    return y32, y64
+
+
+def rel_l2(a: np.ndarray, b: np.ndarray) -> float:
+    """||a-b|| / ||b|| in f64 (src/runtime/kernels.rs:1588-1596 of the reference)."""
+    a = np.asarray(a, dtype=np.float64).reshape(-1)
+    b = np.asarray(b, dtype=np.float64).reshape(-1)
+    return float(np.sqrt(np.sum((a - b) ** 2)) / max(np.sqrt(np.sum(b ** 2)), 1e-12))

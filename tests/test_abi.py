@@ -1,0 +1,50 @@
+"""The C-ABI library loads without a GPU and exports every symbol the header declares; the
+host-only helpers agree with the oracle's layout arithmetic.  No compute call is made here."""
+import ctypes as C
+
+import pytest
+
+import oracle as ro
+from reinstinct_b200 import _lib
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    declared = _lib.declared_symbols()
+    assert len(declared) >= 45
+    missing = [s for s in declared if not hasattr(lib, s)]
+    assert not missing, missing
+    # the Python binding covers the whole header too
+    assert sorted(_lib._SIGNATURES) == declared
+
+
+def test_abi_version_and_error_strings():
+    lib = _lib.load()
+    assert lib.rc_abi_version() == 1
+    assert _lib.error_string(0) == "success"
+    for code in range(-8, 0):
+        assert "unknown" not in _lib.error_string(code)
+    assert "unknown" in _lib.error_string(-99)
+
+
+@pytest.mark.parametrize("t", ro.ALL_TYPES)
+@pytest.mark.parametrize("in_dim,out_dim", [(256, 1), (1024, 3), (2048, 384), (5120, 17408), (16384, 64)])
+def test_layout_helpers_agree_with_oracle(t, in_dim, out_dim):
+    lib = _lib.load()
+    assert lib.rc_repacked_n_sub_padded(in_dim) == ro.nsp(in_dim)
+    assert lib.rc_repacked_len(t, in_dim, out_dim) == ro.repacked_len(t, in_dim, out_dim)
+    assert lib.rc_ondisk_len(t, in_dim, out_dim) == out_dim * (in_dim // ro.block_weights(t)) * ro.block_bytes(t)
+
+
+def test_bad_shapes_and_types_are_rejected_before_any_launch():
+    lib = _lib.load()
+    assert lib.rc_repacked_len(_lib.Q4_K, 96, 4) == 0
+    assert lib.rc_repacked_len(99, 256, 4) == 0
+    # argument errors are reported before the device is touched
+    assert lib.rc_quantize_q8(None, None, None, 33, 1) == -2
+    assert lib.rc_matvec(None, 99, None, None, None, 256, 1) == -1
+    assert lib.rc_matvec(None, _lib.Q4_K, None, None, None, 100, 1) == -2
+    assert lib.rc_matvec(None, _lib.Q4_K, None, None, None, 256, 1) == -3
+    assert lib.rc_matvec_batched(None, _lib.Q4_K, 16, 8, 4, 256, 1, 17) == -5
+    assert lib.rc_matvec(None, _lib.Q4_K, 8, 8, 4, 256, 1) == -4
+    assert lib.rc_matmul_scratch_bytes(5120, 4) == 4 * 160 * 40
