@@ -427,9 +427,11 @@ void ro_quantize_q8(const float *x, uint8_t *out, size_t in_dim, size_t n_vec)
             memcpy(o, &d, 4);
             memcpy(o + 4, &sum, 4);
             for (int l = 0; l < 32; l++) {
-                int q = (int)rintf(p[l] * inv); /* default rounding mode: half-even */
-                if (q > 127) q = 127;
-                if (q < -127) q = -127;
+                /* rint in the default mode is round-half-even.  The float->int conversion
+                 * saturates and maps NaN to 0, as the GPU conversion instruction does (a
+                 * subnormal amax makes inv infinite). */
+                float r = rintf(p[l] * inv);
+                int q = isnan(r) ? 0 : r > 127.0f ? 127 : r < -127.0f ? -127 : (int)r;
                 o[8 + l] = (uint8_t)(int8_t)q;
             }
         }

@@ -392,13 +392,24 @@ int rc_graph_launch(void *graph_exec, void *stream)
 int rc_graph_destroy(void *graph) { return (int)cudaGraphDestroy((cudaGraph_t)graph); }
 int rc_graph_exec_destroy(void *graph_exec) { return (int)cudaGraphExecDestroy((cudaGraphExec_t)graph_exec); }
 
-/* tuning hook for sweeps: 0 restores the built-in heuristic for that knob */
-void rc_tune_matvec(int rows, int threads, int ctas_per_sm);
 
 } // extern "C"
 
-namespace rc { void matvec_set_tuning(int rows, int threads, int ctas_per_sm); }
+namespace rc {
+void matvec_set_tuning(int rows, int threads, int ctas_per_sm);
+void matvec_set_pipe_tuning(int rows_per_stage, int stages, int cwarps, int ctas_per_sm, int disable);
+int matvec_device_error(unsigned int *out);
+} // namespace rc
 extern "C" void rc_tune_matvec(int rows, int threads, int ctas_per_sm)
 {
     rc::matvec_set_tuning(rows, threads, ctas_per_sm);
+}
+extern "C" void rc_tune_matvec_pipe(int rows_per_stage, int stages, int cwarps, int ctas_per_sm, int disable)
+{
+    rc::matvec_set_pipe_tuning(rows_per_stage, stages, cwarps, ctas_per_sm, disable);
+}
+extern "C" int rc_device_status(unsigned int *status)
+{
+    if (!status) return RC_ERR_NULL_POINTER;
+    return rc::matvec_device_error(status);
 }

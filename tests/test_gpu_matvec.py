@@ -76,7 +76,8 @@ def test_small_and_odd_shapes(rt, t):
     bw = ro.block_weights(t)
     for in_dim, out_dim, n_rows in [(bw, 1, 1), (bw, 3, 4), (bw * 3, 17, 2), (bw * 5, 1, 16)]:
         raw, x = cases.synth_case(t, in_dim, out_dim, n_rows, seed=in_dim + out_dim + t)
-        run_case(rt, t, raw, x, in_dim, out_dim)
+        # a handful of outputs is too few for a meaningful norm against the f32 path
+        run_case(rt, t, raw, x, in_dim, out_dim, f32_ref=False)
 
 
 @pytest.mark.parametrize("t", [ro.Q4_0, ro.Q8_0])
