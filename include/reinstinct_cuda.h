@@ -123,6 +123,20 @@ int rc_matvec_f32(void *stream, int ggml_type, const void *w, const float *x, fl
 int rc_matvec_block_dots(void *stream, int ggml_type, const void *w, const void *xq,
                          int32_t *idots, uint32_t in_dim, uint32_t out_dim, uint32_t n_rows);
 
+/* Measurement aid: overrides the matvec launch heuristics for the calling process (ks =
+ * warps that split one weight row, grid_mult = CTAs launched per resident CTA slot; 0 restores
+ * the heuristic).  No counterpart in the reference, whose geometry is fixed in its wrappers
+ * (src/runtime/gemma4.rs:1530-1551). */
+void rc_tune_matvec(int ks, int grid_mult);
+/* Measurement aid: force_dp4a != 0 sends rc_mmq_gemm through the dp4a kernel instead of the
+ * tensor-core kernel, for A/B timing of the two. */
+void rc_tune_mmq(int force_dp4a);
+/* Reads (synchronously) the device-side status word: 0, or the code of the bounded wait that
+ * gave up inside the tensor-core GEMM.  A nonzero value means the affected outputs are invalid;
+ * the context stays usable.  hipDeviceSynchronize + error check in the reference's tests
+ * (src/runtime/kernels.rs) is the nearest counterpart. */
+int rc_device_status(unsigned int *status);
+
 /* ---- int8 MMQ GEMM --------------------------------------------------------------------- */
 
 /* matmul_mmq_into's kernel launch (src/runtime/prefill.rs:512-567), bmm_mmq

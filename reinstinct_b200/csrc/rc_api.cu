@@ -208,7 +208,7 @@ int rc_matmul(void *stream, int type, const void *w, const float *x, float *y, u
     return launch_mmq_gemm(S(stream), type, w, xq_scratch, y, in_dim, out_dim, n_rows);
 }
 
-uint32_t rc_moe_tile_bn(void) { return mmq_grouped_bn(); }
+uint32_t rc_moe_tile_bn(void) { return matvec_grouped_bn(); }
 
 int rc_moe_sort(void *stream, const int32_t *ids, uint32_t n_entries, uint32_t n_expert,
                 uint32_t bn, int32_t *count, int32_t *cursor, int32_t *expert_off,
@@ -396,20 +396,12 @@ int rc_graph_exec_destroy(void *graph_exec) { return (int)cudaGraphExecDestroy((
 } // extern "C"
 
 namespace rc {
-void matvec_set_tuning(int rows, int threads, int ctas_per_sm);
-void matvec_set_pipe_tuning(int rows_per_stage, int stages, int cwarps, int ctas_per_sm, int disable);
-int matvec_device_error(unsigned int *out);
+void matvec_set_tuning(int ks, int grid_mult);
 } // namespace rc
-extern "C" void rc_tune_matvec(int rows, int threads, int ctas_per_sm)
-{
-    rc::matvec_set_tuning(rows, threads, ctas_per_sm);
-}
-extern "C" void rc_tune_matvec_pipe(int rows_per_stage, int stages, int cwarps, int ctas_per_sm, int disable)
-{
-    rc::matvec_set_pipe_tuning(rows_per_stage, stages, cwarps, ctas_per_sm, disable);
-}
+extern "C" void rc_tune_matvec(int ks, int grid_mult) { rc::matvec_set_tuning(ks, grid_mult); }
+extern "C" void rc_tune_mmq(int force_dp4a) { rc::mmq_force_dp4a(force_dp4a); }
 extern "C" int rc_device_status(unsigned int *status)
 {
     if (!status) return RC_ERR_NULL_POINTER;
-    return rc::matvec_device_error(status);
+    return rc::mmq_device_error(status);
 }

@@ -32,6 +32,9 @@ int launch_mmq_grouped(cudaStream_t s, int type, const void *slab, size_t bytes_
                        uint32_t n_entries);
 int mmq_set_attributes();
 uint32_t mmq_grouped_bn();
+uint32_t matvec_grouped_bn();
+void mmq_force_dp4a(int on);
+int mmq_device_error(unsigned int *out);
 
 int launch_moe_sort(cudaStream_t s, const int32_t *ids, uint32_t n_entries, uint32_t n_expert,
                     uint32_t bn, int32_t *count, int32_t *cursor, int32_t *expert_off,

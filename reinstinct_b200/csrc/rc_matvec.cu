@@ -8,15 +8,30 @@
 //   Q8_0   kernels/matvec_q8_0_repacked.cpp:77-86     dw*dx*idot
 //   Q4_0   kernels/matvec_q4_0_repacked.cpp:84-111    dw*dx*(idot - 8*sum(xq))
 //   IQ4_XS kernels/matvec_iq4xs_repacked.cpp:104-116  dw*dx*sum(LUT[q]*xq)
-// and of their _batched forms (kernels/matvec_q4k_repacked_batched.cpp:107-126).
+// and of their _batched forms (kernels/matvec_q4k_repacked_batched.cpp:107-126).  The
+// per-block integers are formed exactly as there; the f32 factors are associated slightly
+// differently (one rounding of d*dx, one of (float)(sc*idot)), far inside the 1e-3 bound.
 //
-// How it runs on B200 is not the reference's Wave64 scheme.  The kernel is HBM-bound, so
-// the design is about bytes in flight: a CTA stages the BlockQ8 activations once into
-// shared memory in planar form (two 16-byte halves, scale/sum pair, integer half sums), then
-// each warp streams whole weight rows with 128-bit non-allocating loads — lane l owns
-// sub-blocks l, l+32, ... of the row, so one warp instruction reads 512 contiguous bytes of
-// the nibble plane — issues every plane load of ROWS rows before the first dot, and reduces
-// with five shuffles per output.  CTAs are persistent over row groups.
+// How it runs on B200 is not the reference's Wave64 scheme.  The kernel is HBM-bound and
+// lasts a few microseconds, so the design is about bytes in flight and about starting early:
+//   - a CTA is 8 warps arranged as RB weight rows x KS splits of the row ("split-K" across
+//     warps, chosen on the host so that short-and-wide and long-and-narrow matrices both give
+//     every SM several waves of work); CTAs are persistent over row blocks;
+//   - lane l owns sub-blocks l, l+32, ... so one warp instruction reads 512 contiguous bytes
+//     of the nibble plane with 128-bit non-allocating loads; a warp issues the plane loads of
+//     a whole group of G such iterations into registers (2.5 KB and more in flight per warp, 32
+//     warps per SM) before the first dot, and issues the next group's loads before it reduces
+//     the finished one;
+//   - the first group's weight loads are issued before the activations are staged: weights
+//     never depend on the preceding kernel, activations do;
+//   - the BlockQ8 activations are staged once per CTA in shared memory in planar form (two
+//     16-byte halves, pre-scaled scale/sum pair, integer half sums), so the inner loop reads
+//     them with conflict-free 128-bit loads.
+// A shared-memory ring filled by cp.async.bulk with a producer warp was built and measured
+// first: 12.3 us on the 5120->17408 Q4_K matrix against 9.9 us for this form (a plain read of
+// the same bytes takes 8.7 us), so the ring is not used.
+#include <type_traits>
+
 #include "rc_common.cuh"
 #include "rc_internal.h"
 
@@ -24,272 +39,45 @@ namespace rc {
 
 namespace {
 
-// Staged activations: [n_rows][chunk] arrays, sub-block index fastest, so a warp's reads
-// are conflict-free 16-byte (or 8-byte) rows.
+constexpr size_t kMaxStageBytesHost = 200 * 1024;
+constexpr int kWarpsPerCta = 8;
+
+template <int FMT> struct FmtTraits {
+    // integer half sums of the activation block are needed for the "-32" / "-8" offsets
+    static constexpr bool needs_is = (FMT == Q6_K || FMT == Q4_0);
+    static constexpr uint32_t x_bytes = needs_is ? 48 : 40; // staged bytes per activation block
+    // iterations (32 sub-blocks each) whose raw weight registers a warp holds at once
+    static constexpr int G = (FMT == Q8_0) ? 3 : (FMT == Q5_K || FMT == Q6_K || FMT == IQ4_XS) ? 4 : 5;
+};
+
+// Staged activations: [n_rows][n_sub] arrays, sub-block index fastest, so a warp's reads are
+// conflict-free 16-byte (or 8-byte) rows.
 struct XStage {
     int4 *lo, *hi;
     float2 *ds;
     int2 *is;
 };
 
-__device__ __forceinline__ XStage carve_stage(uint8_t *smem, uint32_t n_rows, uint32_t chunk)
+template <int FMT>
+__device__ __forceinline__ XStage carve_stage(uint8_t *smem, uint32_t n_blocks)
 {
     XStage s;
-    const size_t n = (size_t)n_rows * chunk;
     s.lo = reinterpret_cast<int4 *>(smem);
-    s.hi = s.lo + n;
-    s.ds = reinterpret_cast<float2 *>(s.hi + n);
-    s.is = reinterpret_cast<int2 *>(s.ds + n);
+    s.hi = s.lo + n_blocks;
+    s.ds = reinterpret_cast<float2 *>(s.hi + n_blocks);
+    s.is = reinterpret_cast<int2 *>(s.ds + n_blocks);
     return s;
 }
 
-constexpr size_t kStageBytesPerBlock = 16 + 16 + 8 + 8;
-constexpr size_t kMaxStageBytesHost = 200 * 1024;
-
-// Weight registers of one (row, sub-block) and the math on them -----------------------------
-
-template <int FMT> struct WBlk;
-
-// Weight-plane loads: SM = false streams from global memory (non-allocating), SM = true
-// reads the copy a bulk-async stage holds in shared memory.
-template <bool SM> __device__ __forceinline__ uint4 ldw_u4(const uint8_t *p)
+// Stages n_blocks BlockQ8 blocks.  What is stored is arranged for the consumer math below:
+//   Q4_K, Q4_0  ds.x = d/16 (their dots are formed 16x too large, see dot_nibbles16)
+//   Q4_K, Q5_K  ds.y = -xsum (the min term is added with one FMA)
+//   Q6_K        is = (32*sum(lo half), 32*sum(hi half));   Q4_0  is.x = 128*sum(all)
+//   IQ4_XS      quants permuted into iq4_lookup8 order
+template <int FMT>
+__device__ __forceinline__ void stage_x(const XStage &st, const uint8_t *__restrict__ xq, uint32_t n_blocks)
 {
-    if (SM) return *reinterpret_cast<const uint4 *>(p);
-    return ld_stream_u4(p);
-}
-template <bool SM> __device__ __forceinline__ uint2 ldw_u2(const uint8_t *p)
-{
-    if (SM) return *reinterpret_cast<const uint2 *>(p);
-    return ld_stream_u2(p);
-}
-template <bool SM> __device__ __forceinline__ uint32_t ldw_u32(const uint8_t *p)
-{
-    if (SM) return *reinterpret_cast<const uint32_t *>(p);
-    return ld_stream_u32(p);
-}
-template <bool SM> __device__ __forceinline__ uint32_t ldw_u16(const uint8_t *p)
-{
-    if (SM) return (uint32_t)*reinterpret_cast<const unsigned short *>(p);
-    return ld_nc_u16(p);
-}
-// d|dmin word of a superblock; in global memory its plane base may be only 2-byte aligned
-template <bool SM> __device__ __forceinline__ uint32_t ld_sup32(const uint8_t *p, bool aligned4)
-{
-    if (SM) return *reinterpret_cast<const uint32_t *>(p);
-    if (aligned4) return __ldg(reinterpret_cast<const uint32_t *>(p));
-    return ld_nc_u16(p) | (ld_nc_u16(p + 2) << 16);
-}
-
-__device__ __forceinline__ int dot_nibbles(const uint4 &q, const int4 &lo, const int4 &hi)
-{
-    const uint32_t M = 0x0F0F0F0Fu;
-    int a = 0;
-    a = __dp4a((int)(q.x & M), lo.x, a);
-    a = __dp4a((int)((q.x >> 4) & M), hi.x, a);
-    a = __dp4a((int)(q.y & M), lo.y, a);
-    a = __dp4a((int)((q.y >> 4) & M), hi.y, a);
-    a = __dp4a((int)(q.z & M), lo.z, a);
-    a = __dp4a((int)((q.z >> 4) & M), hi.z, a);
-    a = __dp4a((int)(q.w & M), lo.w, a);
-    a = __dp4a((int)((q.w >> 4) & M), hi.w, a);
-    return a;
-}
-
-template <> struct WBlk<Q4_K> {
-    uint4 q;
-    float dsc, deff;
-    template <bool SM> __device__ __forceinline__ void load(const Planes &p, size_t idx, size_t sup, bool a4)
-    {
-        q = ldw_u4<SM>(p.nib + idx * 16);
-        const uint32_t sm = ldw_u16<SM>(p.sc + idx * 2);
-        const uint32_t dd = ld_sup32<SM>(p.sup + sup * 4, a4);
-        dsc = f16_bits_to_f32(dd) * (float)(sm & 0xFFu);
-        deff = f16_bits_to_f32(dd >> 16) * (float)(sm >> 8);
-    }
-    __device__ __forceinline__ float term(const int4 &lo, const int4 &hi, float2 ds, int2,
-                                          int &i0, int &i1) const
-    {
-        i0 = dot_nibbles(q, lo, hi);
-        i1 = 0;
-        return dsc * ds.x * (float)i0 - deff * ds.y;
-    }
-};
-
-template <> struct WBlk<Q5_K> {
-    uint4 lo4, hi4; // the eight expanded 5-bit words: lo4 = weights 0..15, hi4 = 16..31
-    float dsc, deff;
-    template <bool SM> __device__ __forceinline__ void load(const Planes &p, size_t idx, size_t sup, bool a4)
-    {
-        const uint4 q = ldw_u4<SM>(p.nib + idx * 16);
-        const uint32_t qh = ldw_u32<SM>(p.aux + idx * 4);
-        const uint32_t sm = ldw_u16<SM>(p.sc + idx * 2);
-        const uint32_t dd = ld_sup32<SM>(p.sup + sup * 4, a4);
-        const uint32_t M = 0x0F0F0F0Fu;
-        // bit 4g+c of qh is the 5th bit of weight c of group g; group 2j pairs with the
-        // low nibbles of word j, group 2j+1 with the high nibbles (src/quant/q5_k.rs:134-137)
-        lo4.x = (q.x & M) | bits4_to_bit4(qh);
-        hi4.x = ((q.x >> 4) & M) | bits4_to_bit4(qh >> 4);
-        lo4.y = (q.y & M) | bits4_to_bit4(qh >> 8);
-        hi4.y = ((q.y >> 4) & M) | bits4_to_bit4(qh >> 12);
-        lo4.z = (q.z & M) | bits4_to_bit4(qh >> 16);
-        hi4.z = ((q.z >> 4) & M) | bits4_to_bit4(qh >> 20);
-        lo4.w = (q.w & M) | bits4_to_bit4(qh >> 24);
-        hi4.w = ((q.w >> 4) & M) | bits4_to_bit4(qh >> 28);
-        dsc = f16_bits_to_f32(dd) * (float)(sm & 0xFFu);
-        deff = f16_bits_to_f32(dd >> 16) * (float)(sm >> 8);
-    }
-    __device__ __forceinline__ float term(const int4 &lo, const int4 &hi, float2 ds, int2,
-                                          int &i0, int &i1) const
-    {
-        int a = 0;
-        a = __dp4a((int)lo4.x, lo.x, a);
-        a = __dp4a((int)hi4.x, hi.x, a);
-        a = __dp4a((int)lo4.y, lo.y, a);
-        a = __dp4a((int)hi4.y, hi.y, a);
-        a = __dp4a((int)lo4.z, lo.z, a);
-        a = __dp4a((int)hi4.z, hi.z, a);
-        a = __dp4a((int)lo4.w, lo.w, a);
-        a = __dp4a((int)hi4.w, hi.w, a);
-        i0 = a;
-        i1 = 0;
-        return dsc * ds.x * (float)a - deff * ds.y;
-    }
-};
-
-template <> struct WBlk<Q6_K> {
-    uint4 lo6, hi6; // expanded 6-bit words, unsigned 0..63
-    float dlo, dhi;
-    template <bool SM> __device__ __forceinline__ void load(const Planes &p, size_t idx, size_t sup, bool)
-    {
-        const uint4 q = ldw_u4<SM>(p.nib + idx * 16);
-        const uint2 h = ldw_u2<SM>(p.aux + idx * 8);
-        const uint32_t sm = ldw_u16<SM>(p.sc + idx * 2);
-        const float d = f16_bits_to_f32(ldw_u16<SM>(p.sup + sup * 2));
-        const uint32_t M = 0x0F0F0F0Fu;
-        // byte g of the high-2 plane belongs to group g (src/quant/q6_k.rs:128-133)
-        lo6.x = (q.x & M) | fields2_to_bits45(h.x & 0xFFu);
-        hi6.x = ((q.x >> 4) & M) | fields2_to_bits45((h.x >> 8) & 0xFFu);
-        lo6.y = (q.y & M) | fields2_to_bits45((h.x >> 16) & 0xFFu);
-        hi6.y = ((q.y >> 4) & M) | fields2_to_bits45(h.x >> 24);
-        lo6.z = (q.z & M) | fields2_to_bits45(h.y & 0xFFu);
-        hi6.z = ((q.z >> 4) & M) | fields2_to_bits45((h.y >> 8) & 0xFFu);
-        lo6.w = (q.w & M) | fields2_to_bits45((h.y >> 16) & 0xFFu);
-        hi6.w = ((q.w >> 4) & M) | fields2_to_bits45(h.y >> 24);
-        dlo = d * (float)(int)(int8_t)(sm & 0xFFu);
-        dhi = d * (float)(int)(int8_t)(sm >> 8);
-    }
-    __device__ __forceinline__ float term(const int4 &lo, const int4 &hi, float2 ds, int2 is,
-                                          int &i0, int &i1) const
-    {
-        int a = 0, b = 0;
-        a = __dp4a((int)lo6.x, lo.x, a);
-        b = __dp4a((int)hi6.x, hi.x, b);
-        a = __dp4a((int)lo6.y, lo.y, a);
-        b = __dp4a((int)hi6.y, hi.y, b);
-        a = __dp4a((int)lo6.z, lo.z, a);
-        b = __dp4a((int)hi6.z, hi.z, b);
-        a = __dp4a((int)lo6.w, lo.w, a);
-        b = __dp4a((int)hi6.w, hi.w, b);
-        i0 = a - 32 * is.x;
-        i1 = b - 32 * is.y;
-        return dlo * ds.x * (float)i0 + dhi * ds.x * (float)i1;
-    }
-};
-
-template <> struct WBlk<Q8_0> {
-    uint4 wl, wh;
-    float dw;
-    template <bool SM> __device__ __forceinline__ void load(const Planes &p, size_t idx, size_t, bool)
-    {
-        wl = ldw_u4<SM>(p.nib + idx * 16);
-        wh = ldw_u4<SM>(p.aux + idx * 16);
-        dw = f16_bits_to_f32(ldw_u16<SM>(p.sc + idx * 2));
-    }
-    __device__ __forceinline__ float term(const int4 &lo, const int4 &hi, float2 ds, int2,
-                                          int &i0, int &i1) const
-    {
-        int a = 0;
-        a = __dp4a((int)wl.x, lo.x, a);
-        a = __dp4a((int)wl.y, lo.y, a);
-        a = __dp4a((int)wl.z, lo.z, a);
-        a = __dp4a((int)wl.w, lo.w, a);
-        a = __dp4a((int)wh.x, hi.x, a);
-        a = __dp4a((int)wh.y, hi.y, a);
-        a = __dp4a((int)wh.z, hi.z, a);
-        a = __dp4a((int)wh.w, hi.w, a);
-        i0 = a;
-        i1 = 0;
-        return dw * ds.x * (float)a;
-    }
-};
-
-template <> struct WBlk<Q4_0> {
-    uint4 q;
-    float dw;
-    template <bool SM> __device__ __forceinline__ void load(const Planes &p, size_t idx, size_t, bool)
-    {
-        q = ldw_u4<SM>(p.nib + idx * 16);
-        dw = f16_bits_to_f32(ldw_u16<SM>(p.sc + idx * 2));
-    }
-    __device__ __forceinline__ float term(const int4 &lo, const int4 &hi, float2 ds, int2 is,
-                                          int &i0, int &i1) const
-    {
-        i0 = dot_nibbles(q, lo, hi) - 8 * (is.x + is.y);
-        i1 = 0;
-        return dw * ds.x * (float)i0;
-    }
-};
-
-template <> struct WBlk<IQ4_XS> {
-    int4 a, b; // codebook values in iq4_lookup8 order: a = words 0,1; b = words 2,3
-    float dw;
-    template <bool SM> __device__ __forceinline__ void load(const Planes &p, size_t idx, size_t, bool)
-    {
-        const uint4 q = ldw_u4<SM>(p.nib + idx * 16);
-        dw = f16_bits_to_f32(ldw_u16<SM>(p.sc + idx * 2));
-        iq4_lookup8(q.x, a.x, a.y);
-        iq4_lookup8(q.y, a.z, a.w);
-        iq4_lookup8(q.z, b.x, b.y);
-        iq4_lookup8(q.w, b.z, b.w);
-    }
-    // lo/hi hold the activations already permuted by xperm_iq4 at staging time.
-    __device__ __forceinline__ float term(const int4 &lo, const int4 &hi, float2 ds, int2,
-                                          int &i0, int &i1) const
-    {
-        int s = 0;
-        s = __dp4a(a.x, lo.x, s);
-        s = __dp4a(a.y, lo.y, s);
-        s = __dp4a(a.z, lo.z, s);
-        s = __dp4a(a.w, lo.w, s);
-        s = __dp4a(b.x, hi.x, s);
-        s = __dp4a(b.y, hi.y, s);
-        s = __dp4a(b.z, hi.z, s);
-        s = __dp4a(b.w, hi.w, s);
-        i0 = s;
-        i1 = 0;
-        return dw * ds.x * (float)s;
-    }
-};
-
-// --------------------------------------------------------------------------------------------
-
-// NB    compile-time bound on activation rows (n_rows <= NB)
-// ROWS  weight rows a warp streams together
-// DUMP  also write the per-block integers (debug entry point)
-template <int FMT, int NB, int ROWS, bool DUMP>
-__device__ __forceinline__ void
-matvec_body(uint8_t *smem, const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq,
-            float *__restrict__ y, int32_t *__restrict__ idots, uint32_t in_dim, uint32_t out_dim,
-            uint32_t n_rows, uint32_t group_begin, uint32_t group_stride)
-{
-    const uint32_t n_sub = in_dim >> 5;
-    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-    const Planes p = planes_of<FMT>(w, in_dim, out_dim);
-    const bool sup_a4 = (reinterpret_cast<uintptr_t>(p.sup) & 3u) == 0;
-    const XStage st = carve_stage(smem, n_rows, n_sub);
-
-    // Stage every activation block once per CTA.
-    for (uint32_t i = threadIdx.x; i < n_rows * n_sub; i += blockDim.x) {
+    for (uint32_t i = threadIdx.x; i < n_blocks; i += blockDim.x) {
         XBlock x = load_blockq8(xq + (size_t)i * RC_BLOCKQ8_BYTES);
         if (FMT == IQ4_XS) {
             int4 a, b;
@@ -302,76 +90,353 @@ matvec_body(uint8_t *smem, const uint8_t *__restrict__ w, const uint8_t *__restr
         }
         st.lo[i] = x.lo;
         st.hi[i] = x.hi;
-        st.ds[i] = make_float2(x.d, x.xsum);
-        st.is[i] = make_int2(x.s_lo, x.s_hi);
+        const float dscale = (FMT == Q4_K || FMT == Q4_0) ? 0.0625f : 1.0f;
+        const float ssign = (FMT == Q4_K || FMT == Q5_K) ? -1.0f : 1.0f;
+        st.ds[i] = make_float2(x.d * dscale, x.xsum * ssign);
+        if (FMT == Q6_K) st.is[i] = make_int2(32 * x.s_lo, 32 * x.s_hi);
+        if (FMT == Q4_0) st.is[i] = make_int2(128 * (x.s_lo + x.s_hi), 0);
     }
+}
+
+// ---- raw weight registers of one (row, sub-block) ---------------------------------------------
+// fetch() only loads, so a warp can issue the loads of a whole group before any of them is used.
+
+template <int FMT> struct Raw;
+template <> struct Raw<Q4_K> { uint4 q; uint32_t sm, dd; };
+template <> struct Raw<Q5_K> { uint4 q; uint32_t qh, sm, dd; };
+template <> struct Raw<Q6_K> { uint4 q; uint2 h; uint32_t sm, d; };
+template <> struct Raw<Q8_0> { uint4 wl, wh; uint32_t d; };
+template <> struct Raw<Q4_0> { uint4 q; uint32_t d; };
+template <> struct Raw<IQ4_XS> { uint4 q; uint32_t d; };
+
+// d|dmin word of a superblock; the plane base may be only 2-byte aligned
+__device__ __forceinline__ uint32_t ld_sup32(const uint8_t *p, bool aligned4)
+{
+    if (aligned4) return __ldg(reinterpret_cast<const uint32_t *>(p));
+    return ld_nc_u16(p) | (ld_nc_u16(p + 2) << 16);
+}
+
+template <int FMT>
+__device__ __forceinline__ void fetch(Raw<FMT> &r, const Planes &p, size_t idx, size_t sup, bool a4)
+{
+    if constexpr (FMT == Q4_K) {
+        r.q = ld_stream_u4(p.nib + idx * 16);
+        r.sm = ld_nc_u16(p.sc + idx * 2);
+        r.dd = ld_sup32(p.sup + sup * 4, a4);
+    } else if constexpr (FMT == Q5_K) {
+        r.q = ld_stream_u4(p.nib + idx * 16);
+        r.qh = ld_stream_u32(p.aux + idx * 4);
+        r.sm = ld_nc_u16(p.sc + idx * 2);
+        r.dd = ld_sup32(p.sup + sup * 4, a4);
+    } else if constexpr (FMT == Q6_K) {
+        r.q = ld_stream_u4(p.nib + idx * 16);
+        r.h = ld_stream_u2(p.aux + idx * 8);
+        r.sm = ld_nc_u16(p.sc + idx * 2);
+        r.d = ld_nc_u16(p.sup + sup * 2);
+    } else if constexpr (FMT == Q8_0) {
+        r.wl = ld_stream_u4(p.nib + idx * 16);
+        r.wh = ld_stream_u4(p.aux + idx * 16);
+        r.d = ld_nc_u16(p.sc + idx * 2);
+    } else {
+        r.q = ld_stream_u4(p.nib + idx * 16);
+        r.d = ld_nc_u16(p.sc + idx * 2);
+    }
+}
+
+// unsigned bytes x signed bytes
+__device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c)
+{
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// 16 x the dot of 32 unsigned nibbles with the activation quants: the high nibbles are used in
+// place as unsigned bytes 16*nibble (one AND instead of shift + AND), the low-nibble dot is
+// scaled by 16 once at the end.  Exact: |result| <= 16*32*15*127 < 2^20.
+__device__ __forceinline__ int dot_nibbles16(const uint4 &q, const int4 &xl, const int4 &xh)
+{
+    const uint32_t M = 0x0F0F0F0Fu, H = 0xF0F0F0F0u;
+    int lo = 0, hi = 0;
+    lo = __dp4a((int)(q.x & M), xl.x, lo);
+    hi = dp4a_us(q.x & H, xh.x, hi);
+    lo = __dp4a((int)(q.y & M), xl.y, lo);
+    hi = dp4a_us(q.y & H, xh.y, hi);
+    lo = __dp4a((int)(q.z & M), xl.z, lo);
+    hi = dp4a_us(q.z & H, xh.z, hi);
+    lo = __dp4a((int)(q.w & M), xl.w, lo);
+    hi = dp4a_us(q.w & H, xh.w, hi);
+    return lo * 16 + hi;
+}
+
+// Exact float of an integer 0..255 without the conversion unit.
+__device__ __forceinline__ float small_uint_to_float(uint32_t v)
+{
+    return __uint_as_float(0x4B000000u | v) - 8388608.0f;
+}
+
+// One (weight row, sub-block) against one activation block: the f32 term, and the block
+// integers i0/i1 (i1 is the second 16-weight half, Q6_K only).
+template <int FMT>
+__device__ __forceinline__ float term(const Raw<FMT> &r, const int4 &xl, const int4 &xh, float2 ds,
+                                      int2 is, int &i0, int &i1)
+{
+    const uint32_t M = 0x0F0F0F0Fu;
+    i1 = 0;
+    if constexpr (FMT == Q4_K) {
+        const int idot16 = dot_nibbles16(r.q, xl, xh);
+        i0 = idot16 >> 4;
+        const float d = f16_bits_to_f32(r.dd), dmin = f16_bits_to_f32(r.dd >> 16);
+        const int sc = (int)(r.sm & 0xFFu);
+        float t = (d * ds.x) * (float)(sc * idot16);
+        return fmaf(dmin * ds.y, small_uint_to_float(r.sm >> 8), t);
+    } else if constexpr (FMT == Q5_K) {
+        // bit 4g+c of qh is the 5th bit of weight c of group g; group 2j pairs with the low
+        // nibbles of word j, group 2j+1 with the high nibbles (src/quant/q5_k.rs:134-137)
+        const uint4 q = r.q;
+        const uint32_t qh = r.qh;
+        int s = 0, t = 0;
+        s = __dp4a((int)((q.x & M) | bits4_to_bit4(qh)), xl.x, s);
+        t = __dp4a((int)(((q.x >> 4) & M) | bits4_to_bit4(qh >> 4)), xh.x, t);
+        s = __dp4a((int)((q.y & M) | bits4_to_bit4(qh >> 8)), xl.y, s);
+        t = __dp4a((int)(((q.y >> 4) & M) | bits4_to_bit4(qh >> 12)), xh.y, t);
+        s = __dp4a((int)((q.z & M) | bits4_to_bit4(qh >> 16)), xl.z, s);
+        t = __dp4a((int)(((q.z >> 4) & M) | bits4_to_bit4(qh >> 20)), xh.z, t);
+        s = __dp4a((int)((q.w & M) | bits4_to_bit4(qh >> 24)), xl.w, s);
+        t = __dp4a((int)(((q.w >> 4) & M) | bits4_to_bit4(qh >> 28)), xh.w, t);
+        i0 = s + t;
+        const float d = f16_bits_to_f32(r.dd), dmin = f16_bits_to_f32(r.dd >> 16);
+        const int sc = (int)(r.sm & 0xFFu);
+        float v = (d * ds.x) * (float)(sc * i0);
+        return fmaf(dmin * ds.y, small_uint_to_float(r.sm >> 8), v);
+    } else if constexpr (FMT == Q6_K) {
+        // byte g of the high-2 plane belongs to group g (src/quant/q6_k.rs:128-133)
+        const uint4 q = r.q;
+        const uint2 h = r.h;
+        int s = 0, t = 0;
+        s = __dp4a((int)((q.x & M) | fields2_to_bits45(h.x & 0xFFu)), xl.x, s);
+        t = __dp4a((int)(((q.x >> 4) & M) | fields2_to_bits45((h.x >> 8) & 0xFFu)), xh.x, t);
+        s = __dp4a((int)((q.y & M) | fields2_to_bits45((h.x >> 16) & 0xFFu)), xl.y, s);
+        t = __dp4a((int)(((q.y >> 4) & M) | fields2_to_bits45(h.x >> 24)), xh.y, t);
+        s = __dp4a((int)((q.z & M) | fields2_to_bits45(h.y & 0xFFu)), xl.z, s);
+        t = __dp4a((int)(((q.z >> 4) & M) | fields2_to_bits45((h.y >> 8) & 0xFFu)), xh.z, t);
+        s = __dp4a((int)((q.w & M) | fields2_to_bits45((h.y >> 16) & 0xFFu)), xl.w, s);
+        t = __dp4a((int)(((q.w >> 4) & M) | fields2_to_bits45(h.y >> 24)), xh.w, t);
+        i0 = s - is.x;
+        i1 = t - is.y;
+        const int slo = (int)(int8_t)(r.sm & 0xFFu), shi = (int)(int8_t)(r.sm >> 8);
+        return (f16_bits_to_f32(r.d) * ds.x) * (float)(slo * i0 + shi * i1);
+    } else if constexpr (FMT == Q8_0) {
+        int s = 0, t = 0;
+        s = __dp4a((int)r.wl.x, xl.x, s);
+        t = __dp4a((int)r.wh.x, xh.x, t);
+        s = __dp4a((int)r.wl.y, xl.y, s);
+        t = __dp4a((int)r.wh.y, xh.y, t);
+        s = __dp4a((int)r.wl.z, xl.z, s);
+        t = __dp4a((int)r.wh.z, xh.z, t);
+        s = __dp4a((int)r.wl.w, xl.w, s);
+        t = __dp4a((int)r.wh.w, xh.w, t);
+        i0 = s + t;
+        return (f16_bits_to_f32(r.d) * ds.x) * (float)i0;
+    } else if constexpr (FMT == Q4_0) {
+        const int idot16 = dot_nibbles16(r.q, xl, xh) - is.x; // 16 * sum((q-8)*xq)
+        i0 = idot16 >> 4;
+        return (f16_bits_to_f32(r.d) * ds.x) * (float)idot16;
+    } else { // IQ4_XS, activations staged in iq4_lookup8 order
+        int c0, c1, c2, c3, c4, c5, c6, c7;
+        iq4_lookup8(r.q.x, c0, c1);
+        iq4_lookup8(r.q.y, c2, c3);
+        iq4_lookup8(r.q.z, c4, c5);
+        iq4_lookup8(r.q.w, c6, c7);
+        int s = 0, t = 0;
+        s = __dp4a(c0, xl.x, s);
+        t = __dp4a(c1, xl.y, t);
+        s = __dp4a(c2, xl.z, s);
+        t = __dp4a(c3, xl.w, t);
+        s = __dp4a(c4, xh.x, s);
+        t = __dp4a(c5, xh.y, t);
+        s = __dp4a(c6, xh.z, s);
+        t = __dp4a(c7, xh.w, t);
+        i0 = s + t;
+        return (f16_bits_to_f32(r.d) * ds.x) * (float)i0;
+    }
+}
+
+// --------------------------------------------------------------------------------------------
+// NB    compile-time bound on activation rows (n_rows <= NB)
+// DUMP  write the per-block integers instead of y (debug entry point)
+// ks    warps that split one weight row (1, 2, 4 or 8; ks <= iterations per row)
+// The CTA walks row blocks block_begin, block_begin + block_stride, ...
+// smem: staged activations (n_rows * n_sub * x_bytes), then 2 * warps * NB partial sums.
+template <int FMT, int NB, bool DUMP>
+__device__ __forceinline__ void
+stream_body(uint8_t *smem, const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq,
+            float *__restrict__ y, int32_t *__restrict__ idots, uint32_t in_dim, uint32_t out_dim,
+            uint32_t n_rows, uint32_t ks, uint32_t block_begin, uint32_t block_stride)
+{
+    constexpr int G = FmtTraits<FMT>::G;
+    const uint32_t n_sub = in_dim >> 5, n_iters = (n_sub + 31u) >> 5;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const uint32_t rb_rows = n_warps / ks, r_local = warp / ks, chunk = warp - r_local * ks;
+    const uint32_t it0 = chunk * n_iters / ks, it1 = (chunk + 1u) * n_iters / ks;
+    const uint32_t n_blocks = (out_dim + rb_rows - 1u) / rb_rows;
+    const Planes p = planes_of<FMT>(w, in_dim, out_dim);
+    const bool sup_a4 = (reinterpret_cast<uintptr_t>(p.sup) & 3u) == 0;
+    const uint32_t n_xblocks = n_rows * n_sub;
+    const XStage st = carve_stage<FMT>(smem, n_xblocks);
+    float *partial = reinterpret_cast<float *>(smem + (((size_t)n_xblocks * FmtTraits<FMT>::x_bytes + 15u) & ~(size_t)15u));
+
+    Raw<FMT> cur[G];
+    // A group of n <= G iterations in which every lane has a sub-block is compiled once per n
+    // without guards or clamps (the loads of a group must issue back to back); only the last
+    // group of a row whose sub-block count is not a multiple of 32 takes the guarded form.
+    auto lanes_full = [&](uint32_t it, uint32_t n) { return (it + n) * 32u <= n_sub; };
+    auto with_count = [&](uint32_t n, auto &&f) {
+        switch (n) {
+        case 1: f(std::integral_constant<int, 1>{}); break;
+        case 2: if constexpr (G >= 2) f(std::integral_constant<int, 2>{}); break;
+        case 3: if constexpr (G >= 3) f(std::integral_constant<int, 3>{}); break;
+        case 4: if constexpr (G >= 4) f(std::integral_constant<int, 4>{}); break;
+        default: if constexpr (G >= 5) f(std::integral_constant<int, 5>{}); break;
+        }
+    };
+    auto fetch_group = [&](uint32_t row, uint32_t it) {
+        // rows past the end are clamped: their loads stay legal, their results unused
+        row = min(row, out_dim - 1u);
+        const size_t rbase = (size_t)row * p.nsp, sbase = (size_t)row * p.n_super;
+        const uint32_t n = min((uint32_t)G, it1 - it);
+        if (lanes_full(it, n)) {
+            with_count(n, [&](auto nc) {
+#pragma unroll
+                for (int i = 0; i < decltype(nc)::value; i++) {
+                    const uint32_t sb = (it + i) * 32u + lane;
+                    fetch<FMT>(cur[i], p, rbase + sb, sbase + (sb >> 3), sup_a4);
+                }
+            });
+        } else {
+#pragma unroll
+            for (int i = 0; i < G; i++) {
+                if (it + i < it1) {
+                    const uint32_t sb = min((it + i) * 32u + lane, n_sub - 1u);
+                    fetch<FMT>(cur[i], p, rbase + sb, sbase + (sb >> 3), sup_a4);
+                }
+            }
+        }
+    };
+
+    uint32_t blk = block_begin, it = it0;
+    if (blk < n_blocks) fetch_group(blk * rb_rows + r_local, it); // weights do not wait for x
+    stage_x<FMT>(st, xq, n_xblocks);
     __syncthreads();
 
-    const uint32_t rows_per_cta = n_warps * ROWS;
-    const uint32_t n_groups = (out_dim + rows_per_cta - 1) / rows_per_cta;
-    for (uint32_t g = group_begin; g < n_groups; g += group_stride) {
-        const uint32_t row0 = g * rows_per_cta + warp * ROWS;
-        if (row0 >= out_dim) continue;
-        float acc[ROWS][NB];
+    float acc[NB];
 #pragma unroll
-        for (int r = 0; r < ROWS; r++)
-#pragma unroll
-            for (int b = 0; b < NB; b++) acc[r][b] = 0.0f;
+    for (int b = 0; b < NB; b++) acc[b] = 0.0f;
+    uint32_t parity = 0;
 
-        for (uint32_t sb = lane; sb < n_sub; sb += 32) {
-            WBlk<FMT> wb[ROWS];
+    while (blk < n_blocks) {
+        const uint32_t row = blk * rb_rows + r_local;
+        const uint32_t n_now = min((uint32_t)G, it1 - it);
+        if (lanes_full(it, n_now)) {
+            with_count(n_now, [&](auto nc) {
 #pragma unroll
-            for (int r = 0; r < ROWS; r++) {
-                // rows past the end are clamped: their loads stay legal, their results unused
-                const uint32_t row = min(row0 + r, out_dim - 1);
-                wb[r].template load<false>(p, (size_t)row * p.nsp + sb, (size_t)row * p.n_super + (sb >> 3), sup_a4);
-            }
+                for (int i = 0; i < decltype(nc)::value; i++) {
+                    const uint32_t sb = (it + i) * 32u + lane;
 #pragma unroll
-            for (int b = 0; b < NB; b++) {
-                if (b < (int)n_rows) {
-                    const uint32_t xi = b * n_sub + sb;
-                    const int4 lo = st.lo[xi], hi = st.hi[xi];
-                    const float2 ds = st.ds[xi];
-                    const int2 is = (FMT == Q6_K || FMT == Q4_0) ? st.is[xi] : make_int2(0, 0);
+                    for (int b = 0; b < NB; b++) {
+                        if (b < (int)n_rows) {
+                            const uint32_t xi = b * n_sub + sb;
+                            const int4 xl = st.lo[xi], xh = st.hi[xi];
+                            const float2 ds = st.ds[xi];
+                            const int2 is = FmtTraits<FMT>::needs_is ? st.is[xi] : make_int2(0, 0);
+                            int i0, i1;
+                            acc[b] += term<FMT>(cur[i], xl, xh, ds, is, i0, i1);
+                            if (DUMP && row < out_dim) {
+                                int32_t *o = idots + (((size_t)b * out_dim + row) * n_sub + sb) * 2;
+                                o[0] = i0;
+                                o[1] = i1;
+                            }
+                        }
+                    }
+                }
+            });
+        } else {
 #pragma unroll
-                    for (int r = 0; r < ROWS; r++) {
-                        int i0, i1;
-                        acc[r][b] += wb[r].term(lo, hi, ds, is, i0, i1);
-                        if (DUMP && row0 + r < out_dim) {
-                            int32_t *o = idots + (((size_t)b * out_dim + row0 + r) * n_sub + sb) * 2;
-                            o[0] = i0;
-                            o[1] = i1;
+            for (int i = 0; i < G; i++) {
+                if (it + i < it1) {
+                    const uint32_t sb_raw = (it + i) * 32u + lane;
+                    const bool valid = sb_raw < n_sub;
+                    const uint32_t sb = min(sb_raw, n_sub - 1u);
+#pragma unroll
+                    for (int b = 0; b < NB; b++) {
+                        if (b < (int)n_rows) {
+                            const uint32_t xi = b * n_sub + sb;
+                            const int4 xl = st.lo[xi], xh = st.hi[xi];
+                            const float2 ds = st.ds[xi];
+                            const int2 is = FmtTraits<FMT>::needs_is ? st.is[xi] : make_int2(0, 0);
+                            int i0, i1;
+                            const float t = term<FMT>(cur[i], xl, xh, ds, is, i0, i1);
+                            acc[b] += valid ? t : 0.0f;
+                            if (DUMP && valid && row < out_dim) {
+                                int32_t *o = idots + (((size_t)b * out_dim + row) * n_sub + sb) * 2;
+                                o[0] = i0;
+                                o[1] = i1;
+                            }
                         }
                     }
                 }
             }
         }
-#pragma unroll
-        for (int r = 0; r < ROWS; r++)
+        it += G;
+        const bool item_done = it >= it1;
+        const uint32_t nblk = item_done ? blk + block_stride : blk;
+        const uint32_t nit = item_done ? it0 : it;
+        if (nblk < n_blocks) fetch_group(nblk * rb_rows + r_local, nit); // in flight during the reduction
+        if (item_done) {
 #pragma unroll
             for (int b = 0; b < NB; b++) {
-                const float v = warp_sum(acc[r][b]);
-                if (!DUMP && lane == 0 && b < (int)n_rows && row0 + r < out_dim)
-                    y[(size_t)b * out_dim + row0 + r] = v;
+                const float v = warp_sum(acc[b]);
+                acc[b] = 0.0f;
+                if (DUMP) continue;
+                if (ks == 1) {
+                    if (lane == 0 && b < (int)n_rows && row < out_dim) y[(size_t)b * out_dim + row] = v;
+                } else if (lane == 0) {
+                    partial[(parity * n_warps + warp) * NB + b] = v;
+                }
             }
+            if (!DUMP && ks > 1) {
+                // every warp of the CTA finishes exactly one item per row block
+                __syncthreads();
+                if (chunk == 0 && lane < n_rows && row < out_dim) {
+                    float v = 0.0f;
+                    for (uint32_t c = 0; c < ks; c++) v += partial[(parity * n_warps + warp + c) * NB + lane];
+                    y[(size_t)lane * out_dim + row] = v;
+                }
+                parity ^= 1u;
+            }
+        }
+        blk = nblk;
+        it = nit;
     }
 }
 
-template <int FMT, int NB, int ROWS, bool DUMP>
-__global__ void __launch_bounds__(512)
-matvec_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq, float *__restrict__ y,
-              int32_t *__restrict__ idots, uint32_t in_dim, uint32_t out_dim, uint32_t n_rows)
+template <int NB> struct MinBlocks { static constexpr int v = NB <= 2 ? 4 : NB <= 4 ? 3 : 2; };
+
+template <int FMT, int NB, bool DUMP>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, MinBlocks<NB>::v)
+matvec_stream_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq, float *__restrict__ y,
+                     int32_t *__restrict__ idots, uint32_t in_dim, uint32_t out_dim, uint32_t n_rows,
+                     uint32_t ks)
 {
     extern __shared__ __align__(16) uint8_t smem[];
-    matvec_body<FMT, NB, ROWS, DUMP>(smem, w, xq, y, idots, in_dim, out_dim, n_rows, blockIdx.x,
-                                     gridDim.x);
+    stream_body<FMT, NB, DUMP>(smem, w, xq, y, idots, in_dim, out_dim, n_rows, ks, blockIdx.x, gridDim.x);
 }
 
 // Expert-grouped form: blockIdx.y is a global token tile, mapped to (expert, local tile) by
 // binary search over tile_off as in kernels/mmq_gemm_q4k_grouped.cpp:49-60; the tile's rows
 // of xq / y are contiguous in expert-sorted order.
 template <int FMT, int BN>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(kWarpsPerCta * 32, MinBlocks<BN>::v)
 matvec_grouped_kernel(const uint8_t *__restrict__ slab, size_t bytes_per_expert,
                       const int32_t *__restrict__ expert_off, const int32_t *__restrict__ tile_off,
                       uint32_t n_expert, const uint8_t *__restrict__ xq, float *__restrict__ y,
@@ -389,295 +454,49 @@ matvec_grouped_kernel(const uint8_t *__restrict__ slab, size_t bytes_per_expert,
     const uint32_t tok0 = (uint32_t)expert_off[e] + (by - (uint32_t)tile_off[e]) * BN;
     const uint32_t n = min((uint32_t)BN, (uint32_t)expert_off[e + 1] - tok0);
     const uint32_t n_sub = in_dim >> 5;
-    matvec_body<FMT, BN, 1, false>(smem, slab + (size_t)e * bytes_per_expert,
-                                   xq + (size_t)tok0 * n_sub * RC_BLOCKQ8_BYTES,
-                                   y + (size_t)tok0 * out_dim, nullptr, in_dim, out_dim, n,
-                                   blockIdx.x, gridDim.x);
-}
-
-
-// ---------------------------------------------------------------------------------------------
-// Bulk-async pipelined form (the decode fast path).
-//
-// A persistent CTA owns groups of R consecutive weight rows.  For R a multiple of 8 and
-// out_dim a multiple of 8, the R rows' share of every plane is one contiguous, 16-byte aligned
-// run of bytes, so a group is fetched by one cp.async.bulk per plane into a ring of shared
-// memory stages, completion counted on an mbarrier.  One elected producer thread keeps every
-// free stage in flight — the bytes in flight are bounded by shared memory (~190 KB per SM),
-// not by registers or occupancy, which is what an 8 us HBM-bound kernel needs.  Consumer
-// warps take one row each from a full stage, dot it against the staged activations and
-// release the stage.  Every wait is bounded: after kSpinLimit polls the kernel records an
-// error in g_pipe_error and returns (the context stays usable, the output is invalid).
-
-constexpr uint32_t kSpinLimit = 1u << 22; // ~4M polls with back-off, far beyond any legal wait
-__device__ unsigned int g_pipe_error;
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p)
-{
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// Bounded wait for the phase with the given parity; false if the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
-{
-    const uint32_t addr = smem_u32(bar);
-    for (uint32_t spin = 0; spin < kSpinLimit; spin++) {
-        uint32_t done;
-        asm volatile("{\n\t.reg .pred p;\n\t"
-                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                     "selp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(done)
-                     : "r"(addr), "r"(parity)
-                     : "memory");
-        if (done) return true;
-        if (spin > 64) __nanosleep(32);
-    }
-    return false;
-}
-__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-
-// Bytes of plane `k` (0 nib, 1 aux, 2 sc, 3 sup) per weight row.
-template <int FMT> __host__ __device__ inline uint32_t plane_row_bytes(int k, uint32_t nsp, uint32_t n_super)
-{
-    switch (k) {
-    case 0: return nsp * 16;
-    case 1: return FMT == Q5_K ? nsp * 4 : FMT == Q6_K ? nsp * 8 : FMT == Q8_0 ? nsp * 16 : 0;
-    case 2: return nsp * 2;
-    default: return (FMT == Q4_K || FMT == Q5_K) ? n_super * 4 : FMT == Q6_K ? n_super * 2 : 0;
-    }
-}
-
-template <int FMT> __host__ __device__ inline uint32_t row_bytes_all(uint32_t nsp, uint32_t n_super)
-{
-    return plane_row_bytes<FMT>(0, nsp, n_super) + plane_row_bytes<FMT>(1, nsp, n_super) +
-           plane_row_bytes<FMT>(2, nsp, n_super) + plane_row_bytes<FMT>(3, nsp, n_super);
-}
-
-// smem: [x stage][pad to 128][S stages of R*row_bytes][full[S], empty[S] barriers]
-template <int FMT, int NB>
-__global__ void __launch_bounds__(544)
-matvec_pipe_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq, float *__restrict__ y,
-                   uint32_t in_dim, uint32_t out_dim, uint32_t n_rows, uint32_t R, uint32_t S)
-{
-    extern __shared__ __align__(128) uint8_t smem[];
-    const uint32_t n_sub = in_dim >> 5;
-    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
-    const uint32_t n_cwarps = (blockDim.x >> 5) - 1; // the last warp is the producer
-    const Planes gp = planes_of<FMT>(w, in_dim, out_dim);
-    const uint32_t nsp = gp.nsp, n_super = gp.n_super;
-
-    const size_t x_bytes = ((size_t)n_rows * n_sub * kStageBytesPerBlock + 127) & ~(size_t)127;
-    const uint32_t rb[4] = {plane_row_bytes<FMT>(0, nsp, n_super), plane_row_bytes<FMT>(1, nsp, n_super),
-                            plane_row_bytes<FMT>(2, nsp, n_super), plane_row_bytes<FMT>(3, nsp, n_super)};
-    // plane offsets inside one stage; every plane's run of R rows is a multiple of 16 bytes
-    const uint32_t off1 = R * rb[0], off2 = off1 + R * rb[1], off3 = off2 + R * rb[2];
-    const uint32_t stage_bytes = (off3 + R * rb[3] + 127u) & ~127u;
-    uint8_t *stages = smem + x_bytes;
-    uint64_t *full = reinterpret_cast<uint64_t *>(stages + (size_t)S * stage_bytes);
-    uint64_t *empty = full + S;
-
-    if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < S; s++) {
-            mbar_init(full + s, 1);
-            mbar_init(empty + s, n_cwarps);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    __syncthreads();
-
-    const uint32_t n_groups = (out_dim + R - 1) / R;
-
-    if (warp == n_cwarps) {
-        // ---- producer: one thread keeps the ring full ----
-        if (lane == 0) {
-            const uint8_t *gbase[4] = {gp.nib, gp.aux, gp.sc, gp.sup};
-            uint32_t it = 0;
-            for (uint32_t g = blockIdx.x; g < n_groups; g += gridDim.x, it++) {
-                const uint32_t s = it % S;
-                if (it >= S && !mbar_wait(empty + s, ((it / S) - 1u) & 1u)) {
-                    atomicExch(&g_pipe_error, 1u);
-                    break;
-                }
-                const uint32_t r0 = g * R, nr = min(R, out_dim - r0);
-                uint8_t *dst = stages + (size_t)s * stage_bytes;
-                const uint32_t offs[4] = {0, off1, off2, off3};
-                uint32_t total = 0;
-#pragma unroll
-                for (int k = 0; k < 4; k++) total += nr * rb[k];
-                mbar_expect_tx(full + s, total);
-#pragma unroll
-                for (int k = 0; k < 4; k++)
-                    if (rb[k]) bulk_g2s(dst + offs[k], gbase[k] + (size_t)r0 * rb[k], nr * rb[k], full + s);
-            }
-        }
-        return;
-    }
-
-    // ---- consumers ----
-    const uint32_t n_cthreads = n_cwarps * 32;
-    const XStage st = carve_stage(smem, n_rows, n_sub);
-    for (uint32_t i = threadIdx.x; i < n_rows * n_sub; i += n_cthreads) {
-        XBlock x = load_blockq8(xq + (size_t)i * RC_BLOCKQ8_BYTES);
-        if (FMT == IQ4_XS) {
-            int4 a, b;
-            xperm_iq4(x.lo.x, x.hi.x, a.x, a.y);
-            xperm_iq4(x.lo.y, x.hi.y, a.z, a.w);
-            xperm_iq4(x.lo.z, x.hi.z, b.x, b.y);
-            xperm_iq4(x.lo.w, x.hi.w, b.z, b.w);
-            x.lo = a;
-            x.hi = b;
-        }
-        st.lo[i] = x.lo;
-        st.hi[i] = x.hi;
-        st.ds[i] = make_float2(x.d, x.xsum);
-        st.is[i] = make_int2(x.s_lo, x.s_hi);
-    }
-    asm volatile("bar.sync 1, %0;" ::"r"(n_cthreads) : "memory");
-
-    uint32_t it = 0;
-    for (uint32_t g = blockIdx.x; g < n_groups; g += gridDim.x, it++) {
-        const uint32_t s = it % S;
-        if (!mbar_wait(full + s, (it / S) & 1u)) {
-            atomicExch(&g_pipe_error, 2u);
-            return;
-        }
-        const uint8_t *sb_base = stages + (size_t)s * stage_bytes;
-        Planes sp;
-        sp.nib = sb_base;
-        sp.aux = sb_base + off1;
-        sp.sc = sb_base + off2;
-        sp.sup = sb_base + off3;
-        sp.nsp = nsp;
-        sp.n_super = n_super;
-        const uint32_t r0 = g * R, nr = min(R, out_dim - r0);
-        for (uint32_t r = warp; r < nr; r += n_cwarps) {
-            float acc[NB];
-#pragma unroll
-            for (int b = 0; b < NB; b++) acc[b] = 0.0f;
-#pragma unroll 5
-            for (uint32_t sb = lane; sb < n_sub; sb += 32) {
-                WBlk<FMT> wb;
-                wb.template load<true>(sp, (size_t)r * nsp + sb, (size_t)r * n_super + (sb >> 3), true);
-#pragma unroll
-                for (int b = 0; b < NB; b++) {
-                    if (b < (int)n_rows) {
-                        const uint32_t xi = b * n_sub + sb;
-                        const int2 is = (FMT == Q6_K || FMT == Q4_0) ? st.is[xi] : make_int2(0, 0);
-                        int i0, i1;
-                        acc[b] += wb.term(st.lo[xi], st.hi[xi], st.ds[xi], is, i0, i1);
-                    }
-                }
-            }
-#pragma unroll
-            for (int b = 0; b < NB; b++) {
-                const float v = warp_sum(acc[b]);
-                if (lane == 0 && b < (int)n_rows) y[(size_t)b * out_dim + r0 + r] = v;
-            }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty + s);
-    }
-}
-
-struct PipeTuning {
-    int rows_per_stage = 0, stages = 0, cwarps = 0, ctas_per_sm = 0, disable = 0;
-};
-PipeTuning g_pipe;
-
-template <int FMT, int NB>
-int launch_pipe(cudaStream_t s, const void *w, const void *xq, float *y, uint32_t in_dim,
-                uint32_t out_dim, uint32_t n_rows)
-{
-    const uint32_t n_sub = in_dim >> 5, nsp = nsp_of(n_sub), n_super = n_sub >> 3;
-    const uint32_t rowb = row_bytes_all<FMT>(nsp, n_super);
-    const size_t x_bytes = ((size_t)n_rows * n_sub * kStageBytesPerBlock + 127) & ~(size_t)127;
-    const size_t budget = 208 * 1024;
-    uint32_t ctas_per_sm = g_pipe.ctas_per_sm > 0 ? (uint32_t)g_pipe.ctas_per_sm : 1;
-    const size_t per_cta = budget / ctas_per_sm;
-    if (x_bytes + 2 * (size_t)8 * rowb + 256 > per_cta) return RC_ERR_TOO_MANY_ROWS; // caller uses the generic kernel
-    uint32_t R = g_pipe.rows_per_stage > 0 ? ((uint32_t)g_pipe.rows_per_stage + 7u) & ~7u : 8;
-    const uint32_t stage_bytes = (R * rowb + 127u) & ~127u;
-    uint32_t S = (uint32_t)((per_cta - x_bytes - 256) / stage_bytes);
-    if (g_pipe.stages > 0) S = min(S, (uint32_t)g_pipe.stages);
-    S = min(S, 16u);
-    if (S < 2) {
-        R = 8;
-        S = (uint32_t)((per_cta - x_bytes - 256) / ((8 * rowb + 127u) & ~127u));
-        if (S < 2) return RC_ERR_TOO_MANY_ROWS;
-    }
-    const uint32_t cwarps = g_pipe.cwarps > 0 ? min((uint32_t)g_pipe.cwarps, 16u) : min(R, 16u);
-    const uint32_t n_groups = (out_dim + R - 1) / R;
-    const uint32_t grid = min(n_groups, (uint32_t)sm_count() * ctas_per_sm);
-    const size_t smem = x_bytes + (size_t)S * ((R * rowb + 127u) & ~127u) + 2 * S * sizeof(uint64_t);
-    matvec_pipe_kernel<FMT, NB><<<grid, (cwarps + 1) * 32, smem, s>>>(
-        (const uint8_t *)w, (const uint8_t *)xq, y, in_dim, out_dim, n_rows, R, S);
-    return (int)cudaGetLastError();
-}
-
-// The pipelined kernel needs every plane's per-group run to start on a 16-byte boundary.
-inline bool pipe_eligible(const void *w, uint32_t out_dim, uint32_t n_rows)
-{
-    return !g_pipe.disable && out_dim % 8 == 0 && n_rows <= 4 && ((uintptr_t)w & 15u) == 0;
-}
-
-template <int FMT>
-int launch_pipe_fmt(cudaStream_t s, const void *w, const void *xq, float *y, uint32_t in_dim,
-                    uint32_t out_dim, uint32_t n_rows)
-{
-    if (n_rows == 1) return launch_pipe<FMT, 1>(s, w, xq, y, in_dim, out_dim, n_rows);
-    if (n_rows == 2) return launch_pipe<FMT, 2>(s, w, xq, y, in_dim, out_dim, n_rows);
-    return launch_pipe<FMT, 4>(s, w, xq, y, in_dim, out_dim, n_rows);
-}
-
-template <int FMT> int set_attr_pipe()
-{
-    int rc = 0;
-    rc |= (int)cudaFuncSetAttribute(matvec_pipe_kernel<FMT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-    rc |= (int)cudaFuncSetAttribute(matvec_pipe_kernel<FMT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-    rc |= (int)cudaFuncSetAttribute(matvec_pipe_kernel<FMT, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-    return rc;
+    stream_body<FMT, BN, false>(smem, slab + (size_t)e * bytes_per_expert,
+                                xq + (size_t)tok0 * n_sub * RC_BLOCKQ8_BYTES, y + (size_t)tok0 * out_dim,
+                                nullptr, in_dim, out_dim, n, 1, blockIdx.x, gridDim.x);
 }
 
 struct Tuning {
-    int rows = 0;     // 0 = heuristic
-    int threads = 0;  // 0 = heuristic
-    int ctas_per_sm = 0;
+    int ks = 0;          // 0 = heuristic
+    int grid_mult = 0;   // CTAs launched per resident CTA slot; 0 = heuristic
 };
 Tuning g_tune;
 
-template <int FMT, int NB, int ROWS, bool DUMP>
-int launch_one(cudaStream_t s, const void *w, const void *xq, float *y, int32_t *idots,
-               uint32_t in_dim, uint32_t out_dim, uint32_t n_rows, uint32_t threads, size_t smem)
+template <int FMT> size_t stream_smem_bytes(uint32_t n_rows, uint32_t n_sub, int nb)
 {
-    auto kern = matvec_kernel<FMT, NB, ROWS, DUMP>;
-    const uint32_t rows_per_cta = (threads / 32) * ROWS;
-    const uint32_t n_groups = (out_dim + rows_per_cta - 1) / rows_per_cta;
-    uint32_t per_sm = 2048 / threads;
-    if (smem) per_sm = min(per_sm, (uint32_t)((227 * 1024) / (smem + 1024)));
-    if (per_sm == 0) per_sm = 1;
-    if (g_tune.ctas_per_sm > 0) per_sm = (uint32_t)g_tune.ctas_per_sm;
-    const uint32_t grid = min(n_groups, (uint32_t)sm_count() * per_sm);
-    kern<<<grid, threads, smem, s>>>((const uint8_t *)w, (const uint8_t *)xq, y, idots, in_dim,
-                                     out_dim, n_rows);
+    const size_t x = (((size_t)n_rows * n_sub * FmtTraits<FMT>::x_bytes) + 15u) & ~(size_t)15u;
+    return x + 2u * kWarpsPerCta * (size_t)nb * sizeof(float);
+}
+
+template <int FMT, int NB, bool DUMP>
+int launch_one(cudaStream_t s, const void *w, const void *xq, float *y, int32_t *idots,
+               uint32_t in_dim, uint32_t out_dim, uint32_t n_rows)
+{
+    const uint32_t n_sub = in_dim >> 5, n_iters = (n_sub + 31u) >> 5;
+    const size_t smem = stream_smem_bytes<FMT>(n_rows, n_sub, NB);
+    if (smem > kMaxStageBytesHost) return RC_ERR_TOO_MANY_ROWS; // caller splits the batch
+    uint32_t resident = (uint32_t)MinBlocks<NB>::v;
+    resident = min(resident, (uint32_t)((227 * 1024) / (smem + 1024)));
+    if (resident == 0) resident = 1;
+    const uint32_t slots = (uint32_t)sm_count() * resident * kWarpsPerCta;
+    // Split rows across warps until every warp slot has about three items, or a split would
+    // leave a warp with no iteration.
+    uint32_t ks = 1;
+    while (ks < (uint32_t)kWarpsPerCta && ks * 2u <= n_iters && (uint64_t)out_dim * ks < 3ull * slots) ks *= 2u;
+    if (g_tune.ks > 0) {
+        ks = 1;
+        while (ks * 2u <= (uint32_t)g_tune.ks && ks * 2u <= (uint32_t)kWarpsPerCta && ks * 2u <= n_iters) ks *= 2u;
+    }
+    if (DUMP) ks = 1;
+    const uint32_t rb_rows = kWarpsPerCta / ks;
+    const uint32_t n_blocks = (out_dim + rb_rows - 1u) / rb_rows;
+    const uint32_t mult = g_tune.grid_mult > 0 ? (uint32_t)g_tune.grid_mult : 2u;
+    const uint32_t grid = min(n_blocks, (uint32_t)sm_count() * resident * mult);
+    matvec_stream_kernel<FMT, NB, DUMP><<<grid, kWarpsPerCta * 32, smem, s>>>(
+        (const uint8_t *)w, (const uint8_t *)xq, y, idots, in_dim, out_dim, n_rows, ks);
     return (int)cudaGetLastError();
 }
 
@@ -685,53 +504,17 @@ template <int FMT, bool DUMP>
 int launch_fmt(cudaStream_t s, const void *w, const void *xq, float *y, int32_t *idots,
                uint32_t in_dim, uint32_t out_dim, uint32_t n_rows)
 {
-    const uint32_t n_sub = in_dim >> 5;
-    const size_t smem = (size_t)n_rows * n_sub * kStageBytesPerBlock;
-    if (smem > kMaxStageBytesHost) return RC_ERR_TOO_MANY_ROWS; // caller splits the batch
-    uint32_t threads = smem > 96 * 1024 ? 512 : 256;
-    if (g_tune.threads > 0) threads = (uint32_t)g_tune.threads;
-    int rows = (n_rows <= 2 && out_dim >= 8192) ? 2 : 1;
-    if (g_tune.rows > 0) rows = g_tune.rows;
-    if (DUMP) rows = 1;
-#define RC_GO(NB, ROWS) \
-    return launch_one<FMT, NB, ROWS, DUMP>(s, w, xq, y, idots, in_dim, out_dim, n_rows, threads, smem)
-#define RC_GO_MULTI(NB, ROWS) \
-    if (!DUMP) return launch_one<FMT, NB, ROWS, false>(s, w, xq, y, idots, in_dim, out_dim, n_rows, threads, smem)
-    if (n_rows == 1) {
-        if (rows >= 4) RC_GO_MULTI(1, 4);
-        if (rows == 2) RC_GO_MULTI(1, 2);
-        RC_GO(1, 1);
-    }
-    if (n_rows == 2) {
-        if (rows >= 2) RC_GO_MULTI(2, 2);
-        RC_GO(2, 1);
-    }
-    if (n_rows <= 4) {
-        if (rows >= 2) RC_GO_MULTI(4, 2);
-        RC_GO(4, 1);
-    }
-    if (n_rows <= 8) RC_GO(8, 1);
-    RC_GO(16, 1);
-#undef RC_GO
-#undef RC_GO_MULTI
+    if (n_rows == 1) return launch_one<FMT, 1, DUMP>(s, w, xq, y, idots, in_dim, out_dim, n_rows);
+    if (n_rows == 2) return launch_one<FMT, 2, DUMP>(s, w, xq, y, idots, in_dim, out_dim, n_rows);
+    if (n_rows <= 4) return launch_one<FMT, 4, DUMP>(s, w, xq, y, idots, in_dim, out_dim, n_rows);
+    if (n_rows <= 8) return launch_one<FMT, 8, DUMP>(s, w, xq, y, idots, in_dim, out_dim, n_rows);
+    return launch_one<FMT, 16, DUMP>(s, w, xq, y, idots, in_dim, out_dim, n_rows);
 }
 
 template <bool DUMP>
 int launch_any(cudaStream_t s, int type, const void *w, const void *xq, float *y, int32_t *idots,
                uint32_t in_dim, uint32_t out_dim, uint32_t n_rows)
 {
-    if (!DUMP && pipe_eligible(w, out_dim, n_rows)) {
-        int rc = RC_ERR_BAD_TYPE;
-        switch (type) {
-        case Q4_0: rc = launch_pipe_fmt<Q4_0>(s, w, xq, y, in_dim, out_dim, n_rows); break;
-        case Q8_0: rc = launch_pipe_fmt<Q8_0>(s, w, xq, y, in_dim, out_dim, n_rows); break;
-        case Q4_K: rc = launch_pipe_fmt<Q4_K>(s, w, xq, y, in_dim, out_dim, n_rows); break;
-        case Q5_K: rc = launch_pipe_fmt<Q5_K>(s, w, xq, y, in_dim, out_dim, n_rows); break;
-        case Q6_K: rc = launch_pipe_fmt<Q6_K>(s, w, xq, y, in_dim, out_dim, n_rows); break;
-        case IQ4_XS: rc = launch_pipe_fmt<IQ4_XS>(s, w, xq, y, in_dim, out_dim, n_rows); break;
-        }
-        if (rc != RC_ERR_TOO_MANY_ROWS) return rc; // rows too long for the stage ring: generic kernel
-    }
     switch (type) {
     case Q4_0: return launch_fmt<Q4_0, DUMP>(s, w, xq, y, idots, in_dim, out_dim, n_rows);
     case Q8_0: return launch_fmt<Q8_0, DUMP>(s, w, xq, y, idots, in_dim, out_dim, n_rows);
@@ -743,36 +526,49 @@ int launch_any(cudaStream_t s, int type, const void *w, const void *xq, float *y
     return RC_ERR_BAD_TYPE;
 }
 
-} // namespace
-
-namespace {
-
-constexpr int kMaxStageBytes = 200 * 1024;
-
-template <int FMT, int NB, int ROWS, bool DUMP> int set_attr_one()
+template <int FMT, int NB, bool DUMP> int set_attr_one()
 {
-    return (int)cudaFuncSetAttribute(matvec_kernel<FMT, NB, ROWS, DUMP>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxStageBytes);
+    return (int)cudaFuncSetAttribute(matvec_stream_kernel<FMT, NB, DUMP>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
 }
+
+constexpr int kGroupedBN = 16;
 
 template <int FMT> int set_attr_fmt()
 {
     int rc = 0;
-    rc |= set_attr_one<FMT, 1, 1, false>();
-    rc |= set_attr_one<FMT, 1, 2, false>();
-    rc |= set_attr_one<FMT, 1, 4, false>();
-    rc |= set_attr_one<FMT, 2, 1, false>();
-    rc |= set_attr_one<FMT, 2, 2, false>();
-    rc |= set_attr_one<FMT, 4, 1, false>();
-    rc |= set_attr_one<FMT, 4, 2, false>();
-    rc |= set_attr_one<FMT, 8, 1, false>();
-    rc |= set_attr_one<FMT, 16, 1, false>();
-    rc |= set_attr_one<FMT, 1, 1, true>();
-    rc |= set_attr_one<FMT, 2, 1, true>();
-    rc |= set_attr_one<FMT, 4, 1, true>();
-    rc |= set_attr_one<FMT, 8, 1, true>();
-    rc |= set_attr_one<FMT, 16, 1, true>();
+    rc |= set_attr_one<FMT, 1, false>();
+    rc |= set_attr_one<FMT, 2, false>();
+    rc |= set_attr_one<FMT, 4, false>();
+    rc |= set_attr_one<FMT, 8, false>();
+    rc |= set_attr_one<FMT, 16, false>();
+    rc |= set_attr_one<FMT, 1, true>();
+    rc |= set_attr_one<FMT, 2, true>();
+    rc |= set_attr_one<FMT, 4, true>();
+    rc |= set_attr_one<FMT, 8, true>();
+    rc |= set_attr_one<FMT, 16, true>();
+    rc |= (int)cudaFuncSetAttribute(matvec_grouped_kernel<FMT, kGroupedBN>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
     return rc;
+}
+
+template <int FMT>
+int launch_grouped_fmt(cudaStream_t s, const void *slab, size_t bpe, const int32_t *expert_off,
+                       const int32_t *tile_off, uint32_t n_expert, const void *xq, float *y,
+                       uint32_t in_dim, uint32_t out_dim, uint32_t n_entries)
+{
+    constexpr int BN = kGroupedBN;
+    const uint32_t n_sub = in_dim >> 5;
+    const size_t smem = stream_smem_bytes<FMT>(BN, n_sub, BN);
+    if (smem > kMaxStageBytesHost) return RC_ERR_BAD_SHAPE;
+    const uint32_t n_blocks = (out_dim + kWarpsPerCta - 1) / kWarpsPerCta;
+    const uint32_t gx = min(n_blocks, 8u);
+    const uint32_t tiles_ub = (n_entries + BN - 1) / BN + n_expert;
+    if (tiles_ub > 65535u) return RC_ERR_BAD_ARGUMENT;
+    matvec_grouped_kernel<FMT, BN><<<dim3(gx, tiles_ub), kWarpsPerCta * 32, smem, s>>>(
+        (const uint8_t *)slab, bpe, expert_off, tile_off, n_expert, (const uint8_t *)xq, y, in_dim,
+        out_dim);
+    return (int)cudaGetLastError();
 }
 
 } // namespace
@@ -786,58 +582,8 @@ int matvec_set_attributes()
     rc |= set_attr_fmt<Q5_K>();
     rc |= set_attr_fmt<Q6_K>();
     rc |= set_attr_fmt<IQ4_XS>();
-    rc |= set_attr_pipe<Q4_0>();
-    rc |= set_attr_pipe<Q8_0>();
-    rc |= set_attr_pipe<Q4_K>();
-    rc |= set_attr_pipe<Q5_K>();
-    rc |= set_attr_pipe<Q6_K>();
-    rc |= set_attr_pipe<IQ4_XS>();
     return rc;
 }
-
-void matvec_set_pipe_tuning(int rows_per_stage, int stages, int cwarps, int ctas_per_sm, int disable)
-{
-    g_pipe.rows_per_stage = rows_per_stage;
-    g_pipe.stages = stages;
-    g_pipe.cwarps = cwarps;
-    g_pipe.ctas_per_sm = ctas_per_sm;
-    g_pipe.disable = disable;
-}
-
-int matvec_device_error(unsigned int *out)
-{
-    return (int)cudaMemcpyFromSymbol(out, g_pipe_error, sizeof(unsigned int));
-}
-
-namespace {
-template <int FMT>
-int launch_grouped_fmt(cudaStream_t s, const void *slab, size_t bpe, const int32_t *expert_off,
-                       const int32_t *tile_off, uint32_t n_expert, const void *xq, float *y,
-                       uint32_t in_dim, uint32_t out_dim, uint32_t n_entries)
-{
-    constexpr int BN = 16;
-    const uint32_t n_sub = in_dim >> 5;
-    const size_t smem = (size_t)BN * n_sub * kStageBytesPerBlock;
-    if (smem > kMaxStageBytesHost) return RC_ERR_BAD_SHAPE;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(matvec_grouped_kernel<FMT, BN>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)kMaxStageBytesHost);
-        if (e != cudaSuccess) return (int)e;
-        attr_done = true;
-    }
-    const uint32_t threads = 256;
-    const uint32_t n_groups = (out_dim + 7) / 8;
-    const uint32_t gx = min(n_groups, 8u);
-    const uint32_t tiles_ub = (n_entries + BN - 1) / BN + n_expert;
-    if (tiles_ub > 65535u) return RC_ERR_BAD_ARGUMENT;
-    matvec_grouped_kernel<FMT, BN><<<dim3(gx, tiles_ub), threads, smem, s>>>(
-        (const uint8_t *)slab, bpe, expert_off, tile_off, n_expert, (const uint8_t *)xq, y, in_dim,
-        out_dim);
-    return (int)cudaGetLastError();
-}
-} // namespace
 
 // dp4a grouped GEMM with a 16-token tile: every tile streams its expert's weights once.
 int launch_matvec_grouped(cudaStream_t s, int type, const void *slab, size_t bpe,
@@ -858,11 +604,12 @@ int launch_matvec_grouped(cudaStream_t s, int type, const void *slab, size_t bpe
     return RC_ERR_BAD_TYPE;
 }
 
-void matvec_set_tuning(int rows, int threads, int ctas_per_sm)
+uint32_t matvec_grouped_bn() { return kGroupedBN; }
+
+void matvec_set_tuning(int ks, int grid_mult)
 {
-    g_tune.rows = rows;
-    g_tune.threads = threads;
-    g_tune.ctas_per_sm = ctas_per_sm;
+    g_tune.ks = ks;
+    g_tune.grid_mult = grid_mult;
 }
 
 int launch_matvec(cudaStream_t s, int type, const void *w, const void *xq, float *y,
@@ -872,8 +619,9 @@ int launch_matvec(cudaStream_t s, int type, const void *w, const void *xq, float
     // each part reads the weights once more, which only very long rows ever need.
     uint32_t part = n_rows;
     const uint32_t n_sub = in_dim >> 5;
-    while (part > 1 && (size_t)part * n_sub * kStageBytesPerBlock > kMaxStageBytesHost) part = (part + 1) / 2;
-    if ((size_t)part * n_sub * kStageBytesPerBlock > kMaxStageBytesHost) return RC_ERR_BAD_SHAPE;
+    const size_t per_row = (size_t)n_sub * 48 + 2u * kWarpsPerCta * sizeof(float);
+    while (part > 1 && (size_t)part * per_row + 64 > kMaxStageBytesHost) part = (part + 1) / 2;
+    if ((size_t)part * per_row + 64 > kMaxStageBytesHost) return RC_ERR_BAD_SHAPE;
     for (uint32_t b0 = 0; b0 < n_rows; b0 += part) {
         const uint32_t nb = min(part, n_rows - b0);
         const uint8_t *xp = (const uint8_t *)xq + (size_t)b0 * n_sub * RC_BLOCKQ8_BYTES;
