@@ -50,7 +50,8 @@ enum rc_error {
     RC_ERR_TOO_MANY_ROWS = -5, /* n_rows beyond what the entry point accepts          */
     RC_ERR_SCRATCH_TOO_SMALL = -6,
     RC_ERR_NO_DEVICE = -7,     /* no sm_100 device / kernels not loadable             */
-    RC_ERR_BAD_ARGUMENT = -8
+    RC_ERR_BAD_ARGUMENT = -8,
+    RC_ERR_STATIC_LIMIT = -9   /* size beyond the fixed scratch of rc_matvec_f32_noalloc     */
 };
 
 #define RC_BLOCKQ8_BYTES 40          /* kernels/quantize_q8.cpp:16-21 */
@@ -116,6 +117,24 @@ int rc_matvec_batched(void *stream, int ggml_type, const void *w, const void *xq
  * ((in_dim/32)*40 bytes), then rc_matvec. */
 int rc_matvec_f32(void *stream, int ggml_type, const void *w, const float *x, float *y,
                   uint32_t in_dim, uint32_t out_dim, void *xq_scratch, size_t scratch_bytes);
+
+/* Same result as rc_matvec_f32, for callers that cannot hand in a scratch buffer and must not
+ * allocate one: a decode thread for which cudaMalloc's device-wide synchronisation would stall
+ * every stream, or a plug-in living inside a host runtime that has already reserved all of HBM
+ * for its own pool, so that cudaMalloc would simply fail.  It has no counterpart in the
+ * reference, whose wrappers always own an xq8 buffer (src/runtime/gemma4.rs:1508-1520).
+ * The quantized activations go to a fixed array inside the library instead
+ * (RC_NOALLOC_SCRATCH_BYTES of device memory, held by every GPU that loads the library until
+ * the process exits); x, w and y are still the caller's.  in_dim above RC_NOALLOC_MAX_IN_DIM
+ * returns RC_ERR_STATIC_LIMIT.  The call allocates and frees nothing.
+ * The first call on each device looks the array's address up once (with that device current);
+ * make that first call before any stream capture.  All calls on a device share the one array
+ * and each overwrites the part it uses, so nothing needs clearing between calls, but two calls
+ * whose kernels overlap on the GPU (different streams) race on it: keep them on one stream. */
+#define RC_NOALLOC_SCRATCH_BYTES (64 * 1024)
+#define RC_NOALLOC_MAX_IN_DIM ((RC_NOALLOC_SCRATCH_BYTES / RC_BLOCKQ8_BYTES) * 32)
+int rc_matvec_f32_noalloc(void *stream, int ggml_type, const void *w, const float *x, float *y,
+                          uint32_t in_dim, uint32_t out_dim);
 
 /* Test and debug aid: the per-(activation row, weight row, sub-block) integers the
  * matvec forms before scaling.  idots int32 [n_rows][out_dim][in_dim/32][2]; slot 1 is

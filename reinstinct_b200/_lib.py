@@ -42,6 +42,7 @@ _SIGNATURES = {
     "rc_matvec": (_i, [_vp, _i, _vp, _vp, _vp, _u32, _u32]),
     "rc_matvec_batched": (_i, [_vp, _i, _vp, _vp, _vp, _u32, _u32, _u32]),
     "rc_matvec_f32": (_i, [_vp, _i, _vp, _vp, _vp, _u32, _u32, _vp, _sz]),
+    "rc_matvec_f32_noalloc": (_i, [_vp, _i, _vp, _vp, _vp, _u32, _u32]),
     "rc_matvec_block_dots": (_i, [_vp, _i, _vp, _vp, _vp, _u32, _u32, _u32]),
     "rc_tune_matvec": (None, [_i, _i]),
     "rc_tune_mmq": (None, [_i]),

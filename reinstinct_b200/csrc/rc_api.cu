@@ -89,6 +89,7 @@ const char *rc_error_string(int code)
     case RC_ERR_SCRATCH_TOO_SMALL: return "scratch buffer too small";
     case RC_ERR_NO_DEVICE: return "no usable sm_100 device";
     case RC_ERR_BAD_ARGUMENT: return "bad argument";
+    case RC_ERR_STATIC_LIMIT: return "in_dim exceeds RC_NOALLOC_MAX_IN_DIM, the fixed scratch of rc_matvec_f32_noalloc";
     }
     if (code > 0) return cudaGetErrorString((cudaError_t)code);
     return "unknown reinstinct_cuda error";
@@ -206,6 +207,55 @@ int rc_matmul(void *stream, int type, const void *w, const float *x, float *y, u
     if (n_rows <= RC_MATVEC_MAX_ROWS)
         return launch_matvec(S(stream), type, w, xq_scratch, y, in_dim, out_dim, n_rows, nullptr);
     return launch_mmq_gemm(S(stream), type, w, xq_scratch, y, in_dim, out_dim, n_rows);
+}
+
+/* ---- allocation-free matvec ---------------------------------------------------------------- */
+
+} // extern "C"
+
+namespace {
+// Quantized-activation scratch of rc_matvec_f32_noalloc.  In host code this name is only a
+// handle for cudaGetSymbolAddress; kernels must be given the address that call returns.
+static __device__ __align__(256) unsigned char g_noalloc_xq[RC_NOALLOC_SCRATCH_BYTES];
+void *g_noalloc_ptr[kMaxDevices];
+
+// Device address of g_noalloc_xq on the current device, looked up once per device.
+int noalloc_scratch(void **out)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return RC_ERR_NO_DEVICE;
+    if (!g_noalloc_ptr[dev]) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_xq);
+        if (e != cudaSuccess) return (int)e;
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return RC_OK;
+}
+} // namespace
+
+extern "C" {
+
+int rc_matvec_f32_noalloc(void *stream, int type, const void *w, const float *x, float *y,
+                          uint32_t in_dim, uint32_t out_dim)
+{
+    if (!x) return RC_ERR_NULL_POINTER;
+    if (in_dim > RC_NOALLOC_MAX_IN_DIM) return RC_ERR_STATIC_LIMIT;
+    int rc = ensure_device_ready();
+    if (rc) return rc;
+    void *xq = nullptr;
+    rc = noalloc_scratch(&xq);
+    if (rc) return rc;
+    rc = check_weight_args(type, w, xq, y, in_dim, out_dim);
+    if (rc) return rc;
+    if (((uintptr_t)x & 3u)) return RC_ERR_MISALIGNED;
+    // the quantizer rewrites every block the matvec reads, so stale contents never matter
+    rc = launch_quantize_q8(S(stream), x, xq, in_dim, 1);
+    if (rc) return rc;
+    return launch_matvec(S(stream), type, w, xq, y, in_dim, out_dim, 1, nullptr);
 }
 
 uint32_t rc_moe_tile_bn(void) { return matvec_grouped_bn(); }
