@@ -189,6 +189,35 @@ def workload_config(n_gpus: int) -> dict:
 
 # ------------------------------------------------------------------------------------- GPU arm
 
+# DRAM bytes of one Q4_K 5120->17408 matvec launch, from the ncu capture summarised in
+# profiles/matvec_stream_q4k_5120x17408.md (algorithmic bytes: 51,527,680).
+Q4K_DRAM_TRAFFIC_BYTES = 51_566_000
+INT8_DENSE_PEAK_TOPS = 4500.0  # nominal B200 dense int8; no measured int8 figure is supplied
+
+
+def mmq_prefill(rt, synth, torch, dev, timed):
+    """Config 4: dense prefill GEMM, 512 tokens x Q4_K 5120->17408, through PrefillGemm
+    (quantize + tensor-core MMQ) and the MMQ kernel alone.  TOPS = 2*P*K*N / t."""
+    P = 512
+    raw = synth.synth_blocks(Q4_K, HIDDEN, FFN, seed=77)
+    w = rt.GpuMatvecTensor.from_bytes_matvec(raw, Q4_K, HIDDEN, FFN, device=dev)
+    x = torch.from_numpy(synth.synth_activations(P, HIDDEN, 78)).to(dev)
+    gemm = rt.PrefillGemm(max_x=P * HIDDEN, device=dev)
+    y = torch.empty((P, FFN), dtype=torch.float32, device=dev)
+    xq = torch.empty(P * (HIDDEN // 32) * 40, dtype=torch.uint8, device=dev)
+    rt.launch_quantize_q8(x, xq, HIDDEN, P)
+    ops = 2.0 * P * HIDDEN * FFN
+    reps = 10
+    ms_k = timed(lambda i: rt.launch_mmq_gemm(w, xq, y, P), reps, 3) / reps
+    ms_q = timed(lambda i: gemm.matmul_into(y, w, x, P), reps, 3) / reps
+    tops = ops / (ms_k * 1e-3) / 1e12
+    return {"workload": "config 4: 512 tokens x Q4_K 5120->17408 (91.3 GOP)", "kernel": "mmq_kernel<Q4_K,128> (tcgen05 kind::i8)",
+            "us_kernel": ms_k * 1e3, "tops_kernel": tops, "us_with_quantize": ms_q * 1e3,
+            "tops_with_quantize": ops / (ms_q * 1e-3) / 1e12,
+            "roofline": {"bound": "tensor", "achieved": tops, "peak": INT8_DENSE_PEAK_TOPS, "unit": "TOP/s",
+                         "frac": tops / INT8_DENSE_PEAK_TOPS, "peak_kind": "nominal dense int8"},
+            "tok_per_s_per_layer_gate_only": P / (ms_q * 1e-3)}
+
 
 def run_gpu_arm(args):
     import torch
@@ -345,6 +374,7 @@ def run_gpu_arm(args):
     q4k_us = ms_q * 1e3 / (reps * len(mats))
     clocks = sampler.stop() if rank == 0 else None
 
+    clocks = clocks  # sampled over the layer, e2e and Q4_K regions above
     # Q6_K down alone, for the per-format report
     q6_bytes = copies[0][2].data.numel()
     downs = [copies[c][2] for c in range(n_copies)]
@@ -354,6 +384,10 @@ def run_gpu_arm(args):
             rt.launch_matvec_xq8(w, hq, y_down)
     ms_6 = timed(q6_only, reps, 5)
     q6_us = ms_6 * 1e3 / (reps * len(downs))
+
+    mmq = None
+    if world == 1 and not args.skip_mmq:
+        mmq = mmq_prefill(rt, synth, torch, dev, timed)
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
@@ -368,15 +402,18 @@ def run_gpu_arm(args):
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": launches_per_step * steps_timed,
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": "matvec_kernel<Q4_K> 5120->%d" % (FFN // world),
+            "roofline": {"bound": "hbm", "kernel": "matvec_stream_kernel<Q4_K,1> 5120->%d" % (FFN // world),
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "us_per_launch": q4k_us, "bytes_per_launch": q4k_bytes,
-                         "traffic": None},
+                         "traffic": Q4K_DRAM_TRAFFIC_BYTES if world == 1 else None,
+                         "traffic_source": "profiles/matvec_stream_q4k_5120x17408.md (ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch)"},
             "per_kernel": {"q4k_gate_up_gbs": achieved, "q6k_down_gbs": q6_bytes / (q6_us * 1e-6) / 1e9,
                            "q6k_us": q6_us},
             "tok_per_s_per_layer": 1e3 / ms_per_step,
             "graph_replay": use_graph,
         }
+        if mmq is not None:
+            line["mmq_prefill"] = mmq
         if world == 1 and not args.no_cpu_baseline:
             v, sample, _ = cpu_layer_sample(seconds=12.0, threads=os.cpu_count() or 1)
             line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port",
@@ -394,6 +431,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-mmq", action="store_true", help="leave the config-4 prefill GEMM section out")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -144,9 +144,10 @@ int rc_matvec_block_dots(void *stream, int ggml_type, const void *w, const void 
 
 /* Measurement aid: overrides the matvec launch heuristics for the calling process (ks =
  * warps that split one weight row, grid_mult = CTAs launched per resident CTA slot; 0 restores
- * the heuristic).  No counterpart in the reference, whose geometry is fixed in its wrappers
+ * the heuristic; no_pdl != 0 launches the matvec and quantize kernels without programmatic
+ * stream serialization).  No counterpart in the reference, whose geometry is fixed in its wrappers
  * (src/runtime/gemma4.rs:1530-1551). */
-void rc_tune_matvec(int ks, int grid_mult);
+void rc_tune_matvec(int ks, int grid_mult, int no_pdl);
 /* Measurement aid: force_dp4a != 0 sends rc_mmq_gemm through the dp4a kernel instead of the
  * tensor-core kernel, for A/B timing of the two. */
 void rc_tune_mmq(int force_dp4a);

@@ -446,9 +446,9 @@ int rc_graph_exec_destroy(void *graph_exec) { return (int)cudaGraphExecDestroy((
 } // extern "C"
 
 namespace rc {
-void matvec_set_tuning(int ks, int grid_mult);
+void matvec_set_tuning(int ks, int grid_mult, int no_pdl);
 } // namespace rc
-extern "C" void rc_tune_matvec(int ks, int grid_mult) { rc::matvec_set_tuning(ks, grid_mult); }
+extern "C" void rc_tune_matvec(int ks, int grid_mult, int no_pdl) { rc::matvec_set_tuning(ks, grid_mult, no_pdl); }
 extern "C" void rc_tune_mmq(int force_dp4a) { rc::mmq_force_dp4a(force_dp4a); }
 extern "C" int rc_device_status(unsigned int *status)
 {

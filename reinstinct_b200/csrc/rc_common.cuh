@@ -93,6 +93,32 @@ __host__ __device__ inline size_t repacked_len_of(int t, size_t in_dim, size_t o
     return out_dim * nsp * per_sub + out_dim * (in_dim >> 8) * per_super;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// The kernels of the decode chain run back to back on one stream and last a few microseconds,
+// so launch ramp and tail are a sizeable share.  Launched with programmatic stream
+// serialization, a kernel may start while its predecessor drains: it calls
+// pdl_launch_dependents() early (its own successor may then start too) and pdl_wait() before it
+// touches anything a predecessor wrote or still reads — weights are never such data, so their
+// first loads go out before the wait.  Both instructions are no-ops in a plain launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- loads -------------------------------------------------------------------------
 
 // Weight bytes are read exactly once per launch: bypass L1 allocation.
@@ -173,6 +199,23 @@ __device__ __forceinline__ uint32_t fields2_to_bits45(uint32_t h)
     const uint32_t even = ((h & 0x33u) * 0x00010010u) & 0x00300030u;  // fields 0,2: <<4, <<16
     const uint32_t odd = ((h & 0xCCu) * 0x00400400u) & 0x30003000u;   // fields 1,3: <<10, <<22
     return even | odd;
+}
+
+// The same spreading for the four bytes of a word at once: h holds the high-2 bytes of groups
+// 0..3 (byte g = four 2-bit fields of group g); g0..g3 receive, for each group, its four fields
+// in bits 4..5 of bytes 0..3.  Four shift-and-mask steps pull field c of every group into one
+// word, a 4x4 byte transpose (eight PRMT) regroups them: 15 operations for 16 fields and no
+// multiplies.
+__device__ __forceinline__ void spread_fields4(uint32_t h, uint32_t &g0, uint32_t &g1, uint32_t &g2, uint32_t &g3)
+{
+    const uint32_t K = 0x30303030u;
+    const uint32_t f0 = (h << 4) & K, f1 = (h << 2) & K, f2 = h & K, f3 = (h >> 2) & K; // [grp0..grp3] of field c
+    const uint32_t t0 = __byte_perm(f0, f1, 0x5140u), t1 = __byte_perm(f2, f3, 0x5140u); // groups 0,1
+    const uint32_t t2 = __byte_perm(f0, f1, 0x7362u), t3 = __byte_perm(f2, f3, 0x7362u); // groups 2,3
+    g0 = __byte_perm(t0, t1, 0x5410u);
+    g1 = __byte_perm(t0, t1, 0x7632u);
+    g2 = __byte_perm(t2, t3, 0x5410u);
+    g3 = __byte_perm(t2, t3, 0x7632u);
 }
 
 // IQ4_NL codebook {-127,-104,-83,-65,-49,-35,-22,-10,1,13,25,38,53,69,89,113}

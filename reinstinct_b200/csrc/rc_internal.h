@@ -18,6 +18,7 @@ int launch_repack(cudaStream_t s, int type, const void *blocks, size_t in_dim, s
 int launch_matvec(cudaStream_t s, int type, const void *w, const void *xq, float *y,
                   uint32_t in_dim, uint32_t out_dim, uint32_t n_rows, int32_t *idots);
 int matvec_set_attributes();
+bool matvec_pdl_enabled();
 int launch_matvec_grouped(cudaStream_t s, int type, const void *slab, size_t bytes_per_expert,
                           const int32_t *expert_off, const int32_t *tile_off, uint32_t n_expert,
                           const void *xq, float *y, uint32_t in_dim, uint32_t out_dim,

@@ -212,16 +212,18 @@ __device__ __forceinline__ float term(const Raw<FMT> &r, const int4 &xl, const i
     } else if constexpr (FMT == Q6_K) {
         // byte g of the high-2 plane belongs to group g (src/quant/q6_k.rs:128-133)
         const uint4 q = r.q;
-        const uint2 h = r.h;
+        uint32_t g0, g1, g2, g3, g4, g5, g6, g7;
+        spread_fields4(r.h.x, g0, g1, g2, g3);
+        spread_fields4(r.h.y, g4, g5, g6, g7);
         int s = 0, t = 0;
-        s = __dp4a((int)((q.x & M) | fields2_to_bits45(h.x & 0xFFu)), xl.x, s);
-        t = __dp4a((int)(((q.x >> 4) & M) | fields2_to_bits45((h.x >> 8) & 0xFFu)), xh.x, t);
-        s = __dp4a((int)((q.y & M) | fields2_to_bits45((h.x >> 16) & 0xFFu)), xl.y, s);
-        t = __dp4a((int)(((q.y >> 4) & M) | fields2_to_bits45(h.x >> 24)), xh.y, t);
-        s = __dp4a((int)((q.z & M) | fields2_to_bits45(h.y & 0xFFu)), xl.z, s);
-        t = __dp4a((int)(((q.z >> 4) & M) | fields2_to_bits45((h.y >> 8) & 0xFFu)), xh.z, t);
-        s = __dp4a((int)((q.w & M) | fields2_to_bits45((h.y >> 16) & 0xFFu)), xl.w, s);
-        t = __dp4a((int)(((q.w >> 4) & M) | fields2_to_bits45(h.y >> 24)), xh.w, t);
+        s = __dp4a((int)((q.x & M) | g0), xl.x, s);
+        t = __dp4a((int)(((q.x >> 4) & M) | g1), xh.x, t);
+        s = __dp4a((int)((q.y & M) | g2), xl.y, s);
+        t = __dp4a((int)(((q.y >> 4) & M) | g3), xh.y, t);
+        s = __dp4a((int)((q.z & M) | g4), xl.z, s);
+        t = __dp4a((int)(((q.z >> 4) & M) | g5), xh.z, t);
+        s = __dp4a((int)((q.w & M) | g6), xl.w, s);
+        t = __dp4a((int)(((q.w >> 4) & M) | g7), xh.w, t);
         i0 = s - is.x;
         i1 = t - is.y;
         const int slo = (int)(int8_t)(r.sm & 0xFFu), shi = (int)(int8_t)(r.sm >> 8);
@@ -280,6 +282,12 @@ stream_body(uint8_t *smem, const uint8_t *__restrict__ w, const uint8_t *__restr
     const uint32_t rb_rows = n_warps / ks, r_local = warp / ks, chunk = warp - r_local * ks;
     const uint32_t it0 = chunk * n_iters / ks, it1 = (chunk + 1u) * n_iters / ks;
     const uint32_t n_blocks = (out_dim + rb_rows - 1u) / rb_rows;
+    // The chunk's iterations are cut into groups of at most G, as evenly as possible (17
+    // iterations with G = 4 become 4,4,3,3,3 rather than 4,4,4,4,1).
+    const uint32_t chunk_iters = it1 - it0;
+    const uint32_t n_groups = (chunk_iters + G - 1u) / G;
+    const uint32_t g_base = n_groups ? chunk_iters / n_groups : 0u, g_rem = n_groups ? chunk_iters % n_groups : 0u;
+    auto group_len = [&](uint32_t gi) { return g_base + (gi < g_rem ? 1u : 0u); };
     const Planes p = planes_of<FMT>(w, in_dim, out_dim);
     const bool sup_a4 = (reinterpret_cast<uintptr_t>(p.sup) & 3u) == 0;
     const uint32_t n_xblocks = n_rows * n_sub;
@@ -300,11 +308,10 @@ stream_body(uint8_t *smem, const uint8_t *__restrict__ w, const uint8_t *__restr
         default: if constexpr (G >= 5) f(std::integral_constant<int, 5>{}); break;
         }
     };
-    auto fetch_group = [&](uint32_t row, uint32_t it) {
+    auto fetch_group = [&](uint32_t row, uint32_t it, uint32_t n) {
         // rows past the end are clamped: their loads stay legal, their results unused
         row = min(row, out_dim - 1u);
         const size_t rbase = (size_t)row * p.nsp, sbase = (size_t)row * p.n_super;
-        const uint32_t n = min((uint32_t)G, it1 - it);
         if (lanes_full(it, n)) {
             with_count(n, [&](auto nc) {
 #pragma unroll
@@ -316,7 +323,7 @@ stream_body(uint8_t *smem, const uint8_t *__restrict__ w, const uint8_t *__restr
         } else {
 #pragma unroll
             for (int i = 0; i < G; i++) {
-                if (it + i < it1) {
+                if (i < (int)n) {
                     const uint32_t sb = min((it + i) * 32u + lane, n_sub - 1u);
                     fetch<FMT>(cur[i], p, rbase + sb, sbase + (sb >> 3), sup_a4);
                 }
@@ -324,8 +331,10 @@ stream_body(uint8_t *smem, const uint8_t *__restrict__ w, const uint8_t *__restr
         }
     };
 
-    uint32_t blk = block_begin, it = it0;
-    if (blk < n_blocks) fetch_group(blk * rb_rows + r_local, it); // weights do not wait for x
+    uint32_t blk = block_begin, it = it0, gi = 0;
+    if (blk < n_blocks) fetch_group(blk * rb_rows + r_local, it, group_len(0)); // weights do not wait for x
+    pdl_launch_dependents();
+    pdl_wait(); // activations (and y) belong to the preceding kernels
     stage_x<FMT>(st, xq, n_xblocks);
     __syncthreads();
 
@@ -336,7 +345,7 @@ stream_body(uint8_t *smem, const uint8_t *__restrict__ w, const uint8_t *__restr
 
     while (blk < n_blocks) {
         const uint32_t row = blk * rb_rows + r_local;
-        const uint32_t n_now = min((uint32_t)G, it1 - it);
+        const uint32_t n_now = group_len(gi);
         if (lanes_full(it, n_now)) {
             with_count(n_now, [&](auto nc) {
 #pragma unroll
@@ -363,7 +372,7 @@ stream_body(uint8_t *smem, const uint8_t *__restrict__ w, const uint8_t *__restr
         } else {
 #pragma unroll
             for (int i = 0; i < G; i++) {
-                if (it + i < it1) {
+                if (i < (int)n_now) {
                     const uint32_t sb_raw = (it + i) * 32u + lane;
                     const bool valid = sb_raw < n_sub;
                     const uint32_t sb = min(sb_raw, n_sub - 1u);
@@ -387,11 +396,13 @@ stream_body(uint8_t *smem, const uint8_t *__restrict__ w, const uint8_t *__restr
                 }
             }
         }
-        it += G;
-        const bool item_done = it >= it1;
+        it += n_now;
+        gi++;
+        const bool item_done = gi >= n_groups;
         const uint32_t nblk = item_done ? blk + block_stride : blk;
         const uint32_t nit = item_done ? it0 : it;
-        if (nblk < n_blocks) fetch_group(nblk * rb_rows + r_local, nit); // in flight during the reduction
+        const uint32_t ngi = item_done ? 0u : gi;
+        if (nblk < n_blocks) fetch_group(nblk * rb_rows + r_local, nit, group_len(ngi)); // in flight during the reduction
         if (item_done) {
 #pragma unroll
             for (int b = 0; b < NB; b++) {
@@ -417,6 +428,7 @@ stream_body(uint8_t *smem, const uint8_t *__restrict__ w, const uint8_t *__restr
         }
         blk = nblk;
         it = nit;
+        gi = ngi;
     }
 }
 
@@ -462,6 +474,7 @@ matvec_grouped_kernel(const uint8_t *__restrict__ slab, size_t bytes_per_expert,
 struct Tuning {
     int ks = 0;          // 0 = heuristic
     int grid_mult = 0;   // CTAs launched per resident CTA slot; 0 = heuristic
+    int no_pdl = 0;      // plain launches (for A/B timing)
 };
 Tuning g_tune;
 
@@ -482,10 +495,10 @@ int launch_one(cudaStream_t s, const void *w, const void *xq, float *y, int32_t 
     resident = min(resident, (uint32_t)((227 * 1024) / (smem + 1024)));
     if (resident == 0) resident = 1;
     const uint32_t slots = (uint32_t)sm_count() * resident * kWarpsPerCta;
-    // Split rows across warps until every warp slot has about three items, or a split would
-    // leave a warp with no iteration.
+    // One warp per row is best whenever the rows fill most of the warp slots; only narrower
+    // matrices split rows across warps (never leaving a warp without an iteration).
     uint32_t ks = 1;
-    while (ks < (uint32_t)kWarpsPerCta && ks * 2u <= n_iters && (uint64_t)out_dim * ks < 3ull * slots) ks *= 2u;
+    while (ks < (uint32_t)kWarpsPerCta && ks * 2u <= n_iters && (uint64_t)out_dim * ks * 4u < 3ull * slots) ks *= 2u;
     if (g_tune.ks > 0) {
         ks = 1;
         while (ks * 2u <= (uint32_t)g_tune.ks && ks * 2u <= (uint32_t)kWarpsPerCta && ks * 2u <= n_iters) ks *= 2u;
@@ -493,11 +506,17 @@ int launch_one(cudaStream_t s, const void *w, const void *xq, float *y, int32_t 
     if (DUMP) ks = 1;
     const uint32_t rb_rows = kWarpsPerCta / ks;
     const uint32_t n_blocks = (out_dim + rb_rows - 1u) / rb_rows;
-    const uint32_t mult = g_tune.grid_mult > 0 ? (uint32_t)g_tune.grid_mult : 2u;
-    const uint32_t grid = min(n_blocks, (uint32_t)sm_count() * resident * mult);
-    matvec_stream_kernel<FMT, NB, DUMP><<<grid, kWarpsPerCta * 32, smem, s>>>(
-        (const uint8_t *)w, (const uint8_t *)xq, y, idots, in_dim, out_dim, n_rows, ks);
-    return (int)cudaGetLastError();
+    // Two CTAs per resident slot even out the tail once a CTA has three or more row blocks.
+    const uint32_t capacity = (uint32_t)sm_count() * resident;
+    const uint32_t mult = g_tune.grid_mult > 0 ? (uint32_t)g_tune.grid_mult : (n_blocks >= 3u * capacity ? 2u : 1u);
+    const uint32_t grid = min(n_blocks, capacity * mult);
+    if (g_tune.no_pdl) {
+        matvec_stream_kernel<FMT, NB, DUMP><<<grid, kWarpsPerCta * 32, smem, s>>>(
+            (const uint8_t *)w, (const uint8_t *)xq, y, idots, in_dim, out_dim, n_rows, ks);
+        return (int)cudaGetLastError();
+    }
+    return (int)launch_pdl(matvec_stream_kernel<FMT, NB, DUMP>, dim3(grid), dim3(kWarpsPerCta * 32), smem, s,
+                           (const uint8_t *)w, (const uint8_t *)xq, y, idots, in_dim, out_dim, n_rows, ks);
 }
 
 template <int FMT, bool DUMP>
@@ -606,11 +625,13 @@ int launch_matvec_grouped(cudaStream_t s, int type, const void *slab, size_t bpe
 
 uint32_t matvec_grouped_bn() { return kGroupedBN; }
 
-void matvec_set_tuning(int ks, int grid_mult)
+void matvec_set_tuning(int ks, int grid_mult, int no_pdl)
 {
     g_tune.ks = ks;
     g_tune.grid_mult = grid_mult;
+    g_tune.no_pdl = no_pdl;
 }
+bool matvec_pdl_enabled() { return !g_tune.no_pdl; }
 
 int launch_matvec(cudaStream_t s, int type, const void *w, const void *xq, float *y,
                   uint32_t in_dim, uint32_t out_dim, uint32_t n_rows, int32_t *idots)

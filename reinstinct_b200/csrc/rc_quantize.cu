@@ -17,6 +17,8 @@ __global__ void __launch_bounds__(256) quantize_q8_kernel(const float *__restric
                                                            uint8_t *__restrict__ out,
                                                            uint32_t in_dim)
 {
+    pdl_launch_dependents(); // a following matvec may start fetching its weights now
+    pdl_wait();              // x comes from the preceding kernel
     const uint32_t n_sub = in_dim >> 5;
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warps_per_cta = blockDim.x >> 5;
@@ -57,8 +59,14 @@ int launch_quantize_q8(cudaStream_t s, const float *x, void *xq, uint32_t in_dim
     // gridDim.y is limited to 65535: fold larger batches by looping on the host.
     for (uint32_t v0 = 0; v0 < n_vec; v0 += 65535u) {
         const uint32_t nv = min(65535u, n_vec - v0);
-        quantize_q8_kernel<<<dim3(gx, nv), 256, 0, s>>>(
-            x + (size_t)v0 * in_dim, (uint8_t *)xq + (size_t)v0 * n_sub * RC_BLOCKQ8_BYTES, in_dim);
+        const float *xp = x + (size_t)v0 * in_dim;
+        uint8_t *op = (uint8_t *)xq + (size_t)v0 * n_sub * RC_BLOCKQ8_BYTES;
+        if (matvec_pdl_enabled()) {
+            cudaError_t e = launch_pdl(quantize_q8_kernel, dim3(gx, nv), dim3(256), 0, s, xp, op, in_dim);
+            if (e != cudaSuccess) return (int)e;
+        } else {
+            quantize_q8_kernel<<<dim3(gx, nv), 256, 0, s>>>(xp, op, in_dim);
+        }
     }
     return (int)cudaGetLastError();
 }
