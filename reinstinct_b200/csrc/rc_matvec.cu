@@ -143,6 +143,55 @@ __device__ __forceinline__ void fetch(Raw<FMT> &r, const Planes &p, size_t idx, 
     }
 }
 
+// The same loads from per-group base pointers (the lane's sub-block of the group's first
+// iteration) plus the constant byte offsets of iteration i, so that an unrolled group costs one
+// set of 64-bit address computations instead of one per load.  A4: the superblock plane is
+// 4-byte aligned.
+struct GroupPtrs {
+    const uint8_t *nib, *aux, *sc, *sup;
+};
+
+template <int FMT, bool A4>
+__device__ __forceinline__ void fetch_off(Raw<FMT> &r, const GroupPtrs &g, int i)
+{
+    if constexpr (FMT == Q4_K) {
+        r.q = ld_stream_u4(g.nib + i * 512);
+        r.sm = ld_nc_u16(g.sc + i * 64);
+        r.dd = ld_sup32(g.sup + i * 16, A4);
+    } else if constexpr (FMT == Q5_K) {
+        r.q = ld_stream_u4(g.nib + i * 512);
+        r.qh = ld_stream_u32(g.aux + i * 128);
+        r.sm = ld_nc_u16(g.sc + i * 64);
+        r.dd = ld_sup32(g.sup + i * 16, A4);
+    } else if constexpr (FMT == Q6_K) {
+        r.q = ld_stream_u4(g.nib + i * 512);
+        r.h = ld_stream_u2(g.aux + i * 256);
+        r.sm = ld_nc_u16(g.sc + i * 64);
+        r.d = ld_nc_u16(g.sup + i * 8);
+    } else if constexpr (FMT == Q8_0) {
+        r.wl = ld_stream_u4(g.nib + i * 512);
+        r.wh = ld_stream_u4(g.aux + i * 512);
+        r.d = ld_nc_u16(g.sc + i * 64);
+    } else {
+        r.q = ld_stream_u4(g.nib + i * 512);
+        r.d = ld_nc_u16(g.sc + i * 64);
+    }
+}
+
+template <int FMT>
+__device__ __forceinline__ GroupPtrs group_ptrs(const Planes &p, uint32_t row, uint32_t sb0)
+{
+    constexpr uint32_t aux_b = FMT == Q5_K ? 4 : FMT == Q6_K ? 8 : FMT == Q8_0 ? 16 : 0;
+    constexpr uint32_t sup_b = FMT == Q6_K ? 2 : 4;
+    const size_t idx = (size_t)row * p.nsp + sb0;
+    GroupPtrs g;
+    g.nib = p.nib + idx * 16;
+    g.aux = aux_b ? p.aux + idx * aux_b : nullptr;
+    g.sc = p.sc + idx * 2;
+    g.sup = (FMT == Q4_K || FMT == Q5_K || FMT == Q6_K) ? p.sup + ((size_t)row * p.n_super + (sb0 >> 3)) * sup_b : nullptr;
+    return g;
+}
+
 // unsigned bytes x signed bytes
 __device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c)
 {
@@ -313,11 +362,14 @@ stream_body(uint8_t *smem, const uint8_t *__restrict__ w, const uint8_t *__restr
         row = min(row, out_dim - 1u);
         const size_t rbase = (size_t)row * p.nsp, sbase = (size_t)row * p.n_super;
         if (lanes_full(it, n)) {
+            const GroupPtrs g = group_ptrs<FMT>(p, row, it * 32u + lane);
             with_count(n, [&](auto nc) {
+                if (sup_a4) {
 #pragma unroll
-                for (int i = 0; i < decltype(nc)::value; i++) {
-                    const uint32_t sb = (it + i) * 32u + lane;
-                    fetch<FMT>(cur[i], p, rbase + sb, sbase + (sb >> 3), sup_a4);
+                    for (int i = 0; i < decltype(nc)::value; i++) fetch_off<FMT, true>(cur[i], g, i);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < decltype(nc)::value; i++) fetch_off<FMT, false>(cur[i], g, i);
                 }
             });
         } else {
@@ -447,6 +499,10 @@ matvec_stream_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ 
 // Expert-grouped form: blockIdx.y is a global token tile, mapped to (expert, local tile) by
 // binary search over tile_off as in kernels/mmq_gemm_q4k_grouped.cpp:49-60; the tile's rows
 // of xq / y are contiguous in expert-sorted order.
+// A tile of the sort is kGroupedTile tokens; this kernel takes it as halves of BN = 16 rows
+// (blockIdx.y = 2 * tile + half).
+constexpr int kGroupedTile = 32;
+
 template <int FMT, int BN>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, MinBlocks<BN>::v)
 matvec_grouped_kernel(const uint8_t *__restrict__ slab, size_t bytes_per_expert,
@@ -455,7 +511,7 @@ matvec_grouped_kernel(const uint8_t *__restrict__ slab, size_t bytes_per_expert,
                       uint32_t in_dim, uint32_t out_dim)
 {
     extern __shared__ __align__(16) uint8_t smem[];
-    const uint32_t by = blockIdx.y;
+    const uint32_t by = blockIdx.y / (kGroupedTile / BN), part = blockIdx.y % (kGroupedTile / BN);
     if (by >= (uint32_t)tile_off[n_expert]) return; // over-launched tile
     uint32_t lo = 0, hi = n_expert;
     while (lo + 1 < hi) {
@@ -463,7 +519,8 @@ matvec_grouped_kernel(const uint8_t *__restrict__ slab, size_t bytes_per_expert,
         if ((uint32_t)tile_off[mid] <= by) lo = mid; else hi = mid;
     }
     const uint32_t e = lo;
-    const uint32_t tok0 = (uint32_t)expert_off[e] + (by - (uint32_t)tile_off[e]) * BN;
+    const uint32_t tok0 = (uint32_t)expert_off[e] + (by - (uint32_t)tile_off[e]) * kGroupedTile + part * BN;
+    if (tok0 >= (uint32_t)expert_off[e + 1]) return; // the tile's second half is empty
     const uint32_t n = min((uint32_t)BN, (uint32_t)expert_off[e + 1] - tok0);
     const uint32_t n_sub = in_dim >> 5;
     stream_body<FMT, BN, false>(smem, slab + (size_t)e * bytes_per_expert,
@@ -582,7 +639,7 @@ int launch_grouped_fmt(cudaStream_t s, const void *slab, size_t bpe, const int32
     if (smem > kMaxStageBytesHost) return RC_ERR_BAD_SHAPE;
     const uint32_t n_blocks = (out_dim + kWarpsPerCta - 1) / kWarpsPerCta;
     const uint32_t gx = min(n_blocks, 8u);
-    const uint32_t tiles_ub = (n_entries + BN - 1) / BN + n_expert;
+    const uint32_t tiles_ub = ((n_entries + kGroupedTile - 1) / kGroupedTile + n_expert) * (kGroupedTile / BN);
     if (tiles_ub > 65535u) return RC_ERR_BAD_ARGUMENT;
     matvec_grouped_kernel<FMT, BN><<<dim3(gx, tiles_ub), kWarpsPerCta * 32, smem, s>>>(
         (const uint8_t *)slab, bpe, expert_off, tile_off, n_expert, (const uint8_t *)xq, y, in_dim,
@@ -604,7 +661,7 @@ int matvec_set_attributes()
     return rc;
 }
 
-// dp4a grouped GEMM with a 16-token tile: every tile streams its expert's weights once.
+// dp4a grouped GEMM: every 16-token half tile streams its expert's weights once.
 int launch_matvec_grouped(cudaStream_t s, int type, const void *slab, size_t bpe,
                           const int32_t *expert_off, const int32_t *tile_off, uint32_t n_expert,
                           const void *xq, float *y, uint32_t in_dim, uint32_t out_dim,
@@ -623,7 +680,7 @@ int launch_matvec_grouped(cudaStream_t s, int type, const void *slab, size_t bpe
     return RC_ERR_BAD_TYPE;
 }
 
-uint32_t matvec_grouped_bn() { return kGroupedBN; }
+uint32_t matvec_grouped_bn() { return kGroupedTile; }
 
 void matvec_set_tuning(int ks, int grid_mult, int no_pdl)
 {

@@ -163,6 +163,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
                  : "r"(taddr)
                  : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+                   "=r"(r[15])
+                 : "r"(taddr)
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, K-major, no swizzle (version 1 = sm_100).
@@ -513,7 +523,10 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const MmqParams P)
 #pragma unroll
                         for (int ch = 0; ch < CHUNKS; ch++) {
                             uint32_t d[32];
-                            tmem_ld32(tmem_base + ((quarter * 32u) << 16) + b * BN + half * COLS + ch * 32, d);
+                            if constexpr (CW == 32)
+                                tmem_ld32(tmem_base + ((quarter * 32u) << 16) + b * BN + half * COLS + ch * 32, d);
+                            else
+                                tmem_ld16(tmem_base + ((quarter * 32u) << 16) + b * BN + half * COLS, d);
                             tmem_wait_ld();
                             if (ch == CHUNKS - 1) {
                                 // every column of this warp's share is in registers: release the buffer
@@ -642,6 +655,11 @@ int mmq_set_attributes()
     rc |= set_attr<Q4_K, kDenseBN>();
     rc |= set_attr<Q5_K, kDenseBN>();
     rc |= set_attr<IQ4_XS, kDenseBN>();
+    rc |= set_attr<Q4_0, kGroupedBN>();
+    rc |= set_attr<Q8_0, kGroupedBN>();
+    rc |= set_attr<Q4_K, kGroupedBN>();
+    rc |= set_attr<Q5_K, kGroupedBN>();
+    rc |= set_attr<IQ4_XS, kGroupedBN>();
     return rc;
 }
 
@@ -690,11 +708,37 @@ int launch_mmq_gemm(cudaStream_t s, int type, const void *w, const void *xq, flo
     return RC_OK;
 }
 
+// Expert tiles are kGroupedBN tokens wide (the width rc_moe_sort must be given): at a mean of
+// 16 tokens per expert a wider tile would be mostly padding, and the kernel is bound by the
+// expert weights it streams, not by the MMA shape.
 int launch_mmq_grouped(cudaStream_t s, int type, const void *slab, size_t bytes_per_expert,
                        const int32_t *expert_off, const int32_t *tile_off, uint32_t n_expert,
                        const void *xq, float *y, uint32_t in_dim, uint32_t out_dim,
                        uint32_t n_entries)
 {
+    if (type != Q6_K && !g_force_dp4a) {
+        MmqParams P;
+        P.w = (const uint8_t *)slab;
+        P.bytes_per_expert = bytes_per_expert;
+        P.expert_off = expert_off;
+        P.tile_off = tile_off;
+        P.n_expert = n_expert;
+        P.xq = (const uint8_t *)xq;
+        P.y = y;
+        P.in_dim = in_dim;
+        P.out_dim = out_dim;
+        P.n_tok = n_entries;
+        // the tile count lives on the device (tile_off[n_expert]); this is its upper bound
+        const uint32_t tiles = ((out_dim + kBM - 1) / kBM) * ((n_entries + kGroupedBN - 1) / kGroupedBN + n_expert);
+        switch (type) {
+        case Q4_0: return launch_tc<Q4_0, kGroupedBN>(s, P, tiles);
+        case Q8_0: return launch_tc<Q8_0, kGroupedBN>(s, P, tiles);
+        case Q4_K: return launch_tc<Q4_K, kGroupedBN>(s, P, tiles);
+        case Q5_K: return launch_tc<Q5_K, kGroupedBN>(s, P, tiles);
+        case IQ4_XS: return launch_tc<IQ4_XS, kGroupedBN>(s, P, tiles);
+        }
+        return RC_ERR_BAD_TYPE;
+    }
     return launch_matvec_grouped(s, type, slab, bytes_per_expert, expert_off, tile_off, n_expert,
                                  xq, y, in_dim, out_dim, n_entries);
 }
