@@ -93,6 +93,52 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def moe_layer(rt, synth, torch, dev, timed):
+    """Config 5: 256 experts, top-8 of 512 tokens, hidden 2048, expert FFN 512: sort, gather,
+    grouped gate+up GEMM (Q4_K [1024, 2048] per expert), SwiGLU glue (torch), quantize, grouped down
+    GEMM (Q6_K [2048, 512]), scatter.  HBM-bound: the figure of merit is expert-weight bytes / s."""
+    E, H, F, NT, K = 256, 2048, 512, 512, 8
+    lib_tile = 8  # experts' worth of distinct blocks, tiled to 256 experts (bytes are what matter)
+
+    def slab(t, in_dim, out_dim, seed):
+        one = synth.synth_blocks(t, in_dim, out_dim * lib_tile, seed)
+        return rt.GpuExpertTensor.from_bytes(np.tile(one, E // lib_tile), t, in_dim, out_dim, E, device=dev)
+
+    gu, dn = slab(Q4_K, H, 2 * F, 91), slab(Q6_K, F, H, 92)
+    logits = torch.from_numpy(synth.synth_router_logits(NT, E, 93)).to(dev)
+    ids = torch.topk(torch.softmax(logits, -1), K, dim=-1).indices.to(torch.int32).reshape(-1).contiguous()
+    NE = NT * K
+    x = torch.from_numpy(synth.synth_activations(NT, H, 94)).to(dev)
+    moe = rt.MoeGroupedScratch.new(E, NE, device=dev)
+    u8 = dict(dtype=torch.uint8, device=dev)
+    xq, xg = torch.empty(NT * (H // 32) * 40, **u8), torch.empty(NE * (H // 32) * 40, **u8)
+    hq = torch.empty(NE * (F // 32) * 40, **u8)
+    y1, h = torch.empty(NE, 2 * F, device=dev), torch.empty(NE, F, device=dev)
+    y2, out = torch.empty(NE, H, device=dev), torch.empty(NE, H, device=dev)
+
+    def step(i):
+        rt.launch_quantize_q8(x, xq, H, NT)
+        rt.launch_moe_sort(moe, ids, NE)
+        rt.launch_moe_gather_xq(moe, xq, xg, H // 32, K, NE)
+        rt.launch_moe_grouped_gemm(moe, gu, xg, y1, H, 2 * F, NE)
+        torch.mul(torch.nn.functional.silu(y1[:, :F]), y1[:, F:], out=h)  # glue, not part of the path
+        rt.launch_quantize_q8(h, hq, F, NE)
+        rt.launch_moe_grouped_gemm(moe, dn, hq, y2, F, H, NE)
+        rt.launch_moe_scatter_rows(moe, y2, out, H, NE)
+
+    reps = 10
+    us = timed(step, reps, 3) / reps * 1e3
+    us_gu = timed(lambda i: rt.launch_moe_grouped_gemm(moe, gu, xg, y1, H, 2 * F, NE), reps, 3) / reps * 1e3
+    us_dn = timed(lambda i: rt.launch_moe_grouped_gemm(moe, dn, hq, y2, F, H, NE), reps, 3) / reps * 1e3
+    wbytes = gu.data.numel() + dn.data.numel()
+    peak, _ = measured_peaks()
+    return {"workload": "config 5: 256 experts top-8, 512 tokens, hidden 2048, ffn 512 (548.9 MB of expert weights, 25.8 GOP)",
+            "us_layer": us, "tok_per_s_per_layer": NT / (us * 1e-6), "tops": 2.0 * NE * (H * 2 * F + F * H) / us / 1e6,
+            "us_gate_up": us_gu, "us_down": us_dn,
+            "roofline": {"bound": "hbm", "achieved": wbytes / us / 1e3, "peak": peak, "unit": "GB/s",
+                         "frac": wbytes / us / 1e3 / peak, "note": "expert-weight bytes over the whole layer time"}}
+
+
 # ------------------------------------------------------------------------------------- CPU arm
 
 
@@ -183,7 +229,8 @@ def workload_config(n_gpus: int) -> dict:
         "workload": "config 2: dense-27B decode FFN projections, batch 1 (Q4_K gate+up 5120->17408, Q6_K down 17408->5120)",
         "bytes_per_step": 176168960,
         "l2": "weights rotate over 3 distinct layer copies (528 MB > 4x L2); every launch reads cold HBM",
-        "parallelism": f"row-shard x{n_gpus} + all-gather" if n_gpus > 1 else "single GPU",
+        "parallelism": (f"row-shard x{n_gpus}; all-gather of the quantized intermediate and of down's output (NCCL)"
+                        if n_gpus > 1 else "single GPU"),
     }
 
 
@@ -275,24 +322,32 @@ def run_gpu_arm(args):
     yd_host = torch.empty(HIDDEN, dtype=torch.float32).pin_memory()
     launches_per_step = 5
 
+    # N > 1: gate and up stay sharded (the activation between them and down is elementwise); each
+    # rank quantizes its 1/N of the intermediate and the BlockQ8 shards are all-gathered (21.7 KB
+    # instead of 2 x 68 KB of f32); down's output rows are all-gathered for the next layer.
+    h_local = FFN // world
+    hq_local = torch.empty((h_local // 32) * 40, dtype=torch.uint8, device=dev) if world > 1 else hq
+
     def step(c: int):
         ws = copies[c % n_copies]
         rt.launch_quantize_q8(x_dev, xq, HIDDEN, 1)
         rt.launch_matvec_xq8(ws[0], xq, y_gate)
         rt.launch_matvec_xq8(ws[1], xq, y_up)
-        rt.launch_quantize_q8(h_dev, hq, FFN, 1)
+        if world > 1:
+            rt.launch_quantize_q8(h_dev[:, rank * h_local:(rank + 1) * h_local], hq_local, h_local, 1)
+            dist.all_gather_into_tensor(hq, hq_local)
+        else:
+            rt.launch_quantize_q8(h_dev, hq, FFN, 1)
         rt.launch_matvec_xq8(ws[2], hq, y_down)
         if world > 1:
-            dist.all_gather_into_tensor(g_gate, y_gate)
-            dist.all_gather_into_tensor(g_up, y_up)
             dist.all_gather_into_tensor(g_down, y_down)
 
     def step_e2e(c: int):
         x_dev.copy_(x_host, non_blocking=True)
         h_dev.copy_(h_host, non_blocking=True)
         step(c)
-        yg_host.copy_(g_gate, non_blocking=True)
-        yu_host.copy_(g_up, non_blocking=True)
+        yg_host[:y_gate.numel()].copy_(y_gate, non_blocking=True)
+        yu_host[:y_up.numel()].copy_(y_up, non_blocking=True)
         yd_host.copy_(g_down, non_blocking=True)
 
     def barrier():
@@ -318,6 +373,8 @@ def run_gpu_arm(args):
 
     # The decode loop is launch-bound from Python (8 us kernels), so the steps are replayed
     # from a CUDA graph, as the reference's engine replays its forward (graph of n_copies steps).
+    # (Replaying NCCL collectives captured together with these launches hung on 2 GPUs, so with
+    # N > 1 the steps are launched eagerly and are bound by host launch latency.)
     use_graph = world == 1 and not args.no_graph
     if use_graph:
         side = torch.cuda.Stream()
@@ -385,9 +442,10 @@ def run_gpu_arm(args):
     ms_6 = timed(q6_only, reps, 5)
     q6_us = ms_6 * 1e3 / (reps * len(downs))
 
-    mmq = None
+    mmq = moe = None
     if world == 1 and not args.skip_mmq:
         mmq = mmq_prefill(rt, synth, torch, dev, timed)
+        moe = moe_layer(rt, synth, torch, dev, timed)
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
@@ -398,7 +456,7 @@ def run_gpu_arm(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 dp4a, f32 accumulate",
             "data": "synthetic", "config": workload_config(world),
             "e2e": {"value": e2e_value, "unit": "GB/s",
-                    "h2d_bytes_per_step": (HIDDEN + FFN) * 4, "d2h_bytes_per_step": (2 * FFN + HIDDEN) * 4,
+                    "h2d_bytes_per_step": (HIDDEN + FFN) * 4, "d2h_bytes_per_step": (2 * FFN // world + HIDDEN) * 4,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": launches_per_step * steps_timed,
             "clocks": clocks,
@@ -414,6 +472,8 @@ def run_gpu_arm(args):
         }
         if mmq is not None:
             line["mmq_prefill"] = mmq
+        if moe is not None:
+            line["moe_grouped"] = moe
         if world == 1 and not args.no_cpu_baseline:
             v, sample, _ = cpu_layer_sample(seconds=12.0, threads=os.cpu_count() or 1)
             line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port",

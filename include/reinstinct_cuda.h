@@ -148,9 +148,11 @@ int rc_matvec_block_dots(void *stream, int ggml_type, const void *w, const void 
  * stream serialization).  No counterpart in the reference, whose geometry is fixed in its wrappers
  * (src/runtime/gemma4.rs:1530-1551). */
 void rc_tune_matvec(int ks, int grid_mult, int no_pdl);
-/* Measurement aid: force_dp4a != 0 sends rc_mmq_gemm through the dp4a kernel instead of the
- * tensor-core kernel, for A/B timing of the two. */
-void rc_tune_mmq(int force_dp4a);
+/* Measurement aid: force_dp4a != 0 sends the MMQ entry points through the dp4a kernel instead of
+ * the tensor-core kernels; the low byte of kind forces the int8-operand (8) or f16-operand (16)
+ * tcgen05 kernel, 0 restores the per-format choice; the upper bits are a mask of pipeline parts
+ * the f16 kernel skips (its results are then invalid) — for A/B timing and cross-checking. */
+void rc_tune_mmq(int force_dp4a, int kind);
 /* Reads (synchronously) the device-side status word: 0, or the code of the bounded wait that
  * gave up inside the tensor-core GEMM.  A nonzero value means the affected outputs are invalid;
  * the context stays usable.  hipDeviceSynchronize + error check in the reference's tests

@@ -45,7 +45,7 @@ _SIGNATURES = {
     "rc_matvec_f32_noalloc": (_i, [_vp, _i, _vp, _vp, _vp, _u32, _u32]),
     "rc_matvec_block_dots": (_i, [_vp, _i, _vp, _vp, _vp, _u32, _u32, _u32]),
     "rc_tune_matvec": (None, [_i, _i, _i]),
-    "rc_tune_mmq": (None, [_i]),
+    "rc_tune_mmq": (None, [_i, _i]),
     "rc_device_status": (_i, [C.POINTER(C.c_uint)]),
     "rc_mmq_gemm": (_i, [_vp, _i, _vp, _vp, _vp, _u32, _u32, _u32]),
     "rc_matmul": (_i, [_vp, _i, _vp, _vp, _vp, _u32, _u32, _u32, _vp, _sz]),

@@ -449,7 +449,11 @@ namespace rc {
 void matvec_set_tuning(int ks, int grid_mult, int no_pdl);
 } // namespace rc
 extern "C" void rc_tune_matvec(int ks, int grid_mult, int no_pdl) { rc::matvec_set_tuning(ks, grid_mult, no_pdl); }
-extern "C" void rc_tune_mmq(int force_dp4a) { rc::mmq_force_dp4a(force_dp4a); }
+extern "C" void rc_tune_mmq(int force_dp4a, int kind)
+{
+    rc::mmq_force_dp4a(force_dp4a);
+    rc::mmq_set_kind(kind);
+}
 extern "C" int rc_device_status(unsigned int *status)
 {
     if (!status) return RC_ERR_NULL_POINTER;

@@ -35,6 +35,7 @@ int mmq_set_attributes();
 uint32_t mmq_grouped_bn();
 uint32_t matvec_grouped_bn();
 void mmq_force_dp4a(int on);
+void mmq_set_kind(int kind);
 int mmq_device_error(unsigned int *out);
 
 int launch_moe_sort(cudaStream_t s, const int32_t *ids, uint32_t n_entries, uint32_t n_expert,

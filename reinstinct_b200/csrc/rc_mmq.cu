@@ -55,6 +55,8 @@ struct MmqParams {
     float *y;
     uint32_t in_dim, out_dim;
     uint32_t n_tok;             // P (dense) or n_entries (grouped)
+    uint32_t b_tma;             // BlockQ8 rows are fetched by TMA (base 16-byte aligned, even sub-block count)
+    uint32_t debug;             // measurement aid: bit mask of pipeline parts to skip (results invalid)
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
@@ -117,6 +119,13 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, "
                  "%4, %5}], [%6];" ::"r"(dst),
                  "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(map), "r"(c0), "r"(c1), "r"(bar)
                  : "memory");
 }
 
@@ -580,6 +589,498 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const MmqParams P)
     }
 }
 
+// =====================================================================================================
+// The same GEMM with the operands held as f16 (tcgen05 kind::f16, f32 accumulator).
+//
+// Every operand value is a small integer that f16 represents exactly (|v| <= 2048), every product
+// and every 32-term sum stays below 2^24, so the f32 accumulator in tensor memory holds the exact
+// integer the int8 MMA would produce — already as a float, which removes the int->float step of the
+// drain.  And because the operand is no longer limited to 8 bits, the integer sub-block scale of the
+// K-quants rides inside it: A = sc * q (at most 63 * 31 = 1953), so the drain multiplies by the
+// per-superblock f16 d instead of a per-sub-block product.  Q6_K, whose (q - 32) * sc reaches 4096,
+// is split exactly as (q - 32) * 2*(sc >> 1) + (q - 32) * (sc & 1): two operands accumulated into the
+// same tile, which also gives each 16-weight half its own scale (one K=16 MMA per half).
+// Per (row, token, sub-block) the drain is then  acc += d * (dx * D)  [- (dmin * m) * xsum].
+//
+// Layout: a 128 x 32-element f16 operand is [kc 0..3][row][16 B] (core matrices of 8 rows x 8
+// halves); one K=16 MMA reads two adjacent kc blocks.  Roles: warp 0 TMA, warp 1 MMA issue, warps
+// 2..5 expanders, warps 6.. epilogue (16 warps of 32 columns for the dense tile: four per scheduler,
+// so that one warp's tensor-memory load and barrier latency hides behind the others' math).
+
+constexpr int kKS16 = 2;      // sub-blocks per stage
+constexpr int kExpanders16 = 64;
+
+__device__ unsigned int g_mmq16_error;
+
+__device__ __forceinline__ bool mbar_wait16(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, uint32_t code)
+{
+    if (mbar_try(bar, parity)) return true;
+    const uint64_t t0 = global_ns();
+    for (uint32_t spin = 1;; spin++) {
+        if (mbar_try(bar, parity)) return true;
+        if ((spin & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > kWaitLimitNs) break;
+        }
+    }
+    atomicExch(&g_mmq16_error, code);
+    *abort_flag = 1u;
+    return false;
+}
+
+// D[128 x N] (f32) (+)= A[128 x 16] * B[N x 16]^T, f16 operands from shared memory.
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+                 "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+// f32 accumulator, f16 A and B, both K-major, M = 128
+__host__ __device__ constexpr uint32_t make_idesc_f16(uint32_t n)
+{
+    return (1u << 4) | ((n >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+
+template <int FMT> struct Mmq16Traits {
+    static constexpr bool has_min = (FMT == Q4_K || FMT == Q5_K);
+    static constexpr bool fold = (FMT == Q4_K || FMT == Q5_K || FMT == Q6_K); // integer scale inside A
+    static constexpr int a_parts = (FMT == Q6_K) ? 2 : 1;                     // operands accumulated per sub-block
+    static constexpr int raw_planes = (FMT == Q8_0) ? 2 : 1;
+    static constexpr uint32_t raw_bytes = raw_planes * kBM * 16;
+    static constexpr int stages = (FMT == Q6_K) ? 3 : 4; // Q6_K carries two A operands per sub-block
+};
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
+
+// Four unsigned bytes (each < 256) -> two half2 words holding 1024 + byte: 0x64 in the high byte of
+// each half makes the exponent 2^10, the byte lands in the mantissa.
+__device__ __forceinline__ void bytes_to_h2_biased(uint32_t t, uint32_t &p01, uint32_t &p23)
+{
+    p01 = __byte_perm(t, 0x64646464u, 0x4140u);
+    p23 = __byte_perm(t, 0x64646464u, 0x4342u);
+}
+
+// Eight weights (two words of four unsigned bytes) -> one 16-byte kc block of the operand, computed
+// as  (1024 + byte) * mul + add  in half2 (one rounding of an exactly representable result).
+__device__ __forceinline__ uint4 kc_block(uint32_t t0, uint32_t t1, __half2 mul, __half2 add)
+{
+    uint32_t a, b, c, d;
+    bytes_to_h2_biased(t0, a, b);
+    bytes_to_h2_biased(t1, c, d);
+    return make_uint4(h2_as_u32(__hfma2(u32_as_h2(a), mul, add)), h2_as_u32(__hfma2(u32_as_h2(b), mul, add)),
+                      h2_as_u32(__hfma2(u32_as_h2(c), mul, add)), h2_as_u32(__hfma2(u32_as_h2(d), mul, add)));
+}
+
+// One (row, sub-block): raw bytes -> the f16 operand rows.  out[part][kc]: part 0 (and 1 for Q6_K).
+// sm: the sub-block's scale word (K-quants: sc | m << 8; Q6_K: sc_lo | sc_hi << 8).
+template <int FMT>
+__device__ __forceinline__ void expand_f16(const uint4 &q, const uint4 &q2, uint32_t extra0, uint32_t extra1, uint32_t sm,
+                                           uint4 (&out)[2][4])
+{
+    const uint32_t M = 0x0F0F0F0Fu;
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    uint32_t lo[4], hi[4]; // unsigned byte values of weights 4j..4j+3 and 16+4j..16+4j+3
+    if constexpr (FMT == Q4_K || FMT == Q4_0) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) { lo[j] = w[j] & M; hi[j] = (w[j] >> 4) & M; }
+    } else if constexpr (FMT == Q5_K) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            lo[j] = (w[j] & M) | bits4_to_bit4(extra0 >> (8 * j));
+            hi[j] = ((w[j] >> 4) & M) | bits4_to_bit4(extra0 >> (8 * j + 4));
+        }
+    } else if constexpr (FMT == Q6_K) {
+        uint32_t g[8];
+        spread_fields4(extra0, g[0], g[1], g[2], g[3]);
+        spread_fields4(extra1, g[4], g[5], g[6], g[7]);
+#pragma unroll
+        for (int j = 0; j < 4; j++) { lo[j] = (w[j] & M) | g[2 * j]; hi[j] = ((w[j] >> 4) & M) | g[2 * j + 1]; }
+    } else if constexpr (FMT == Q8_0) {
+        const uint32_t w2[4] = {q2.x, q2.y, q2.z, q2.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) { lo[j] = w[j] ^ 0x80808080u; hi[j] = w2[j] ^ 0x80808080u; } // + 128
+    } else { // IQ4_XS: codebook bytes, + 128
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            int a0, a1;
+            iq4_lookup8(w[j], a0, a1);
+            lo[j] = __byte_perm(a0, a1, 0x6420) ^ 0x80808080u;
+            hi[j] = __byte_perm(a0, a1, 0x7531) ^ 0x80808080u;
+        }
+    }
+    if constexpr (FMT == Q4_K || FMT == Q5_K) {
+        // sc * v  =  (1024 + v) * sc - 1024 * sc
+        const __half2 sc = __half2half2(__ushort2half_rn((unsigned short)(sm & 0xFFu)));
+        const __half2 nb = __hmul2(sc, __half2half2(__float2half(-1024.0f)));
+        out[0][0] = kc_block(lo[0], lo[1], sc, nb);
+        out[0][1] = kc_block(lo[2], lo[3], sc, nb);
+        out[0][2] = kc_block(hi[0], hi[1], sc, nb);
+        out[0][3] = kc_block(hi[2], hi[3], sc, nb);
+    } else if constexpr (FMT == Q6_K) {
+        // (v - 32) * sc  =  (v - 32) * 2*(sc >> 1)  +  (v - 32) * (sc & 1), per 16-weight half
+        const int s_lo = (int)(int8_t)(sm & 0xFFu), s_hi = (int)(int8_t)(sm >> 8);
+        const __half2 one = __half2half2(__float2half(1.0f)), off = __half2half2(__float2half(-1056.0f));
+        const __half2 x_lo = __half2half2(__int2half_rn(2 * (s_lo >> 1))), y_lo = __half2half2(__int2half_rn(s_lo & 1));
+        const __half2 x_hi = __half2half2(__int2half_rn(2 * (s_hi >> 1))), y_hi = __half2half2(__int2half_rn(s_hi & 1));
+        const __half2 zero = __half2half2(__float2half(0.0f));
+        const uint4 u0 = kc_block(lo[0], lo[1], one, off), u1 = kc_block(lo[2], lo[3], one, off); // v - 32
+        const uint4 u2 = kc_block(hi[0], hi[1], one, off), u3 = kc_block(hi[2], hi[3], one, off);
+        auto scale = [&](const uint4 &u, __half2 s) {
+            return make_uint4(h2_as_u32(__hfma2(u32_as_h2(u.x), s, zero)), h2_as_u32(__hfma2(u32_as_h2(u.y), s, zero)),
+                              h2_as_u32(__hfma2(u32_as_h2(u.z), s, zero)), h2_as_u32(__hfma2(u32_as_h2(u.w), s, zero)));
+        };
+        out[0][0] = scale(u0, x_lo); out[0][1] = scale(u1, x_lo); out[0][2] = scale(u2, x_hi); out[0][3] = scale(u3, x_hi);
+        out[1][0] = scale(u0, y_lo); out[1][1] = scale(u1, y_lo); out[1][2] = scale(u2, y_hi); out[1][3] = scale(u3, y_hi);
+    } else {
+        const float bias = (FMT == Q4_0) ? -1032.0f : -1152.0f; // remove 1024 and the format's offset (8 or 128)
+        const __half2 one = __half2half2(__float2half(1.0f)), off = __half2half2(__float2half(bias));
+        out[0][0] = kc_block(lo[0], lo[1], one, off);
+        out[0][1] = kc_block(lo[2], lo[3], one, off);
+        out[0][2] = kc_block(hi[0], hi[1], one, off);
+        out[0][3] = kc_block(hi[2], hi[3], one, off);
+    }
+}
+
+template <int FMT, int BN> struct Smem16 {
+    static constexpr uint32_t stages = Mmq16Traits<FMT>::stages;
+    static constexpr uint32_t raw_stage = kKS16 * Mmq16Traits<FMT>::raw_bytes;
+    static constexpr uint32_t a_part = kBM * 64;                                  // one operand of one sub-block
+    static constexpr uint32_t a_sub = a_part * Mmq16Traits<FMT>::a_parts;
+    static constexpr uint32_t b_sub = BN * 64, sx_sub = BN * 4;
+    static constexpr uint32_t braw_stage = BN * kKS16 * RC_BLOCKQ8_BYTES;         // [token][kKS16 blocks of 40 B]
+    static constexpr uint32_t rsc_stage = (kKS16 + 1) * kBM * 4;                  // row scale words + superblock word
+    static constexpr uint32_t raw_off = 0;
+    static constexpr uint32_t braw_off = raw_off + stages * raw_stage;
+    static constexpr uint32_t a_off = braw_off + stages * braw_stage;
+    static constexpr uint32_t b_off = a_off + stages * kKS16 * a_sub;
+    static constexpr uint32_t dx_off = b_off + stages * kKS16 * b_sub;
+    static constexpr uint32_t xs_off = dx_off + stages * kKS16 * sx_sub;
+    static constexpr uint32_t rsc_off = xs_off + stages * kKS16 * sx_sub;
+    static constexpr uint32_t bar_off = rsc_off + stages * rsc_stage;
+    static constexpr uint32_t n_bars = 4 * stages + 2 * kBufs;
+    static constexpr uint32_t misc_off = bar_off + n_bars * 8;
+    static constexpr uint32_t total = misc_off + 16 + 1024;
+};
+
+template <int FMT, int BN, int EPW>
+__global__ void __launch_bounds__((4 + EPW) * 32, 1)
+mmq16_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_b, const MmqParams P)
+{
+    using L = Smem16<FMT, BN>;
+    using T = Mmq16Traits<FMT>;
+    constexpr uint32_t kStages16 = L::stages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bars = sbase + L::bar_off;
+    auto raw_full = [&](uint32_t s) { return bars + s * 8u; };
+    auto raw_empty = [&](uint32_t s) { return bars + (kStages16 + s) * 8u; };
+    auto op_full = [&](uint32_t s) { return bars + (2 * kStages16 + s) * 8u; };
+    auto op_empty = [&](uint32_t s) { return bars + (3 * kStages16 + s) * 8u; };
+    auto tm_full = [&](uint32_t b) { return bars + (4 * kStages16 + b) * 8u; };
+    auto tm_empty = [&](uint32_t b) { return bars + (4 * kStages16 + kBufs + b) * 8u; };
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L::misc_off);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t n_sub = P.in_dim >> 5;
+    const uint32_t n_iters = (n_sub + kKS16 - 1) / kKS16;
+    const uint32_t tiles_m = (P.out_dim + kBM - 1) / kBM;
+    const uint32_t n_tiles = tile_count<BN>(P, tiles_m);
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kStages16; s++) {
+            mbar_init(raw_full(s), 1);
+            mbar_init(raw_empty(s), kExpanders16);
+            mbar_init(op_full(s), kExpanders16);
+            mbar_init(op_empty(s), EPW); // an epilogue warp arrives after the tm_full of the stage's last MMA
+        }
+        for (uint32_t b = 0; b < kBufs; b++) {
+            mbar_init(tm_full(b), 1);
+            mbar_init(tm_empty(b), EPW);
+        }
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), kBufs * BN);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 2) {
+      if (warp == 0) {
+        // ---- TMA producer: raw 16-byte planes, one box per (sub-block, plane) -----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x) {
+                const Tile t = decode_tile<BN>(P, id);
+                for (uint32_t i = 0; i < n_iters; i++, it++) {
+                    const uint32_t s = it % kStages16;
+                    if (it >= kStages16 && !mbar_wait16(raw_empty(s), ((it / kStages16) - 1u) & 1u, abort_flag, 1u)) break;
+                    const uint32_t nsteps = min((uint32_t)kKS16, n_sub - i * kKS16);
+                    if (P.debug & 8u) continue;
+                    mbar_expect_tx(raw_full(s), nsteps * T::raw_bytes + (P.b_tma ? L::braw_stage : 0u));
+                    if (P.b_tma) // BN activation rows x the stage's blocks (a partly outside box is zero-filled)
+                        tma_load_2d(sbase + L::braw_off + s * L::braw_stage, &tmap_b, raw_full(s),
+                                    (int)(i * kKS16 * RC_BLOCKQ8_BYTES), (int)t.tok0);
+                    for (uint32_t j = 0; j < nsteps; j++)
+                        for (int pl = 0; pl < T::raw_planes; pl++)
+                            tma_load_4d(sbase + L::raw_off + s * L::raw_stage + j * T::raw_bytes + pl * kBM * 16, &tmap,
+                                        raw_full(s), (int)((i * kKS16 + j) * 16u), (int)t.m0, pl, (int)t.e);
+                }
+            }
+        }
+      } else if (warp == 1) {
+        // ---- MMA issuer: two K=16 MMAs per operand part per sub-block ----------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_f16(BN);
+            uint32_t it = 0, kc = 0;
+            for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x) {
+                for (uint32_t i = 0; i < n_iters; i++, it++) {
+                    const uint32_t s = it % kStages16;
+                    if (!mbar_wait16(op_full(s), (it / kStages16) & 1u, abort_flag, 2u)) goto mma_done;
+                    tc_fence_after();
+                    const uint32_t nsteps = min((uint32_t)kKS16, n_sub - i * kKS16);
+                    for (uint32_t j = 0; j < nsteps; j++, kc++) {
+                        const uint32_t b = kc % kBufs;
+                        if (kc >= kBufs && !mbar_wait16(tm_empty(b), ((kc / kBufs) - 1u) & 1u, abort_flag, 3u)) goto mma_done;
+                        tc_fence_after();
+                        const uint32_t a0 = sbase + L::a_off + (s * kKS16 + j) * L::a_sub;
+                        const uint32_t b0 = sbase + L::b_off + (s * kKS16 + j) * L::b_sub;
+#pragma unroll
+                        for (int part = 0; part < T::a_parts; part++) {
+#pragma unroll
+                            for (int kh = 0; kh < 2; kh++) {
+                                const uint64_t da = make_desc(a0 + part * L::a_part + kh * 2 * kBM * 16, kBM * 16, 128);
+                                const uint64_t db = make_desc(b0 + kh * 2 * BN * 16, BN * 16, 128);
+                                if (!(P.debug & 128u)) mma_f16(tmem_base + b * BN, da, db, idesc, (part | kh) ? 1u : 0u);
+                            }
+                        }
+                        mma_commit(tm_full(b));
+                    }
+                }
+            }
+        mma_done:;
+        }
+      }
+    } else if (warp < 4) {
+        // ---- expanders -----------------------------------------------------------------------------
+        const uint32_t tid = threadIdx.x - 64u; // 0..63
+        constexpr int ROWS_PT = kBM / kExpanders16; // weight rows per thread
+        constexpr int ITEMS_PT = (BN * kKS16 + kExpanders16 - 1) / kExpanders16; // (token, sub-block) items per thread
+        uint32_t it = 0;
+        for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x) {
+            const Tile t = decode_tile<BN>(P, id);
+            const Planes pl = planes_of<FMT>(P.w + (size_t)t.e * P.bytes_per_expert, P.in_dim, P.out_dim);
+            for (uint32_t i = 0; i < n_iters; i++, it++) {
+                const uint32_t s = it % kStages16;
+                const uint32_t k0 = i * kKS16, nsteps = min((uint32_t)kKS16, n_sub - k0);
+                // global loads first: activations of this stage and the format's side planes
+                uint2 xb[ITEMS_PT][5];
+#pragma unroll
+                for (int n = 0; n < ITEMS_PT; n++) {
+                    const uint32_t q = tid + n * kExpanders16, tok = q % BN, j = q / BN;
+                    if (j < nsteps && tok < t.n_valid && !(P.debug & 1u) && !P.b_tma) {
+                        const uint2 *src = reinterpret_cast<const uint2 *>(
+                            P.xq + ((size_t)(t.tok0 + tok) * n_sub + k0 + j) * RC_BLOCKQ8_BYTES);
+#pragma unroll
+                        for (int w = 0; w < 5; w++) xb[n][w] = __ldg(src + w);
+                    } else {
+#pragma unroll
+                        for (int w = 0; w < 5; w++) xb[n][w] = make_uint2(0u, 0u);
+                    }
+                }
+                uint32_t e0[ROWS_PT][kKS16], e1[ROWS_PT][kKS16], smw[ROWS_PT][kKS16], ddw[ROWS_PT];
+#pragma unroll
+                for (int rr = 0; rr < ROWS_PT; rr++) {
+                    const uint32_t row = min(t.m0 + tid + rr * kExpanders16, P.out_dim - 1u);
+                    ddw[rr] = 0;
+#pragma unroll
+                    for (int j = 0; j < kKS16; j++) {
+                        e0[rr][j] = e1[rr][j] = smw[rr][j] = 0;
+                        if (j < (int)nsteps && !(P.debug & 32u)) {
+                            const size_t idx = (size_t)row * pl.nsp + k0 + j;
+                            if constexpr (FMT == Q5_K) e0[rr][j] = ld_stream_u32(pl.aux + idx * 4);
+                            if constexpr (FMT == Q6_K) {
+                                const uint2 h = ld_stream_u2(pl.aux + idx * 8);
+                                e0[rr][j] = h.x;
+                                e1[rr][j] = h.y;
+                            }
+                            smw[rr][j] = ld_nc_u16(pl.sc + idx * 2);
+                        }
+                    }
+                    // the superblock word of the stage (a stage never straddles two superblocks)
+                    if constexpr (T::has_min) {
+                        const uint8_t *sp = pl.sup + ((size_t)row * pl.n_super + (k0 >> 3)) * 4;
+                        ddw[rr] = ((reinterpret_cast<uintptr_t>(pl.sup) & 3u) == 0)
+                                      ? __ldg(reinterpret_cast<const uint32_t *>(sp))
+                                      : (ld_nc_u16(sp) | (ld_nc_u16(sp + 2) << 16));
+                    } else if constexpr (FMT == Q6_K) {
+                        ddw[rr] = ld_nc_u16(pl.sup + ((size_t)row * pl.n_super + (k0 >> 3)) * 2);
+                    }
+                }
+                if (it >= kStages16 && !mbar_wait16(op_empty(s), ((it / kStages16) - 1u) & 1u, abort_flag, 4u)) goto exp_done;
+                if (!(P.debug & 8u) && !mbar_wait16(raw_full(s), (it / kStages16) & 1u, abort_flag, 5u)) goto exp_done;
+                // A: this thread's weight rows, and their scale words for the epilogue
+#pragma unroll
+                for (int rr = 0; rr < ROWS_PT; rr++) {
+                    const uint32_t r = tid + rr * kExpanders16;
+                    uint32_t *rs = reinterpret_cast<uint32_t *>(smem + L::rsc_off + s * L::rsc_stage);
+#pragma unroll
+                    for (int j = 0; j < kKS16; j++) rs[j * kBM + r] = smw[rr][j];
+                    rs[kKS16 * kBM + r] = ddw[rr];
+#pragma unroll
+                    for (int j = 0; j < kKS16; j++) {
+                        if (j < (int)nsteps && !(P.debug & 2u)) {
+                            const uint8_t *rp = smem + L::raw_off + s * L::raw_stage + j * T::raw_bytes + r * 16u;
+                            const uint4 q = *reinterpret_cast<const uint4 *>(rp);
+                            uint4 q2 = make_uint4(0, 0, 0, 0);
+                            if constexpr (FMT == Q8_0) q2 = *reinterpret_cast<const uint4 *>(rp + kBM * 16);
+                            uint4 o[2][4];
+                            expand_f16<FMT>(q, q2, e0[rr][j], e1[rr][j], smw[rr][j], o);
+#pragma unroll
+                            for (int part = 0; part < T::a_parts; part++) {
+                                uint8_t *ap = smem + L::a_off + (s * kKS16 + j) * L::a_sub + part * L::a_part + r * 16u;
+#pragma unroll
+                                for (int c = 0; c < 4; c++) *reinterpret_cast<uint4 *>(ap + c * kBM * 16) = o[part][c];
+                            }
+                        }
+                    }
+                }
+                // B: int8 quants -> f16 in the same layout; scales beside them
+#pragma unroll
+                for (int n = 0; n < ITEMS_PT; n++) {
+                    const uint32_t q = tid + n * kExpanders16, tok = q % BN, j = q / BN;
+                    if (j < nsteps && !(P.debug & 16u)) {
+                        const __half2 one = __half2half2(__float2half(1.0f)), off = __half2half2(__float2half(-1152.0f));
+                        if (P.b_tma) {
+                            const uint2 *src = reinterpret_cast<const uint2 *>(
+                                smem + L::braw_off + s * L::braw_stage + (tok * kKS16 + j) * RC_BLOCKQ8_BYTES);
+                            const bool ok = tok < t.n_valid; // rows past the tile's tokens belong to someone else
+#pragma unroll
+                            for (int w = 0; w < 5; w++) xb[n][w] = ok ? src[w] : make_uint2(0u, 0u);
+                        }
+                        uint8_t *bp = smem + L::b_off + (s * kKS16 + j) * L::b_sub + tok * 16u;
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {
+                            const uint2 w2 = xb[n][1 + c]; // qs[8c .. 8c+7]
+                            *reinterpret_cast<uint4 *>(bp + c * BN * 16) =
+                                kc_block(w2.x ^ 0x80808080u, w2.y ^ 0x80808080u, one, off);
+                        }
+                        reinterpret_cast<uint32_t *>(smem + L::dx_off + (s * kKS16 + j) * L::sx_sub)[tok] = xb[n][0].x;
+                        reinterpret_cast<uint32_t *>(smem + L::xs_off + (s * kKS16 + j) * L::sx_sub)[tok] = xb[n][0].y;
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(op_full(s));
+                mbar_arrive(raw_empty(s));
+            }
+        }
+    exp_done:;
+    } else {
+        // ---- epilogue -------------------------------------------------------------------------------------
+        const uint32_t quarter = warp & 3u;        // tensor-memory lanes this warp may read
+        const uint32_t half = (warp - 4u) >> 2;    // which group of COLS columns
+        constexpr int COLS = BN / (EPW / 4);
+        constexpr int CHUNKS = COLS / 32 > 0 ? COLS / 32 : 1;
+        constexpr int CW = COLS < 32 ? COLS : 32;
+        static_assert(COLS == 16 || COLS % 32 == 0, "16 or a multiple of 32 columns per epilogue warp");
+        float acc[COLS];
+        uint32_t it = 0, kc = 0;
+        for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x) {
+            const Tile t = decode_tile<BN>(P, id);
+            const Planes pl = planes_of<FMT>(P.w + (size_t)t.e * P.bytes_per_expert, P.in_dim, P.out_dim);
+            const uint32_t row_raw = t.m0 + quarter * 32u + lane;
+#pragma unroll
+            for (int c = 0; c < COLS; c++) acc[c] = 0.0f;
+            for (uint32_t i = 0; i < n_iters; i++, it++) {
+                const uint32_t s = it % kStages16;
+                const uint32_t k0 = i * kKS16, nsteps = min((uint32_t)kKS16, n_sub - k0);
+                if (!mbar_wait16(op_full(s), (it / kStages16) & 1u, abort_flag, 6u)) goto epi_done;
+                // this row's scale words, staged by the expanders before op_full completed
+                const uint32_t *rs = reinterpret_cast<const uint32_t *>(smem + L::rsc_off + s * L::rsc_stage) + quarter * 32u + lane;
+                const uint32_t dd_cur = rs[kKS16 * kBM];
+                uint32_t s_cur[kKS16];
+#pragma unroll
+                for (int j = 0; j < kKS16; j++) s_cur[j] = rs[j * kBM];
+                const float d_sup = T::fold ? f16_bits_to_f32(dd_cur) : 0.0f;
+                const float dmin_sup = T::has_min ? f16_bits_to_f32(dd_cur >> 16) : 0.0f;
+#pragma unroll
+                for (int j = 0; j < kKS16; j++) {
+                    if (j < (int)nsteps) {
+                        const uint32_t b = kc % kBufs;
+                        if (!mbar_wait16(tm_full(b), (kc / kBufs) & 1u, abort_flag, 7u)) goto epi_done;
+                        tc_fence_after();
+                        const float dsc = T::fold ? d_sup : f16_bits_to_f32(s_cur[j]);
+                        const float ndeff = T::has_min ? -dmin_sup * (float)(s_cur[j] >> 8) : 0.0f;
+                        const float *dxp = reinterpret_cast<const float *>(smem + L::dx_off + (s * kKS16 + j) * L::sx_sub) + half * COLS;
+                        const float *xsp = reinterpret_cast<const float *>(smem + L::xs_off + (s * kKS16 + j) * L::sx_sub) + half * COLS;
+#pragma unroll
+                        for (int ch = 0; ch < CHUNKS; ch++) {
+                            uint32_t d[32];
+                            if (!(P.debug & 256u)) {
+                            if constexpr (CW == 32)
+                                tmem_ld32(tmem_base + ((quarter * 32u) << 16) + b * BN + half * COLS + ch * 32, d);
+                            else
+                                tmem_ld16(tmem_base + ((quarter * 32u) << 16) + b * BN + half * COLS, d);
+                            tmem_wait_ld();
+                            }
+                            if (ch == CHUNKS - 1) {
+                                tc_fence_before();
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(tm_empty(b));
+                            }
+                            if (P.debug & 4u) continue;
+#pragma unroll
+                            for (int c = 0; c < CW; c += 4) {
+                                const float4 dx4 = *reinterpret_cast<const float4 *>(dxp + ch * 32 + c);
+                                float4 xs4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if constexpr (T::has_min) xs4 = *reinterpret_cast<const float4 *>(xsp + ch * 32 + c);
+                                const float dxv[4] = {dx4.x, dx4.y, dx4.z, dx4.w};
+                                const float xsv[4] = {xs4.x, xs4.y, xs4.z, xs4.w};
+#pragma unroll
+                                for (int u = 0; u < 4; u++) {
+                                    float a = acc[ch * 32 + c + u];
+                                    a = fmaf(dsc, __uint_as_float(d[c + u]) * dxv[u], a);
+                                    if constexpr (T::has_min) a = fmaf(ndeff, xsv[u], a);
+                                    acc[ch * 32 + c + u] = a;
+                                }
+                            }
+                        }
+                        kc++;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(op_empty(s));
+            }
+            if (row_raw < P.out_dim) {
+#pragma unroll
+                for (int c = 0; c < COLS; c++) {
+                    const uint32_t col = half * COLS + c;
+                    if (col < t.n_valid) P.y[(size_t)(t.tok0 + col) * P.out_dim + row_raw] = acc[c];
+                }
+            }
+        }
+    epi_done:;
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kBufs * BN);
+    }
+}
+
 // ---- host ---------------------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -632,6 +1133,44 @@ int launch_tc(cudaStream_t s, const MmqParams &P, uint32_t tiles_upper_bound)
     return (int)cudaGetLastError();
 }
 
+// epilogue warps of the f16 kernel: 32 columns per warp for the dense tile, 16 for the expert tile
+template <int BN> struct Epw16 { static constexpr int v = BN >= 128 ? 16 : 8; };
+
+template <int FMT, int BN>
+int launch_tc16(cudaStream_t s, const MmqParams &P, uint32_t tiles_upper_bound)
+{
+    CUtensorMap map;
+    int rc = make_tmap<FMT>(&map, P.w, P.bytes_per_expert, P.expert_off ? P.n_expert : 1u, P.in_dim, P.out_dim);
+    if (rc) return rc;
+    const uint32_t grid = min(tiles_upper_bound, (uint32_t)sm_count());
+    constexpr int EPW = Epw16<BN>::v;
+    // The BlockQ8 rows go through TMA when their layout allows it: 16-byte aligned base and row
+    // pitch (an even sub-block count); otherwise the expanders fetch them with plain loads.
+    CUtensorMap map_b = map;
+    MmqParams Q = P;
+    const uint64_t pitch = (uint64_t)(P.in_dim >> 5) * RC_BLOCKQ8_BYTES;
+    Q.b_tma = 0;
+    if (((uintptr_t)P.xq & 15u) == 0 && pitch % 16 == 0 && !(P.debug & 64u)) {
+        EncodeTiledFn fn = encode_fn();
+        const cuuint64_t dims[2] = {pitch, P.n_tok};
+        const cuuint64_t strides[1] = {pitch};
+        const cuuint32_t box[2] = {kKS16 * RC_BLOCKQ8_BYTES, (cuuint32_t)BN};
+        const cuuint32_t estr[2] = {1, 1};
+        if (fn && fn(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(P.xq), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+            Q.b_tma = 1;
+    }
+    mmq16_kernel<FMT, BN, EPW><<<grid, (4 + EPW) * 32, Smem16<FMT, BN>::total, s>>>(map, map_b, Q);
+    return (int)cudaGetLastError();
+}
+
+template <int FMT, int BN> int set_attr16()
+{
+    return (int)cudaFuncSetAttribute(mmq16_kernel<FMT, BN, Epw16<BN>::v>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)Smem16<FMT, BN>::total);
+}
+
 template <int FMT, int BN> int set_attr()
 {
     return (int)cudaFuncSetAttribute(mmq_kernel<FMT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -642,6 +1181,8 @@ constexpr int kDenseBN = 128;
 constexpr int kGroupedBN = 32;
 
 bool g_force_dp4a = false;
+int g_mmq_debug = 0;
+int g_mmq_kind = 0; // 0: by format (int8 operands, f16 for Q6_K); 16 / 8: force one kernel (8 has no Q6_K)
 
 } // namespace
 
@@ -660,14 +1201,27 @@ int mmq_set_attributes()
     rc |= set_attr<Q4_K, kGroupedBN>();
     rc |= set_attr<Q5_K, kGroupedBN>();
     rc |= set_attr<IQ4_XS, kGroupedBN>();
+    rc |= set_attr16<Q4_0, kDenseBN>() | set_attr16<Q8_0, kDenseBN>() | set_attr16<Q4_K, kDenseBN>() |
+          set_attr16<Q5_K, kDenseBN>() | set_attr16<Q6_K, kDenseBN>() | set_attr16<IQ4_XS, kDenseBN>();
+    rc |= set_attr16<Q4_0, kGroupedBN>() | set_attr16<Q8_0, kGroupedBN>() | set_attr16<Q4_K, kGroupedBN>() |
+          set_attr16<Q5_K, kGroupedBN>() | set_attr16<Q6_K, kGroupedBN>() | set_attr16<IQ4_XS, kGroupedBN>();
     return rc;
 }
 
 void mmq_force_dp4a(int on) { g_force_dp4a = on != 0; }
+void mmq_set_kind(int kind)
+{
+    g_mmq_kind = (kind & 0xFF) == 8 ? 8 : (kind & 0xFF) == 16 ? 16 : 0;
+    g_mmq_debug = kind >> 8; // upper bits: parts of the f16 kernel's pipeline to skip (timing experiments)
+}
 
 int mmq_device_error(unsigned int *out)
 {
-    return (int)cudaMemcpyFromSymbol(out, g_mmq_error, sizeof(unsigned int));
+    unsigned int a = 0, b = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&a, g_mmq_error, sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(&b, g_mmq16_error, sizeof(unsigned int));
+    *out = a | (b << 8);
+    return (int)e;
 }
 
 // Formats with one scale per 32-wide sub-block run on the tensor cores.  Q6_K scales each half
@@ -677,7 +1231,8 @@ int launch_mmq_gemm(cudaStream_t s, int type, const void *w, const void *xq, flo
                     uint32_t in_dim, uint32_t out_dim, uint32_t p_rows)
 {
     const uint32_t n_sub = in_dim >> 5;
-    if (type != Q6_K && !g_force_dp4a) {
+    const bool use16 = g_mmq_kind == 16 || (g_mmq_kind == 0 && type == Q6_K);
+    if ((type != Q6_K || use16) && !g_force_dp4a) {
         MmqParams P;
         P.w = (const uint8_t *)w;
         P.bytes_per_expert = 0;
@@ -689,7 +1244,20 @@ int launch_mmq_gemm(cudaStream_t s, int type, const void *w, const void *xq, flo
         P.in_dim = in_dim;
         P.out_dim = out_dim;
         P.n_tok = p_rows;
+        P.b_tma = 0;
+        P.debug = (uint32_t)g_mmq_debug;
         const uint32_t tiles = ((out_dim + kBM - 1) / kBM) * ((p_rows + kDenseBN - 1) / kDenseBN);
+        if (use16) {
+            switch (type) {
+            case Q4_0: return launch_tc16<Q4_0, kDenseBN>(s, P, tiles);
+            case Q8_0: return launch_tc16<Q8_0, kDenseBN>(s, P, tiles);
+            case Q4_K: return launch_tc16<Q4_K, kDenseBN>(s, P, tiles);
+            case Q5_K: return launch_tc16<Q5_K, kDenseBN>(s, P, tiles);
+            case Q6_K: return launch_tc16<Q6_K, kDenseBN>(s, P, tiles);
+            case IQ4_XS: return launch_tc16<IQ4_XS, kDenseBN>(s, P, tiles);
+            }
+            return RC_ERR_BAD_TYPE;
+        }
         switch (type) {
         case Q4_0: return launch_tc<Q4_0, kDenseBN>(s, P, tiles);
         case Q8_0: return launch_tc<Q8_0, kDenseBN>(s, P, tiles);
@@ -716,7 +1284,8 @@ int launch_mmq_grouped(cudaStream_t s, int type, const void *slab, size_t bytes_
                        const void *xq, float *y, uint32_t in_dim, uint32_t out_dim,
                        uint32_t n_entries)
 {
-    if (type != Q6_K && !g_force_dp4a) {
+    const bool use16 = g_mmq_kind == 16 || (g_mmq_kind == 0 && type == Q6_K);
+    if ((type != Q6_K || use16) && !g_force_dp4a) {
         MmqParams P;
         P.w = (const uint8_t *)slab;
         P.bytes_per_expert = bytes_per_expert;
@@ -728,8 +1297,21 @@ int launch_mmq_grouped(cudaStream_t s, int type, const void *slab, size_t bytes_
         P.in_dim = in_dim;
         P.out_dim = out_dim;
         P.n_tok = n_entries;
+        P.b_tma = 0;
+        P.debug = (uint32_t)g_mmq_debug;
         // the tile count lives on the device (tile_off[n_expert]); this is its upper bound
         const uint32_t tiles = ((out_dim + kBM - 1) / kBM) * ((n_entries + kGroupedBN - 1) / kGroupedBN + n_expert);
+        if (use16) {
+            switch (type) {
+            case Q4_0: return launch_tc16<Q4_0, kGroupedBN>(s, P, tiles);
+            case Q8_0: return launch_tc16<Q8_0, kGroupedBN>(s, P, tiles);
+            case Q4_K: return launch_tc16<Q4_K, kGroupedBN>(s, P, tiles);
+            case Q5_K: return launch_tc16<Q5_K, kGroupedBN>(s, P, tiles);
+            case Q6_K: return launch_tc16<Q6_K, kGroupedBN>(s, P, tiles);
+            case IQ4_XS: return launch_tc16<IQ4_XS, kGroupedBN>(s, P, tiles);
+            }
+            return RC_ERR_BAD_TYPE;
+        }
         switch (type) {
         case Q4_0: return launch_tc<Q4_0, kGroupedBN>(s, P, tiles);
         case Q8_0: return launch_tc<Q8_0, kGroupedBN>(s, P, tiles);

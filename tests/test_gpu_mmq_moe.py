@@ -139,3 +139,28 @@ def test_grouped_gemm_matches_oracle(rt, t, in_dim, out_dim):
     eoff = moe.expert_off.cpu().numpy()
     _, y64 = ro.grouped_q8(t, slab, et.bytes_per_expert, eoff, g.cpu().numpy(), in_dim, out_dim)
     assert ro.rel_l2(y.cpu().numpy(), y64) < F32_TOL
+
+
+@pytest.mark.parametrize("kind", [8, 16])
+@pytest.mark.parametrize("t", ro.ALL_TYPES)
+def test_mmq_both_tensor_core_kernels(rt, t, kind):
+    """The int8-operand and the f16-operand tcgen05 kernels against the oracle, dense (a ragged
+    200 x 300 problem over two token tiles) and grouped; Q6_K exists only in the f16 kernel (the
+    int8 setting then runs the dp4a kernel)."""
+    from reinstinct_b200 import _lib
+
+    lib = _lib.load()
+    lib.rc_tune_mmq(0, kind)
+    try:
+        in_dim, out_dim, p = 1024, 300, 200
+        raw, x = cases.synth_case(t, in_dim, out_dim, p, seed=7 * t + kind)
+        w = rt.GpuMatvecTensor.from_bytes_matvec(raw, t, in_dim, out_dim)
+        y = torch.full((p, out_dim), float("nan"), device="cuda")
+        rt.launch_mmq_gemm(w, quantize(rt, x), y, p)
+        torch.cuda.synchronize()
+        _, y64, _ = ro.matvec_q8(t, ro.repack(t, raw, in_dim, out_dim), ro.quantize_q8(x), in_dim, out_dim, p)
+        assert ro.rel_l2(y.cpu().numpy(), y64) < F32_TOL
+        st = __import__("ctypes").c_uint(0)
+        assert lib.rc_device_status(__import__("ctypes").byref(st)) == 0 and st.value == 0
+    finally:
+        lib.rc_tune_mmq(0, 0)
