@@ -229,8 +229,8 @@ def workload_config(n_gpus: int) -> dict:
         "workload": "config 2: dense-27B decode FFN projections, batch 1 (Q4_K gate+up 5120->17408, Q6_K down 17408->5120)",
         "bytes_per_step": 176168960,
         "l2": "weights rotate over 3 distinct layer copies (528 MB > 4x L2); every launch reads cold HBM",
-        "parallelism": (f"row-shard x{n_gpus}; all-gather of the quantized intermediate and of down's output (NCCL)"
-                        if n_gpus > 1 else "single GPU"),
+        "parallelism": (f"row-shard x{n_gpus}; all-gather of the quantized intermediate and of down's output "
+                        "(peer-memory push over NVLink, or NCCL with --nccl-gather)" if n_gpus > 1 else "single GPU"),
     }
 
 
@@ -324,9 +324,18 @@ def run_gpu_arm(args):
 
     # N > 1: gate and up stay sharded (the activation between them and down is elementwise); each
     # rank quantizes its 1/N of the intermediate and the BlockQ8 shards are all-gathered (21.7 KB
-    # instead of 2 x 68 KB of f32); down's output rows are all-gathered for the next layer.
+    # instead of 2 x 68 KB of f32); down's output rows are all-gathered for the next layer.  The
+    # gathers are rc_allgather_push (stores into peer memory over NVLink + a counter handshake),
+    # so the whole sharded step replays from one CUDA graph; --nccl-gather uses NCCL instead.
     h_local = FFN // world
     hq_local = torch.empty((h_local // 32) * 40, dtype=torch.uint8, device=dev) if world > 1 else hq
+    push = world > 1 and not args.nccl_gather
+    if push:
+        ga_h = rt.PeerAllGather(hq_local.numel())
+        ga_y = rt.PeerAllGather(y_down.numel() * 4)
+        hq_in, y_full = ga_h.buffer_ptr, ga_y
+    else:
+        hq_in = hq
 
     def step(c: int):
         ws = copies[c % n_copies]
@@ -335,12 +344,27 @@ def run_gpu_arm(args):
         rt.launch_matvec_xq8(ws[1], xq, y_up)
         if world > 1:
             rt.launch_quantize_q8(h_dev[:, rank * h_local:(rank + 1) * h_local], hq_local, h_local, 1)
-            dist.all_gather_into_tensor(hq, hq_local)
+            if push:
+                ga_h.gather(hq_local)
+            else:
+                dist.all_gather_into_tensor(hq, hq_local)
         else:
             rt.launch_quantize_q8(h_dev, hq, FFN, 1)
-        rt.launch_matvec_xq8(ws[2], hq, y_down)
+        rt.launch_matvec_xq8(ws[2], hq_in, y_down)
         if world > 1:
-            dist.all_gather_into_tensor(g_down, y_down)
+            if push:
+                ga_y.gather(y_down)
+            else:
+                dist.all_gather_into_tensor(g_down, y_down)
+
+    if push:
+        # one checked step: the gathered BlockQ8 must equal quantizing the whole vector locally
+        step(0)
+        got = torch.empty_like(hq)
+        ga_h.copy_out(got)
+        rt.launch_quantize_q8(h_dev, hq, FFN, 1)
+        torch.cuda.synchronize()
+        assert torch.equal(got, hq), "peer gather of the quantized intermediate differs from the local quantization"
 
     def step_e2e(c: int):
         x_dev.copy_(x_host, non_blocking=True)
@@ -348,7 +372,10 @@ def run_gpu_arm(args):
         step(c)
         yg_host[:y_gate.numel()].copy_(y_gate, non_blocking=True)
         yu_host[:y_up.numel()].copy_(y_up, non_blocking=True)
-        yd_host.copy_(g_down, non_blocking=True)
+        if push:
+            ga_y.copy_out(yd_host)
+        else:
+            yd_host.copy_(g_down, non_blocking=True)
 
     def barrier():
         if world > 1:
@@ -374,8 +401,8 @@ def run_gpu_arm(args):
     # The decode loop is launch-bound from Python (8 us kernels), so the steps are replayed
     # from a CUDA graph, as the reference's engine replays its forward (graph of n_copies steps).
     # (Replaying NCCL collectives captured together with these launches hung on 2 GPUs, so with
-    # N > 1 the steps are launched eagerly and are bound by host launch latency.)
-    use_graph = world == 1 and not args.no_graph
+    # --nccl-gather the steps are launched eagerly and are bound by host launch latency.)
+    use_graph = (world == 1 or push) and not args.no_graph
     if use_graph:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -458,7 +485,8 @@ def run_gpu_arm(args):
             "e2e": {"value": e2e_value, "unit": "GB/s",
                     "h2d_bytes_per_step": (HIDDEN + FFN) * 4, "d2h_bytes_per_step": (2 * FFN // world + HIDDEN) * 4,
                     "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": launches_per_step * steps_timed,
+            "gpu_launches": (launches_per_step + (2 if push else 0)) * steps_timed,
+            "gather": ("peer-push" if push else "nccl") if world > 1 else None,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "matvec_stream_kernel<Q4_K,1> 5120->%d" % (FFN // world),
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -491,6 +519,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--nccl-gather", action="store_true", help="N > 1: gather with NCCL instead of rc_allgather_push")
     ap.add_argument("--skip-mmq", action="store_true", help="leave the config-4 prefill GEMM section out")
     args = ap.parse_args()
     if args.impl == "reference":

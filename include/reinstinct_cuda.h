@@ -209,6 +209,30 @@ int rc_mmq_gemm_grouped(void *stream, int ggml_type, const void *slab,
                         const int32_t *tile_off, uint32_t n_expert, const void *xq, float *y,
                         uint32_t in_dim, uint32_t out_dim, uint32_t n_entries);
 
+/* ---- row-shard gather over NVLink peer memory ---------------------------------------------- */
+
+/* The reference has no collectives (its multi-GPU mode is layer pipelining over
+ * hipMemcpyPeerAsync, src/runtime/pipeline.rs:1-19).  Row-sharded matvec outputs of a decode
+ * step are tens of kilobytes, far below the size at which a library collective's launch latency
+ * is amortised, so the gather is one small kernel: every rank stores its shard straight into
+ * every peer's gathered buffer (peer-mapped memory), publishes a step counter in each peer's flag
+ * array and waits, with a time limit, until all peers' counters have arrived.  No host
+ * involvement, so a whole sharded layer can be replayed from one CUDA graph.
+ *
+ * rc_ipc_*: export / import a cudaMalloc'ed buffer between the processes of one box (one process
+ * per GPU); `handle` is 64 bytes.  peer_dst[r] is rank r's gathered buffer (world * bytes, own
+ * entry included), peer_flags[r] rank r's array of `world` 64-bit counters (zeroed once),
+ * epoch a 64-bit counter in this rank's memory (zeroed once); both arrays are HOST arrays of
+ * `world` <= RC_MAX_PEERS device pointers.  bytes % 16 == 0.  A wait that runs out sets the device status word
+ * (rc_device_status, bit 16) and lets the kernel end. */
+#define RC_MAX_PEERS 8
+#define RC_IPC_HANDLE_BYTES 64
+int rc_ipc_get_handle(const void *dev_ptr, void *handle);
+int rc_ipc_open_handle(const void *handle, void **dev_ptr);
+int rc_ipc_close_handle(void *dev_ptr);
+int rc_allgather_push(void *stream, const void *src, size_t bytes, void *const *peer_dst,
+                      void *const *peer_flags, void *epoch, uint32_t rank, uint32_t world);
+
 /* ---- device API mirror (src/hip/sys.rs:57-101, src/hip/mod.rs) --------------------------- */
 
 enum rc_memcpy_kind { /* src/hip/sys.rs:45-53 */

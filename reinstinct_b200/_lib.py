@@ -55,6 +55,10 @@ _SIGNATURES = {
     "rc_moe_gather_xq": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32]),
     "rc_moe_scatter_rows": (_i, [_vp, _vp, _vp, _vp, _u32, _u32]),
     "rc_mmq_gemm_grouped": (_i, [_vp, _i, _vp, _sz, _vp, _vp, _u32, _vp, _vp, _u32, _u32, _u32]),
+    "rc_ipc_get_handle": (_i, [_vp, _vp]),
+    "rc_ipc_open_handle": (_i, [_vp, C.POINTER(_vp)]),
+    "rc_ipc_close_handle": (_i, [_vp]),
+    "rc_allgather_push": (_i, [_vp, _vp, _sz, C.POINTER(_vp), C.POINTER(_vp), _vp, _u32, _u32]),
     "rc_get_device_count": (_i, [C.POINTER(_i)]),
     "rc_set_device": (_i, [_i]),
     "rc_get_device": (_i, [C.POINTER(_i)]),

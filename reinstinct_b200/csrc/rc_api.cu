@@ -314,6 +314,38 @@ int rc_mmq_gemm_grouped(void *stream, int type, const void *slab, size_t bytes_p
                               n_expert, xq, y, in_dim, out_dim, n_entries);
 }
 
+/* ---- peer gather -------------------------------------------------------------------------------- */
+
+int rc_ipc_get_handle(const void *dev_ptr, void *handle)
+{
+    if (!dev_ptr || !handle) return RC_ERR_NULL_POINTER;
+    static_assert(sizeof(cudaIpcMemHandle_t) == RC_IPC_HANDLE_BYTES, "IPC handle size");
+    return (int)cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t *>(handle), const_cast<void *>(dev_ptr));
+}
+int rc_ipc_open_handle(const void *handle, void **dev_ptr)
+{
+    if (!dev_ptr || !handle) return RC_ERR_NULL_POINTER;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, sizeof(h));
+    return (int)cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+}
+int rc_ipc_close_handle(void *dev_ptr) { return (int)cudaIpcCloseMemHandle(dev_ptr); }
+
+int rc_allgather_push(void *stream, const void *src, size_t bytes, void *const *peer_dst,
+                      void *const *peer_flags, void *epoch, uint32_t rank, uint32_t world)
+{
+    if (world == 0 || world > RC_MAX_PEERS || rank >= world) return RC_ERR_BAD_ARGUMENT;
+    if (bytes == 0) return RC_OK;
+    if (bytes % 16 || bytes / 16 > 0xFFFFFFFFull) return RC_ERR_BAD_SHAPE;
+    if (!src || !peer_dst || !peer_flags || !epoch) return RC_ERR_NULL_POINTER;
+    if ((uintptr_t)src & 15u) return RC_ERR_MISALIGNED;
+    for (uint32_t r = 0; r < world; r++) {
+        if (!peer_dst[r] || !peer_flags[r]) return RC_ERR_NULL_POINTER;
+        if (((uintptr_t)peer_dst[r] & 15u) || ((uintptr_t)peer_flags[r] & 7u)) return RC_ERR_MISALIGNED;
+    }
+    return launch_allgather_push(S(stream), src, bytes, peer_dst, peer_flags, epoch, rank, world);
+}
+
 /* ---- device API mirror ------------------------------------------------------------------- */
 
 int rc_get_device_count(int *count) { return count ? (int)cudaGetDeviceCount(count) : RC_ERR_NULL_POINTER; }
@@ -457,5 +489,10 @@ extern "C" void rc_tune_mmq(int force_dp4a, int kind)
 extern "C" int rc_device_status(unsigned int *status)
 {
     if (!status) return RC_ERR_NULL_POINTER;
-    return rc::mmq_device_error(status);
+    unsigned int g = 0;
+    int rc = rc::mmq_device_error(status);
+    if (rc) return rc;
+    rc = rc::gather_device_error(&g);
+    *status |= g << 16;
+    return rc;
 }

@@ -46,6 +46,10 @@ int launch_moe_gather_xq(cudaStream_t s, const void *xq_src, const int32_t *perm
 int launch_moe_scatter_rows(cudaStream_t s, const float *src, const int32_t *perm, float *dst,
                             uint32_t dim, uint32_t n_entries);
 
+int launch_allgather_push(cudaStream_t s, const void *src, size_t bytes, void *const *peer_dst,
+                          void *const *peer_flags, void *epoch, uint32_t rank, uint32_t world);
+int gather_device_error(unsigned int *out);
+
 // Per-device one-time setup (kernel attributes); returns RC_OK or an error.
 int ensure_device_ready();
 int sm_count();

@@ -21,7 +21,7 @@ __all__ = [
     "GpuMatvecTensor", "GpuExpertTensor", "PrefillGemm", "MoeGroupedScratch",
     "launch_quantize_q8", "launch_matvec", "launch_matvec_xq8", "launch_matvec_batched",
     "matvec_block_dots", "launch_mmq_gemm", "launch_moe_sort", "launch_moe_gather_xq",
-    "launch_moe_grouped_gemm", "launch_moe_scatter_rows", "repacked_len", "init",
+    "launch_moe_grouped_gemm", "launch_moe_scatter_rows", "repacked_len", "init", "PeerAllGather",
 ]
 
 
@@ -29,8 +29,12 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def _ptr(t: torch.Tensor | None) -> int:
-    return 0 if t is None else t.data_ptr()
+def _ptr(t) -> int:
+    """Device address of a tensor; a plain int is taken as an address already (buffers that were
+    not allocated by torch, e.g. PeerAllGather's)."""
+    if t is None:
+        return 0
+    return t if isinstance(t, int) else t.data_ptr()
 
 
 def init(device: int | None = None) -> None:
@@ -122,7 +126,7 @@ def launch_quantize_q8(x: torch.Tensor, out: torch.Tensor, in_dim: int, n_vec: i
 def launch_matvec_xq8(w: GpuMatvecTensor, xq8: torch.Tensor, y: torch.Tensor) -> None:
     """launch_matvec_xq8(w, xq8, y) (src/runtime/gemma4.rs:1526-1564)."""
     assert w.repacked, "launch_matvec_xq8 requires a repacked weight"
-    assert y.dtype == torch.float32 and y.numel() >= w.out_dim
+    assert isinstance(y, int) or (y.dtype == torch.float32 and y.numel() >= w.out_dim)
     check(_lib.load().rc_matvec(_stream(), w.dtype, _ptr(w.data), _ptr(xq8), _ptr(y), w.in_dim,
                                 w.out_dim), "rc_matvec")
 
@@ -250,3 +254,64 @@ def launch_moe_grouped_gemm(moe: MoeGroupedScratch, et: GpuExpertTensor, xq: tor
                                           _ptr(moe.expert_off), _ptr(moe.tile_off), moe.n_expert,
                                           _ptr(xq), _ptr(y), in_dim, out_dim, n_entries),
           "rc_mmq_gemm_grouped")
+
+
+class PeerAllGather:
+    """All-gather of one small shard per rank by direct stores into the peers' memory
+    (rc_allgather_push): one process per GPU on one box, buffers exported with CUDA IPC.  The
+    gathered buffer (`world * bytes_per_rank` bytes at `buffer_ptr`, rank r's shard at offset
+    r * bytes_per_rank) is written by all ranks; a call returns, on the stream, once every
+    rank's shard of this call has arrived.  Safe to capture in a CUDA graph."""
+
+    def __init__(self, bytes_per_rank: int, group=None):
+        import torch.distributed as dist
+
+        assert bytes_per_rank % 16 == 0, "shards are copied in 16-byte units"
+        lib = _lib.load()
+        self.lib, self.bytes = lib, bytes_per_rank
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        data = (self.world * bytes_per_rank + 255) // 256 * 256
+        flags = (self.world * 8 + 255) // 256 * 256
+        base = C.c_void_p()
+        check(lib.rc_malloc(C.byref(base), data + flags + 256), "rc_malloc")
+        self._base = base.value
+        check(lib.rc_memset_async(self._base, 0, data + flags + 256, _stream()), "rc_memset_async")
+        torch.cuda.current_stream().synchronize()
+        handle = (C.c_ubyte * 64)()
+        check(lib.rc_ipc_get_handle(self._base, handle), "rc_ipc_get_handle")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle), group=group)  # also orders the memset before any peer store
+        self._opened = []
+        bases = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                bases.append(self._base)
+                continue
+            p = C.c_void_p()
+            hb = (C.c_ubyte * 64).from_buffer_copy(h)
+            check(lib.rc_ipc_open_handle(hb, C.byref(p)), "rc_ipc_open_handle")
+            self._opened.append(p.value)
+            bases.append(p.value)
+        self._dst = (C.c_void_p * self.world)(*bases)
+        self._flags = (C.c_void_p * self.world)(*[b + data for b in bases])
+        self._epoch = self._base + data + flags
+        self.buffer_ptr = self._base
+        dist.barrier(group=group)
+
+    def gather(self, src) -> None:
+        check(self.lib.rc_allgather_push(_stream(), _ptr(src), self.bytes, self._dst, self._flags, self._epoch,
+                                         self.rank, self.world), "rc_allgather_push")
+
+    def copy_out(self, dst: torch.Tensor) -> None:
+        """Gathered bytes -> a torch tensor (device or pinned host), on the current stream."""
+        kind = 3 if dst.is_cuda else 2
+        check(self.lib.rc_memcpy_async(dst.data_ptr(), self.buffer_ptr, self.world * self.bytes, kind, _stream()),
+              "rc_memcpy_async")
+
+    def close(self) -> None:
+        for p in self._opened:
+            self.lib.rc_ipc_close_handle(p)
+        self._opened = []
+        if self._base:
+            self.lib.rc_free(self._base)
+            self._base = 0

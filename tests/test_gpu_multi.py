@@ -1,0 +1,82 @@
+"""Two-GPU tests (skipped on a single-GPU box): the peer-memory all-gather and a row-sharded
+matvec whose gathered output must equal the single-GPU result bit for bit."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, q):
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    for p in (str(root), str(root / "tests")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import torch.distributed as dist
+
+    import cases
+    import oracle as ro
+    from reinstinct_b200 import runtime as rt
+    from reinstinct_b200 import sharding as sh
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        rt.init(rank)
+        t, in_dim, out_dim = ro.Q4_K, 2048, 640
+        raw, x = cases.synth_case(t, in_dim, out_dim, 1, seed=5)
+        part, rows = sh.shard_raw_rows(raw, t, in_dim, out_dim, rank, world)
+        w = rt.GpuMatvecTensor.from_bytes_matvec(part, t, in_dim, rows)
+        xq = torch.empty((in_dim // 32) * 40, dtype=torch.uint8, device="cuda")
+        rt.launch_quantize_q8(torch.from_numpy(x).cuda(), xq, in_dim, 1)
+        y = torch.empty(rows, device="cuda")
+        ga = rt.PeerAllGather(rows * 4)
+        for _ in range(3):  # several rounds over the same buffers and counters
+            rt.launch_matvec_xq8(w, xq, y)
+            ga.gather(y)
+        got = torch.empty(out_dim, device="cuda")
+        ga.copy_out(got)
+        torch.cuda.synchronize()
+        full32, _, _ = ro.matvec_q8(t, ro.repack(t, raw, in_dim, out_dim), ro.quantize_q8(x), in_dim, out_dim, 1)
+        # same kernel, same rows, same arithmetic as the unsharded launch
+        w_full = rt.GpuMatvecTensor.from_bytes_matvec(raw, t, in_dim, out_dim)
+        y_full = torch.empty(out_dim, device="cuda")
+        rt.launch_matvec_xq8(w_full, xq, y_full)
+        torch.cuda.synchronize()
+        assert torch.equal(got, y_full), "gathered shards differ from the single-GPU launch"
+        assert ro.rel_l2(got.cpu().numpy(), full32.astype(np.float64)) < 1e-3
+        ga.close()
+        q.put((rank, "ok"))
+    except Exception as e:  # report instead of leaving the peer waiting
+        q.put((rank, f"{type(e).__name__}: {e}"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_gather_row_sharded_matvec_two_gpus():
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(msg == "ok" for _, msg in results), results
