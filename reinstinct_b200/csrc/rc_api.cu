@@ -170,7 +170,10 @@ int rc_matvec_block_dots(void *stream, int type, const void *w, const void *xq, 
 
 size_t rc_matmul_scratch_bytes(uint32_t in_dim, uint32_t n_rows)
 {
-    return (size_t)n_rows * (in_dim / 32) * RC_BLOCKQ8_BYTES;
+    // BlockQ8 records, or the planar form of the same values (a few bytes of row padding more)
+    const size_t records = (size_t)n_rows * (in_dim / 32) * RC_BLOCKQ8_BYTES;
+    const size_t planar = quantize_planar_bytes(in_dim, n_rows);
+    return records > planar ? records : planar;
 }
 
 int rc_matvec_f32(void *stream, int type, const void *w, const float *x, float *y, uint32_t in_dim,
@@ -197,16 +200,17 @@ int rc_matmul(void *stream, int type, const void *w, const float *x, float *y, u
     if (!x) return RC_ERR_NULL_POINTER;
     int rc = check_weight_args(type, w, xq_scratch, y, in_dim, out_dim);
     if (rc) return rc;
-    if (scratch_bytes < rc_matmul_scratch_bytes(in_dim, n_rows)) return RC_ERR_SCRATCH_TOO_SMALL;
+    if (scratch_bytes < (size_t)n_rows * (in_dim / 32) * RC_BLOCKQ8_BYTES) return RC_ERR_SCRATCH_TOO_SMALL;
     rc = ensure_device_ready();
-    if (rc) return rc;
-    rc = launch_quantize_q8(S(stream), x, xq_scratch, in_dim, n_rows);
     if (rc) return rc;
     // Row-count dispatch of PrefillGemm::matmul_into_raw (src/runtime/prefill.rs:343-437):
     // few rows stream the weights once through the matvec, more rows go to the tensor cores.
-    if (n_rows <= RC_MATVEC_MAX_ROWS)
+    if (n_rows <= RC_MATVEC_MAX_ROWS) {
+        rc = launch_quantize_q8(S(stream), x, xq_scratch, in_dim, n_rows);
+        if (rc) return rc;
         return launch_matvec(S(stream), type, w, xq_scratch, y, in_dim, out_dim, n_rows, nullptr);
-    return launch_mmq_gemm(S(stream), type, w, xq_scratch, y, in_dim, out_dim, n_rows);
+    }
+    return launch_mmq_gemm_f32(S(stream), type, w, x, y, in_dim, out_dim, n_rows, xq_scratch, scratch_bytes);
 }
 
 /* ---- allocation-free matvec ---------------------------------------------------------------- */

@@ -10,6 +10,10 @@ namespace rc {
 
 int launch_quantize_q8(cudaStream_t s, const float *x, void *xq, uint32_t in_dim, uint32_t n_vec);
 
+// planar form for the tensor-core GEMM (see rc_quantize.cu)
+size_t quantize_planar_bytes(uint32_t in_dim, uint32_t n_vec);
+int launch_quantize_q8_planar(cudaStream_t s, const float *x, void *out, uint32_t in_dim, uint32_t n_vec);
+
 int launch_repack(cudaStream_t s, int type, const void *blocks, size_t in_dim, size_t out_dim,
                   void *out);
 
@@ -27,6 +31,9 @@ int moe_set_attributes();
 
 int launch_mmq_gemm(cudaStream_t s, int type, const void *w, const void *xq, float *y,
                     uint32_t in_dim, uint32_t out_dim, uint32_t p_rows);
+// quantize + GEMM from f32 activations; uses the planar form when the scratch allows it
+int launch_mmq_gemm_f32(cudaStream_t s, int type, const void *w, const float *x, float *y, uint32_t in_dim,
+                        uint32_t out_dim, uint32_t p_rows, void *scratch, size_t scratch_bytes);
 int launch_mmq_grouped(cudaStream_t s, int type, const void *slab, size_t bytes_per_expert,
                        const int32_t *expert_off, const int32_t *tile_off, uint32_t n_expert,
                        const void *xq, float *y, uint32_t in_dim, uint32_t out_dim,

@@ -38,9 +38,7 @@ constexpr int kBM = 128;     // weight rows per tile = tensor-memory lanes
 constexpr int kKS = 4;       // sub-blocks (K=32 MMA steps) per pipeline stage
 constexpr int kStages = 4;   // operand ring depth
 constexpr int kBufs = 4;     // tensor-memory accumulator buffers
-constexpr int kThreads = 384;
 constexpr int kExpanderThreads = 64;
-constexpr int kEpilogueWarps = 8;
 constexpr uint64_t kWaitLimitNs = 500ull * 1000 * 1000; // far beyond any legal wait (microseconds)
 
 __device__ unsigned int g_mmq_error;
@@ -55,6 +53,7 @@ struct MmqParams {
     float *y;
     uint32_t in_dim, out_dim;
     uint32_t n_tok;             // P (dense) or n_entries (grouped)
+    uint32_t planar;            // activations come from rc_matmul's planar scratch through TMA (int8 kernel)
     uint32_t b_tma;             // BlockQ8 rows are fetched by TMA (base 16-byte aligned, even sub-block count)
     uint32_t debug;             // measurement aid: bit mask of pipeline parts to skip (results invalid)
 };
@@ -122,6 +121,12 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
                  : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2)
+{
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+                 "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1)
 {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
@@ -304,21 +309,52 @@ __device__ __forceinline__ Tile decode_tile(const MmqParams &P, uint32_t id)
 template <int FMT, int BN> struct Smem {
     static constexpr uint32_t raw_stage = kKS * MmqTraits<FMT>::raw_bytes;
     static constexpr uint32_t a_sub = kBM * 32, b_sub = BN * 32, sx_sub = BN * 4;
+    static constexpr uint32_t rsc_stage = (kKS + 1) * kBM * 4; // row scale words + superblock word
     static constexpr uint32_t raw_off = 0;
     static constexpr uint32_t a_off = raw_off + kStages * raw_stage;
     static constexpr uint32_t b_off = a_off + kStages * kKS * a_sub;
     static constexpr uint32_t dx_off = b_off + kStages * kKS * b_sub;
     static constexpr uint32_t xs_off = dx_off + kStages * kKS * sx_sub;
-    static constexpr uint32_t bar_off = xs_off + kStages * kKS * sx_sub;
+    static constexpr uint32_t rsc_off = xs_off + kStages * kKS * sx_sub;
+    static constexpr uint32_t bar_off = rsc_off + kStages * rsc_stage;
     // barriers: raw_full, raw_empty, op_full, op_empty [kStages each]; tm_full, tm_empty [kBufs each]
     static constexpr uint32_t n_bars = 4 * kStages + 2 * kBufs;
     static constexpr uint32_t misc_off = bar_off + n_bars * 8; // tmem base slot, abort flag
     static constexpr uint32_t total = misc_off + 16 + 1024;    // + alignment slack
 };
 
-template <int FMT, int BN>
-__global__ void __launch_bounds__(kThreads, 1)
-mmq_kernel(const __grid_constant__ CUtensorMap tmap, const MmqParams P)
+// Packed pairs of f32 (one instruction, two lanes' worth of results): halves the issue slots of the drain.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi)
+{
+    return (unsigned long long)__float_as_uint(lo) | ((unsigned long long)__float_as_uint(hi) << 32);
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b)
+{
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigned long long b)
+{
+    unsigned long long d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c)
+{
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+// EPW epilogue warps (16 for the dense tile: four per scheduler, 32 columns each; 8 for the expert
+// tile).  With P.planar the activations come from rc_matmul's planar scratch: the int8 quants land
+// by TMA directly in the operand layout and the token scales beside them, so the expanders only
+// split nibbles.
+template <int FMT, int BN, int EPW>
+__global__ void __launch_bounds__((4 + EPW) * 32, 1)
+mmq_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_b,
+           const __grid_constant__ CUtensorMap tmap_dx, const __grid_constant__ CUtensorMap tmap_xs, const MmqParams P)
 {
     using L = Smem<FMT, BN>;
     extern __shared__ uint8_t smem_raw[];
@@ -345,11 +381,11 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const MmqParams P)
             mbar_init(raw_full(s), 1);
             mbar_init(raw_empty(s), kExpanderThreads);
             mbar_init(op_full(s), kExpanderThreads);
-            mbar_init(op_empty(s), 1 + kEpilogueWarps);
+            mbar_init(op_empty(s), EPW); // an epilogue warp arrives after the tm_full of the stage's last MMA
         }
         for (uint32_t b = 0; b < kBufs; b++) {
             mbar_init(tm_full(b), 1);
-            mbar_init(tm_empty(b), kEpilogueWarps);
+            mbar_init(tm_empty(b), EPW);
         }
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -372,15 +408,27 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const MmqParams P)
                 const Tile t = decode_tile<BN>(P, id);
                 for (uint32_t i = 0; i < n_iters; i++, it++) {
                     const uint32_t s = it % kStages;
-                    if (it >= kStages && !mbar_wait(raw_empty(s), ((it / kStages) - 1u) & 1u, abort_flag, 1u)) break;
+                    if (it >= kStages) {
+                        if (!mbar_wait(raw_empty(s), ((it / kStages) - 1u) & 1u, abort_flag, 1u)) goto tma_done;
+                        // planar: this thread also overwrites the operand and scale areas of the slot
+                        if (P.planar && !mbar_wait(op_empty(s), ((it / kStages) - 1u) & 1u, abort_flag, 8u)) goto tma_done;
+                    }
                     const uint32_t nsteps = min((uint32_t)kKS, n_sub - i * kKS);
-                    mbar_expect_tx(raw_full(s), nsteps * MmqTraits<FMT>::raw_bytes);
+                    const uint32_t planar_bytes = P.planar ? kKS * (L::b_sub + 2u * L::sx_sub) : 0u; // whole boxes, zero-filled outside
+                    mbar_expect_tx(raw_full(s), nsteps * MmqTraits<FMT>::raw_bytes + planar_bytes);
                     for (uint32_t j = 0; j < nsteps; j++)
                         for (int pl = 0; pl < MmqTraits<FMT>::raw_planes; pl++)
                             tma_load_4d(sbase + L::raw_off + s * L::raw_stage + j * MmqTraits<FMT>::raw_bytes + pl * kBM * 16,
                                         &tmap, raw_full(s), (int)((i * kKS + j) * 16u), (int)t.m0, pl, (int)t.e);
+                    if (P.planar) {
+                        // (16 bytes, token, 16-byte chunk of K): lands as [chunk][token][16 B] = kKS operands [half][token][16 B]
+                        tma_load_3d(sbase + L::b_off + s * kKS * L::b_sub, &tmap_b, raw_full(s), 0, (int)t.tok0, (int)(i * kKS * 2u));
+                        tma_load_2d(sbase + L::dx_off + s * kKS * L::sx_sub, &tmap_dx, raw_full(s), (int)t.tok0, (int)(i * kKS));
+                        tma_load_2d(sbase + L::xs_off + s * kKS * L::sx_sub, &tmap_xs, raw_full(s), (int)t.tok0, (int)(i * kKS));
+                    }
                 }
             }
+        tma_done:;
         }
     } else if (warp == 1) {
         // ---- MMA issuer -------------------------------------------------------------------------
@@ -402,7 +450,6 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const MmqParams P)
                         mma_i8(tmem_base + b * BN, da, db, idesc, 0u);
                         mma_commit(tm_full(b));
                     }
-                    mma_commit(op_empty(s)); // the stage's operands are free once its MMAs have run
                 }
             }
         mma_done:;
@@ -410,46 +457,42 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const MmqParams P)
     } else if (warp < 4) {
         // ---- expanders ------------------------------------------------------------------------------
         const uint32_t tid = threadIdx.x - 64u; // 0..63
-        constexpr int ROWS_PT = kBM / kExpanderThreads;            // weight rows per thread
-        constexpr int ITEMS_PT = BN * kKS / kExpanderThreads;      // (token, sub-block) items per thread
+        constexpr int ROWS_PT = kBM / kExpanderThreads;                                // weight rows per thread
+        constexpr int ITEMS_PT = (BN * kKS + kExpanderThreads - 1) / kExpanderThreads; // (token, sub-block) items per thread
         uint32_t it = 0;
         for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x) {
             const Tile t = decode_tile<BN>(P, id);
             const Planes pl = planes_of<FMT>(P.w + (size_t)t.e * P.bytes_per_expert, P.in_dim, P.out_dim);
+            const bool sup_a4 = (reinterpret_cast<uintptr_t>(pl.sup) & 3u) == 0;
             for (uint32_t i = 0; i < n_iters; i++, it++) {
                 const uint32_t s = it % kStages;
                 const uint32_t k0 = i * kKS, nsteps = min((uint32_t)kKS, n_sub - k0);
-                // global loads first: activations of this stage (and the format's side plane)
-                uint2 xb[ITEMS_PT][5];
-#pragma unroll
-                for (int n = 0; n < ITEMS_PT; n++) {
-                    const uint32_t q = tid + n * kExpanderThreads, tok = q % BN, j = q / BN;
-                    if (j < nsteps && tok < t.n_valid) {
-                        const uint2 *src = reinterpret_cast<const uint2 *>(
-                            P.xq + ((size_t)(t.tok0 + tok) * n_sub + k0 + j) * RC_BLOCKQ8_BYTES);
-#pragma unroll
-                        for (int w = 0; w < 5; w++) xb[n][w] = __ldg(src + w);
-                    } else {
-#pragma unroll
-                        for (int w = 0; w < 5; w++) xb[n][w] = make_uint2(0u, 0u);
-                    }
-                }
+                // global loads first: side planes and row scales
                 uint32_t extra[ROWS_PT][kKS];
-                if constexpr (FMT == Q5_K) {
+                StageScales sc[ROWS_PT];
 #pragma unroll
-                    for (int rr = 0; rr < ROWS_PT; rr++) {
-                        const uint32_t row = min(t.m0 + tid + rr * kExpanderThreads, P.out_dim - 1u);
+                for (int rr = 0; rr < ROWS_PT; rr++) {
+                    const uint32_t row = min(t.m0 + tid + rr * kExpanderThreads, P.out_dim - 1u);
+                    sc[rr].dd = 0;
 #pragma unroll
-                        for (int j = 0; j < kKS; j++)
+                    for (int j = 0; j < kKS; j++) {
+                        sc[rr].s[j] = 0;
+                        extra[rr][j] = 0;
+                        if constexpr (FMT == Q5_K)
                             if (j < (int)nsteps) extra[rr][j] = ld_stream_u32(pl.aux + ((size_t)row * pl.nsp + k0 + j) * 4);
                     }
+                    load_scales<FMT>(sc[rr], pl, sup_a4, row, k0, nsteps);
                 }
                 if (it >= kStages && !mbar_wait(op_empty(s), ((it / kStages) - 1u) & 1u, abort_flag, 4u)) goto exp_done;
                 if (!mbar_wait(raw_full(s), (it / kStages) & 1u, abort_flag, 5u)) goto exp_done;
-                // A: whole weight rows of the tile
+                // A: whole weight rows of the tile, and their scale words for the epilogue
 #pragma unroll
                 for (int rr = 0; rr < ROWS_PT; rr++) {
                     const uint32_t r = tid + rr * kExpanderThreads;
+                    uint32_t *rs = reinterpret_cast<uint32_t *>(smem + L::rsc_off + s * L::rsc_stage);
+#pragma unroll
+                    for (int j = 0; j < kKS; j++) rs[j * kBM + r] = sc[rr].s[j];
+                    rs[kKS * kBM + r] = sc[rr].dd;
 #pragma unroll
                     for (int j = 0; j < kKS; j++) {
                         if (j < (int)nsteps) {
@@ -458,23 +501,44 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const MmqParams P)
                             uint4 q2 = make_uint4(0, 0, 0, 0);
                             if constexpr (FMT == Q8_0) q2 = *reinterpret_cast<const uint4 *>(rp + kBM * 16);
                             uint4 lo, hi;
-                            expand_weights<FMT>(q, q2, FMT == Q5_K ? extra[rr][j] : 0u, lo, hi);
+                            expand_weights<FMT>(q, q2, extra[rr][j], lo, hi);
                             uint8_t *ap = smem + L::a_off + (s * kKS + j) * L::a_sub + r * 16u;
                             *reinterpret_cast<uint4 *>(ap) = lo;
                             *reinterpret_cast<uint4 *>(ap + kBM * 16) = hi;
                         }
                     }
                 }
-                // B: the int8 quants in the same layout, the scales beside them
+                // B from BlockQ8 records (rc_mmq_gemm, grouped GEMM): the int8 quants in the same layout, the
+                // token scales beside them; a few items at a time to bound the registers in flight
+                if (!P.planar) {
+                    constexpr int GROUP = ITEMS_PT < 4 ? ITEMS_PT : 4;
 #pragma unroll
-                for (int n = 0; n < ITEMS_PT; n++) {
-                    const uint32_t q = tid + n * kExpanderThreads, tok = q % BN, j = q / BN;
-                    if (j < nsteps) {
-                        uint8_t *bp = smem + L::b_off + (s * kKS + j) * L::b_sub + tok * 16u;
-                        *reinterpret_cast<uint4 *>(bp) = make_uint4(xb[n][1].x, xb[n][1].y, xb[n][2].x, xb[n][2].y);
-                        *reinterpret_cast<uint4 *>(bp + BN * 16) = make_uint4(xb[n][3].x, xb[n][3].y, xb[n][4].x, xb[n][4].y);
-                        reinterpret_cast<uint32_t *>(smem + L::dx_off + (s * kKS + j) * L::sx_sub)[tok] = xb[n][0].x;
-                        reinterpret_cast<uint32_t *>(smem + L::xs_off + (s * kKS + j) * L::sx_sub)[tok] = xb[n][0].y;
+                    for (int n0 = 0; n0 < ITEMS_PT; n0 += GROUP) {
+                        uint2 xb[GROUP][5];
+#pragma unroll
+                        for (int n = 0; n < GROUP; n++) {
+                            const uint32_t q = tid + (n0 + n) * kExpanderThreads, tok = q % BN, j = q / BN;
+                            if (j < nsteps && tok < t.n_valid) {
+                                const uint2 *src = reinterpret_cast<const uint2 *>(
+                                    P.xq + ((size_t)(t.tok0 + tok) * n_sub + k0 + j) * RC_BLOCKQ8_BYTES);
+#pragma unroll
+                                for (int w = 0; w < 5; w++) xb[n][w] = __ldg(src + w);
+                            } else {
+#pragma unroll
+                                for (int w = 0; w < 5; w++) xb[n][w] = make_uint2(0u, 0u);
+                            }
+                        }
+#pragma unroll
+                        for (int n = 0; n < GROUP; n++) {
+                            const uint32_t q = tid + (n0 + n) * kExpanderThreads, tok = q % BN, j = q / BN;
+                            if (j < nsteps) {
+                                uint8_t *bp = smem + L::b_off + (s * kKS + j) * L::b_sub + tok * 16u;
+                                *reinterpret_cast<uint4 *>(bp) = make_uint4(xb[n][1].x, xb[n][1].y, xb[n][2].x, xb[n][2].y);
+                                *reinterpret_cast<uint4 *>(bp + BN * 16) = make_uint4(xb[n][3].x, xb[n][3].y, xb[n][4].x, xb[n][4].y);
+                                reinterpret_cast<uint32_t *>(smem + L::dx_off + (s * kKS + j) * L::sx_sub)[tok] = xb[n][0].x;
+                                reinterpret_cast<uint32_t *>(smem + L::xs_off + (s * kKS + j) * L::sx_sub)[tok] = xb[n][0].y;
+                            }
+                        }
                     }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic writes -> MMA reads
@@ -486,47 +550,46 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const MmqParams P)
     } else {
         // ---- epilogue -----------------------------------------------------------------------------------
         const uint32_t quarter = warp & 3u;        // tensor-memory lanes this warp may read
-        const uint32_t half = (warp - 4u) >> 2;    // which half of the BN columns
-        constexpr int COLS = BN / 2;               // columns per thread
+        const uint32_t half = (warp - 4u) >> 2;    // which group of COLS columns
+        constexpr int COLS = BN / (EPW / 4);       // columns per thread
         constexpr int CHUNKS = COLS / 32 > 0 ? COLS / 32 : 1;
         constexpr int CW = COLS < 32 ? COLS : 32;  // columns per tensor-memory load
-        static_assert(COLS == 16 || COLS % 32 == 0, "BN must be 32 or a multiple of 64");
-        float acc[COLS];
+        static_assert(COLS == 16 || COLS % 32 == 0, "16 or a multiple of 32 columns per epilogue warp");
+        unsigned long long acc[COLS / 2]; // pairs of adjacent tokens
         uint32_t it = 0, kc = 0;
         for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x) {
             const Tile t = decode_tile<BN>(P, id);
-            const Planes pl = planes_of<FMT>(P.w + (size_t)t.e * P.bytes_per_expert, P.in_dim, P.out_dim);
-            const bool sup_a4 = (reinterpret_cast<uintptr_t>(pl.sup) & 3u) == 0;
             const uint32_t row_raw = t.m0 + quarter * 32u + lane;
-            const uint32_t row = min(row_raw, P.out_dim - 1u);
 #pragma unroll
-            for (int c = 0; c < COLS; c++) acc[c] = 0.0f;
-            StageScales cur, nxt;
-            load_scales<FMT>(cur, pl, sup_a4, row, 0, min((uint32_t)kKS, n_sub));
+            for (int c = 0; c < COLS / 2; c++) acc[c] = 0ull;
             for (uint32_t i = 0; i < n_iters; i++, it++) {
                 const uint32_t s = it % kStages;
-                const uint32_t k0 = i * kKS, nsteps = min((uint32_t)kKS, n_sub - k0);
-                if (i + 1 < n_iters) load_scales<FMT>(nxt, pl, sup_a4, row, k0 + kKS, min((uint32_t)kKS, n_sub - k0 - kKS));
-                // the stage's activation scales were written before op_full completed
+                const uint32_t nsteps = min((uint32_t)kKS, n_sub - i * kKS);
+                // the stage's token scales and this row's scale words were staged before op_full completed
                 if (!mbar_wait(op_full(s), (it / kStages) & 1u, abort_flag, 6u)) goto epi_done;
+                const uint32_t *rs = reinterpret_cast<const uint32_t *>(smem + L::rsc_off + s * L::rsc_stage) + quarter * 32u + lane;
                 float d_sup = 0.0f, dmin_sup = 0.0f;
                 if constexpr (MmqTraits<FMT>::has_min) {
-                    d_sup = f16_bits_to_f32(cur.dd);
-                    dmin_sup = f16_bits_to_f32(cur.dd >> 16);
+                    const uint32_t dd = rs[kKS * kBM];
+                    d_sup = f16_bits_to_f32(dd);
+                    dmin_sup = f16_bits_to_f32(dd >> 16);
                 }
 #pragma unroll
                 for (int j = 0; j < kKS; j++) {
                     if (j < (int)nsteps) {
                         const uint32_t b = kc % kBufs;
-                        if (!mbar_wait(tm_full(b), (kc / kBufs) & 1u, abort_flag, 7u)) goto epi_done;
-                        tc_fence_after();
+                        const uint32_t sw = rs[j * kBM];
                         float dsc, ndeff = 0.0f;
                         if constexpr (MmqTraits<FMT>::has_min) {
-                            dsc = d_sup * (float)(cur.s[j] & 0xFFu);
-                            ndeff = -dmin_sup * (float)(cur.s[j] >> 8);
+                            dsc = d_sup * (float)(sw & 0xFFu);
+                            ndeff = -dmin_sup * (float)(sw >> 8);
                         } else {
-                            dsc = f16_bits_to_f32(cur.s[j]);
+                            dsc = f16_bits_to_f32(sw);
                         }
+                        const unsigned long long dsc2 = pack2(dsc, dsc), ndeff2 = pack2(ndeff, ndeff);
+                        const unsigned long long unbias2 = pack2(-12582912.0f, -12582912.0f);
+                        if (!mbar_wait(tm_full(b), (kc / kBufs) & 1u, abort_flag, 7u)) goto epi_done;
+                        tc_fence_after();
                         const float *dxp = reinterpret_cast<const float *>(smem + L::dx_off + (s * kKS + j) * L::sx_sub) + half * COLS;
                         const float *xsp = reinterpret_cast<const float *>(smem + L::xs_off + (s * kKS + j) * L::sx_sub) + half * COLS;
 #pragma unroll
@@ -545,35 +608,37 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const MmqParams P)
                             }
 #pragma unroll
                             for (int c = 0; c < CW; c += 4) {
-                                const float4 dx4 = *reinterpret_cast<const float4 *>(dxp + ch * 32 + c);
-                                float4 xs4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                                if constexpr (MmqTraits<FMT>::has_min) xs4 = *reinterpret_cast<const float4 *>(xsp + ch * 32 + c);
-                                const float dxv[4] = {dx4.x, dx4.y, dx4.z, dx4.w};
-                                const float xsv[4] = {xs4.x, xs4.y, xs4.z, xs4.w};
-#pragma unroll
-                                for (int u = 0; u < 4; u++) {
-                                    // exact int -> float: bias into [2^23, 2^24) as an integer, remove it as a float
-                                    const float z = __uint_as_float(d[c + u] + 0x4B400000u) - 12582912.0f;
-                                    float a = acc[ch * 32 + c + u];
-                                    a = fmaf(dsc, z * dxv[u], a);
-                                    if constexpr (MmqTraits<FMT>::has_min) a = fmaf(ndeff, xsv[u], a);
-                                    acc[ch * 32 + c + u] = a;
+                                const ulonglong2 dx4 = *reinterpret_cast<const ulonglong2 *>(dxp + ch * 32 + c);
+                                // exact int -> float: bias into [2^23, 2^24) as an integer, remove it as a float
+                                const unsigned long long f01 = (unsigned long long)(d[c] + 0x4B400000u) |
+                                                               ((unsigned long long)(d[c + 1] + 0x4B400000u) << 32);
+                                const unsigned long long f23 = (unsigned long long)(d[c + 2] + 0x4B400000u) |
+                                                               ((unsigned long long)(d[c + 3] + 0x4B400000u) << 32);
+                                unsigned long long a01 = acc[(ch * 32 + c) / 2], a23 = acc[(ch * 32 + c) / 2 + 1];
+                                a01 = fma2(dsc2, mul2(add2(f01, unbias2), dx4.x), a01);
+                                a23 = fma2(dsc2, mul2(add2(f23, unbias2), dx4.y), a23);
+                                if constexpr (MmqTraits<FMT>::has_min) {
+                                    const ulonglong2 xs4 = *reinterpret_cast<const ulonglong2 *>(xsp + ch * 32 + c);
+                                    a01 = fma2(ndeff2, xs4.x, a01);
+                                    a23 = fma2(ndeff2, xs4.y, a23);
                                 }
+                                acc[(ch * 32 + c) / 2] = a01;
+                                acc[(ch * 32 + c) / 2 + 1] = a23;
                             }
                         }
                         kc++;
                     }
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(op_empty(s)); // done with the stage's activation scales
-                cur = nxt;
+                if (lane == 0) mbar_arrive(op_empty(s)); // done with the stage's operands (its MMAs have completed) and scales
             }
             // tile end: Y[tok][row], a warp writes 32 consecutive rows of one token per store
             if (row_raw < P.out_dim) {
 #pragma unroll
                 for (int c = 0; c < COLS; c++) {
                     const uint32_t col = half * COLS + c;
-                    if (col < t.n_valid) P.y[(size_t)(t.tok0 + col) * P.out_dim + row_raw] = acc[c];
+                    const float v = __uint_as_float((uint32_t)(acc[c / 2] >> (32 * (c & 1))));
+                    if (col < t.n_valid) P.y[(size_t)(t.tok0 + col) * P.out_dim + row_raw] = v;
                 }
             }
         }
@@ -1122,14 +1187,46 @@ int make_tmap(CUtensorMap *map, const void *w, size_t bytes_per_expert, uint32_t
     return r == CUDA_SUCCESS ? RC_OK : RC_ERR_BAD_ARGUMENT;
 }
 
+template <int BN> struct Epw8 { static constexpr int v = BN >= 128 ? 16 : 8; };
+
 template <int FMT, int BN>
 int launch_tc(cudaStream_t s, const MmqParams &P, uint32_t tiles_upper_bound)
 {
     CUtensorMap map;
     int rc = make_tmap<FMT>(&map, P.w, P.bytes_per_expert, P.expert_off ? P.n_expert : 1u, P.in_dim, P.out_dim);
     if (rc) return rc;
+    CUtensorMap map_b = map, map_dx = map, map_xs = map;
+    if (P.planar) {
+        // views of rc_matmul's planar scratch (rc_quantize.cu): quants as (16 bytes, token, 16-byte chunk
+        // of K), so that one box lands as kKS operands [half][token][16 B]; scales as (token, sub-block)
+        EncodeTiledFn fn = encode_fn();
+        if (!fn) return RC_ERR_NO_DEVICE;
+        const uint32_t n_sub = P.in_dim >> 5;
+        const uint64_t ld = ((uint64_t)P.n_tok + 3u) & ~3ull;
+        uint8_t *base = const_cast<uint8_t *>(P.xq);
+        const cuuint64_t bd[3] = {16, P.n_tok, P.in_dim / 16};
+        const cuuint64_t bs[2] = {P.in_dim, 16};
+        const cuuint32_t bb[3] = {16, (cuuint32_t)BN, 2 * kKS};
+        const cuuint32_t one3[3] = {1, 1, 1};
+        CUresult r = fn(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, base, bd, bs, bb, one3, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        const cuuint64_t sd[2] = {P.n_tok, n_sub};
+        const cuuint64_t ss[1] = {ld * 4};
+        const cuuint32_t sb[2] = {(cuuint32_t)BN, kKS};
+        const cuuint32_t one2[2] = {1, 1};
+        uint8_t *dx = base + (size_t)P.n_tok * P.in_dim;
+        if (r == CUDA_SUCCESS)
+            r = fn(&map_dx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, dx, sd, ss, sb, one2, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r == CUDA_SUCCESS)
+            r = fn(&map_xs, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, dx + (size_t)n_sub * ld * 4, sd, ss, sb, one2,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return RC_ERR_BAD_ARGUMENT;
+    }
     const uint32_t grid = min(tiles_upper_bound, (uint32_t)sm_count());
-    mmq_kernel<FMT, BN><<<grid, kThreads, Smem<FMT, BN>::total, s>>>(map, P);
+    constexpr int EPW = Epw8<BN>::v;
+    mmq_kernel<FMT, BN, EPW><<<grid, (4 + EPW) * 32, Smem<FMT, BN>::total, s>>>(map, map_b, map_dx, map_xs, P);
     return (int)cudaGetLastError();
 }
 
@@ -1173,7 +1270,7 @@ template <int FMT, int BN> int set_attr16()
 
 template <int FMT, int BN> int set_attr()
 {
-    return (int)cudaFuncSetAttribute(mmq_kernel<FMT, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    return (int)cudaFuncSetAttribute(mmq_kernel<FMT, BN, Epw8<BN>::v>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)Smem<FMT, BN>::total);
 }
 
@@ -1182,6 +1279,7 @@ constexpr int kGroupedBN = 32;
 
 bool g_force_dp4a = false;
 int g_mmq_debug = 0;
+bool g_no_planar = false;
 int g_mmq_kind = 0; // 0: by format (int8 operands, f16 for Q6_K); 16 / 8: force one kernel (8 has no Q6_K)
 
 } // namespace
@@ -1212,6 +1310,7 @@ void mmq_force_dp4a(int on) { g_force_dp4a = on != 0; }
 void mmq_set_kind(int kind)
 {
     g_mmq_kind = (kind & 0xFF) == 8 ? 8 : (kind & 0xFF) == 16 ? 16 : 0;
+    g_no_planar = ((kind >> 8) & 512) != 0; // bit 9 of the mask: keep rc_matmul on BlockQ8 records
     g_mmq_debug = kind >> 8; // upper bits: parts of the f16 kernel's pipeline to skip (timing experiments)
 }
 
@@ -1227,8 +1326,35 @@ int mmq_device_error(unsigned int *out)
 // Formats with one scale per 32-wide sub-block run on the tensor cores.  Q6_K scales each half
 // of a sub-block separately (kernels/mmq_gemm_q6k_repacked.cpp), which a K=32 int8 MMA cannot
 // keep apart; it goes through the dp4a kernel in slabs of 16 activation rows.
+namespace {
+int mmq_dense(cudaStream_t s, int type, const void *w, const void *xq, float *y, uint32_t in_dim, uint32_t out_dim,
+              uint32_t p_rows, bool planar);
+}
+
 int launch_mmq_gemm(cudaStream_t s, int type, const void *w, const void *xq, float *y,
                     uint32_t in_dim, uint32_t out_dim, uint32_t p_rows)
+{
+    return mmq_dense(s, type, w, xq, y, in_dim, out_dim, p_rows, false);
+}
+
+// PrefillGemm's quantize + GEMM.  When the int8 tensor-core kernel will run and the scratch is
+// large and aligned enough, the activations are quantized straight into the planar form that
+// kernel reads through TMA (same values as the BlockQ8 records, no per-tile conversion).
+int launch_mmq_gemm_f32(cudaStream_t s, int type, const void *w, const float *x, float *y, uint32_t in_dim,
+                        uint32_t out_dim, uint32_t p_rows, void *scratch, size_t scratch_bytes)
+{
+    const bool i8_kernel = !g_force_dp4a && g_mmq_kind != 16 && type != Q6_K;
+    const bool planar = i8_kernel && !g_no_planar && ((uintptr_t)scratch & 15u) == 0 && p_rows <= 65535u &&
+                        scratch_bytes >= quantize_planar_bytes(in_dim, p_rows);
+    int rc = planar ? launch_quantize_q8_planar(s, x, scratch, in_dim, p_rows)
+                    : launch_quantize_q8(s, x, scratch, in_dim, p_rows);
+    if (rc) return rc;
+    return mmq_dense(s, type, w, scratch, y, in_dim, out_dim, p_rows, planar);
+}
+
+namespace {
+int mmq_dense(cudaStream_t s, int type, const void *w, const void *xq, float *y, uint32_t in_dim, uint32_t out_dim,
+              uint32_t p_rows, bool planar)
 {
     const uint32_t n_sub = in_dim >> 5;
     const bool use16 = g_mmq_kind == 16 || (g_mmq_kind == 0 && type == Q6_K);
@@ -1244,6 +1370,7 @@ int launch_mmq_gemm(cudaStream_t s, int type, const void *w, const void *xq, flo
         P.in_dim = in_dim;
         P.out_dim = out_dim;
         P.n_tok = p_rows;
+        P.planar = planar ? 1u : 0u;
         P.b_tma = 0;
         P.debug = (uint32_t)g_mmq_debug;
         const uint32_t tiles = ((out_dim + kBM - 1) / kBM) * ((p_rows + kDenseBN - 1) / kDenseBN);
@@ -1275,6 +1402,7 @@ int launch_mmq_gemm(cudaStream_t s, int type, const void *w, const void *xq, flo
     }
     return RC_OK;
 }
+} // namespace
 
 // Expert tiles are kGroupedBN tokens wide (the width rc_moe_sort must be given): at a mean of
 // 16 tokens per expert a wider tile would be mostly padding, and the kernel is bound by the
@@ -1297,6 +1425,7 @@ int launch_mmq_grouped(cudaStream_t s, int type, const void *slab, size_t bytes_
         P.in_dim = in_dim;
         P.out_dim = out_dim;
         P.n_tok = n_entries;
+        P.planar = 0;
         P.b_tma = 0;
         P.debug = (uint32_t)g_mmq_debug;
         // the tile count lives on the device (tile_off[n_expert]); this is its upper bound

@@ -51,6 +51,61 @@ __global__ void __launch_bounds__(256) quantize_q8_kernel(const float *__restric
     }
 }
 
+// The same quantizer writing the planar form the tensor-core GEMM takes through TMA instead of
+// 40-byte records: qs int8 [n_vec][in_dim], then d f32 [in_dim/32][ld], then xsum f32
+// [in_dim/32][ld], ld = n_vec rounded up to 4 (16-byte row pitch).  Same arithmetic, same values.
+__global__ void __launch_bounds__(256) quantize_q8_planar_kernel(const float *__restrict__ x, uint8_t *__restrict__ out,
+                                                                  uint32_t in_dim, uint32_t n_vec)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t n_sub = in_dim >> 5;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warps_per_cta = blockDim.x >> 5;
+    const uint32_t vec = blockIdx.y;
+    const uint32_t ld = (n_vec + 3u) & ~3u;
+    uint32_t *qs = reinterpret_cast<uint32_t *>(out + (size_t)vec * in_dim);
+    float *dT = reinterpret_cast<float *>(out + (size_t)n_vec * in_dim);
+    float *sT = dT + (size_t)n_sub * ld;
+    x += (size_t)vec * in_dim;
+    for (uint32_t sb = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); sb < n_sub; sb += gridDim.x * warps_per_cta) {
+        const float v = x[(size_t)sb * 32 + lane];
+        float amax = fabsf(v), sum = v;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+            sum = __fadd_rn(sum, __shfl_xor_sync(0xFFFFFFFFu, sum, o));
+        }
+        const float d = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+        const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+        int q = __float2int_rn(__fmul_rn(v, inv));
+        q = max(-127, min(127, q));
+        uint32_t b = (uint32_t)(q & 0xFF) << (8 * (lane & 3u));
+        b |= __shfl_xor_sync(0xFFFFFFFFu, b, 1);
+        b |= __shfl_xor_sync(0xFFFFFFFFu, b, 2);
+        if ((lane & 3u) == 0) qs[sb * 8 + (lane >> 2)] = b;
+        if (lane == 0) {
+            dT[(size_t)sb * ld + vec] = d;
+            sT[(size_t)sb * ld + vec] = sum;
+        }
+    }
+}
+
+size_t quantize_planar_bytes(uint32_t in_dim, uint32_t n_vec)
+{
+    const size_t ld = ((size_t)n_vec + 3u) & ~(size_t)3u;
+    return (size_t)n_vec * in_dim + 2u * (size_t)(in_dim >> 5) * ld * sizeof(float);
+}
+
+int launch_quantize_q8_planar(cudaStream_t s, const float *x, void *out, uint32_t in_dim, uint32_t n_vec)
+{
+    if (n_vec == 0) return RC_OK;
+    if (n_vec > 65535u) return RC_ERR_TOO_MANY_ROWS;
+    const uint32_t n_sub = in_dim >> 5;
+    quantize_q8_planar_kernel<<<dim3((n_sub + 7u) / 8u, n_vec), 256, 0, s>>>(x, (uint8_t *)out, in_dim, n_vec);
+    return (int)cudaGetLastError();
+}
+
 int launch_quantize_q8(cudaStream_t s, const float *x, void *xq, uint32_t in_dim, uint32_t n_vec)
 {
     if (n_vec == 0) return RC_OK;
