@@ -38,7 +38,6 @@ constexpr int kBM = 128;     // weight rows per tile = tensor-memory lanes
 constexpr int kKS = 4;       // sub-blocks (K=32 MMA steps) per pipeline stage
 constexpr int kStages = 4;   // operand ring depth
 constexpr int kBufs = 4;     // tensor-memory accumulator buffers
-constexpr int kExpanderThreads = 64;
 constexpr uint64_t kWaitLimitNs = 500ull * 1000 * 1000; // far beyond any legal wait (microseconds)
 
 __device__ unsigned int g_mmq_error;
@@ -351,12 +350,13 @@ __device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigne
 // tile).  With P.planar the activations come from rc_matmul's planar scratch: the int8 quants land
 // by TMA directly in the operand layout and the token scales beside them, so the expanders only
 // split nibbles.
-template <int FMT, int BN, int EPW>
-__global__ void __launch_bounds__((4 + EPW) * 32, 1)
+template <int FMT, int BN, int EPW, int EXW>
+__global__ void __launch_bounds__((2 + EXW + EPW) * 32, 1)
 mmq_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_b,
            const __grid_constant__ CUtensorMap tmap_dx, const __grid_constant__ CUtensorMap tmap_xs, const MmqParams P)
 {
     using L = Smem<FMT, BN>;
+    constexpr int kExpT = EXW * 32; // expander threads (the narrow expert tile is bound by them: four warps)
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     const uint32_t sbase = smem_u32(smem);
@@ -379,8 +379,8 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUt
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; s++) {
             mbar_init(raw_full(s), 1);
-            mbar_init(raw_empty(s), kExpanderThreads);
-            mbar_init(op_full(s), kExpanderThreads);
+            mbar_init(raw_empty(s), kExpT);
+            mbar_init(op_full(s), kExpT);
             mbar_init(op_empty(s), EPW); // an epilogue warp arrives after the tm_full of the stage's last MMA
         }
         for (uint32_t b = 0; b < kBufs; b++) {
@@ -454,11 +454,11 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUt
             }
         mma_done:;
         }
-    } else if (warp < 4) {
+    } else if (warp < 2 + EXW) {
         // ---- expanders ------------------------------------------------------------------------------
-        const uint32_t tid = threadIdx.x - 64u; // 0..63
-        constexpr int ROWS_PT = kBM / kExpanderThreads;                                // weight rows per thread
-        constexpr int ITEMS_PT = (BN * kKS + kExpanderThreads - 1) / kExpanderThreads; // (token, sub-block) items per thread
+        const uint32_t tid = threadIdx.x - 64u;
+        constexpr int ROWS_PT = kBM / kExpT;                                // weight rows per thread
+        constexpr int ITEMS_PT = (BN * kKS + kExpT - 1) / kExpT; // (token, sub-block) items per thread
         uint32_t it = 0;
         for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x) {
             const Tile t = decode_tile<BN>(P, id);
@@ -467,12 +467,30 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUt
             for (uint32_t i = 0; i < n_iters; i++, it++) {
                 const uint32_t s = it % kStages;
                 const uint32_t k0 = i * kKS, nsteps = min((uint32_t)kKS, n_sub - k0);
-                // global loads first: side planes and row scales
+                // global loads first: side planes, row scales, and the first group of BlockQ8 items
+                constexpr int GROUP = ITEMS_PT < 4 ? ITEMS_PT : 4;
+                uint2 xb[GROUP][5];
+                auto load_items = [&](int n0) {
+#pragma unroll
+                    for (int n = 0; n < GROUP; n++) {
+                        const uint32_t q = tid + (n0 + n) * kExpT, tok = q % BN, j = q / BN;
+                        if (j < nsteps && tok < t.n_valid) {
+                            const uint2 *src = reinterpret_cast<const uint2 *>(
+                                P.xq + ((size_t)(t.tok0 + tok) * n_sub + k0 + j) * RC_BLOCKQ8_BYTES);
+#pragma unroll
+                            for (int w = 0; w < 5; w++) xb[n][w] = __ldg(src + w);
+                        } else {
+#pragma unroll
+                            for (int w = 0; w < 5; w++) xb[n][w] = make_uint2(0u, 0u);
+                        }
+                    }
+                };
+                if (!P.planar) load_items(0);
                 uint32_t extra[ROWS_PT][kKS];
                 StageScales sc[ROWS_PT];
 #pragma unroll
                 for (int rr = 0; rr < ROWS_PT; rr++) {
-                    const uint32_t row = min(t.m0 + tid + rr * kExpanderThreads, P.out_dim - 1u);
+                    const uint32_t row = min(t.m0 + tid + rr * kExpT, P.out_dim - 1u);
                     sc[rr].dd = 0;
 #pragma unroll
                     for (int j = 0; j < kKS; j++) {
@@ -488,7 +506,7 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUt
                 // A: whole weight rows of the tile, and their scale words for the epilogue
 #pragma unroll
                 for (int rr = 0; rr < ROWS_PT; rr++) {
-                    const uint32_t r = tid + rr * kExpanderThreads;
+                    const uint32_t r = tid + rr * kExpT;
                     uint32_t *rs = reinterpret_cast<uint32_t *>(smem + L::rsc_off + s * L::rsc_stage);
 #pragma unroll
                     for (int j = 0; j < kKS; j++) rs[j * kBM + r] = sc[rr].s[j];
@@ -511,26 +529,12 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUt
                 // B from BlockQ8 records (rc_mmq_gemm, grouped GEMM): the int8 quants in the same layout, the
                 // token scales beside them; a few items at a time to bound the registers in flight
                 if (!P.planar) {
-                    constexpr int GROUP = ITEMS_PT < 4 ? ITEMS_PT : 4;
 #pragma unroll
                     for (int n0 = 0; n0 < ITEMS_PT; n0 += GROUP) {
-                        uint2 xb[GROUP][5];
+                        if (n0 > 0) load_items(n0);
 #pragma unroll
                         for (int n = 0; n < GROUP; n++) {
-                            const uint32_t q = tid + (n0 + n) * kExpanderThreads, tok = q % BN, j = q / BN;
-                            if (j < nsteps && tok < t.n_valid) {
-                                const uint2 *src = reinterpret_cast<const uint2 *>(
-                                    P.xq + ((size_t)(t.tok0 + tok) * n_sub + k0 + j) * RC_BLOCKQ8_BYTES);
-#pragma unroll
-                                for (int w = 0; w < 5; w++) xb[n][w] = __ldg(src + w);
-                            } else {
-#pragma unroll
-                                for (int w = 0; w < 5; w++) xb[n][w] = make_uint2(0u, 0u);
-                            }
-                        }
-#pragma unroll
-                        for (int n = 0; n < GROUP; n++) {
-                            const uint32_t q = tid + (n0 + n) * kExpanderThreads, tok = q % BN, j = q / BN;
+                            const uint32_t q = tid + (n0 + n) * kExpT, tok = q % BN, j = q / BN;
                             if (j < nsteps) {
                                 uint8_t *bp = smem + L::b_off + (s * kKS + j) * L::b_sub + tok * 16u;
                                 *reinterpret_cast<uint4 *>(bp) = make_uint4(xb[n][1].x, xb[n][1].y, xb[n][2].x, xb[n][2].y);
@@ -550,7 +554,7 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUt
     } else {
         // ---- epilogue -----------------------------------------------------------------------------------
         const uint32_t quarter = warp & 3u;        // tensor-memory lanes this warp may read
-        const uint32_t half = (warp - 4u) >> 2;    // which group of COLS columns
+        const uint32_t half = (warp - (2u + EXW)) >> 2; // which group of COLS columns
         constexpr int COLS = BN / (EPW / 4);       // columns per thread
         constexpr int CHUNKS = COLS / 32 > 0 ? COLS / 32 : 1;
         constexpr int CW = COLS < 32 ? COLS : 32;  // columns per tensor-memory load
@@ -574,24 +578,46 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUt
                     d_sup = f16_bits_to_f32(dd);
                     dmin_sup = f16_bits_to_f32(dd >> 16);
                 }
+                // drain of one sub-block's columns (already in registers) into the accumulators
+                auto drain = [&](const uint32_t (&d)[32], int j, int ch) {
+                    const uint32_t sw = rs[j * kBM];
+                    float dsc, ndeff = 0.0f;
+                    if constexpr (MmqTraits<FMT>::has_min) {
+                        dsc = d_sup * (float)(sw & 0xFFu);
+                        ndeff = -dmin_sup * (float)(sw >> 8);
+                    } else {
+                        dsc = f16_bits_to_f32(sw);
+                    }
+                    const unsigned long long dsc2 = pack2(dsc, dsc), ndeff2 = pack2(ndeff, ndeff);
+                    const unsigned long long unbias2 = pack2(-12582912.0f, -12582912.0f);
+                    const float *dxp = reinterpret_cast<const float *>(smem + L::dx_off + (s * kKS + j) * L::sx_sub) + half * COLS;
+                    const float *xsp = reinterpret_cast<const float *>(smem + L::xs_off + (s * kKS + j) * L::sx_sub) + half * COLS;
+#pragma unroll
+                    for (int c = 0; c < CW; c += 4) {
+                        const ulonglong2 dx4 = *reinterpret_cast<const ulonglong2 *>(dxp + ch * 32 + c);
+                        // exact int -> float: bias into [2^23, 2^24) as an integer, remove it as a float
+                        const unsigned long long f01 = (unsigned long long)(d[c] + 0x4B400000u) |
+                                                       ((unsigned long long)(d[c + 1] + 0x4B400000u) << 32);
+                        const unsigned long long f23 = (unsigned long long)(d[c + 2] + 0x4B400000u) |
+                                                       ((unsigned long long)(d[c + 3] + 0x4B400000u) << 32);
+                        unsigned long long a01 = acc[(ch * 32 + c) / 2], a23 = acc[(ch * 32 + c) / 2 + 1];
+                        a01 = fma2(dsc2, mul2(add2(f01, unbias2), dx4.x), a01);
+                        a23 = fma2(dsc2, mul2(add2(f23, unbias2), dx4.y), a23);
+                        if constexpr (MmqTraits<FMT>::has_min) {
+                            const ulonglong2 xs4 = *reinterpret_cast<const ulonglong2 *>(xsp + ch * 32 + c);
+                            a01 = fma2(ndeff2, xs4.x, a01);
+                            a23 = fma2(ndeff2, xs4.y, a23);
+                        }
+                        acc[(ch * 32 + c) / 2] = a01;
+                        acc[(ch * 32 + c) / 2 + 1] = a23;
+                    }
+                };
 #pragma unroll
                 for (int j = 0; j < kKS; j++) {
                     if (j < (int)nsteps) {
                         const uint32_t b = kc % kBufs;
-                        const uint32_t sw = rs[j * kBM];
-                        float dsc, ndeff = 0.0f;
-                        if constexpr (MmqTraits<FMT>::has_min) {
-                            dsc = d_sup * (float)(sw & 0xFFu);
-                            ndeff = -dmin_sup * (float)(sw >> 8);
-                        } else {
-                            dsc = f16_bits_to_f32(sw);
-                        }
-                        const unsigned long long dsc2 = pack2(dsc, dsc), ndeff2 = pack2(ndeff, ndeff);
-                        const unsigned long long unbias2 = pack2(-12582912.0f, -12582912.0f);
                         if (!mbar_wait(tm_full(b), (kc / kBufs) & 1u, abort_flag, 7u)) goto epi_done;
                         tc_fence_after();
-                        const float *dxp = reinterpret_cast<const float *>(smem + L::dx_off + (s * kKS + j) * L::sx_sub) + half * COLS;
-                        const float *xsp = reinterpret_cast<const float *>(smem + L::xs_off + (s * kKS + j) * L::sx_sub) + half * COLS;
 #pragma unroll
                         for (int ch = 0; ch < CHUNKS; ch++) {
                             uint32_t d[32];
@@ -606,25 +632,7 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUt
                                 __syncwarp();
                                 if (lane == 0) mbar_arrive(tm_empty(b));
                             }
-#pragma unroll
-                            for (int c = 0; c < CW; c += 4) {
-                                const ulonglong2 dx4 = *reinterpret_cast<const ulonglong2 *>(dxp + ch * 32 + c);
-                                // exact int -> float: bias into [2^23, 2^24) as an integer, remove it as a float
-                                const unsigned long long f01 = (unsigned long long)(d[c] + 0x4B400000u) |
-                                                               ((unsigned long long)(d[c + 1] + 0x4B400000u) << 32);
-                                const unsigned long long f23 = (unsigned long long)(d[c + 2] + 0x4B400000u) |
-                                                               ((unsigned long long)(d[c + 3] + 0x4B400000u) << 32);
-                                unsigned long long a01 = acc[(ch * 32 + c) / 2], a23 = acc[(ch * 32 + c) / 2 + 1];
-                                a01 = fma2(dsc2, mul2(add2(f01, unbias2), dx4.x), a01);
-                                a23 = fma2(dsc2, mul2(add2(f23, unbias2), dx4.y), a23);
-                                if constexpr (MmqTraits<FMT>::has_min) {
-                                    const ulonglong2 xs4 = *reinterpret_cast<const ulonglong2 *>(xsp + ch * 32 + c);
-                                    a01 = fma2(ndeff2, xs4.x, a01);
-                                    a23 = fma2(ndeff2, xs4.y, a23);
-                                }
-                                acc[(ch * 32 + c) / 2] = a01;
-                                acc[(ch * 32 + c) / 2 + 1] = a23;
-                            }
+                            drain(d, j, ch);
                         }
                         kc++;
                     }
@@ -673,7 +681,6 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUt
 // so that one warp's tensor-memory load and barrier latency hides behind the others' math).
 
 constexpr int kKS16 = 2;      // sub-blocks per stage
-constexpr int kExpanders16 = 64;
 
 __device__ unsigned int g_mmq16_error;
 
@@ -830,13 +837,14 @@ template <int FMT, int BN> struct Smem16 {
     static constexpr uint32_t total = misc_off + 16 + 1024;
 };
 
-template <int FMT, int BN, int EPW>
-__global__ void __launch_bounds__((4 + EPW) * 32, 1)
+template <int FMT, int BN, int EPW, int EXW>
+__global__ void __launch_bounds__((2 + EXW + EPW) * 32, 1)
 mmq16_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_b, const MmqParams P)
 {
     using L = Smem16<FMT, BN>;
     using T = Mmq16Traits<FMT>;
     constexpr uint32_t kStages16 = L::stages;
+    constexpr int kExpanders16 = EXW * 32;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     const uint32_t sbase = smem_u32(smem);
@@ -936,9 +944,9 @@ mmq16_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ C
         mma_done:;
         }
       }
-    } else if (warp < 4) {
+    } else if (warp < 2 + EXW) {
         // ---- expanders -----------------------------------------------------------------------------
-        const uint32_t tid = threadIdx.x - 64u; // 0..63
+        const uint32_t tid = threadIdx.x - 64u;
         constexpr int ROWS_PT = kBM / kExpanders16; // weight rows per thread
         constexpr int ITEMS_PT = (BN * kKS16 + kExpanders16 - 1) / kExpanders16; // (token, sub-block) items per thread
         uint32_t it = 0;
@@ -1053,7 +1061,7 @@ mmq16_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ C
     } else {
         // ---- epilogue -------------------------------------------------------------------------------------
         const uint32_t quarter = warp & 3u;        // tensor-memory lanes this warp may read
-        const uint32_t half = (warp - 4u) >> 2;    // which group of COLS columns
+        const uint32_t half = (warp - (2u + EXW)) >> 2;    // which group of COLS columns
         constexpr int COLS = BN / (EPW / 4);
         constexpr int CHUNKS = COLS / 32 > 0 ? COLS / 32 : 1;
         constexpr int CW = COLS < 32 ? COLS : 32;
@@ -1188,6 +1196,7 @@ int make_tmap(CUtensorMap *map, const void *w, size_t bytes_per_expert, uint32_t
 }
 
 template <int BN> struct Epw8 { static constexpr int v = BN >= 128 ? 16 : 8; };
+template <int BN> struct Exw { static constexpr int v = BN >= 128 ? 2 : 4; }; // expander warps
 
 template <int FMT, int BN>
 int launch_tc(cudaStream_t s, const MmqParams &P, uint32_t tiles_upper_bound)
@@ -1225,8 +1234,8 @@ int launch_tc(cudaStream_t s, const MmqParams &P, uint32_t tiles_upper_bound)
         if (r != CUDA_SUCCESS) return RC_ERR_BAD_ARGUMENT;
     }
     const uint32_t grid = min(tiles_upper_bound, (uint32_t)sm_count());
-    constexpr int EPW = Epw8<BN>::v;
-    mmq_kernel<FMT, BN, EPW><<<grid, (4 + EPW) * 32, Smem<FMT, BN>::total, s>>>(map, map_b, map_dx, map_xs, P);
+    constexpr int EPW = Epw8<BN>::v, EXW = Exw<BN>::v;
+    mmq_kernel<FMT, BN, EPW, EXW><<<grid, (2 + EXW + EPW) * 32, Smem<FMT, BN>::total, s>>>(map, map_b, map_dx, map_xs, P);
     return (int)cudaGetLastError();
 }
 
@@ -1258,19 +1267,20 @@ int launch_tc16(cudaStream_t s, const MmqParams &P, uint32_t tiles_upper_bound)
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
             Q.b_tma = 1;
     }
-    mmq16_kernel<FMT, BN, EPW><<<grid, (4 + EPW) * 32, Smem16<FMT, BN>::total, s>>>(map, map_b, Q);
+    constexpr int EXW = Exw<BN>::v;
+    mmq16_kernel<FMT, BN, EPW, EXW><<<grid, (2 + EXW + EPW) * 32, Smem16<FMT, BN>::total, s>>>(map, map_b, Q);
     return (int)cudaGetLastError();
 }
 
 template <int FMT, int BN> int set_attr16()
 {
-    return (int)cudaFuncSetAttribute(mmq16_kernel<FMT, BN, Epw16<BN>::v>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    return (int)cudaFuncSetAttribute(mmq16_kernel<FMT, BN, Epw16<BN>::v, Exw<BN>::v>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)Smem16<FMT, BN>::total);
 }
 
 template <int FMT, int BN> int set_attr()
 {
-    return (int)cudaFuncSetAttribute(mmq_kernel<FMT, BN, Epw8<BN>::v>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    return (int)cudaFuncSetAttribute(mmq_kernel<FMT, BN, Epw8<BN>::v, Exw<BN>::v>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)Smem<FMT, BN>::total);
 }
 
