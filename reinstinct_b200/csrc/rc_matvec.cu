@@ -48,6 +48,8 @@ template <int FMT> struct FmtTraits {
     static constexpr uint32_t x_bytes = needs_is ? 48 : 40; // staged bytes per activation block
     // iterations (32 sub-blocks each) whose raw weight registers a warp holds at once
     static constexpr int G = (FMT == Q8_0) ? 3 : (FMT == Q5_K || FMT == Q6_K || FMT == IQ4_XS) ? 4 : 5;
+    // group lengths the plain row kernel is built for (longer groups of the wide formats spill)
+    static constexpr bool rows_len_ok(int len) { return len <= ((FMT == Q6_K) ? 3 : (FMT == Q8_0 || FMT == Q5_K) ? 4 : 5); }
 };
 
 // Staged activations: [n_rows][n_sub] arrays, sub-block index fastest, so a warp's reads are
@@ -326,6 +328,7 @@ stream_body(uint8_t *smem, const uint8_t *__restrict__ w, const uint8_t *__restr
             uint32_t n_rows, uint32_t ks, uint32_t block_begin, uint32_t block_stride)
 {
     constexpr int G = FmtTraits<FMT>::G;
+    if (NB <= 2) n_rows = NB; // the launchers pick NB = n_rows for one and two rows: a compile-time count
     const uint32_t n_sub = in_dim >> 5, n_iters = (n_sub + 31u) >> 5;
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const uint32_t rb_rows = n_warps / ks, r_local = warp / ks, chunk = warp - r_local * ks;
@@ -484,7 +487,79 @@ stream_body(uint8_t *smem, const uint8_t *__restrict__ w, const uint8_t *__restr
     }
 }
 
-template <int NB> struct MinBlocks { static constexpr int v = NB <= 2 ? 4 : NB <= 4 ? 3 : 2; };
+template <int NB> struct MinBlocks { static constexpr int v = NB <= 1 ? 4 : NB <= 4 ? 3 : 2; };
+
+// --------------------------------------------------------------------------------------------
+// The common decode shape gets a loop with nothing else in it: one warp per weight row (no row
+// split), every lane busy in every iteration (in_dim a multiple of 1024), and a row that is a
+// whole number of LEN-iteration groups.  Same loads, same term(), same order of additions per
+// lane as stream_body; it only sheds that kernel's bookkeeping, which is a third of its
+// instructions on a 5-iteration row.
+template <int FMT, int NB, int LEN>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, MinBlocks<NB>::v)
+matvec_rows_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq, float *__restrict__ y,
+                   uint32_t in_dim, uint32_t out_dim, uint32_t n_rows)
+{
+    extern __shared__ __align__(16) uint8_t smem[];
+    if (NB <= 2) n_rows = NB;
+    const uint32_t n_sub = in_dim >> 5, n_groups = (n_sub >> 5) / LEN;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const Planes p = planes_of<FMT>(w, in_dim, out_dim);
+    const bool sup_a4 = (reinterpret_cast<uintptr_t>(p.sup) & 3u) == 0;
+    const XStage st = carve_stage<FMT>(smem, n_rows * n_sub);
+    const uint32_t row_stride = gridDim.x * kWarpsPerCta;
+
+    Raw<FMT> cur[LEN];
+    auto fetch_group = [&](uint32_t row, uint32_t g) {
+        const GroupPtrs gp = group_ptrs<FMT>(p, min(row, out_dim - 1u), g * (LEN * 32u) + lane);
+        if (sup_a4) {
+#pragma unroll
+            for (int i = 0; i < LEN; i++) fetch_off<FMT, true>(cur[i], gp, i);
+        } else {
+#pragma unroll
+            for (int i = 0; i < LEN; i++) fetch_off<FMT, false>(cur[i], gp, i);
+        }
+    };
+
+    uint32_t row = blockIdx.x * kWarpsPerCta + warp;
+    if (row < out_dim) fetch_group(row, 0); // weights do not wait for x
+    pdl_launch_dependents();
+    pdl_wait();
+    stage_x<FMT>(st, xq, n_rows * n_sub);
+    __syncthreads();
+
+    for (; row < out_dim; row += row_stride) {
+        float acc[NB];
+#pragma unroll
+        for (int b = 0; b < NB; b++) acc[b] = 0.0f;
+        for (uint32_t g = 0; g < n_groups; g++) {
+            const uint32_t sb0 = g * (LEN * 32u) + lane;
+#pragma unroll
+            for (int i = 0; i < LEN; i++) {
+#pragma unroll
+                for (int b = 0; b < NB; b++) {
+                    if (b < (int)n_rows) {
+                        const uint32_t xi = b * n_sub + sb0 + i * 32u;
+                        const int4 xl = st.lo[xi], xh = st.hi[xi];
+                        const float2 ds = st.ds[xi];
+                        const int2 is = FmtTraits<FMT>::needs_is ? st.is[xi] : make_int2(0, 0);
+                        int i0, i1;
+                        acc[b] += term<FMT>(cur[i], xl, xh, ds, is, i0, i1);
+                    }
+                }
+            }
+            // the next group's loads go out before this row is reduced
+            if (g + 1 < n_groups) fetch_group(row, g + 1);
+            else if (row + row_stride < out_dim) fetch_group(row + row_stride, 0);
+        }
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            const float v = warp_sum(acc[b]);
+            if (lane == 0 && b < (int)n_rows) y[(size_t)b * out_dim + row] = v;
+        }
+    }
+}
+
 
 template <int FMT, int NB, bool DUMP>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, MinBlocks<NB>::v)
@@ -532,6 +607,7 @@ struct Tuning {
     int ks = 0;          // 0 = heuristic
     int grid_mult = 0;   // CTAs launched per resident CTA slot; 0 = heuristic
     int no_pdl = 0;      // plain launches (for A/B timing)
+    int no_rows_kernel = 0;
 };
 Tuning g_tune;
 
@@ -539,6 +615,19 @@ template <int FMT> size_t stream_smem_bytes(uint32_t n_rows, uint32_t n_sub, int
 {
     const size_t x = (((size_t)n_rows * n_sub * FmtTraits<FMT>::x_bytes) + 15u) & ~(size_t)15u;
     return x + 2u * kWarpsPerCta * (size_t)nb * sizeof(float);
+}
+
+template <int FMT, int NB, int LEN>
+int launch_rows(cudaStream_t s, const void *w, const void *xq, float *y, uint32_t in_dim, uint32_t out_dim,
+                uint32_t n_rows, uint32_t grid, size_t smem)
+{
+    if (g_tune.no_pdl) {
+        matvec_rows_kernel<FMT, NB, LEN><<<grid, kWarpsPerCta * 32, smem, s>>>((const uint8_t *)w, (const uint8_t *)xq, y,
+                                                                            in_dim, out_dim, n_rows);
+        return (int)cudaGetLastError();
+    }
+    return (int)launch_pdl(matvec_rows_kernel<FMT, NB, LEN>, dim3(grid), dim3(kWarpsPerCta * 32), smem, s,
+                           (const uint8_t *)w, (const uint8_t *)xq, y, in_dim, out_dim, n_rows);
 }
 
 template <int FMT, int NB, bool DUMP>
@@ -561,6 +650,32 @@ int launch_one(cudaStream_t s, const void *w, const void *xq, float *y, int32_t 
         while (ks * 2u <= (uint32_t)g_tune.ks && ks * 2u <= (uint32_t)kWarpsPerCta && ks * 2u <= n_iters) ks *= 2u;
     }
     if (DUMP) ks = 1;
+    if constexpr (!DUMP && NB <= 4) {
+        if (ks == 1 && n_sub % 32u == 0 && !g_tune.no_rows_kernel) {
+            // group length: the whole row if it is short, else its largest divisor up to 5 (3 at least)
+            uint32_t len = 0;
+            if (n_iters <= 5) len = n_iters;
+            else
+                for (uint32_t c = 5; c >= 3 && !len; c--)
+                    if (n_iters % c == 0) len = c;
+            const uint32_t capacity = (uint32_t)sm_count() * resident;
+            const uint32_t n_cta_rows = (out_dim + kWarpsPerCta - 1u) / kWarpsPerCta;
+            const uint32_t mult = g_tune.grid_mult > 0 ? (uint32_t)g_tune.grid_mult : (n_cta_rows >= 3u * capacity ? 2u : 1u);
+            const uint32_t grid = min(n_cta_rows, capacity * mult);
+            const size_t xsm = (((size_t)n_rows * n_sub * FmtTraits<FMT>::x_bytes) + 15u) & ~(size_t)15u;
+#define RC_ROWS(L) \
+    case L: \
+        if (FmtTraits<FMT>::rows_len_ok(L)) \
+            return launch_rows<FMT, NB, L>(s, w, xq, y, in_dim, out_dim, n_rows, grid, xsm); \
+        break;
+            switch (len) {
+                RC_ROWS(3)
+                RC_ROWS(4)
+                RC_ROWS(5)
+            }
+#undef RC_ROWS
+        }
+    }
     const uint32_t rb_rows = kWarpsPerCta / ks;
     const uint32_t n_blocks = (out_dim + rb_rows - 1u) / rb_rows;
     // Two CTAs per resident slot even out the tail once a CTA has three or more row blocks.
@@ -610,6 +725,15 @@ template <int FMT, int NB, bool DUMP> int set_attr_one()
 
 constexpr int kGroupedBN = 16;
 
+template <int FMT, int NB> int set_attr_rows()
+{
+    int rc = 0;
+    rc |= (int)cudaFuncSetAttribute(matvec_rows_kernel<FMT, NB, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
+    rc |= (int)cudaFuncSetAttribute(matvec_rows_kernel<FMT, NB, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
+    rc |= (int)cudaFuncSetAttribute(matvec_rows_kernel<FMT, NB, 5>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
+    return rc;
+}
+
 template <int FMT> int set_attr_fmt()
 {
     int rc = 0;
@@ -623,6 +747,7 @@ template <int FMT> int set_attr_fmt()
     rc |= set_attr_one<FMT, 4, true>();
     rc |= set_attr_one<FMT, 8, true>();
     rc |= set_attr_one<FMT, 16, true>();
+    rc |= set_attr_rows<FMT, 1>() | set_attr_rows<FMT, 2>() | set_attr_rows<FMT, 4>();
     rc |= (int)cudaFuncSetAttribute(matvec_grouped_kernel<FMT, kGroupedBN>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
     return rc;
@@ -686,7 +811,8 @@ void matvec_set_tuning(int ks, int grid_mult, int no_pdl)
 {
     g_tune.ks = ks;
     g_tune.grid_mult = grid_mult;
-    g_tune.no_pdl = no_pdl;
+    g_tune.no_pdl = no_pdl & 1;
+    g_tune.no_rows_kernel = (no_pdl >> 1) & 1;
 }
 bool matvec_pdl_enabled() { return !g_tune.no_pdl; }
 
