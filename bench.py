@@ -237,7 +237,7 @@ def workload_config(n_gpus: int) -> dict:
 # ------------------------------------------------------------------------------------- GPU arm
 
 # DRAM bytes of one Q4_K 5120->17408 matvec launch, from the ncu capture summarised in
-# profiles/matvec_stream_q4k_5120x17408.md (algorithmic bytes: 51,527,680).
+# profiles/matvec_q4k_5120x17408.md (algorithmic bytes: 51,527,680).
 Q4K_DRAM_TRAFFIC_BYTES = 51_566_000
 INT8_DENSE_PEAK_TOPS = 4500.0  # nominal B200 dense int8; no measured int8 figure is supplied
 
@@ -258,7 +258,7 @@ def mmq_prefill(rt, synth, torch, dev, timed):
     ms_k = timed(lambda i: rt.launch_mmq_gemm(w, xq, y, P), reps, 3) / reps
     ms_q = timed(lambda i: gemm.matmul_into(y, w, x, P), reps, 3) / reps
     tops = ops / (ms_k * 1e-3) / 1e12
-    return {"workload": "config 4: 512 tokens x Q4_K 5120->17408 (91.3 GOP)", "kernel": "mmq_kernel<Q4_K,128> (tcgen05 kind::i8)",
+    return {"workload": "config 4: 512 tokens x Q4_K 5120->17408 (91.3 GOP)", "kernel": "mmq_kernel<Q4_K,128,16,2> (tcgen05 kind::i8; TMA-fed planar activations through PrefillGemm)",
             "us_kernel": ms_k * 1e3, "tops_kernel": tops, "us_with_quantize": ms_q * 1e3,
             "tops_with_quantize": ops / (ms_q * 1e-3) / 1e12,
             "roofline": {"bound": "tensor", "achieved": tops, "peak": INT8_DENSE_PEAK_TOPS, "unit": "TOP/s",
@@ -303,22 +303,22 @@ def run_gpu_arm(args):
     layer_bytes_local = sum(w.data.numel() for w in copies[0])
     layer_bytes_total = layer_bytes_local * world
 
-    x_host = torch.from_numpy(synth.synth_activations(1, HIDDEN, 5)).pin_memory()
-    h_host = torch.from_numpy(synth.synth_activations(1, FFN, 6)).pin_memory()
-    x_dev = torch.empty_like(x_host, device=dev)
-    h_dev = torch.empty_like(h_host, device=dev)
-    x_dev.copy_(x_host)
-    h_dev.copy_(h_host)
+    # one pinned input block [x | h] and one device copy of it, so a step uploads with one copy
+    in_host = torch.cat([torch.from_numpy(synth.synth_activations(1, HIDDEN, 5)),
+                         torch.from_numpy(synth.synth_activations(1, FFN, 6))], dim=1).pin_memory()
+    in_dev = torch.empty_like(in_host, device=dev)
+    in_dev.copy_(in_host)
+    x_dev, h_dev = in_dev[:, :HIDDEN], in_dev[:, HIDDEN:]
     xq = torch.empty((HIDDEN // 32) * 40, dtype=torch.uint8, device=dev)
     hq = torch.empty((FFN // 32) * 40, dtype=torch.uint8, device=dev)
-    y_gate = torch.empty(FFN // world, device=dev)
-    y_up = torch.empty(FFN // world, device=dev)
+    # gate | up outputs side by side: one download per step for them, one for down's gathered rows
+    y_gu = torch.empty(2 * (FFN // world), device=dev)
+    y_gate, y_up = y_gu[:FFN // world], y_gu[FFN // world:]
     y_down = torch.empty(HIDDEN // world, device=dev)
     g_gate = torch.empty(FFN, device=dev) if world > 1 else y_gate
     g_up = torch.empty(FFN, device=dev) if world > 1 else y_up
     g_down = torch.empty(HIDDEN, device=dev) if world > 1 else y_down
-    yg_host = torch.empty(FFN, dtype=torch.float32).pin_memory()
-    yu_host = torch.empty(FFN, dtype=torch.float32).pin_memory()
+    ygu_host = torch.empty(2 * (FFN // world), dtype=torch.float32).pin_memory()
     yd_host = torch.empty(HIDDEN, dtype=torch.float32).pin_memory()
     launches_per_step = 5
 
@@ -367,11 +367,9 @@ def run_gpu_arm(args):
         assert torch.equal(got, hq), "peer gather of the quantized intermediate differs from the local quantization"
 
     def step_e2e(c: int):
-        x_dev.copy_(x_host, non_blocking=True)
-        h_dev.copy_(h_host, non_blocking=True)
+        in_dev.copy_(in_host, non_blocking=True)
         step(c)
-        yg_host[:y_gate.numel()].copy_(y_gate, non_blocking=True)
-        yu_host[:y_up.numel()].copy_(y_up, non_blocking=True)
+        ygu_host.copy_(y_gu, non_blocking=True)
         if push:
             ga_y.copy_out(yd_host)
         else:
@@ -431,9 +429,24 @@ def run_gpu_arm(args):
     ms_per_step = ms / steps_timed
     value = layer_bytes_total / (ms_per_step * 1e-3) / 1e9
 
-    # end to end: host buffers in, host buffers out, copies inside the timed region
-    ms_e2e = timed(step_e2e, args.steps, max(3, args.warmup))
-    e2e_value = layer_bytes_total / (ms_e2e / args.steps * 1e-3) / 1e9
+    # end to end: host buffers in, host buffers out, copies inside the timed region.  Like the
+    # device-resident steps, a user replays this from a CUDA graph (pinned-memory copies are
+    # ordinary graph nodes): n_copies steps per graph, every one with its own uploads and downloads.
+    if use_graph:
+        for i in range(2):
+            step_e2e(i)
+        torch.cuda.synchronize()
+        graph_e2e = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph_e2e):
+            for c in range(n_copies):
+                step_e2e(c)
+        e2e_calls = max(1, (args.steps + n_copies - 1) // n_copies)
+        ms_e2e = timed(lambda i: graph_e2e.replay(), e2e_calls, 3)
+        e2e_steps = e2e_calls * n_copies
+    else:
+        ms_e2e = timed(step_e2e, args.steps, max(3, args.warmup))
+        e2e_steps = args.steps
+    e2e_value = layer_bytes_total / (ms_e2e / e2e_steps * 1e-3) / 1e9
 
     # dominant kernel alone: the Q4_K matvec over rotating copies, CUDA events on its stream
     q4k_bytes = copies[0][0].data.numel()
@@ -484,15 +497,15 @@ def run_gpu_arm(args):
             "data": "synthetic", "config": workload_config(world),
             "e2e": {"value": e2e_value, "unit": "GB/s",
                     "h2d_bytes_per_step": (HIDDEN + FFN) * 4, "d2h_bytes_per_step": (2 * FFN // world + HIDDEN) * 4,
-                    "ms_per_step": ms_e2e / args.steps},
+                    "ms_per_step": ms_e2e / e2e_steps, "graph_replay": use_graph},
             "gpu_launches": (launches_per_step + (2 if push else 0)) * steps_timed,
             "gather": ("peer-push" if push else "nccl") if world > 1 else None,
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": "matvec_stream_kernel<Q4_K,1> 5120->%d" % (FFN // world),
+            "roofline": {"bound": "hbm", "kernel": "matvec_rows_kernel<Q4_K,1,5> 5120->%d" % (FFN // world),
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "us_per_launch": q4k_us, "bytes_per_launch": q4k_bytes,
                          "traffic": Q4K_DRAM_TRAFFIC_BYTES if world == 1 else None,
-                         "traffic_source": "profiles/matvec_stream_q4k_5120x17408.md (ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch)"},
+                         "traffic_source": "profiles/matvec_q4k_5120x17408.md (ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch)"},
             "per_kernel": {"q4k_gate_up_gbs": achieved, "q6k_down_gbs": q6_bytes / (q6_us * 1e-6) / 1e9,
                            "q6k_us": q6_us},
             "tok_per_s_per_layer": 1e3 / ms_per_step,
