@@ -322,6 +322,41 @@ template <int FMT, int BN> struct Smem {
     static constexpr uint32_t total = misc_off + 16 + 1024;    // + alignment slack
 };
 
+// Explicit shared-space loads (the operand areas are addressed through a realigned pointer, which
+// the compiler would otherwise treat as generic).
+__device__ __forceinline__ ulonglong2 lds_u64x2(uint32_t addr)
+{
+    ulonglong2 v;
+    asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(v.x), "=l"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds_u4(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds_u2(uint32_t addr)
+{
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts_u4(uint32_t addr, const uint4 &v)
+{
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void sts_u32(uint32_t addr, uint32_t v)
+{
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
 // Packed pairs of f32 (one instruction, two lanes' worth of results): halves the issue slots of the drain.
 __device__ __forceinline__ unsigned long long pack2(float lo, float hi)
 {
@@ -507,22 +542,22 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUt
 #pragma unroll
                 for (int rr = 0; rr < ROWS_PT; rr++) {
                     const uint32_t r = tid + rr * kExpT;
-                    uint32_t *rs = reinterpret_cast<uint32_t *>(smem + L::rsc_off + s * L::rsc_stage);
+                    const uint32_t rs = sbase + L::rsc_off + s * L::rsc_stage + r * 4u;
 #pragma unroll
-                    for (int j = 0; j < kKS; j++) rs[j * kBM + r] = sc[rr].s[j];
-                    rs[kKS * kBM + r] = sc[rr].dd;
+                    for (int j = 0; j < kKS; j++) sts_u32(rs + j * kBM * 4u, sc[rr].s[j]);
+                    sts_u32(rs + kKS * kBM * 4u, sc[rr].dd);
 #pragma unroll
                     for (int j = 0; j < kKS; j++) {
                         if (j < (int)nsteps) {
-                            const uint8_t *rp = smem + L::raw_off + s * L::raw_stage + j * MmqTraits<FMT>::raw_bytes + r * 16u;
-                            const uint4 q = *reinterpret_cast<const uint4 *>(rp);
+                            const uint32_t rp = sbase + L::raw_off + s * L::raw_stage + j * MmqTraits<FMT>::raw_bytes + r * 16u;
+                            const uint4 q = lds_u4(rp);
                             uint4 q2 = make_uint4(0, 0, 0, 0);
-                            if constexpr (FMT == Q8_0) q2 = *reinterpret_cast<const uint4 *>(rp + kBM * 16);
+                            if constexpr (FMT == Q8_0) q2 = lds_u4(rp + kBM * 16);
                             uint4 lo, hi;
                             expand_weights<FMT>(q, q2, extra[rr][j], lo, hi);
-                            uint8_t *ap = smem + L::a_off + (s * kKS + j) * L::a_sub + r * 16u;
-                            *reinterpret_cast<uint4 *>(ap) = lo;
-                            *reinterpret_cast<uint4 *>(ap + kBM * 16) = hi;
+                            const uint32_t ap = sbase + L::a_off + (s * kKS + j) * L::a_sub + r * 16u;
+                            sts_u4(ap, lo);
+                            sts_u4(ap + kBM * 16, hi);
                         }
                     }
                 }
@@ -536,11 +571,11 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUt
                         for (int n = 0; n < GROUP; n++) {
                             const uint32_t q = tid + (n0 + n) * kExpT, tok = q % BN, j = q / BN;
                             if (j < nsteps) {
-                                uint8_t *bp = smem + L::b_off + (s * kKS + j) * L::b_sub + tok * 16u;
-                                *reinterpret_cast<uint4 *>(bp) = make_uint4(xb[n][1].x, xb[n][1].y, xb[n][2].x, xb[n][2].y);
-                                *reinterpret_cast<uint4 *>(bp + BN * 16) = make_uint4(xb[n][3].x, xb[n][3].y, xb[n][4].x, xb[n][4].y);
-                                reinterpret_cast<uint32_t *>(smem + L::dx_off + (s * kKS + j) * L::sx_sub)[tok] = xb[n][0].x;
-                                reinterpret_cast<uint32_t *>(smem + L::xs_off + (s * kKS + j) * L::sx_sub)[tok] = xb[n][0].y;
+                                const uint32_t bp = sbase + L::b_off + (s * kKS + j) * L::b_sub + tok * 16u;
+                                sts_u4(bp, make_uint4(xb[n][1].x, xb[n][1].y, xb[n][2].x, xb[n][2].y));
+                                sts_u4(bp + BN * 16, make_uint4(xb[n][3].x, xb[n][3].y, xb[n][4].x, xb[n][4].y));
+                                sts_u32(sbase + L::dx_off + (s * kKS + j) * L::sx_sub + tok * 4u, xb[n][0].x);
+                                sts_u32(sbase + L::xs_off + (s * kKS + j) * L::sx_sub + tok * 4u, xb[n][0].y);
                             }
                         }
                     }
@@ -571,16 +606,16 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUt
                 const uint32_t nsteps = min((uint32_t)kKS, n_sub - i * kKS);
                 // the stage's token scales and this row's scale words were staged before op_full completed
                 if (!mbar_wait(op_full(s), (it / kStages) & 1u, abort_flag, 6u)) goto epi_done;
-                const uint32_t *rs = reinterpret_cast<const uint32_t *>(smem + L::rsc_off + s * L::rsc_stage) + quarter * 32u + lane;
+                const uint32_t rs = sbase + L::rsc_off + s * L::rsc_stage + (quarter * 32u + lane) * 4u;
                 float d_sup = 0.0f, dmin_sup = 0.0f;
                 if constexpr (MmqTraits<FMT>::has_min) {
-                    const uint32_t dd = rs[kKS * kBM];
+                    const uint32_t dd = lds_u32(rs + kKS * kBM * 4u);
                     d_sup = f16_bits_to_f32(dd);
                     dmin_sup = f16_bits_to_f32(dd >> 16);
                 }
                 // drain of one sub-block's columns (already in registers) into the accumulators
                 auto drain = [&](const uint32_t (&d)[32], int j, int ch) {
-                    const uint32_t sw = rs[j * kBM];
+                    const uint32_t sw = lds_u32(rs + j * kBM * 4u);
                     float dsc, ndeff = 0.0f;
                     if constexpr (MmqTraits<FMT>::has_min) {
                         dsc = d_sup * (float)(sw & 0xFFu);
@@ -590,11 +625,11 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUt
                     }
                     const unsigned long long dsc2 = pack2(dsc, dsc), ndeff2 = pack2(ndeff, ndeff);
                     const unsigned long long unbias2 = pack2(-12582912.0f, -12582912.0f);
-                    const float *dxp = reinterpret_cast<const float *>(smem + L::dx_off + (s * kKS + j) * L::sx_sub) + half * COLS;
-                    const float *xsp = reinterpret_cast<const float *>(smem + L::xs_off + (s * kKS + j) * L::sx_sub) + half * COLS;
+                    const uint32_t dxp = sbase + L::dx_off + (s * kKS + j) * L::sx_sub + half * COLS * 4u;
+                    const uint32_t xsp = sbase + L::xs_off + (s * kKS + j) * L::sx_sub + half * COLS * 4u;
 #pragma unroll
                     for (int c = 0; c < CW; c += 4) {
-                        const ulonglong2 dx4 = *reinterpret_cast<const ulonglong2 *>(dxp + ch * 32 + c);
+                        const ulonglong2 dx4 = lds_u64x2(dxp + (ch * 32 + c) * 4u);
                         // exact int -> float: bias into [2^23, 2^24) as an integer, remove it as a float
                         const unsigned long long f01 = (unsigned long long)(d[c] + 0x4B400000u) |
                                                        ((unsigned long long)(d[c + 1] + 0x4B400000u) << 32);
@@ -604,7 +639,7 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUt
                         a01 = fma2(dsc2, mul2(add2(f01, unbias2), dx4.x), a01);
                         a23 = fma2(dsc2, mul2(add2(f23, unbias2), dx4.y), a23);
                         if constexpr (MmqTraits<FMT>::has_min) {
-                            const ulonglong2 xs4 = *reinterpret_cast<const ulonglong2 *>(xsp + ch * 32 + c);
+                            const ulonglong2 xs4 = lds_u64x2(xsp + (ch * 32 + c) * 4u);
                             a01 = fma2(ndeff2, xs4.x, a01);
                             a23 = fma2(ndeff2, xs4.y, a23);
                         }
@@ -1006,24 +1041,24 @@ mmq16_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ C
 #pragma unroll
                 for (int rr = 0; rr < ROWS_PT; rr++) {
                     const uint32_t r = tid + rr * kExpanders16;
-                    uint32_t *rs = reinterpret_cast<uint32_t *>(smem + L::rsc_off + s * L::rsc_stage);
+                    const uint32_t rs = sbase + L::rsc_off + s * L::rsc_stage + r * 4u;
 #pragma unroll
-                    for (int j = 0; j < kKS16; j++) rs[j * kBM + r] = smw[rr][j];
-                    rs[kKS16 * kBM + r] = ddw[rr];
+                    for (int j = 0; j < kKS16; j++) sts_u32(rs + j * kBM * 4u, smw[rr][j]);
+                    sts_u32(rs + kKS16 * kBM * 4u, ddw[rr]);
 #pragma unroll
                     for (int j = 0; j < kKS16; j++) {
                         if (j < (int)nsteps && !(P.debug & 2u)) {
-                            const uint8_t *rp = smem + L::raw_off + s * L::raw_stage + j * T::raw_bytes + r * 16u;
-                            const uint4 q = *reinterpret_cast<const uint4 *>(rp);
+                            const uint32_t rp = sbase + L::raw_off + s * L::raw_stage + j * T::raw_bytes + r * 16u;
+                            const uint4 q = lds_u4(rp);
                             uint4 q2 = make_uint4(0, 0, 0, 0);
-                            if constexpr (FMT == Q8_0) q2 = *reinterpret_cast<const uint4 *>(rp + kBM * 16);
+                            if constexpr (FMT == Q8_0) q2 = lds_u4(rp + kBM * 16);
                             uint4 o[2][4];
                             expand_f16<FMT>(q, q2, e0[rr][j], e1[rr][j], smw[rr][j], o);
 #pragma unroll
                             for (int part = 0; part < T::a_parts; part++) {
-                                uint8_t *ap = smem + L::a_off + (s * kKS16 + j) * L::a_sub + part * L::a_part + r * 16u;
+                                const uint32_t ap = sbase + L::a_off + (s * kKS16 + j) * L::a_sub + part * L::a_part + r * 16u;
 #pragma unroll
-                                for (int c = 0; c < 4; c++) *reinterpret_cast<uint4 *>(ap + c * kBM * 16) = o[part][c];
+                                for (int c = 0; c < 4; c++) sts_u4(ap + c * kBM * 16, o[part][c]);
                             }
                         }
                     }
@@ -1035,21 +1070,19 @@ mmq16_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ C
                     if (j < nsteps && !(P.debug & 16u)) {
                         const __half2 one = __half2half2(__float2half(1.0f)), off = __half2half2(__float2half(-1152.0f));
                         if (P.b_tma) {
-                            const uint2 *src = reinterpret_cast<const uint2 *>(
-                                smem + L::braw_off + s * L::braw_stage + (tok * kKS16 + j) * RC_BLOCKQ8_BYTES);
+                            const uint32_t src = sbase + L::braw_off + s * L::braw_stage + (tok * kKS16 + j) * RC_BLOCKQ8_BYTES;
                             const bool ok = tok < t.n_valid; // rows past the tile's tokens belong to someone else
 #pragma unroll
-                            for (int w = 0; w < 5; w++) xb[n][w] = ok ? src[w] : make_uint2(0u, 0u);
+                            for (int w = 0; w < 5; w++) xb[n][w] = ok ? lds_u2(src + w * 8u) : make_uint2(0u, 0u);
                         }
-                        uint8_t *bp = smem + L::b_off + (s * kKS16 + j) * L::b_sub + tok * 16u;
+                        const uint32_t bp = sbase + L::b_off + (s * kKS16 + j) * L::b_sub + tok * 16u;
 #pragma unroll
                         for (int c = 0; c < 4; c++) {
                             const uint2 w2 = xb[n][1 + c]; // qs[8c .. 8c+7]
-                            *reinterpret_cast<uint4 *>(bp + c * BN * 16) =
-                                kc_block(w2.x ^ 0x80808080u, w2.y ^ 0x80808080u, one, off);
+                            sts_u4(bp + c * BN * 16, kc_block(w2.x ^ 0x80808080u, w2.y ^ 0x80808080u, one, off));
                         }
-                        reinterpret_cast<uint32_t *>(smem + L::dx_off + (s * kKS16 + j) * L::sx_sub)[tok] = xb[n][0].x;
-                        reinterpret_cast<uint32_t *>(smem + L::xs_off + (s * kKS16 + j) * L::sx_sub)[tok] = xb[n][0].y;
+                        sts_u32(sbase + L::dx_off + (s * kKS16 + j) * L::sx_sub + tok * 4u, xb[n][0].x);
+                        sts_u32(sbase + L::xs_off + (s * kKS16 + j) * L::sx_sub + tok * 4u, xb[n][0].y);
                     }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1079,11 +1112,11 @@ mmq16_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ C
                 const uint32_t k0 = i * kKS16, nsteps = min((uint32_t)kKS16, n_sub - k0);
                 if (!mbar_wait16(op_full(s), (it / kStages16) & 1u, abort_flag, 6u)) goto epi_done;
                 // this row's scale words, staged by the expanders before op_full completed
-                const uint32_t *rs = reinterpret_cast<const uint32_t *>(smem + L::rsc_off + s * L::rsc_stage) + quarter * 32u + lane;
-                const uint32_t dd_cur = rs[kKS16 * kBM];
+                const uint32_t rs = sbase + L::rsc_off + s * L::rsc_stage + (quarter * 32u + lane) * 4u;
+                const uint32_t dd_cur = lds_u32(rs + kKS16 * kBM * 4u);
                 uint32_t s_cur[kKS16];
 #pragma unroll
-                for (int j = 0; j < kKS16; j++) s_cur[j] = rs[j * kBM];
+                for (int j = 0; j < kKS16; j++) s_cur[j] = lds_u32(rs + j * kBM * 4u);
                 const float d_sup = T::fold ? f16_bits_to_f32(dd_cur) : 0.0f;
                 const float dmin_sup = T::has_min ? f16_bits_to_f32(dd_cur >> 16) : 0.0f;
 #pragma unroll
@@ -1094,8 +1127,8 @@ mmq16_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ C
                         tc_fence_after();
                         const float dsc = T::fold ? d_sup : f16_bits_to_f32(s_cur[j]);
                         const float ndeff = T::has_min ? -dmin_sup * (float)(s_cur[j] >> 8) : 0.0f;
-                        const float *dxp = reinterpret_cast<const float *>(smem + L::dx_off + (s * kKS16 + j) * L::sx_sub) + half * COLS;
-                        const float *xsp = reinterpret_cast<const float *>(smem + L::xs_off + (s * kKS16 + j) * L::sx_sub) + half * COLS;
+                        const uint32_t dxp = sbase + L::dx_off + (s * kKS16 + j) * L::sx_sub + half * COLS * 4u;
+                        const uint32_t xsp = sbase + L::xs_off + (s * kKS16 + j) * L::sx_sub + half * COLS * 4u;
 #pragma unroll
                         for (int ch = 0; ch < CHUNKS; ch++) {
                             uint32_t d[32];
@@ -1114,11 +1147,11 @@ mmq16_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ C
                             if (P.debug & 4u) continue;
 #pragma unroll
                             for (int c = 0; c < CW; c += 4) {
-                                const float4 dx4 = *reinterpret_cast<const float4 *>(dxp + ch * 32 + c);
-                                float4 xs4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                                if constexpr (T::has_min) xs4 = *reinterpret_cast<const float4 *>(xsp + ch * 32 + c);
-                                const float dxv[4] = {dx4.x, dx4.y, dx4.z, dx4.w};
-                                const float xsv[4] = {xs4.x, xs4.y, xs4.z, xs4.w};
+                                const uint4 dx4 = lds_u4(dxp + (ch * 32 + c) * 4u);
+                                uint4 xs4 = make_uint4(0u, 0u, 0u, 0u);
+                                if constexpr (T::has_min) xs4 = lds_u4(xsp + (ch * 32 + c) * 4u);
+                                const float dxv[4] = {__uint_as_float(dx4.x), __uint_as_float(dx4.y), __uint_as_float(dx4.z), __uint_as_float(dx4.w)};
+                                const float xsv[4] = {__uint_as_float(xs4.x), __uint_as_float(xs4.y), __uint_as_float(xs4.z), __uint_as_float(xs4.w)};
 #pragma unroll
                                 for (int u = 0; u < 4; u++) {
                                     float a = acc[ch * 32 + c + u];
