@@ -624,20 +624,17 @@ mmq_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUt
                         dsc = f16_bits_to_f32(sw);
                     }
                     const unsigned long long dsc2 = pack2(dsc, dsc), ndeff2 = pack2(ndeff, ndeff);
-                    const unsigned long long unbias2 = pack2(-12582912.0f, -12582912.0f);
                     const uint32_t dxp = sbase + L::dx_off + (s * kKS + j) * L::sx_sub + half * COLS * 4u;
                     const uint32_t xsp = sbase + L::xs_off + (s * kKS + j) * L::sx_sub + half * COLS * 4u;
 #pragma unroll
                     for (int c = 0; c < CW; c += 4) {
                         const ulonglong2 dx4 = lds_u64x2(dxp + (ch * 32 + c) * 4u);
-                        // exact int -> float: bias into [2^23, 2^24) as an integer, remove it as a float
-                        const unsigned long long f01 = (unsigned long long)(d[c] + 0x4B400000u) |
-                                                       ((unsigned long long)(d[c + 1] + 0x4B400000u) << 32);
-                        const unsigned long long f23 = (unsigned long long)(d[c + 2] + 0x4B400000u) |
-                                                       ((unsigned long long)(d[c + 3] + 0x4B400000u) << 32);
+                        // int -> float is exact here (|idot| < 2^24) and a full-rate conversion on this part
+                        const unsigned long long f01 = pack2((float)(int)d[c], (float)(int)d[c + 1]);
+                        const unsigned long long f23 = pack2((float)(int)d[c + 2], (float)(int)d[c + 3]);
                         unsigned long long a01 = acc[(ch * 32 + c) / 2], a23 = acc[(ch * 32 + c) / 2 + 1];
-                        a01 = fma2(dsc2, mul2(add2(f01, unbias2), dx4.x), a01);
-                        a23 = fma2(dsc2, mul2(add2(f23, unbias2), dx4.y), a23);
+                        a01 = fma2(dsc2, mul2(f01, dx4.x), a01);
+                        a23 = fma2(dsc2, mul2(f23, dx4.y), a23);
                         if constexpr (MmqTraits<FMT>::has_min) {
                             const ulonglong2 xs4 = lds_u64x2(xsp + (ch * 32 + c) * 4u);
                             a01 = fma2(ndeff2, xs4.x, a01);
