@@ -49,7 +49,7 @@ template <int FMT> struct FmtTraits {
     // iterations (32 sub-blocks each) whose raw weight registers a warp holds at once
     static constexpr int G = (FMT == Q8_0) ? 3 : (FMT == Q5_K || FMT == Q6_K || FMT == IQ4_XS) ? 4 : 5;
     // group lengths the plain row kernel is built for (longer groups of the wide formats spill)
-    static constexpr bool rows_len_ok(int len) { return len <= ((FMT == Q6_K) ? 3 : (FMT == Q8_0 || FMT == Q5_K) ? 4 : 5); }
+    static constexpr int rows_max_len = (FMT == Q6_K) ? 3 : (FMT == Q8_0 || FMT == Q5_K) ? 4 : 5;
 };
 
 // Staged activations: [n_rows][n_sub] arrays, sub-block index fastest, so a warp's reads are
@@ -491,8 +491,8 @@ template <int NB> struct MinBlocks { static constexpr int v = NB <= 1 ? 4 : NB <
 
 // --------------------------------------------------------------------------------------------
 // The common decode shape gets a loop with nothing else in it: one warp per weight row (no row
-// split), every lane busy in every iteration (in_dim a multiple of 1024), and a row that is a
-// whole number of LEN-iteration groups.  Same loads, same term(), same order of additions per
+// split), every lane busy in every iteration (in_dim a multiple of 1024), a row cut into groups of
+// LEN iterations plus at most one shorter group.  Same loads, same term(), same order of additions per
 // lane as stream_body; it only sheds that kernel's bookkeeping, which is a third of its
 // instructions on a 5-iteration row.
 template <int FMT, int NB, int LEN>
@@ -502,7 +502,8 @@ matvec_rows_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq
 {
     extern __shared__ __align__(16) uint8_t smem[];
     if (NB <= 2) n_rows = NB;
-    const uint32_t n_sub = in_dim >> 5, n_groups = (n_sub >> 5) / LEN;
+    const uint32_t n_sub = in_dim >> 5, n_iters = n_sub >> 5;
+    const uint32_t n_groups = n_iters / LEN, tail = n_iters - n_groups * LEN; // a row = n_groups full groups + a shorter one
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
     const Planes p = planes_of<FMT>(w, in_dim, out_dim);
     const bool sup_a4 = (reinterpret_cast<uintptr_t>(p.sup) & 3u) == 0;
@@ -510,32 +511,33 @@ matvec_rows_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq
     const uint32_t row_stride = gridDim.x * kWarpsPerCta;
 
     Raw<FMT> cur[LEN];
+    // group g of a row; g == n_groups is the short last group (`tail` iterations)
     auto fetch_group = [&](uint32_t row, uint32_t g) {
         const GroupPtrs gp = group_ptrs<FMT>(p, min(row, out_dim - 1u), g * (LEN * 32u) + lane);
-        if (sup_a4) {
+        if (g < n_groups) {
+            if (sup_a4) {
 #pragma unroll
-            for (int i = 0; i < LEN; i++) fetch_off<FMT, true>(cur[i], gp, i);
+                for (int i = 0; i < LEN; i++) fetch_off<FMT, true>(cur[i], gp, i);
+            } else {
+#pragma unroll
+                for (int i = 0; i < LEN; i++) fetch_off<FMT, false>(cur[i], gp, i);
+            }
         } else {
 #pragma unroll
-            for (int i = 0; i < LEN; i++) fetch_off<FMT, false>(cur[i], gp, i);
+            for (int i = 0; i < LEN; i++) {
+                if (i < (int)tail) {
+                    if (sup_a4) fetch_off<FMT, true>(cur[i], gp, i);
+                    else fetch_off<FMT, false>(cur[i], gp, i);
+                }
+            }
         }
     };
-
-    uint32_t row = blockIdx.x * kWarpsPerCta + warp;
-    if (row < out_dim) fetch_group(row, 0); // weights do not wait for x
-    pdl_launch_dependents();
-    pdl_wait();
-    stage_x<FMT>(st, xq, n_rows * n_sub);
-    __syncthreads();
-
-    for (; row < out_dim; row += row_stride) {
-        float acc[NB];
+    float acc[NB];
+    auto compute = [&](uint32_t g, uint32_t n) {
+        const uint32_t sb0 = g * (LEN * 32u) + lane;
 #pragma unroll
-        for (int b = 0; b < NB; b++) acc[b] = 0.0f;
-        for (uint32_t g = 0; g < n_groups; g++) {
-            const uint32_t sb0 = g * (LEN * 32u) + lane;
-#pragma unroll
-            for (int i = 0; i < LEN; i++) {
+        for (int i = 0; i < LEN; i++) {
+            if (i < (int)n) {
 #pragma unroll
                 for (int b = 0; b < NB; b++) {
                     if (b < (int)n_rows) {
@@ -548,9 +550,29 @@ matvec_rows_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq
                     }
                 }
             }
+        }
+    };
+
+    uint32_t row = blockIdx.x * kWarpsPerCta + warp;
+    const uint32_t first_group = n_groups ? 0u : n_groups; // rows shorter than LEN are one short group
+    if (row < out_dim) fetch_group(row, first_group);       // weights do not wait for x
+    pdl_launch_dependents();
+    pdl_wait();
+    stage_x<FMT>(st, xq, n_rows * n_sub);
+    __syncthreads();
+
+    for (; row < out_dim; row += row_stride) {
+#pragma unroll
+        for (int b = 0; b < NB; b++) acc[b] = 0.0f;
+        for (uint32_t g = 0; g < n_groups; g++) {
+            compute(g, LEN);
             // the next group's loads go out before this row is reduced
-            if (g + 1 < n_groups) fetch_group(row, g + 1);
-            else if (row + row_stride < out_dim) fetch_group(row + row_stride, 0);
+            if (g + 1 < n_groups || tail) fetch_group(row, g + 1);
+            else if (row + row_stride < out_dim) fetch_group(row + row_stride, first_group);
+        }
+        if (tail) {
+            compute(n_groups, tail);
+            if (row + row_stride < out_dim) fetch_group(row + row_stride, first_group);
         }
 #pragma unroll
         for (int b = 0; b < NB; b++) {
@@ -559,7 +581,6 @@ matvec_rows_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq
         }
     }
 }
-
 
 template <int FMT, int NB, bool DUMP>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, MinBlocks<NB>::v)
@@ -652,12 +673,12 @@ int launch_one(cudaStream_t s, const void *w, const void *xq, float *y, int32_t 
     if (DUMP) ks = 1;
     if constexpr (!DUMP && NB <= 4) {
         if (ks == 1 && n_sub % 32u == 0 && !g_tune.no_rows_kernel) {
-            // group length: the whole row if it is short, else its largest divisor up to 5 (3 at least)
-            uint32_t len = 0;
-            if (n_iters <= 5) len = n_iters;
-            else
-                for (uint32_t c = 5; c >= 3 && !len; c--)
-                    if (n_iters % c == 0) len = c;
+            // group length: as long as the format's registers allow, the whole row if it is shorter
+            uint32_t len = min(n_iters, (uint32_t)FmtTraits<FMT>::rows_max_len);
+            if (len < 3) len = 3; // shorter rows run as one short group of the LEN = 3 kernel
+            // with several activation rows the math dominates and a ragged last group costs more than
+            // the leaner loop saves: those shapes stay on the general kernel
+            if (NB > 1 && n_iters % len != 0) len = 0;
             const uint32_t capacity = (uint32_t)sm_count() * resident;
             const uint32_t n_cta_rows = (out_dim + kWarpsPerCta - 1u) / kWarpsPerCta;
             const uint32_t mult = g_tune.grid_mult > 0 ? (uint32_t)g_tune.grid_mult : (n_cta_rows >= 3u * capacity ? 2u : 1u);
@@ -665,7 +686,7 @@ int launch_one(cudaStream_t s, const void *w, const void *xq, float *y, int32_t 
             const size_t xsm = (((size_t)n_rows * n_sub * FmtTraits<FMT>::x_bytes) + 15u) & ~(size_t)15u;
 #define RC_ROWS(L) \
     case L: \
-        if (FmtTraits<FMT>::rows_len_ok(L)) \
+        if (L <= FmtTraits<FMT>::rows_max_len) \
             return launch_rows<FMT, NB, L>(s, w, xq, y, in_dim, out_dim, n_rows, grid, xsm); \
         break;
             switch (len) {
