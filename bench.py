@@ -94,9 +94,10 @@ class ClockSampler:
 
 
 def moe_layer(rt, synth, torch, dev, timed):
-    """Config 5: 256 experts, top-8 of 512 tokens, hidden 2048, expert FFN 512: sort, gather,
-    grouped gate+up GEMM (Q4_K [1024, 2048] per expert), SwiGLU glue (torch), quantize, grouped down
-    GEMM (Q6_K [2048, 512]), scatter.  HBM-bound: the figure of merit is expert-weight bytes / s."""
+    """Config 5: 256 experts, top-8 of 512 tokens, hidden 2048, expert FFN 512: router top-k, sort,
+    gather, grouped gate+up GEMM (Q4_K [1024, 2048] per expert), SwiGLU + quantize, grouped down
+    GEMM (Q6_K [2048, 512]), scatter, weighted combine; every step a launch of the library.
+    HBM-bound: the figure of merit is expert-weight bytes / s."""
     E, H, F, NT, K = 256, 2048, 512, 512, 8
     lib_tile = 8  # experts' worth of distinct blocks, tiled to 256 experts (bytes are what matter)
 
@@ -106,25 +107,28 @@ def moe_layer(rt, synth, torch, dev, timed):
 
     gu, dn = slab(Q4_K, H, 2 * F, 91), slab(Q6_K, F, H, 92)
     logits = torch.from_numpy(synth.synth_router_logits(NT, E, 93)).to(dev)
-    ids = torch.topk(torch.softmax(logits, -1), K, dim=-1).indices.to(torch.int32).reshape(-1).contiguous()
     NE = NT * K
+    ids = torch.empty(NT, K, dtype=torch.int32, device=dev)
+    wts = torch.empty(NT, K, device=dev)
     x = torch.from_numpy(synth.synth_activations(NT, H, 94)).to(dev)
     moe = rt.MoeGroupedScratch.new(E, NE, device=dev)
     u8 = dict(dtype=torch.uint8, device=dev)
     xq, xg = torch.empty(NT * (H // 32) * 40, **u8), torch.empty(NE * (H // 32) * 40, **u8)
     hq = torch.empty(NE * (F // 32) * 40, **u8)
-    y1, h = torch.empty(NE, 2 * F, device=dev), torch.empty(NE, F, device=dev)
-    y2, out = torch.empty(NE, H, device=dev), torch.empty(NE, H, device=dev)
+    y1 = torch.empty(NE, 2 * F, device=dev)
+    y2, per_entry = torch.empty(NE, H, device=dev), torch.empty(NE, H, device=dev)
+    out = torch.empty(NT, H, device=dev)
 
     def step(i):
+        rt.launch_moe_topk(logits, ids, wts, E, K, NT)
         rt.launch_quantize_q8(x, xq, H, NT)
         rt.launch_moe_sort(moe, ids, NE)
         rt.launch_moe_gather_xq(moe, xq, xg, H // 32, K, NE)
         rt.launch_moe_grouped_gemm(moe, gu, xg, y1, H, 2 * F, NE)
-        torch.mul(torch.nn.functional.silu(y1[:, :F]), y1[:, F:], out=h)  # glue, not part of the path
-        rt.launch_quantize_q8(h, hq, F, NE)
+        rt.launch_moe_act_q8(y1, hq, F, NE, rt.ACT_SWIGLU)
         rt.launch_moe_grouped_gemm(moe, dn, hq, y2, F, H, NE)
-        rt.launch_moe_scatter_rows(moe, y2, out, H, NE)
+        rt.launch_moe_scatter_rows(moe, y2, per_entry, H, NE)
+        rt.launch_moe_combine(per_entry, ids, wts, None, out, H, K, NT)
 
     reps = 10
     us = timed(step, reps, 3) / reps * 1e3

@@ -209,6 +209,30 @@ int rc_mmq_gemm_grouped(void *stream, int ggml_type, const void *slab,
                         const int32_t *tile_off, uint32_t n_expert, const void *xq, float *y,
                         uint32_t in_dim, uint32_t out_dim, uint32_t n_entries);
 
+/* ---- MoE glue around the grouped GEMMs ------------------------------------------------------- */
+
+/* launch_moe_topk (src/runtime/gemma4.rs:1649-1670); kernel moe_topk_f32 (kernels/moe_topk.cpp:17-107):
+ * softmax over n_expert logits per token (NaN logits count as -inf), the n_used largest
+ * probabilities (ties: lowest expert index) renormalised over their sum with the floor
+ * 6.103515625e-5.  logits f32 [n_tok][n_expert]; ids int32, weights f32 [n_tok][n_used].
+ * n_expert <= 1024, n_used <= 32. */
+int rc_moe_topk(void *stream, const float *logits, uint32_t n_tok, uint32_t n_expert, uint32_t n_used,
+                int32_t *ids, float *weights);
+
+/* launch_moe_geglu_q8 (src/runtime/gemma4.rs:1784-1800); kernel moe_geglu_q8_f32
+ * (kernels/moe_geglu_q8.cpp:34-66): act(gate) * up of the fused gate_up GEMM output, quantized
+ * straight to BlockQ8 for the down GEMM.  gu f32 [n_slot][2*ff] (gate half, then up half),
+ * out BlockQ8 [n_slot][ff/32]; ff % 32 == 0.  act: RC_ACT_GEGLU (tanh GELU) or RC_ACT_SWIGLU
+ * (x / (1 + exp(-x)), kernels/swiglu.cpp:11-21). */
+enum rc_gated_act { RC_ACT_GEGLU = 0, RC_ACT_SWIGLU = 1 };
+int rc_moe_act_q8(void *stream, const float *gu, void *out, uint32_t ff, uint32_t n_slot, int act);
+
+/* launch_moe_combine (src/runtime/gemma4.rs:1804-1823); kernel moe_combine_f32
+ * (kernels/moe_combine.cpp:16-37): out[t][i] = sum_j weights[t][j] * expert_scale[ids[t][j]] *
+ * experts[t][j][i], accumulated in slot order.  expert_scale may be NULL (all ones). */
+int rc_moe_combine(void *stream, const float *experts, const int32_t *ids, const float *weights,
+                   const float *expert_scale, float *out, uint32_t hidden, uint32_t n_used, uint32_t n_tok);
+
 /* ---- row-shard gather over NVLink peer memory ---------------------------------------------- */
 
 /* The reference has no collectives (its multi-GPU mode is layer pipelining over

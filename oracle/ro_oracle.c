@@ -754,3 +754,45 @@ void ro_router_topk(const float *logits, size_t n_tok, size_t n_expert, size_t n
     }
     free(p);
 }
+
+/* kernels/moe_geglu_q8.cpp:20-66 (GeGLU) and kernels/swiglu.cpp:11-21 (SwiGLU): the gated
+ * activation of a fused gate_up row, then the BlockQ8 quantizer of ro_quantize_q8.  act_out
+ * (optional) receives the f32 values before quantization. */
+static float ro_gelu_tanh(float x)
+{
+    const float k = 0.7978845608028654f;
+    float c = x + 0.044715f * x * x * x;
+    return 0.5f * x * (1.0f + tanhf(k * c));
+}
+
+void ro_moe_act_q8(const float *gu, uint8_t *out, size_t ff, size_t n_slot, int act, float *act_out)
+{
+    float *v = (float *)malloc(sizeof(float) * (ff ? ff : 1));
+    for (size_t s = 0; s < n_slot; s++) {
+        const float *g = gu + s * 2 * ff, *u = g + ff;
+        for (size_t i = 0; i < ff; i++) {
+            float a = act == 0 ? ro_gelu_tanh(g[i]) : g[i] / (1.0f + expf(-g[i]));
+            v[i] = a * u[i];
+        }
+        if (act_out) memcpy(act_out + s * ff, v, sizeof(float) * ff);
+        ro_quantize_q8(v, out + s * (ff / 32) * RO_BLOCKQ8_BYTES, ff, 1);
+    }
+    free(v);
+}
+
+/* kernels/moe_combine.cpp:16-37: slot-order accumulation; the device compiler contracts the
+ * source's acc += s * v into one fused multiply-add, written out here. */
+void ro_moe_combine(const float *experts, const int32_t *ids, const float *weights, const float *expert_scale,
+                    float *out, size_t hidden, size_t n_used, size_t n_tok)
+{
+    for (size_t t = 0; t < n_tok; t++)
+        for (size_t i = 0; i < hidden; i++) {
+            float acc = 0.0f;
+            for (size_t j = 0; j < n_used; j++) {
+                float w = weights[t * n_used + j];
+                float sc = expert_scale ? w * expert_scale[ids[t * n_used + j]] : w;
+                acc = fmaf(sc, experts[(t * n_used + j) * hidden + i], acc);
+            }
+            out[t * hidden + i] = acc;
+        }
+}

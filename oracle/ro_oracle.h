@@ -101,6 +101,15 @@ void ro_moe_sort(const int32_t *ids, size_t n_entries, size_t n_expert, size_t b
 void ro_router_topk(const float *logits, size_t n_tok, size_t n_expert, size_t n_used,
                     int32_t *ids, float *weights);
 
+/* kernels/moe_geglu_q8.cpp:34-66: BlockQ8(act(gate) * up) of gu [n_slot][2*ff]; act 0 = tanh GELU,
+ * 1 = SiLU (kernels/swiglu.cpp:11-21).  act_out (may be NULL) gets the f32 values. */
+void ro_moe_act_q8(const float *gu, uint8_t *out, size_t ff, size_t n_slot, int act, float *act_out);
+
+/* kernels/moe_combine.cpp:16-37: out[t][i] = sum_j (weights[t][j] * expert_scale[ids[t][j]]) *
+ * experts[t][j][i]; expert_scale may be NULL. */
+void ro_moe_combine(const float *experts, const int32_t *ids, const float *weights, const float *expert_scale,
+                    float *out, size_t hidden, size_t n_used, size_t n_tok);
+
 /* Grouped GEMM over expert-sorted rows (kernels/mmq_gemm_q4k_grouped.cpp:38-165):
  * rows expert_off[e]..expert_off[e+1] of xq use slab + e*bytes_per_expert. */
 int ro_grouped_q8(int type, const uint8_t *slab, size_t bytes_per_expert,

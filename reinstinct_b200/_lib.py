@@ -55,6 +55,9 @@ _SIGNATURES = {
     "rc_moe_gather_xq": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32]),
     "rc_moe_scatter_rows": (_i, [_vp, _vp, _vp, _vp, _u32, _u32]),
     "rc_mmq_gemm_grouped": (_i, [_vp, _i, _vp, _sz, _vp, _vp, _u32, _vp, _vp, _u32, _u32, _u32]),
+    "rc_moe_topk": (_i, [_vp, _vp, _u32, _u32, _u32, _vp, _vp]),
+    "rc_moe_act_q8": (_i, [_vp, _vp, _vp, _u32, _u32, _i]),
+    "rc_moe_combine": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32]),
     "rc_ipc_get_handle": (_i, [_vp, _vp]),
     "rc_ipc_open_handle": (_i, [_vp, C.POINTER(_vp)]),
     "rc_ipc_close_handle": (_i, [_vp]),

@@ -318,6 +318,42 @@ int rc_mmq_gemm_grouped(void *stream, int type, const void *slab, size_t bytes_p
                               n_expert, xq, y, in_dim, out_dim, n_entries);
 }
 
+/* ---- MoE glue ------------------------------------------------------------------------------------ */
+
+int rc_moe_topk(void *stream, const float *logits, uint32_t n_tok, uint32_t n_expert, uint32_t n_used,
+                int32_t *ids, float *weights)
+{
+    if (n_tok == 0) return RC_OK;
+    if (n_expert == 0 || n_expert > 1024 || n_used == 0 || n_used > 32 || n_used > n_expert) return RC_ERR_BAD_ARGUMENT;
+    if (!logits || !ids || !weights) return RC_ERR_NULL_POINTER;
+    int rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_moe_topk(S(stream), logits, n_tok, n_expert, n_used, ids, weights);
+}
+
+int rc_moe_act_q8(void *stream, const float *gu, void *out, uint32_t ff, uint32_t n_slot, int act)
+{
+    if (ff == 0 || ff % 32) return RC_ERR_BAD_SHAPE;
+    if (act != RC_ACT_GEGLU && act != RC_ACT_SWIGLU) return RC_ERR_BAD_ARGUMENT;
+    if (n_slot == 0) return RC_OK;
+    if (!gu || !out) return RC_ERR_NULL_POINTER;
+    if (((uintptr_t)gu & 3u) || ((uintptr_t)out & 7u)) return RC_ERR_MISALIGNED;
+    int rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_moe_act_q8(S(stream), gu, out, ff, n_slot, act);
+}
+
+int rc_moe_combine(void *stream, const float *experts, const int32_t *ids, const float *weights,
+                   const float *expert_scale, float *out, uint32_t hidden, uint32_t n_used, uint32_t n_tok)
+{
+    if (n_tok == 0 || hidden == 0) return RC_OK;
+    if (n_used == 0) return RC_ERR_BAD_ARGUMENT;
+    if (!experts || !ids || !weights || !out) return RC_ERR_NULL_POINTER;
+    int rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_moe_combine(S(stream), experts, ids, weights, expert_scale, out, hidden, n_used, n_tok);
+}
+
 /* ---- peer gather -------------------------------------------------------------------------------- */
 
 int rc_ipc_get_handle(const void *dev_ptr, void *handle)

@@ -57,6 +57,12 @@ int launch_allgather_push(cudaStream_t s, const void *src, size_t bytes, void *c
                           void *const *peer_flags, void *epoch, uint32_t rank, uint32_t world);
 int gather_device_error(unsigned int *out);
 
+int launch_moe_topk(cudaStream_t s, const float *logits, uint32_t n_tok, uint32_t n_expert, uint32_t n_used,
+                    int32_t *ids, float *weights);
+int launch_moe_act_q8(cudaStream_t s, const float *gu, void *out, uint32_t ff, uint32_t n_slot, int act);
+int launch_moe_combine(cudaStream_t s, const float *experts, const int32_t *ids, const float *weights,
+                       const float *expert_scale, float *out, uint32_t hidden, uint32_t n_used, uint32_t n_tok);
+
 // Per-device one-time setup (kernel attributes); returns RC_OK or an error.
 int ensure_device_ready();
 int sm_count();

@@ -22,6 +22,7 @@ __all__ = [
     "launch_quantize_q8", "launch_matvec", "launch_matvec_xq8", "launch_matvec_batched",
     "matvec_block_dots", "launch_mmq_gemm", "launch_moe_sort", "launch_moe_gather_xq",
     "launch_moe_grouped_gemm", "launch_moe_scatter_rows", "repacked_len", "init", "PeerAllGather",
+    "launch_moe_topk", "launch_moe_act_q8", "launch_moe_combine", "ACT_GEGLU", "ACT_SWIGLU",
 ]
 
 
@@ -254,6 +255,29 @@ def launch_moe_grouped_gemm(moe: MoeGroupedScratch, et: GpuExpertTensor, xq: tor
                                           _ptr(moe.expert_off), _ptr(moe.tile_off), moe.n_expert,
                                           _ptr(xq), _ptr(y), in_dim, out_dim, n_entries),
           "rc_mmq_gemm_grouped")
+
+
+ACT_GEGLU, ACT_SWIGLU = 0, 1
+
+
+def launch_moe_topk(logits: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, n_expert: int, n_used: int,
+                    n_tok: int) -> None:
+    """launch_moe_topk (src/runtime/gemma4.rs:1649-1670)."""
+    assert logits.dtype == torch.float32 and ids.dtype == torch.int32 and weights.dtype == torch.float32
+    check(_lib.load().rc_moe_topk(_stream(), _ptr(logits), n_tok, n_expert, n_used, _ptr(ids), _ptr(weights)),
+          "rc_moe_topk")
+
+
+def launch_moe_act_q8(gu: torch.Tensor, out: torch.Tensor, ff: int, n_slot: int, act: int = ACT_GEGLU) -> None:
+    """launch_moe_geglu_q8 (src/runtime/gemma4.rs:1784-1800); act selects GeGLU or SwiGLU."""
+    check(_lib.load().rc_moe_act_q8(_stream(), _ptr(gu), _ptr(out), ff, n_slot, act), "rc_moe_act_q8")
+
+
+def launch_moe_combine(experts: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, expert_scale,
+                       out: torch.Tensor, hidden: int, n_used: int, n_tok: int) -> None:
+    """launch_moe_combine (src/runtime/gemma4.rs:1804-1823)."""
+    check(_lib.load().rc_moe_combine(_stream(), _ptr(experts), _ptr(ids), _ptr(weights), _ptr(expert_scale),
+                                     _ptr(out), hidden, n_used, n_tok), "rc_moe_combine")
 
 
 class PeerAllGather:

@@ -61,6 +61,10 @@ def lib() -> C.CDLL:
         L.ro_moe_sort.argtypes = [vp, sz, sz, sz, vp, vp, vp, vp]
         L.ro_router_topk.restype = None
         L.ro_router_topk.argtypes = [vp, sz, sz, sz, vp, vp]
+        L.ro_moe_act_q8.restype = None
+        L.ro_moe_act_q8.argtypes = [vp, vp, sz, sz, i, vp]
+        L.ro_moe_combine.restype = None
+        L.ro_moe_combine.argtypes = [vp, vp, vp, vp, vp, sz, sz, sz]
         L.ro_grouped_q8.restype = i
         L.ro_grouped_q8.argtypes = [i, vp, sz, vp, sz, vp, sz, sz, vp, vp]
         _lib = L
@@ -179,6 +183,27 @@ def router_topk(logits: np.ndarray, n_used: int):
     wts = np.empty((n_tok, n_used), dtype=np.float32)
     lib().ro_router_topk(_p(logits), n_tok, n_expert, n_used, _p(ids), _p(wts))
     return ids, wts
+
+
+def moe_act_q8(gu: np.ndarray, act: int):
+    """gu f32 [n_slot, 2*ff] -> (BlockQ8 bytes [n_slot, ff/32, 40], f32 activations [n_slot, ff])."""
+    gu = np.ascontiguousarray(gu, dtype=np.float32)
+    n_slot, ff2 = gu.shape
+    ff = ff2 // 2
+    out = np.zeros((n_slot, ff // 32, 40), dtype=np.uint8)
+    v = np.zeros((n_slot, ff), dtype=np.float32)
+    lib().ro_moe_act_q8(_p(gu), _p(out), ff, n_slot, act, _p(v))
+    return out, v
+
+
+def moe_combine(experts: np.ndarray, ids: np.ndarray, weights: np.ndarray, expert_scale: np.ndarray | None):
+    experts = np.ascontiguousarray(experts, dtype=np.float32)
+    n_tok, n_used, hidden = experts.shape
+    out = np.zeros((n_tok, hidden), dtype=np.float32)
+    sc = None if expert_scale is None else np.ascontiguousarray(expert_scale, dtype=np.float32)
+    lib().ro_moe_combine(_p(experts), _p(np.ascontiguousarray(ids, dtype=np.int32)),
+                         _p(np.ascontiguousarray(weights, dtype=np.float32)), _p(sc), _p(out), hidden, n_used, n_tok)
+    return out
 
 
 def grouped_q8(t: int, slab: np.ndarray, bytes_per_expert: int, expert_off: np.ndarray, xq: np.ndarray,

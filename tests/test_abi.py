@@ -47,4 +47,16 @@ def test_bad_shapes_and_types_are_rejected_before_any_launch():
     assert lib.rc_matvec(None, _lib.Q4_K, None, None, None, 256, 1) == -3
     assert lib.rc_matvec_batched(None, _lib.Q4_K, 16, 8, 4, 256, 1, 17) == -5
     assert lib.rc_matvec(None, _lib.Q4_K, 8, 8, 4, 256, 1) == -4
+    # MoE glue: expert and slot counts beyond what one warp per token holds, odd shapes
+    assert lib.rc_moe_topk(None, 4, 1, 2000, 8, 4, 4) == -8
+    assert lib.rc_moe_topk(None, 4, 1, 128, 33, 4, 4) == -8
+    assert lib.rc_moe_topk(None, 4, 1, 4, 8, 4, 4) == -8
+    assert lib.rc_moe_topk(None, None, 1, 128, 8, 4, 4) == -3
+    assert lib.rc_moe_topk(None, None, 0, 128, 8, None, None) == 0
+    assert lib.rc_moe_act_q8(None, 8, 8, 48, 1, 0) == -2
+    assert lib.rc_moe_act_q8(None, 8, 8, 64, 1, 2) == -8
+    assert lib.rc_moe_act_q8(None, 8, 4, 64, 1, 0) == -4
+    assert lib.rc_moe_act_q8(None, None, None, 64, 0, 0) == 0
+    assert lib.rc_moe_combine(None, 4, 4, 4, None, 4, 16, 0, 1) == -8
+    assert lib.rc_moe_combine(None, None, 4, 4, None, 4, 16, 2, 1) == -3
     assert lib.rc_matmul_scratch_bytes(5120, 4) == 4 * 160 * 40

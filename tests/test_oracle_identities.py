@@ -158,3 +158,34 @@ def test_shapes_rejected():
     assert ro.repacked_len(ro.Q6_K, 17408, 5120) == 73113600
     assert ro.repacked_len(ro.Q4_K, 2048, 1024) == 1230848
     assert ro.repacked_len(ro.Q6_K, 512, 2048) == 913408
+
+
+def test_moe_act_q8_is_quantizer_of_activation():
+    """ro_moe_act_q8 = gated activation in f32, then the ro_quantize_q8 record stream; both
+    activations against f64 formulas (kernels/moe_geglu_q8.cpp:20-32, kernels/swiglu.cpp:11-21)."""
+    rng = np.random.default_rng(3)
+    ff, n_slot = 256, 5
+    gu = (rng.standard_normal((n_slot, 2 * ff)) * 2).astype(np.float32)
+    g, u = gu[:, :ff].astype(np.float64), gu[:, ff:].astype(np.float64)
+    for act, a64 in ((0, 0.5 * g * (1 + np.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))),
+                     (1, g / (1 + np.exp(-g)))):
+        q, v = ro.moe_act_q8(gu, act)
+        # 1 + tanh cancels for negative gates: the error scales with |gate * up|, not the result
+        assert np.all(np.abs(v - a64 * u) <= 2e-6 * np.abs(a64 * u) + 1.5e-7 * np.abs(g * u))
+        np.testing.assert_array_equal(q.reshape(-1), ro.quantize_q8(v).reshape(-1))
+
+
+def test_moe_combine_weighted_sum():
+    rng = np.random.default_rng(4)
+    n_tok, n_used, hidden, n_expert = 3, 4, 40, 16
+    ex = rng.standard_normal((n_tok, n_used, hidden)).astype(np.float32)
+    ids = rng.integers(0, n_expert, (n_tok, n_used)).astype(np.int32)
+    w = rng.random((n_tok, n_used)).astype(np.float32)
+    sc = (rng.random(n_expert) + 0.5).astype(np.float32)
+    out = ro.moe_combine(ex, ids, w, sc)
+    ref = np.einsum("tj,tjh->th", w.astype(np.float64) * sc[ids], ex.astype(np.float64))
+    np.testing.assert_allclose(out, ref, rtol=1e-5, atol=1e-6)
+    ones = ro.moe_combine(ex, ids, w, np.ones(n_expert, dtype=np.float32))
+    np.testing.assert_array_equal(ro.moe_combine(ex, ids, w, None), ones)
+    # one slot with weight 1 and scale 1 returns that expert's row unchanged
+    np.testing.assert_array_equal(ro.moe_combine(ex[:, :1], ids[:, :1], np.ones((n_tok, 1), np.float32), None), ex[:, 0])
