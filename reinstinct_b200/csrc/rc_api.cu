@@ -41,6 +41,8 @@ int ensure_device_ready()
     if (rc) return rc;
     rc = mmq_set_attributes();
     if (rc) return rc;
+    rc = mmq_deq_set_attributes();
+    if (rc) return rc;
     rc = moe_set_attributes();
     if (rc) return rc;
     g_ready[dev] = true;
@@ -173,7 +175,10 @@ size_t rc_matmul_scratch_bytes(uint32_t in_dim, uint32_t n_rows)
     // BlockQ8 records, or the planar form of the same values (a few bytes of row padding more)
     const size_t records = (size_t)n_rows * (in_dim / 32) * RC_BLOCKQ8_BYTES;
     const size_t planar = quantize_planar_bytes(in_dim, n_rows);
-    return records > planar ? records : planar;
+    // beyond the matvec's row limit: the f16 image of the activations the dense GEMM reads
+    const size_t image = n_rows > RC_MATVEC_MAX_ROWS ? mmq_deq_scratch_bytes(in_dim, n_rows) : 0;
+    const size_t m = records > planar ? records : planar;
+    return m > image ? m : image;
 }
 
 int rc_matvec_f32(void *stream, int type, const void *w, const float *x, float *y, uint32_t in_dim,
@@ -526,6 +531,8 @@ extern "C" void rc_tune_mmq(int force_dp4a, int kind)
     rc::mmq_force_dp4a(force_dp4a);
     rc::mmq_set_kind(kind);
 }
+namespace rc { int mmq_deq_read_trace(void *out, size_t bytes); }
+extern "C" int rc_debug_read_trace(void *out, size_t bytes) { return rc::mmq_deq_read_trace(out, bytes); }
 extern "C" int rc_device_status(unsigned int *status)
 {
     if (!status) return RC_ERR_NULL_POINTER;
@@ -534,5 +541,8 @@ extern "C" int rc_device_status(unsigned int *status)
     if (rc) return rc;
     rc = rc::gather_device_error(&g);
     *status |= g << 16;
+    if (rc) return rc;
+    rc = rc::mmq_deq_device_error(&g);
+    *status |= g << 24;
     return rc;
 }

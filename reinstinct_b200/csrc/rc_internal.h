@@ -39,6 +39,13 @@ int launch_mmq_grouped(cudaStream_t s, int type, const void *slab, size_t bytes_
                        const void *xq, float *y, uint32_t in_dim, uint32_t out_dim,
                        uint32_t n_entries);
 int mmq_set_attributes();
+// rc_mmq_deq.cu: the f16-operand dense GEMM (activations as f32 in, scratch holds their f16 image)
+int mmq_deq_set_attributes();
+void mmq_deq_set_bn(int bn);
+int mmq_deq_device_error(unsigned int *out);
+size_t mmq_deq_scratch_bytes(uint32_t in_dim, uint32_t n_tok);
+int launch_mmq_deq_f32(cudaStream_t s, int type, const void *w, const float *x, float *y, uint32_t in_dim, uint32_t out_dim,
+                       uint32_t n_tok, void *scratch);
 uint32_t mmq_grouped_bn();
 uint32_t matvec_grouped_bn();
 void mmq_force_dp4a(int on);

@@ -1,0 +1,647 @@
+// Dense prefill GEMM with both operands dequantized to f16 (tcgen05 kind::f16, f32 accumulator in
+// tensor memory across the whole K range).
+//
+// The block-scaled contraction of the reference's MMQ kernels (kernels/mmq_gemm_q4k_repacked.cpp:63-208
+// and siblings),
+//   Y[tok][row] = sum_sb  dsc[row,sb] * dx[tok,sb] * idot[row,tok,sb]  -  deff[row,sb] * xsum[tok,sb],
+// is the plain product  sum_k w[row,k] * a[tok,k]  of the dequantized weights  w = dsc * q  and the
+// dequantized BlockQ8 activations  a = dx * qx  (plus, for Q4_K / Q5_K, a second product over the
+// sub-blocks:  sum_sb (-deff[row,sb]) * xsum[tok,sb]).  The int8 kernel (rc_mmq.cu) keeps the integer
+// dots exact and pays for it with a drain of the accumulator tile after every 32-wide sub-block, on
+// the CUDA cores.  Here each operand value is rounded ONCE to f16 (a weight is the product of an exact
+// small integer and the format's f16 scale; an activation is dx * qx scaled by a power of two per
+// token so that the token's largest value lands in [256, 512)), the accumulator never leaves tensor
+// memory until the tile is done, and every weight is expanded once for up to 512 tokens.  The result
+// differs from the exact-integer formulation by the two f16 roundings: about 3e-4 in relative L2, a
+// third of the 1e-3 that the reference's own GPU-vs-CPU tests allow.
+//
+// Activations arrive from activations_to_f16_kernel below as the shared-memory image of the B operand:
+//   [16-byte chunk of K][token][8 halves]   (main part: in_dim/8 chunks; then the xsum chunks, one half
+//   per sub-block; then one f32 per token: the inverse of the token's power-of-two scale)
+// so one chunk of a token tile is one contiguous bulk copy.
+//
+// One persistent CTA per SM, 23 warps: warp 0 one thread issuing the activation bulk copies, warp 1 one
+// thread of MMA issue, warp 2 one thread issuing the raw weight TMA loads, warps 3..18 expanders (four
+// groups that take the K steps in turn, thread = weight row), warps 19..22 epilogue.  A tile is
+// 128 weight rows x BN tokens (BN = 512 fills tensor memory: 128 lanes x 512 f32 columns; 256 and 128
+// leave room for two and four accumulator buffers).  Every wait is bounded (see rc_mmq.cu).
+#include <cuda.h>
+
+#include "rc_common.cuh"
+#include "rc_internal.h"
+#include "rc_tc.cuh"
+
+namespace rc {
+namespace {
+
+__device__ unsigned int g_mmqd_error;
+__device__ unsigned long long g_mmqd_trace[160 * 8]; // measurement aid (debug bit 128): phase timestamps per CTA
+
+__device__ __forceinline__ bool mbar_wait_d(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, uint32_t code)
+{
+    if (mbar_try(bar, parity)) return true;
+    // the limit is kept on the SM's own cycle counter, first read after 64 failed polls: a wait
+    // that is about to succeed never pays for a timer read
+    long long t0 = 0;
+    for (uint32_t spin = 1;; spin++) {
+        if (mbar_try(bar, parity)) return true;
+        if ((spin & 63u) == 0u) {
+            if (*abort_flag) return false;
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitCycles) break;
+        }
+    }
+    atomicExch(&g_mmqd_error, code);
+    *abort_flag = 1u;
+    return false;
+}
+// The wait of a single-thread role (producers, MMA issuer): a tight spin on the non-blocking probe.
+__device__ __forceinline__ bool mbar_spin_d(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, uint32_t code)
+{
+    long long t0 = 0;
+    for (uint32_t spin = 1;; spin++) {
+        if (mbar_test(bar, parity)) return true;
+        if ((spin & 1023u) == 0u) {
+            if (*abort_flag) return false;
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitCycles) break;
+        }
+    }
+    atomicExch(&g_mmqd_error, code);
+    *abort_flag = 1u;
+    return false;
+}
+// The same wait made by lane 0 for its warp (one poller instead of 32).
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, uint32_t code)
+{
+    uint32_t ok = 1u;
+    if ((threadIdx.x & 31u) == 0u) ok = mbar_wait_d(bar, parity, abort_flag, code) ? 1u : 0u;
+    return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0u;
+}
+
+// Contiguous global -> shared copy by the TMA unit (no tensor map), completion counted on `bar`.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+template <int FMT> struct DeqTraits {
+    static constexpr bool has_min = (FMT == Q4_K || FMT == Q5_K);
+    static constexpr bool sup_scale = (FMT == Q4_K || FMT == Q5_K || FMT == Q6_K); // f16 d per superblock
+    static constexpr int raw_planes = (FMT == Q8_0) ? 2 : 1;
+    static constexpr uint32_t raw_bytes = raw_planes * kBM * 16;
+};
+
+template <int BN> struct DeqCfg {
+    static constexpr uint32_t stages = BN == 512 ? 4 : 8;
+    static constexpr uint32_t bufs = 512 / BN;
+};
+
+template <int FMT, int BN> struct SmemD {
+    static constexpr uint32_t stages = DeqCfg<BN>::stages;
+    // the raw weight planes come from HBM and run far ahead of the operand ring, in a ring of their own
+    static constexpr uint32_t raw_stages = (BN >= 256 && FMT == Q8_0) ? 8 : 16;
+    static constexpr uint32_t raw_stage = DeqTraits<FMT>::raw_bytes;
+    static constexpr uint32_t a_stage = kBM * 64;  // 128 rows x 32 halves: [chunk 0..3][row][16 B]
+    static constexpr uint32_t b_stage = BN * 64;   // BN tokens x 32 halves: [chunk 0..3][token][16 B]
+    static constexpr uint32_t raw_off = 0;
+    static constexpr uint32_t a_off = raw_off + raw_stages * raw_stage;
+    static constexpr uint32_t b_off = a_off + stages * a_stage;
+    static constexpr uint32_t bar_off = b_off + stages * b_stage;
+    static constexpr uint32_t n_bars = 2 * stages + 2 * raw_stages + 2 * DeqCfg<BN>::bufs;
+    static constexpr uint32_t misc_off = bar_off + n_bars * 8;
+    static constexpr uint32_t total = misc_off + 16 + 1024;
+};
+
+struct DeqParams {
+    const uint8_t *w;
+    const uint8_t *xh;      // f16 operand image written by activations_to_f16_kernel
+    const float *inv_scale; // per token
+    float *y;
+    uint32_t in_dim, out_dim, n_tok, tok_ld;
+    uint32_t debug; // measurement aid: pipeline parts to skip (results invalid): 1 expand, 2 activation copies, 4 MMAs, 8 raw loads
+};
+
+constexpr int kExpGroups = 4;                // groups of four expander warps, one K step each in turn
+constexpr int kExpWarps = 4 * kExpGroups, kEpiWarps = 4;
+constexpr int kLeadWarps = 3;                // activation producer, MMA issuer, raw weight producer
+constexpr int kDeqThreads = (kLeadWarps + kExpWarps + kEpiWarps) * 32;
+
+__device__ __forceinline__ uint4 mul_h2x4(const uint4 &v, __half2 s)
+{
+    return make_uint4(h2_as_u32(__hmul2(u32_as_h2(v.x), s)), h2_as_u32(__hmul2(u32_as_h2(v.y), s)),
+                      h2_as_u32(__hmul2(u32_as_h2(v.z), s)), h2_as_u32(__hmul2(u32_as_h2(v.w), s)));
+}
+__device__ __forceinline__ uint4 add_h2x4(const uint4 &a, const uint4 &b)
+{
+    return make_uint4(h2_as_u32(__hadd2(u32_as_h2(a.x), u32_as_h2(b.x))), h2_as_u32(__hadd2(u32_as_h2(a.y), u32_as_h2(b.y))),
+                      h2_as_u32(__hadd2(u32_as_h2(a.z), u32_as_h2(b.z))), h2_as_u32(__hadd2(u32_as_h2(a.w), u32_as_h2(b.w))));
+}
+__device__ __forceinline__ __half2 h2_from_bits(uint32_t bits16)
+{
+    const uint32_t b = bits16 & 0xFFFFu;
+    return u32_as_h2(b | (b << 16));
+}
+
+template <int FMT, int BN>
+__global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_constant__ CUtensorMap tmap, const DeqParams P)
+{
+    using L = SmemD<FMT, BN>;
+    using T = DeqTraits<FMT>;
+    constexpr uint32_t S = L::stages, R = L::raw_stages, NB = DeqCfg<BN>::bufs;
+    constexpr bool kAllDrain = (NB == 1);
+    constexpr uint32_t kDrainWarps = kAllDrain ? kExpWarps + kEpiWarps : kEpiWarps;
+    constexpr uint32_t kExpanders = 4; // arrivals per stage: lane 0 of each warp of one expander group
+    static_assert(L::stages % kExpGroups == 0 && L::raw_stages % kExpGroups == 0, "a stage always belongs to the same expander group");
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bars = sbase + L::bar_off;
+    auto op_full = [&](uint32_t s) { return bars + s * 8u; };
+    auto op_empty = [&](uint32_t s) { return bars + (S + s) * 8u; };
+    auto raw_full = [&](uint32_t s) { return bars + (2 * S + s) * 8u; };
+    auto raw_empty = [&](uint32_t s) { return bars + (2 * S + R + s) * 8u; };
+    auto tm_full = [&](uint32_t b) { return bars + (2 * S + 2 * R + b) * 8u; };
+    auto tm_empty = [&](uint32_t b) { return bars + (2 * S + 2 * R + NB + b) * 8u; };
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L::misc_off);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const bool trace = (P.debug & 128u) && blockIdx.x < 160u;
+    if (trace && threadIdx.x == 0) g_mmqd_trace[blockIdx.x * 8 + 0] = global_ns();
+    const uint32_t n_sub = P.in_dim >> 5;
+    const uint32_t n_extra = T::has_min ? (n_sub + 31u) / 32u : 0u; // K=32 steps over the sub-block minima
+    const uint32_t n_iters = n_sub + n_extra;
+    const uint32_t tiles_m = (P.out_dim + kBM - 1) / kBM;
+    const uint32_t tiles_n = (P.n_tok + BN - 1) / BN;
+    const uint32_t n_tiles = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < S; s++) {
+            mbar_init(op_full(s), kExpanders + 1); // expanders (A) + the producer's expect_tx (B)
+            mbar_init(op_empty(s), 1);             // the commit after the stage's MMAs
+        }
+        for (uint32_t s = 0; s < R; s++) {
+            mbar_init(raw_full(s), 1);
+            mbar_init(raw_empty(s), kExpanders);
+        }
+        for (uint32_t b = 0; b < NB; b++) {
+            mbar_init(tm_full(b), 1);
+            mbar_init(tm_empty(b), kDrainWarps);
+        }
+        *abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    if (trace && threadIdx.x == 0) g_mmqd_trace[blockIdx.x * 8 + 1] = global_ns();
+    pdl_launch_dependents();
+    pdl_wait(); // the activation image is the predecessor's output
+    if (trace && threadIdx.x == 0) g_mmqd_trace[blockIdx.x * 8 + 2] = global_ns();
+
+    // Tensor memory -> y for one finished tile: the warp's lane quarter, the 32-column chunks rank,
+    // rank + n_ranks, ...; one inverse token scale per column.  Arrives on tm_empty when done.
+    auto drain = [&](uint32_t id, uint32_t tile, uint32_t rank, uint32_t n_ranks) -> bool {
+        const uint32_t quarter = warp & 3u; // tensor-memory lanes this warp may read
+        const uint32_t m0 = (id % tiles_m) * kBM, tok0 = (id / tiles_m) * BN;
+        const uint32_t n_valid = min((uint32_t)BN, P.n_tok - tok0);
+        const uint32_t buf = tile % NB;
+        const uint32_t row = m0 + quarter * 32u + lane;
+        if (!mbar_wait_d(tm_full(buf), (tile / NB) & 1u, abort_flag, 7u)) return false;
+        tc_fence_after();
+        if (trace && warp == kLeadWarps + kExpWarps && lane == 0) g_mmqd_trace[blockIdx.x * 8 + 5] = global_ns();
+        float *yrow = P.y + (size_t)tok0 * P.out_dim + row;
+        for (uint32_t ch = rank; ch < BN / 32u; ch += n_ranks) {
+            const uint32_t col0 = ch * 32u;
+            if (col0 >= n_valid) break; // warp-uniform
+            uint32_t d[32];
+            tmem_ld32(tmem_base + ((quarter * 32u) << 16) + buf * BN + col0, d);
+            const float inv = (col0 + lane < n_valid) ? __ldg(P.inv_scale + tok0 + col0 + lane) : 0.0f; // lane c: column col0 + c
+            tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 32; c++) {
+                const float sc = __shfl_sync(0xFFFFFFFFu, inv, c);
+                if (row < P.out_dim && col0 + c < n_valid) yrow[(size_t)(col0 + c) * P.out_dim] = __uint_as_float(d[c]) * sc;
+            }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tm_empty(buf));
+        if (trace && warp == kLeadWarps + kExpWarps && lane == 0) g_mmqd_trace[blockIdx.x * 8 + 6] = global_ns();
+        return true;
+    };
+    // With a single accumulator buffer (BN = 512) the next tile cannot start before this one is
+    // drained, so the expander warps drain too: five warps per lane quarter.
+
+    if (warp == 0) {
+        // ---- activation producer: chunks 4i..4i+3 of the image per K step, by bulk copies -------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x) {
+                const uint32_t tok0 = (id / tiles_m) * BN;
+                const uint32_t n_rows_b = min((uint32_t)BN, P.tok_ld - tok0); // tokens present in the image
+                for (uint32_t i = 0; i < n_iters; i++, it++) {
+                    const uint32_t s = it % S;
+                    if (it >= S && !mbar_spin_d(op_empty(s), ((it / S) - 1u) & 1u, abort_flag, 2u)) goto prod_done;
+                    if (P.debug & 2u) {
+                        mbar_arrive(op_full(s));
+                        continue;
+                    }
+                    mbar_expect_tx(op_full(s), 4u * n_rows_b * 16u);
+                    // (the xsum chunks follow the main ones seamlessly)
+                    const uint8_t *src = P.xh + ((size_t)(4u * i) * P.tok_ld + tok0) * 16u;
+                    for (uint32_t c = 0; c < 4; c++)
+                        bulk_load(sbase + L::b_off + s * L::b_stage + c * BN * 16u, src + (size_t)c * P.tok_ld * 16u,
+                                  n_rows_b * 16u, op_full(s));
+                }
+            }
+        prod_done:;
+        }
+    } else if (warp == 2) {
+        // ---- raw weight producer: one 16-byte x 128-row box per plane and K step, by tiled TMA ---------
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x) {
+                const uint32_t m0 = (id % tiles_m) * kBM;
+                for (uint32_t i = 0; i < n_iters; i++, it++) {
+                    const uint32_t s = it % R;
+                    if (it >= R && !mbar_spin_d(raw_empty(s), ((it / R) - 1u) & 1u, abort_flag, 1u)) goto raw_done;
+                    if (i < n_sub && !(P.debug & 8u)) {
+                        mbar_expect_tx(raw_full(s), T::raw_bytes);
+                        for (int pl = 0; pl < T::raw_planes; pl++)
+                            tma_load_4d(sbase + L::raw_off + s * L::raw_stage + pl * kBM * 16, &tmap, raw_full(s),
+                                        (int)(i * 16u), (int)m0, pl, 0);
+                    } else {
+                        mbar_arrive(raw_full(s)); // nothing raw in a minima step; keeps the ring in phase
+                    }
+                }
+            }
+        raw_done:;
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer -------------------------------------------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t NI = BN > 256 ? 256 : BN; // columns per instruction
+            constexpr uint32_t idesc = make_idesc_f16(NI);
+            uint32_t it = 0, tile = 0;
+            for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x, tile++) {
+                const uint32_t buf = tile % NB;
+                if (tile >= NB && !mbar_spin_d(tm_empty(buf), ((tile / NB) - 1u) & 1u, abort_flag, 3u)) goto mma_done;
+                tc_fence_after();
+                for (uint32_t i = 0; i < n_iters; i++, it++) {
+                    const uint32_t s = it % S;
+                    if (!mbar_spin_d(op_full(s), (it / S) & 1u, abort_flag, 4u)) goto mma_done;
+                    tc_fence_after();
+                    if (trace && it == 0) g_mmqd_trace[blockIdx.x * 8 + 3] = global_ns();
+                    const uint32_t a0 = sbase + L::a_off + s * L::a_stage;
+                    const uint32_t b0 = sbase + L::b_off + s * L::b_stage;
+#pragma unroll
+                    for (int kh = 0; kh < 2; kh++) {
+                        const uint64_t da = make_desc(a0 + kh * 2 * kBM * 16, kBM * 16, 128);
+#pragma unroll
+                        for (uint32_t nh = 0; nh < BN / NI; nh++) {
+                            const uint64_t db = make_desc(b0 + kh * 2 * BN * 16 + nh * NI * 16, BN * 16, 128);
+                            if (!(P.debug & 4u)) mma_f16(tmem_base + buf * BN + nh * NI, da, db, idesc, (i | (uint32_t)kh) ? 1u : 0u);
+                        }
+                    }
+                    if (P.debug & 64u) mbar_arrive(op_empty(s)); else mma_commit(op_empty(s));
+                }
+                mma_commit(tm_full(buf));
+                if (trace) g_mmqd_trace[blockIdx.x * 8 + 4] = global_ns();
+            }
+        mma_done:;
+        }
+    } else if (warp < kLeadWarps + kExpWarps) {
+        // ---- expanders: kExpGroups groups of 128 threads take the K steps in turn; in a group thread r
+        // owns weight row m0 + r.  Side planes (scales, high bits) come from HBM: they are requested three
+        // of the group's steps early, into three fixed register slots used in turn.
+        constexpr uint32_t G = kExpGroups;
+        const uint32_t grp = (warp - kLeadWarps) >> 2, r = (threadIdx.x - kLeadWarps * 32u) & 127u;
+        const Planes pl = planes_of<FMT>(P.w, P.in_dim, P.out_dim);
+        struct Side { uint32_t e0, e1, smw, ddw; };
+        uint32_t tile_it0 = 0; // global step number of the tile's first step
+        for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x, tile_it0 += n_iters) {
+            const uint32_t row = min((id % tiles_m) * kBM + r, P.out_dim - 1u);
+            const uint8_t *scp = pl.sc + (size_t)row * pl.nsp * 2u;
+            const uint8_t *auxp = (FMT == Q5_K || FMT == Q6_K) ? pl.aux + (size_t)row * pl.nsp * (FMT == Q6_K ? 8u : 4u) : nullptr;
+            const uint8_t *supp = T::sup_scale ? pl.sup + (size_t)row * pl.n_super * (FMT == Q6_K ? 2u : 4u) : nullptr;
+            auto request = [&](Side &slot, uint32_t i) {
+                slot = Side{0u, 0u, 0u, 0u};
+                if (i < n_sub && !(P.debug & 32u)) {
+                    if constexpr (FMT == Q5_K) slot.e0 = ld_stream_u32(auxp + i * 4u);
+                    if constexpr (FMT == Q6_K) {
+                        const uint2 h = ld_stream_u2(auxp + i * 8u);
+                        slot.e0 = h.x;
+                        slot.e1 = h.y;
+                    }
+                    slot.smw = ld_nc_u16(scp + i * 2u);
+                    if constexpr (T::has_min) slot.ddw = ld_nc_u16(supp + (i >> 3) * 4u);
+                    if constexpr (FMT == Q6_K) slot.ddw = ld_nc_u16(supp + (i >> 3) * 2u);
+                }
+            };
+            auto step = [&](Side &slot, uint32_t i) -> bool {
+                const Side cur = slot;
+                request(slot, i + 3u * G);
+                const uint32_t it = tile_it0 + i, s = it % S, rs = it % R;
+                uint4 o[4];
+                if constexpr (T::has_min) {
+                    if (i >= n_sub) {
+                        // minima step: chunk c = superblock (i - n_sub) * 4 + c, one half per sub-block: -dmin * m
+                        const uint32_t sb0 = (i - n_sub) * 4u;
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {
+                            uint32_t h[4] = {0u, 0u, 0u, 0u};
+                            if (sb0 + c < pl.n_super) {
+                                const uint32_t dmin_bits = ld_nc_u16(supp + (sb0 + c) * 4u + 2u);
+                                const __half2 ndm = __hneg2(h2_from_bits(dmin_bits));
+#pragma unroll
+                                for (int u = 0; u < 4; u++) {
+                                    const uint32_t m_lo = ld_nc_u16(scp + ((sb0 + c) * 8u + 2 * u) * 2u) >> 8;
+                                    const uint32_t m_hi = ld_nc_u16(scp + ((sb0 + c) * 8u + 2 * u + 1) * 2u) >> 8;
+                                    const __half2 mm = __halves2half2(__ushort2half_rn((unsigned short)m_lo),
+                                                                      __ushort2half_rn((unsigned short)m_hi));
+                                    h[u] = h2_as_u32(__hmul2(mm, ndm));
+                                }
+                            }
+                            o[c] = make_uint4(h[0], h[1], h[2], h[3]);
+                        }
+                    }
+                }
+                if (!mbar_wait_d(raw_full(rs), (it / R) & 1u, abort_flag, 6u)) return false;
+                if (i < n_sub && !(P.debug & 1u)) {
+                    const uint32_t rp = sbase + L::raw_off + rs * L::raw_stage + r * 16u;
+                    const uint4 q = lds_u4(rp);
+                    uint4 q2 = make_uint4(0, 0, 0, 0);
+                    if constexpr (FMT == Q8_0) q2 = lds_u4(rp + kBM * 16);
+                    uint4 t[2][4];
+                    expand_f16<FMT>(q, q2, cur.e0, cur.e1, cur.smw, t); // exact integers: sc * q, q - 8, q, codebook value
+                    const __half2 sc = h2_from_bits(T::sup_scale ? cur.ddw : cur.smw);
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        uint4 v = t[0][c];
+                        if constexpr (FMT == Q6_K) v = add_h2x4(v, t[1][c]); // the two exact parts of (q - 32) * sc
+                        o[c] = mul_h2x4(v, sc);
+                    }
+                }
+                // the operand slot is needed only now: the expansion above ran while its MMAs finished
+                if (it >= S && !mbar_wait_d(op_empty(s), ((it / S) - 1u) & 1u, abort_flag, 5u)) return false;
+                const uint32_t ap = sbase + L::a_off + s * L::a_stage + r * 16u;
+#pragma unroll
+                for (int c = 0; c < 4; c++) sts_u4(ap + c * kBM * 16, o[c]);
+                if (!(P.debug & 16u)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp(); // one arrival per warp
+                if (lane == 0) {
+                    mbar_arrive(op_full(s));
+                    mbar_arrive(raw_empty(rs));
+                }
+                return true;
+            };
+            uint32_t i = (grp + G - (tile_it0 % G)) % G; // the group's first step in this tile
+            Side slot0, slot1, slot2;
+            request(slot0, i);
+            request(slot1, i + G);
+            request(slot2, i + 2u * G);
+            bool ok = true;
+            while (ok && i < n_iters) {
+                ok = step(slot0, i);
+                i += G;
+                if (ok && i < n_iters) {
+                    ok = step(slot1, i);
+                    i += G;
+                }
+                if (ok && i < n_iters) {
+                    ok = step(slot2, i);
+                    i += G;
+                }
+            }
+            if (!ok) break;
+            if constexpr (kAllDrain) {
+                if (!drain(id, tile_it0 / n_iters, grp, kExpGroups + 1u)) break;
+            }
+        }
+    } else {
+        // ---- epilogue warps ---------------------------------------------------------------------------------
+        uint32_t tile = 0;
+        for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x, tile++)
+            if (!drain(id, tile, kAllDrain ? (uint32_t)kExpGroups : 0u, kAllDrain ? kExpGroups + 1u : 1u)) break;
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+        if (trace && lane == 0) g_mmqd_trace[blockIdx.x * 8 + 7] = global_ns();
+    }
+}
+
+// ---- activations: f32 rows -> the f16 operand image ---------------------------------------------------
+//
+// One CTA per token row (rows n_tok..tok_ld-1 are written as zeros).  The BlockQ8 quantizer of
+// quantize_q8_kernel (kernels/quantize_q8.cpp:23-66: same butterfly, same IEEE divides, same
+// rounding), then a = f16((d * q) * s) with s the token's power-of-two scale, and f16(xsum * s).
+__global__ void __launch_bounds__(256) activations_to_f16_kernel(const float *__restrict__ x, uint8_t *__restrict__ out,
+                                                                  uint32_t in_dim, uint32_t n_tok, uint32_t tok_ld,
+                                                                  uint32_t n_xchunks)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t n_sub = in_dim >> 5, n_kc = in_dim >> 3;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t tok = blockIdx.x;
+    __half *img = reinterpret_cast<__half *>(out);
+    float *inv_scale = reinterpret_cast<float *>(out + (size_t)(n_kc + n_xchunks) * tok_ld * 16u);
+    auto at = [&](uint32_t chunk, uint32_t h) { return img + ((size_t)chunk * tok_ld + tok) * 8u + h; };
+    if (tok >= n_tok) {
+        for (uint32_t i = threadIdx.x; i < (n_kc + n_xchunks) * 8u; i += blockDim.x) *at(i >> 3, i & 7u) = __float2half(0.0f);
+        if (threadIdx.x == 0) inv_scale[tok] = 0.0f;
+        return;
+    }
+    x += (size_t)tok * in_dim;
+    __shared__ float s_max[8];
+    float amax = 0.0f;
+    {
+        // rows are 128-byte aligned relative to x (in_dim % 32 == 0); x itself is only known to be 4-byte aligned
+        const bool vec = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+        if (vec) {
+            const float4 *x4 = reinterpret_cast<const float4 *>(x);
+#pragma unroll 4
+            for (uint32_t i = threadIdx.x; i < in_dim / 4u; i += blockDim.x) {
+                const float4 v = __ldg(x4 + i);
+                amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+            }
+        } else {
+#pragma unroll 4
+            for (uint32_t i = threadIdx.x; i < in_dim; i += blockDim.x) amax = fmaxf(amax, fabsf(x[i]));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    if (lane == 0) s_max[warp] = amax;
+    __syncthreads();
+    amax = s_max[0];
+#pragma unroll
+    for (int w = 1; w < 8; w++) amax = fmaxf(amax, s_max[w]);
+    // s = 2^(8 - floor(log2 amax)): amax * s in [256, 512); a block sum is then below 2^14
+    const uint32_t ebits = (__float_as_uint(amax) >> 23) & 0xFFu;
+    const bool scaled = ebits >= 9u && ebits <= 254u;
+    const float s = scaled ? __uint_as_float((262u - ebits) << 23) : 1.0f;
+    if (threadIdx.x == 0) inv_scale[tok] = scaled ? __uint_as_float((ebits - 8u) << 23) : 1.0f;
+    // four sub-blocks per warp and turn: their loads and butterflies overlap
+    constexpr int U = 4;
+    // (each token starts at a different sub-block, so that the CTAs running together do not all write
+    // the same few chunks of the image at the same time)
+    const uint32_t rot = (tok * 29u) % n_sub;
+    for (uint32_t sbn = warp * U; sbn < n_sub; sbn += 8u * U) {
+        float v[U], bmax[U], sum[U];
+        uint32_t sbv[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            sbv[u] = sbn + u + rot;
+            if (sbv[u] >= n_sub) sbv[u] -= n_sub;
+            v[u] = (sbn + u < n_sub) ? x[(size_t)sbv[u] * 32 + lane] : 0.0f;
+            bmax[u] = fabsf(v[u]);
+            sum[u] = v[u];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                bmax[u] = fmaxf(bmax[u], __shfl_xor_sync(0xFFFFFFFFu, bmax[u], o));
+                sum[u] = __fadd_rn(sum[u], __shfl_xor_sync(0xFFFFFFFFu, sum[u], o));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const uint32_t sb = sbv[u];
+            const float d = bmax[u] > 0.0f ? __fdiv_rn(bmax[u], 127.0f) : 1.0f;
+            const float inv = bmax[u] > 0.0f ? __fdiv_rn(127.0f, bmax[u]) : 0.0f;
+            int q = __float2int_rn(__fmul_rn(v[u], inv));
+            q = max(-127, min(127, q));
+            const float a = __fmul_rn(__fmul_rn(d, (float)q), s);
+            // lanes 2j, 2j+1 -> one 32-bit store of two halves
+            const float a_hi = __shfl_down_sync(0xFFFFFFFFu, a, 1);
+            if (sbn + u < n_sub) {
+                if ((lane & 1u) == 0u)
+                    *reinterpret_cast<__half2 *>(at(sb * 4u + (lane >> 3), lane & 7u)) = __floats2half2_rn(a, a_hi);
+                if (lane == 0) *at(n_kc + (sb >> 3), sb & 7u) = __float2half_rn(__fmul_rn(sum[u], s));
+            }
+        }
+    }
+    // xsum slots past the last sub-block (the minima steps read whole groups of four chunks)
+    for (uint32_t i = n_sub + threadIdx.x; i < n_xchunks * 8u; i += blockDim.x) *at(n_kc + (i >> 3), i & 7u) = __float2half(0.0f);
+}
+
+uint32_t xchunks_of(uint32_t in_dim)
+{
+    const uint32_t n_sub = in_dim >> 5;
+    return (((n_sub + 7u) / 8u) + 3u) & ~3u;
+}
+uint32_t tok_ld_of(uint32_t n_tok) { return (n_tok + 7u) & ~7u; }
+
+template <int FMT, int BN>
+int launch_deq(cudaStream_t s, const DeqParams &P)
+{
+    CUtensorMap map;
+    int rc = make_tmap<FMT>(&map, P.w, 0, 1u, P.in_dim, P.out_dim);
+    if (rc) return rc;
+    const uint32_t tiles = ((P.out_dim + kBM - 1) / kBM) * ((P.n_tok + BN - 1) / BN);
+    const uint32_t grid = min(tiles, (uint32_t)sm_count());
+    return (int)launch_pdl(mmqd_kernel<FMT, BN>, dim3(grid), dim3(kDeqThreads), SmemD<FMT, BN>::total, s, map, P);
+}
+
+template <int FMT>
+int launch_deq_bn(cudaStream_t s, const DeqParams &P, uint32_t bn)
+{
+    if (bn == 512) return launch_deq<FMT, 512>(s, P);
+    if (bn == 256) return launch_deq<FMT, 256>(s, P);
+    return launch_deq<FMT, 128>(s, P);
+}
+
+template <int FMT> int set_attr_deq()
+{
+    int rc = (int)cudaFuncSetAttribute(mmqd_kernel<FMT, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemD<FMT, 512>::total);
+    rc |= (int)cudaFuncSetAttribute(mmqd_kernel<FMT, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemD<FMT, 256>::total);
+    rc |= (int)cudaFuncSetAttribute(mmqd_kernel<FMT, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemD<FMT, 128>::total);
+    return rc;
+}
+
+int g_deq_bn = 0; // 0: by shape
+int g_deq_debug = 0;
+
+} // namespace
+
+int mmq_deq_set_attributes()
+{
+    return set_attr_deq<Q4_0>() | set_attr_deq<Q8_0>() | set_attr_deq<Q4_K>() | set_attr_deq<Q5_K>() | set_attr_deq<Q6_K>() |
+           set_attr_deq<IQ4_XS>();
+}
+
+void mmq_deq_set_bn(int bn)
+{
+    g_deq_debug = bn >> 12;
+    bn &= 0xFFF;
+    g_deq_bn = (bn == 128 || bn == 256 || bn == 512) ? bn : 0;
+}
+
+int mmq_deq_read_trace(void *out, size_t bytes)
+{
+    return (int)cudaMemcpyFromSymbol(out, g_mmqd_trace, bytes < sizeof(g_mmqd_trace) ? bytes : sizeof(g_mmqd_trace));
+}
+
+int mmq_deq_device_error(unsigned int *out)
+{
+    return (int)cudaMemcpyFromSymbol(out, g_mmqd_error, sizeof(unsigned int));
+}
+
+size_t mmq_deq_scratch_bytes(uint32_t in_dim, uint32_t n_tok)
+{
+    const size_t ld = tok_ld_of(n_tok);
+    return ((size_t)(in_dim >> 3) + xchunks_of(in_dim)) * ld * 16u + ld * sizeof(float);
+}
+
+// x f32 [n_tok][in_dim] -> y f32 [n_tok][out_dim]; scratch 16-byte aligned, mmq_deq_scratch_bytes large.
+int launch_mmq_deq_f32(cudaStream_t s, int type, const void *w, const float *x, float *y, uint32_t in_dim, uint32_t out_dim,
+                       uint32_t n_tok, void *scratch)
+{
+    const uint32_t ld = tok_ld_of(n_tok), n_xc = xchunks_of(in_dim);
+    cudaError_t e = launch_pdl(activations_to_f16_kernel, dim3(ld), dim3(256), 0, s, x, (uint8_t *)scratch, in_dim, n_tok, ld, n_xc);
+    if (e != cudaSuccess) return (int)e;
+    DeqParams P;
+    P.w = (const uint8_t *)w;
+    P.xh = (const uint8_t *)scratch;
+    P.inv_scale = reinterpret_cast<const float *>((const uint8_t *)scratch + ((size_t)(in_dim >> 3) + n_xc) * ld * 16u);
+    P.y = y;
+    P.in_dim = in_dim;
+    P.out_dim = out_dim;
+    P.n_tok = n_tok;
+    P.tok_ld = ld;
+    P.debug = (uint32_t)g_deq_debug;
+    // The widest token tile the batch fills: a K step costs about the same at every width (it is
+    // bound by the latency of the operand ring, not by the MMA), so fewer, wider tiles win, and every
+    // weight is expanded once per tile column.
+    const uint32_t bn = g_deq_bn ? (uint32_t)g_deq_bn : n_tok > 256u ? 512u : n_tok > 128u ? 256u : 128u;
+    switch (type) {
+    case Q4_0: return launch_deq_bn<Q4_0>(s, P, bn);
+    case Q8_0: return launch_deq_bn<Q8_0>(s, P, bn);
+    case Q4_K: return launch_deq_bn<Q4_K>(s, P, bn);
+    case Q5_K: return launch_deq_bn<Q5_K>(s, P, bn);
+    case Q6_K: return launch_deq_bn<Q6_K>(s, P, bn);
+    case IQ4_XS: return launch_deq_bn<IQ4_XS>(s, P, bn);
+    }
+    return RC_ERR_BAD_TYPE;
+}
+
+} // namespace rc
