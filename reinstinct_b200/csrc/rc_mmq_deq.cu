@@ -123,7 +123,7 @@ struct DeqParams {
     const float *inv_scale; // per token
     float *y;
     uint32_t in_dim, out_dim, n_tok, tok_ld;
-    uint32_t debug; // measurement aid: pipeline parts to skip (results invalid): 1 expand, 2 activation copies, 4 MMAs, 8 raw loads
+    uint32_t debug; // measurement aid: pipeline parts to skip (results invalid): 1 expand, 2 activation copies, 4 MMAs, 8 raw loads; 128 records phase timestamps
 };
 
 constexpr int kExpGroups = 4;                // groups of four expander warps, one K step each in turn
@@ -294,28 +294,36 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
         if (lane == 0) {
             constexpr uint32_t NI = BN > 256 ? 256 : BN; // columns per instruction
             constexpr uint32_t idesc = make_idesc_f16(NI);
+            // Descriptors differ from stage 0's only in the start-address field (bits 0..13, in units of
+            // 16 bytes; shared memory never carries out of it): one add per MMA instead of rebuilding them,
+            // which keeps this thread's instruction stream shorter than the MMAs it feeds.
+            const uint64_t da0 = make_desc(sbase + L::a_off, kBM * 16, 128);
+            const uint64_t db0 = make_desc(sbase + L::b_off, BN * 16, 128);
+            const bool do_mma = !(P.debug & 4u);
             uint32_t it = 0, tile = 0;
             for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x, tile++) {
                 const uint32_t buf = tile % NB;
                 if (tile >= NB && !mbar_spin_d(tm_empty(buf), ((tile / NB) - 1u) & 1u, abort_flag, 3u)) goto mma_done;
                 tc_fence_after();
+                const uint32_t d0 = tmem_base + buf * BN;
                 for (uint32_t i = 0; i < n_iters; i++, it++) {
                     const uint32_t s = it % S;
-                    if (!mbar_spin_d(op_full(s), (it / S) & 1u, abort_flag, 4u)) goto mma_done;
+                    if (!mbar_test(op_full(s), (it / S) & 1u) && !mbar_spin_d(op_full(s), (it / S) & 1u, abort_flag, 4u)) goto mma_done;
                     tc_fence_after();
                     if (trace && it == 0) g_mmqd_trace[blockIdx.x * 8 + 3] = global_ns();
-                    const uint32_t a0 = sbase + L::a_off + s * L::a_stage;
-                    const uint32_t b0 = sbase + L::b_off + s * L::b_stage;
+                    const uint64_t da = da0 + (uint64_t)(s * (L::a_stage >> 4));
+                    const uint64_t db = db0 + (uint64_t)(s * (L::b_stage >> 4));
+                    if (do_mma) {
 #pragma unroll
-                    for (int kh = 0; kh < 2; kh++) {
-                        const uint64_t da = make_desc(a0 + kh * 2 * kBM * 16, kBM * 16, 128);
+                        for (uint32_t kh = 0; kh < 2; kh++) {
 #pragma unroll
-                        for (uint32_t nh = 0; nh < BN / NI; nh++) {
-                            const uint64_t db = make_desc(b0 + kh * 2 * BN * 16 + nh * NI * 16, BN * 16, 128);
-                            if (!(P.debug & 4u)) mma_f16(tmem_base + buf * BN + nh * NI, da, db, idesc, (i | (uint32_t)kh) ? 1u : 0u);
+                            for (uint32_t nh = 0; nh < BN / NI; nh++) {
+                                mma_f16(d0 + nh * NI, da + kh * ((2 * kBM * 16) >> 4), db + ((kh * 2 * BN * 16 + nh * NI * 16) >> 4), idesc,
+                                        (i | kh) ? 1u : 0u); // the tile's first K=16 step overwrites every column
+                            }
                         }
                     }
-                    if (P.debug & 64u) mbar_arrive(op_empty(s)); else mma_commit(op_empty(s));
+                    mma_commit(op_empty(s));
                 }
                 mma_commit(tm_full(buf));
                 if (trace) g_mmqd_trace[blockIdx.x * 8 + 4] = global_ns();
@@ -338,7 +346,7 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
             const uint8_t *supp = T::sup_scale ? pl.sup + (size_t)row * pl.n_super * (FMT == Q6_K ? 2u : 4u) : nullptr;
             auto request = [&](Side &slot, uint32_t i) {
                 slot = Side{0u, 0u, 0u, 0u};
-                if (i < n_sub && !(P.debug & 32u)) {
+                if (i < n_sub) {
                     if constexpr (FMT == Q5_K) slot.e0 = ld_stream_u32(auxp + i * 4u);
                     if constexpr (FMT == Q6_K) {
                         const uint2 h = ld_stream_u2(auxp + i * 8u);
@@ -399,7 +407,7 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
                 const uint32_t ap = sbase + L::a_off + s * L::a_stage + r * 16u;
 #pragma unroll
                 for (int c = 0; c < 4; c++) sts_u4(ap + c * kBM * 16, o[c]);
-                if (!(P.debug & 16u)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp(); // one arrival per warp
                 if (lane == 0) {
                     mbar_arrive(op_full(s));
@@ -449,99 +457,120 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
 
 // ---- activations: f32 rows -> the f16 operand image ---------------------------------------------------
 //
-// One CTA per token row (rows n_tok..tok_ld-1 are written as zeros).  The BlockQ8 quantizer of
-// quantize_q8_kernel (kernels/quantize_q8.cpp:23-66: same butterfly, same IEEE divides, same
-// rounding), then a = f16((d * q) * s) with s the token's power-of-two scale, and f16(xsum * s).
-__global__ void __launch_bounds__(256) activations_to_f16_kernel(const float *__restrict__ x, uint8_t *__restrict__ out,
-                                                                  uint32_t in_dim, uint32_t n_tok, uint32_t tok_ld,
-                                                                  uint32_t n_xchunks)
+// One CTA of 32 warps per 8 consecutive tokens (gridDim.y CTAs share the sub-blocks of those tokens).
+// Pass 1: the tokens' largest magnitudes (four warps per token), giving the power-of-two scales.
+// Pass 2: a warp takes one sub-block of all 8 tokens at a time: the BlockQ8 quantizer of
+// quantize_q8_kernel (kernels/quantize_q8.cpp:23-66: same sum butterfly, same IEEE divides, same
+// rounding), a = f16((d * q) * s) and f16(xsum * s); the 8 x 32 halves are transposed through shared
+// memory so that every store instruction writes one chunk of the 8 tokens: 128 contiguous bytes of
+// the image.  Tokens n_tok..tok_ld-1 are written as zeros.
+constexpr int kActTokens = 8, kActWarps = 32;
+
+__global__ void __launch_bounds__(kActWarps * 32) activations_to_f16_kernel(const float *__restrict__ x, uint8_t *__restrict__ out,
+                                                                             uint32_t in_dim, uint32_t n_tok, uint32_t tok_ld,
+                                                                             uint32_t n_xchunks)
 {
     pdl_launch_dependents();
     pdl_wait();
     const uint32_t n_sub = in_dim >> 5, n_kc = in_dim >> 3;
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
-    const uint32_t tok = blockIdx.x;
-    __half *img = reinterpret_cast<__half *>(out);
+    const uint32_t tok0 = blockIdx.x * kActTokens;
     float *inv_scale = reinterpret_cast<float *>(out + (size_t)(n_kc + n_xchunks) * tok_ld * 16u);
-    auto at = [&](uint32_t chunk, uint32_t h) { return img + ((size_t)chunk * tok_ld + tok) * 8u + h; };
-    if (tok >= n_tok) {
-        for (uint32_t i = threadIdx.x; i < (n_kc + n_xchunks) * 8u; i += blockDim.x) *at(i >> 3, i & 7u) = __float2half(0.0f);
-        if (threadIdx.x == 0) inv_scale[tok] = 0.0f;
-        return;
-    }
-    x += (size_t)tok * in_dim;
-    __shared__ float s_max[8];
-    float amax = 0.0f;
-    {
-        // rows are 128-byte aligned relative to x (in_dim % 32 == 0); x itself is only known to be 4-byte aligned
-        const bool vec = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
-        if (vec) {
-            const float4 *x4 = reinterpret_cast<const float4 *>(x);
+    __shared__ float s_part[kActTokens][4];
+    __shared__ float s_scale[kActTokens];
+    __shared__ __align__(16) __half s_tile[kActWarps][kActTokens][32];
+
+    {   // pass 1: warp -> (token, quarter of the row)
+        const uint32_t t = warp >> 2, qk = warp & 3u, tok = tok0 + t;
+        float amax = 0.0f;
+        if (tok < n_tok) {
+            const float *row = x + (size_t)tok * in_dim;
+            const uint32_t per = in_dim / 4u, lo = qk * per, hi = lo + per; // in_dim is a multiple of 32
+            if ((reinterpret_cast<uintptr_t>(row) & 15u) == 0) {
+                const float4 *r4 = reinterpret_cast<const float4 *>(row);
 #pragma unroll 4
-            for (uint32_t i = threadIdx.x; i < in_dim / 4u; i += blockDim.x) {
-                const float4 v = __ldg(x4 + i);
-                amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+                for (uint32_t i = lo / 4u + lane; i < hi / 4u; i += 32u) {
+                    const float4 v = __ldg(r4 + i);
+                    amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+                }
+            } else {
+#pragma unroll 4
+                for (uint32_t i = lo + lane; i < hi; i += 32u) amax = fmaxf(amax, fabsf(row[i]));
             }
-        } else {
-#pragma unroll 4
-            for (uint32_t i = threadIdx.x; i < in_dim; i += blockDim.x) amax = fmaxf(amax, fabsf(x[i]));
         }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+        if (lane == 0) s_part[t][qk] = amax;
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-    if (lane == 0) s_max[warp] = amax;
     __syncthreads();
-    amax = s_max[0];
+    if (threadIdx.x < kActTokens) {
+        const uint32_t t = threadIdx.x;
+        const float amax = fmaxf(fmaxf(s_part[t][0], s_part[t][1]), fmaxf(s_part[t][2], s_part[t][3]));
+        // s = 2^(8 - floor(log2 amax)): amax * s in [256, 512); a block sum is then below 2^14
+        const uint32_t ebits = (__float_as_uint(amax) >> 23) & 0xFFu;
+        const bool scaled = ebits >= 9u && ebits <= 254u;
+        s_scale[t] = scaled ? __uint_as_float((262u - ebits) << 23) : 1.0f;
+        if (blockIdx.y == 0 && tok0 + t < tok_ld)
+            inv_scale[tok0 + t] = tok0 + t >= n_tok ? 0.0f : scaled ? __uint_as_float((ebits - 8u) << 23) : 1.0f;
+    }
+    __syncthreads();
+
+    // pass 2: sub-blocks warp + 32 * (blockIdx.y + gridDim.y * k)
+    const uint32_t tl = lane >> 2, pair = lane & 3u; // store role: token tl, halves 2*pair, 2*pair + 1 of a chunk
+    const float s_mine = s_scale[lane & 7u];         // lane t < 8 also does token t's divides and xsum
+    for (uint32_t sb = warp + 32u * blockIdx.y; sb < n_sub; sb += 32u * gridDim.y) {
+        float v[kActTokens], sum[kActTokens];
+        uint32_t bmax[kActTokens]; // |v| as bits: non-negative floats order like unsigned integers
 #pragma unroll
-    for (int w = 1; w < 8; w++) amax = fmaxf(amax, s_max[w]);
-    // s = 2^(8 - floor(log2 amax)): amax * s in [256, 512); a block sum is then below 2^14
-    const uint32_t ebits = (__float_as_uint(amax) >> 23) & 0xFFu;
-    const bool scaled = ebits >= 9u && ebits <= 254u;
-    const float s = scaled ? __uint_as_float((262u - ebits) << 23) : 1.0f;
-    if (threadIdx.x == 0) inv_scale[tok] = scaled ? __uint_as_float((ebits - 8u) << 23) : 1.0f;
-    // four sub-blocks per warp and turn: their loads and butterflies overlap
-    constexpr int U = 4;
-    // (each token starts at a different sub-block, so that the CTAs running together do not all write
-    // the same few chunks of the image at the same time)
-    const uint32_t rot = (tok * 29u) % n_sub;
-    for (uint32_t sbn = warp * U; sbn < n_sub; sbn += 8u * U) {
-        float v[U], bmax[U], sum[U];
-        uint32_t sbv[U];
-#pragma unroll
-        for (int u = 0; u < U; u++) {
-            sbv[u] = sbn + u + rot;
-            if (sbv[u] >= n_sub) sbv[u] -= n_sub;
-            v[u] = (sbn + u < n_sub) ? x[(size_t)sbv[u] * 32 + lane] : 0.0f;
-            bmax[u] = fabsf(v[u]);
-            sum[u] = v[u];
+        for (int t = 0; t < kActTokens; t++) {
+            v[t] = (tok0 + t < n_tok) ? x[(size_t)(tok0 + t) * in_dim + (size_t)sb * 32u + lane] : 0.0f;
+            const float a = fabsf(v[t]);
+            bmax[t] = __reduce_max_sync(0xFFFFFFFFu, a == a ? __float_as_uint(a) : 0u); // fmaxf skips a NaN: so does this
+            sum[t] = v[t];
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
 #pragma unroll
-            for (int u = 0; u < U; u++) {
-                bmax[u] = fmaxf(bmax[u], __shfl_xor_sync(0xFFFFFFFFu, bmax[u], o));
-                sum[u] = __fadd_rn(sum[u], __shfl_xor_sync(0xFFFFFFFFu, sum[u], o));
-            }
+            for (int t = 0; t < kActTokens; t++) sum[t] = __fadd_rn(sum[t], __shfl_xor_sync(0xFFFFFFFFu, sum[t], o));
         }
+        // the two IEEE divides of a block, once per token: lane t does token t's
+        float my_max = 0.0f, my_sum = 0.0f;
 #pragma unroll
-        for (int u = 0; u < U; u++) {
-            const uint32_t sb = sbv[u];
-            const float d = bmax[u] > 0.0f ? __fdiv_rn(bmax[u], 127.0f) : 1.0f;
-            const float inv = bmax[u] > 0.0f ? __fdiv_rn(127.0f, bmax[u]) : 0.0f;
-            int q = __float2int_rn(__fmul_rn(v[u], inv));
-            q = max(-127, min(127, q));
-            const float a = __fmul_rn(__fmul_rn(d, (float)q), s);
-            // lanes 2j, 2j+1 -> one 32-bit store of two halves
-            const float a_hi = __shfl_down_sync(0xFFFFFFFFu, a, 1);
-            if (sbn + u < n_sub) {
-                if ((lane & 1u) == 0u)
-                    *reinterpret_cast<__half2 *>(at(sb * 4u + (lane >> 3), lane & 7u)) = __floats2half2_rn(a, a_hi);
-                if (lane == 0) *at(n_kc + (sb >> 3), sb & 7u) = __float2half_rn(__fmul_rn(sum[u], s));
+        for (int t = 0; t < kActTokens; t++) {
+            if ((int)(lane & 7u) == t) {
+                my_max = __uint_as_float(bmax[t]);
+                my_sum = sum[t];
             }
         }
+        const float my_d = my_max > 0.0f ? __fdiv_rn(my_max, 127.0f) : 1.0f;
+        const float my_inv = my_max > 0.0f ? __fdiv_rn(127.0f, my_max) : 0.0f;
+#pragma unroll
+        for (int t = 0; t < kActTokens; t++) {
+            const float d = __shfl_sync(0xFFFFFFFFu, my_d, t), inv = __shfl_sync(0xFFFFFFFFu, my_inv, t);
+            int q = __float2int_rn(__fmul_rn(v[t], inv));
+            q = max(-127, min(127, q));
+            s_tile[warp][t][lane] = __float2half_rn(__fmul_rn(__fmul_rn(d, (float)q), s_scale[t]));
+        }
+        __syncwarp();
+        if (tok0 + tl < tok_ld) {
+#pragma unroll
+            for (uint32_t c = 0; c < 4; c++) {
+                const uint32_t h2 = *reinterpret_cast<const uint32_t *>(&s_tile[warp][tl][8u * c + 2u * pair]);
+                *reinterpret_cast<uint32_t *>(out + ((size_t)(sb * 4u + c) * tok_ld + tok0 + tl) * 16u + pair * 4u) = h2;
+            }
+        }
+        if (lane < kActTokens && tok0 + lane < tok_ld)
+            *reinterpret_cast<__half *>(out + ((size_t)(n_kc + (sb >> 3)) * tok_ld + tok0 + lane) * 16u + (sb & 7u) * 2u) =
+                __float2half_rn(__fmul_rn(my_sum, s_mine));
+        __syncwarp();
     }
     // xsum slots past the last sub-block (the minima steps read whole groups of four chunks)
-    for (uint32_t i = n_sub + threadIdx.x; i < n_xchunks * 8u; i += blockDim.x) *at(n_kc + (i >> 3), i & 7u) = __float2half(0.0f);
+    if (blockIdx.y == 0)
+        for (uint32_t i = n_sub * kActTokens + threadIdx.x; i < n_xchunks * 8u * kActTokens; i += blockDim.x) {
+            const uint32_t slot = i / kActTokens, t = i % kActTokens;
+            if (tok0 + t < tok_ld)
+                *reinterpret_cast<__half *>(out + ((size_t)(n_kc + (slot >> 3)) * tok_ld + tok0 + t) * 16u + (slot & 7u) * 2u) = __float2half(0.0f);
+        }
 }
 
 uint32_t xchunks_of(uint32_t in_dim)
@@ -617,7 +646,10 @@ int launch_mmq_deq_f32(cudaStream_t s, int type, const void *w, const float *x, 
                        uint32_t n_tok, void *scratch)
 {
     const uint32_t ld = tok_ld_of(n_tok), n_xc = xchunks_of(in_dim);
-    cudaError_t e = launch_pdl(activations_to_f16_kernel, dim3(ld), dim3(256), 0, s, x, (uint8_t *)scratch, in_dim, n_tok, ld, n_xc);
+    // 8 tokens per CTA; a second CTA shares their sub-blocks while that still adds SMs
+    const uint32_t groups = ld / kActTokens, ysplit = groups * 2u <= (uint32_t)sm_count() ? 2u : 1u;
+    cudaError_t e = launch_pdl(activations_to_f16_kernel, dim3(groups, ysplit), dim3(kActWarps * 32), 0, s, x, (uint8_t *)scratch, in_dim,
+                               n_tok, ld, n_xc);
     if (e != cudaSuccess) return (int)e;
     DeqParams P;
     P.w = (const uint8_t *)w;
