@@ -149,15 +149,25 @@ int rc_matvec_block_dots(void *stream, int ggml_type, const void *w, const void 
  * (src/runtime/gemma4.rs:1530-1551). */
 void rc_tune_matvec(int ks, int grid_mult, int no_pdl);
 /* Measurement aid: force_dp4a != 0 sends the MMQ entry points through the dp4a kernel instead of
- * the tensor-core kernels; the low byte of kind forces the int8-operand (8) or f16-operand (16)
- * tcgen05 kernel, 0 restores the per-format choice; the upper bits are a mask of pipeline parts
- * the f16 kernel skips (its results are then invalid) — for A/B timing and cross-checking. */
+ * the tensor-core kernels.  The low byte of kind picks the kernel: 0 the default (rc_matmul: the
+ * f16-operand GEMM with whole-K accumulation; rc_mmq_gemm and the grouped GEMM: int8 operands,
+ * Q6_K on the exact-integer f16 kernel), 8 the int8-operand kernel and 16 the exact-integer
+ * f16-operand kernel everywhere (rc_matmul then quantizes to BlockQ8 / its planar form), 32 the
+ * default again with (kind >> 8) & 0xFFF forcing its token-tile width (128, 256, 512) and
+ * kind >> 20 a mask of pipeline parts it skips or traces (results then invalid).  With kind 16 the
+ * upper bits are the skip mask of that kernel.  For A/B timing and cross-checking only. */
 void rc_tune_mmq(int force_dp4a, int kind);
-/* Reads (synchronously) the device-side status word: 0, or the code of the bounded wait that
- * gave up inside the tensor-core GEMM.  A nonzero value means the affected outputs are invalid;
- * the context stays usable.  hipDeviceSynchronize + error check in the reference's tests
+/* Reads (synchronously) the device-side status word: 0, or the codes of the bounded waits that
+ * gave up: bits 0-7 the int8 GEMM, 8-15 the exact-integer f16 GEMM, 16-23 the peer gather, 24-31
+ * the f16-operand dense GEMM.  A nonzero value means the affected outputs are invalid; the
+ * context stays usable.  hipDeviceSynchronize + error check in the reference's tests
  * (src/runtime/kernels.rs) is the nearest counterpart. */
 int rc_device_status(unsigned int *status);
+/* Measurement aid: copies out (synchronously) the phase timestamps the f16-operand GEMM records
+ * per CTA when bit 7 of its rc_tune_mmq mask is set: 160 x 8 uint64 (globaltimer ns: start,
+ * set-up done, predecessor done, first stage full, last commit, accumulator full, drain done,
+ * tensor memory freed).  No counterpart in the reference. */
+int rc_debug_read_trace(void *out, size_t bytes);
 
 /* ---- int8 MMQ GEMM --------------------------------------------------------------------- */
 
@@ -167,9 +177,14 @@ int rc_device_status(unsigned int *status);
 int rc_mmq_gemm(void *stream, int ggml_type, const void *w, const void *xq, float *y,
                 uint32_t in_dim, uint32_t out_dim, uint32_t p_rows);
 
-/* PrefillGemm::matmul_into_raw (src/runtime/prefill.rs:343-437): quantize X into the
- * caller's scratch (n_rows*(in_dim/32)*40 bytes), then the batched matvec for
- * n_rows <= RC_MATVEC_MAX_ROWS, else the MMQ GEMM.  x f32 [n_rows][in_dim]. */
+/* PrefillGemm::matmul_into_raw (src/runtime/prefill.rs:343-437).  x f32 [n_rows][in_dim].
+ * n_rows <= RC_MATVEC_MAX_ROWS: quantize X to BlockQ8 in the caller's scratch, then the batched
+ * matvec (integer block dots exact).  More rows: the same quantizer, its values written
+ * dequantized as an f16 operand image into the scratch, then the tensor-core GEMM with f16
+ * operands and whole-K f32 accumulation: within 1e-3 relative L2 of the exact-integer
+ * formulation (about 3e-4), not bit-identical to it; rc_quantize_q8 + rc_mmq_gemm is the
+ * exact-integer route.  xq_scratch: 16-byte aligned, rc_matmul_scratch_bytes large (with a
+ * smaller or misaligned scratch that still holds the BlockQ8 records the exact route runs). */
 int rc_matmul(void *stream, int ggml_type, const void *w, const float *x, float *y,
               uint32_t in_dim, uint32_t out_dim, uint32_t n_rows, void *xq_scratch,
               size_t scratch_bytes);
