@@ -360,11 +360,13 @@ def run_gpu_arm(args):
     else:
         hq_in = hq
 
-    def step(c: int):
+    def step(c: int, after_gate_up=None):
         ws = copies[c % n_copies]
         rt.launch_quantize_q8(x_dev, xq, HIDDEN, 1)
         rt.launch_matvec_xq8(ws[0], xq, y_gate)
         rt.launch_matvec_xq8(ws[1], xq, y_up)
+        if after_gate_up is not None:
+            after_gate_up()
         if world > 1:
             rt.launch_quantize_q8(h_dev[:, rank * h_local:(rank + 1) * h_local], hq_local, h_local, 1)
             if push:
@@ -389,14 +391,30 @@ def run_gpu_arm(args):
         torch.cuda.synchronize()
         assert torch.equal(got, hq), "peer gather of the quantized intermediate differs from the local quantization"
 
+    # End-to-end step: x is uploaded first; the upload of h (down's input) and the download of the
+    # gate / up outputs run on a second stream beside the kernels that do not need them, and join
+    # before the step ends.  Every byte still crosses PCIe inside the step.
+    side = torch.cuda.Stream(device=dev)
+
     def step_e2e(c: int):
-        in_dev.copy_(in_host, non_blocking=True)
-        step(c)
-        ygu_host.copy_(y_gu, non_blocking=True)
+        main = torch.cuda.current_stream()
+        side.wait_stream(main)                       # the previous step has read h and y_gu
+        x_dev.copy_(in_host[:, :HIDDEN], non_blocking=True)
+        with torch.cuda.stream(side):
+            h_dev.copy_(in_host[:, HIDDEN:], non_blocking=True)
+
+        def after_gate_up():
+            main.wait_stream(side)                   # h has arrived
+            side.wait_stream(main)                   # gate and up are done
+            with torch.cuda.stream(side):
+                ygu_host.copy_(y_gu, non_blocking=True)
+
+        step(c, after_gate_up)
         if push:
             ga_y.copy_out(yd_host)
         else:
             yd_host.copy_(g_down, non_blocking=True)
+        main.wait_stream(side)
 
     def barrier():
         if world > 1:
