@@ -224,6 +224,19 @@ int rc_mmq_gemm_grouped(void *stream, int ggml_type, const void *slab,
                         const int32_t *tile_off, uint32_t n_expert, const void *xq, float *y,
                         uint32_t in_dim, uint32_t out_dim, uint32_t n_entries);
 
+/* launch_moe_expert_matvec and launch_moe_down (src/runtime/qwen35.rs:3066-3139); kernels
+ * moe_matvec_{q4k,q5k,q6k,q8_0}_repacked_f32 and moe_matvec_{q5k,q6k}_down_f32: the decode-side
+ * routed-expert matvec.  For token t and routing slot j:
+ *   y[t][j][:] = W[ids[t][j]] . xq[t * xq_tok_stride + j * xq_slot_stride]
+ * with W[e] = slab + e * bytes_per_expert and the strides in BlockQ8 blocks, as the reference passes
+ * them (gate and up share the token's row: tok stride in_dim/32, slot stride 0; down has one row per
+ * slot: tok stride n_used * in_dim/32, slot stride in_dim/32).  ids int32 [n_tok][n_used] on the device; an id outside [0, n_expert) yields zeros.
+ * All six types; one geometry for both reference wrappers (rows are split across warps by shape). */
+int rc_moe_expert_matvec(void *stream, int ggml_type, const void *slab, size_t bytes_per_expert,
+                         const int32_t *ids, uint32_t n_expert, const void *xq, float *y, uint32_t in_dim,
+                         uint32_t out_dim, uint32_t n_used, uint32_t n_tok, uint32_t xq_tok_stride,
+                         uint32_t xq_slot_stride);
+
 /* ---- MoE glue around the grouped GEMMs ------------------------------------------------------- */
 
 /* launch_moe_topk (src/runtime/gemma4.rs:1649-1670); kernel moe_topk_f32 (kernels/moe_topk.cpp:17-107):

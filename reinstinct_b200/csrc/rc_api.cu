@@ -323,6 +323,22 @@ int rc_mmq_gemm_grouped(void *stream, int type, const void *slab, size_t bytes_p
                               n_expert, xq, y, in_dim, out_dim, n_entries);
 }
 
+int rc_moe_expert_matvec(void *stream, int type, const void *slab, size_t bytes_per_expert, const int32_t *ids,
+                         uint32_t n_expert, const void *xq, float *y, uint32_t in_dim, uint32_t out_dim, uint32_t n_used,
+                         uint32_t n_tok, uint32_t xq_tok_stride, uint32_t xq_slot_stride)
+{
+    if (n_tok == 0 || n_used == 0) return RC_OK;
+    int rc = check_weight_args(type, slab, xq, y, in_dim, out_dim);
+    if (rc) return rc;
+    if (!ids) return RC_ERR_NULL_POINTER;
+    if (n_expert == 0 || n_used > 65535u) return RC_ERR_BAD_ARGUMENT;
+    if (n_expert > 1 && (bytes_per_expert & 15u)) return RC_ERR_MISALIGNED;
+    rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_moe_expert_matvec(S(stream), type, slab, bytes_per_expert, ids, n_expert, xq, y, in_dim, out_dim, n_used,
+                                    n_tok, xq_tok_stride, xq_slot_stride);
+}
+
 /* ---- MoE glue ------------------------------------------------------------------------------------ */
 
 int rc_moe_topk(void *stream, const float *logits, uint32_t n_tok, uint32_t n_expert, uint32_t n_used,

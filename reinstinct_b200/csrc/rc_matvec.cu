@@ -624,6 +624,32 @@ matvec_grouped_kernel(const uint8_t *__restrict__ slab, size_t bytes_per_expert,
                                 nullptr, in_dim, out_dim, n, 1, blockIdx.x, gridDim.x);
 }
 
+// Routed-expert matvec of the decode path (kernels/moe_matvec_q4k_repacked.cpp and siblings, launched by
+// src/runtime/qwen35.rs:3066-3103 and, for the down projection, :3105-3139): blockIdx.y is the routing slot,
+// blockIdx.z the token; the slot's expert comes from ids on the device, its weights are
+// slab + ids * bytes_per_expert, its activation block row tok * xq_tok_stride + slot * xq_slot_stride
+// (in BlockQ8 blocks: gate / up share one row per token, down has one per slot).  An id outside the slab
+// writes zeros.
+template <int FMT>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, MinBlocks<1>::v)
+moe_expert_matvec_kernel(const uint8_t *__restrict__ slab, size_t bytes_per_expert, const int32_t *__restrict__ ids,
+                         uint32_t n_expert, const uint8_t *__restrict__ xq, float *__restrict__ y, uint32_t in_dim,
+                         uint32_t out_dim, uint32_t n_used, uint32_t xq_tok_stride, uint32_t xq_slot_stride, uint32_t ks)
+{
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t slot = blockIdx.y, tok = blockIdx.z;
+    float *yo = y + ((size_t)tok * n_used + slot) * out_dim;
+    pdl_wait(); // ids are a predecessor's output
+    const int32_t e = ids[(size_t)tok * n_used + slot];
+    if (e < 0 || (uint32_t)e >= n_expert) {
+        for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < out_dim; i += gridDim.x * blockDim.x) yo[i] = 0.0f;
+        return;
+    }
+    stream_body<FMT, 1, false>(smem, slab + (size_t)e * bytes_per_expert,
+                               xq + ((size_t)tok * xq_tok_stride + (size_t)slot * xq_slot_stride) * RC_BLOCKQ8_BYTES, yo,
+                               nullptr, in_dim, out_dim, 1, ks, blockIdx.x, gridDim.x);
+}
+
 struct Tuning {
     int ks = 0;          // 0 = heuristic
     int grid_mult = 0;   // CTAs launched per resident CTA slot; 0 = heuristic
@@ -793,7 +819,55 @@ int launch_grouped_fmt(cudaStream_t s, const void *slab, size_t bpe, const int32
     return (int)cudaGetLastError();
 }
 
+template <int FMT>
+int launch_expert_fmt(cudaStream_t s, const void *slab, size_t bpe, const int32_t *ids, uint32_t n_expert, const void *xq,
+                      float *y, uint32_t in_dim, uint32_t out_dim, uint32_t n_used, uint32_t n_tok, uint32_t tok_stride,
+                      uint32_t slot_stride)
+{
+    const uint32_t n_sub = in_dim >> 5, n_iters = (n_sub + 31u) >> 5;
+    const size_t smem = stream_smem_bytes<FMT>(1, n_sub, 1);
+    if (smem > kMaxStageBytesHost) return RC_ERR_BAD_SHAPE;
+    // all slots of all tokens run at once: split rows across warps only while they leave warp slots idle
+    const uint32_t slots = (uint32_t)sm_count() * (uint32_t)MinBlocks<1>::v * kWarpsPerCta;
+    const uint64_t rows_total = (uint64_t)out_dim * n_used * n_tok;
+    uint32_t ks = 1;
+    while (ks < (uint32_t)kWarpsPerCta && ks * 2u <= n_iters && rows_total * ks * 4u < 3ull * slots) ks *= 2u;
+    const uint32_t rb_rows = kWarpsPerCta / ks;
+    const uint32_t gx = (out_dim + rb_rows - 1u) / rb_rows;
+    for (uint32_t t0 = 0; t0 < n_tok; t0 += 65535u) {
+        const uint32_t nt = min(65535u, n_tok - t0);
+        cudaError_t e = launch_pdl(moe_expert_matvec_kernel<FMT>, dim3(gx, n_used, nt), dim3(kWarpsPerCta * 32), smem, s,
+                                   (const uint8_t *)slab, bpe, ids + (size_t)t0 * n_used, n_expert,
+                                   (const uint8_t *)xq + (size_t)t0 * tok_stride * RC_BLOCKQ8_BYTES,
+                                   y + (size_t)t0 * n_used * out_dim, in_dim, out_dim, n_used, tok_stride, slot_stride, ks);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return RC_OK;
+}
+
+template <int FMT> int set_attr_expert()
+{
+    return (int)cudaFuncSetAttribute(moe_expert_matvec_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
+}
+
 } // namespace
+
+int launch_moe_expert_matvec(cudaStream_t s, int type, const void *slab, size_t bpe, const int32_t *ids, uint32_t n_expert,
+                             const void *xq, float *y, uint32_t in_dim, uint32_t out_dim, uint32_t n_used, uint32_t n_tok,
+                             uint32_t tok_stride, uint32_t slot_stride)
+{
+#define RC_E(F) return launch_expert_fmt<F>(s, slab, bpe, ids, n_expert, xq, y, in_dim, out_dim, n_used, n_tok, tok_stride, slot_stride)
+    switch (type) {
+    case Q4_0: RC_E(Q4_0);
+    case Q8_0: RC_E(Q8_0);
+    case Q4_K: RC_E(Q4_K);
+    case Q5_K: RC_E(Q5_K);
+    case Q6_K: RC_E(Q6_K);
+    case IQ4_XS: RC_E(IQ4_XS);
+    }
+#undef RC_E
+    return RC_ERR_BAD_TYPE;
+}
 
 int matvec_set_attributes()
 {
@@ -804,6 +878,8 @@ int matvec_set_attributes()
     rc |= set_attr_fmt<Q5_K>();
     rc |= set_attr_fmt<Q6_K>();
     rc |= set_attr_fmt<IQ4_XS>();
+    rc |= set_attr_expert<Q4_0>() | set_attr_expert<Q8_0>() | set_attr_expert<Q4_K>() | set_attr_expert<Q5_K>() |
+          set_attr_expert<Q6_K>() | set_attr_expert<IQ4_XS>();
     return rc;
 }
 

@@ -22,7 +22,7 @@ __all__ = [
     "launch_quantize_q8", "launch_matvec", "launch_matvec_xq8", "launch_matvec_batched",
     "matvec_block_dots", "launch_mmq_gemm", "launch_moe_sort", "launch_moe_gather_xq",
     "launch_moe_grouped_gemm", "launch_moe_scatter_rows", "repacked_len", "init", "PeerAllGather",
-    "launch_moe_topk", "launch_moe_act_q8", "launch_moe_combine", "ACT_GEGLU", "ACT_SWIGLU",
+    "launch_moe_expert_matvec", "launch_moe_topk", "launch_moe_act_q8", "launch_moe_combine", "ACT_GEGLU", "ACT_SWIGLU",
 ]
 
 
@@ -255,6 +255,16 @@ def launch_moe_grouped_gemm(moe: MoeGroupedScratch, et: GpuExpertTensor, xq: tor
                                           _ptr(moe.expert_off), _ptr(moe.tile_off), moe.n_expert,
                                           _ptr(xq), _ptr(y), in_dim, out_dim, n_entries),
           "rc_mmq_gemm_grouped")
+
+
+def launch_moe_expert_matvec(et: GpuExpertTensor, ids: torch.Tensor, xq8: torch.Tensor, y: torch.Tensor, n_used: int,
+                             n_tok: int, xq_tok_stride: int, xq_slot_stride: int) -> None:
+    """launch_moe_expert_matvec / launch_moe_down (src/runtime/qwen35.rs:3066-3139): decode-side
+    routed-expert matvec, y [n_tok, n_used, out_dim]."""
+    assert ids.dtype == torch.int32
+    check(_lib.load().rc_moe_expert_matvec(_stream(), et.dtype, _ptr(et.data), et.bytes_per_expert, _ptr(ids), et.n_expert,
+                                           _ptr(xq8), _ptr(y), et.in_dim, et.out_dim, n_used, n_tok, xq_tok_stride,
+                                           xq_slot_stride), "rc_moe_expert_matvec")
 
 
 ACT_GEGLU, ACT_SWIGLU = 0, 1

@@ -59,4 +59,9 @@ def test_bad_shapes_and_types_are_rejected_before_any_launch():
     assert lib.rc_moe_act_q8(None, None, None, 64, 0, 0) == 0
     assert lib.rc_moe_combine(None, 4, 4, 4, None, 4, 16, 0, 1) == -8
     assert lib.rc_moe_combine(None, None, 4, 4, None, 4, 16, 2, 1) == -3
+    assert lib.rc_moe_expert_matvec(None, 99, 16, 64, 4, 2, 8, 4, 256, 8, 2, 1, 1, 0) == -1
+    assert lib.rc_moe_expert_matvec(None, _lib.Q4_K, 16, 64, None, 2, 8, 4, 256, 8, 2, 1, 1, 0) == -3
+    assert lib.rc_moe_expert_matvec(None, _lib.Q4_K, 16, 60, 4, 2, 8, 4, 256, 8, 2, 1, 1, 0) == -4
+    assert lib.rc_moe_expert_matvec(None, _lib.Q4_K, 16, 64, 4, 0, 8, 4, 256, 8, 2, 1, 1, 0) == -8
+    assert lib.rc_moe_expert_matvec(None, _lib.Q4_K, None, 64, None, 2, None, None, 256, 8, 2, 0, 1, 0) == 0
     assert lib.rc_matmul_scratch_bytes(5120, 4) == 4 * 160 * 40
