@@ -136,9 +136,38 @@ def moe_layer(rt, synth, torch, dev, timed):
     us_dn = timed(lambda i: rt.launch_moe_grouped_gemm(moe, dn, hq, y2, F, H, NE), reps, 3) / reps * 1e3
     wbytes = gu.data.numel() + dn.data.numel()
     peak, _ = measured_peaks()
+
+    # decode side of the same layer: one token, its 8 routed experts through the expert-indexed matvec
+    # (gate+up then down).  Each call takes the next 8 experts of the slab, so every weight byte comes
+    # from HBM (549 MB of experts > 4x L2).
+    ids_dec = torch.arange(E, dtype=torch.int32, device=dev).reshape(E // K, K)
+    xq1 = torch.empty((H // 32) * 40, **u8)
+    hq1 = torch.empty(K * (F // 32) * 40, **u8)
+    g1, d1 = torch.empty(1, K, 2 * F, device=dev), torch.empty(1, K, H, device=dev)
+    rt.launch_quantize_q8(x[:1], xq1, H, 1)
+
+    def decode_step(i):
+        sel = ids_dec[i % (E // K)]
+        rt.launch_moe_expert_matvec(gu, sel, xq1, g1, K, 1, H // 32, 0)
+        rt.launch_moe_act_q8(g1, hq1, F, K, rt.ACT_SWIGLU)
+        rt.launch_moe_expert_matvec(dn, sel, hq1, d1, K, 1, K * (F // 32), F // 32)
+
+    # replayed from a CUDA graph of one pass over all 32 expert groups, as a decode loop would be
+    for i in range(3):
+        decode_step(i)
+    torch.cuda.synchronize()
+    g_dec = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g_dec):
+        for i in range(E // K):
+            decode_step(i)
+    us_dec = timed(lambda i: g_dec.replay(), 4, 2) / (4 * (E // K)) * 1e3
+    dec_bytes = (gu.bytes_per_expert + dn.bytes_per_expert) * K
     return {"workload": "config 5: 256 experts top-8, 512 tokens, hidden 2048, ffn 512 (548.9 MB of expert weights, 25.8 GOP)",
             "us_layer": us, "tok_per_s_per_layer": NT / (us * 1e-6), "tops": 2.0 * NE * (H * 2 * F + F * H) / us / 1e6,
             "us_gate_up": us_gu, "us_down": us_dn,
+            "decode_1_token": {"us": us_dec, "expert_bytes": dec_bytes, "gbs": dec_bytes / us_dec / 1e3,
+                               "frac_of_hbm_peak": dec_bytes / us_dec / 1e3 / peak,
+                               "launches": "expert matvec (gate+up), SwiGLU+quantize, expert matvec (down)"},
             "roofline": {"bound": "hbm", "achieved": wbytes / us / 1e3, "peak": peak, "unit": "GB/s",
                          "frac": wbytes / us / 1e3 / peak, "note": "expert-weight bytes over the whole layer time"}}
 
