@@ -796,3 +796,138 @@ void ro_moe_combine(const float *experts, const int32_t *ids, const float *weigh
             out[t * hidden + i] = acc;
         }
 }
+
+/* ------------------------------------------- relabelled source formats --- */
+/* Tensor types the loaders accept by mapping them exactly onto a layout that has kernels
+ * (src/runtime/qwen35.rs:274-307): Q3_K -> Q6_K blocks, IQ4_NL -> the repacked IQ4_XS planes,
+ * BF16 -> Q8_0 blocks (the only lossy one: a requantization). */
+
+/* The sixteen 6-bit sub-block scales of a Q3_K block (src/quant/q3_k.rs:43-65): scale i has its
+ * low nibble in byte (i & 7) of the first eight (low half for i < 8, high half for i >= 8) and
+ * its two high bits in field (i >> 2) of byte 8 + (i & 3). */
+static int q3k_scale(const uint8_t *sc, int i)
+{
+    int j = i & 3, grp = i >> 2;
+    int low = grp < 2 ? (sc[grp * 4 + j] & 15) : ((sc[(grp - 2) * 4 + j] >> 4) & 15);
+    int high = (sc[8 + j] >> (2 * grp)) & 3;
+    return low | (high << 4);
+}
+
+/* Stored 3-bit quant (0..7) of weight y of a block (src/quant/q3_k.rs:67-90): weight
+ * y = 128*c + 32*j + l has its low two bits in field j of qs[32*c + l] and its third bit in bit
+ * 4*c + j of hmask[l]. */
+static int q3k_quant(const uint8_t *b, int y)
+{
+    int c = y >> 7, j = (y >> 5) & 3, l = y & 31;
+    int lo = (b[32 + 32 * c + l] >> (2 * j)) & 3;
+    int hi = (b[l] >> (4 * c + j)) & 1;
+    return lo | (hi << 2);
+}
+
+/* src/quant/q3_k.rs:123-162: w = (d * (sc - 32)) * (q3 - 4), sub-blocks of 16 weights. */
+void ro_dequantize_q3_k(const uint8_t *blocks, float *out, size_t n_weights)
+{
+    for (size_t blk = 0; blk < n_weights / 256; blk++) {
+        const uint8_t *b = blocks + blk * 110;
+        float d = ro_f16_to_f32(rd16(b + 108));
+        for (int y = 0; y < 256; y++) {
+            float dl = d * (float)(q3k_scale(b + 96, y >> 4) - 32);
+            out[blk * 256 + y] = dl * (float)(q3k_quant(b, y) - 4);
+        }
+    }
+}
+
+/* src/quant/q3_k.rs:92-121: q6 = q3 + 28, sc6 = sc3 - 32, same d; packed the way the Q6_K decoder
+ * reads ql / qh (src/quant/q6_k.rs). */
+void ro_q3k_to_q6k(const uint8_t *blocks, uint8_t *out, size_t n_weights)
+{
+    for (size_t blk = 0; blk < n_weights / 256; blk++) {
+        const uint8_t *b = blocks + blk * 110;
+        uint8_t *o = out + blk * 210;
+        memset(o, 0, 210);
+        for (int c = 0; c < 2; c++)
+            for (int l = 0; l < 32; l++) {
+                int q1 = q3k_quant(b, 128 * c + l) + 28, q2 = q3k_quant(b, 128 * c + 32 + l) + 28;
+                int q3 = q3k_quant(b, 128 * c + 64 + l) + 28, q4 = q3k_quant(b, 128 * c + 96 + l) + 28;
+                o[64 * c + l] = (uint8_t)((q1 & 15) | ((q3 & 15) << 4));
+                o[64 * c + 32 + l] = (uint8_t)((q2 & 15) | ((q4 & 15) << 4));
+                o[128 + 32 * c + l] = (uint8_t)((q1 >> 4) | ((q2 >> 4) << 2) | ((q3 >> 4) << 4) | ((q4 >> 4) << 6));
+            }
+        for (int i = 0; i < 16; i++) o[192 + i] = (uint8_t)(int8_t)(q3k_scale(b + 96, i) - 32);
+        o[208] = b[108];
+        o[209] = b[109];
+    }
+}
+
+/* src/quant/iq4_nl.rs:32-46: w = d * codebook[nibble]; byte k = weight k (low) and k + 16 (high). */
+void ro_dequantize_iq4_nl(const uint8_t *blocks, float *out, size_t n_weights)
+{
+    for (size_t blk = 0; blk < n_weights / 32; blk++) {
+        const uint8_t *b = blocks + blk * 18;
+        float d = ro_f16_to_f32(rd16(b));
+        for (int k = 0; k < 16; k++) {
+            out[blk * 32 + k] = d * (float)IQ4NL[b[2 + k] & 15];
+            out[blk * 32 + k + 16] = d * (float)IQ4NL[b[2 + k] >> 4];
+        }
+    }
+}
+
+/* src/quant/q8_0.rs:45-61: d = amax / 127, q = round-half-away(v * (1/d)) clamped to +-127,
+ * d stored as f16. */
+void ro_quantize_q8_0(const float *vals, uint8_t *out, size_t n)
+{
+    for (size_t blk = 0; blk < n / 32; blk++) {
+        const float *v = vals + blk * 32;
+        uint8_t *o = out + blk * 34;
+        float amax = 0.0f;
+        for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(v[i]));
+        float d = amax / 127.0f;
+        float inv = d > 0.0f ? 1.0f / d : 0.0f;
+        wr16(o, ro_f32_to_f16(d));
+        for (int i = 0; i < 32; i++) {
+            float r = roundf(v[i] * inv);
+            r = r > 127.0f ? 127.0f : r < -127.0f ? -127.0f : r;
+            o[2 + i] = (uint8_t)(int8_t)(isnan(r) ? 0 : (int)r);
+        }
+    }
+}
+
+/* Source type -> the type whose kernels run it (src/runtime/qwen35.rs:274-307); -1 if none. */
+int ro_kernel_type(int src_type)
+{
+    switch (src_type) {
+    case RO_Q4_0: case RO_Q8_0: case RO_Q4_K: case RO_Q5_K: case RO_Q6_K: case RO_IQ4_XS: return src_type;
+    case RO_Q3_K: return RO_Q6_K;
+    case RO_IQ4_NL: return RO_IQ4_XS;
+    case RO_BF16: return RO_Q8_0;
+    }
+    return -1;
+}
+
+/* On-disk rows of a source type -> the repacked planes of its kernel type. */
+int ro_repack_any(int src_type, const uint8_t *src, size_t in_dim, size_t out_dim, uint8_t *out)
+{
+    size_t n = in_dim * out_dim;
+    if (src_type == RO_Q3_K) {
+        if (in_dim % 256) return -2;
+        uint8_t *q6 = (uint8_t *)malloc((n / 256) * 210);
+        ro_q3k_to_q6k(src, q6, n);
+        int rc = ro_repack(RO_Q6_K, q6, in_dim, out_dim, out);
+        free(q6);
+        return rc;
+    }
+    if (src_type == RO_IQ4_NL) /* same block shape and byte order as Q4_0; d is the sub-block scale as-is */
+        return ro_repack(RO_Q4_0, src, in_dim, out_dim, out);
+    if (src_type == RO_BF16) {
+        if (in_dim % 32) return -2;
+        float *f = (float *)malloc(n * sizeof(float));
+        uint8_t *q8 = (uint8_t *)malloc((n / 32) * 34);
+        for (size_t i = 0; i < n; i++) f[i] = ro_bf16_to_f32(rd16(src + 2 * i));
+        ro_quantize_q8_0(f, q8, n);
+        int rc = ro_repack(RO_Q8_0, q8, in_dim, out_dim, out);
+        free(f);
+        free(q8);
+        return rc;
+    }
+    return ro_repack(src_type, src, in_dim, out_dim, out);
+}

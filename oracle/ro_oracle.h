@@ -33,7 +33,11 @@ enum {
     RO_Q4_K = 12,
     RO_Q5_K = 13,
     RO_Q6_K = 14,
-    RO_IQ4_XS = 23
+    RO_IQ4_XS = 23,
+    /* accepted as sources only: relabelled onto one of the six above */
+    RO_Q3_K = 11,
+    RO_IQ4_NL = 20,
+    RO_BF16 = 30
 };
 
 /* Activation block, packed 40 bytes: f32 d, f32 xsum, i8 qs[32]
@@ -100,6 +104,17 @@ void ro_moe_sort(const int32_t *ids, size_t n_entries, size_t n_expert, size_t b
  * renormalised with the floor 6.103515625e-5 on the sum. */
 void ro_router_topk(const float *logits, size_t n_tok, size_t n_expert, size_t n_used,
                     int32_t *ids, float *weights);
+
+/* Relabelled source formats (src/runtime/qwen35.rs:274-307): decoders of the source blocks
+ * (src/quant/q3_k.rs:123-162, iq4_nl.rs:32-46), the exact Q3_K -> Q6_K block transcode
+ * (q3_k.rs:92-121), the Q8_0 quantizer BF16 tensors go through (q8_0.rs:45-61), the kernel type
+ * of a source type, and the source rows -> repacked planes of that kernel type. */
+void ro_dequantize_q3_k(const uint8_t *blocks, float *out, size_t n_weights);
+void ro_q3k_to_q6k(const uint8_t *blocks, uint8_t *out, size_t n_weights);
+void ro_dequantize_iq4_nl(const uint8_t *blocks, float *out, size_t n_weights);
+void ro_quantize_q8_0(const float *vals, uint8_t *out, size_t n);
+int ro_kernel_type(int src_type);
+int ro_repack_any(int src_type, const uint8_t *src, size_t in_dim, size_t out_dim, uint8_t *out);
 
 /* kernels/moe_geglu_q8.cpp:34-66: BlockQ8(act(gate) * up) of gu [n_slot][2*ff]; act 0 = tanh GELU,
  * 1 = SiLU (kernels/swiglu.cpp:11-21).  act_out (may be NULL) gets the f32 values. */

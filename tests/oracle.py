@@ -61,6 +61,13 @@ def lib() -> C.CDLL:
         L.ro_moe_sort.argtypes = [vp, sz, sz, sz, vp, vp, vp, vp]
         L.ro_router_topk.restype = None
         L.ro_router_topk.argtypes = [vp, sz, sz, sz, vp, vp]
+        for name in ("ro_dequantize_q3_k", "ro_q3k_to_q6k", "ro_dequantize_iq4_nl", "ro_quantize_q8_0"):
+            getattr(L, name).restype = None
+            getattr(L, name).argtypes = [vp, vp, sz]
+        L.ro_kernel_type.restype = i
+        L.ro_kernel_type.argtypes = [i]
+        L.ro_repack_any.restype = i
+        L.ro_repack_any.argtypes = [i, vp, sz, sz, vp]
         L.ro_moe_act_q8.restype = None
         L.ro_moe_act_q8.argtypes = [vp, vp, sz, sz, i, vp]
         L.ro_moe_combine.restype = None
@@ -183,6 +190,54 @@ def router_topk(logits: np.ndarray, n_used: int):
     wts = np.empty((n_tok, n_used), dtype=np.float32)
     lib().ro_router_topk(_p(logits), n_tok, n_expert, n_used, _p(ids), _p(wts))
     return ids, wts
+
+
+Q3_K, IQ4_NL, BF16 = 11, 20, 30  # source-only types, relabelled onto Q6_K / IQ4_XS / Q8_0
+SRC_BLOCK = {Q3_K: (256, 110), IQ4_NL: (32, 18), BF16: (1, 2)}  # weights, bytes per source block
+
+
+def kernel_type(src_type: int) -> int:
+    return lib().ro_kernel_type(src_type)
+
+
+def dequantize_src(src_type: int, blocks: np.ndarray, n_weights: int) -> np.ndarray:
+    """Direct decode of a source-only type (not through the relabelling)."""
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+    out = np.empty(n_weights, dtype=np.float32)
+    if src_type == Q3_K:
+        lib().ro_dequantize_q3_k(_p(blocks), _p(out), n_weights)
+    elif src_type == IQ4_NL:
+        lib().ro_dequantize_iq4_nl(_p(blocks), _p(out), n_weights)
+    elif src_type == BF16:
+        out = (blocks.view(np.uint16).astype(np.uint32) << 16).view(np.float32)[:n_weights].copy()
+    else:
+        raise ValueError(src_type)
+    return out
+
+
+def q3k_to_q6k(blocks: np.ndarray, n_weights: int) -> np.ndarray:
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+    out = np.empty(n_weights // 256 * 210, dtype=np.uint8)
+    lib().ro_q3k_to_q6k(_p(blocks), _p(out), n_weights)
+    return out
+
+
+def quantize_q8_0(vals: np.ndarray) -> np.ndarray:
+    vals = np.ascontiguousarray(vals, dtype=np.float32).reshape(-1)
+    out = np.empty(vals.size // 32 * 34, dtype=np.uint8)
+    lib().ro_quantize_q8_0(_p(vals), _p(out), vals.size)
+    return out
+
+
+def repack_any(src_type: int, blocks: np.ndarray, in_dim: int, out_dim: int) -> np.ndarray:
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+    # IQ4_NL has no superblock: its planes (those of Q4_0) exist for any in_dim % 32 == 0
+    n = repacked_len(Q4_0 if src_type == IQ4_NL else kernel_type(src_type), in_dim, out_dim)
+    assert n > 0, "shape not allowed for the type"
+    out = np.zeros(n, dtype=np.uint8)
+    rc = lib().ro_repack_any(src_type, _p(blocks), in_dim, out_dim, _p(out))
+    assert rc == 0, rc
+    return out
 
 
 def moe_act_q8(gu: np.ndarray, act: int):
