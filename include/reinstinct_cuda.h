@@ -38,7 +38,12 @@ enum rc_ggml_type {
     RC_TYPE_Q4_K = 12,
     RC_TYPE_Q5_K = 13,
     RC_TYPE_Q6_K = 14,
-    RC_TYPE_IQ4_XS = 23
+    RC_TYPE_IQ4_XS = 23,
+    /* accepted by rc_repack_for_matvec / rc_ondisk_len as SOURCE types only: the loaders relabel
+     * them onto one of the six above (src/runtime/qwen35.rs:274-307) */
+    RC_SRC_Q3_K = 11,   /* exact: Q6_K blocks with q6 = q3 + 28, sc6 = sc3 - 32 (src/quant/q3_k.rs:92-121) */
+    RC_SRC_IQ4_NL = 20, /* exact: the repacked IQ4_XS planes with d as the sub-block scale (src/quant/iq4_nl.rs:51-73) */
+    RC_SRC_BF16 = 30    /* requantized to Q8_0 (src/quant/q8_0.rs:45-61) */
 };
 
 enum rc_error {
@@ -78,11 +83,17 @@ size_t rc_repacked_len(int ggml_type, size_t in_dim, size_t out_dim);
 /* bytes of the on-disk GGUF rows for the same shape; 0 if unsupported */
 size_t rc_ondisk_len(int ggml_type, size_t in_dim, size_t out_dim);
 
+/* The type whose kernels run tensors of `src_type` (itself for the six native types, Q6_K / IQ4_XS /
+ * Q8_0 for RC_SRC_Q3_K / RC_SRC_IQ4_NL / RC_SRC_BF16); -1 if the type is not supported. */
+int rc_kernel_type(int src_type);
+
 /* On-disk GGUF rows (device) -> repacked-v2 planes (device), done on the GPU.
  * Produces byte-for-byte what src/quant/<fmt>.rs::repack_for_matvec produces on the
  * host (q4_0.rs:86-104, q4_k.rs:126-176, q5_k.rs:97-151, q6_k.rs:86-148,
  * q8_0.rs:93-119, iq4_xs.rs:106-136); the step GpuMatvecTensor::from_bytes_matvec
- * (src/runtime/qwen35.rs:251-331) performs at load.  `blocks_dev` needs 2-byte
+ * (src/runtime/qwen35.rs:251-331) performs at load.  A source-only type (RC_SRC_*) comes out as
+ * the planes of rc_kernel_type(type), which is the type to pass to every other entry point; its
+ * output size is rc_repacked_len(rc_kernel_type(type), ...).  `blocks_dev` needs 2-byte
  * alignment, `out_dev` 16-byte. */
 int rc_repack_for_matvec(void *stream, int ggml_type, const void *blocks_dev,
                          size_t in_dim, size_t out_dim, void *out_dev);

@@ -106,15 +106,23 @@ size_t rc_repacked_len(int type, size_t in_dim, size_t out_dim)
 
 size_t rc_ondisk_len(int type, size_t in_dim, size_t out_dim)
 {
+    if (type == SRC_Q3_K || type == SRC_IQ4_NL || type == SRC_BF16) {
+        // the relabelled tensor must be a legal tensor of its kernel type
+        if (in_dim == 0 || in_dim % fmt_block_weights(fmt_kernel_type(type))) return 0;
+        return out_dim * (in_dim / src_block_weights(type)) * src_block_bytes(type);
+    }
     if (!fmt_known(type) || in_dim == 0 || in_dim % fmt_block_weights(type)) return 0;
     return out_dim * (in_dim / fmt_block_weights(type)) * fmt_block_bytes(type);
 }
 
+int rc_kernel_type(int src_type) { return fmt_kernel_type(src_type); }
+
 int rc_repack_for_matvec(void *stream, int type, const void *blocks_dev, size_t in_dim,
                          size_t out_dim, void *out_dev)
 {
-    if (!fmt_known(type)) return RC_ERR_BAD_TYPE;
-    if (in_dim == 0 || in_dim % fmt_block_weights(type) || in_dim > 0xFFFFFFE0ull ||
+    const int ktype = fmt_kernel_type(type); // a source-only type is repacked as the type it relabels onto
+    if (ktype < 0) return RC_ERR_BAD_TYPE;
+    if (in_dim == 0 || in_dim % fmt_block_weights(ktype) || in_dim > 0xFFFFFFE0ull ||
         out_dim > 0xFFFFFFFFull)
         return RC_ERR_BAD_SHAPE;
     if (out_dim == 0) return RC_OK;

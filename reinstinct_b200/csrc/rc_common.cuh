@@ -14,6 +14,25 @@ constexpr int kWarp = 32;
 
 enum Fmt : int { Q4_0 = 2, Q8_0 = 8, Q4_K = 12, Q5_K = 13, Q6_K = 14, IQ4_XS = 23 };
 
+// Tensor types accepted as SOURCES of rc_repack_for_matvec only: each maps exactly (BF16: by a Q8_0
+// requantization) onto one of the six layouts above (src/runtime/qwen35.rs:274-307).
+enum SrcFmt : int { SRC_Q3_K = 11, SRC_IQ4_NL = 20, SRC_BF16 = 30 };
+
+// The type whose kernels run a source type; -1 if there is none.
+__host__ __device__ inline int fmt_kernel_type(int t)
+{
+    switch (t) {
+    case Q4_0: case Q8_0: case Q4_K: case Q5_K: case Q6_K: case IQ4_XS: return t;
+    case SRC_Q3_K: return Q6_K;
+    case SRC_IQ4_NL: return IQ4_XS;
+    case SRC_BF16: return Q8_0;
+    }
+    return -1;
+}
+// weights and bytes of one source block (BF16: rows are handled 32 values at a time)
+__host__ __device__ inline uint32_t src_block_weights(int t) { return t == SRC_Q3_K ? 256u : 32u; }
+__host__ __device__ inline uint32_t src_block_bytes(int t) { return t == SRC_Q3_K ? 110u : t == SRC_IQ4_NL ? 18u : 64u; }
+
 __host__ __device__ inline bool fmt_known(int t)
 {
     return t == Q4_0 || t == Q8_0 || t == Q4_K || t == Q5_K || t == Q6_K || t == IQ4_XS;

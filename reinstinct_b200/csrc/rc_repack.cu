@@ -67,6 +67,7 @@ __global__ void __launch_bounds__(256)
 repack_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ out, uint32_t in_dim,
               uint32_t out_dim)
 {
+    constexpr int OUT = FMT == SRC_Q3_K ? (int)Q6_K : FMT == SRC_BF16 ? (int)Q8_0 : FMT == SRC_IQ4_NL ? (int)IQ4_XS : FMT; // planes written
     const uint32_t n_sub = in_dim >> 5, nsp = nsp_of(n_sub), n_super = n_sub >> 3;
     const size_t total = (size_t)out_dim * nsp;
     const size_t q = total;
@@ -79,19 +80,74 @@ repack_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ out, uint32
 #pragma unroll
             for (int k = 0; k < 16; k++) v[k] = 0;
             store16(nib + i * 16, v);
-            if (FMT == Q8_0) store16(out + q * 16 + i * 16, v);
-            if (FMT == Q5_K) *reinterpret_cast<uint32_t *>(out + q * 16 + i * 4) = 0;
-            if (FMT == Q6_K) *reinterpret_cast<uint2 *>(out + q * 16 + i * 8) = make_uint2(0, 0);
-            const size_t sc_off = FMT == Q8_0 ? q * 32 : FMT == Q5_K ? q * 20 : FMT == Q6_K ? q * 24 : q * 16;
+            if (OUT == Q8_0) store16(out + q * 16 + i * 16, v);
+            if (OUT == Q5_K) *reinterpret_cast<uint32_t *>(out + q * 16 + i * 4) = 0;
+            if (OUT == Q6_K) *reinterpret_cast<uint2 *>(out + q * 16 + i * 8) = make_uint2(0, 0);
+            const size_t sc_off = OUT == Q8_0 ? q * 32 : OUT == Q5_K ? q * 20 : OUT == Q6_K ? q * 24 : q * 16;
             *reinterpret_cast<uint16_t *>(out + sc_off + i * 2) = 0;
             continue;
         }
-        if (FMT == Q4_0) {
+        if (FMT == Q4_0 || FMT == SRC_IQ4_NL) { // IQ4_NL: the same block shape and byte order; d is the sub-block scale as-is (src/quant/iq4_nl.rs:51-73)
             const uint8_t *b = src + ((size_t)row * n_sub + sb) * 18;
 #pragma unroll
             for (int k = 0; k < 16; k++) v[k] = b[2 + k];
             store16(nib + i * 16, v);
             *reinterpret_cast<uint16_t *>(out + q * 16 + i * 2) = (uint16_t)rd16(b);
+        } else if (FMT == SRC_BF16) {
+            // requantization to Q8_0 (src/quant/q8_0.rs:45-61): d = amax / 127 (kept as f16),
+            // q = round-half-away(v * (1 / d)) clamped to +-127
+            const uint8_t *b = src + ((size_t)row * n_sub + sb) * 64;
+            float f[32], amax = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 32; k++) {
+                f[k] = __uint_as_float(rd16(b + 2 * k) << 16);
+                amax = fmaxf(amax, fabsf(f[k]));
+            }
+            const float d = __fdiv_rn(amax, 127.0f);
+            const float inv = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+#pragma unroll
+                for (int k = 0; k < 16; k++) {
+                    float r = roundf(__fmul_rn(f[16 * h + k], inv));
+                    r = r > 127.0f ? 127.0f : r < -127.0f ? -127.0f : r;
+                    v[k] = (uint8_t)(int8_t)(r != r ? 0 : (int)r);
+                }
+                store16(h ? out + q * 16 + i * 16 : nib + i * 16, v);
+            }
+            *reinterpret_cast<uint16_t *>(out + q * 32 + i * 2) = (uint16_t)f32_to_f16_ref(d);
+        } else if (FMT == SRC_Q3_K) {
+            // exact relabel onto Q6_K (src/quant/q3_k.rs:92-121): q6 = q3 + 28, sc6 = sc3 - 32, same d.
+            // Sub-block sb of the row = weights 32*s .. 32*s+31 of block blk: chunk c = s >> 2, level j = s & 3.
+            const uint32_t blk = sb >> 3, s = sb & 7u, c = s >> 2, j = s & 3u;
+            const uint8_t *b = src + ((size_t)row * n_super + blk) * 110;
+            uint32_t q6[32];
+#pragma unroll
+            for (int l = 0; l < 32; l++) {
+                const uint32_t lo = ((uint32_t)b[32 + 32 * c + l] >> (2 * j)) & 3u;
+                const uint32_t hi = ((uint32_t)b[l] >> (4 * c + j)) & 1u;
+                q6[l] = (lo | (hi << 2)) + 28u;
+            }
+#pragma unroll
+            for (int k = 0; k < 16; k++) v[k] = (uint8_t)((q6[k] & 15u) | ((q6[k + 16] & 15u) << 4));
+            store16(nib + i * 16, v);
+            uint32_t h[2] = {0, 0};
+#pragma unroll
+            for (int g = 0; g < 8; g++)
+#pragma unroll
+                for (int cc = 0; cc < 4; cc++) h[g >> 2] |= (q6[group_weight(g, cc)] >> 4) << (8 * (g & 3) + 2 * cc);
+            *reinterpret_cast<uint2 *>(out + q * 16 + i * 8) = make_uint2(h[0], h[1]);
+            uint32_t scw = 0;
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const uint32_t si = 2u * s + u, jj = si & 3u, grp = si >> 2;
+                const uint32_t low = grp < 2 ? (b[96 + grp * 4 + jj] & 15u) : ((b[96 + (grp - 2) * 4 + jj] >> 4) & 15u);
+                const uint32_t high = ((uint32_t)b[104 + jj] >> (2 * grp)) & 3u;
+                scw |= ((uint32_t)(uint8_t)(int8_t)((int)(low | (high << 4)) - 32)) << (8 * u);
+            }
+            *reinterpret_cast<uint16_t *>(out + q * 24 + i * 2) = (uint16_t)scw;
+            if (s == 0)
+                *reinterpret_cast<uint16_t *>(out + q * 26 + ((size_t)row * n_super + blk) * 2) = (uint16_t)rd16(b + 108);
         } else if (FMT == Q8_0) {
             const uint8_t *b = src + ((size_t)row * n_sub + sb) * 34;
 #pragma unroll
@@ -192,6 +248,9 @@ int launch_repack(cudaStream_t s, int type, const void *blocks, size_t in_dim, s
     case Q5_K: repack_kernel<Q5_K><<<grid, 256, 0, s>>>(src, dst, (uint32_t)in_dim, (uint32_t)out_dim); break;
     case Q6_K: repack_kernel<Q6_K><<<grid, 256, 0, s>>>(src, dst, (uint32_t)in_dim, (uint32_t)out_dim); break;
     case IQ4_XS: repack_kernel<IQ4_XS><<<grid, 256, 0, s>>>(src, dst, (uint32_t)in_dim, (uint32_t)out_dim); break;
+    case SRC_Q3_K: repack_kernel<SRC_Q3_K><<<grid, 256, 0, s>>>(src, dst, (uint32_t)in_dim, (uint32_t)out_dim); break;
+    case SRC_IQ4_NL: repack_kernel<SRC_IQ4_NL><<<grid, 256, 0, s>>>(src, dst, (uint32_t)in_dim, (uint32_t)out_dim); break;
+    case SRC_BF16: repack_kernel<SRC_BF16><<<grid, 256, 0, s>>>(src, dst, (uint32_t)in_dim, (uint32_t)out_dim); break;
     default: return RC_ERR_BAD_TYPE;
     }
     return (int)cudaGetLastError();

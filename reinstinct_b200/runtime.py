@@ -66,8 +66,11 @@ class GpuMatvecTensor:
     def from_bytes_matvec(raw, dtype: int, in_dim: int, out_dim: int,
                           device: torch.device | str = "cuda") -> "GpuMatvecTensor":
         """from_bytes_matvec (src/runtime/qwen35.rs:251-331): on-disk GGUF rows -> repacked-v2
-        planes.  The raw blocks are uploaded and repacked on the GPU (rc_repack_for_matvec)."""
+        planes.  The raw blocks are uploaded and repacked on the GPU (rc_repack_for_matvec).  Source-only
+        types (Q3_K = 11, IQ4_NL = 20, BF16 = 30) come out tagged with the type they relabel onto
+        (src/runtime/qwen35.rs:274-307)."""
         lib = _lib.load()
+        ktype = lib.rc_kernel_type(dtype)
         need = lib.rc_ondisk_len(dtype, in_dim, out_dim)
         if need == 0:
             raise ValueError(f"from_bytes_matvec: unsupported dtype {dtype} or in_dim {in_dim}")
@@ -76,12 +79,12 @@ class GpuMatvecTensor:
         if raw_t.numel() < need:
             raise ValueError(f"from_bytes_matvec: {raw_t.numel()} bytes < {need} needed")
         raw_d = raw_t[:need].to(device, non_blocking=False).contiguous()
-        out = torch.empty(repacked_len(dtype, in_dim, out_dim), dtype=torch.uint8, device=device)
+        out = torch.empty(repacked_len(ktype, in_dim, out_dim), dtype=torch.uint8, device=device)
         with torch.cuda.device(out.device):
             check(lib.rc_repack_for_matvec(_stream(), dtype, raw_d.data_ptr(), in_dim, out_dim,
                                            out.data_ptr()), "rc_repack_for_matvec")
             torch.cuda.current_stream().synchronize()
-        return GpuMatvecTensor(out, dtype, in_dim, out_dim, True)
+        return GpuMatvecTensor(out, ktype, in_dim, out_dim, True)
 
 
 @dataclass

@@ -47,6 +47,12 @@ def test_bad_shapes_and_types_are_rejected_before_any_launch():
     assert lib.rc_matvec(None, _lib.Q4_K, None, None, None, 256, 1) == -3
     assert lib.rc_matvec_batched(None, _lib.Q4_K, 16, 8, 4, 256, 1, 17) == -5
     assert lib.rc_matvec(None, _lib.Q4_K, 8, 8, 4, 256, 1) == -4
+    # source-only tensor types relabel onto a kernel type; unsupported ones are refused
+    assert lib.rc_kernel_type(11) == 14 and lib.rc_kernel_type(20) == 23 and lib.rc_kernel_type(30) == 8
+    assert lib.rc_kernel_type(13) == 13 and lib.rc_kernel_type(10) == -1
+    assert lib.rc_ondisk_len(11, 512, 3) == 660 and lib.rc_ondisk_len(30, 512, 3) == 3072 and lib.rc_ondisk_len(20, 384, 3) == 0
+    assert lib.rc_repack_for_matvec(None, 10, 16, 256, 1, 16) == -1
+    assert lib.rc_repack_for_matvec(None, 11, 16, 384, 1, 16) == -2
     # MoE glue: expert and slot counts beyond what one warp per token holds, odd shapes
     assert lib.rc_moe_topk(None, 4, 1, 2000, 8, 4, 4) == -8
     assert lib.rc_moe_topk(None, 4, 1, 128, 33, 4, 4) == -8
