@@ -235,6 +235,22 @@ int rc_mmq_gemm_grouped(void *stream, int ggml_type, const void *slab,
                         const int32_t *tile_off, uint32_t n_expert, const void *xq, float *y,
                         uint32_t in_dim, uint32_t out_dim, uint32_t n_entries);
 
+/* ---- fused BlockQ8 producers ------------------------------------------------------------------- */
+
+/* launch_rmsnorm_q8; kernel rmsnorm_q8_f32 (kernels/rmsnorm_q8.cpp:38-103): per vector
+ * v = x * rsqrt(mean(x^2) + eps) * w, quantized to BlockQ8 (out [n_vec][n/32]).  n % 32 == 0. */
+int rc_rmsnorm_q8(void *stream, const float *x, const float *w, void *out, uint32_t n, uint32_t n_vec, float eps);
+
+/* launch_add_rmsnorm_q8; kernel add_rmsnorm_q8_f32 (kernels/qwen35_fused.cpp:66-118): hidden += add
+ * (add may be NULL: hidden is then only read), y = rmsnorm(hidden) * w as f32 (y may be NULL) and as
+ * BlockQ8.  One vector per row of n_vec; any n % 32 == 0 (the reference's kernel stops at 8192). */
+int rc_add_rmsnorm_q8(void *stream, float *hidden, const float *add, const float *w, float *y, void *out,
+                      uint32_t n, uint32_t n_vec, float eps);
+
+/* launch_swiglu_q8; kernel swiglu_q8_f32 (kernels/qwen35_fused.cpp:123-138): out = silu(gate) * up as
+ * f32 (out may be NULL) and as BlockQ8 (q8 [n/32]); n % 32 == 0 (several vectors: pass their total). */
+int rc_swiglu_q8(void *stream, const float *gate, const float *up, float *out, void *q8, size_t n);
+
 /* launch_moe_expert_matvec and launch_moe_down (src/runtime/qwen35.rs:3066-3139); kernels
  * moe_matvec_{q4k,q5k,q6k,q8_0}_repacked_f32 and moe_matvec_{q5k,q6k}_down_f32: the decode-side
  * routed-expert matvec.  For token t and routing slot j:

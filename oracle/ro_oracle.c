@@ -931,3 +931,64 @@ int ro_repack_any(int src_type, const uint8_t *src, size_t in_dim, size_t out_di
     }
     return ro_repack(src_type, src, in_dim, out_dim, out);
 }
+
+/* ------------------------------------------- fused BlockQ8 producers --- */
+/* kernels/rmsnorm_q8.cpp:38-103 and kernels/qwen35_fused.cpp:66-118: x (+ add) -> rmsnorm * w -> BlockQ8.
+ * The sum of squares is reduced in the order the CUDA kernel fixes (the reference's own order, a
+ * 512-thread tree or a wave64 reduction, is a property of its launch geometry): 1024 strided partial
+ * sums, a 32-lane xor-butterfly per group of 32, the 32 group sums added in order; rrms with IEEE
+ * divide and square root.  hidden_out / y_out may be NULL. */
+void ro_rmsnorm_q8(const float *x, const float *add, const float *w, float *hidden_out, float *y_out,
+                   uint8_t *out, size_t n, size_t n_vec, float eps)
+{
+    float *v = (float *)malloc(sizeof(float) * n);
+    for (size_t vec = 0; vec < n_vec; vec++) {
+        const float *xv = x + vec * n, *av = add ? add + vec * n : NULL;
+        float part[1024];
+        for (int t = 0; t < 1024; t++) {
+            float p = 0.0f;
+            for (size_t i = (size_t)t; i < n; i += 1024) {
+                float e = av ? xv[i] + av[i] : xv[i];
+                float sq = e * e;
+                p = p + sq;
+            }
+            part[t] = p;
+        }
+        float tot = 0.0f;
+        for (int wp = 0; wp < 32; wp++) {
+            float s[32];
+            memcpy(s, part + 32 * wp, sizeof s);
+            for (int off = 16; off > 0; off >>= 1) {
+                float ns[32];
+                for (int l = 0; l < 32; l++) ns[l] = s[l] + s[l ^ off];
+                memcpy(s, ns, sizeof s);
+            }
+            tot = wp == 0 ? s[0] : tot + s[0];
+        }
+        float mean = tot / (float)n;
+        float rrms = 1.0f / sqrtf(mean + eps);
+        for (size_t i = 0; i < n; i++) {
+            float e = av ? xv[i] + av[i] : xv[i];
+            if (hidden_out) hidden_out[vec * n + i] = e;
+            float t = e * rrms;
+            v[i] = t * w[i];
+        }
+        if (y_out) memcpy(y_out + vec * n, v, sizeof(float) * n);
+        ro_quantize_q8(v, out + vec * (n / 32) * RO_BLOCKQ8_BYTES, n, 1);
+    }
+    free(v);
+}
+
+/* kernels/qwen35_fused.cpp:123-138: silu(gate) * up as f32 and BlockQ8. */
+void ro_swiglu_q8(const float *gate, const float *up, float *out_f32, uint8_t *q8, size_t n)
+{
+    float *v = (float *)malloc(sizeof(float) * (n ? n : 1));
+    for (size_t i = 0; i < n; i++) {
+        float e = 1.0f + expf(-gate[i]);
+        float s = gate[i] / e;
+        v[i] = s * up[i];
+    }
+    if (out_f32) memcpy(out_f32, v, sizeof(float) * n);
+    ro_quantize_q8(v, q8, n, 1);
+    free(v);
+}

@@ -105,6 +105,12 @@ void ro_moe_sort(const int32_t *ids, size_t n_entries, size_t n_expert, size_t b
 void ro_router_topk(const float *logits, size_t n_tok, size_t n_expert, size_t n_used,
                     int32_t *ids, float *weights);
 
+/* Fused BlockQ8 producers: rmsnorm (+ residual add) and SwiGLU followed by the quantizer
+ * (kernels/rmsnorm_q8.cpp:38-103, kernels/qwen35_fused.cpp:66-138). */
+void ro_rmsnorm_q8(const float *x, const float *add, const float *w, float *hidden_out, float *y_out,
+                   uint8_t *out, size_t n, size_t n_vec, float eps);
+void ro_swiglu_q8(const float *gate, const float *up, float *out_f32, uint8_t *q8, size_t n);
+
 /* Relabelled source formats (src/runtime/qwen35.rs:274-307): decoders of the source blocks
  * (src/quant/q3_k.rs:123-162, iq4_nl.rs:32-46), the exact Q3_K -> Q6_K block transcode
  * (q3_k.rs:92-121), the Q8_0 quantizer BF16 tensors go through (q8_0.rs:45-61), the kernel type

@@ -331,6 +331,43 @@ int rc_mmq_gemm_grouped(void *stream, int type, const void *slab, size_t bytes_p
                               n_expert, xq, y, in_dim, out_dim, n_entries);
 }
 
+/* ---- fused BlockQ8 producers ------------------------------------------------------------------- */
+
+int rc_add_rmsnorm_q8(void *stream, float *hidden, const float *add, const float *w, float *y, void *out, uint32_t n,
+                      uint32_t n_vec, float eps)
+{
+    if (n == 0 || n % 32) return RC_ERR_BAD_SHAPE;
+    if (n_vec == 0) return RC_OK;
+    if (!hidden || !w || !out) return RC_ERR_NULL_POINTER;
+    if (((uintptr_t)hidden & 3u) || ((uintptr_t)add & 3u) || ((uintptr_t)w & 3u) || ((uintptr_t)y & 3u) || ((uintptr_t)out & 7u))
+        return RC_ERR_MISALIGNED;
+    int rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_rmsnorm_q8(S(stream), hidden, add, w, hidden, y, out, n, n_vec, eps);
+}
+
+int rc_rmsnorm_q8(void *stream, const float *x, const float *w, void *out, uint32_t n, uint32_t n_vec, float eps)
+{
+    if (n == 0 || n % 32) return RC_ERR_BAD_SHAPE;
+    if (n_vec == 0) return RC_OK;
+    if (!x || !w || !out) return RC_ERR_NULL_POINTER;
+    if (((uintptr_t)x & 3u) || ((uintptr_t)w & 3u) || ((uintptr_t)out & 7u)) return RC_ERR_MISALIGNED;
+    int rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_rmsnorm_q8(S(stream), x, nullptr, w, nullptr, nullptr, out, n, n_vec, eps);
+}
+
+int rc_swiglu_q8(void *stream, const float *gate, const float *up, float *out, void *q8, size_t n)
+{
+    if (n % 32) return RC_ERR_BAD_SHAPE;
+    if (n == 0) return RC_OK;
+    if (!gate || !up || !q8) return RC_ERR_NULL_POINTER;
+    if (((uintptr_t)gate & 3u) || ((uintptr_t)up & 3u) || ((uintptr_t)out & 3u) || ((uintptr_t)q8 & 7u)) return RC_ERR_MISALIGNED;
+    int rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_swiglu_q8(S(stream), gate, up, out, q8, n);
+}
+
 int rc_moe_expert_matvec(void *stream, int type, const void *slab, size_t bytes_per_expert, const int32_t *ids,
                          uint32_t n_expert, const void *xq, float *y, uint32_t in_dim, uint32_t out_dim, uint32_t n_used,
                          uint32_t n_tok, uint32_t xq_tok_stride, uint32_t xq_slot_stride)

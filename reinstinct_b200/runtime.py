@@ -22,6 +22,7 @@ __all__ = [
     "launch_quantize_q8", "launch_matvec", "launch_matvec_xq8", "launch_matvec_batched",
     "matvec_block_dots", "launch_mmq_gemm", "launch_moe_sort", "launch_moe_gather_xq",
     "launch_moe_grouped_gemm", "launch_moe_scatter_rows", "repacked_len", "init", "PeerAllGather",
+    "launch_rmsnorm_q8", "launch_add_rmsnorm_q8", "launch_swiglu_q8",
     "launch_moe_expert_matvec", "launch_moe_topk", "launch_moe_act_q8", "launch_moe_combine", "ACT_GEGLU", "ACT_SWIGLU",
 ]
 
@@ -258,6 +259,23 @@ def launch_moe_grouped_gemm(moe: MoeGroupedScratch, et: GpuExpertTensor, xq: tor
                                           _ptr(moe.expert_off), _ptr(moe.tile_off), moe.n_expert,
                                           _ptr(xq), _ptr(y), in_dim, out_dim, n_entries),
           "rc_mmq_gemm_grouped")
+
+
+def launch_rmsnorm_q8(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n: int, n_vec: int, eps: float) -> None:
+    """launch_rmsnorm_q8 (kernels/rmsnorm_q8.cpp:38-103)."""
+    check(_lib.load().rc_rmsnorm_q8(_stream(), _ptr(x), _ptr(w), _ptr(out), n, n_vec, eps), "rc_rmsnorm_q8")
+
+
+def launch_add_rmsnorm_q8(hidden: torch.Tensor, add, w: torch.Tensor, y, out: torch.Tensor, n: int, n_vec: int,
+                          eps: float) -> None:
+    """launch_add_rmsnorm_q8 (kernels/qwen35_fused.cpp:66-118); add and y may be None."""
+    check(_lib.load().rc_add_rmsnorm_q8(_stream(), _ptr(hidden), _ptr(add), _ptr(w), _ptr(y), _ptr(out), n, n_vec, eps),
+          "rc_add_rmsnorm_q8")
+
+
+def launch_swiglu_q8(gate: torch.Tensor, up: torch.Tensor, out, q8: torch.Tensor, n: int) -> None:
+    """launch_swiglu_q8 (kernels/qwen35_fused.cpp:123-138); out may be None."""
+    check(_lib.load().rc_swiglu_q8(_stream(), _ptr(gate), _ptr(up), _ptr(out), _ptr(q8), n), "rc_swiglu_q8")
 
 
 def launch_moe_expert_matvec(et: GpuExpertTensor, ids: torch.Tensor, xq8: torch.Tensor, y: torch.Tensor, n_used: int,

@@ -64,6 +64,10 @@ def lib() -> C.CDLL:
         for name in ("ro_dequantize_q3_k", "ro_q3k_to_q6k", "ro_dequantize_iq4_nl", "ro_quantize_q8_0"):
             getattr(L, name).restype = None
             getattr(L, name).argtypes = [vp, vp, sz]
+        L.ro_rmsnorm_q8.restype = None
+        L.ro_rmsnorm_q8.argtypes = [vp, vp, vp, vp, vp, vp, sz, sz, C.c_float]
+        L.ro_swiglu_q8.restype = None
+        L.ro_swiglu_q8.argtypes = [vp, vp, vp, vp, sz]
         L.ro_kernel_type.restype = i
         L.ro_kernel_type.argtypes = [i]
         L.ro_repack_any.restype = i
@@ -238,6 +242,26 @@ def repack_any(src_type: int, blocks: np.ndarray, in_dim: int, out_dim: int) -> 
     rc = lib().ro_repack_any(src_type, _p(blocks), in_dim, out_dim, _p(out))
     assert rc == 0, rc
     return out
+
+
+def rmsnorm_q8(x: np.ndarray, w: np.ndarray, eps: float, add: np.ndarray | None = None):
+    """x [n_vec, n] (+ add) -> (hidden f32, y f32, BlockQ8 bytes)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    n_vec, n = x.shape
+    a = None if add is None else np.ascontiguousarray(add, dtype=np.float32)
+    hid, y = np.empty_like(x), np.empty_like(x)
+    out = np.zeros(n_vec * (n // 32) * 40, dtype=np.uint8)
+    lib().ro_rmsnorm_q8(_p(x), _p(a), _p(np.ascontiguousarray(w, dtype=np.float32)), _p(hid), _p(y), _p(out), n, n_vec, eps)
+    return hid, y, out
+
+
+def swiglu_q8(gate: np.ndarray, up: np.ndarray):
+    gate = np.ascontiguousarray(gate, dtype=np.float32).reshape(-1)
+    up = np.ascontiguousarray(up, dtype=np.float32).reshape(-1)
+    v = np.empty_like(gate)
+    out = np.zeros(gate.size // 32 * 40, dtype=np.uint8)
+    lib().ro_swiglu_q8(_p(gate), _p(up), _p(v), _p(out), gate.size)
+    return v, out
 
 
 def moe_act_q8(gu: np.ndarray, act: int):

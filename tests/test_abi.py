@@ -53,6 +53,15 @@ def test_bad_shapes_and_types_are_rejected_before_any_launch():
     assert lib.rc_ondisk_len(11, 512, 3) == 660 and lib.rc_ondisk_len(30, 512, 3) == 3072 and lib.rc_ondisk_len(20, 384, 3) == 0
     assert lib.rc_repack_for_matvec(None, 10, 16, 256, 1, 16) == -1
     assert lib.rc_repack_for_matvec(None, 11, 16, 384, 1, 16) == -2
+    # fused BlockQ8 producers
+    assert lib.rc_rmsnorm_q8(None, 4, 4, 8, 48, 1, 1e-6) == -2
+    assert lib.rc_rmsnorm_q8(None, None, 4, 8, 64, 1, 1e-6) == -3
+    assert lib.rc_rmsnorm_q8(None, 4, 4, 4, 64, 1, 1e-6) == -4
+    assert lib.rc_add_rmsnorm_q8(None, None, None, 4, None, 8, 64, 1, 1e-6) == -3
+    assert lib.rc_add_rmsnorm_q8(None, None, None, None, None, None, 64, 0, 1e-6) == 0
+    assert lib.rc_swiglu_q8(None, 4, 4, None, 8, 33) == -2
+    assert lib.rc_swiglu_q8(None, 4, None, None, 8, 64) == -3
+    assert lib.rc_swiglu_q8(None, None, None, None, None, 0) == 0
     # MoE glue: expert and slot counts beyond what one warp per token holds, odd shapes
     assert lib.rc_moe_topk(None, 4, 1, 2000, 8, 4, 4) == -8
     assert lib.rc_moe_topk(None, 4, 1, 128, 33, 4, 4) == -8

@@ -189,3 +189,30 @@ def test_moe_combine_weighted_sum():
     np.testing.assert_array_equal(ro.moe_combine(ex, ids, w, None), ones)
     # one slot with weight 1 and scale 1 returns that expert's row unchanged
     np.testing.assert_array_equal(ro.moe_combine(ex[:, :1], ids[:, :1], np.ones((n_tok, 1), np.float32), None), ex[:, 0])
+
+
+def test_rmsnorm_q8_is_norm_then_quantizer():
+    """ro_rmsnorm_q8 = (x + add) * rsqrt(mean + eps) * w in f32 (against f64), then the ro_quantize_q8
+    record stream of exactly those values (kernels/rmsnorm_q8.cpp:38-103, qwen35_fused.cpp:66-118)."""
+    rng = np.random.default_rng(21)
+    for n, n_vec in ((2048, 3), (5120, 1), (96, 2)):
+        x = rng.standard_normal((n_vec, n)).astype(np.float32) * 3
+        add = rng.standard_normal((n_vec, n)).astype(np.float32)
+        w = (rng.random(n) + 0.5).astype(np.float32)
+        for a in (None, add):
+            hid, y, q = ro.rmsnorm_q8(x, w, 1e-6, a)
+            h64 = x.astype(np.float64) + (0 if a is None else a.astype(np.float64))
+            np.testing.assert_array_equal(hid, x if a is None else x + a)
+            ref = h64 / np.sqrt((h64 ** 2).mean(1, keepdims=True) + 1e-6) * w
+            np.testing.assert_allclose(y, ref, rtol=3e-6, atol=1e-7)
+            np.testing.assert_array_equal(q, ro.quantize_q8(y))
+
+
+def test_swiglu_q8_is_activation_then_quantizer():
+    rng = np.random.default_rng(22)
+    g = (rng.standard_normal(4096) * 3).astype(np.float32)
+    u = rng.standard_normal(4096).astype(np.float32)
+    v, q = ro.swiglu_q8(g, u)
+    g64 = g.astype(np.float64)
+    np.testing.assert_allclose(v, g64 / (1 + np.exp(-g64)) * u, rtol=3e-6, atol=1e-7)
+    np.testing.assert_array_equal(q, ro.quantize_q8(v.reshape(1, -1)))
