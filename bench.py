@@ -259,7 +259,7 @@ def run_reference_arm(args):
 
 def workload_config(n_gpus: int) -> dict:
     return {
-        "workload": "config 2: dense-27B decode FFN projections, batch 1 (Q4_K gate+up 5120->17408, Q6_K down 17408->5120)",
+        "workload": "config 2: dense-27B decode FFN, batch 1 (quantize x; Q4_K gate, up 5120->17408; SwiGLU+quantize; Q6_K down 17408->5120)",
         "bytes_per_step": 176168960,
         "l2": "weights rotate over 3 distinct layer copies (528 MB > 4x L2); every launch reads cold HBM",
         "parallelism": (f"row-shard x{n_gpus}; all-gather of the quantized intermediate and of down's output "
@@ -355,27 +355,26 @@ def run_gpu_arm(args):
     layer_bytes_local = sum(w.data.numel() for w in copies[0])
     layer_bytes_total = layer_bytes_local * world
 
-    # one pinned input block [x | h] and one device copy of it, so a step uploads with one copy
-    in_host = torch.cat([torch.from_numpy(synth.synth_activations(1, HIDDEN, 5)),
-                         torch.from_numpy(synth.synth_activations(1, FFN, 6))], dim=1).pin_memory()
-    in_dev = torch.empty_like(in_host, device=dev)
-    in_dev.copy_(in_host)
-    x_dev, h_dev = in_dev[:, :HIDDEN], in_dev[:, HIDDEN:]
+    # the layer's input: one pinned host vector and its device copy
+    in_host = torch.from_numpy(synth.synth_activations(1, HIDDEN, 5)).pin_memory()
+    x_dev = torch.empty_like(in_host, device=dev)
+    x_dev.copy_(in_host)
     xq = torch.empty((HIDDEN // 32) * 40, dtype=torch.uint8, device=dev)
     hq = torch.empty((FFN // 32) * 40, dtype=torch.uint8, device=dev)
-    # gate | up outputs side by side: one download per step for them, one for down's gathered rows
+    # gate | up outputs side by side (this rank's rows)
     y_gu = torch.empty(2 * (FFN // world), device=dev)
     y_gate, y_up = y_gu[:FFN // world], y_gu[FFN // world:]
     y_down = torch.empty(HIDDEN // world, device=dev)
     g_gate = torch.empty(FFN, device=dev) if world > 1 else y_gate
     g_up = torch.empty(FFN, device=dev) if world > 1 else y_up
     g_down = torch.empty(HIDDEN, device=dev) if world > 1 else y_down
-    ygu_host = torch.empty(2 * (FFN // world), dtype=torch.float32).pin_memory()
     yd_host = torch.empty(HIDDEN, dtype=torch.float32).pin_memory()
     launches_per_step = 5
 
+    # The intermediate h = silu(gate) * up is made and quantized in one launch (rc_swiglu_q8), so the
+    # step is the decode FFN as the engine runs it: quantize x, gate, up, SwiGLU+quantize, down.
     # N > 1: gate and up stay sharded (the activation between them and down is elementwise); each
-    # rank quantizes its 1/N of the intermediate and the BlockQ8 shards are all-gathered (21.7 KB
+    # rank produces its 1/N of the quantized intermediate and the BlockQ8 shards are all-gathered (21.7 KB
     # instead of 2 x 68 KB of f32); down's output rows are all-gathered for the next layer.  The
     # gathers are rc_allgather_push (stores into peer memory over NVLink + a counter handshake),
     # so the whole sharded step replays from one CUDA graph; --nccl-gather uses NCCL instead.
@@ -389,21 +388,17 @@ def run_gpu_arm(args):
     else:
         hq_in = hq
 
-    def step(c: int, after_gate_up=None):
+    def step(c: int):
         ws = copies[c % n_copies]
         rt.launch_quantize_q8(x_dev, xq, HIDDEN, 1)
         rt.launch_matvec_xq8(ws[0], xq, y_gate)
         rt.launch_matvec_xq8(ws[1], xq, y_up)
-        if after_gate_up is not None:
-            after_gate_up()
+        rt.launch_swiglu_q8(y_gate, y_up, None, hq_local, h_local)
         if world > 1:
-            rt.launch_quantize_q8(h_dev[:, rank * h_local:(rank + 1) * h_local], hq_local, h_local, 1)
             if push:
                 ga_h.gather(hq_local)
             else:
                 dist.all_gather_into_tensor(hq, hq_local)
-        else:
-            rt.launch_quantize_q8(h_dev, hq, FFN, 1)
         rt.launch_matvec_xq8(ws[2], hq_in, y_down)
         if world > 1:
             if push:
@@ -412,38 +407,25 @@ def run_gpu_arm(args):
                 dist.all_gather_into_tensor(g_down, y_down)
 
     if push:
-        # one checked step: the gathered BlockQ8 must equal quantizing the whole vector locally
+        # one checked step: the gathered BlockQ8 must equal SwiGLU+quantize of the whole gathered vectors
         step(0)
         got = torch.empty_like(hq)
         ga_h.copy_out(got)
-        rt.launch_quantize_q8(h_dev, hq, FFN, 1)
+        dist.all_gather_into_tensor(g_gate, y_gate)
+        dist.all_gather_into_tensor(g_up, y_up)
+        rt.launch_swiglu_q8(g_gate, g_up, None, hq, FFN)
         torch.cuda.synchronize()
         assert torch.equal(got, hq), "peer gather of the quantized intermediate differs from the local quantization"
 
-    # End-to-end step: x is uploaded first; the upload of h (down's input) and the download of the
-    # gate / up outputs run on a second stream beside the kernels that do not need them, and join
-    # before the step ends.  Every byte still crosses PCIe inside the step.
-    side = torch.cuda.Stream(device=dev)
-
+    # End-to-end step: the layer's input comes from pinned host memory and its output goes back there,
+    # both inside the step.
     def step_e2e(c: int):
-        main = torch.cuda.current_stream()
-        side.wait_stream(main)                       # the previous step has read h and y_gu
-        x_dev.copy_(in_host[:, :HIDDEN], non_blocking=True)
-        with torch.cuda.stream(side):
-            h_dev.copy_(in_host[:, HIDDEN:], non_blocking=True)
-
-        def after_gate_up():
-            main.wait_stream(side)                   # h has arrived
-            side.wait_stream(main)                   # gate and up are done
-            with torch.cuda.stream(side):
-                ygu_host.copy_(y_gu, non_blocking=True)
-
-        step(c, after_gate_up)
+        x_dev.copy_(in_host, non_blocking=True)
+        step(c)
         if push:
             ga_y.copy_out(yd_host)
         else:
             yd_host.copy_(g_down, non_blocking=True)
-        main.wait_stream(side)
 
     def barrier():
         if world > 1:
@@ -518,6 +500,33 @@ def run_gpu_arm(args):
         e2e_steps = args.steps
     e2e_value = layer_bytes_total / (ms_e2e / e2e_steps * 1e-3) / 1e9
 
+    # The same step with no copy nodes: pinned host memory is addressable from the device, so the first
+    # kernel reads x and the last one writes y straight across PCIe (single GPU; reported beside e2e).
+    zero_copy = None
+    if world == 1 and use_graph:
+        def step_zc(c: int):
+            ws = copies[c % n_copies]
+            rt.launch_quantize_q8(in_host, xq, HIDDEN, 1)
+            rt.launch_matvec_xq8(ws[0], xq, y_gate)
+            rt.launch_matvec_xq8(ws[1], xq, y_up)
+            rt.launch_swiglu_q8(y_gate, y_up, None, hq, FFN)
+            rt.launch_matvec_xq8(ws[2], hq, yd_host)
+        yd_host.zero_()
+        step(0)
+        torch.cuda.synchronize()
+        want = y_down.cpu()
+        step_zc(0)
+        torch.cuda.synchronize()
+        if torch.equal(yd_host.reshape(-1), want.reshape(-1)):
+            graph_zc = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph_zc):
+                for c in range(n_copies):
+                    step_zc(c)
+            calls = max(1, (args.steps + n_copies - 1) // n_copies)
+            ms_zc = timed(lambda i: graph_zc.replay(), calls, 3) / (calls * n_copies)
+            zero_copy = {"value": layer_bytes_total / (ms_zc * 1e-3) / 1e9, "ms_per_step": ms_zc,
+                         "note": "x read and y written in pinned host memory by the kernels themselves"}
+
     # dominant kernel alone: the Q4_K matvec over rotating copies, CUDA events on its stream
     q4k_bytes = copies[0][0].data.numel()
     mats = [copies[c][i] for c in range(n_copies) for i in (0, 1)]
@@ -566,8 +575,8 @@ def run_gpu_arm(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 dp4a, f32 accumulate",
             "data": "synthetic", "config": workload_config(world),
             "e2e": {"value": e2e_value, "unit": "GB/s",
-                    "h2d_bytes_per_step": (HIDDEN + FFN) * 4, "d2h_bytes_per_step": (2 * FFN // world + HIDDEN) * 4,
-                    "ms_per_step": ms_e2e / e2e_steps, "graph_replay": use_graph},
+                    "h2d_bytes_per_step": HIDDEN * 4, "d2h_bytes_per_step": HIDDEN * 4,
+                    "ms_per_step": ms_e2e / e2e_steps, "graph_replay": use_graph, "zero_copy": zero_copy},
             "gpu_launches": (launches_per_step + (2 if push else 0)) * steps_timed,
             "gather": ("peer-push" if push else "nccl") if world > 1 else None,
             "clocks": clocks,
