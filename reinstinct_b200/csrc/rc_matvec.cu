@@ -488,6 +488,9 @@ stream_body(uint8_t *smem, const uint8_t *__restrict__ w, const uint8_t *__restr
 }
 
 template <int NB> struct MinBlocks { static constexpr int v = NB <= 1 ? 4 : NB <= 4 ? 3 : 2; };
+// weight rows a warp of matvec_multi_kernel owns: as many as the accumulators (R * NB) leave registers for
+template <int NB> struct MultiRows { static constexpr int v = NB <= 4 ? 4 : 2; };
+constexpr int kMultiMinBlocks = 2; // 128 registers: R weight rows in flight twice over, plus R * NB sums
 
 // --------------------------------------------------------------------------------------------
 // The common decode shape gets a loop with nothing else in it: one warp per weight row (no row
@@ -579,6 +582,93 @@ matvec_rows_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq
             const float v = warp_sum(acc[b]);
             if (lane == 0 && b < (int)n_rows) y[(size_t)b * out_dim + row] = v;
         }
+    }
+}
+
+// --------------------------------------------------------------------------------------------
+// Several activation rows: the row kernels above read every activation block from shared memory
+// once per weight row, and at NB rows that traffic (48 bytes per lane, sub-block and activation
+// row) outruns the math.  Here a warp owns R consecutive weight rows: each activation block is
+// loaded once and used for all R, so shared-memory reads per weight row drop by R.  Same loads,
+// same term(), same order of additions per lane as the other kernels (iterations in turn, then
+// the warp reduction), hence the same bits.  The next iteration's weights are requested before
+// the current one is used.
+template <int FMT, int NB, int R>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, kMultiMinBlocks)
+matvec_multi_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq, float *__restrict__ y,
+                    uint32_t in_dim, uint32_t out_dim, uint32_t n_rows)
+{
+    extern __shared__ __align__(16) uint8_t smem[];
+    if (NB <= 2) n_rows = NB;
+    const uint32_t n_sub = in_dim >> 5, n_iters = n_sub >> 5;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const Planes p = planes_of<FMT>(w, in_dim, out_dim);
+    const bool sup_a4 = (reinterpret_cast<uintptr_t>(p.sup) & 3u) == 0;
+    const XStage st = carve_stage<FMT>(smem, n_rows * n_sub);
+    const uint32_t row_stride = gridDim.x * kWarpsPerCta * R;
+
+    Raw<FMT> cur[R], nxt[R];
+    GroupPtrs gp[R];
+    auto set_rows = [&](uint32_t base) {
+#pragma unroll
+        for (int r = 0; r < R; r++) gp[r] = group_ptrs<FMT>(p, min(base + r, out_dim - 1u), lane);
+    };
+    auto fetch = [&](Raw<FMT>(&dst)[R], uint32_t it) {
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            if (sup_a4) fetch_off<FMT, true>(dst[r], gp[r], (int)it);
+            else fetch_off<FMT, false>(dst[r], gp[r], (int)it);
+        }
+    };
+
+    uint32_t row = (blockIdx.x * kWarpsPerCta + warp) * R;
+    if (row < out_dim) { // weights do not wait for x
+        set_rows(row);
+        fetch(cur, 0);
+    }
+    pdl_launch_dependents();
+    pdl_wait();
+    stage_x<FMT>(st, xq, n_rows * n_sub);
+    __syncthreads();
+
+    for (; row < out_dim; row += row_stride) {
+        float acc[R][NB];
+#pragma unroll
+        for (int r = 0; r < R; r++)
+#pragma unroll
+            for (int b = 0; b < NB; b++) acc[r][b] = 0.0f;
+        for (uint32_t it = 0; it < n_iters; it++) {
+            if (it + 1 < n_iters) {
+                fetch(nxt, it + 1);
+            } else if (row + row_stride < out_dim) {
+                set_rows(row + row_stride);
+                fetch(nxt, 0);
+            }
+            const uint32_t sb = it * 32u + lane;
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                if (b < (int)n_rows) {
+                    const uint32_t xi = b * n_sub + sb;
+                    const int4 xl = st.lo[xi], xh = st.hi[xi];
+                    const float2 ds = st.ds[xi];
+                    const int2 is = FmtTraits<FMT>::needs_is ? st.is[xi] : make_int2(0, 0);
+#pragma unroll
+                    for (int r = 0; r < R; r++) {
+                        int i0, i1;
+                        acc[r][b] += term<FMT>(cur[r], xl, xh, ds, is, i0, i1);
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < R; r++) cur[r] = nxt[r];
+        }
+#pragma unroll
+        for (int r = 0; r < R; r++)
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                const float v = warp_sum(acc[r][b]);
+                if (lane == 0 && b < (int)n_rows && row + r < out_dim) y[(size_t)b * out_dim + row + r] = v;
+            }
     }
 }
 
@@ -697,6 +787,23 @@ int launch_one(cudaStream_t s, const void *w, const void *xq, float *y, int32_t 
         while (ks * 2u <= (uint32_t)g_tune.ks && ks * 2u <= (uint32_t)kWarpsPerCta && ks * 2u <= n_iters) ks *= 2u;
     }
     if (DUMP) ks = 1;
+    if constexpr (!DUMP && NB >= 2) {
+        // several activation rows on a matrix with enough weight rows to give every warp slot R of them
+        constexpr int R = MultiRows<NB>::v;
+        if (n_sub % 32u == 0 && !g_tune.no_rows_kernel && (uint64_t)out_dim >= (uint64_t)sm_count() * kWarpsPerCta * R) {
+            const uint32_t capacity = (uint32_t)sm_count() * min(resident, (uint32_t)kMultiMinBlocks);
+            const uint32_t n_cta_rows = (out_dim + kWarpsPerCta * R - 1u) / (kWarpsPerCta * R);
+            const uint32_t grid = min(n_cta_rows, capacity);
+            const size_t xsm = (((size_t)n_rows * n_sub * FmtTraits<FMT>::x_bytes) + 15u) & ~(size_t)15u;
+            if (g_tune.no_pdl) {
+                matvec_multi_kernel<FMT, NB, R><<<grid, kWarpsPerCta * 32, xsm, s>>>((const uint8_t *)w, (const uint8_t *)xq, y, in_dim,
+                                                                                    out_dim, n_rows);
+                return (int)cudaGetLastError();
+            }
+            return (int)launch_pdl(matvec_multi_kernel<FMT, NB, R>, dim3(grid), dim3(kWarpsPerCta * 32), xsm, s, (const uint8_t *)w,
+                                   (const uint8_t *)xq, y, in_dim, out_dim, n_rows);
+        }
+    }
     if constexpr (!DUMP && NB <= 4) {
         if (ks == 1 && n_sub % 32u == 0 && !g_tune.no_rows_kernel) {
             // group length: as long as the format's registers allow, the whole row if it is shorter
@@ -775,6 +882,9 @@ constexpr int kGroupedBN = 16;
 template <int FMT, int NB> int set_attr_rows()
 {
     int rc = 0;
+    if constexpr (NB >= 2)
+        rc |= (int)cudaFuncSetAttribute(matvec_multi_kernel<FMT, NB, MultiRows<NB>::v>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)kMaxStageBytesHost);
     rc |= (int)cudaFuncSetAttribute(matvec_rows_kernel<FMT, NB, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
     rc |= (int)cudaFuncSetAttribute(matvec_rows_kernel<FMT, NB, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
     rc |= (int)cudaFuncSetAttribute(matvec_rows_kernel<FMT, NB, 5>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
@@ -795,6 +905,8 @@ template <int FMT> int set_attr_fmt()
     rc |= set_attr_one<FMT, 8, true>();
     rc |= set_attr_one<FMT, 16, true>();
     rc |= set_attr_rows<FMT, 1>() | set_attr_rows<FMT, 2>() | set_attr_rows<FMT, 4>();
+    rc |= (int)cudaFuncSetAttribute(matvec_multi_kernel<FMT, 8, MultiRows<8>::v>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
+    rc |= (int)cudaFuncSetAttribute(matvec_multi_kernel<FMT, 16, MultiRows<16>::v>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
     rc |= (int)cudaFuncSetAttribute(matvec_grouped_kernel<FMT, kGroupedBN>,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
     return rc;

@@ -1095,8 +1095,34 @@ int launch_mmq_gemm_f32(cudaStream_t s, int type, const void *w, const float *x,
     // f32 activations and a large enough scratch: the f16-operand kernel (rc_mmq_deq.cu), unless one of
     // the exact-integer kernels was asked for
     if (!g_force_dp4a && (g_mmq_kind == 0 || g_mmq_kind == 32) && ((uintptr_t)scratch & 15u) == 0 &&
-        scratch_bytes >= mmq_deq_scratch_bytes(in_dim, p_rows))
+        scratch_bytes >= mmq_deq_scratch_bytes(in_dim, p_rows)) {
+        // Small matrices and few rows: the GEMM's fixed cost (two launches, ring start-up, the drain) and
+        // its K steps of ~0.4 us each outlast a few 16-row passes of the batched matvec.  Both costs
+        // are modelled from measurements on B200: a 16-row matvec pass takes max(8 us, 0.95 us per
+        // million weights); the GEMM 7 us + 0.42 us per K=32 step and wave of tiles.
+        if (g_mmq_kind == 0) {
+            const uint32_t n_sub = in_dim >> 5;
+            const double t16 = fmax(8.0, 0.95e-6 * (double)in_dim * (double)out_dim);
+            const double t_mv = (double)((p_rows + 15u) / 16u) * t16;
+            const uint32_t bn = p_rows > 256u ? 512u : p_rows > 128u ? 256u : 128u;
+            const uint64_t tiles = (uint64_t)((out_dim + kBM - 1) / kBM) * ((p_rows + bn - 1u) / bn);
+            const double waves = (double)((tiles + (uint64_t)sm_count() - 1u) / (uint64_t)sm_count());
+            const double steps = (double)n_sub + ((type == Q4_K || type == Q5_K) ? (double)((n_sub + 31u) / 32u) : 0.0);
+            const double t_gemm = 7.0 + 0.42 * steps * waves;
+            if (t_mv < t_gemm) {
+                int rc = launch_quantize_q8(s, x, scratch, in_dim, p_rows);
+                if (rc) return rc;
+                for (uint32_t p0 = 0; p0 < p_rows; p0 += 16) {
+                    const uint32_t n = min(16u, p_rows - p0);
+                    rc = launch_matvec(s, type, w, (const uint8_t *)scratch + (size_t)p0 * n_sub * RC_BLOCKQ8_BYTES,
+                                       y + (size_t)p0 * out_dim, in_dim, out_dim, n, nullptr);
+                    if (rc) return rc;
+                }
+                return RC_OK;
+            }
+        }
         return launch_mmq_deq_f32(s, type, w, x, y, in_dim, out_dim, p_rows, scratch);
+    }
     const bool i8_kernel = !g_force_dp4a && g_mmq_kind != 16 && type != Q6_K;
     const bool planar = i8_kernel && !g_no_planar && ((uintptr_t)scratch & 15u) == 0 && p_rows <= 65535u &&
                         scratch_bytes >= quantize_planar_bytes(in_dim, p_rows);
