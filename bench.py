@@ -130,10 +130,28 @@ def moe_layer(rt, synth, torch, dev, timed):
         rt.launch_moe_scatter_rows(moe, y2, per_entry, H, NE)
         rt.launch_moe_combine(per_entry, ids, wts, None, out, H, K, NT)
 
+    # The same layer through the grouped GEMM that takes f32 activations (f16 operands, whole-K
+    # accumulation): the gather, the activation and both quantizations happen inside its prologue.
+    gg = rt.MoeGroupedGemm(device=dev)
+
+    def step_f32(i):
+        rt.launch_moe_topk(logits, ids, wts, E, K, NT)
+        rt.launch_moe_sort(moe, ids, NE)
+        gg.gate_up(moe, gu, x, K, y1, NE)
+        gg.down(moe, dn, y1, rt.ACT_SWIGLU, y2, NE)
+        rt.launch_moe_scatter_rows(moe, y2, per_entry, H, NE)
+        rt.launch_moe_combine(per_entry, ids, wts, None, out, H, K, NT)
+
     reps = 10
-    us = timed(step, reps, 3) / reps * 1e3
+    us_i8 = timed(step, reps, 3) / reps * 1e3
+    out_i8 = out.clone()
+    us_f32 = timed(step_f32, reps, 3) / reps * 1e3
+    rel = float((out - out_i8).norm() / out_i8.norm())
+    us = min(us_i8, us_f32)
     us_gu = timed(lambda i: rt.launch_moe_grouped_gemm(moe, gu, xg, y1, H, 2 * F, NE), reps, 3) / reps * 1e3
     us_dn = timed(lambda i: rt.launch_moe_grouped_gemm(moe, dn, hq, y2, F, H, NE), reps, 3) / reps * 1e3
+    us_gu32 = timed(lambda i: gg.gate_up(moe, gu, x, K, y1, NE), reps, 3) / reps * 1e3
+    us_dn32 = timed(lambda i: gg.down(moe, dn, y1, rt.ACT_SWIGLU, y2, NE), reps, 3) / reps * 1e3
     wbytes = gu.data.numel() + dn.data.numel()
     peak, _ = measured_peaks()
 
@@ -164,7 +182,8 @@ def moe_layer(rt, synth, torch, dev, timed):
     dec_bytes = (gu.bytes_per_expert + dn.bytes_per_expert) * K
     return {"workload": "config 5: 256 experts top-8, 512 tokens, hidden 2048, ffn 512 (548.9 MB of expert weights, 25.8 GOP)",
             "us_layer": us, "tok_per_s_per_layer": NT / (us * 1e-6), "tops": 2.0 * NE * (H * 2 * F + F * H) / us / 1e6,
-            "us_gate_up": us_gu, "us_down": us_dn,
+            "us_layer_blockq8_route": us_i8, "us_layer_f32_route": us_f32, "rel_l2_between_routes": rel,
+            "us_gate_up": us_gu, "us_down": us_dn, "us_gate_up_f32_route": us_gu32, "us_down_f32_route": us_dn32,
             "decode_1_token": {"us": us_dec, "expert_bytes": dec_bytes, "gbs": dec_bytes / us_dec / 1e3,
                                "frac_of_hbm_peak": dec_bytes / us_dec / 1e3 / peak,
                                "launches": "expert matvec (gate+up), SwiGLU+quantize, expert matvec (down)"},

@@ -251,6 +251,23 @@ int rc_add_rmsnorm_q8(void *stream, float *hidden, const float *add, const float
  * f32 (out may be NULL) and as BlockQ8 (q8 [n/32]); n % 32 == 0 (several vectors: pass their total). */
 int rc_swiglu_q8(void *stream, const float *gate, const float *up, float *out, void *q8, size_t n);
 
+/* The grouped GEMM taking f32 activations: what the sequence quantize_q8 -> moe_gather_xq ->
+ * rc_mmq_gemm_grouped (gate / up) and moe_geglu_q8 -> rc_mmq_gemm_grouped (down) computes, through the
+ * f16-operand tensor-core kernel of rc_matmul (same quantizer, operands rounded once to f16, whole-K
+ * accumulation: within 1e-3 relative L2 of the exact-integer route, about 3e-4).  Sorted entry j takes
+ * its activation row from x[(index ? index[j] / div : j) * row_stride ...]: for gate / up pass the
+ * sort's perm and div = n_used (token rows, row_stride = in_dim); for down pass the gate_up output in
+ * sorted order (index NULL, row_stride = 2 * in_dim) and act = RC_ACT_GEGLU / RC_ACT_SWIGLU, which
+ * applies act(gate) * up on the fly; act = -1 takes x as is.  y f32 [n_entries][out_dim] in sorted
+ * order.  scratch: 16-byte aligned, rc_mmq_gemm_grouped_scratch_bytes large.  No reference counterpart
+ * as one call (launch_moe_grouped_gemm takes BlockQ8: src/runtime/qwen35.rs:3036-3064). */
+size_t rc_mmq_gemm_grouped_scratch_bytes(uint32_t in_dim, uint32_t n_entries);
+int rc_mmq_gemm_grouped_f32(void *stream, int ggml_type, const void *slab, size_t bytes_per_expert,
+                            const int32_t *expert_off, const int32_t *tile_off, uint32_t n_expert,
+                            const float *x, const int32_t *index, uint32_t div, size_t row_stride, int act,
+                            float *y, uint32_t in_dim, uint32_t out_dim, uint32_t n_entries, void *scratch,
+                            size_t scratch_bytes);
+
 /* launch_moe_expert_matvec and launch_moe_down (src/runtime/qwen35.rs:3066-3139); kernels
  * moe_matvec_{q4k,q5k,q6k,q8_0}_repacked_f32 and moe_matvec_{q5k,q6k}_down_f32: the decode-side
  * routed-expert matvec.  For token t and routing slot j:

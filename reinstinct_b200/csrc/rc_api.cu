@@ -368,6 +368,30 @@ int rc_swiglu_q8(void *stream, const float *gate, const float *up, float *out, v
     return launch_swiglu_q8(S(stream), gate, up, out, q8, n);
 }
 
+size_t rc_mmq_gemm_grouped_scratch_bytes(uint32_t in_dim, uint32_t n_entries)
+{
+    return mmq_deq_grouped_scratch_bytes(in_dim, n_entries);
+}
+
+int rc_mmq_gemm_grouped_f32(void *stream, int type, const void *slab, size_t bytes_per_expert, const int32_t *expert_off,
+                            const int32_t *tile_off, uint32_t n_expert, const float *x, const int32_t *index, uint32_t div,
+                            size_t row_stride, int act, float *y, uint32_t in_dim, uint32_t out_dim, uint32_t n_entries,
+                            void *scratch, size_t scratch_bytes)
+{
+    if (n_entries == 0) return RC_OK;
+    int rc = check_weight_args(type, slab, scratch, y, in_dim, out_dim);
+    if (rc) return rc;
+    if (!x || !expert_off || !tile_off) return RC_ERR_NULL_POINTER;
+    if (n_expert == 0 || act < -1 || act > 1 || (index && div == 0) || row_stride < (size_t)in_dim * (act >= 0 ? 2u : 1u))
+        return RC_ERR_BAD_ARGUMENT;
+    if (((uintptr_t)scratch & 15u) || ((uintptr_t)x & 3u) || (n_expert > 1 && (bytes_per_expert & 15u))) return RC_ERR_MISALIGNED;
+    if (scratch_bytes < mmq_deq_grouped_scratch_bytes(in_dim, n_entries)) return RC_ERR_SCRATCH_TOO_SMALL;
+    rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_mmq_deq_grouped_f32(S(stream), type, slab, bytes_per_expert, expert_off, tile_off, n_expert, x, index, div,
+                                      row_stride, act, y, in_dim, out_dim, n_entries, scratch);
+}
+
 int rc_moe_expert_matvec(void *stream, int type, const void *slab, size_t bytes_per_expert, const int32_t *ids,
                          uint32_t n_expert, const void *xq, float *y, uint32_t in_dim, uint32_t out_dim, uint32_t n_used,
                          uint32_t n_tok, uint32_t xq_tok_stride, uint32_t xq_slot_stride)

@@ -44,6 +44,11 @@ int mmq_deq_set_attributes();
 void mmq_deq_set_bn(int bn);
 int mmq_deq_device_error(unsigned int *out);
 size_t mmq_deq_scratch_bytes(uint32_t in_dim, uint32_t n_tok);
+size_t mmq_deq_grouped_scratch_bytes(uint32_t in_dim, uint32_t n_entries);
+int launch_mmq_deq_grouped_f32(cudaStream_t s, int type, const void *slab, size_t bytes_per_expert, const int32_t *expert_off,
+                               const int32_t *tile_off, uint32_t n_expert, const float *x, const int32_t *index, uint32_t div,
+                               size_t row_stride, int act, float *y, uint32_t in_dim, uint32_t out_dim, uint32_t n_entries,
+                               void *scratch);
 int launch_mmq_deq_f32(cudaStream_t s, int type, const void *w, const float *x, float *y, uint32_t in_dim, uint32_t out_dim,
                        uint32_t n_tok, void *scratch);
 uint32_t mmq_grouped_bn();

@@ -27,6 +27,8 @@
 // leave room for two and four accumulator buffers).  Every wait is bounded (see rc_mmq.cu).
 #include <cuda.h>
 
+#include <algorithm>
+
 #include "rc_common.cuh"
 #include "rc_internal.h"
 #include "rc_tc.cuh"
@@ -123,6 +125,12 @@ struct DeqParams {
     const float *inv_scale; // per token
     float *y;
     uint32_t in_dim, out_dim, n_tok, tok_ld;
+    // expert-grouped form (expert_off != nullptr): rows of the image are expert-sorted entries, expert e
+    // owns entries expert_off[e]..expert_off[e+1] and token tiles tile_off[e]..tile_off[e+1], its weights
+    // are w + e * bytes_per_expert
+    size_t bytes_per_expert;
+    const int32_t *expert_off, *tile_off;
+    uint32_t n_expert;
     uint32_t debug; // measurement aid: pipeline parts to skip (results invalid): 1 expand, 2 activation copies, 4 MMAs, 8 raw loads; 128 records phase timestamps
 };
 
@@ -147,7 +155,37 @@ __device__ __forceinline__ __half2 h2_from_bits(uint32_t bits16)
     return u32_as_h2(b | (b << 16));
 }
 
-template <int FMT, int BN>
+struct DeqTile {
+    uint32_t m0, tok0, n_valid, e;
+};
+
+// Tile id -> weight-row tile, first token row of the image, valid tokens, expert.  Dense: ids walk the
+// row tiles of one token tile after another.  Grouped: the same with global token tiles of BN entries,
+// mapped to (expert, local tile) by binary search over tile_off (kernels/mmq_gemm_q4k_grouped.cpp:49-60).
+template <int BN, bool GR>
+__device__ __forceinline__ DeqTile deq_tile(const DeqParams &P, uint32_t id, uint32_t tiles_m)
+{
+    DeqTile t;
+    t.m0 = (id % tiles_m) * kBM;
+    const uint32_t gt = id / tiles_m;
+    if constexpr (!GR) {
+        t.e = 0;
+        t.tok0 = gt * BN;
+        t.n_valid = min((uint32_t)BN, P.n_tok - t.tok0);
+    } else {
+        uint32_t lo = 0, hi = P.n_expert;
+        while (lo + 1 < hi) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if ((uint32_t)P.tile_off[mid] <= gt) lo = mid; else hi = mid;
+        }
+        t.e = lo;
+        t.tok0 = (uint32_t)P.expert_off[lo] + (gt - (uint32_t)P.tile_off[lo]) * BN;
+        t.n_valid = min((uint32_t)BN, (uint32_t)P.expert_off[lo + 1] - t.tok0);
+    }
+    return t;
+}
+
+template <int FMT, int BN, bool GR>
 __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_constant__ CUtensorMap tmap, const DeqParams P)
 {
     using L = SmemD<FMT, BN>;
@@ -177,7 +215,7 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
     const uint32_t n_extra = T::has_min ? (n_sub + 31u) / 32u : 0u; // K=32 steps over the sub-block minima
     const uint32_t n_iters = n_sub + n_extra;
     const uint32_t tiles_m = (P.out_dim + kBM - 1) / kBM;
-    const uint32_t tiles_n = (P.n_tok + BN - 1) / BN;
+    const uint32_t tiles_n = GR ? (uint32_t)P.tile_off[P.n_expert] : (P.n_tok + BN - 1) / BN; // grouped: known on the device only
     const uint32_t n_tiles = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
@@ -214,8 +252,8 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
     // rank + n_ranks, ...; one inverse token scale per column.  Arrives on tm_empty when done.
     auto drain = [&](uint32_t id, uint32_t tile, uint32_t rank, uint32_t n_ranks) -> bool {
         const uint32_t quarter = warp & 3u; // tensor-memory lanes this warp may read
-        const uint32_t m0 = (id % tiles_m) * kBM, tok0 = (id / tiles_m) * BN;
-        const uint32_t n_valid = min((uint32_t)BN, P.n_tok - tok0);
+        const DeqTile tl = deq_tile<BN, GR>(P, id, tiles_m);
+        const uint32_t m0 = tl.m0, tok0 = tl.tok0, n_valid = tl.n_valid;
         const uint32_t buf = tile % NB;
         const uint32_t row = m0 + quarter * 32u + lane;
         if (!mbar_wait_d(tm_full(buf), (tile / NB) & 1u, abort_flag, 7u)) return false;
@@ -249,8 +287,9 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
         if (lane == 0) {
             uint32_t it = 0;
             for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x) {
-                const uint32_t tok0 = (id / tiles_m) * BN;
-                const uint32_t n_rows_b = min((uint32_t)BN, P.tok_ld - tok0); // tokens present in the image
+                const uint32_t tok0 = deq_tile<BN, GR>(P, id, tiles_m).tok0;
+                const uint32_t n_rows_b = min((uint32_t)BN, P.tok_ld - tok0); // rows present in the image (a grouped tile may
+                                                                              // take the next expert's first rows along: unused columns)
                 for (uint32_t i = 0; i < n_iters; i++, it++) {
                     const uint32_t s = it % S;
                     if (it >= S && !mbar_spin_d(op_empty(s), ((it / S) - 1u) & 1u, abort_flag, 2u)) goto prod_done;
@@ -273,7 +312,8 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
         if (lane == 0) {
             uint32_t it = 0;
             for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x) {
-                const uint32_t m0 = (id % tiles_m) * kBM;
+                const DeqTile tl = deq_tile<BN, GR>(P, id, tiles_m);
+                const uint32_t m0 = tl.m0;
                 for (uint32_t i = 0; i < n_iters; i++, it++) {
                     const uint32_t s = it % R;
                     if (it >= R && !mbar_spin_d(raw_empty(s), ((it / R) - 1u) & 1u, abort_flag, 1u)) goto raw_done;
@@ -281,7 +321,7 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
                         mbar_expect_tx(raw_full(s), T::raw_bytes);
                         for (int pl = 0; pl < T::raw_planes; pl++)
                             tma_load_4d(sbase + L::raw_off + s * L::raw_stage + pl * kBM * 16, &tmap, raw_full(s),
-                                        (int)(i * 16u), (int)m0, pl, 0);
+                                        (int)(i * 16u), (int)m0, pl, (int)tl.e);
                     } else {
                         mbar_arrive(raw_full(s)); // nothing raw in a minima step; keeps the ring in phase
                     }
@@ -336,11 +376,12 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
         // of the group's steps early, into three fixed register slots used in turn.
         constexpr uint32_t G = kExpGroups;
         const uint32_t grp = (warp - kLeadWarps) >> 2, r = (threadIdx.x - kLeadWarps * 32u) & 127u;
-        const Planes pl = planes_of<FMT>(P.w, P.in_dim, P.out_dim);
         struct Side { uint32_t e0, e1, smw, ddw; };
         uint32_t tile_it0 = 0; // global step number of the tile's first step
         for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x, tile_it0 += n_iters) {
-            const uint32_t row = min((id % tiles_m) * kBM + r, P.out_dim - 1u);
+            const DeqTile tl = deq_tile<BN, GR>(P, id, tiles_m);
+            const Planes pl = planes_of<FMT>(P.w + (size_t)tl.e * P.bytes_per_expert, P.in_dim, P.out_dim);
+            const uint32_t row = min(tl.m0 + r, P.out_dim - 1u);
             const uint8_t *scp = pl.sc + (size_t)row * pl.nsp * 2u;
             const uint8_t *auxp = (FMT == Q5_K || FMT == Q6_K) ? pl.aux + (size_t)row * pl.nsp * (FMT == Q6_K ? 8u : 4u) : nullptr;
             const uint8_t *supp = T::sup_scale ? pl.sup + (size_t)row * pl.n_super * (FMT == Q6_K ? 2u : 4u) : nullptr;
@@ -466,7 +507,32 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
 // the image.  Tokens n_tok..tok_ld-1 are written as zeros.
 constexpr int kActTokens = 8, kActWarps = 32;
 
-__global__ void __launch_bounds__(kActWarps * 32) activations_to_f16_kernel(const float *__restrict__ x, uint8_t *__restrict__ out,
+// Where row t of the image comes from: row (index ? index[t] / div : t) of x, rows row_stride floats
+// apart; with act >= 0 a source row is [gate | up] of 2 * in_dim floats and the value is
+// act(gate) * up (0: tanh GELU, 1: SiLU; kernels/moe_geglu_q8.cpp:20-32, kernels/swiglu.cpp:11-21).
+struct ActSource {
+    const float *x;
+    const int32_t *index;
+    uint32_t div;
+    size_t row_stride;
+    int act;
+};
+
+__device__ __forceinline__ float act_value(const float *row, uint32_t i, uint32_t in_dim, int act)
+{
+    if (act < 0) return row[i];
+    const float g = row[i], u = row[in_dim + i];
+    float a;
+    if (act == 0) {
+        const float c = g + 0.044715f * g * g * g;
+        a = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * c));
+    } else {
+        a = g / (1.0f + expf(-g));
+    }
+    return __fmul_rn(a, u);
+}
+
+__global__ void __launch_bounds__(kActWarps * 32) activations_to_f16_kernel(const ActSource src, uint8_t *__restrict__ out,
                                                                              uint32_t in_dim, uint32_t n_tok, uint32_t tok_ld,
                                                                              uint32_t n_xchunks)
 {
@@ -484,9 +550,12 @@ __global__ void __launch_bounds__(kActWarps * 32) activations_to_f16_kernel(cons
         const uint32_t t = warp >> 2, qk = warp & 3u, tok = tok0 + t;
         float amax = 0.0f;
         if (tok < n_tok) {
-            const float *row = x + (size_t)tok * in_dim;
+            const float *row = src.x + (size_t)(src.index ? (uint32_t)src.index[tok] / src.div : tok) * src.row_stride;
             const uint32_t per = in_dim / 4u, lo = qk * per, hi = lo + per; // in_dim is a multiple of 32
-            if ((reinterpret_cast<uintptr_t>(row) & 15u) == 0) {
+            if (src.act >= 0) {
+#pragma unroll 4
+                for (uint32_t i = lo + lane; i < hi; i += 32u) amax = fmaxf(amax, fabsf(act_value(row, i, in_dim, src.act)));
+            } else if ((reinterpret_cast<uintptr_t>(row) & 15u) == 0) {
                 const float4 *r4 = reinterpret_cast<const float4 *>(row);
 #pragma unroll 4
                 for (uint32_t i = lo / 4u + lane; i < hi / 4u; i += 32u) {
@@ -518,12 +587,18 @@ __global__ void __launch_bounds__(kActWarps * 32) activations_to_f16_kernel(cons
     // pass 2: sub-blocks warp + 32 * (blockIdx.y + gridDim.y * k)
     const uint32_t tl = lane >> 2, pair = lane & 3u; // store role: token tl, halves 2*pair, 2*pair + 1 of a chunk
     const float s_mine = s_scale[lane & 7u];         // lane t < 8 also does token t's divides and xsum
+    const float *rows[kActTokens];
+#pragma unroll
+    for (int t = 0; t < kActTokens; t++) {
+        const uint32_t tok = min(tok0 + t, n_tok - 1u);
+        rows[t] = src.x + (size_t)(src.index ? (uint32_t)src.index[tok] / src.div : tok) * src.row_stride;
+    }
     for (uint32_t sb = warp + 32u * blockIdx.y; sb < n_sub; sb += 32u * gridDim.y) {
         float v[kActTokens], sum[kActTokens];
         uint32_t bmax[kActTokens]; // |v| as bits: non-negative floats order like unsigned integers
 #pragma unroll
         for (int t = 0; t < kActTokens; t++) {
-            v[t] = (tok0 + t < n_tok) ? x[(size_t)(tok0 + t) * in_dim + (size_t)sb * 32u + lane] : 0.0f;
+            v[t] = (tok0 + t < n_tok) ? act_value(rows[t], sb * 32u + lane, in_dim, src.act) : 0.0f;
             const float a = fabsf(v[t]);
             bmax[t] = __reduce_max_sync(0xFFFFFFFFu, a == a ? __float_as_uint(a) : 0u); // fmaxf skips a NaN: so does this
             sum[t] = v[t];
@@ -588,7 +663,22 @@ int launch_deq(cudaStream_t s, const DeqParams &P)
     if (rc) return rc;
     const uint32_t tiles = ((P.out_dim + kBM - 1) / kBM) * ((P.n_tok + BN - 1) / BN);
     const uint32_t grid = min(tiles, (uint32_t)sm_count());
-    return (int)launch_pdl(mmqd_kernel<FMT, BN>, dim3(grid), dim3(kDeqThreads), SmemD<FMT, BN>::total, s, map, P);
+    return (int)launch_pdl(mmqd_kernel<FMT, BN, false>, dim3(grid), dim3(kDeqThreads), SmemD<FMT, BN>::total, s, map, P);
+}
+
+constexpr int kGroupedDeqBN = 32; // the expert tile of rc_moe_sort
+
+template <int FMT>
+int launch_deq_grouped(cudaStream_t s, const DeqParams &P)
+{
+    CUtensorMap map;
+    int rc = make_tmap<FMT>(&map, P.w, P.bytes_per_expert, P.n_expert, P.in_dim, P.out_dim);
+    if (rc) return rc;
+    // the tile count lives on the device (tile_off[n_expert]); this is its upper bound
+    const uint64_t tiles = (uint64_t)((P.out_dim + kBM - 1) / kBM) * ((P.n_tok + kGroupedDeqBN - 1) / kGroupedDeqBN + P.n_expert);
+    const uint32_t grid = (uint32_t)std::min<uint64_t>(tiles, (uint64_t)sm_count());
+    return (int)launch_pdl(mmqd_kernel<FMT, kGroupedDeqBN, true>, dim3(grid), dim3(kDeqThreads), SmemD<FMT, kGroupedDeqBN>::total, s,
+                           map, P);
 }
 
 template <int FMT>
@@ -601,9 +691,11 @@ int launch_deq_bn(cudaStream_t s, const DeqParams &P, uint32_t bn)
 
 template <int FMT> int set_attr_deq()
 {
-    int rc = (int)cudaFuncSetAttribute(mmqd_kernel<FMT, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemD<FMT, 512>::total);
-    rc |= (int)cudaFuncSetAttribute(mmqd_kernel<FMT, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemD<FMT, 256>::total);
-    rc |= (int)cudaFuncSetAttribute(mmqd_kernel<FMT, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemD<FMT, 128>::total);
+    int rc = (int)cudaFuncSetAttribute(mmqd_kernel<FMT, 512, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemD<FMT, 512>::total);
+    rc |= (int)cudaFuncSetAttribute(mmqd_kernel<FMT, 256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemD<FMT, 256>::total);
+    rc |= (int)cudaFuncSetAttribute(mmqd_kernel<FMT, 128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemD<FMT, 128>::total);
+    rc |= (int)cudaFuncSetAttribute(mmqd_kernel<FMT, kGroupedDeqBN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)SmemD<FMT, kGroupedDeqBN>::total);
     return rc;
 }
 
@@ -648,10 +740,14 @@ int launch_mmq_deq_f32(cudaStream_t s, int type, const void *w, const float *x, 
     const uint32_t ld = tok_ld_of(n_tok), n_xc = xchunks_of(in_dim);
     // 8 tokens per CTA; a second CTA shares their sub-blocks while that still adds SMs
     const uint32_t groups = ld / kActTokens, ysplit = groups * 2u <= (uint32_t)sm_count() ? 2u : 1u;
-    cudaError_t e = launch_pdl(activations_to_f16_kernel, dim3(groups, ysplit), dim3(kActWarps * 32), 0, s, x, (uint8_t *)scratch, in_dim,
+    const ActSource src = {x, nullptr, 1u, (size_t)in_dim, -1};
+    cudaError_t e = launch_pdl(activations_to_f16_kernel, dim3(groups, ysplit), dim3(kActWarps * 32), 0, s, src, (uint8_t *)scratch, in_dim,
                                n_tok, ld, n_xc);
     if (e != cudaSuccess) return (int)e;
     DeqParams P;
+    P.bytes_per_expert = 0;
+    P.expert_off = P.tile_off = nullptr;
+    P.n_expert = 1;
     P.w = (const uint8_t *)w;
     P.xh = (const uint8_t *)scratch;
     P.inv_scale = reinterpret_cast<const float *>((const uint8_t *)scratch + ((size_t)(in_dim >> 3) + n_xc) * ld * 16u);
@@ -672,6 +768,55 @@ int launch_mmq_deq_f32(cudaStream_t s, int type, const void *w, const float *x, 
     case Q5_K: return launch_deq_bn<Q5_K>(s, P, bn);
     case Q6_K: return launch_deq_bn<Q6_K>(s, P, bn);
     case IQ4_XS: return launch_deq_bn<IQ4_XS>(s, P, bn);
+    }
+    return RC_ERR_BAD_TYPE;
+}
+
+// ---- expert-grouped form -----------------------------------------------------------------------------
+// Image rows = expert-sorted entries (plus one tile of zero rows, so a tile's copy never leaves the image).
+static uint32_t grouped_ld(uint32_t n_entries) { return tok_ld_of(n_entries) + kGroupedDeqBN; }
+
+size_t mmq_deq_grouped_scratch_bytes(uint32_t in_dim, uint32_t n_entries)
+{
+    const size_t ld = grouped_ld(n_entries);
+    return ((size_t)(in_dim >> 3) + xchunks_of(in_dim)) * ld * 16u + ld * sizeof(float);
+}
+
+// Entry j of the sorted order takes its activations from row (index ? index[j] / div : j) of x (rows
+// row_stride floats apart; act >= 0: rows are [gate | up] and the value is act(gate) * up).
+// y f32 [n_entries][out_dim] in sorted order.
+int launch_mmq_deq_grouped_f32(cudaStream_t s, int type, const void *slab, size_t bytes_per_expert, const int32_t *expert_off,
+                               const int32_t *tile_off, uint32_t n_expert, const float *x, const int32_t *index, uint32_t div,
+                               size_t row_stride, int act, float *y, uint32_t in_dim, uint32_t out_dim, uint32_t n_entries,
+                               void *scratch)
+{
+    const uint32_t ld = grouped_ld(n_entries), n_xc = xchunks_of(in_dim);
+    const uint32_t groups = ld / kActTokens, ysplit = groups * 2u <= (uint32_t)sm_count() ? 2u : 1u;
+    const ActSource src = {x, index, div ? div : 1u, row_stride, act};
+    cudaError_t e = launch_pdl(activations_to_f16_kernel, dim3(groups, ysplit), dim3(kActWarps * 32), 0, s, src, (uint8_t *)scratch, in_dim,
+                               n_entries, ld, n_xc);
+    if (e != cudaSuccess) return (int)e;
+    DeqParams P;
+    P.w = (const uint8_t *)slab;
+    P.xh = (const uint8_t *)scratch;
+    P.inv_scale = reinterpret_cast<const float *>((const uint8_t *)scratch + ((size_t)(in_dim >> 3) + n_xc) * ld * 16u);
+    P.y = y;
+    P.in_dim = in_dim;
+    P.out_dim = out_dim;
+    P.n_tok = n_entries;
+    P.tok_ld = ld;
+    P.bytes_per_expert = bytes_per_expert;
+    P.expert_off = expert_off;
+    P.tile_off = tile_off;
+    P.n_expert = n_expert;
+    P.debug = (uint32_t)g_deq_debug;
+    switch (type) {
+    case Q4_0: return launch_deq_grouped<Q4_0>(s, P);
+    case Q8_0: return launch_deq_grouped<Q8_0>(s, P);
+    case Q4_K: return launch_deq_grouped<Q4_K>(s, P);
+    case Q5_K: return launch_deq_grouped<Q5_K>(s, P);
+    case Q6_K: return launch_deq_grouped<Q6_K>(s, P);
+    case IQ4_XS: return launch_deq_grouped<IQ4_XS>(s, P);
     }
     return RC_ERR_BAD_TYPE;
 }

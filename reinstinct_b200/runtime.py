@@ -22,7 +22,7 @@ __all__ = [
     "launch_quantize_q8", "launch_matvec", "launch_matvec_xq8", "launch_matvec_batched",
     "matvec_block_dots", "launch_mmq_gemm", "launch_moe_sort", "launch_moe_gather_xq",
     "launch_moe_grouped_gemm", "launch_moe_scatter_rows", "repacked_len", "init", "PeerAllGather",
-    "launch_rmsnorm_q8", "launch_add_rmsnorm_q8", "launch_swiglu_q8",
+    "MoeGroupedGemm", "launch_rmsnorm_q8", "launch_add_rmsnorm_q8", "launch_swiglu_q8",
     "launch_moe_expert_matvec", "launch_moe_topk", "launch_moe_act_q8", "launch_moe_combine", "ACT_GEGLU", "ACT_SWIGLU",
 ]
 
@@ -259,6 +259,35 @@ def launch_moe_grouped_gemm(moe: MoeGroupedScratch, et: GpuExpertTensor, xq: tor
                                           _ptr(moe.expert_off), _ptr(moe.tile_off), moe.n_expert,
                                           _ptr(xq), _ptr(y), in_dim, out_dim, n_entries),
           "rc_mmq_gemm_grouped")
+
+
+class MoeGroupedGemm:
+    """The grouped GEMM from f32 activations (rc_mmq_gemm_grouped_f32), owning its scratch like
+    PrefillGemm owns its own.  `gate_up` gathers token rows through the sort's perm; `down` applies
+    the gated activation to the gate_up output on the fly."""
+
+    def __init__(self, device: torch.device | str = "cuda"):
+        self.device = torch.device(device)
+        self.scratch = torch.empty(16, dtype=torch.uint8, device=self.device)
+
+    def _grow(self, n_bytes: int) -> None:
+        if self.scratch.numel() < n_bytes:
+            torch.cuda.current_stream().synchronize()
+            self.scratch = torch.empty(n_bytes, dtype=torch.uint8, device=self.device)
+
+    def _run(self, moe: "MoeGroupedScratch", et: GpuExpertTensor, x, index, div, row_stride, act, y, n_entries) -> None:
+        lib = _lib.load()
+        self._grow(lib.rc_mmq_gemm_grouped_scratch_bytes(et.in_dim, n_entries))
+        check(lib.rc_mmq_gemm_grouped_f32(_stream(), et.dtype, _ptr(et.data), et.bytes_per_expert, _ptr(moe.expert_off),
+                                          _ptr(moe.tile_off), moe.n_expert, _ptr(x), _ptr(index), div, row_stride, act,
+                                          _ptr(y), et.in_dim, et.out_dim, n_entries, _ptr(self.scratch), self.scratch.numel()),
+              "rc_mmq_gemm_grouped_f32")
+
+    def gate_up(self, moe, et: GpuExpertTensor, x_tokens: torch.Tensor, n_used: int, y_sorted: torch.Tensor, n_entries: int) -> None:
+        self._run(moe, et, x_tokens, moe.perm, n_used, et.in_dim, -1, y_sorted, n_entries)
+
+    def down(self, moe, et: GpuExpertTensor, gate_up_sorted: torch.Tensor, act: int, y_sorted: torch.Tensor, n_entries: int) -> None:
+        self._run(moe, et, gate_up_sorted, None, 1, 2 * et.in_dim, act, y_sorted, n_entries)
 
 
 def launch_rmsnorm_q8(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n: int, n_vec: int, eps: float) -> None:
