@@ -80,3 +80,91 @@ def test_peer_gather_row_sharded_matvec_two_gpus():
     for p in procs:
         p.join(timeout=60)
     assert all(msg == "ok" for _, msg in results), results
+
+
+def _moe_worker(rank: int, world: int, port: int, q):
+    """Expert parallelism over two GPUs: rank g owns half of the experts, every rank routes its own
+    tokens; routed activation rows travel to the owning rank by all-to-all (counts first), go through
+    the grouped GEMM there and travel back.  Must equal the same layer computed with all experts on
+    one GPU, bit for bit (same kernel, per-entry arithmetic independent of the tile an entry lands in)."""
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    for p in (str(root), str(root / "tests")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import torch.distributed as dist
+
+    import cases
+    import oracle as ro
+    from reinstinct_b200 import runtime as rt
+    from reinstinct_b200 import sharding as sh
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        rt.init(rank)
+        t, hidden, out_dim, n_expert, n_used, n_tok = ro.Q4_K, 512, 256, 8, 2, 24
+        raws = [cases.synth_case(t, hidden, out_dim, 1, seed=300 + e)[0] for e in range(n_expert)]
+        e0, e1 = sh.expert_range(n_expert, rank, world)
+        et_local = rt.GpuExpertTensor.from_bytes(np.concatenate(raws[e0:e1]), t, hidden, out_dim, e1 - e0)
+        et_all = rt.GpuExpertTensor.from_bytes(np.concatenate(raws), t, hidden, out_dim, n_expert)
+        rng = np.random.default_rng(40 + rank)          # every rank has its own tokens
+        x = torch.from_numpy(rng.standard_normal((n_tok, hidden)).astype(np.float32)).cuda()
+        logits = torch.from_numpy(rng.standard_normal((n_tok, n_expert)).astype(np.float32)).cuda()
+        ids = torch.empty(n_tok, n_used, dtype=torch.int32, device="cuda")
+        wts = torch.empty(n_tok, n_used, device="cuda")
+        rt.launch_moe_topk(logits, ids, wts, n_expert, n_used, n_tok)
+        n_ent = n_tok * n_used
+        gg = rt.MoeGroupedGemm()
+
+        # one GPU, all experts: sorted GEMM, rows scattered back to entry order
+        moe = rt.MoeGroupedScratch.new(n_expert, n_ent)
+        rt.launch_moe_sort(moe, ids, n_ent)
+        y_sorted = torch.empty(n_ent, out_dim, device="cuda")
+        gg.gate_up(moe, et_all, x, n_used, y_sorted, n_ent)
+        want = torch.empty(n_ent, out_dim, device="cuda")
+        rt.launch_moe_scatter_rows(moe, y_sorted, want, out_dim, n_ent)
+        torch.cuda.synchronize()
+
+        # expert-parallel: entries (token row, expert id) go to the owner of the expert
+        flat_ids = ids.reshape(-1)
+        plan = sh.plan_dispatch(flat_ids, n_expert)
+        rows = x.repeat_interleave(n_used, dim=0).contiguous()            # one row per entry
+        rows_in = sh.dispatch_rows(rows, plan)
+        ids_in = sh.dispatch_rows(flat_ids.to(torch.float32).reshape(-1, 1), plan).reshape(-1).to(torch.int32) - e0
+        n_in = rows_in.shape[0]
+        assert int(ids_in.min()) >= 0 and int(ids_in.max()) < e1 - e0
+        moe_l = rt.MoeGroupedScratch.new(e1 - e0, n_in)
+        rt.launch_moe_sort(moe_l, ids_in.contiguous(), n_in)
+        y_l = torch.empty(n_in, out_dim, device="cuda")
+        gg.gate_up(moe_l, et_local, rows_in, 1, y_l, n_in)                 # perm indexes the received rows
+        y_in = torch.empty(n_in, out_dim, device="cuda")
+        rt.launch_moe_scatter_rows(moe_l, y_l, y_in, out_dim, n_in)
+        torch.cuda.synchronize()
+        got = sh.combine_rows(y_in, plan)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), f"expert-parallel result differs: rel {float((got - want).norm() / want.norm()):.3e}"
+        q.put((rank, "ok"))
+    except Exception as e:  # report instead of leaving the peer waiting
+        q.put((rank, f"{type(e).__name__}: {e}"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_expert_parallel_grouped_gemm_two_gpus():
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_moe_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(msg == "ok" for _, msg in results), results
