@@ -268,6 +268,16 @@ int rc_mmq_gemm_grouped_f32(void *stream, int ggml_type, const void *slab, size_
                             float *y, uint32_t in_dim, uint32_t out_dim, uint32_t n_entries, void *scratch,
                             size_t scratch_bytes);
 
+/* kernel sigmoid_mul_q8_f32 (kernels/qwen35_fused.cpp:139-152): x[i] = x[i] * sigmoid(gate[i]) in place
+ * and as BlockQ8; n % 32 == 0. */
+int rc_sigmoid_mul_q8(void *stream, float *x, const float *gate, void *q8, size_t n);
+
+/* kernel rmsnorm_gated_q8_f32 (kernels/qwen35_fused.cpp:204-224): per head h of head_dim values
+ * y = rmsnorm(x_h) * w * silu(z_h) as f32 (y may be NULL) and as BlockQ8; w has head_dim entries shared
+ * by the heads.  head_dim % 32 == 0, head_dim <= 1024. */
+int rc_rmsnorm_gated_q8(void *stream, const float *x, const float *z, const float *w, float *y, void *q8,
+                        uint32_t n_heads, uint32_t head_dim, float eps);
+
 /* launch_moe_expert_matvec and launch_moe_down (src/runtime/qwen35.rs:3066-3139); kernels
  * moe_matvec_{q4k,q5k,q6k,q8_0}_repacked_f32 and moe_matvec_{q5k,q6k}_down_f32: the decode-side
  * routed-expert matvec.  For token t and routing slot j:

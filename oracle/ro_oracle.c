@@ -992,3 +992,47 @@ void ro_swiglu_q8(const float *gate, const float *up, float *out_f32, uint8_t *q
     ro_quantize_q8(v, q8, n, 1);
     free(v);
 }
+
+/* kernels/qwen35_fused.cpp:139-152: x *= sigmoid(gate), in place and as BlockQ8. */
+void ro_sigmoid_mul_q8(float *x, const float *gate, uint8_t *q8, size_t n)
+{
+    for (size_t i = 0; i < n; i++) {
+        float e = 1.0f + expf(-gate[i]);
+        x[i] = x[i] / e;
+    }
+    ro_quantize_q8(x, q8, n, 1);
+}
+
+/* kernels/qwen35_fused.cpp:204-224: per head y = ((x * rrms) * w) * silu(z); the head's sum of squares
+ * by xor-butterfly per 32 values, the group sums added in order (the CUDA kernel's order). */
+void ro_rmsnorm_gated_q8(const float *x, const float *z, const float *w, float *y, uint8_t *q8,
+                         size_t n_heads, size_t head_dim, float eps)
+{
+    float *v = (float *)malloc(sizeof(float) * n_heads * head_dim);
+    for (size_t h = 0; h < n_heads; h++) {
+        const float *xh = x + h * head_dim, *zh = z + h * head_dim;
+        float tot = 0.0f;
+        for (size_t g = 0; g < head_dim / 32; g++) {
+            float s[32];
+            for (int l = 0; l < 32; l++) s[l] = xh[g * 32 + l] * xh[g * 32 + l];
+            for (int off = 16; off > 0; off >>= 1) {
+                float ns[32];
+                for (int l = 0; l < 32; l++) ns[l] = s[l] + s[l ^ off];
+                memcpy(s, ns, sizeof s);
+            }
+            tot = g == 0 ? s[0] : tot + s[0];
+        }
+        float mean = tot / (float)head_dim;
+        float rrms = 1.0f / sqrtf(mean + eps);
+        for (size_t i = 0; i < head_dim; i++) {
+            float e = 1.0f + expf(-zh[i]);
+            float silu = zh[i] / e;
+            float a = xh[i] * rrms;
+            float b = a * w[i];
+            v[h * head_dim + i] = b * silu;
+        }
+    }
+    if (y) memcpy(y, v, sizeof(float) * n_heads * head_dim);
+    ro_quantize_q8(v, q8, n_heads * head_dim, 1);
+    free(v);
+}

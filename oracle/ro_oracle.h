@@ -110,6 +110,10 @@ void ro_router_topk(const float *logits, size_t n_tok, size_t n_expert, size_t n
 void ro_rmsnorm_q8(const float *x, const float *add, const float *w, float *hidden_out, float *y_out,
                    uint8_t *out, size_t n, size_t n_vec, float eps);
 void ro_swiglu_q8(const float *gate, const float *up, float *out_f32, uint8_t *q8, size_t n);
+/* kernels/qwen35_fused.cpp:139-152 and :204-224 */
+void ro_sigmoid_mul_q8(float *x, const float *gate, uint8_t *q8, size_t n);
+void ro_rmsnorm_gated_q8(const float *x, const float *z, const float *w, float *y, uint8_t *q8,
+                         size_t n_heads, size_t head_dim, float eps);
 
 /* Relabelled source formats (src/runtime/qwen35.rs:274-307): decoders of the source blocks
  * (src/quant/q3_k.rs:123-162, iq4_nl.rs:32-46), the exact Q3_K -> Q6_K block transcode

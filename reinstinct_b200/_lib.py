@@ -57,6 +57,8 @@ _SIGNATURES = {
     "rc_mmq_gemm_grouped": (_i, [_vp, _i, _vp, _sz, _vp, _vp, _u32, _vp, _vp, _u32, _u32, _u32]),
     "rc_rmsnorm_q8": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, C.c_float]),
     "rc_add_rmsnorm_q8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, C.c_float]),
+    "rc_sigmoid_mul_q8": (_i, [_vp, _vp, _vp, _vp, _sz]),
+    "rc_rmsnorm_gated_q8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, C.c_float]),
     "rc_swiglu_q8": (_i, [_vp, _vp, _vp, _vp, _vp, _sz]),
     "rc_kernel_type": (_i, [_i]),
     "rc_debug_read_trace": (_i, [_vp, C.c_size_t]),

@@ -357,6 +357,30 @@ int rc_rmsnorm_q8(void *stream, const float *x, const float *w, void *out, uint3
     return launch_rmsnorm_q8(S(stream), x, nullptr, w, nullptr, nullptr, out, n, n_vec, eps);
 }
 
+int rc_sigmoid_mul_q8(void *stream, float *x, const float *gate, void *q8, size_t n)
+{
+    if (n % 32) return RC_ERR_BAD_SHAPE;
+    if (n == 0) return RC_OK;
+    if (!x || !gate || !q8) return RC_ERR_NULL_POINTER;
+    if (((uintptr_t)x & 3u) || ((uintptr_t)gate & 3u) || ((uintptr_t)q8 & 7u)) return RC_ERR_MISALIGNED;
+    int rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_sigmoid_mul_q8(S(stream), x, gate, q8, n);
+}
+
+int rc_rmsnorm_gated_q8(void *stream, const float *x, const float *z, const float *w, float *y, void *q8, uint32_t n_heads,
+                        uint32_t head_dim, float eps)
+{
+    if (head_dim == 0 || head_dim % 32 || head_dim > 1024) return RC_ERR_BAD_SHAPE;
+    if (n_heads == 0) return RC_OK;
+    if (!x || !z || !w || !q8) return RC_ERR_NULL_POINTER;
+    if (((uintptr_t)x & 3u) || ((uintptr_t)z & 3u) || ((uintptr_t)w & 3u) || ((uintptr_t)y & 3u) || ((uintptr_t)q8 & 7u))
+        return RC_ERR_MISALIGNED;
+    int rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_rmsnorm_gated_q8(S(stream), x, z, w, y, q8, n_heads, head_dim, eps);
+}
+
 int rc_swiglu_q8(void *stream, const float *gate, const float *up, float *out, void *q8, size_t n)
 {
     if (n % 32) return RC_ERR_BAD_SHAPE;

@@ -3,6 +3,8 @@
 //   rmsnorm_q8       kernels/rmsnorm_q8.cpp:38-103        y = x * rsqrt(mean(x^2) + eps) * w -> BlockQ8
 //   add_rmsnorm_q8   kernels/qwen35_fused.cpp:66-118      hidden += add, then the same (also writes y)
 //   swiglu_q8        kernels/qwen35_fused.cpp:123-138     silu(gate) * up -> f32 and BlockQ8
+//   sigmoid_mul_q8   kernels/qwen35_fused.cpp:139-152     x *= sigmoid(gate) -> f32 (in place) and BlockQ8
+//   rmsnorm_gated_q8 kernels/qwen35_fused.cpp:204-224     per head: rmsnorm(x) * w * silu(z) -> f32 and BlockQ8
 // The quantizer is quantize_q8_kernel's (same butterfly order, IEEE divides).  The sum of squares is
 // reduced in one fixed order, restated by the oracle: thread t of 1024 adds the squares of elements
 // t, t + 1024, ... in turn; a warp reduces by xor-butterfly 16, 8, 4, 2, 1; the 32 warp sums are added
@@ -94,7 +96,63 @@ __global__ void __launch_bounds__(256) swiglu_q8_kernel(const float *__restrict_
     q8_store_block(q8 + (i >> 5) * RC_BLOCKQ8_BYTES, threadIdx.x & 31u, v);
 }
 
+__global__ void __launch_bounds__(256) sigmoid_mul_q8_kernel(float *__restrict__ x, const float *__restrict__ gate,
+                                                              uint8_t *__restrict__ q8, uint32_t n)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = __fdiv_rn(x[i], __fadd_rn(1.0f, expf(-gate[i])));
+    x[i] = v;
+    q8_store_block(q8 + (i >> 5) * RC_BLOCKQ8_BYTES, threadIdx.x & 31u, v);
+}
+
+// One CTA of head_dim threads per head (head_dim a multiple of 32, at most 1024).  The head's sum of
+// squares: xor-butterfly per warp, the warp sums added in warp order.
+__global__ void __launch_bounds__(1024) rmsnorm_gated_q8_kernel(const float *__restrict__ x, const float *__restrict__ z,
+                                                                  const float *__restrict__ w, float *__restrict__ y,
+                                                                  uint8_t *__restrict__ q8, uint32_t head_dim, float eps)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float s_warp[32];
+    __shared__ float s_rrms;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, n_warps = head_dim >> 5;
+    const size_t i = (size_t)blockIdx.x * head_dim + tid;
+    const float xv = x[i];
+    float part = __fmul_rn(xv, xv);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xFFFFFFFFu, part, o));
+    if (lane == 0) s_warp[warp] = part;
+    __syncthreads();
+    if (tid == 0) {
+        float tot = s_warp[0];
+        for (uint32_t k = 1; k < n_warps; k++) tot = __fadd_rn(tot, s_warp[k]);
+        s_rrms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)head_dim), eps)));
+    }
+    __syncthreads();
+    const float zg = z[i];
+    const float silu = __fdiv_rn(zg, __fadd_rn(1.0f, expf(-zg)));
+    const float v = __fmul_rn(__fmul_rn(__fmul_rn(xv, s_rrms), w[tid]), silu);
+    if (y) y[i] = v;
+    q8_store_block(q8 + (i >> 5) * RC_BLOCKQ8_BYTES, lane, v);
+}
+
 } // namespace
+
+int launch_sigmoid_mul_q8(cudaStream_t s, float *x, const float *gate, void *q8, size_t n)
+{
+    const size_t blocks = (n + 255) / 256;
+    if (blocks > 0x7FFFFFFFull) return RC_ERR_BAD_SHAPE;
+    return (int)launch_pdl(sigmoid_mul_q8_kernel, dim3((uint32_t)blocks), dim3(256), 0, s, x, gate, (uint8_t *)q8, (uint32_t)n);
+}
+
+int launch_rmsnorm_gated_q8(cudaStream_t s, const float *x, const float *z, const float *w, float *y, void *q8, uint32_t n_heads,
+                            uint32_t head_dim, float eps)
+{
+    return (int)launch_pdl(rmsnorm_gated_q8_kernel, dim3(n_heads), dim3(head_dim), 0, s, x, z, w, y, (uint8_t *)q8, head_dim, eps);
+}
 
 int launch_rmsnorm_q8(cudaStream_t s, const float *x, const float *add, const float *w, float *hidden_io, float *y, void *out,
                       uint32_t n, uint32_t n_vec, float eps)

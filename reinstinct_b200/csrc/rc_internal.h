@@ -71,6 +71,9 @@ int gather_device_error(unsigned int *out);
 
 int launch_rmsnorm_q8(cudaStream_t s, const float *x, const float *add, const float *w, float *hidden_io, float *y, void *out,
                       uint32_t n, uint32_t n_vec, float eps);
+int launch_sigmoid_mul_q8(cudaStream_t s, float *x, const float *gate, void *q8, size_t n);
+int launch_rmsnorm_gated_q8(cudaStream_t s, const float *x, const float *z, const float *w, float *y, void *q8, uint32_t n_heads,
+                            uint32_t head_dim, float eps);
 int launch_swiglu_q8(cudaStream_t s, const float *gate, const float *up, float *out, void *q8, size_t n);
 int launch_moe_expert_matvec(cudaStream_t s, int type, const void *slab, size_t bpe, const int32_t *ids, uint32_t n_expert,
                              const void *xq, float *y, uint32_t in_dim, uint32_t out_dim, uint32_t n_used, uint32_t n_tok,

@@ -307,6 +307,18 @@ def launch_swiglu_q8(gate: torch.Tensor, up: torch.Tensor, out, q8: torch.Tensor
     check(_lib.load().rc_swiglu_q8(_stream(), _ptr(gate), _ptr(up), _ptr(out), _ptr(q8), n), "rc_swiglu_q8")
 
 
+def launch_sigmoid_mul_q8(x: torch.Tensor, gate: torch.Tensor, q8: torch.Tensor, n: int) -> None:
+    """sigmoid_mul_q8_f32 (kernels/qwen35_fused.cpp:139-152); x is updated in place."""
+    check(_lib.load().rc_sigmoid_mul_q8(_stream(), _ptr(x), _ptr(gate), _ptr(q8), n), "rc_sigmoid_mul_q8")
+
+
+def launch_rmsnorm_gated_q8(x: torch.Tensor, z: torch.Tensor, w: torch.Tensor, y, q8: torch.Tensor, n_heads: int,
+                            head_dim: int, eps: float) -> None:
+    """rmsnorm_gated_q8_f32 (kernels/qwen35_fused.cpp:204-224); y may be None."""
+    check(_lib.load().rc_rmsnorm_gated_q8(_stream(), _ptr(x), _ptr(z), _ptr(w), _ptr(y), _ptr(q8), n_heads, head_dim, eps),
+          "rc_rmsnorm_gated_q8")
+
+
 def launch_moe_expert_matvec(et: GpuExpertTensor, ids: torch.Tensor, xq8: torch.Tensor, y: torch.Tensor, n_used: int,
                              n_tok: int, xq_tok_stride: int, xq_slot_stride: int) -> None:
     """launch_moe_expert_matvec / launch_moe_down (src/runtime/qwen35.rs:3066-3139): decode-side

@@ -66,6 +66,10 @@ def lib() -> C.CDLL:
             getattr(L, name).argtypes = [vp, vp, sz]
         L.ro_rmsnorm_q8.restype = None
         L.ro_rmsnorm_q8.argtypes = [vp, vp, vp, vp, vp, vp, sz, sz, C.c_float]
+        L.ro_sigmoid_mul_q8.restype = None
+        L.ro_sigmoid_mul_q8.argtypes = [vp, vp, vp, sz]
+        L.ro_rmsnorm_gated_q8.restype = None
+        L.ro_rmsnorm_gated_q8.argtypes = [vp, vp, vp, vp, vp, sz, sz, C.c_float]
         L.ro_swiglu_q8.restype = None
         L.ro_swiglu_q8.argtypes = [vp, vp, vp, vp, sz]
         L.ro_kernel_type.restype = i
@@ -253,6 +257,24 @@ def rmsnorm_q8(x: np.ndarray, w: np.ndarray, eps: float, add: np.ndarray | None 
     out = np.zeros(n_vec * (n // 32) * 40, dtype=np.uint8)
     lib().ro_rmsnorm_q8(_p(x), _p(a), _p(np.ascontiguousarray(w, dtype=np.float32)), _p(hid), _p(y), _p(out), n, n_vec, eps)
     return hid, y, out
+
+
+def sigmoid_mul_q8(x: np.ndarray, gate: np.ndarray):
+    v = np.ascontiguousarray(x, dtype=np.float32).reshape(-1).copy()
+    gate = np.ascontiguousarray(gate, dtype=np.float32).reshape(-1)
+    out = np.zeros(v.size // 32 * 40, dtype=np.uint8)
+    lib().ro_sigmoid_mul_q8(_p(v), _p(gate), _p(out), v.size)
+    return v, out
+
+
+def rmsnorm_gated_q8(x: np.ndarray, z: np.ndarray, w: np.ndarray, eps: float):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    n_heads, head_dim = x.shape
+    y = np.empty_like(x)
+    out = np.zeros(x.size // 32 * 40, dtype=np.uint8)
+    lib().ro_rmsnorm_gated_q8(_p(x), _p(np.ascontiguousarray(z, dtype=np.float32)), _p(np.ascontiguousarray(w, dtype=np.float32)),
+                              _p(y), _p(out), n_heads, head_dim, eps)
+    return y, out
 
 
 def swiglu_q8(gate: np.ndarray, up: np.ndarray):

@@ -62,6 +62,10 @@ def test_bad_shapes_and_types_are_rejected_before_any_launch():
     assert lib.rc_swiglu_q8(None, 4, 4, None, 8, 33) == -2
     assert lib.rc_swiglu_q8(None, 4, None, None, 8, 64) == -3
     assert lib.rc_swiglu_q8(None, None, None, None, None, 0) == 0
+    assert lib.rc_sigmoid_mul_q8(None, 4, 4, 8, 40) == -2
+    assert lib.rc_sigmoid_mul_q8(None, None, 4, 8, 64) == -3
+    assert lib.rc_rmsnorm_gated_q8(None, 4, 4, 4, None, 8, 2, 2048, 1e-6) == -2
+    assert lib.rc_rmsnorm_gated_q8(None, 4, None, 4, None, 8, 2, 128, 1e-6) == -3
     # MoE glue: expert and slot counts beyond what one warp per token holds, odd shapes
     assert lib.rc_moe_topk(None, 4, 1, 2000, 8, 4, 4) == -8
     assert lib.rc_moe_topk(None, 4, 1, 128, 33, 4, 4) == -8

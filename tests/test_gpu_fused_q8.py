@@ -84,3 +84,38 @@ def test_fused_q8_feeds_the_matvec(rt):
     _, _, q = ro.rmsnorm_q8(x, w_norm, 1e-6)
     _, y64, _ = ro.matvec_q8(t, ro.repack(t, raw, in_dim, out_dim), q, in_dim, out_dim, 1)
     assert ro.rel_l2(y.cpu().numpy(), y64) < 1e-5
+
+
+@pytest.mark.parametrize("n", [32, 6144])
+def test_sigmoid_mul_q8_matches_oracle(rt, n):
+    rng = np.random.default_rng(n + 1)
+    x = rng.standard_normal(n).astype(np.float32)
+    g = (rng.standard_normal(n) * 3).astype(np.float32)
+    v_w, q_w = ro.sigmoid_mul_q8(x, g)
+    xd = torch.from_numpy(x.copy()).cuda()
+    q8 = torch.zeros(n // 32 * 40, dtype=torch.uint8, device="cuda")
+    rt.launch_sigmoid_mul_q8(xd, torch.from_numpy(g).cuda(), q8, n)
+    torch.cuda.synchronize()
+    v = xd.cpu().numpy()
+    np.testing.assert_allclose(v, v_w, rtol=4e-6, atol=1e-9)                        # expf: device vs host libm
+    np.testing.assert_array_equal(q8.cpu().numpy(), ro.quantize_q8(v.reshape(1, -1)))   # records of the device's own values
+
+
+@pytest.mark.parametrize("n_heads,head_dim", [(1, 32), (16, 128), (48, 128), (3, 1024)])
+def test_rmsnorm_gated_q8_matches_oracle(rt, n_heads, head_dim):
+    rng = np.random.default_rng(n_heads * head_dim)
+    x = (rng.standard_normal((n_heads, head_dim)) * 2).astype(np.float32)
+    z = (rng.standard_normal((n_heads, head_dim)) * 2).astype(np.float32)
+    w = (rng.random(head_dim) + 0.5).astype(np.float32)
+    y_w, q_w = ro.rmsnorm_gated_q8(x, z, w, 1e-6)
+    y = torch.full((n_heads, head_dim), float("nan"), device="cuda")
+    q8 = torch.zeros(n_heads * head_dim // 32 * 40, dtype=torch.uint8, device="cuda")
+    rt.launch_rmsnorm_gated_q8(torch.from_numpy(x).cuda(), torch.from_numpy(z).cuda(), torch.from_numpy(w).cuda(), y, q8,
+                               n_heads, head_dim, 1e-6)
+    torch.cuda.synchronize()
+    yv = y.cpu().numpy()
+    np.testing.assert_allclose(yv, y_w, rtol=4e-6, atol=1e-9)
+    np.testing.assert_array_equal(q8.cpu().numpy(), ro.quantize_q8(yv.reshape(1, -1)))
+    x64, z64 = x.astype(np.float64), z.astype(np.float64)
+    ref = x64 / np.sqrt((x64 ** 2).mean(1, keepdims=True) + 1e-6) * w * (z64 / (1 + np.exp(-z64)))
+    np.testing.assert_allclose(yv, ref, rtol=1e-5, atol=1e-6)
