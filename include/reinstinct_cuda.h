@@ -291,6 +291,15 @@ int rc_moe_expert_matvec(void *stream, int ggml_type, const void *slab, size_t b
                          uint32_t out_dim, uint32_t n_used, uint32_t n_tok, uint32_t xq_tok_stride,
                          uint32_t xq_slot_stride);
 
+/* launch_moe_gate_up_swiglu (src/runtime/qwen35.rs:3141-3167); kernel moe_gate_up_swiglu_q4k_repacked_f32:
+ * y[t][j][i] = silu(Wgate[ids[t][j]][i] . x) * (Wup[ids[t][j]][i] . x), one launch in place of two expert
+ * matvecs and the activation.  gate_slab and up_slab have the same type, shape and bytes_per_expert;
+ * x is addressed as in rc_moe_expert_matvec.  All six types (the reference: Q4_K); in_dim % 1024 == 0. */
+int rc_moe_gate_up_swiglu(void *stream, int ggml_type, const void *gate_slab, const void *up_slab,
+                          size_t bytes_per_expert, const int32_t *ids, uint32_t n_expert, const void *xq, float *y,
+                          uint32_t in_dim, uint32_t out_dim, uint32_t n_used, uint32_t n_tok, uint32_t xq_tok_stride,
+                          uint32_t xq_slot_stride);
+
 /* ---- MoE glue around the grouped GEMMs ------------------------------------------------------- */
 
 /* launch_moe_topk (src/runtime/gemma4.rs:1649-1670); kernel moe_topk_f32 (kernels/moe_topk.cpp:17-107):

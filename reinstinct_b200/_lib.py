@@ -64,6 +64,7 @@ _SIGNATURES = {
     "rc_debug_read_trace": (_i, [_vp, C.c_size_t]),
     "rc_mmq_gemm_grouped_scratch_bytes": (_sz, [_u32, _u32]),
     "rc_mmq_gemm_grouped_f32": (_i, [_vp, _i, _vp, _sz, _vp, _vp, _u32, _vp, _vp, _u32, _sz, _i, _vp, _u32, _u32, _u32, _vp, _sz]),
+    "rc_moe_gate_up_swiglu": (_i, [_vp, _i, _vp, _vp, _sz, _vp, _u32, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32]),
     "rc_moe_expert_matvec": (_i, [_vp, _i, _vp, _sz, _vp, _u32, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32]),
     "rc_moe_topk": (_i, [_vp, _vp, _u32, _u32, _u32, _vp, _vp]),
     "rc_moe_act_q8": (_i, [_vp, _vp, _vp, _u32, _u32, _i]),

@@ -432,6 +432,24 @@ int rc_moe_expert_matvec(void *stream, int type, const void *slab, size_t bytes_
                                     n_tok, xq_tok_stride, xq_slot_stride);
 }
 
+int rc_moe_gate_up_swiglu(void *stream, int type, const void *gate_slab, const void *up_slab, size_t bytes_per_expert,
+                          const int32_t *ids, uint32_t n_expert, const void *xq, float *y, uint32_t in_dim, uint32_t out_dim,
+                          uint32_t n_used, uint32_t n_tok, uint32_t xq_tok_stride, uint32_t xq_slot_stride)
+{
+    if (n_tok == 0 || n_used == 0) return RC_OK;
+    int rc = check_weight_args(type, gate_slab, xq, y, in_dim, out_dim);
+    if (rc) return rc;
+    if (!up_slab || !ids) return RC_ERR_NULL_POINTER;
+    if ((uintptr_t)up_slab & 15u) return RC_ERR_MISALIGNED;
+    if (in_dim % 1024u) return RC_ERR_BAD_SHAPE;
+    if (n_expert == 0 || n_used > 65535u) return RC_ERR_BAD_ARGUMENT;
+    if (n_expert > 1 && (bytes_per_expert & 15u)) return RC_ERR_MISALIGNED;
+    rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_moe_gate_up_swiglu(S(stream), type, gate_slab, up_slab, bytes_per_expert, ids, n_expert, xq, y, in_dim, out_dim,
+                                     n_used, n_tok, xq_tok_stride, xq_slot_stride);
+}
+
 /* ---- MoE glue ------------------------------------------------------------------------------------ */
 
 int rc_moe_topk(void *stream, const float *logits, uint32_t n_tok, uint32_t n_expert, uint32_t n_used,

@@ -78,6 +78,9 @@ int launch_swiglu_q8(cudaStream_t s, const float *gate, const float *up, float *
 int launch_moe_expert_matvec(cudaStream_t s, int type, const void *slab, size_t bpe, const int32_t *ids, uint32_t n_expert,
                              const void *xq, float *y, uint32_t in_dim, uint32_t out_dim, uint32_t n_used, uint32_t n_tok,
                              uint32_t tok_stride, uint32_t slot_stride);
+int launch_moe_gate_up_swiglu(cudaStream_t s, int type, const void *gate_slab, const void *up_slab, size_t bpe, const int32_t *ids,
+                              uint32_t n_expert, const void *xq, float *y, uint32_t in_dim, uint32_t out_dim, uint32_t n_used,
+                              uint32_t n_tok, uint32_t tok_stride, uint32_t slot_stride);
 int launch_moe_topk(cudaStream_t s, const float *logits, uint32_t n_tok, uint32_t n_expert, uint32_t n_used,
                     int32_t *ids, float *weights);
 int launch_moe_act_q8(cudaStream_t s, const float *gu, void *out, uint32_t ff, uint32_t n_slot, int act);

@@ -740,6 +740,62 @@ moe_expert_matvec_kernel(const uint8_t *__restrict__ slab, size_t bytes_per_expe
                                nullptr, in_dim, out_dim, 1, ks, blockIdx.x, gridDim.x);
 }
 
+// Fused gate + up + SwiGLU of the decode-side routed experts (kernels/moe_gate_up_swiglu_q4k_repacked.cpp,
+// launched by src/runtime/qwen35.rs:3141-3167): a warp computes row i of the expert's gate tensor and
+// row i of its up tensor against the same activation blocks and writes silu(gate) * up: one launch in
+// place of two matvecs and the activation.  Whole iterations only (in_dim a multiple of 1024).
+template <int FMT>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, MinBlocks<1>::v)
+moe_gate_up_swiglu_kernel(const uint8_t *__restrict__ gate_slab, const uint8_t *__restrict__ up_slab, size_t bytes_per_expert,
+                          const int32_t *__restrict__ ids, uint32_t n_expert, const uint8_t *__restrict__ xq,
+                          float *__restrict__ y, uint32_t in_dim, uint32_t out_dim, uint32_t n_used, uint32_t xq_tok_stride,
+                          uint32_t xq_slot_stride)
+{
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t n_sub = in_dim >> 5, n_iters = n_sub >> 5;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t slot = blockIdx.y, tok = blockIdx.z;
+    float *yo = y + ((size_t)tok * n_used + slot) * out_dim;
+    pdl_launch_dependents();
+    pdl_wait(); // ids and activations are predecessors' outputs
+    const int32_t e = ids[(size_t)tok * n_used + slot];
+    if (e < 0 || (uint32_t)e >= n_expert) {
+        for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < out_dim; i += gridDim.x * blockDim.x) yo[i] = 0.0f;
+        return;
+    }
+    const Planes pg = planes_of<FMT>(gate_slab + (size_t)e * bytes_per_expert, in_dim, out_dim);
+    const Planes pu = planes_of<FMT>(up_slab + (size_t)e * bytes_per_expert, in_dim, out_dim);
+    const bool a4 = ((reinterpret_cast<uintptr_t>(pg.sup) | reinterpret_cast<uintptr_t>(pu.sup)) & 3u) == 0;
+    const XStage st = carve_stage<FMT>(smem, n_sub);
+    stage_x<FMT>(st, xq + ((size_t)tok * xq_tok_stride + (size_t)slot * xq_slot_stride) * RC_BLOCKQ8_BYTES, n_sub);
+    __syncthreads();
+    for (uint32_t row = blockIdx.x * kWarpsPerCta + warp; row < out_dim; row += gridDim.x * kWarpsPerCta) {
+        const GroupPtrs gg = group_ptrs<FMT>(pg, row, lane), gu = group_ptrs<FMT>(pu, row, lane);
+        float ag = 0.0f, au = 0.0f;
+        Raw<FMT> rg, ru;
+        if (a4) { fetch_off<FMT, true>(rg, gg, 0); fetch_off<FMT, true>(ru, gu, 0); }
+        else { fetch_off<FMT, false>(rg, gg, 0); fetch_off<FMT, false>(ru, gu, 0); }
+        for (uint32_t it = 0; it < n_iters; it++) {
+            Raw<FMT> ng = rg, nu = ru;
+            if (it + 1 < n_iters) {
+                if (a4) { fetch_off<FMT, true>(ng, gg, (int)it + 1); fetch_off<FMT, true>(nu, gu, (int)it + 1); }
+                else { fetch_off<FMT, false>(ng, gg, (int)it + 1); fetch_off<FMT, false>(nu, gu, (int)it + 1); }
+            }
+            const uint32_t xi = it * 32u + lane;
+            const int4 xl = st.lo[xi], xh = st.hi[xi];
+            const float2 ds = st.ds[xi];
+            const int2 is = FmtTraits<FMT>::needs_is ? st.is[xi] : make_int2(0, 0);
+            int i0, i1;
+            ag += term<FMT>(rg, xl, xh, ds, is, i0, i1);
+            au += term<FMT>(ru, xl, xh, ds, is, i0, i1);
+            rg = ng;
+            ru = nu;
+        }
+        const float g = warp_sum(ag), u = warp_sum(au);
+        if (lane == 0) yo[row] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
+    }
+}
+
 struct Tuning {
     int ks = 0;          // 0 = heuristic
     int grid_mult = 0;   // CTAs launched per resident CTA slot; 0 = heuristic
@@ -957,8 +1013,31 @@ int launch_expert_fmt(cudaStream_t s, const void *slab, size_t bpe, const int32_
     return RC_OK;
 }
 
+template <int FMT>
+int launch_gate_up_swiglu_fmt(cudaStream_t s, const void *gate_slab, const void *up_slab, size_t bpe, const int32_t *ids,
+                              uint32_t n_expert, const void *xq, float *y, uint32_t in_dim, uint32_t out_dim, uint32_t n_used,
+                              uint32_t n_tok, uint32_t tok_stride, uint32_t slot_stride)
+{
+    const uint32_t n_sub = in_dim >> 5;
+    if (n_sub % 32u) return RC_ERR_BAD_SHAPE; // whole iterations only
+    const size_t smem = stream_smem_bytes<FMT>(1, n_sub, 1);
+    if (smem > kMaxStageBytesHost) return RC_ERR_BAD_SHAPE;
+    const uint32_t gx = (out_dim + kWarpsPerCta - 1u) / kWarpsPerCta;
+    for (uint32_t t0 = 0; t0 < n_tok; t0 += 65535u) {
+        const uint32_t nt = min(65535u, n_tok - t0);
+        cudaError_t e = launch_pdl(moe_gate_up_swiglu_kernel<FMT>, dim3(gx, n_used, nt), dim3(kWarpsPerCta * 32), smem, s,
+                                   (const uint8_t *)gate_slab, (const uint8_t *)up_slab, bpe, ids + (size_t)t0 * n_used, n_expert,
+                                   (const uint8_t *)xq + (size_t)t0 * tok_stride * RC_BLOCKQ8_BYTES,
+                                   y + (size_t)t0 * n_used * out_dim, in_dim, out_dim, n_used, tok_stride, slot_stride);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return RC_OK;
+}
+
 template <int FMT> int set_attr_expert()
 {
+    if ((int)cudaFuncSetAttribute(moe_gate_up_swiglu_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost))
+        return 1;
     return (int)cudaFuncSetAttribute(moe_expert_matvec_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
 }
 
@@ -978,6 +1057,23 @@ int launch_moe_expert_matvec(cudaStream_t s, int type, const void *slab, size_t 
     case IQ4_XS: RC_E(IQ4_XS);
     }
 #undef RC_E
+    return RC_ERR_BAD_TYPE;
+}
+
+int launch_moe_gate_up_swiglu(cudaStream_t s, int type, const void *gate_slab, const void *up_slab, size_t bpe, const int32_t *ids,
+                              uint32_t n_expert, const void *xq, float *y, uint32_t in_dim, uint32_t out_dim, uint32_t n_used,
+                              uint32_t n_tok, uint32_t tok_stride, uint32_t slot_stride)
+{
+#define RC_S(F) return launch_gate_up_swiglu_fmt<F>(s, gate_slab, up_slab, bpe, ids, n_expert, xq, y, in_dim, out_dim, n_used, n_tok, tok_stride, slot_stride)
+    switch (type) {
+    case Q4_0: RC_S(Q4_0);
+    case Q8_0: RC_S(Q8_0);
+    case Q4_K: RC_S(Q4_K);
+    case Q5_K: RC_S(Q5_K);
+    case Q6_K: RC_S(Q6_K);
+    case IQ4_XS: RC_S(IQ4_XS);
+    }
+#undef RC_S
     return RC_ERR_BAD_TYPE;
 }
 

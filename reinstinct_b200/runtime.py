@@ -23,7 +23,7 @@ __all__ = [
     "matvec_block_dots", "launch_mmq_gemm", "launch_moe_sort", "launch_moe_gather_xq",
     "launch_moe_grouped_gemm", "launch_moe_scatter_rows", "repacked_len", "init", "PeerAllGather",
     "MoeGroupedGemm", "launch_rmsnorm_q8", "launch_add_rmsnorm_q8", "launch_swiglu_q8",
-    "launch_moe_expert_matvec", "launch_moe_topk", "launch_moe_act_q8", "launch_moe_combine", "ACT_GEGLU", "ACT_SWIGLU",
+    "launch_moe_expert_matvec", "launch_moe_gate_up_swiglu", "launch_moe_topk", "launch_moe_act_q8", "launch_moe_combine", "ACT_GEGLU", "ACT_SWIGLU",
 ]
 
 
@@ -327,6 +327,15 @@ def launch_moe_expert_matvec(et: GpuExpertTensor, ids: torch.Tensor, xq8: torch.
     check(_lib.load().rc_moe_expert_matvec(_stream(), et.dtype, _ptr(et.data), et.bytes_per_expert, _ptr(ids), et.n_expert,
                                            _ptr(xq8), _ptr(y), et.in_dim, et.out_dim, n_used, n_tok, xq_tok_stride,
                                            xq_slot_stride), "rc_moe_expert_matvec")
+
+
+def launch_moe_gate_up_swiglu(gate: GpuExpertTensor, up: GpuExpertTensor, ids: torch.Tensor, xq8: torch.Tensor,
+                              y: torch.Tensor, n_used: int, n_tok: int, xq_tok_stride: int, xq_slot_stride: int) -> None:
+    """launch_moe_gate_up_swiglu (src/runtime/qwen35.rs:3141-3167): y [n_tok, n_used, out_dim] = silu(gate) * up."""
+    assert gate.dtype == up.dtype and gate.bytes_per_expert == up.bytes_per_expert and ids.dtype == torch.int32
+    check(_lib.load().rc_moe_gate_up_swiglu(_stream(), gate.dtype, _ptr(gate.data), _ptr(up.data), gate.bytes_per_expert,
+                                            _ptr(ids), gate.n_expert, _ptr(xq8), _ptr(y), gate.in_dim, gate.out_dim, n_used,
+                                            n_tok, xq_tok_stride, xq_slot_stride), "rc_moe_gate_up_swiglu")
 
 
 ACT_GEGLU, ACT_SWIGLU = 0, 1

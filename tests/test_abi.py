@@ -78,6 +78,8 @@ def test_bad_shapes_and_types_are_rejected_before_any_launch():
     assert lib.rc_moe_act_q8(None, None, None, 64, 0, 0) == 0
     assert lib.rc_moe_combine(None, 4, 4, 4, None, 4, 16, 0, 1) == -8
     assert lib.rc_moe_combine(None, None, 4, 4, None, 4, 16, 2, 1) == -3
+    assert lib.rc_moe_gate_up_swiglu(None, _lib.Q4_K, 16, 16, 64, 4, 2, 8, 4, 512, 8, 2, 1, 16, 0) == -2   # in_dim % 1024
+    assert lib.rc_moe_gate_up_swiglu(None, _lib.Q4_K, 16, None, 64, 4, 2, 8, 4, 1024, 8, 2, 1, 32, 0) == -3
     assert lib.rc_moe_expert_matvec(None, 99, 16, 64, 4, 2, 8, 4, 256, 8, 2, 1, 1, 0) == -1
     assert lib.rc_moe_expert_matvec(None, _lib.Q4_K, 16, 64, None, 2, 8, 4, 256, 8, 2, 1, 1, 0) == -3
     assert lib.rc_moe_expert_matvec(None, _lib.Q4_K, 16, 60, 4, 2, 8, 4, 256, 8, 2, 1, 1, 0) == -4

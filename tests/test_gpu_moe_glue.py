@@ -232,3 +232,30 @@ def test_expert_matvec_bad_id_and_arguments(rt):
     got = y.cpu().numpy()
     assert np.all(got[0, 1] == 0) and np.all(got[0, 2] == 0)
     assert np.all(np.isfinite(got)) and np.any(got[0, 0] != 0) and np.any(got[0, 3] != 0)
+
+
+@pytest.mark.parametrize("t", ro.ALL_TYPES)
+def test_gate_up_swiglu_equals_two_matvecs_and_activation(rt, t):
+    """The fused decode kernel against two expert matvecs (same per-block arithmetic, same order) and
+    the SiLU product in f32."""
+    import cases
+    n_expert, n_used, n_tok, in_dim, out_dim = 5, 3, 4, 2048, 96
+    rng = np.random.default_rng(t)
+    gates = [cases.synth_case(t, in_dim, out_dim, 1, seed=60 * t + e)[0] for e in range(n_expert)]
+    ups = [cases.synth_case(t, in_dim, out_dim, 1, seed=70 * t + e)[0] for e in range(n_expert)]
+    g = rt.GpuExpertTensor.from_bytes(np.concatenate(gates), t, in_dim, out_dim, n_expert)
+    u = rt.GpuExpertTensor.from_bytes(np.concatenate(ups), t, in_dim, out_dim, n_expert)
+    ids = torch.from_numpy(rng.integers(0, n_expert, (n_tok, n_used)).astype(np.int32)).cuda()
+    x = rng.standard_normal((n_tok, in_dim)).astype(np.float32) * 0.1
+    n_sub = in_dim // 32
+    xq = torch.empty(n_tok * n_sub * 40, dtype=torch.uint8, device="cuda")
+    rt.launch_quantize_q8(torch.from_numpy(x).cuda(), xq, in_dim, n_tok)
+    y = torch.full((n_tok, n_used, out_dim), float("nan"), device="cuda")
+    rt.launch_moe_gate_up_swiglu(g, u, ids, xq, y, n_used, n_tok, n_sub, 0)
+    yg, yu = torch.empty_like(y), torch.empty_like(y)
+    rt.launch_moe_expert_matvec(g, ids, xq, yg, n_used, n_tok, n_sub, 0)
+    rt.launch_moe_expert_matvec(u, ids, xq, yu, n_used, n_tok, n_sub, 0)
+    torch.cuda.synchronize()
+    gv, uv = yg.cpu().numpy().astype(np.float64), yu.cpu().numpy().astype(np.float64)
+    want = gv / (1 + np.exp(-gv)) * uv
+    assert ro.rel_l2(y.cpu().numpy(), want) < 1e-5
