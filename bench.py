@@ -305,6 +305,50 @@ def measured_tensor_peak() -> tuple[float, str]:
     return 1590.0, "fallback"
 
 
+def moe_expert_parallel(rt, synth, torch, dist, dev, timed, rank, world):
+    """Config 5 sharded by experts over the ranks (N > 1): 256 experts split evenly, every rank routes its
+    own 512 / N tokens (top-8), the routed activation rows go to the owner of their expert by NCCL
+    all-to-all (counts first), through the grouped gate+up GEMM there, and the results travel back.  The
+    collectives are host-driven (eager NCCL), so the step is timed eagerly; value = tokens of all ranks per
+    second through this gate+up stage."""
+    from reinstinct_b200 import sharding as sh
+
+    E, H, F, NT, K = 256, 2048, 512, 512, 8
+    nt = NT // world
+    e0, e1 = sh.expert_range(E, rank, world)
+    one = synth.synth_blocks(Q4_K, H, 2 * F * 8, 91)
+    n_local = e1 - e0
+    gu = rt.GpuExpertTensor.from_bytes(np.tile(one, (n_local + 7) // 8)[: (n_local * one.size) // 8], Q4_K, H, 2 * F, n_local, device=dev)
+    logits = torch.from_numpy(synth.synth_router_logits(NT, E, 93)[rank * nt:(rank + 1) * nt].copy()).to(dev)
+    x = torch.from_numpy(synth.synth_activations(NT, H, 94)[rank * nt:(rank + 1) * nt].copy()).to(dev)
+    ids = torch.empty(nt, K, dtype=torch.int32, device=dev)
+    wts = torch.empty(nt, K, device=dev)
+    gg = rt.MoeGroupedGemm(device=dev)
+    state = {}
+
+    def step(i):
+        rt.launch_moe_topk(logits, ids, wts, E, K, nt)
+        flat = ids.reshape(-1)
+        plan = sh.plan_dispatch(flat, E)
+        rows_in = sh.dispatch_rows(x.repeat_interleave(K, dim=0).contiguous(), plan)
+        ids_in = (sh.dispatch_rows(flat.to(torch.float32).reshape(-1, 1), plan).reshape(-1).to(torch.int32) - e0).contiguous()
+        n_in = rows_in.shape[0]
+        moe = rt.MoeGroupedScratch.new(n_local, n_in, device=dev)
+        rt.launch_moe_sort(moe, ids_in, n_in)
+        y_sorted = torch.empty(n_in, 2 * F, device=dev)
+        gg.gate_up(moe, gu, rows_in, 1, y_sorted, n_in)
+        y_in = torch.empty(n_in, 2 * F, device=dev)
+        rt.launch_moe_scatter_rows(moe, y_sorted, y_in, 2 * F, n_in)
+        state["y"] = sh.combine_rows(y_in, plan)
+        state["n_in"] = n_in
+
+    reps = 5
+    us = timed(step, reps, 3) / reps * 1e3
+    return {"workload": f"config 5 gate+up stage, {E} experts over {world} ranks, {nt} tokens per rank, top-{K}",
+            "us_step": us, "tok_per_s": NT / (us * 1e-6), "rows_received_rank0": state.get("n_in"),
+            "collectives": "NCCL all_to_all_single: counts, rows, expert ids, results (eager, host-driven)"}
+
+
 def mmq_prefill(rt, synth, torch, dev, timed):
     """Config 4: dense prefill GEMM, 512 tokens x Q4_K 5120->17408, through PrefillGemm (f32
     activations in: f16 image + tcgen05 kind::f16 GEMM) and through the int8 entry point given
@@ -585,6 +629,13 @@ def run_gpu_arm(args):
         mmq = mmq_prefill(rt, synth, torch, dev, timed)
         moe = moe_layer(rt, synth, torch, dev, timed)
 
+    moe_ep = None
+    if world > 1 and not args.skip_mmq:
+        try:
+            moe_ep = moe_expert_parallel(rt, synth, torch, dist, dev, timed, rank, world)
+        except Exception as e:  # the headline line must not depend on this extra
+            moe_ep = {"error": f"{type(e).__name__}: {e}"}
+
     if rank == 0:
         peak, peak_kind = measured_peaks()
         achieved = q4k_bytes / (q4k_us * 1e-6) / 1e9
@@ -613,6 +664,8 @@ def run_gpu_arm(args):
             line["mmq_prefill"] = mmq
         if moe is not None:
             line["moe_grouped"] = moe
+        if moe_ep is not None:
+            line["moe_expert_parallel"] = moe_ep
         if world == 1 and not args.no_cpu_baseline:
             v, sample, _ = cpu_layer_sample(seconds=12.0, threads=os.cpu_count() or 1)
             line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port",
