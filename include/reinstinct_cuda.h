@@ -39,6 +39,12 @@ enum rc_ggml_type {
     RC_TYPE_Q5_K = 13,
     RC_TYPE_Q6_K = 14,
     RC_TYPE_IQ4_XS = 23,
+    /* KERNEL type of an IQ3_S tensor (src/runtime/qwen35.rs:281-286): the repacked IQ4_XS planes
+     * (16 nibble bytes and one fp16 scale per 32 weights) read through the codebook v = 2n - 15
+     * (src/quant/iq3_s.rs:193-214).  Every matvec / GEMM entry point takes it; rc_repack_for_matvec
+     * does not (RC_ERR_BAD_TYPE): the planes come from the caller's own iq3_s::repack_for_matvec
+     * (src/quant/iq3_s.rs:216-260), which needs ggml's 512-entry grid table. */
+    RC_TYPE_IQ3_S = 21,
     /* accepted by rc_repack_for_matvec / rc_ondisk_len as SOURCE types only: the loaders relabel
      * them onto one of the six above (src/runtime/qwen35.rs:274-307) */
     RC_SRC_Q3_K = 11,   /* exact: Q6_K blocks with q6 = q3 + 28, sc6 = sc3 - 32 (src/quant/q3_k.rs:92-121) */

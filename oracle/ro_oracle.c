@@ -84,6 +84,7 @@ size_t ro_block_bytes(int t)
     case RO_Q5_K: return 176;   /* src/quant/q5_k.rs:22 */
     case RO_Q6_K: return 210;   /* src/quant/q6_k.rs:18 */
     case RO_IQ4_XS: return 136; /* src/quant/iq4_xs.rs:24 */
+    case RO_IQ3_S: return 110;  /* src/quant/iq3_s.rs:27 */
     default: return 0;
     }
 }
@@ -92,7 +93,7 @@ size_t ro_block_weights(int t)
 {
     switch (t) {
     case RO_Q4_0: case RO_Q8_0: return 32;
-    case RO_Q4_K: case RO_Q5_K: case RO_Q6_K: case RO_IQ4_XS: return 256;
+    case RO_Q4_K: case RO_Q5_K: case RO_Q6_K: case RO_IQ4_XS: case RO_IQ3_S: return 256;
     default: return 0;
     }
 }
@@ -110,7 +111,7 @@ static void plane_bytes(int t, size_t *per_sub, size_t *per_super)
 {
     *per_sub = 0; *per_super = 0;
     switch (t) {
-    case RO_Q4_0: case RO_IQ4_XS: *per_sub = 18; break;
+    case RO_Q4_0: case RO_IQ4_XS: case RO_IQ3_S: *per_sub = 18; break;
     case RO_Q8_0: *per_sub = 34; break;
     case RO_Q4_K: *per_sub = 18; *per_super = 4; break;
     case RO_Q5_K: *per_sub = 22; *per_super = 4; break;
@@ -248,6 +249,7 @@ int ro_dequantize(int t, const uint8_t *blocks, float *out, size_t n_weights)
         case RO_Q5_K: deq_q45_k(b, o, 1); break;
         case RO_Q6_K: deq_q6_k(b, o); break;
         case RO_IQ4_XS: deq_iq4_xs(b, o); break;
+        default: return -1; /* IQ3_S: planes only, no on-disk decode */
         }
     }
     return 0;
@@ -465,7 +467,7 @@ static void find_planes(int t, const uint8_t *w, size_t in_dim, size_t out_dim, 
     p->sc = NULL;
     p->sup = NULL;
     switch (t) {
-    case RO_Q4_0: case RO_IQ4_XS: p->sc = w + q * 16; p->sup = NULL; break;
+    case RO_Q4_0: case RO_IQ4_XS: case RO_IQ3_S: p->sc = w + q * 16; p->sup = NULL; break;
     case RO_Q8_0: p->aux = w + q * 16; p->sc = w + q * 32; p->sup = NULL; break;
     case RO_Q4_K: p->sc = w + q * 16; p->sup = p->sc + q * 2; break;
     case RO_Q5_K: p->aux = w + q * 16; p->sc = p->aux + q * 4; p->sup = p->sc + q * 2; break;
@@ -562,6 +564,15 @@ static float block_term(int t, const planes_t *p, size_t row, size_t sb,
         int32_t idot = 0;
         for (int k = 0; k < 16; k++)
             idot += IQ4NL[nb[k] & 15] * xq[k] + IQ4NL[nb[k] >> 4] * xq[16 + k];
+        ints[0] = idot;
+        float a = ro_f16_to_f32(rd16(p->sc + i * 2)) * dx;
+        return a * (float)idot;
+    }
+    case RO_IQ3_S: {
+        /* The IQ4_XS kernel body with the codebook v = 2n - 15 (src/quant/iq3_s.rs:193-214). */
+        int32_t idot = 0;
+        for (int k = 0; k < 16; k++)
+            idot += (2 * (nb[k] & 15) - 15) * xq[k] + (2 * (nb[k] >> 4) - 15) * xq[16 + k];
         ints[0] = idot;
         float a = ro_f16_to_f32(rd16(p->sc + i * 2)) * dx;
         return a * (float)idot;
@@ -896,7 +907,7 @@ void ro_quantize_q8_0(const float *vals, uint8_t *out, size_t n)
 int ro_kernel_type(int src_type)
 {
     switch (src_type) {
-    case RO_Q4_0: case RO_Q8_0: case RO_Q4_K: case RO_Q5_K: case RO_Q6_K: case RO_IQ4_XS: return src_type;
+    case RO_Q4_0: case RO_Q8_0: case RO_Q4_K: case RO_Q5_K: case RO_Q6_K: case RO_IQ4_XS: case RO_IQ3_S: return src_type;
     case RO_Q3_K: return RO_Q6_K;
     case RO_IQ4_NL: return RO_IQ4_XS;
     case RO_BF16: return RO_Q8_0;

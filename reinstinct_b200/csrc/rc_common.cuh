@@ -12,7 +12,13 @@ namespace rc {
 
 constexpr int kWarp = 32;
 
-enum Fmt : int { Q4_0 = 2, Q8_0 = 8, Q4_K = 12, Q5_K = 13, Q6_K = 14, IQ4_XS = 23 };
+// IQ3_S names the KERNEL type of an IQ3_S tensor: the IQ4_XS planes (a nibble and one fp16 scale per
+// 32 weights) read through the codebook v = 2n - 15 (src/quant/iq3_s.rs:193-214).  The 110-byte
+// on-disk blocks are turned into those planes by the caller's host code; there is no device repack.
+enum Fmt : int { Q4_0 = 2, Q8_0 = 8, Q4_K = 12, Q5_K = 13, Q6_K = 14, IQ3_S = 21, IQ4_XS = 23 };
+
+// the two formats whose nibbles index a 16-entry int8 codebook
+template <int FMT> constexpr bool kCodebook = (FMT == IQ4_XS || FMT == IQ3_S);
 
 // Tensor types accepted as SOURCES of rc_repack_for_matvec only: each maps exactly (BF16: by a Q8_0
 // requantization) onto one of the six layouts above (src/runtime/qwen35.rs:274-307).
@@ -22,7 +28,7 @@ enum SrcFmt : int { SRC_Q3_K = 11, SRC_IQ4_NL = 20, SRC_BF16 = 30 };
 __host__ __device__ inline int fmt_kernel_type(int t)
 {
     switch (t) {
-    case Q4_0: case Q8_0: case Q4_K: case Q5_K: case Q6_K: case IQ4_XS: return t;
+    case Q4_0: case Q8_0: case Q4_K: case Q5_K: case Q6_K: case IQ4_XS: case IQ3_S: return t;
     case SRC_Q3_K: return Q6_K;
     case SRC_IQ4_NL: return IQ4_XS;
     case SRC_BF16: return Q8_0;
@@ -35,7 +41,7 @@ __host__ __device__ inline uint32_t src_block_bytes(int t) { return t == SRC_Q3_
 
 __host__ __device__ inline bool fmt_known(int t)
 {
-    return t == Q4_0 || t == Q8_0 || t == Q4_K || t == Q5_K || t == Q6_K || t == IQ4_XS;
+    return t == Q4_0 || t == Q8_0 || t == Q4_K || t == Q5_K || t == Q6_K || t == IQ4_XS || t == IQ3_S;
 }
 __host__ __device__ inline uint32_t fmt_block_weights(int t)
 {
@@ -50,6 +56,7 @@ __host__ __device__ inline uint32_t fmt_block_bytes(int t)
     case Q5_K: return 176;
     case Q6_K: return 210;
     case IQ4_XS: return 136;
+    case IQ3_S: return 110;
     }
     return 0;
 }
@@ -80,7 +87,7 @@ __host__ __device__ inline Planes planes_of(const uint8_t *w, uint32_t in_dim, u
     p.nib = w;
     p.aux = nullptr;
     p.sup = nullptr;
-    if (FMT == Q4_0 || FMT == IQ4_XS) {
+    if (FMT == Q4_0 || FMT == IQ4_XS || FMT == IQ3_S) {
         p.sc = w + q * 16;
     } else if (FMT == Q8_0) {
         p.aux = w + q * 16;
@@ -238,9 +245,14 @@ __device__ __forceinline__ void spread_fields4(uint32_t h, uint32_t &g0, uint32_
 }
 
 // IQ4_NL codebook {-127,-104,-83,-65,-49,-35,-22,-10,1,13,25,38,53,69,89,113}
-// (src/quant/iq4_xs.rs:28-31) as four little-endian words.
-constexpr uint32_t kIq4Lut0 = 0xBFAD9881u, kIq4Lut1 = 0xF6EADDCFu, kIq4Lut2 = 0x26190D01u,
-                   kIq4Lut3 = 0x71594535u;
+// (src/quant/iq4_xs.rs:28-31) and the IQ3_S codebook {-15,-13,...,13,15}
+// (src/quant/iq3_s.rs:193-194), each as four little-endian words.
+template <int FMT> struct Codebook {
+    static constexpr uint32_t w0 = 0xBFAD9881u, w1 = 0xF6EADDCFu, w2 = 0x26190D01u, w3 = 0x71594535u;
+};
+template <> struct Codebook<IQ3_S> {
+    static constexpr uint32_t w0 = 0xF7F5F3F1u, w1 = 0xFFFDFBF9u, w2 = 0x07050301u, w3 = 0x0F0D0B09u;
+};
 
 // Eight 4-bit codebook indices packed in q (byte k = index a_k low, b_k high) -> two
 // words of int8 codebook values, in the order the selector nibbles arrive:
@@ -248,14 +260,16 @@ constexpr uint32_t kIq4Lut0 = 0xBFAD9881u, kIq4Lut1 = 0xF6EADDCFu, kIq4Lut2 = 0x
 // PRMT reads selector nibbles directly, so no unpacking to bytes is needed: the low three
 // bits pick within a half-table, bit 3 then picks the half.  The matching activation
 // order is produced once per CTA when the activations are staged (xperm_iq4).
+template <int FMT = IQ4_XS>
 __device__ __forceinline__ void iq4_lookup8(uint32_t q, int &first, int &second)
 {
+    using C = Codebook<FMT>;
     const uint32_t sel = q & 0x77777777u;
     const uint32_t pick = 0x32103210u | ((q & 0x88888888u) >> 1);
-    const uint32_t l0 = __byte_perm(kIq4Lut0, kIq4Lut1, sel);
-    const uint32_t h0 = __byte_perm(kIq4Lut2, kIq4Lut3, sel);
-    const uint32_t l1 = __byte_perm(kIq4Lut0, kIq4Lut1, sel >> 16);
-    const uint32_t h1 = __byte_perm(kIq4Lut2, kIq4Lut3, sel >> 16);
+    const uint32_t l0 = __byte_perm(C::w0, C::w1, sel);
+    const uint32_t h0 = __byte_perm(C::w2, C::w3, sel);
+    const uint32_t l1 = __byte_perm(C::w0, C::w1, sel >> 16);
+    const uint32_t h1 = __byte_perm(C::w2, C::w3, sel >> 16);
     first = (int)__byte_perm(l0, h0, pick);
     second = (int)__byte_perm(l1, h1, pick >> 16);
 }

@@ -47,7 +47,7 @@ template <int FMT> struct FmtTraits {
     static constexpr bool needs_is = (FMT == Q6_K || FMT == Q4_0);
     static constexpr uint32_t x_bytes = needs_is ? 48 : 40; // staged bytes per activation block
     // iterations (32 sub-blocks each) whose raw weight registers a warp holds at once
-    static constexpr int G = (FMT == Q8_0) ? 3 : (FMT == Q5_K || FMT == Q6_K || FMT == IQ4_XS) ? 4 : 5;
+    static constexpr int G = (FMT == Q8_0) ? 3 : (FMT == Q5_K || FMT == Q6_K || kCodebook<FMT>) ? 4 : 5;
     // group lengths the plain row kernel is built for (longer groups of the wide formats spill)
     static constexpr int rows_max_len = (FMT == Q6_K) ? 3 : (FMT == Q8_0 || FMT == Q5_K) ? 4 : 5;
 };
@@ -75,13 +75,13 @@ __device__ __forceinline__ XStage carve_stage(uint8_t *smem, uint32_t n_blocks)
 //   Q4_K, Q4_0  ds.x = d/16 (their dots are formed 16x too large, see dot_nibbles16)
 //   Q4_K, Q5_K  ds.y = -xsum (the min term is added with one FMA)
 //   Q6_K        is = (32*sum(lo half), 32*sum(hi half));   Q4_0  is.x = 128*sum(all)
-//   IQ4_XS      quants permuted into iq4_lookup8 order
+//   IQ4_XS, IQ3_S  quants permuted into iq4_lookup8 order
 template <int FMT>
 __device__ __forceinline__ void stage_x(const XStage &st, const uint8_t *__restrict__ xq, uint32_t n_blocks)
 {
     for (uint32_t i = threadIdx.x; i < n_blocks; i += blockDim.x) {
         XBlock x = load_blockq8(xq + (size_t)i * RC_BLOCKQ8_BYTES);
-        if (FMT == IQ4_XS) {
+        if (kCodebook<FMT>) {
             int4 a, b;
             xperm_iq4(x.lo.x, x.hi.x, a.x, a.y);
             xperm_iq4(x.lo.y, x.hi.y, a.z, a.w);
@@ -110,6 +110,7 @@ template <> struct Raw<Q6_K> { uint4 q; uint2 h; uint32_t sm, d; };
 template <> struct Raw<Q8_0> { uint4 wl, wh; uint32_t d; };
 template <> struct Raw<Q4_0> { uint4 q; uint32_t d; };
 template <> struct Raw<IQ4_XS> { uint4 q; uint32_t d; };
+template <> struct Raw<IQ3_S> { uint4 q; uint32_t d; };
 
 // d|dmin word of a superblock; the plane base may be only 2-byte aligned
 __device__ __forceinline__ uint32_t ld_sup32(const uint8_t *p, bool aligned4)
@@ -295,12 +296,12 @@ __device__ __forceinline__ float term(const Raw<FMT> &r, const int4 &xl, const i
         const int idot16 = dot_nibbles16(r.q, xl, xh) - is.x; // 16 * sum((q-8)*xq)
         i0 = idot16 >> 4;
         return (f16_bits_to_f32(r.d) * ds.x) * (float)idot16;
-    } else { // IQ4_XS, activations staged in iq4_lookup8 order
+    } else { // IQ4_XS and IQ3_S, activations staged in iq4_lookup8 order
         int c0, c1, c2, c3, c4, c5, c6, c7;
-        iq4_lookup8(r.q.x, c0, c1);
-        iq4_lookup8(r.q.y, c2, c3);
-        iq4_lookup8(r.q.z, c4, c5);
-        iq4_lookup8(r.q.w, c6, c7);
+        iq4_lookup8<FMT>(r.q.x, c0, c1);
+        iq4_lookup8<FMT>(r.q.y, c2, c3);
+        iq4_lookup8<FMT>(r.q.z, c4, c5);
+        iq4_lookup8<FMT>(r.q.w, c6, c7);
         int s = 0, t = 0;
         s = __dp4a(c0, xl.x, s);
         t = __dp4a(c1, xl.y, t);
@@ -923,6 +924,7 @@ int launch_any(cudaStream_t s, int type, const void *w, const void *xq, float *y
     case Q5_K: return launch_fmt<Q5_K, DUMP>(s, w, xq, y, idots, in_dim, out_dim, n_rows);
     case Q6_K: return launch_fmt<Q6_K, DUMP>(s, w, xq, y, idots, in_dim, out_dim, n_rows);
     case IQ4_XS: return launch_fmt<IQ4_XS, DUMP>(s, w, xq, y, idots, in_dim, out_dim, n_rows);
+    case IQ3_S: return launch_fmt<IQ3_S, DUMP>(s, w, xq, y, idots, in_dim, out_dim, n_rows);
     }
     return RC_ERR_BAD_TYPE;
 }
@@ -1055,6 +1057,7 @@ int launch_moe_expert_matvec(cudaStream_t s, int type, const void *slab, size_t 
     case Q5_K: RC_E(Q5_K);
     case Q6_K: RC_E(Q6_K);
     case IQ4_XS: RC_E(IQ4_XS);
+    case IQ3_S: RC_E(IQ3_S);
     }
 #undef RC_E
     return RC_ERR_BAD_TYPE;
@@ -1072,6 +1075,7 @@ int launch_moe_gate_up_swiglu(cudaStream_t s, int type, const void *gate_slab, c
     case Q5_K: RC_S(Q5_K);
     case Q6_K: RC_S(Q6_K);
     case IQ4_XS: RC_S(IQ4_XS);
+    case IQ3_S: RC_S(IQ3_S);
     }
 #undef RC_S
     return RC_ERR_BAD_TYPE;
@@ -1086,8 +1090,9 @@ int matvec_set_attributes()
     rc |= set_attr_fmt<Q5_K>();
     rc |= set_attr_fmt<Q6_K>();
     rc |= set_attr_fmt<IQ4_XS>();
+    rc |= set_attr_fmt<IQ3_S>();
     rc |= set_attr_expert<Q4_0>() | set_attr_expert<Q8_0>() | set_attr_expert<Q4_K>() | set_attr_expert<Q5_K>() |
-          set_attr_expert<Q6_K>() | set_attr_expert<IQ4_XS>();
+          set_attr_expert<Q6_K>() | set_attr_expert<IQ4_XS>() | set_attr_expert<IQ3_S>();
     return rc;
 }
 
@@ -1105,6 +1110,7 @@ int launch_matvec_grouped(cudaStream_t s, int type, const void *slab, size_t bpe
     case Q5_K: RC_G(Q5_K);
     case Q6_K: RC_G(Q6_K);
     case IQ4_XS: RC_G(IQ4_XS);
+    case IQ3_S: RC_G(IQ3_S);
     }
 #undef RC_G
     return RC_ERR_BAD_TYPE;

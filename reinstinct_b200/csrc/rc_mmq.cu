@@ -121,10 +121,10 @@ __device__ __forceinline__ void expand_weights(const uint4 &q, const uint4 &q2, 
         hi = make_uint4(sub8((q.x >> 4) & M), sub8((q.y >> 4) & M), sub8((q.z >> 4) & M), sub8((q.w >> 4) & M));
     } else { // IQ4_XS: codebook lookup, then undo iq4_lookup8's (low, high) interleave
         int a0, a1, b0, b1, c0, c1, d0, d1;
-        iq4_lookup8(q.x, a0, a1);
-        iq4_lookup8(q.y, b0, b1);
-        iq4_lookup8(q.z, c0, c1);
-        iq4_lookup8(q.w, d0, d1);
+        iq4_lookup8<FMT>(q.x, a0, a1);
+        iq4_lookup8<FMT>(q.y, b0, b1);
+        iq4_lookup8<FMT>(q.z, c0, c1);
+        iq4_lookup8<FMT>(q.w, d0, d1);
         lo = make_uint4(__byte_perm(a0, a1, 0x6420), __byte_perm(b0, b1, 0x6420), __byte_perm(c0, c1, 0x6420),
                         __byte_perm(d0, d1, 0x6420));
         hi = make_uint4(__byte_perm(a0, a1, 0x7531), __byte_perm(b0, b1, 0x7531), __byte_perm(c0, c1, 0x7531),
@@ -1042,15 +1042,17 @@ int mmq_set_attributes()
     rc |= set_attr<Q4_K, kDenseBN>();
     rc |= set_attr<Q5_K, kDenseBN>();
     rc |= set_attr<IQ4_XS, kDenseBN>();
+    rc |= set_attr<IQ3_S, kDenseBN>();
     rc |= set_attr<Q4_0, kGroupedBN>();
     rc |= set_attr<Q8_0, kGroupedBN>();
     rc |= set_attr<Q4_K, kGroupedBN>();
     rc |= set_attr<Q5_K, kGroupedBN>();
     rc |= set_attr<IQ4_XS, kGroupedBN>();
+    rc |= set_attr<IQ3_S, kGroupedBN>();
     rc |= set_attr16<Q4_0, kDenseBN>() | set_attr16<Q8_0, kDenseBN>() | set_attr16<Q4_K, kDenseBN>() |
-          set_attr16<Q5_K, kDenseBN>() | set_attr16<Q6_K, kDenseBN>() | set_attr16<IQ4_XS, kDenseBN>();
+          set_attr16<Q5_K, kDenseBN>() | set_attr16<Q6_K, kDenseBN>() | set_attr16<IQ4_XS, kDenseBN>() | set_attr16<IQ3_S, kDenseBN>();
     rc |= set_attr16<Q4_0, kGroupedBN>() | set_attr16<Q8_0, kGroupedBN>() | set_attr16<Q4_K, kGroupedBN>() |
-          set_attr16<Q5_K, kGroupedBN>() | set_attr16<Q6_K, kGroupedBN>() | set_attr16<IQ4_XS, kGroupedBN>();
+          set_attr16<Q5_K, kGroupedBN>() | set_attr16<Q6_K, kGroupedBN>() | set_attr16<IQ4_XS, kGroupedBN>() | set_attr16<IQ3_S, kGroupedBN>();
     return rc;
 }
 
@@ -1162,6 +1164,7 @@ int mmq_dense(cudaStream_t s, int type, const void *w, const void *xq, float *y,
             case Q5_K: return launch_tc16<Q5_K, kDenseBN>(s, P, tiles);
             case Q6_K: return launch_tc16<Q6_K, kDenseBN>(s, P, tiles);
             case IQ4_XS: return launch_tc16<IQ4_XS, kDenseBN>(s, P, tiles);
+            case IQ3_S: return launch_tc16<IQ3_S, kDenseBN>(s, P, tiles);
             }
             return RC_ERR_BAD_TYPE;
         }
@@ -1171,6 +1174,7 @@ int mmq_dense(cudaStream_t s, int type, const void *w, const void *xq, float *y,
         case Q4_K: return launch_tc<Q4_K, kDenseBN>(s, P, tiles);
         case Q5_K: return launch_tc<Q5_K, kDenseBN>(s, P, tiles);
         case IQ4_XS: return launch_tc<IQ4_XS, kDenseBN>(s, P, tiles);
+        case IQ3_S: return launch_tc<IQ3_S, kDenseBN>(s, P, tiles);
         }
         return RC_ERR_BAD_TYPE;
     }
@@ -1218,6 +1222,7 @@ int launch_mmq_grouped(cudaStream_t s, int type, const void *slab, size_t bytes_
             case Q5_K: return launch_tc16<Q5_K, kGroupedBN>(s, P, tiles);
             case Q6_K: return launch_tc16<Q6_K, kGroupedBN>(s, P, tiles);
             case IQ4_XS: return launch_tc16<IQ4_XS, kGroupedBN>(s, P, tiles);
+            case IQ3_S: return launch_tc16<IQ3_S, kGroupedBN>(s, P, tiles);
             }
             return RC_ERR_BAD_TYPE;
         }
@@ -1227,6 +1232,7 @@ int launch_mmq_grouped(cudaStream_t s, int type, const void *slab, size_t bytes_
         case Q4_K: return launch_tc<Q4_K, kGroupedBN>(s, P, tiles);
         case Q5_K: return launch_tc<Q5_K, kGroupedBN>(s, P, tiles);
         case IQ4_XS: return launch_tc<IQ4_XS, kGroupedBN>(s, P, tiles);
+        case IQ3_S: return launch_tc<IQ3_S, kGroupedBN>(s, P, tiles);
         }
         return RC_ERR_BAD_TYPE;
     }

@@ -707,7 +707,7 @@ int g_deq_debug = 0;
 int mmq_deq_set_attributes()
 {
     return set_attr_deq<Q4_0>() | set_attr_deq<Q8_0>() | set_attr_deq<Q4_K>() | set_attr_deq<Q5_K>() | set_attr_deq<Q6_K>() |
-           set_attr_deq<IQ4_XS>();
+           set_attr_deq<IQ4_XS>() | set_attr_deq<IQ3_S>();
 }
 
 void mmq_deq_set_bn(int bn)
@@ -768,6 +768,7 @@ int launch_mmq_deq_f32(cudaStream_t s, int type, const void *w, const float *x, 
     case Q5_K: return launch_deq_bn<Q5_K>(s, P, bn);
     case Q6_K: return launch_deq_bn<Q6_K>(s, P, bn);
     case IQ4_XS: return launch_deq_bn<IQ4_XS>(s, P, bn);
+    case IQ3_S: return launch_deq_bn<IQ3_S>(s, P, bn);
     }
     return RC_ERR_BAD_TYPE;
 }
@@ -817,6 +818,7 @@ int launch_mmq_deq_grouped_f32(cudaStream_t s, int type, const void *slab, size_
     case Q5_K: return launch_deq_grouped<Q5_K>(s, P);
     case Q6_K: return launch_deq_grouped<Q6_K>(s, P);
     case IQ4_XS: return launch_deq_grouped<IQ4_XS>(s, P);
+    case IQ3_S: return launch_deq_grouped<IQ3_S>(s, P);
     }
     return RC_ERR_BAD_TYPE;
 }

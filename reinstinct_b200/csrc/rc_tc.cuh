@@ -293,7 +293,7 @@ __device__ __forceinline__ void expand_f16(const uint4 &q, const uint4 &q2, uint
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             int a0, a1;
-            iq4_lookup8(w[j], a0, a1);
+            iq4_lookup8<FMT>(w[j], a0, a1);
             lo[j] = __byte_perm(a0, a1, 0x6420) ^ 0x80808080u;
             hi[j] = __byte_perm(a0, a1, 0x7531) ^ 0x80808080u;
         }

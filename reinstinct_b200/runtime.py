@@ -87,6 +87,20 @@ class GpuMatvecTensor:
             torch.cuda.current_stream().synchronize()
         return GpuMatvecTensor(out, ktype, in_dim, out_dim, True)
 
+    @staticmethod
+    def from_repacked(planes, dtype: int, in_dim: int, out_dim: int,
+                      device: torch.device | str = "cuda") -> "GpuMatvecTensor":
+        """Upload planes the caller has already repacked on the host, as the reference does with the
+        output of `<fmt>::repack_for_matvec` (`DeviceBuf::from_slice(&p)`, src/runtime/qwen35.rs:309-317).
+        The only way in for IQ3_S, whose planes are built by src/quant/iq3_s.rs:216-260."""
+        need = repacked_len(dtype, in_dim, out_dim)
+        if need == 0:
+            raise ValueError(f"from_repacked: unsupported dtype {dtype} or in_dim {in_dim}")
+        t = torch.as_tensor(planes).reshape(-1)
+        if t.dtype != torch.uint8 or t.numel() < need:
+            raise ValueError(f"from_repacked: need {need} uint8 bytes")
+        return GpuMatvecTensor(t[:need].to(device).contiguous(), dtype, in_dim, out_dim, True)
+
 
 @dataclass
 class GpuExpertTensor:
@@ -118,6 +132,16 @@ class GpuExpertTensor:
                       "rc_repack_for_matvec")
             torch.cuda.current_stream().synchronize()
         return GpuExpertTensor(out, dtype, in_dim, out_dim, per_dst, n_expert, True)
+
+    @staticmethod
+    def from_repacked(slab, dtype: int, in_dim: int, out_dim: int, n_expert: int,
+                      device: torch.device | str = "cuda") -> "GpuExpertTensor":
+        """Upload a slab of experts already repacked on the host, one after the other."""
+        per = repacked_len(dtype, in_dim, out_dim)
+        t = torch.as_tensor(slab).reshape(-1)
+        if per == 0 or t.dtype != torch.uint8 or t.numel() < per * n_expert:
+            raise ValueError("GpuExpertTensor.from_repacked: bad dtype, shape or slab size")
+        return GpuExpertTensor(t[:per * n_expert].to(device).contiguous(), dtype, in_dim, out_dim, per, n_expert, True)
 
 
 def launch_quantize_q8(x: torch.Tensor, out: torch.Tensor, in_dim: int, n_vec: int) -> None:

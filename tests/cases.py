@@ -43,3 +43,23 @@ def synth_case(t: int, in_dim: int, out_dim: int, n_rows: int, seed: int, signed
     raw = synth.synth_blocks(t, in_dim, out_dim, seed, signed_scales=signed)
     x = synth.synth_activations(n_rows, in_dim, seed + 1000)
     return raw, x
+
+
+def iq3s_planes(in_dim: int, out_dim: int, seed: int):
+    """Planes of an IQ3_S-tagged tensor as src/quant/iq3_s.rs:216-260 writes them — the IQ4_XS layout:
+    16 nibble bytes per (row, sub-block) (weight k low, k + 16 high, nibble n = (v + 15) / 2), then one
+    fp16 `db` per (row, sub-block); the padding sub-block of a power-of-two row stays zero.  Returns the
+    planes and the f64 weights db * (2n - 15) they stand for."""
+    rng = np.random.default_rng(seed)
+    n_sub, nsp = in_dim // 32, ro.nsp(in_dim)
+    nib = np.zeros((out_dim, nsp, 16), dtype=np.uint8)
+    nib[:, :n_sub] = rng.integers(0, 256, (out_dim, n_sub, 16), dtype=np.uint8)
+    # db = d * (1 + 2 * scale4): spread over the 1..31 range of the sub-scale, both signs
+    db = (rng.uniform(2e-4, 2e-3, (out_dim, n_sub)) * (1 + 2 * rng.integers(0, 16, (out_dim, n_sub)))
+          * rng.choice([-1.0, 1.0], (out_dim, n_sub))).astype(np.float16)
+    sc = np.zeros((out_dim, nsp), dtype=np.float16)
+    sc[:, :n_sub] = db
+    planes = np.concatenate([nib.reshape(-1), sc.reshape(-1).view(np.uint8)])
+    n = np.concatenate([nib[:, :n_sub] & 15, nib[:, :n_sub] >> 4], axis=2).astype(np.float64)  # weights 0..15, 16..31
+    w = (db.astype(np.float64)[:, :, None] * (2.0 * n - 15.0)).reshape(out_dim, in_dim)
+    return planes, w

@@ -119,3 +119,29 @@ def test_bf16_requantizes_to_q8_0():
     assert ro.kernel_type(ro.BF16) == ro.Q8_0
     packed = ro.repack_any(ro.BF16, bf.view(np.uint8), in_dim, out_dim)
     assert np.array_equal(packed, ro.repack(ro.Q8_0, q8.reshape(-1), in_dim, out_dim))
+
+
+def test_iq3s_kernel_type_is_iq4xs_planes_with_linear_codebook():
+    """IQ3_S runs as its own kernel type on the IQ4_XS planes with the codebook 2n - 15
+    (src/runtime/qwen35.rs:281-286, src/quant/iq3_s.rs:193-214): same plane sizes as IQ4_XS, the
+    integer dots are sum((2n - 15) * xq), and the f32 result is the weights db * (2n - 15) against the
+    dequantized activations."""
+    import cases
+    in_dim, out_dim, rows = 512, 37, 3
+    assert ro.kernel_type(ro.IQ3_S) == ro.IQ3_S
+    assert ro.repacked_len(ro.IQ3_S, in_dim, out_dim) == ro.repacked_len(ro.IQ4_XS, in_dim, out_dim)
+    assert ro.block_bytes(ro.IQ3_S) == 110 and ro.block_weights(ro.IQ3_S) == 256
+    planes, w = cases.iq3s_planes(in_dim, out_dim, seed=3)
+    assert planes.size == ro.repacked_len(ro.IQ3_S, in_dim, out_dim)
+    x = np.random.default_rng(4).standard_normal((rows, in_dim)).astype(np.float32)
+    xq = ro.quantize_q8(x)
+    y32, y64, idots = ro.matvec_q8(ro.IQ3_S, planes, xq, in_dim, out_dim, rows, want_idots=True)
+    recs = xq.reshape(rows, in_dim // 32, 40)
+    q = recs[:, :, 8:].view(np.int8).astype(np.int64)                       # [rows, n_sub, 32]
+    nib = planes[:out_dim * ro.nsp(in_dim) * 16].reshape(out_dim, ro.nsp(in_dim), 16)[:, :in_dim // 32]
+    v = 2 * np.concatenate([nib & 15, nib >> 4], axis=2).astype(np.int64) - 15
+    want = np.einsum("osk,rsk->ros", v, q)
+    assert np.array_equal(idots.reshape(rows, out_dim, in_dim // 32, 2)[..., 0], want)
+    xd = ro.dequantize_q8(xq, in_dim, rows).astype(np.float64)
+    assert ro.rel_l2(y64, xd @ w.T) < 1e-6
+    assert ro.rel_l2(y32, y64) < 1e-5
