@@ -34,6 +34,8 @@ extern "C" {
 /* src/gguf/types.rs:16-35 */
 enum rc_ggml_type {
     RC_TYPE_Q4_0 = 2,
+    RC_TYPE_Q5_1 = 7,   /* MoE expert tensors (src/runtime/qwen35.rs:421): Q5_K nibble and 5th-bit planes, then d | m << 16
+                         * per sub-block (src/quant/q5_1.rs:62-100); the Q5_K kernel bodies with dsc = d, deff = -m */
     RC_TYPE_Q8_0 = 8,
     RC_TYPE_Q4_K = 12,
     RC_TYPE_Q5_K = 13,

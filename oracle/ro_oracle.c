@@ -79,6 +79,7 @@ size_t ro_block_bytes(int t)
 {
     switch (t) {
     case RO_Q4_0: return 18;    /* src/quant/q4_0.rs:23 */
+    case RO_Q5_1: return 24;    /* src/quant/q5_1.rs:27 */
     case RO_Q8_0: return 34;    /* src/quant/q8_0.rs:9 */
     case RO_Q4_K: return 144;   /* src/quant/q4_k.rs:18 */
     case RO_Q5_K: return 176;   /* src/quant/q5_k.rs:22 */
@@ -92,7 +93,7 @@ size_t ro_block_bytes(int t)
 size_t ro_block_weights(int t)
 {
     switch (t) {
-    case RO_Q4_0: case RO_Q8_0: return 32;
+    case RO_Q4_0: case RO_Q8_0: case RO_Q5_1: return 32;
     case RO_Q4_K: case RO_Q5_K: case RO_Q6_K: case RO_IQ4_XS: case RO_IQ3_S: return 256;
     default: return 0;
     }
@@ -113,6 +114,7 @@ static void plane_bytes(int t, size_t *per_sub, size_t *per_super)
     switch (t) {
     case RO_Q4_0: case RO_IQ4_XS: case RO_IQ3_S: *per_sub = 18; break;
     case RO_Q8_0: *per_sub = 34; break;
+    case RO_Q5_1: *per_sub = 24; break; /* src/quant/q5_1.rs:73-78 */
     case RO_Q4_K: *per_sub = 18; *per_super = 4; break;
     case RO_Q5_K: *per_sub = 22; *per_super = 4; break;
     case RO_Q6_K: *per_sub = 26; *per_super = 2; break;
@@ -162,6 +164,19 @@ static void deq_q4_0(const uint8_t *b, float *o)
     for (int k = 0; k < 16; k++) {
         o[k] = d * (float)((int)(b[2 + k] & 15) - 8);
         o[k + 16] = d * (float)((int)(b[2 + k] >> 4) - 8);
+    }
+}
+
+/* src/quant/q5_1.rs:41-59 */
+static void deq_q5_1(const uint8_t *b, float *o)
+{
+    float d = ro_f16_to_f32(rd16(b)), m = ro_f16_to_f32(rd16(b + 2));
+    uint32_t qh = (uint32_t)b[4] | ((uint32_t)b[5] << 8) | ((uint32_t)b[6] << 16) | ((uint32_t)b[7] << 24);
+    for (int k = 0; k < 16; k++) {
+        uint32_t lo = (uint32_t)(b[8 + k] & 15) | (((qh >> k) & 1u) << 4);
+        uint32_t hi = (uint32_t)(b[8 + k] >> 4) | (((qh >> (k + 16)) & 1u) << 4);
+        o[k] = d * (float)lo + m;
+        o[k + 16] = d * (float)hi + m;
     }
 }
 
@@ -245,6 +260,7 @@ int ro_dequantize(int t, const uint8_t *blocks, float *out, size_t n_weights)
         switch (t) {
         case RO_Q4_0: deq_q4_0(b, o); break;
         case RO_Q8_0: deq_q8_0(b, o); break;
+        case RO_Q5_1: deq_q5_1(b, o); break;
         case RO_Q4_K: deq_q45_k(b, o, 0); break;
         case RO_Q5_K: deq_q45_k(b, o, 1); break;
         case RO_Q6_K: deq_q6_k(b, o); break;
@@ -280,6 +296,27 @@ static void repack_q4_0(const uint8_t *src, size_t in_dim, size_t out_dim, uint8
             const uint8_t *b = src + (r * nb + k) * 18;
             memcpy(out + (r * nsp + k) * 16, b + 2, 16);
             memcpy(out + nib + (r * nsp + k) * 2, b, 2);
+        }
+}
+
+/* src/quant/q5_1.rs:62-100: nibbles verbatim, the 5th bits regrouped to bit 4g+b = dp4a group g lane b,
+ * then d | m << 16 as raw fp16. */
+static void repack_q5_1(const uint8_t *src, size_t in_dim, size_t out_dim, uint8_t *out)
+{
+    size_t nb = in_dim / 32, nsp = ro_nsp(in_dim), nib = out_dim * nsp * 16, qhl = out_dim * nsp * 4;
+    for (size_t r = 0; r < out_dim; r++)
+        for (size_t k = 0; k < nb; k++) {
+            const uint8_t *b = src + (r * nb + k) * 24;
+            size_t i = r * nsp + k;
+            memcpy(out + i * 16, b + 8, 16);
+            uint32_t qh = (uint32_t)b[4] | ((uint32_t)b[5] << 8) | ((uint32_t)b[6] << 16) | ((uint32_t)b[7] << 24);
+            uint32_t bits = 0;
+            for (int g = 0; g < 8; g++)
+                for (int c = 0; c < 4; c++)
+                    bits |= ((qh >> group_weight(g, c)) & 1u) << (4 * g + c);
+            uint8_t *p = out + nib + i * 4;
+            p[0] = (uint8_t)bits; p[1] = (uint8_t)(bits >> 8); p[2] = (uint8_t)(bits >> 16); p[3] = (uint8_t)(bits >> 24);
+            memcpy(out + nib + qhl + i * 4, b, 4);
         }
 }
 
@@ -390,6 +427,7 @@ int ro_repack(int t, const uint8_t *blocks, size_t in_dim, size_t out_dim, uint8
     switch (t) {
     case RO_Q4_0: repack_q4_0(blocks, in_dim, out_dim, out); break;
     case RO_Q8_0: repack_q8_0(blocks, in_dim, out_dim, out); break;
+    case RO_Q5_1: repack_q5_1(blocks, in_dim, out_dim, out); break;
     case RO_Q4_K: repack_q45_k(blocks, in_dim, out_dim, out, 0); break;
     case RO_Q5_K: repack_q45_k(blocks, in_dim, out_dim, out, 1); break;
     case RO_Q6_K: repack_q6_k(blocks, in_dim, out_dim, out); break;
@@ -469,6 +507,7 @@ static void find_planes(int t, const uint8_t *w, size_t in_dim, size_t out_dim, 
     switch (t) {
     case RO_Q4_0: case RO_IQ4_XS: case RO_IQ3_S: p->sc = w + q * 16; p->sup = NULL; break;
     case RO_Q8_0: p->aux = w + q * 16; p->sc = w + q * 32; p->sup = NULL; break;
+    case RO_Q5_1: p->aux = w + q * 16; p->sc = w + q * 20; p->sup = NULL; break; /* sc: d | m << 16 per sub-block */
     case RO_Q4_K: p->sc = w + q * 16; p->sup = p->sc + q * 2; break;
     case RO_Q5_K: p->aux = w + q * 16; p->sc = p->aux + q * 4; p->sup = p->sc + q * 2; break;
     case RO_Q6_K: p->aux = w + q * 16; p->sc = p->aux + q * 8; p->sup = p->sc + q * 2; break;
@@ -516,6 +555,26 @@ static float block_term(int t, const planes_t *p, size_t row, size_t sb,
         const uint8_t *dd = p->sup + (row * p->n_super + sb / 8) * 4;
         float dsc = ro_f16_to_f32(rd16(dd)) * (float)p->sc[i * 2];
         float deff = ro_f16_to_f32(rd16(dd + 2)) * (float)p->sc[i * 2 + 1];
+        float a = dsc * dx;
+        a = a * (float)idot;
+        float b = deff * xsum;
+        return a - b;
+    }
+    case RO_Q5_1: {
+        /* The Q5_K body with dsc = d, deff = -m (kernels/moe_matvec_q5k_repacked.cpp:86-91). */
+        const uint8_t *h = p->aux + i * 4;
+        uint32_t hb = (uint32_t)h[0] | ((uint32_t)h[1] << 8) | ((uint32_t)h[2] << 16) | ((uint32_t)h[3] << 24);
+        int32_t idot = 0;
+        for (int g = 0; g < 8; g++)
+            for (int c = 0; c < 4; c++) {
+                int wi = group_weight(g, c);
+                int q = (wi < 16) ? (nb[wi] & 15) : (nb[wi - 16] >> 4);
+                q |= (int)((hb >> (4 * g + c)) & 1u) << 4;
+                idot += q * xq[wi];
+            }
+        ints[0] = idot;
+        float dsc = ro_f16_to_f32(rd16(p->sc + i * 4));
+        float deff = -ro_f16_to_f32(rd16(p->sc + i * 4 + 2));
         float a = dsc * dx;
         a = a * (float)idot;
         float b = deff * xsum;
@@ -907,7 +966,7 @@ void ro_quantize_q8_0(const float *vals, uint8_t *out, size_t n)
 int ro_kernel_type(int src_type)
 {
     switch (src_type) {
-    case RO_Q4_0: case RO_Q8_0: case RO_Q4_K: case RO_Q5_K: case RO_Q6_K: case RO_IQ4_XS: case RO_IQ3_S: return src_type;
+    case RO_Q4_0: case RO_Q5_1: case RO_Q8_0: case RO_Q4_K: case RO_Q5_K: case RO_Q6_K: case RO_IQ4_XS: case RO_IQ3_S: return src_type;
     case RO_Q3_K: return RO_Q6_K;
     case RO_IQ4_NL: return RO_IQ4_XS;
     case RO_BF16: return RO_Q8_0;

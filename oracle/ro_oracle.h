@@ -33,6 +33,7 @@ enum {
     RO_Q4_K = 12,
     RO_Q5_K = 13,
     RO_Q6_K = 14,
+    RO_Q5_1 = 7,   /* runs on the Q5_K kernel bodies with dsc = d, deff = -m (src/quant/q5_1.rs:11-20) */
     RO_IQ3_S = 21, /* kernel type only: IQ4_XS planes read through the codebook 2n - 15; no on-disk decode here */
     RO_IQ4_XS = 23,
     /* accepted as sources only: relabelled onto one of the six above */

@@ -14,9 +14,10 @@ LIB_PATH = PKG / "libreinstinct_cuda.so"
 HEADER = PKG.parent / "include" / "reinstinct_cuda.h"
 
 Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS = 2, 8, 12, 13, 14, 23
+Q5_1 = 7    # MoE expert tensors: the Q5_K kernels with raw fp16 d, m per sub-block (src/quant/q5_1.rs)
 IQ3_S = 21  # kernel type only: planes built by the caller (src/quant/iq3_s.rs:216-260), no device repack
 ALL_TYPES = (Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS)
-TYPE_NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K", IQ4_XS: "IQ4_XS", IQ3_S: "IQ3_S"}
+TYPE_NAMES = {Q4_0: "Q4_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K", IQ4_XS: "IQ4_XS", IQ3_S: "IQ3_S", Q5_1: "Q5_1"}
 BLOCKQ8_BYTES = 40
 MATVEC_MAX_ROWS = 16
 

@@ -83,7 +83,7 @@ const char *rc_error_string(int code)
 {
     switch (code) {
     case RC_OK: return "success";
-    case RC_ERR_BAD_TYPE: return "unsupported ggml type (expected Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS or IQ3_S planes)";
+    case RC_ERR_BAD_TYPE: return "unsupported ggml type (expected Q4_0, Q5_1, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS or IQ3_S planes)";
     case RC_ERR_BAD_SHAPE: return "bad shape (zero dimension, or in_dim not a multiple of the format's block size)";
     case RC_ERR_NULL_POINTER: return "null pointer argument";
     case RC_ERR_MISALIGNED: return "misaligned pointer (weights need 16 bytes, BlockQ8 8 bytes, f32 4 bytes)";

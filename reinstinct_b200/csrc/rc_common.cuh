@@ -15,7 +15,10 @@ constexpr int kWarp = 32;
 // IQ3_S names the KERNEL type of an IQ3_S tensor: the IQ4_XS planes (a nibble and one fp16 scale per
 // 32 weights) read through the codebook v = 2n - 15 (src/quant/iq3_s.rs:193-214).  The 110-byte
 // on-disk blocks are turned into those planes by the caller's host code; there is no device repack.
-enum Fmt : int { Q4_0 = 2, Q8_0 = 8, Q4_K = 12, Q5_K = 13, Q6_K = 14, IQ3_S = 21, IQ4_XS = 23 };
+// Q5_1 (24-byte blocks of 32: fp16 d, fp16 m, 4 bytes of 5th bits, 16 nibble bytes; w = d * q5 + m) runs
+// on the Q5_K kernel bodies with dsc = d, deff = -m (src/quant/q5_1.rs:11-20): planes = the Q5_K nibble
+// and 5th-bit planes, then one word d | m << 16 per sub-block; no superblock plane.
+enum Fmt : int { Q4_0 = 2, Q5_1 = 7, Q8_0 = 8, Q4_K = 12, Q5_K = 13, Q6_K = 14, IQ3_S = 21, IQ4_XS = 23 };
 
 // the two formats whose nibbles index a 16-entry int8 codebook
 template <int FMT> constexpr bool kCodebook = (FMT == IQ4_XS || FMT == IQ3_S);
@@ -28,7 +31,7 @@ enum SrcFmt : int { SRC_Q3_K = 11, SRC_IQ4_NL = 20, SRC_BF16 = 30 };
 __host__ __device__ inline int fmt_kernel_type(int t)
 {
     switch (t) {
-    case Q4_0: case Q8_0: case Q4_K: case Q5_K: case Q6_K: case IQ4_XS: case IQ3_S: return t;
+    case Q4_0: case Q5_1: case Q8_0: case Q4_K: case Q5_K: case Q6_K: case IQ4_XS: case IQ3_S: return t;
     case SRC_Q3_K: return Q6_K;
     case SRC_IQ4_NL: return IQ4_XS;
     case SRC_BF16: return Q8_0;
@@ -41,16 +44,17 @@ __host__ __device__ inline uint32_t src_block_bytes(int t) { return t == SRC_Q3_
 
 __host__ __device__ inline bool fmt_known(int t)
 {
-    return t == Q4_0 || t == Q8_0 || t == Q4_K || t == Q5_K || t == Q6_K || t == IQ4_XS || t == IQ3_S;
+    return t == Q4_0 || t == Q5_1 || t == Q8_0 || t == Q4_K || t == Q5_K || t == Q6_K || t == IQ4_XS || t == IQ3_S;
 }
 __host__ __device__ inline uint32_t fmt_block_weights(int t)
 {
-    return (t == Q4_0 || t == Q8_0) ? 32u : 256u;
+    return (t == Q4_0 || t == Q8_0 || t == Q5_1) ? 32u : 256u;
 }
 __host__ __device__ inline uint32_t fmt_block_bytes(int t)
 {
     switch (t) {
     case Q4_0: return 18;
+    case Q5_1: return 24;
     case Q8_0: return 34;
     case Q4_K: return 144;
     case Q5_K: return 176;
@@ -95,6 +99,9 @@ __host__ __device__ inline Planes planes_of(const uint8_t *w, uint32_t in_dim, u
     } else if (FMT == Q4_K) {
         p.sc = w + q * 16;
         p.sup = p.sc + q * 2;
+    } else if (FMT == Q5_1) {
+        p.aux = w + q * 16;
+        p.sc = p.aux + q * 4; // d | m << 16, four bytes per sub-block
     } else if (FMT == Q5_K) {
         p.aux = w + q * 16;
         p.sc = p.aux + q * 4;
@@ -113,6 +120,7 @@ __host__ __device__ inline size_t repacked_len_of(int t, size_t in_dim, size_t o
     const size_t nsp = nsp_of((uint32_t)(in_dim >> 5));
     size_t per_sub = 18, per_super = 0;
     if (t == Q8_0) per_sub = 34;
+    if (t == Q5_1) per_sub = 24;
     if (t == Q4_K) per_super = 4;
     if (t == Q5_K) { per_sub = 22; per_super = 4; }
     if (t == Q6_K) { per_sub = 26; per_super = 2; }

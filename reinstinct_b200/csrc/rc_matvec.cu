@@ -47,9 +47,9 @@ template <int FMT> struct FmtTraits {
     static constexpr bool needs_is = (FMT == Q6_K || FMT == Q4_0);
     static constexpr uint32_t x_bytes = needs_is ? 48 : 40; // staged bytes per activation block
     // iterations (32 sub-blocks each) whose raw weight registers a warp holds at once
-    static constexpr int G = (FMT == Q8_0) ? 3 : (FMT == Q5_K || FMT == Q6_K || kCodebook<FMT>) ? 4 : 5;
+    static constexpr int G = (FMT == Q8_0) ? 3 : (FMT == Q5_K || FMT == Q5_1 || FMT == Q6_K || kCodebook<FMT>) ? 4 : 5;
     // group lengths the plain row kernel is built for (longer groups of the wide formats spill)
-    static constexpr int rows_max_len = (FMT == Q6_K) ? 3 : (FMT == Q8_0 || FMT == Q5_K) ? 4 : 5;
+    static constexpr int rows_max_len = (FMT == Q6_K) ? 3 : (FMT == Q8_0 || FMT == Q5_K || FMT == Q5_1) ? 4 : 5;
 };
 
 // Staged activations: [n_rows][n_sub] arrays, sub-block index fastest, so a warp's reads are
@@ -73,7 +73,7 @@ __device__ __forceinline__ XStage carve_stage(uint8_t *smem, uint32_t n_blocks)
 
 // Stages n_blocks BlockQ8 blocks.  What is stored is arranged for the consumer math below:
 //   Q4_K, Q4_0  ds.x = d/16 (their dots are formed 16x too large, see dot_nibbles16)
-//   Q4_K, Q5_K  ds.y = -xsum (the min term is added with one FMA)
+//   Q4_K, Q5_K  ds.y = -xsum (the min term is added with one FMA; Q5_1 adds +m * xsum, ds.y = xsum)
 //   Q6_K        is = (32*sum(lo half), 32*sum(hi half));   Q4_0  is.x = 128*sum(all)
 //   IQ4_XS, IQ3_S  quants permuted into iq4_lookup8 order
 template <int FMT>
@@ -106,6 +106,7 @@ __device__ __forceinline__ void stage_x(const XStage &st, const uint8_t *__restr
 template <int FMT> struct Raw;
 template <> struct Raw<Q4_K> { uint4 q; uint32_t sm, dd; };
 template <> struct Raw<Q5_K> { uint4 q; uint32_t qh, sm, dd; };
+template <> struct Raw<Q5_1> { uint4 q; uint32_t qh, dm; };
 template <> struct Raw<Q6_K> { uint4 q; uint2 h; uint32_t sm, d; };
 template <> struct Raw<Q8_0> { uint4 wl, wh; uint32_t d; };
 template <> struct Raw<Q4_0> { uint4 q; uint32_t d; };
@@ -131,6 +132,10 @@ __device__ __forceinline__ void fetch(Raw<FMT> &r, const Planes &p, size_t idx, 
         r.qh = ld_stream_u32(p.aux + idx * 4);
         r.sm = ld_nc_u16(p.sc + idx * 2);
         r.dd = ld_sup32(p.sup + sup * 4, a4);
+    } else if constexpr (FMT == Q5_1) {
+        r.q = ld_stream_u4(p.nib + idx * 16);
+        r.qh = ld_stream_u32(p.aux + idx * 4);
+        r.dm = ld_stream_u32(p.sc + idx * 4);
     } else if constexpr (FMT == Q6_K) {
         r.q = ld_stream_u4(p.nib + idx * 16);
         r.h = ld_stream_u2(p.aux + idx * 8);
@@ -166,6 +171,10 @@ __device__ __forceinline__ void fetch_off(Raw<FMT> &r, const GroupPtrs &g, int i
         r.qh = ld_stream_u32(g.aux + i * 128);
         r.sm = ld_nc_u16(g.sc + i * 64);
         r.dd = ld_sup32(g.sup + i * 16, A4);
+    } else if constexpr (FMT == Q5_1) {
+        r.q = ld_stream_u4(g.nib + i * 512);
+        r.qh = ld_stream_u32(g.aux + i * 128);
+        r.dm = ld_stream_u32(g.sc + i * 128);
     } else if constexpr (FMT == Q6_K) {
         r.q = ld_stream_u4(g.nib + i * 512);
         r.h = ld_stream_u2(g.aux + i * 256);
@@ -184,13 +193,14 @@ __device__ __forceinline__ void fetch_off(Raw<FMT> &r, const GroupPtrs &g, int i
 template <int FMT>
 __device__ __forceinline__ GroupPtrs group_ptrs(const Planes &p, uint32_t row, uint32_t sb0)
 {
-    constexpr uint32_t aux_b = FMT == Q5_K ? 4 : FMT == Q6_K ? 8 : FMT == Q8_0 ? 16 : 0;
+    constexpr uint32_t aux_b = (FMT == Q5_K || FMT == Q5_1) ? 4 : FMT == Q6_K ? 8 : FMT == Q8_0 ? 16 : 0;
+    constexpr uint32_t sc_b = FMT == Q5_1 ? 4 : 2;
     constexpr uint32_t sup_b = FMT == Q6_K ? 2 : 4;
     const size_t idx = (size_t)row * p.nsp + sb0;
     GroupPtrs g;
     g.nib = p.nib + idx * 16;
     g.aux = aux_b ? p.aux + idx * aux_b : nullptr;
-    g.sc = p.sc + idx * 2;
+    g.sc = p.sc + idx * sc_b;
     g.sup = (FMT == Q4_K || FMT == Q5_K || FMT == Q6_K) ? p.sup + ((size_t)row * p.n_super + (sb0 >> 3)) * sup_b : nullptr;
     return g;
 }
@@ -242,7 +252,7 @@ __device__ __forceinline__ float term(const Raw<FMT> &r, const int4 &xl, const i
         const int sc = (int)(r.sm & 0xFFu);
         float t = (d * ds.x) * (float)(sc * idot16);
         return fmaf(dmin * ds.y, small_uint_to_float(r.sm >> 8), t);
-    } else if constexpr (FMT == Q5_K) {
+    } else if constexpr (FMT == Q5_K || FMT == Q5_1) {
         // bit 4g+c of qh is the 5th bit of weight c of group g; group 2j pairs with the low
         // nibbles of word j, group 2j+1 with the high nibbles (src/quant/q5_k.rs:134-137)
         const uint4 q = r.q;
@@ -257,10 +267,16 @@ __device__ __forceinline__ float term(const Raw<FMT> &r, const int4 &xl, const i
         s = __dp4a((int)((q.w & M) | bits4_to_bit4(qh >> 24)), xl.w, s);
         t = __dp4a((int)(((q.w >> 4) & M) | bits4_to_bit4(qh >> 28)), xh.w, t);
         i0 = s + t;
-        const float d = f16_bits_to_f32(r.dd), dmin = f16_bits_to_f32(r.dd >> 16);
-        const int sc = (int)(r.sm & 0xFFu);
-        float v = (d * ds.x) * (float)(sc * i0);
-        return fmaf(dmin * ds.y, small_uint_to_float(r.sm >> 8), v);
+        if constexpr (FMT == Q5_1) {
+            // dsc = d, deff = -m (kernels/moe_matvec_q5k_repacked.cpp:86-91): dsc*dx*idot - deff*xsum
+            const float v = (f16_bits_to_f32(r.dm) * ds.x) * (float)i0;
+            return fmaf(f16_bits_to_f32(r.dm >> 16), ds.y, v);
+        } else {
+            const float d = f16_bits_to_f32(r.dd), dmin = f16_bits_to_f32(r.dd >> 16);
+            const int sc = (int)(r.sm & 0xFFu);
+            float v = (d * ds.x) * (float)(sc * i0);
+            return fmaf(dmin * ds.y, small_uint_to_float(r.sm >> 8), v);
+        }
     } else if constexpr (FMT == Q6_K) {
         // byte g of the high-2 plane belongs to group g (src/quant/q6_k.rs:128-133)
         const uint4 q = r.q;
@@ -919,6 +935,7 @@ int launch_any(cudaStream_t s, int type, const void *w, const void *xq, float *y
 {
     switch (type) {
     case Q4_0: return launch_fmt<Q4_0, DUMP>(s, w, xq, y, idots, in_dim, out_dim, n_rows);
+    case Q5_1: return launch_fmt<Q5_1, DUMP>(s, w, xq, y, idots, in_dim, out_dim, n_rows);
     case Q8_0: return launch_fmt<Q8_0, DUMP>(s, w, xq, y, idots, in_dim, out_dim, n_rows);
     case Q4_K: return launch_fmt<Q4_K, DUMP>(s, w, xq, y, idots, in_dim, out_dim, n_rows);
     case Q5_K: return launch_fmt<Q5_K, DUMP>(s, w, xq, y, idots, in_dim, out_dim, n_rows);
@@ -1052,6 +1069,7 @@ int launch_moe_expert_matvec(cudaStream_t s, int type, const void *slab, size_t 
 #define RC_E(F) return launch_expert_fmt<F>(s, slab, bpe, ids, n_expert, xq, y, in_dim, out_dim, n_used, n_tok, tok_stride, slot_stride)
     switch (type) {
     case Q4_0: RC_E(Q4_0);
+    case Q5_1: RC_E(Q5_1);
     case Q8_0: RC_E(Q8_0);
     case Q4_K: RC_E(Q4_K);
     case Q5_K: RC_E(Q5_K);
@@ -1070,6 +1088,7 @@ int launch_moe_gate_up_swiglu(cudaStream_t s, int type, const void *gate_slab, c
 #define RC_S(F) return launch_gate_up_swiglu_fmt<F>(s, gate_slab, up_slab, bpe, ids, n_expert, xq, y, in_dim, out_dim, n_used, n_tok, tok_stride, slot_stride)
     switch (type) {
     case Q4_0: RC_S(Q4_0);
+    case Q5_1: RC_S(Q5_1);
     case Q8_0: RC_S(Q8_0);
     case Q4_K: RC_S(Q4_K);
     case Q5_K: RC_S(Q5_K);
@@ -1085,13 +1104,14 @@ int matvec_set_attributes()
 {
     int rc = 0;
     rc |= set_attr_fmt<Q4_0>();
+    rc |= set_attr_fmt<Q5_1>();
     rc |= set_attr_fmt<Q8_0>();
     rc |= set_attr_fmt<Q4_K>();
     rc |= set_attr_fmt<Q5_K>();
     rc |= set_attr_fmt<Q6_K>();
     rc |= set_attr_fmt<IQ4_XS>();
     rc |= set_attr_fmt<IQ3_S>();
-    rc |= set_attr_expert<Q4_0>() | set_attr_expert<Q8_0>() | set_attr_expert<Q4_K>() | set_attr_expert<Q5_K>() |
+    rc |= set_attr_expert<Q4_0>() | set_attr_expert<Q5_1>() | set_attr_expert<Q8_0>() | set_attr_expert<Q4_K>() | set_attr_expert<Q5_K>() |
           set_attr_expert<Q6_K>() | set_attr_expert<IQ4_XS>() | set_attr_expert<IQ3_S>();
     return rc;
 }
@@ -1105,6 +1125,7 @@ int launch_matvec_grouped(cudaStream_t s, int type, const void *slab, size_t bpe
 #define RC_G(F) return launch_grouped_fmt<F>(s, slab, bpe, expert_off, tile_off, n_expert, xq, y, in_dim, out_dim, n_entries)
     switch (type) {
     case Q4_0: RC_G(Q4_0);
+    case Q5_1: RC_G(Q5_1);
     case Q8_0: RC_G(Q8_0);
     case Q4_K: RC_G(Q4_K);
     case Q5_K: RC_G(Q5_K);

@@ -1109,7 +1109,7 @@ int launch_mmq_gemm_f32(cudaStream_t s, int type, const void *w, const float *x,
             const uint32_t bn = p_rows > 256u ? 512u : p_rows > 128u ? 256u : 128u;
             const uint64_t tiles = (uint64_t)((out_dim + kBM - 1) / kBM) * ((p_rows + bn - 1u) / bn);
             const double waves = (double)((tiles + (uint64_t)sm_count() - 1u) / (uint64_t)sm_count());
-            const double steps = (double)n_sub + ((type == Q4_K || type == Q5_K) ? (double)((n_sub + 31u) / 32u) : 0.0);
+            const double steps = (double)n_sub + ((type == Q4_K || type == Q5_K || type == Q5_1) ? (double)((n_sub + 31u) / 32u) : 0.0);
             const double t_gemm = 7.0 + 0.42 * steps * waves;
             if (t_mv < t_gemm) {
                 int rc = launch_quantize_q8(s, x, scratch, in_dim, p_rows);
@@ -1125,7 +1125,7 @@ int launch_mmq_gemm_f32(cudaStream_t s, int type, const void *w, const float *x,
         }
         return launch_mmq_deq_f32(s, type, w, x, y, in_dim, out_dim, p_rows, scratch);
     }
-    const bool i8_kernel = !g_force_dp4a && g_mmq_kind != 16 && type != Q6_K;
+    const bool i8_kernel = !g_force_dp4a && g_mmq_kind != 16 && type != Q6_K && type != Q5_1;
     const bool planar = i8_kernel && !g_no_planar && ((uintptr_t)scratch & 15u) == 0 && p_rows <= 65535u &&
                         scratch_bytes >= quantize_planar_bytes(in_dim, p_rows);
     int rc = planar ? launch_quantize_q8_planar(s, x, scratch, in_dim, p_rows)
@@ -1140,7 +1140,7 @@ int mmq_dense(cudaStream_t s, int type, const void *w, const void *xq, float *y,
 {
     const uint32_t n_sub = in_dim >> 5;
     const bool use16 = g_mmq_kind == 16 || (g_mmq_kind != 8 && type == Q6_K);
-    if ((type != Q6_K || use16) && !g_force_dp4a) {
+    if ((type != Q6_K || use16) && type != Q5_1 && !g_force_dp4a) { // Q5_1 has no exact-integer tensor-core kernel: dp4a passes below
         MmqParams P;
         P.w = (const uint8_t *)w;
         P.bytes_per_expert = 0;
@@ -1197,7 +1197,7 @@ int launch_mmq_grouped(cudaStream_t s, int type, const void *slab, size_t bytes_
                        uint32_t n_entries)
 {
     const bool use16 = g_mmq_kind == 16 || (g_mmq_kind != 8 && type == Q6_K);
-    if ((type != Q6_K || use16) && !g_force_dp4a) {
+    if ((type != Q6_K || use16) && type != Q5_1 && !g_force_dp4a) { // Q5_1 has no exact-integer tensor-core kernel: dp4a passes below
         MmqParams P;
         P.w = (const uint8_t *)slab;
         P.bytes_per_expert = bytes_per_expert;

@@ -92,7 +92,7 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
 }
 
 template <int FMT> struct DeqTraits {
-    static constexpr bool has_min = (FMT == Q4_K || FMT == Q5_K);
+    static constexpr bool has_min = (FMT == Q4_K || FMT == Q5_K || FMT == Q5_1);
     static constexpr bool sup_scale = (FMT == Q4_K || FMT == Q5_K || FMT == Q6_K); // f16 d per superblock
     static constexpr int raw_planes = (FMT == Q8_0) ? 2 : 1;
     static constexpr uint32_t raw_bytes = raw_planes * kBM * 16;
@@ -382,20 +382,21 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
             const DeqTile tl = deq_tile<BN, GR>(P, id, tiles_m);
             const Planes pl = planes_of<FMT>(P.w + (size_t)tl.e * P.bytes_per_expert, P.in_dim, P.out_dim);
             const uint32_t row = min(tl.m0 + r, P.out_dim - 1u);
-            const uint8_t *scp = pl.sc + (size_t)row * pl.nsp * 2u;
-            const uint8_t *auxp = (FMT == Q5_K || FMT == Q6_K) ? pl.aux + (size_t)row * pl.nsp * (FMT == Q6_K ? 8u : 4u) : nullptr;
+            const uint8_t *scp = pl.sc + (size_t)row * pl.nsp * (FMT == Q5_1 ? 4u : 2u);
+            const uint8_t *auxp = (FMT == Q5_K || FMT == Q5_1 || FMT == Q6_K) ? pl.aux + (size_t)row * pl.nsp * (FMT == Q6_K ? 8u : 4u) : nullptr;
             const uint8_t *supp = T::sup_scale ? pl.sup + (size_t)row * pl.n_super * (FMT == Q6_K ? 2u : 4u) : nullptr;
             auto request = [&](Side &slot, uint32_t i) {
                 slot = Side{0u, 0u, 0u, 0u};
                 if (i < n_sub) {
-                    if constexpr (FMT == Q5_K) slot.e0 = ld_stream_u32(auxp + i * 4u);
+                    if constexpr (FMT == Q5_K || FMT == Q5_1) slot.e0 = ld_stream_u32(auxp + i * 4u);
                     if constexpr (FMT == Q6_K) {
                         const uint2 h = ld_stream_u2(auxp + i * 8u);
                         slot.e0 = h.x;
                         slot.e1 = h.y;
                     }
-                    slot.smw = ld_nc_u16(scp + i * 2u);
-                    if constexpr (T::has_min) slot.ddw = ld_nc_u16(supp + (i >> 3) * 4u);
+                    if constexpr (FMT == Q5_1) slot.smw = ld_stream_u32(scp + i * 4u); // d | m << 16; d is the f16 scale
+                    else slot.smw = ld_nc_u16(scp + i * 2u);
+                    if constexpr (T::has_min && T::sup_scale) slot.ddw = ld_nc_u16(supp + (i >> 3) * 4u);
                     if constexpr (FMT == Q6_K) slot.ddw = ld_nc_u16(supp + (i >> 3) * 2u);
                 }
             };
@@ -411,7 +412,16 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
 #pragma unroll
                         for (int c = 0; c < 4; c++) {
                             uint32_t h[4] = {0u, 0u, 0u, 0u};
-                            if (sb0 + c < pl.n_super) {
+                            if constexpr (FMT == Q5_1) {
+                                // the term is + m * xsum: the raw fp16 m of sub-blocks 8 * (sb0 + c) + 0..7
+#pragma unroll
+                                for (int u = 0; u < 4; u++) {
+                                    const uint32_t s0 = (sb0 + c) * 8u + 2u * u;
+                                    const uint32_t m_lo = s0 < n_sub ? ld_nc_u16(scp + s0 * 4u + 2u) : 0u;
+                                    const uint32_t m_hi = s0 + 1u < n_sub ? ld_nc_u16(scp + (s0 + 1u) * 4u + 2u) : 0u;
+                                    h[u] = m_lo | (m_hi << 16);
+                                }
+                            } else if (sb0 + c < pl.n_super) {
                                 const uint32_t dmin_bits = ld_nc_u16(supp + (sb0 + c) * 4u + 2u);
                                 const __half2 ndm = __hneg2(h2_from_bits(dmin_bits));
 #pragma unroll
@@ -706,7 +716,7 @@ int g_deq_debug = 0;
 
 int mmq_deq_set_attributes()
 {
-    return set_attr_deq<Q4_0>() | set_attr_deq<Q8_0>() | set_attr_deq<Q4_K>() | set_attr_deq<Q5_K>() | set_attr_deq<Q6_K>() |
+    return set_attr_deq<Q4_0>() | set_attr_deq<Q5_1>() | set_attr_deq<Q8_0>() | set_attr_deq<Q4_K>() | set_attr_deq<Q5_K>() | set_attr_deq<Q6_K>() |
            set_attr_deq<IQ4_XS>() | set_attr_deq<IQ3_S>();
 }
 
@@ -763,6 +773,7 @@ int launch_mmq_deq_f32(cudaStream_t s, int type, const void *w, const float *x, 
     const uint32_t bn = g_deq_bn ? (uint32_t)g_deq_bn : n_tok > 256u ? 512u : n_tok > 128u ? 256u : 128u;
     switch (type) {
     case Q4_0: return launch_deq_bn<Q4_0>(s, P, bn);
+    case Q5_1: return launch_deq_bn<Q5_1>(s, P, bn);
     case Q8_0: return launch_deq_bn<Q8_0>(s, P, bn);
     case Q4_K: return launch_deq_bn<Q4_K>(s, P, bn);
     case Q5_K: return launch_deq_bn<Q5_K>(s, P, bn);
@@ -813,6 +824,7 @@ int launch_mmq_deq_grouped_f32(cudaStream_t s, int type, const void *slab, size_
     P.debug = (uint32_t)g_deq_debug;
     switch (type) {
     case Q4_0: return launch_deq_grouped<Q4_0>(s, P);
+    case Q5_1: return launch_deq_grouped<Q5_1>(s, P);
     case Q8_0: return launch_deq_grouped<Q8_0>(s, P);
     case Q4_K: return launch_deq_grouped<Q4_K>(s, P);
     case Q5_K: return launch_deq_grouped<Q5_K>(s, P);

@@ -81,7 +81,11 @@ repack_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ out, uint32
             for (int k = 0; k < 16; k++) v[k] = 0;
             store16(nib + i * 16, v);
             if (OUT == Q8_0) store16(out + q * 16 + i * 16, v);
-            if (OUT == Q5_K) *reinterpret_cast<uint32_t *>(out + q * 16 + i * 4) = 0;
+            if (OUT == Q5_K || OUT == Q5_1) *reinterpret_cast<uint32_t *>(out + q * 16 + i * 4) = 0;
+            if (OUT == Q5_1) { // d | m word
+                *reinterpret_cast<uint32_t *>(out + q * 20 + i * 4) = 0;
+                continue;
+            }
             if (OUT == Q6_K) *reinterpret_cast<uint2 *>(out + q * 16 + i * 8) = make_uint2(0, 0);
             const size_t sc_off = OUT == Q8_0 ? q * 32 : OUT == Q5_K ? q * 20 : OUT == Q6_K ? q * 24 : q * 16;
             *reinterpret_cast<uint16_t *>(out + sc_off + i * 2) = 0;
@@ -93,6 +97,23 @@ repack_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ out, uint32
             for (int k = 0; k < 16; k++) v[k] = b[2 + k];
             store16(nib + i * 16, v);
             *reinterpret_cast<uint16_t *>(out + q * 16 + i * 2) = (uint16_t)rd16(b);
+        } else if (FMT == Q5_1) {
+            // src/quant/q5_1.rs:62-100: nibbles verbatim (already weight k low / k+16 high); 5th bits
+            // regrouped so that bit 4g+b belongs to dp4a group g lane b (group 2j = weights 4j.., group
+            // 2j+1 = weights 16+4j..); d and m kept as raw fp16
+            const uint8_t *b = src + ((size_t)row * n_sub + sb) * 24;
+#pragma unroll
+            for (int k = 0; k < 16; k++) v[k] = b[8 + k];
+            store16(nib + i * 16, v);
+            const uint32_t qh = rd16(b + 4) | (rd16(b + 6) << 16);
+            uint32_t packed = 0;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                packed |= ((qh >> (4 * j)) & 0xFu) << (8 * j);
+                packed |= ((qh >> (16 + 4 * j)) & 0xFu) << (8 * j + 4);
+            }
+            *reinterpret_cast<uint32_t *>(out + q * 16 + i * 4) = packed;
+            *reinterpret_cast<uint32_t *>(out + q * 20 + i * 4) = rd16(b) | (rd16(b + 2) << 16);
         } else if (FMT == SRC_BF16) {
             // requantization to Q8_0 (src/quant/q8_0.rs:45-61): d = amax / 127 (kept as f16),
             // q = round-half-away(v * (1 / d)) clamped to +-127
@@ -243,6 +264,7 @@ int launch_repack(cudaStream_t s, int type, const void *blocks, size_t in_dim, s
     uint8_t *dst = (uint8_t *)out;
     switch (type) {
     case Q4_0: repack_kernel<Q4_0><<<grid, 256, 0, s>>>(src, dst, (uint32_t)in_dim, (uint32_t)out_dim); break;
+    case Q5_1: repack_kernel<Q5_1><<<grid, 256, 0, s>>>(src, dst, (uint32_t)in_dim, (uint32_t)out_dim); break;
     case Q8_0: repack_kernel<Q8_0><<<grid, 256, 0, s>>>(src, dst, (uint32_t)in_dim, (uint32_t)out_dim); break;
     case Q4_K: repack_kernel<Q4_K><<<grid, 256, 0, s>>>(src, dst, (uint32_t)in_dim, (uint32_t)out_dim); break;
     case Q5_K: repack_kernel<Q5_K><<<grid, 256, 0, s>>>(src, dst, (uint32_t)in_dim, (uint32_t)out_dim); break;

@@ -273,7 +273,7 @@ __device__ __forceinline__ void expand_f16(const uint4 &q, const uint4 &q2, uint
     if constexpr (FMT == Q4_K || FMT == Q4_0) {
 #pragma unroll
         for (int j = 0; j < 4; j++) { lo[j] = w[j] & M; hi[j] = (w[j] >> 4) & M; }
-    } else if constexpr (FMT == Q5_K) {
+    } else if constexpr (FMT == Q5_K || FMT == Q5_1) {
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             lo[j] = (w[j] & M) | bits4_to_bit4(extra0 >> (8 * j));
@@ -322,7 +322,7 @@ __device__ __forceinline__ void expand_f16(const uint4 &q, const uint4 &q2, uint
         out[0][0] = scale(u0, x_lo); out[0][1] = scale(u1, x_lo); out[0][2] = scale(u2, x_hi); out[0][3] = scale(u3, x_hi);
         out[1][0] = scale(u0, y_lo); out[1][1] = scale(u1, y_lo); out[1][2] = scale(u2, y_hi); out[1][3] = scale(u3, y_hi);
     } else {
-        const float bias = (FMT == Q4_0) ? -1032.0f : -1152.0f; // remove 1024 and the format's offset (8 or 128)
+        const float bias = (FMT == Q4_0) ? -1032.0f : (FMT == Q5_1) ? -1024.0f : -1152.0f; // remove 1024 and the format's offset (8, none, or 128)
         const __half2 one = __half2half2(__float2half(1.0f)), off = __half2half2(__float2half(bias));
         out[0][0] = kc_block(lo[0], lo[1], one, off);
         out[0][1] = kc_block(lo[2], lo[3], one, off);

@@ -200,6 +200,7 @@ def router_topk(logits: np.ndarray, n_used: int):
     return ids, wts
 
 
+Q5_1 = 7    # the Q5_K kernel bodies with dsc = d, deff = -m (src/quant/q5_1.rs:11-20)
 IQ3_S = 21  # kernel type only: IQ4_XS planes read through the codebook 2n - 15 (src/quant/iq3_s.rs:193-214)
 Q3_K, IQ4_NL, BF16 = 11, 20, 30  # source-only types, relabelled onto Q6_K / IQ4_XS / Q8_0
 SRC_BLOCK = {Q3_K: (256, 110), IQ4_NL: (32, 18), BF16: (1, 2)}  # weights, bytes per source block

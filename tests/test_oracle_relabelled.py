@@ -145,3 +145,67 @@ def test_iq3s_kernel_type_is_iq4xs_planes_with_linear_codebook():
     xd = ro.dequantize_q8(xq, in_dim, rows).astype(np.float64)
     assert ro.rel_l2(y64, xd @ w.T) < 1e-6
     assert ro.rel_l2(y32, y64) < 1e-5
+
+
+def test_q5_1_repack_is_bit_exact_against_dequant():
+    """repack_is_bit_exact_against_dequant (q5_1.rs:108-157): in_dim 256 (nsp = 9), 5 rows,
+    d = 0.01 * (b + 1), m = -0.1 * (b % 7), the other 20 bytes of every block from the test's LCG;
+    reading the planes back the way the kernels do (nibble k low / k + 16 high, qh bit 4g + b,
+    dsc = d, deff = -m) reproduces the direct decode bit for bit."""
+    in_dim, out_dim, n_sub = 256, 5, 8
+    nsp = ro.nsp(in_dim)
+    assert nsp == 9
+    seed = 0x05100001
+    raw = np.empty(out_dim * n_sub * 24, dtype=np.uint8)
+    for b in range(out_dim * n_sub):
+        o = b * 24
+        d = np.float32(0.01) * (np.float32(b) + np.float32(1.0))
+        m = np.float32(-0.1) * np.float32(b % 7)
+        raw[o:o + 2] = np.frombuffer(np.uint16(ro.f32_to_f16(float(d))).tobytes(), dtype=np.uint8)
+        raw[o + 2:o + 4] = np.frombuffer(np.uint16(ro.f32_to_f16(float(m))).tobytes(), dtype=np.uint8)
+        raw[o + 4:o + 24], seed = lcg_bytes(seed, 20)
+    assert ro.block_bytes(ro.Q5_1) == 24 and ro.block_weights(ro.Q5_1) == 32
+    direct = ro.dequantize(ro.Q5_1, raw, in_dim * out_dim).reshape(out_dim, in_dim)
+    packed = ro.repack(ro.Q5_1, raw, in_dim, out_dim)
+    nib_len, qh_len = out_dim * nsp * 16, out_dim * nsp * 4
+    assert packed.size == nib_len + qh_len + out_dim * nsp * 4 == ro.repacked_len(ro.Q5_1, in_dim, out_dim)
+    for row in range(out_dim):
+        for sb in range(n_sub):
+            i = row * nsp + sb
+            nib = packed[i * 16:i * 16 + 16]
+            qh = int.from_bytes(packed[nib_len + i * 4:nib_len + i * 4 + 4].tobytes(), "little")
+            dm = nib_len + qh_len + i * 4
+            dsc = np.float32(ro.f16_to_f32(int(packed[dm]) | (int(packed[dm + 1]) << 8)))
+            deff = -np.float32(ro.f16_to_f32(int(packed[dm + 2]) | (int(packed[dm + 3]) << 8)))
+            for w in range(32):
+                g, b = w // 4, w % 4
+                byte = int(nib[(g // 2) * 4 + b])
+                q5 = ((byte & 15) if g % 2 == 0 else (byte >> 4)) | (((qh >> (4 * g + b)) & 1) << 4)
+                widx = (g // 2) * 4 + b if g % 2 == 0 else 16 + (g // 2) * 4 + b
+                assert dsc * np.float32(q5) - deff == direct[row, sb * 32 + widx], (row, sb, widx)
+        assert np.all(packed[(row * nsp + 8) * 16:(row * nsp + 9) * 16] == 0)   # the pad sub-block
+
+
+def test_q5_1_matvec_oracle_against_dequantized_weights():
+    """The Q5_K body with dsc = d, deff = -m (kernels/moe_matvec_q5k_repacked.cpp:86-101) gives the
+    dequantized weights times the dequantized activations: d * q5 . x + m * sum(x)."""
+    from reinstinct_b200 import synth
+    in_dim, out_dim, rows = 160, 23, 2          # five sub-blocks: not a multiple of 256
+    raw = synth.synth_blocks(ro.Q5_1, in_dim, out_dim, seed=51, signed_scales=True)
+    x = np.random.default_rng(52).standard_normal((rows, in_dim)).astype(np.float32)
+    xq = ro.quantize_q8(x)
+    planes = ro.repack(ro.Q5_1, raw, in_dim, out_dim)
+    y32, y64, _ = ro.matvec_q8(ro.Q5_1, planes, xq, in_dim, out_dim, rows)
+    w = ro.dequantize(ro.Q5_1, raw, in_dim * out_dim).reshape(out_dim, in_dim).astype(np.float64)
+    # the kernel's "- deff * xsum" uses the sum of the UNquantized activations of the block
+    recs = xq.reshape(rows, in_dim // 32, 40)
+    dx = recs[:, :, 0:4].copy().view(np.float32)[..., 0].astype(np.float64)
+    xsum = recs[:, :, 4:8].copy().view(np.float32)[..., 0].astype(np.float64)
+    q = recs[:, :, 8:].view(np.int8).astype(np.float64)
+    blocks = raw.reshape(out_dim, in_dim // 32, 24)
+    d = blocks[:, :, 0:2].copy().view(np.float16)[..., 0].astype(np.float64)
+    m = blocks[:, :, 2:4].copy().view(np.float16)[..., 0].astype(np.float64)
+    q5 = ((w.reshape(out_dim, -1, 32) - m[..., None]) / np.where(d == 0, 1, d)[..., None]).round()
+    want = np.einsum("os,rs,osk,rsk->ro", d, dx, q5, q) + np.einsum("os,rs->ro", m, xsum)
+    assert ro.rel_l2(y64, want) < 1e-6
+    assert ro.rel_l2(y32, y64) < 1e-5
