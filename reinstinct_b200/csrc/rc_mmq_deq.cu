@@ -99,17 +99,23 @@ template <int FMT> struct DeqTraits {
 };
 
 template <int BN> struct DeqCfg {
-    static constexpr uint32_t stages = BN == 512 ? 4 : 8;
+    // Sub-blocks (K = 32 each) per operand-ring stage.  A ring hand-over costs about 0.25 us whatever it
+    // carries; at the 32-column expert tiles the MMAs of one sub-block last a tenth of that, so a stage
+    // carries four of them and the hand-overs per tile drop fourfold.
+    static constexpr uint32_t ks = BN == 32 ? 4 : 1;
+    static constexpr uint32_t stages = (BN == 512 || BN == 32) ? 4 : 8;
     static constexpr uint32_t bufs = 512 / BN;
 };
 
 template <int FMT, int BN> struct SmemD {
     static constexpr uint32_t stages = DeqCfg<BN>::stages;
     // the raw weight planes come from HBM and run far ahead of the operand ring, in a ring of their own
-    static constexpr uint32_t raw_stages = (BN >= 256 && FMT == Q8_0) ? 8 : 16;
-    static constexpr uint32_t raw_stage = DeqTraits<FMT>::raw_bytes;
-    static constexpr uint32_t a_stage = kBM * 64;  // 128 rows x 32 halves: [chunk 0..3][row][16 B]
-    static constexpr uint32_t b_stage = BN * 64;   // BN tokens x 32 halves: [chunk 0..3][token][16 B]
+    static constexpr uint32_t ks = DeqCfg<BN>::ks;
+    // (a raw stage, like an operand stage, holds ks sub-blocks: [sub-slot][plane][row][16 B])
+    static constexpr uint32_t raw_stages = ks > 1 ? (FMT == Q8_0 ? 2 : 4) : (BN >= 256 && FMT == Q8_0) ? 8 : 16;
+    static constexpr uint32_t raw_stage = ks * DeqTraits<FMT>::raw_bytes;
+    static constexpr uint32_t a_stage = ks * kBM * 64;  // 128 rows x 32 ks halves: [chunk 0..4 ks - 1][row][16 B]
+    static constexpr uint32_t b_stage = ks * BN * 64;   // BN tokens x 32 ks halves: [chunk 0..4 ks - 1][token][16 B]
     static constexpr uint32_t raw_off = 0;
     static constexpr uint32_t a_off = raw_off + raw_stages * raw_stage;
     static constexpr uint32_t b_off = a_off + stages * a_stage;
@@ -190,11 +196,12 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
 {
     using L = SmemD<FMT, BN>;
     using T = DeqTraits<FMT>;
-    constexpr uint32_t S = L::stages, R = L::raw_stages, NB = DeqCfg<BN>::bufs;
+    constexpr uint32_t S = L::stages, R = L::raw_stages, NB = DeqCfg<BN>::bufs, KS = L::ks;
     constexpr bool kAllDrain = (NB == 1);
     constexpr uint32_t kDrainWarps = kAllDrain ? kExpWarps + kEpiWarps : kEpiWarps;
     constexpr uint32_t kExpanders = 4; // arrivals per stage: lane 0 of each warp of one expander group
-    static_assert(L::stages % kExpGroups == 0 && L::raw_stages % kExpGroups == 0, "a stage always belongs to the same expander group");
+    static_assert(KS > 1 || (L::stages % kExpGroups == 0 && L::raw_stages % kExpGroups == 0), "a stage always belongs to the same expander group");
+    static_assert(KS == 1 || KS == kExpGroups, "with several sub-blocks per stage, group g always fills sub-slot g");
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~(uintptr_t)1023u);
     const uint32_t sbase = smem_u32(smem);
@@ -213,19 +220,20 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
     if (trace && threadIdx.x == 0) g_mmqd_trace[blockIdx.x * 8 + 0] = global_ns();
     const uint32_t n_sub = P.in_dim >> 5;
     const uint32_t n_extra = T::has_min ? (n_sub + 31u) / 32u : 0u; // K=32 steps over the sub-block minima
-    const uint32_t n_iters = n_sub + n_extra;
+    const uint32_t n_real = n_sub + n_extra;
+    const uint32_t n_iters = (n_real + KS - 1u) / KS * KS; // per tile; steps past n_real carry zero weights (the image's zero tail as B)
     const uint32_t tiles_m = (P.out_dim + kBM - 1) / kBM;
     const uint32_t tiles_n = GR ? (uint32_t)P.tile_off[P.n_expert] : (P.n_tok + BN - 1) / BN; // grouped: known on the device only
     const uint32_t n_tiles = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < S; s++) {
-            mbar_init(op_full(s), kExpanders + 1); // expanders (A) + the producer's expect_tx (B)
+            mbar_init(op_full(s), KS * kExpanders + 1); // expanders (A) of every sub-slot + the producer's expect_tx (B)
             mbar_init(op_empty(s), 1);             // the commit after the stage's MMAs
         }
         for (uint32_t s = 0; s < R; s++) {
             mbar_init(raw_full(s), 1);
-            mbar_init(raw_empty(s), kExpanders);
+            mbar_init(raw_empty(s), KS * kExpanders);
         }
         for (uint32_t b = 0; b < NB; b++) {
             mbar_init(tm_full(b), 1);
@@ -283,47 +291,79 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
     // drained, so the expander warps drain too: five warps per lane quarter.
 
     if (warp == 0) {
-        // ---- activation producer: chunks 4i..4i+3 of the image per K step, by bulk copies -------------
-        if (lane == 0) {
-            uint32_t it = 0;
-            for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x) {
+        if constexpr (KS == 1) {
+            // ---- activation producer: chunks 4i..4i+3 of the image per K step, by bulk copies -------------
+            if (lane == 0) {
+                uint32_t it = 0;
+                for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x) {
+                    const uint32_t tok0 = deq_tile<BN, GR>(P, id, tiles_m).tok0;
+                    const uint32_t n_rows_b = min((uint32_t)BN, P.tok_ld - tok0); // rows present in the image (a grouped tile may
+                                                                                  // take the next expert's first rows along: unused columns)
+                    for (uint32_t i = 0; i < n_iters; i++, it++) {
+                        const uint32_t s = it % S;
+                        if (it >= S && !mbar_spin_d(op_empty(s), ((it / S) - 1u) & 1u, abort_flag, 2u)) goto prod_done;
+                        if (P.debug & 2u) {
+                            mbar_arrive(op_full(s));
+                            continue;
+                        }
+                        mbar_expect_tx(op_full(s), 4u * n_rows_b * 16u);
+                        // (the xsum chunks follow the main ones seamlessly)
+                        const uint8_t *src = P.xh + ((size_t)(4u * i) * P.tok_ld + tok0) * 16u;
+                        for (uint32_t c = 0; c < 4; c++)
+                            bulk_load(sbase + L::b_off + s * L::b_stage + c * BN * 16u, src + (size_t)c * P.tok_ld * 16u,
+                                      n_rows_b * 16u, op_full(s));
+                    }
+                }
+            prod_done:;
+            }
+        } else {
+            // ---- activation producer: chunks 4i .. 4(i + KS) - 1 of the image per stage, one bulk copy per lane ----
+            uint32_t m = 0; // stages issued
+            bool ok = true;
+            for (uint32_t id = blockIdx.x; id < n_tiles; id += gridDim.x) {
+                if (lane == 0 && *abort_flag) ok = false;
+                ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                if (!ok) break;
                 const uint32_t tok0 = deq_tile<BN, GR>(P, id, tiles_m).tok0;
                 const uint32_t n_rows_b = min((uint32_t)BN, P.tok_ld - tok0); // rows present in the image (a grouped tile may
                                                                               // take the next expert's first rows along: unused columns)
-                for (uint32_t i = 0; i < n_iters; i++, it++) {
-                    const uint32_t s = it % S;
-                    if (it >= S && !mbar_spin_d(op_empty(s), ((it / S) - 1u) & 1u, abort_flag, 2u)) goto prod_done;
-                    if (P.debug & 2u) {
-                        mbar_arrive(op_full(s));
-                        continue;
+                for (uint32_t i = 0; i < n_iters; i += KS, m++) {
+                    const uint32_t s = m % S;
+                    if (lane == 0) {
+                        if (m >= S && !mbar_spin_d(op_empty(s), ((m / S) - 1u) & 1u, abort_flag, 2u)) ok = false;
+                        else if (P.debug & 2u) mbar_arrive(op_full(s));
+                        else mbar_expect_tx(op_full(s), 4u * KS * n_rows_b * 16u);
                     }
-                    mbar_expect_tx(op_full(s), 4u * n_rows_b * 16u);
-                    // (the xsum chunks follow the main ones seamlessly)
-                    const uint8_t *src = P.xh + ((size_t)(4u * i) * P.tok_ld + tok0) * 16u;
-                    for (uint32_t c = 0; c < 4; c++)
-                        bulk_load(sbase + L::b_off + s * L::b_stage + c * BN * 16u, src + (size_t)c * P.tok_ld * 16u,
-                                  n_rows_b * 16u, op_full(s));
+                    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+                    if (!ok) break;
+                    // (the xsum chunks and the zero tail follow the main ones seamlessly)
+                    if (!(P.debug & 2u) && lane < 4u * KS)
+                        bulk_load(sbase + L::b_off + s * L::b_stage + lane * BN * 16u,
+                                  P.xh + ((size_t)(4u * i + lane) * P.tok_ld + tok0) * 16u, n_rows_b * 16u, op_full(s));
                 }
+                if (!ok) break;
             }
-        prod_done:;
         }
     } else if (warp == 2) {
-        // ---- raw weight producer: one 16-byte x 128-row box per plane and K step, by tiled TMA ---------
+        // ---- raw weight producer: one 16-byte x 128-row box per plane and sub-block, by tiled TMA; one
+        // barrier round per stage of KS sub-blocks ----------------------------------------------------------
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t m = 0; // stages issued
             for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x) {
                 const DeqTile tl = deq_tile<BN, GR>(P, id, tiles_m);
                 const uint32_t m0 = tl.m0;
-                for (uint32_t i = 0; i < n_iters; i++, it++) {
-                    const uint32_t s = it % R;
-                    if (it >= R && !mbar_spin_d(raw_empty(s), ((it / R) - 1u) & 1u, abort_flag, 1u)) goto raw_done;
-                    if (i < n_sub && !(P.debug & 8u)) {
-                        mbar_expect_tx(raw_full(s), T::raw_bytes);
-                        for (int pl = 0; pl < T::raw_planes; pl++)
-                            tma_load_4d(sbase + L::raw_off + s * L::raw_stage + pl * kBM * 16, &tmap, raw_full(s),
-                                        (int)(i * 16u), (int)m0, pl, (int)tl.e);
+                for (uint32_t i = 0; i < n_iters; i += KS, m++) {
+                    const uint32_t s = m % R;
+                    if (m >= R && !mbar_spin_d(raw_empty(s), ((m / R) - 1u) & 1u, abort_flag, 1u)) goto raw_done;
+                    const uint32_t n_raw = i < n_sub ? min((uint32_t)KS, n_sub - i) : 0u; // sub-blocks with weights in this stage
+                    if (n_raw && !(P.debug & 8u)) {
+                        mbar_expect_tx(raw_full(s), n_raw * T::raw_bytes);
+                        for (uint32_t j = 0; j < n_raw; j++)
+                            for (int pl = 0; pl < T::raw_planes; pl++)
+                                tma_load_4d(sbase + L::raw_off + s * L::raw_stage + j * T::raw_bytes + pl * kBM * 16, &tmap, raw_full(s),
+                                            (int)((i + j) * 16u), (int)m0, pl, (int)tl.e);
                     } else {
-                        mbar_arrive(raw_full(s)); // nothing raw in a minima step; keeps the ring in phase
+                        mbar_arrive(raw_full(s)); // nothing raw in a minima stage; keeps the ring in phase
                     }
                 }
             }
@@ -346,7 +386,7 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
                 if (tile >= NB && !mbar_spin_d(tm_empty(buf), ((tile / NB) - 1u) & 1u, abort_flag, 3u)) goto mma_done;
                 tc_fence_after();
                 const uint32_t d0 = tmem_base + buf * BN;
-                for (uint32_t i = 0; i < n_iters; i++, it++) {
+                for (uint32_t i = 0; i < n_iters; i += KS, it++) { // it counts stages here
                     const uint32_t s = it % S;
                     if (!mbar_test(op_full(s), (it / S) & 1u) && !mbar_spin_d(op_full(s), (it / S) & 1u, abort_flag, 4u)) goto mma_done;
                     tc_fence_after();
@@ -355,7 +395,7 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
                     const uint64_t db = db0 + (uint64_t)(s * (L::b_stage >> 4));
                     if (do_mma) {
 #pragma unroll
-                        for (uint32_t kh = 0; kh < 2; kh++) {
+                        for (uint32_t kh = 0; kh < 2 * KS; kh++) { // K = 16 per instruction: two chunks
 #pragma unroll
                             for (uint32_t nh = 0; nh < BN / NI; nh++) {
                                 mma_f16(d0 + nh * NI, da + kh * ((2 * kBM * 16) >> 4), db + ((kh * 2 * BN * 16 + nh * NI * 16) >> 4), idesc,
@@ -403,10 +443,11 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
             auto step = [&](Side &slot, uint32_t i) -> bool {
                 const Side cur = slot;
                 request(slot, i + 3u * G);
-                const uint32_t it = tile_it0 + i, s = it % S, rs = it % R;
+                const uint32_t it = tile_it0 + i, mst = it / KS, s = mst % S, rs = mst % R;
                 uint4 o[4];
+                if (i >= n_sub) o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u); // minima steps fill it below; steps past the last are zero
                 if constexpr (T::has_min) {
-                    if (i >= n_sub) {
+                    if (i >= n_sub && i < n_real) {
                         // minima step: chunk c = superblock (i - n_sub) * 4 + c, one half per sub-block: -dmin * m
                         const uint32_t sb0 = (i - n_sub) * 4u;
 #pragma unroll
@@ -437,9 +478,9 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
                         }
                     }
                 }
-                if (!mbar_wait_d(raw_full(rs), (it / R) & 1u, abort_flag, 6u)) return false;
+                if (!mbar_wait_d(raw_full(rs), (mst / R) & 1u, abort_flag, 6u)) return false;
                 if (i < n_sub && !(P.debug & 1u)) {
-                    const uint32_t rp = sbase + L::raw_off + rs * L::raw_stage + r * 16u;
+                    const uint32_t rp = sbase + L::raw_off + rs * L::raw_stage + (it % KS) * T::raw_bytes + r * 16u;
                     const uint4 q = lds_u4(rp);
                     uint4 q2 = make_uint4(0, 0, 0, 0);
                     if constexpr (FMT == Q8_0) q2 = lds_u4(rp + kBM * 16);
@@ -454,8 +495,8 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
                     }
                 }
                 // the operand slot is needed only now: the expansion above ran while its MMAs finished
-                if (it >= S && !mbar_wait_d(op_empty(s), ((it / S) - 1u) & 1u, abort_flag, 5u)) return false;
-                const uint32_t ap = sbase + L::a_off + s * L::a_stage + r * 16u;
+                if (mst >= S && !mbar_wait_d(op_empty(s), ((mst / S) - 1u) & 1u, abort_flag, 5u)) return false;
+                const uint32_t ap = sbase + L::a_off + s * L::a_stage + (it % KS) * (4u * kBM * 16u) + r * 16u;
 #pragma unroll
                 for (int c = 0; c < 4; c++) sts_u4(ap + c * kBM * 16, o[c]);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -658,10 +699,13 @@ __global__ void __launch_bounds__(kActWarps * 32) activations_to_f16_kernel(cons
         }
 }
 
+// Chunks after the main ones: the sub-block sums (eight per chunk, a whole K = 32 step of four chunks at a
+// time), then zero chunks up to a whole stage of the widest ring (four sub-blocks).
 uint32_t xchunks_of(uint32_t in_dim)
 {
     const uint32_t n_sub = in_dim >> 5;
-    return (((n_sub + 7u) / 8u) + 3u) & ~3u;
+    const uint32_t steps = (n_sub + (n_sub + 31u) / 32u + 3u) & ~3u; // K = 32 steps of a tile, with the minima, padded
+    return 4u * (steps - n_sub);
 }
 uint32_t tok_ld_of(uint32_t n_tok) { return (n_tok + 7u) & ~7u; }
 
