@@ -192,7 +192,7 @@ __device__ __forceinline__ DeqTile deq_tile(const DeqParams &P, uint32_t id, uin
 }
 
 template <int FMT, int BN, bool GR>
-__global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_constant__ CUtensorMap tmap, const DeqParams P)
+__global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap bmap, const DeqParams P)
 {
     using L = SmemD<FMT, BN>;
     using T = DeqTraits<FMT>;
@@ -317,31 +317,26 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
             prod_done:;
             }
         } else {
-            // ---- activation producer: chunks 4i .. 4(i + KS) - 1 of the image per stage, one bulk copy per lane ----
-            uint32_t m = 0; // stages issued
-            bool ok = true;
-            for (uint32_t id = blockIdx.x; id < n_tiles; id += gridDim.x) {
-                if (lane == 0 && *abort_flag) ok = false;
-                ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-                if (!ok) break;
-                const uint32_t tok0 = deq_tile<BN, GR>(P, id, tiles_m).tok0;
-                const uint32_t n_rows_b = min((uint32_t)BN, P.tok_ld - tok0); // rows present in the image (a grouped tile may
-                                                                              // take the next expert's first rows along: unused columns)
-                for (uint32_t i = 0; i < n_iters; i += KS, m++) {
-                    const uint32_t s = m % S;
-                    if (lane == 0) {
-                        if (m >= S && !mbar_spin_d(op_empty(s), ((m / S) - 1u) & 1u, abort_flag, 2u)) ok = false;
-                        else if (P.debug & 2u) mbar_arrive(op_full(s));
-                        else mbar_expect_tx(op_full(s), 4u * KS * n_rows_b * 16u);
+            // ---- activation producer, KS > 1: chunks 4i .. 4(i + KS) - 1 of the image per stage in ONE tiled TMA
+            // load (box 16 B x BN tokens x 4 KS chunks of the 3-D view in bmap; sixteen separate bulk copies per
+            // stage were on the critical path of the narrow tiles).  The image has a whole tile of spare rows
+            // and a zero tail of chunks, so no box leaves it.
+            if (lane == 0) {
+                uint32_t m = 0; // stages issued
+                for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x) {
+                    const uint32_t tok0 = deq_tile<BN, GR>(P, id, tiles_m).tok0;
+                    for (uint32_t i = 0; i < n_iters; i += KS, m++) {
+                        const uint32_t s = m % S;
+                        if (m >= S && !mbar_spin_d(op_empty(s), ((m / S) - 1u) & 1u, abort_flag, 2u)) goto prod4_done;
+                        if (P.debug & 2u) {
+                            mbar_arrive(op_full(s));
+                            continue;
+                        }
+                        mbar_expect_tx(op_full(s), L::b_stage);
+                        tma_load_3d(sbase + L::b_off + s * L::b_stage, &bmap, op_full(s), 0, (int)tok0, (int)(4u * i));
                     }
-                    ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-                    if (!ok) break;
-                    // (the xsum chunks and the zero tail follow the main ones seamlessly)
-                    if (!(P.debug & 2u) && lane < 4u * KS)
-                        bulk_load(sbase + L::b_off + s * L::b_stage + lane * BN * 16u,
-                                  P.xh + ((size_t)(4u * i + lane) * P.tok_ld + tok0) * 16u, n_rows_b * 16u, op_full(s));
                 }
-                if (!ok) break;
+            prod4_done:;
             }
         }
     } else if (warp == 2) {
@@ -717,7 +712,7 @@ int launch_deq(cudaStream_t s, const DeqParams &P)
     if (rc) return rc;
     const uint32_t tiles = ((P.out_dim + kBM - 1) / kBM) * ((P.n_tok + BN - 1) / BN);
     const uint32_t grid = min(tiles, (uint32_t)sm_count());
-    return (int)launch_pdl(mmqd_kernel<FMT, BN, false>, dim3(grid), dim3(kDeqThreads), SmemD<FMT, BN>::total, s, map, P);
+    return (int)launch_pdl(mmqd_kernel<FMT, BN, false>, dim3(grid), dim3(kDeqThreads), SmemD<FMT, BN>::total, s, map, map, P); // (no image map: bulk copies)
 }
 
 constexpr int kGroupedDeqBN = 32; // the expert tile of rc_moe_sort
@@ -731,8 +726,22 @@ int launch_deq_grouped(cudaStream_t s, const DeqParams &P)
     // the tile count lives on the device (tile_off[n_expert]); this is its upper bound
     const uint64_t tiles = (uint64_t)((P.out_dim + kBM - 1) / kBM) * ((P.n_tok + kGroupedDeqBN - 1) / kGroupedDeqBN + P.n_expert);
     const uint32_t grid = (uint32_t)std::min<uint64_t>(tiles, (uint64_t)sm_count());
+    // 3-D view of the activation image: (16 bytes of a chunk, image row, chunk); one box = a stage of the B ring
+    CUtensorMap bmap;
+    {
+        EncodeTiledFn fn = encode_fn();
+        if (!fn) return RC_ERR_NO_DEVICE;
+        const uint64_t n_chunks = (uint64_t)(P.in_dim >> 3) + xchunks_of(P.in_dim);
+        const cuuint64_t dims[3] = {16, P.tok_ld, n_chunks};
+        const cuuint64_t strides[2] = {16, (cuuint64_t)P.tok_ld * 16u};
+        const cuuint32_t box[3] = {16, (cuuint32_t)kGroupedDeqBN, 4u * DeqCfg<kGroupedDeqBN>::ks};
+        const cuuint32_t estr[3] = {1, 1, 1};
+        if (fn(&bmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t *>(P.xh), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return RC_ERR_BAD_ARGUMENT;
+    }
     return (int)launch_pdl(mmqd_kernel<FMT, kGroupedDeqBN, true>, dim3(grid), dim3(kDeqThreads), SmemD<FMT, kGroupedDeqBN>::total, s,
-                           map, P);
+                           map, bmap, P);
 }
 
 template <int FMT>
