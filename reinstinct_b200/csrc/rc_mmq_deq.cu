@@ -161,6 +161,26 @@ __device__ __forceinline__ __half2 h2_from_bits(uint32_t bits16)
     return u32_as_h2(b | (b << 16));
 }
 
+// Q6_K for this kernel: (q - 32) as an exact f16 integer, times f16(d * sc) of its 16-weight half.  Two
+// roundings per weight (the half's scale, the product) like the exact two-part form of expand_f16 (whose
+// sum rounds beyond 2048, then the product with d), at two thirds of its instructions: the expanders
+// bound this format's steps.
+__device__ __forceinline__ void expand_q6k_scaled(const uint4 &q, uint32_t e0, uint32_t e1, uint32_t sm, uint32_t d_bits, uint4 (&o)[4])
+{
+    const uint32_t M = 0x0F0F0F0Fu;
+    uint32_t g[8];
+    spread_fields4(e0, g[0], g[1], g[2], g[3]);
+    spread_fields4(e1, g[4], g[5], g[6], g[7]);
+    const float d = f16_bits_to_f32(d_bits);
+    const __half2 s_lo = __float2half2_rn(d * (float)(int)(int8_t)(sm & 0xFFu));
+    const __half2 s_hi = __float2half2_rn(d * (float)(int)(int8_t)((sm >> 8) & 0xFFu));
+    const __half2 one = __half2half2(__float2half(1.0f)), off = __half2half2(__float2half(-1056.0f)); // 1024 + q -> q - 32
+    o[0] = mul_h2x4(kc_block((q.x & M) | g[0], (q.y & M) | g[2], one, off), s_lo);
+    o[1] = mul_h2x4(kc_block((q.z & M) | g[4], (q.w & M) | g[6], one, off), s_lo);
+    o[2] = mul_h2x4(kc_block(((q.x >> 4) & M) | g[1], ((q.y >> 4) & M) | g[3], one, off), s_hi);
+    o[3] = mul_h2x4(kc_block(((q.z >> 4) & M) | g[5], ((q.w >> 4) & M) | g[7], one, off), s_hi);
+}
+
 struct DeqTile {
     uint32_t m0, tok0, n_valid, e;
 };
@@ -479,14 +499,14 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
                     const uint4 q = lds_u4(rp);
                     uint4 q2 = make_uint4(0, 0, 0, 0);
                     if constexpr (FMT == Q8_0) q2 = lds_u4(rp + kBM * 16);
-                    uint4 t[2][4];
-                    expand_f16<FMT>(q, q2, cur.e0, cur.e1, cur.smw, t); // exact integers: sc * q, q - 8, q, codebook value
-                    const __half2 sc = h2_from_bits(T::sup_scale ? cur.ddw : cur.smw);
+                    if constexpr (FMT == Q6_K) {
+                        expand_q6k_scaled(q, cur.e0, cur.e1, cur.smw, cur.ddw, o);
+                    } else {
+                        uint4 t[2][4];
+                        expand_f16<FMT>(q, q2, cur.e0, cur.e1, cur.smw, t); // exact integers: sc * q, q - 8, q, codebook value
+                        const __half2 sc = h2_from_bits(T::sup_scale ? cur.ddw : cur.smw);
 #pragma unroll
-                    for (int c = 0; c < 4; c++) {
-                        uint4 v = t[0][c];
-                        if constexpr (FMT == Q6_K) v = add_h2x4(v, t[1][c]); // the two exact parts of (q - 32) * sc
-                        o[c] = mul_h2x4(v, sc);
+                        for (int c = 0; c < 4; c++) o[c] = mul_h2x4(t[0][c], sc);
                     }
                 }
                 // the operand slot is needed only now: the expansion above ran while its MMAs finished
