@@ -372,11 +372,12 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
                     if (m >= R && !mbar_spin_d(raw_empty(s), ((m / R) - 1u) & 1u, abort_flag, 1u)) goto raw_done;
                     const uint32_t n_raw = i < n_sub ? min((uint32_t)KS, n_sub - i) : 0u; // sub-blocks with weights in this stage
                     if (n_raw && !(P.debug & 8u)) {
-                        mbar_expect_tx(raw_full(s), n_raw * T::raw_bytes);
-                        for (uint32_t j = 0; j < n_raw; j++)
-                            for (int pl = 0; pl < T::raw_planes; pl++)
-                                tma_load_4d(sbase + L::raw_off + s * L::raw_stage + j * T::raw_bytes + pl * kBM * 16, &tmap, raw_full(s),
-                                            (int)((i + j) * 16u), (int)m0, pl, (int)tl.e);
+                        // the map's box is 16 KS bytes wide: the stage's sub-blocks of a row in one load, landing
+                        // as [plane][row][16 KS bytes] (columns past the row's last sub-block arrive as padding)
+                        mbar_expect_tx(raw_full(s), L::raw_stage);
+                        for (int pl = 0; pl < T::raw_planes; pl++)
+                            tma_load_4d(sbase + L::raw_off + s * L::raw_stage + pl * (KS * kBM * 16), &tmap, raw_full(s), (int)(i * 16u), (int)m0,
+                                        pl, (int)tl.e);
                     } else {
                         mbar_arrive(raw_full(s)); // nothing raw in a minima stage; keeps the ring in phase
                     }
@@ -495,10 +496,10 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
                 }
                 if (!mbar_wait_d(raw_full(rs), (mst / R) & 1u, abort_flag, 6u)) return false;
                 if (i < n_sub && !(P.debug & 1u)) {
-                    const uint32_t rp = sbase + L::raw_off + rs * L::raw_stage + (it % KS) * T::raw_bytes + r * 16u;
+                    const uint32_t rp = sbase + L::raw_off + rs * L::raw_stage + r * (16u * KS) + (it % KS) * 16u;
                     const uint4 q = lds_u4(rp);
                     uint4 q2 = make_uint4(0, 0, 0, 0);
-                    if constexpr (FMT == Q8_0) q2 = lds_u4(rp + kBM * 16);
+                    if constexpr (FMT == Q8_0) q2 = lds_u4(rp + KS * kBM * 16);
                     if constexpr (FMT == Q6_K) {
                         expand_q6k_scaled(q, cur.e0, cur.e1, cur.smw, cur.ddw, o);
                     } else {
@@ -741,7 +742,7 @@ template <int FMT>
 int launch_deq_grouped(cudaStream_t s, const DeqParams &P)
 {
     CUtensorMap map;
-    int rc = make_tmap<FMT>(&map, P.w, P.bytes_per_expert, P.n_expert, P.in_dim, P.out_dim);
+    int rc = make_tmap<FMT>(&map, P.w, P.bytes_per_expert, P.n_expert, P.in_dim, P.out_dim, 16u * DeqCfg<kGroupedDeqBN>::ks);
     if (rc) return rc;
     // the tile count lives on the device (tile_off[n_expert]); this is its upper bound
     const uint64_t tiles = (uint64_t)((P.out_dim + kBM - 1) / kBM) * ((P.n_tok + kGroupedDeqBN - 1) / kGroupedDeqBN + P.n_expert);

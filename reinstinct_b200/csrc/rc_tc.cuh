@@ -242,9 +242,11 @@ inline EncodeTiledFn encode_fn()
 
 // 4-D view of the 16-byte planes of a repacked tensor (or slab of tensors):
 // (byte in row, row, plane, expert); one box = 16 bytes x 128 rows of one plane.
+// box_k: bytes of a row per box (16 = one sub-block; a multiple of 16 takes several sub-blocks at once and
+// lands as [row][box_k bytes]).
 template <int FMT>
 int make_tmap(CUtensorMap *map, const void *w, size_t bytes_per_expert, uint32_t n_expert, uint32_t in_dim,
-              uint32_t out_dim)
+              uint32_t out_dim, uint32_t box_k = 16)
 {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return RC_ERR_NO_DEVICE;
@@ -252,7 +254,7 @@ int make_tmap(CUtensorMap *map, const void *w, size_t bytes_per_expert, uint32_t
     const cuuint64_t dims[4] = {nsp * 16, out_dim, (cuuint64_t)(FMT == Q8_0 ? 2 : 1), n_expert};
     const uint64_t plane = (uint64_t)out_dim * nsp * 16;
     const cuuint64_t strides[3] = {nsp * 16, plane, n_expert > 1 ? (cuuint64_t)bytes_per_expert : plane * 2};
-    const cuuint32_t box[4] = {16, kBM, 1, 1};
+    const cuuint32_t box[4] = {box_k, kBM, 1, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(w), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
