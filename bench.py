@@ -349,6 +349,42 @@ def moe_expert_parallel(rt, synth, torch, dist, dev, timed, rank, world):
             "collectives": "NCCL all_to_all_single: counts, rows, expert ids, results (eager, host-driven)"}
 
 
+def mmq_prefill_row_sharded(rt, synth, torch, dist, dev, timed, rank, world):
+    """Config 4 sharded by output rows (N > 1): every rank holds rows [b, e) of the Q4_K 5120->17408 matrix
+    (multiples of 32 rows), runs the prefill GEMM of all 512 tokens against them, and the [512, e - b]
+    outputs are all-gathered (NCCL all_gather_into_tensor, eager) into [N, 512, widest shard]; no other
+    exchange.  Timed as the whole step, max over ranks; TOPS counts the whole 91.3 GOP."""
+    from reinstinct_b200 import sharding as sh
+
+    P = 512
+    raw = synth.synth_blocks(Q4_K, HIDDEN, FFN, seed=77)
+    shard, n_rows = sh.shard_raw_rows(raw, Q4_K, HIDDEN, FFN, rank, world)
+    w = rt.GpuMatvecTensor.from_bytes_matvec(shard.copy(), Q4_K, HIDDEN, n_rows, device=dev)
+    x = torch.from_numpy(synth.synth_activations(P, HIDDEN, 78)).to(dev)
+    gemm = rt.PrefillGemm(max_x=P * HIDDEN, device=dev)
+    widest = max(e - b for b, e in (sh.row_shard_range(FFN, r, world) for r in range(world)))
+    y = torch.zeros((P, widest), dtype=torch.float32, device=dev)
+    y_local = y if n_rows == widest else torch.empty((P, n_rows), dtype=torch.float32, device=dev)
+    gathered = torch.empty((world * P, widest), dtype=torch.float32, device=dev)
+
+    def step(i):
+        gemm.matmul_into(y_local, w, x, P)
+        if y_local is not y:
+            y[:, :n_rows] = y_local
+        dist.all_gather_into_tensor(gathered, y)
+
+    def gemm_only(i):
+        gemm.matmul_into(y_local, w, x, P)
+
+    reps = 10
+    us = timed(step, reps, 3) / reps * 1e3
+    us_gemm = timed(gemm_only, reps, 3) / reps * 1e3
+    ops = 2.0 * P * HIDDEN * FFN
+    return {"workload": f"config 4 row-sharded: 512 tokens x Q4_K 5120->17408, {n_rows} rows on rank 0 of {world}",
+            "us_step": us, "us_gemm_only": us_gemm, "tops": ops / (us * 1e-6) / 1e12,
+            "gather": f"NCCL all_gather_into_tensor of {P * widest * 4} bytes per rank (eager)"}
+
+
 def mmq_prefill(rt, synth, torch, dev, timed):
     """Config 4: dense prefill GEMM, 512 tokens x Q4_K 5120->17408, through PrefillGemm (f32
     activations in: f16 image + tcgen05 kind::f16 GEMM) and through the int8 entry point given
@@ -636,6 +672,13 @@ def run_gpu_arm(args):
         except Exception as e:  # the headline line must not depend on this extra
             moe_ep = {"error": f"{type(e).__name__}: {e}"}
 
+    mmq_rs = None
+    if world > 1 and not args.skip_mmq:
+        try:
+            mmq_rs = mmq_prefill_row_sharded(rt, synth, torch, dist, dev, timed, rank, world)
+        except Exception as e:
+            mmq_rs = {"error": f"{type(e).__name__}: {e}"}
+
     if rank == 0:
         peak, peak_kind = measured_peaks()
         achieved = q4k_bytes / (q4k_us * 1e-6) / 1e9
@@ -666,6 +709,8 @@ def run_gpu_arm(args):
             line["moe_grouped"] = moe
         if moe_ep is not None:
             line["moe_expert_parallel"] = moe_ep
+        if mmq_rs is not None:
+            line["mmq_prefill_row_sharded"] = mmq_rs
         if world == 1 and not args.no_cpu_baseline:
             v, sample, _ = cpu_layer_sample(seconds=12.0, threads=os.cpu_count() or 1)
             line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port",
