@@ -137,7 +137,8 @@ struct DeqParams {
     size_t bytes_per_expert;
     const int32_t *expert_off, *tile_off;
     uint32_t n_expert;
-    uint32_t debug; // measurement aid: pipeline parts to skip (results invalid): 1 expand, 2 activation copies, 4 MMAs, 8 raw loads; 128 records phase timestamps
+    uint32_t k_splits; // dense form only: work items per tile, each over a contiguous range of K steps, added into a zeroed y
+    uint32_t debug; // measurement aid: pipeline parts to skip (results invalid): 1 expand, 2 activation copies, 4 MMAs, 8 raw loads; 64 no K split (results valid); 128 records phase timestamps
 };
 
 constexpr int kExpGroups = 4;                // groups of four expander warps, one K step each in turn
@@ -188,14 +189,15 @@ struct DeqTile {
 // Tile id -> weight-row tile, first token row of the image, valid tokens, expert.  Dense: ids walk the
 // row tiles of one token tile after another.  Grouped: the same with global token tiles of BN entries,
 // mapped to (expert, local tile) by binary search over tile_off (kernels/mmq_gemm_q4k_grouped.cpp:49-60).
-template <int BN, bool GR>
+template <int BN, bool GR, bool SPLIT = false>
 __device__ __forceinline__ DeqTile deq_tile(const DeqParams &P, uint32_t id, uint32_t tiles_m)
 {
     DeqTile t;
     t.m0 = (id % tiles_m) * kBM;
-    const uint32_t gt = id / tiles_m;
+    uint32_t gt = id / tiles_m;
     if constexpr (!GR) {
         t.e = 0;
+        if constexpr (SPLIT) gt %= (P.n_tok + BN - 1) / BN; // the K split is the slowest index of a dense tile id
         t.tok0 = gt * BN;
         t.n_valid = min((uint32_t)BN, P.n_tok - t.tok0);
     } else {
@@ -211,7 +213,9 @@ __device__ __forceinline__ DeqTile deq_tile(const DeqParams &P, uint32_t id, uin
     return t;
 }
 
-template <int FMT, int BN, bool GR>
+// SPLIT: the K-split form of the dense kernel, a separate instantiation so that the plain one keeps its
+// register budget (the kernel runs at the 80-register cap of its 736 threads).
+template <int FMT, int BN, bool GR, bool SPLIT = false>
 __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap bmap, const DeqParams P)
 {
     using L = SmemD<FMT, BN>;
@@ -244,7 +248,19 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
     const uint32_t n_iters = (n_real + KS - 1u) / KS * KS; // per tile; steps past n_real carry zero weights (the image's zero tail as B)
     const uint32_t tiles_m = (P.out_dim + kBM - 1) / kBM;
     const uint32_t tiles_n = GR ? (uint32_t)P.tile_off[P.n_expert] : (P.n_tok + BN - 1) / BN; // grouped: known on the device only
-    const uint32_t n_tiles = tiles_m * tiles_n;
+    const uint32_t k_splits = SPLIT ? P.k_splits : 1u;
+    const uint32_t n_tiles = tiles_m * tiles_n * k_splits;
+    // K steps [k0, k1) of work item id
+    auto krange = [&](uint32_t id, uint32_t &k0, uint32_t &k1) {
+        if (k_splits <= 1u) {
+            k0 = 0u;
+            k1 = n_iters;
+        } else {
+            const uint32_t per = (n_real + k_splits - 1u) / k_splits;
+            k0 = (id / (tiles_m * tiles_n)) * per;
+            k1 = min(n_real, k0 + per);
+        }
+    };
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < S; s++) {
@@ -280,7 +296,7 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
     // rank + n_ranks, ...; one inverse token scale per column.  Arrives on tm_empty when done.
     auto drain = [&](uint32_t id, uint32_t tile, uint32_t rank, uint32_t n_ranks) -> bool {
         const uint32_t quarter = warp & 3u; // tensor-memory lanes this warp may read
-        const DeqTile tl = deq_tile<BN, GR>(P, id, tiles_m);
+        const DeqTile tl = deq_tile<BN, GR, SPLIT>(P, id, tiles_m);
         const uint32_t m0 = tl.m0, tok0 = tl.tok0, n_valid = tl.n_valid;
         const uint32_t buf = tile % NB;
         const uint32_t row = m0 + quarter * 32u + lane;
@@ -298,7 +314,10 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
 #pragma unroll
             for (int c = 0; c < 32; c++) {
                 const float sc = __shfl_sync(0xFFFFFFFFu, inv, c);
-                if (row < P.out_dim && col0 + c < n_valid) yrow[(size_t)(col0 + c) * P.out_dim] = __uint_as_float(d[c]) * sc;
+                if (row < P.out_dim && col0 + c < n_valid) {
+                    if (k_splits > 1u) atomicAdd(&yrow[(size_t)(col0 + c) * P.out_dim], __uint_as_float(d[c]) * sc);
+                    else yrow[(size_t)(col0 + c) * P.out_dim] = __uint_as_float(d[c]) * sc;
+                }
             }
         }
         tc_fence_before();
@@ -316,10 +335,12 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
             if (lane == 0) {
                 uint32_t it = 0;
                 for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x) {
-                    const uint32_t tok0 = deq_tile<BN, GR>(P, id, tiles_m).tok0;
+                    const uint32_t tok0 = deq_tile<BN, GR, SPLIT>(P, id, tiles_m).tok0;
                     const uint32_t n_rows_b = min((uint32_t)BN, P.tok_ld - tok0); // rows present in the image (a grouped tile may
                                                                                   // take the next expert's first rows along: unused columns)
-                    for (uint32_t i = 0; i < n_iters; i++, it++) {
+                    uint32_t k0, k1;
+                    krange(id, k0, k1);
+                    for (uint32_t i = k0; i < k1; i++, it++) {
                         const uint32_t s = it % S;
                         if (it >= S && !mbar_spin_d(op_empty(s), ((it / S) - 1u) & 1u, abort_flag, 2u)) goto prod_done;
                         if (P.debug & 2u) {
@@ -344,8 +365,10 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
             if (lane == 0) {
                 uint32_t m = 0; // stages issued
                 for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x) {
-                    const uint32_t tok0 = deq_tile<BN, GR>(P, id, tiles_m).tok0;
-                    for (uint32_t i = 0; i < n_iters; i += KS, m++) {
+                    const uint32_t tok0 = deq_tile<BN, GR, SPLIT>(P, id, tiles_m).tok0;
+                    uint32_t k0, k1;
+                    krange(id, k0, k1);
+                    for (uint32_t i = k0; i < k1; i += KS, m++) {
                         const uint32_t s = m % S;
                         if (m >= S && !mbar_spin_d(op_empty(s), ((m / S) - 1u) & 1u, abort_flag, 2u)) goto prod4_done;
                         if (P.debug & 2u) {
@@ -365,9 +388,11 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
         if (lane == 0) {
             uint32_t m = 0; // stages issued
             for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x) {
-                const DeqTile tl = deq_tile<BN, GR>(P, id, tiles_m);
+                const DeqTile tl = deq_tile<BN, GR, SPLIT>(P, id, tiles_m);
                 const uint32_t m0 = tl.m0;
-                for (uint32_t i = 0; i < n_iters; i += KS, m++) {
+                uint32_t k0, k1;
+                krange(id, k0, k1);
+                for (uint32_t i = k0; i < k1; i += KS, m++) {
                     const uint32_t s = m % R;
                     if (m >= R && !mbar_spin_d(raw_empty(s), ((m / R) - 1u) & 1u, abort_flag, 1u)) goto raw_done;
                     const uint32_t n_raw = i < n_sub ? min((uint32_t)KS, n_sub - i) : 0u; // sub-blocks with weights in this stage
@@ -402,7 +427,9 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
                 if (tile >= NB && !mbar_spin_d(tm_empty(buf), ((tile / NB) - 1u) & 1u, abort_flag, 3u)) goto mma_done;
                 tc_fence_after();
                 const uint32_t d0 = tmem_base + buf * BN;
-                for (uint32_t i = 0; i < n_iters; i += KS, it++) { // it counts stages here
+                uint32_t k0, k1;
+                krange(id, k0, k1);
+                for (uint32_t i = k0; i < k1; i += KS, it++) { // it counts stages here
                     const uint32_t s = it % S;
                     if (!mbar_test(op_full(s), (it / S) & 1u) && !mbar_spin_d(op_full(s), (it / S) & 1u, abort_flag, 4u)) goto mma_done;
                     tc_fence_after();
@@ -415,7 +442,7 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
 #pragma unroll
                             for (uint32_t nh = 0; nh < BN / NI; nh++) {
                                 mma_f16(d0 + nh * NI, da + kh * ((2 * kBM * 16) >> 4), db + ((kh * 2 * BN * 16 + nh * NI * 16) >> 4), idesc,
-                                        (i | kh) ? 1u : 0u); // the tile's first K=16 step overwrites every column
+                                        ((i - k0) | kh) ? 1u : 0u); // the work item's first K=16 step overwrites every column
                             }
                         }
                     }
@@ -433,9 +460,11 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
         constexpr uint32_t G = kExpGroups;
         const uint32_t grp = (warp - kLeadWarps) >> 2, r = (threadIdx.x - kLeadWarps * 32u) & 127u;
         struct Side { uint32_t e0, e1, smw, ddw; };
-        uint32_t tile_it0 = 0; // global step number of the tile's first step
-        for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x, tile_it0 += n_iters) {
-            const DeqTile tl = deq_tile<BN, GR>(P, id, tiles_m);
+        uint32_t tile_it0 = 0, tile_no = 0; // global step number of the work item's first step; work items done
+        uint32_t k0 = 0, k1 = 0;
+        for (uint32_t id = blockIdx.x; id < n_tiles && !*abort_flag; id += gridDim.x, tile_it0 += k1 - k0, tile_no += SPLIT ? 1u : 0u) {
+            const DeqTile tl = deq_tile<BN, GR, SPLIT>(P, id, tiles_m);
+            krange(id, k0, k1);
             const Planes pl = planes_of<FMT>(P.w + (size_t)tl.e * P.bytes_per_expert, P.in_dim, P.out_dim);
             const uint32_t row = min(tl.m0 + r, P.out_dim - 1u);
             const uint8_t *scp = pl.sc + (size_t)row * pl.nsp * (FMT == Q5_1 ? 4u : 2u);
@@ -459,7 +488,7 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
             auto step = [&](Side &slot, uint32_t i) -> bool {
                 const Side cur = slot;
                 request(slot, i + 3u * G);
-                const uint32_t it = tile_it0 + i, mst = it / KS, s = mst % S, rs = mst % R;
+                const uint32_t it = tile_it0 + (i - k0), mst = it / KS, s = mst % S, rs = mst % R;
                 uint4 o[4];
                 if (i >= n_sub) o[0] = o[1] = o[2] = o[3] = make_uint4(0u, 0u, 0u, 0u); // minima steps fill it below; steps past the last are zero
                 if constexpr (T::has_min) {
@@ -523,27 +552,27 @@ __global__ void __launch_bounds__(kDeqThreads, 1) mmqd_kernel(const __grid_const
                 }
                 return true;
             };
-            uint32_t i = (grp + G - (tile_it0 % G)) % G; // the group's first step in this tile
+            uint32_t i = k0 + (grp + G - (tile_it0 % G)) % G; // the group's first step in this work item
             Side slot0, slot1, slot2;
             request(slot0, i);
             request(slot1, i + G);
             request(slot2, i + 2u * G);
             bool ok = true;
-            while (ok && i < n_iters) {
+            while (ok && i < k1) {
                 ok = step(slot0, i);
                 i += G;
-                if (ok && i < n_iters) {
+                if (ok && i < k1) {
                     ok = step(slot1, i);
                     i += G;
                 }
-                if (ok && i < n_iters) {
+                if (ok && i < k1) {
                     ok = step(slot2, i);
                     i += G;
                 }
             }
             if (!ok) break;
             if constexpr (kAllDrain) {
-                if (!drain(id, tile_it0 / n_iters, grp, kExpGroups + 1u)) break;
+                if (!drain(id, SPLIT ? tile_no : tile_it0 / n_iters, grp, kExpGroups + 1u)) break;
             }
         }
     } else {
@@ -731,8 +760,10 @@ int launch_deq(cudaStream_t s, const DeqParams &P)
     CUtensorMap map;
     int rc = make_tmap<FMT>(&map, P.w, 0, 1u, P.in_dim, P.out_dim);
     if (rc) return rc;
-    const uint32_t tiles = ((P.out_dim + kBM - 1) / kBM) * ((P.n_tok + BN - 1) / BN);
+    const uint32_t tiles = ((P.out_dim + kBM - 1) / kBM) * ((P.n_tok + BN - 1) / BN) * P.k_splits;
     const uint32_t grid = min(tiles, (uint32_t)sm_count());
+    if (P.k_splits > 1u)
+        return (int)launch_pdl(mmqd_kernel<FMT, BN, false, true>, dim3(grid), dim3(kDeqThreads), SmemD<FMT, BN>::total, s, map, map, P);
     return (int)launch_pdl(mmqd_kernel<FMT, BN, false>, dim3(grid), dim3(kDeqThreads), SmemD<FMT, BN>::total, s, map, map, P); // (no image map: bulk copies)
 }
 
@@ -778,6 +809,9 @@ template <int FMT> int set_attr_deq()
     int rc = (int)cudaFuncSetAttribute(mmqd_kernel<FMT, 512, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemD<FMT, 512>::total);
     rc |= (int)cudaFuncSetAttribute(mmqd_kernel<FMT, 256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemD<FMT, 256>::total);
     rc |= (int)cudaFuncSetAttribute(mmqd_kernel<FMT, 128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemD<FMT, 128>::total);
+    rc |= (int)cudaFuncSetAttribute(mmqd_kernel<FMT, 512, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemD<FMT, 512>::total);
+    rc |= (int)cudaFuncSetAttribute(mmqd_kernel<FMT, 256, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemD<FMT, 256>::total);
+    rc |= (int)cudaFuncSetAttribute(mmqd_kernel<FMT, 128, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemD<FMT, 128>::total);
     rc |= (int)cudaFuncSetAttribute(mmqd_kernel<FMT, kGroupedDeqBN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     (int)SmemD<FMT, kGroupedDeqBN>::total);
     return rc;
@@ -824,6 +858,23 @@ int launch_mmq_deq_f32(cudaStream_t s, int type, const void *w, const float *x, 
     const uint32_t ld = tok_ld_of(n_tok), n_xc = xchunks_of(in_dim);
     // 8 tokens per CTA; a second CTA shares their sub-blocks while that still adds SMs
     const uint32_t groups = ld / kActTokens, ysplit = groups * 2u <= (uint32_t)sm_count() ? 2u : 1u;
+    // Few tiles (a narrow matrix, or a row shard of one): every tile runs its whole K on one SM while the
+    // others idle, and a K step costs the same at every width.  Then each tile becomes up to four work
+    // items over contiguous ranges of K steps that add their partial sums into a zeroed y.
+    const uint32_t bn = g_deq_bn ? (uint32_t)g_deq_bn : n_tok > 256u ? 512u : n_tok > 128u ? 256u : 128u;
+    uint32_t k_splits = 1;
+    {
+        const uint32_t n_sub = in_dim >> 5;
+        const bool has_min = type == Q4_K || type == Q5_K || type == Q5_1;
+        const uint32_t n_real = n_sub + (has_min ? (n_sub + 31u) / 32u : 0u);
+        const uint32_t tiles = ((out_dim + kBM - 1) / kBM) * ((n_tok + bn - 1u) / bn);
+        if (!(g_deq_debug & 64) && tiles * 2u <= (uint32_t)sm_count())
+            k_splits = std::max(1u, std::min(std::min(4u, (uint32_t)sm_count() / tiles), n_real / 32u));
+        if (k_splits > 1u) {
+            cudaError_t e0 = cudaMemsetAsync(y, 0, (size_t)n_tok * out_dim * sizeof(float), s);
+            if (e0 != cudaSuccess) return (int)e0;
+        }
+    }
     const ActSource src = {x, nullptr, 1u, (size_t)in_dim, -1};
     cudaError_t e = launch_pdl(activations_to_f16_kernel, dim3(groups, ysplit), dim3(kActWarps * 32), 0, s, src, (uint8_t *)scratch, in_dim,
                                n_tok, ld, n_xc);
@@ -832,6 +883,7 @@ int launch_mmq_deq_f32(cudaStream_t s, int type, const void *w, const float *x, 
     P.bytes_per_expert = 0;
     P.expert_off = P.tile_off = nullptr;
     P.n_expert = 1;
+    P.k_splits = k_splits;
     P.w = (const uint8_t *)w;
     P.xh = (const uint8_t *)scratch;
     P.inv_scale = reinterpret_cast<const float *>((const uint8_t *)scratch + ((size_t)(in_dim >> 3) + n_xc) * ld * 16u);
@@ -844,7 +896,6 @@ int launch_mmq_deq_f32(cudaStream_t s, int type, const void *w, const float *x, 
     // The widest token tile the batch fills: a K step costs about the same at every width (it is
     // bound by the latency of the operand ring, not by the MMA), so fewer, wider tiles win, and every
     // weight is expanded once per tile column.
-    const uint32_t bn = g_deq_bn ? (uint32_t)g_deq_bn : n_tok > 256u ? 512u : n_tok > 128u ? 256u : 128u;
     switch (type) {
     case Q4_0: return launch_deq_bn<Q4_0>(s, P, bn);
     case Q5_1: return launch_deq_bn<Q5_1>(s, P, bn);
@@ -895,6 +946,7 @@ int launch_mmq_deq_grouped_f32(cudaStream_t s, int type, const void *slab, size_
     P.expert_off = expert_off;
     P.tile_off = tile_off;
     P.n_expert = n_expert;
+    P.k_splits = 1;
     P.debug = (uint32_t)g_deq_debug;
     switch (type) {
     case Q4_0: return launch_deq_grouped<Q4_0>(s, P);
