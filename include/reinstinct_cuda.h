@@ -169,24 +169,34 @@ int rc_matvec_block_dots(void *stream, int ggml_type, const void *w, const void 
 void rc_tune_matvec(int ks, int grid_mult, int no_pdl);
 /* Measurement aid: force_dp4a != 0 sends the MMQ entry points through the dp4a kernel instead of
  * the tensor-core kernels.  The low byte of kind picks the kernel: 0 the default (rc_matmul: the
- * f16-operand GEMM with whole-K accumulation; rc_mmq_gemm and the grouped GEMM: int8 operands,
- * Q6_K on the exact-integer f16 kernel), 8 the int8-operand kernel and 16 the exact-integer
- * f16-operand kernel everywhere (rc_matmul then quantizes to BlockQ8 / its planar form), 32 the
- * default again with (kind >> 8) & 0xFFF forcing its token-tile width (128, 256, 512) and
- * kind >> 20 a mask of pipeline parts it skips or traces (results then invalid).  With kind 16 the
- * upper bits are the skip mask of that kernel.  For A/B timing and cross-checking only. */
+ * integer-operand f16 GEMM with a drain per sub-block; rc_mmq_gemm and the grouped GEMM: int8 operands,
+ * Q6_K on the integer-operand f16 kernel of that family), 8 the int8-operand kernel and 16 the
+ * integer-operand f16 kernel of the BlockQ8-input family everywhere (rc_matmul then quantizes to BlockQ8
+ * / its planar form), 32 sends rc_matmul through the f16-DEQUANTIZED GEMM of rc_matmul_f16 (an
+ * approximation) with (kind >> 8) & 0xFFF forcing its token-tile width (128, 256, 512) and kind >> 20 a
+ * mask of pipeline parts it skips or traces (results then invalid).  With kind 16 the upper bits are the
+ * skip mask of that kernel.  For A/B timing and cross-checking only. */
 void rc_tune_mmq(int force_dp4a, int kind);
 /* Reads (synchronously) the device-side status word: 0, or the codes of the bounded waits that
- * gave up: bits 0-7 the int8 GEMM, 8-15 the exact-integer f16 GEMM, 16-23 the peer gather, 24-31
- * the f16-operand dense GEMM.  A nonzero value means the affected outputs are invalid; the
- * context stays usable.  hipDeviceSynchronize + error check in the reference's tests
- * (src/runtime/kernels.rs) is the nearest counterpart. */
+ * gave up: bits 0-7 the int8 GEMM, 8-11 the BlockQ8-input f16 GEMM, 12-15 the dense exact GEMM of
+ * rc_matmul, 16-23 the peer gather, 24-31 the f16-dequantized GEMM.  A nonzero value means the
+ * affected outputs are invalid; the context stays usable.  The words are sticky: they keep the
+ * last code until rc_device_status_clear.  hipDeviceSynchronize + error check in the
+ * reference's tests (src/runtime/kernels.rs) is the nearest counterpart. */
 int rc_device_status(unsigned int *status);
+/* The same read, then the words are reset to 0 (status may be NULL).  Call it with no kernel of
+ * this library in flight. */
+int rc_device_status_clear(unsigned int *status);
 /* Measurement aid: copies out (synchronously) the phase timestamps the f16-operand GEMM records
  * per CTA when bit 7 of its rc_tune_mmq mask is set: 160 x 8 uint64 (globaltimer ns: start,
  * set-up done, predecessor done, first stage full, last commit, accumulator full, drain done,
  * tensor memory freed).  No counterpart in the reference. */
 int rc_debug_read_trace(void *out, size_t bytes);
+/* Measurement aid: copies out (synchronously) the per-role cycle counters that the dense exact GEMM
+ * of rc_matmul accumulates per CTA when rc_tune_mmq's kind is 64 (Q4_K and Q8_0 only): 160 x 32
+ * uint64, six counters for each of: token producer, MMA issuer, the two expander groups, the first
+ * and the last epilogue warp.  No counterpart in the reference. */
+int rc_debug_read_prof(void *out, size_t bytes);
 
 /* ---- int8 MMQ GEMM --------------------------------------------------------------------- */
 
@@ -198,15 +208,38 @@ int rc_mmq_gemm(void *stream, int ggml_type, const void *w, const void *xq, floa
 
 /* PrefillGemm::matmul_into_raw (src/runtime/prefill.rs:343-437).  x f32 [n_rows][in_dim].
  * n_rows <= RC_MATVEC_MAX_ROWS: quantize X to BlockQ8 in the caller's scratch, then the batched
- * matvec (integer block dots exact).  More rows: the same quantizer, its values written
- * dequantized as an f16 operand image into the scratch, then the tensor-core GEMM with f16
- * operands and whole-K f32 accumulation: within 1e-3 relative L2 of the exact-integer
- * formulation (about 3e-4), not bit-identical to it; rc_quantize_q8 + rc_mmq_gemm is the
- * exact-integer route.  xq_scratch: 16-byte aligned, rc_matmul_scratch_bytes large (with a
- * smaller or misaligned scratch that still holds the BlockQ8 records the exact route runs). */
+ * matvec.  More rows: the same quantizer writes its int8 values as an integer-valued f16 operand
+ * image (plus the d and xsum planes) into the scratch, then the tensor-core GEMM whose accumulator
+ * tile of every 32-wide sub-block is the exact integer block dot (mmq_gemm_q4k_repacked.cpp:98-166),
+ * scaled in f32 per sub-block; small matrices with few rows take 16-row passes of the batched matvec
+ * instead, and Q5_1 always does.  On every route the per-block integer dots are exact and the f32
+ * result is within 1e-3 relative L2 of the reference formulation (seen: 1e-6); which route runs
+ * depends on the shape only, never on the scratch.  xq_scratch: 16-byte aligned and
+ * rc_matmul_scratch_bytes large, else RC_ERR_MISALIGNED / RC_ERR_SCRATCH_TOO_SMALL (the reference
+ * sizes its xq8 buffer as (in_dim / 32) * 40 bytes per row, src/runtime/prefill.rs:283: a binding
+ * sizes it with rc_matmul_scratch_bytes instead). */
 int rc_matmul(void *stream, int ggml_type, const void *w, const float *x, float *y,
               uint32_t in_dim, uint32_t out_dim, uint32_t n_rows, void *xq_scratch,
               size_t scratch_bytes);
+/* An APPROXIMATION of rc_matmul for more than 16 rows, faster on wide batches: both operands
+ * dequantized and rounded once to f16 (weights d * sc * q, activations d * q times a power of two per
+ * token), whole-K f32 accumulation in tensor memory, no per-block integer dots.  About 3e-4 relative
+ * L2 from rc_matmul's result (inside the reference's own 1e-3 GPU-vs-CPU bound, but not bit-exact at
+ * the block level), and with few tiles it splits K and adds partial sums atomically, so two runs may
+ * differ in the last bits and y is zeroed first.  Same arguments and scratch size as rc_matmul.
+ * No counterpart in the reference. */
+int rc_matmul_f16(void *stream, int ggml_type, const void *w, const float *x, float *y,
+                  uint32_t in_dim, uint32_t out_dim, uint32_t n_rows, void *scratch,
+                  size_t scratch_bytes);
+/* Debug variant of rc_matmul's tensor-core route (any n_rows >= 1): besides y it writes the tile the
+ * kernel drains for every (activation row, weight row, sub-block), before any f32 scaling, as
+ * int32 idots[n_rows][out_dim][in_dim / 32]: the integer block dot, times the integer sub-scale
+ * for the K-quants (Q4_K / Q5_K: sc * idot; Q6_K: sc_lo * I0 + sc_hi * I1).  Not Q5_1.  The
+ * reference has no such dump; its kernels hold these integers in registers
+ * (kernels/mmq_gemm_q4k_repacked.cpp:150-161). */
+int rc_matmul_block_dots(void *stream, int ggml_type, const void *w, const float *x, float *y,
+                         int32_t *idots, uint32_t in_dim, uint32_t out_dim, uint32_t n_rows,
+                         void *scratch, size_t scratch_bytes);
 /* bytes rc_matmul / rc_matvec_f32 need in xq_scratch */
 size_t rc_matmul_scratch_bytes(uint32_t in_dim, uint32_t n_rows);
 

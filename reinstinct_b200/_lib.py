@@ -49,9 +49,12 @@ _SIGNATURES = {
     "rc_tune_matvec": (None, [_i, _i, _i]),
     "rc_tune_mmq": (None, [_i, _i]),
     "rc_device_status": (_i, [C.POINTER(C.c_uint)]),
+    "rc_device_status_clear": (_i, [C.POINTER(C.c_uint)]),
     "rc_mmq_gemm": (_i, [_vp, _i, _vp, _vp, _vp, _u32, _u32, _u32]),
     "rc_matmul": (_i, [_vp, _i, _vp, _vp, _vp, _u32, _u32, _u32, _vp, _sz]),
     "rc_matmul_scratch_bytes": (_sz, [_u32, _u32]),
+    "rc_matmul_f16": (_i, [_vp, _i, _vp, _vp, _vp, _u32, _u32, _u32, _vp, _sz]),
+    "rc_matmul_block_dots": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp, _sz]),
     "rc_moe_sort": (_i, [_vp, _vp, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
     "rc_moe_tile_bn": (_u32, []),
     "rc_moe_gather_xq": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32]),
@@ -64,6 +67,7 @@ _SIGNATURES = {
     "rc_swiglu_q8": (_i, [_vp, _vp, _vp, _vp, _vp, _sz]),
     "rc_kernel_type": (_i, [_i]),
     "rc_debug_read_trace": (_i, [_vp, C.c_size_t]),
+    "rc_debug_read_prof": (_i, [_vp, C.c_size_t]),
     "rc_mmq_gemm_grouped_scratch_bytes": (_sz, [_u32, _u32]),
     "rc_mmq_gemm_grouped_f32": (_i, [_vp, _i, _vp, _sz, _vp, _vp, _u32, _vp, _vp, _u32, _sz, _i, _vp, _u32, _u32, _u32, _vp, _sz]),
     "rc_moe_gate_up_swiglu": (_i, [_vp, _i, _vp, _vp, _sz, _vp, _u32, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32]),

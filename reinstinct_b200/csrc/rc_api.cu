@@ -43,6 +43,8 @@ int ensure_device_ready()
     if (rc) return rc;
     rc = mmq_deq_set_attributes();
     if (rc) return rc;
+    rc = mmq_x_set_attributes();
+    if (rc) return rc;
     rc = moe_set_attributes();
     if (rc) return rc;
     g_ready[dev] = true;
@@ -183,10 +185,13 @@ size_t rc_matmul_scratch_bytes(uint32_t in_dim, uint32_t n_rows)
     // BlockQ8 records, or the planar form of the same values (a few bytes of row padding more)
     const size_t records = (size_t)n_rows * (in_dim / 32) * RC_BLOCKQ8_BYTES;
     const size_t planar = quantize_planar_bytes(in_dim, n_rows);
-    // beyond the matvec's row limit: the f16 image of the activations the dense GEMM reads
-    const size_t image = n_rows > RC_MATVEC_MAX_ROWS ? mmq_deq_scratch_bytes(in_dim, n_rows) : 0;
-    const size_t m = records > planar ? records : planar;
-    return m > image ? m : image;
+    // beyond the matvec's row limit: the operand image of the activations the dense GEMM reads (the
+    // integer-valued one of the default route, or the dequantized one of rc_matmul_f16)
+    const size_t image = n_rows > RC_MATVEC_MAX_ROWS ? mmq_x_scratch_bytes(in_dim, n_rows) : 0;
+    const size_t image_deq = n_rows > RC_MATVEC_MAX_ROWS ? mmq_deq_scratch_bytes(in_dim, n_rows) : 0;
+    size_t m = records > planar ? records : planar;
+    m = m > image ? m : image;
+    return m > image_deq ? m : image_deq;
 }
 
 int rc_matvec_f32(void *stream, int type, const void *w, const float *x, float *y, uint32_t in_dim,
@@ -224,6 +229,35 @@ int rc_matmul(void *stream, int type, const void *w, const float *x, float *y, u
         return launch_matvec(S(stream), type, w, xq_scratch, y, in_dim, out_dim, n_rows, nullptr);
     }
     return launch_mmq_gemm_f32(S(stream), type, w, x, y, in_dim, out_dim, n_rows, xq_scratch, scratch_bytes);
+}
+
+int rc_matmul_f16(void *stream, int type, const void *w, const float *x, float *y, uint32_t in_dim,
+                  uint32_t out_dim, uint32_t n_rows, void *scratch, size_t scratch_bytes)
+{
+    if (n_rows == 0) return RC_OK;
+    if (!x) return RC_ERR_NULL_POINTER;
+    int rc = check_weight_args(type, w, scratch, y, in_dim, out_dim);
+    if (rc) return rc;
+    if (((uintptr_t)scratch & 15u)) return RC_ERR_MISALIGNED;
+    if (scratch_bytes < mmq_deq_scratch_bytes(in_dim, n_rows)) return RC_ERR_SCRATCH_TOO_SMALL;
+    rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_mmq_deq_f32(S(stream), type, w, x, y, in_dim, out_dim, n_rows, scratch);
+}
+
+int rc_matmul_block_dots(void *stream, int type, const void *w, const float *x, float *y, int32_t *idots,
+                         uint32_t in_dim, uint32_t out_dim, uint32_t n_rows, void *scratch, size_t scratch_bytes)
+{
+    if (n_rows == 0) return RC_OK;
+    if (!x || !idots) return RC_ERR_NULL_POINTER;
+    int rc = check_weight_args(type, w, scratch, y, in_dim, out_dim);
+    if (rc) return rc;
+    if (!mmq_x_supports(type)) return RC_ERR_BAD_TYPE;
+    if (((uintptr_t)scratch & 15u) || ((uintptr_t)idots & 3u)) return RC_ERR_MISALIGNED;
+    if (scratch_bytes < mmq_x_scratch_bytes(in_dim, n_rows)) return RC_ERR_SCRATCH_TOO_SMALL;
+    rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_mmq_x_f32(S(stream), type, w, x, y, in_dim, out_dim, n_rows, scratch, idots);
 }
 
 /* ---- allocation-free matvec ---------------------------------------------------------------- */
@@ -660,16 +694,33 @@ extern "C" void rc_tune_mmq(int force_dp4a, int kind)
 }
 namespace rc { int mmq_deq_read_trace(void *out, size_t bytes); }
 extern "C" int rc_debug_read_trace(void *out, size_t bytes) { return rc::mmq_deq_read_trace(out, bytes); }
+extern "C" int rc_debug_read_prof(void *out, size_t bytes) { return rc::mmq_x_read_prof(out, bytes); }
+namespace {
+int device_status(unsigned int *status, bool clear)
+{
+    unsigned int g = 0;
+    int rc = rc::mmq_device_error(status, clear);
+    if (rc) return rc;
+    rc = rc::mmq_x_device_error(&g, clear);
+    *status |= (g & 0xFu) << 12;
+    if (rc) return rc;
+    rc = rc::gather_device_error(&g, clear);
+    *status |= (g & 0xFFu) << 16;
+    if (rc) return rc;
+    rc = rc::mmq_deq_device_error(&g, clear);
+    *status |= (g & 0xFFu) << 24;
+    return rc;
+}
+} // namespace
 extern "C" int rc_device_status(unsigned int *status)
 {
     if (!status) return RC_ERR_NULL_POINTER;
-    unsigned int g = 0;
-    int rc = rc::mmq_device_error(status);
-    if (rc) return rc;
-    rc = rc::gather_device_error(&g);
-    *status |= g << 16;
-    if (rc) return rc;
-    rc = rc::mmq_deq_device_error(&g);
-    *status |= g << 24;
+    return device_status(status, false);
+}
+extern "C" int rc_device_status_clear(unsigned int *status)
+{
+    unsigned int s = 0;
+    const int rc = device_status(&s, true);
+    if (status) *status = s;
     return rc;
 }

@@ -70,9 +70,14 @@ allgather_push_kernel(const uint4 *__restrict__ src, uint32_t n16, GatherPeers p
 
 } // namespace
 
-int gather_device_error(unsigned int *out)
+int gather_device_error(unsigned int *out, bool clear)
 {
-    return (int)cudaMemcpyFromSymbol(out, g_gather_error, sizeof(unsigned int));
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_gather_error, sizeof(unsigned int));
+    if (e == cudaSuccess && clear && *out) {
+        const unsigned int zero = 0;
+        e = cudaMemcpyToSymbol(g_gather_error, &zero, sizeof(unsigned int));
+    }
+    return (int)e;
 }
 
 int launch_allgather_push(cudaStream_t s, const void *src, size_t bytes, void *const *peer_dst,

@@ -42,7 +42,7 @@ int mmq_set_attributes();
 // rc_mmq_deq.cu: the f16-operand dense GEMM (activations as f32 in, scratch holds their f16 image)
 int mmq_deq_set_attributes();
 void mmq_deq_set_bn(int bn);
-int mmq_deq_device_error(unsigned int *out);
+int mmq_deq_device_error(unsigned int *out, bool clear);
 size_t mmq_deq_scratch_bytes(uint32_t in_dim, uint32_t n_tok);
 size_t mmq_deq_grouped_scratch_bytes(uint32_t in_dim, uint32_t n_entries);
 int launch_mmq_deq_grouped_f32(cudaStream_t s, int type, const void *slab, size_t bytes_per_expert, const int32_t *expert_off,
@@ -51,11 +51,21 @@ int launch_mmq_deq_grouped_f32(cudaStream_t s, int type, const void *slab, size_
                                void *scratch);
 int launch_mmq_deq_f32(cudaStream_t s, int type, const void *w, const float *x, float *y, uint32_t in_dim, uint32_t out_dim,
                        uint32_t n_tok, void *scratch);
+// rc_mmq_x.cu: the dense GEMM with exact integer block dots (integer-valued f16 operands, per-sub-block drain)
+int mmq_x_set_attributes();
+bool mmq_x_supports(int type);
+void mmq_x_set_prof(int on);
+void mmq_x_set_debug(int mask);
+int mmq_x_read_prof(void *out, size_t bytes);
+int mmq_x_device_error(unsigned int *out, bool clear);
+size_t mmq_x_scratch_bytes(uint32_t in_dim, uint32_t n_tok);
+int launch_mmq_x_f32(cudaStream_t s, int type, const void *w, const float *x, float *y, uint32_t in_dim, uint32_t out_dim,
+                     uint32_t n_tok, void *scratch, int32_t *dump);
 uint32_t mmq_grouped_bn();
 uint32_t matvec_grouped_bn();
 void mmq_force_dp4a(int on);
 void mmq_set_kind(int kind);
-int mmq_device_error(unsigned int *out);
+int mmq_device_error(unsigned int *out, bool clear);
 
 int launch_moe_sort(cudaStream_t s, const int32_t *ids, uint32_t n_entries, uint32_t n_expert,
                     uint32_t bn, int32_t *count, int32_t *cursor, int32_t *expert_off,
@@ -67,7 +77,7 @@ int launch_moe_scatter_rows(cudaStream_t s, const float *src, const int32_t *per
 
 int launch_allgather_push(cudaStream_t s, const void *src, size_t bytes, void *const *peer_dst,
                           void *const *peer_flags, void *epoch, uint32_t rank, uint32_t world);
-int gather_device_error(unsigned int *out);
+int gather_device_error(unsigned int *out, bool clear);
 
 int launch_rmsnorm_q8(cudaStream_t s, const float *x, const float *add, const float *w, float *hidden_io, float *y, void *out,
                       uint32_t n, uint32_t n_vec, float eps);

@@ -1060,17 +1060,24 @@ void mmq_force_dp4a(int on) { g_force_dp4a = on != 0; }
 void mmq_set_kind(int kind)
 {
     g_mmq_kind = (kind & 0xFF) == 8 ? 8 : (kind & 0xFF) == 16 ? 16 : (kind & 0xFF) == 32 ? 32 : 0;
+    mmq_x_set_prof(((kind & 0xFF) == 64 || (kind & 0xFF) == 66) ? 1 : 0); // kinds 64, 66: the default route with per-role cycle counters
+    mmq_x_set_debug(((kind & 0xFF) == 65 || (kind & 0xFF) == 66) ? kind >> 8 : 0); // kinds 65, 66: the default route with the pipeline parts in kind >> 8 skipped
     mmq_deq_set_bn(g_mmq_kind == 32 ? kind >> 8 : 0); // kind 32: the upper bits force the token-tile width
     g_no_planar = ((kind >> 8) & 512) != 0; // bit 9 of the mask: keep rc_matmul on BlockQ8 records
     g_mmq_debug = kind >> 8; // upper bits: parts of the f16 kernel's pipeline to skip (timing experiments)
 }
 
-int mmq_device_error(unsigned int *out)
+int mmq_device_error(unsigned int *out, bool clear)
 {
     unsigned int a = 0, b = 0;
     cudaError_t e = cudaMemcpyFromSymbol(&a, g_mmq_error, sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaMemcpyFromSymbol(&b, g_mmq16_error, sizeof(unsigned int));
-    *out = a | (b << 8);
+    *out = (a & 0xFFu) | ((b & 0xFu) << 8);
+    if (e == cudaSuccess && clear && (a | b)) {
+        const unsigned int zero = 0;
+        e = cudaMemcpyToSymbol(g_mmq_error, &zero, sizeof(unsigned int));
+        if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_mmq16_error, &zero, sizeof(unsigned int));
+    }
     return (int)e;
 }
 
@@ -1088,43 +1095,50 @@ int launch_mmq_gemm(cudaStream_t s, int type, const void *w, const void *xq, flo
     return mmq_dense(s, type, w, xq, y, in_dim, out_dim, p_rows, false);
 }
 
-// PrefillGemm's quantize + GEMM.  When the int8 tensor-core kernel will run and the scratch is
-// large and aligned enough, the activations are quantized straight into the planar form that
-// kernel reads through TMA (same values as the BlockQ8 records, no per-tile conversion).
+// PrefillGemm's quantize + GEMM for more than RC_MATVEC_MAX_ROWS rows.  Every route below keeps the
+// integer block dots exact: the default is the integer-operand f16 kernel of rc_mmq_x.cu (the quantizer
+// writes its operand image into the scratch), small matrices with few rows go through 16-row passes of
+// the batched matvec, Q5_1 through the dp4a passes.  The f16-dequantized GEMM (rc_mmq_deq.cu) is an
+// approximation and runs only when asked for by name (rc_matmul_f16, or rc_tune_mmq kind 32).
 int launch_mmq_gemm_f32(cudaStream_t s, int type, const void *w, const float *x, float *y, uint32_t in_dim,
                         uint32_t out_dim, uint32_t p_rows, void *scratch, size_t scratch_bytes)
 {
-    // f32 activations and a large enough scratch: the f16-operand kernel (rc_mmq_deq.cu), unless one of
-    // the exact-integer kernels was asked for
-    if (!g_force_dp4a && (g_mmq_kind == 0 || g_mmq_kind == 32) && ((uintptr_t)scratch & 15u) == 0 &&
-        scratch_bytes >= mmq_deq_scratch_bytes(in_dim, p_rows)) {
-        // Small matrices and few rows: the GEMM's fixed cost (two launches, ring start-up, the drain) and
-        // its K steps of ~0.4 us each outlast a few 16-row passes of the batched matvec.  Both costs
-        // are modelled from measurements on B200: a 16-row matvec pass takes max(8 us, 0.95 us per
-        // million weights); the GEMM 7 us + 0.42 us per K=32 step and wave of tiles.
-        if (g_mmq_kind == 0) {
-            const uint32_t n_sub = in_dim >> 5;
-            const double t16 = fmax(8.0, 0.95e-6 * (double)in_dim * (double)out_dim);
-            const double t_mv = (double)((p_rows + 15u) / 16u) * t16;
-            const uint32_t bn = p_rows > 256u ? 512u : p_rows > 128u ? 256u : 128u;
-            const uint64_t tiles = (uint64_t)((out_dim + kBM - 1) / kBM) * ((p_rows + bn - 1u) / bn);
-            const double waves = (double)((tiles + (uint64_t)sm_count() - 1u) / (uint64_t)sm_count());
-            const double steps = (double)n_sub + ((type == Q4_K || type == Q5_K || type == Q5_1) ? (double)((n_sub + 31u) / 32u) : 0.0);
-            const double t_gemm = 7.0 + 0.42 * steps * waves;
-            if (t_mv < t_gemm) {
-                int rc = launch_quantize_q8(s, x, scratch, in_dim, p_rows);
-                if (rc) return rc;
-                for (uint32_t p0 = 0; p0 < p_rows; p0 += 16) {
-                    const uint32_t n = min(16u, p_rows - p0);
-                    rc = launch_matvec(s, type, w, (const uint8_t *)scratch + (size_t)p0 * n_sub * RC_BLOCKQ8_BYTES,
-                                       y + (size_t)p0 * out_dim, in_dim, out_dim, n, nullptr);
-                    if (rc) return rc;
-                }
-                return RC_OK;
-            }
-        }
+    if (g_mmq_kind == 32 && !g_force_dp4a) {
+        if (((uintptr_t)scratch & 15u) != 0) return RC_ERR_MISALIGNED;
+        if (scratch_bytes < mmq_deq_scratch_bytes(in_dim, p_rows)) return RC_ERR_SCRATCH_TOO_SMALL;
         return launch_mmq_deq_f32(s, type, w, x, y, in_dim, out_dim, p_rows, scratch);
     }
+    if (g_mmq_kind == 0 && !g_force_dp4a) {
+        const uint32_t n_sub = in_dim >> 5;
+        if (mmq_x_supports(type)) {
+            // Small matrices and few rows: the GEMM's fixed cost (two launches, ring start-up, the last drain)
+            // and its K steps outlast a few 16-row passes of the batched matvec.  Both costs are modelled
+            // from measurements on B200: a 16-row matvec pass takes max(8 us, 0.95 us per million weights);
+            // the GEMM 8 us + 0.16 us per K=32 step and wave of 128 x 128 tiles.
+            const double t16 = fmax(8.0, 0.95e-6 * (double)in_dim * (double)out_dim);
+            const double t_mv = (double)((p_rows + 15u) / 16u) * t16;
+            const uint64_t tiles = (uint64_t)((out_dim + 127u) / 128u) * ((p_rows + 127u) / 128u);
+            const double waves = (double)((tiles + (uint64_t)sm_count() - 1u) / (uint64_t)sm_count());
+            const double steps = (double)n_sub + ((type == Q4_K || type == Q5_K) ? (double)((n_sub + 7u) / 8u) : 0.0);
+            const double t_gemm = 8.0 + 0.16 * steps * waves;
+            if (t_mv >= t_gemm) {
+                if (((uintptr_t)scratch & 15u) != 0) return RC_ERR_MISALIGNED;
+                if (scratch_bytes < mmq_x_scratch_bytes(in_dim, p_rows)) return RC_ERR_SCRATCH_TOO_SMALL;
+                return launch_mmq_x_f32(s, type, w, x, y, in_dim, out_dim, p_rows, scratch, nullptr);
+            }
+        }
+        // batched-matvec passes (also Q5_1, which has no exact tensor-core kernel)
+        int rc = launch_quantize_q8(s, x, scratch, in_dim, p_rows);
+        if (rc) return rc;
+        for (uint32_t p0 = 0; p0 < p_rows; p0 += 16) {
+            const uint32_t n = min(16u, p_rows - p0);
+            rc = launch_matvec(s, type, w, (const uint8_t *)scratch + (size_t)p0 * n_sub * RC_BLOCKQ8_BYTES,
+                               y + (size_t)p0 * out_dim, in_dim, out_dim, n, nullptr);
+            if (rc) return rc;
+        }
+        return RC_OK;
+    }
+    // rc_tune_mmq kinds 8 / 16 (and the dp4a switch): the per-sub-block kernels of this file, for A/B timing
     const bool i8_kernel = !g_force_dp4a && g_mmq_kind != 16 && type != Q6_K && type != Q5_1;
     const bool planar = i8_kernel && !g_no_planar && ((uintptr_t)scratch & 15u) == 0 && p_rows <= 65535u &&
                         scratch_bytes >= quantize_planar_bytes(in_dim, p_rows);

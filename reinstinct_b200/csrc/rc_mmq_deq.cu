@@ -840,9 +840,14 @@ int mmq_deq_read_trace(void *out, size_t bytes)
     return (int)cudaMemcpyFromSymbol(out, g_mmqd_trace, bytes < sizeof(g_mmqd_trace) ? bytes : sizeof(g_mmqd_trace));
 }
 
-int mmq_deq_device_error(unsigned int *out)
+int mmq_deq_device_error(unsigned int *out, bool clear)
 {
-    return (int)cudaMemcpyFromSymbol(out, g_mmqd_error, sizeof(unsigned int));
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_mmqd_error, sizeof(unsigned int));
+    if (e == cudaSuccess && clear && *out) {
+        const unsigned int zero = 0;
+        e = cudaMemcpyToSymbol(g_mmqd_error, &zero, sizeof(unsigned int));
+    }
+    return (int)e;
 }
 
 size_t mmq_deq_scratch_bytes(uint32_t in_dim, uint32_t n_tok)

@@ -222,6 +222,29 @@ class PrefillGemm:
         check(lib.rc_matmul(_stream(), w.dtype, _ptr(w.data), x_ptr, dst_ptr, w.in_dim, w.out_dim,
                             n_rows, _ptr(self.xq8), self.xq8.numel()), "rc_matmul")
 
+    def matmul_f16_into(self, dst: torch.Tensor, w: GpuMatvecTensor, x: torch.Tensor, n_rows: int) -> None:
+        """The opt-in APPROXIMATE GEMM (rc_matmul_f16: operands dequantized and rounded once to f16,
+        about 3e-4 relative L2 from matmul_into, no per-block integer dots).  No reference counterpart."""
+        assert w.repacked
+        if dst.numel() < n_rows * w.out_dim:
+            raise ValueError(f"matmul_f16_into: dst.len={dst.numel()} < n_rows*out_dim={n_rows * w.out_dim}")
+        lib = _lib.load()
+        self._grow(lib.rc_matmul_scratch_bytes(w.in_dim, n_rows))
+        check(lib.rc_matmul_f16(_stream(), w.dtype, _ptr(w.data), _ptr(x), _ptr(dst), w.in_dim, w.out_dim,
+                                n_rows, _ptr(self.xq8), self.xq8.numel()), "rc_matmul_f16")
+
+    def matmul_block_dots(self, w: GpuMatvecTensor, x: torch.Tensor, n_rows: int):
+        """Debug: (y, idots) of the tensor-core route; idots int32 [n_rows][out_dim][in_dim / 32] is the tile
+        the kernel drains per sub-block, before any f32 scaling (rc_matmul_block_dots)."""
+        assert w.repacked
+        lib = _lib.load()
+        self._grow(lib.rc_matmul_scratch_bytes(w.in_dim, max(n_rows, MATVEC_MAX_ROWS + 1)))
+        y = torch.empty((n_rows, w.out_dim), dtype=torch.float32, device=self.device)
+        idots = torch.zeros((n_rows, w.out_dim, w.in_dim // 32), dtype=torch.int32, device=self.device)
+        check(lib.rc_matmul_block_dots(_stream(), w.dtype, _ptr(w.data), _ptr(x), _ptr(y), _ptr(idots), w.in_dim,
+                                       w.out_dim, n_rows, _ptr(self.xq8), self.xq8.numel()), "rc_matmul_block_dots")
+        return y, idots
+
     def matmul_host(self, w: GpuMatvecTensor, x_host: torch.Tensor, y_host: torch.Tensor,
                     x_dev: torch.Tensor, y_dev: torch.Tensor, n_rows: int) -> None:
         """End-to-end call with HOST buffers (pinned): upload x, run, download y, all on the
