@@ -388,6 +388,34 @@ int rc_ipc_open_handle(const void *handle, void **dev_ptr);
 int rc_ipc_close_handle(void *dev_ptr);
 int rc_allgather_push(void *stream, const void *src, size_t bytes, void *const *peer_dst,
                       void *const *peer_flags, void *epoch, uint32_t rank, uint32_t world);
+/* Two calls that gather into the SAME buffers need one more handshake between them: a rank's wait only
+ * proves that its peers have pushed this call's shards, not that their consumers of the previous call have
+ * finished reading.  Alternating between two gathered buffers closes that window (a rank pushes call e + 2
+ * after it saw its peers' call e + 1, which they start only after their consumer of call e: the handshake
+ * kernel waits for its stream predecessor); reinstinct_b200/runtime.py's PeerAllGather does so.
+ *
+ * rc_peer_barrier: the handshake alone (epoch publication + bounded wait), for producers that store into
+ * their peers' memory themselves (rc_matmul_gather).  A peer's stores are complete on this device when the
+ * peer's barrier kernel, launched behind them on the same stream, has published its epoch. */
+int rc_peer_barrier(void *stream, void *const *peer_flags, void *epoch, uint32_t rank, uint32_t world);
+/* The work of `world` ranks done by ONE cooperative launch on one device (one CTA per rank, co-resident):
+ * the way to exercise the gather on a box with fewer GPUs than ranks, since separate launches that wait on
+ * one another are not guaranteed to run at the same time.  srcs, dsts, flags, epochs: host arrays of `world`
+ * device pointers (rank r's shard, gathered buffer, flag array, epoch counter).  The reference tests its
+ * two-stage pipeline on one device the same way (tests/qwen35_pipeline.rs:8-10). */
+int rc_allgather_push_logical(void *stream, const void *const *srcs, size_t bytes, void *const *dsts,
+                              void *const *flags, void *const *epochs, uint32_t world);
+/* Row-sharded PrefillGemm::matmul_into_raw that gathers its own output: this rank holds weight rows
+ * [row_begin, row_begin + out_dim) of an [out_total, in_dim] matrix; the kernel's finished tiles are stored
+ * into columns row_begin.. of EVERY rank's [n_rows][out_total] f32 output (y_peers: host array of `world`
+ * device pointers, this rank's own buffer included, the others peer-mapped with rc_ipc_open_handle), while
+ * other tiles still compute.  Always the tensor-core kernel of rc_matmul (any n_rows >= 1, not Q5_1), so
+ * every rank's rows are bit-identical to the unsharded call.  Follow it with rc_peer_barrier; alternate two
+ * output buffers between consecutive calls (see above).  No counterpart in the reference, whose only
+ * multi-device transfer is a peer copy of the hidden state (src/runtime/pipeline.rs:333-349). */
+int rc_matmul_gather(void *stream, int ggml_type, const void *w, const float *x, float *const *y_peers,
+                     uint32_t world, uint32_t out_total, uint32_t row_begin, uint32_t in_dim,
+                     uint32_t out_dim, uint32_t n_rows, void *scratch, size_t scratch_bytes);
 
 /* ---- device API mirror (src/hip/sys.rs:57-101, src/hip/mod.rs) --------------------------- */
 

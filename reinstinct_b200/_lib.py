@@ -79,6 +79,9 @@ _SIGNATURES = {
     "rc_ipc_open_handle": (_i, [_vp, C.POINTER(_vp)]),
     "rc_ipc_close_handle": (_i, [_vp]),
     "rc_allgather_push": (_i, [_vp, _vp, _sz, C.POINTER(_vp), C.POINTER(_vp), _vp, _u32, _u32]),
+    "rc_peer_barrier": (_i, [_vp, C.POINTER(_vp), _vp, _u32, _u32]),
+    "rc_allgather_push_logical": (_i, [_vp, C.POINTER(_vp), _sz, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _u32]),
+    "rc_matmul_gather": (_i, [_vp, _i, _vp, _vp, C.POINTER(_vp), _u32, _u32, _u32, _u32, _u32, _u32, _vp, _sz]),
     "rc_get_device_count": (_i, [C.POINTER(_i)]),
     "rc_set_device": (_i, [_i]),
     "rc_get_device": (_i, [C.POINTER(_i)]),

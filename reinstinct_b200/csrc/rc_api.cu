@@ -537,6 +537,53 @@ int rc_ipc_open_handle(const void *handle, void **dev_ptr)
 }
 int rc_ipc_close_handle(void *dev_ptr) { return (int)cudaIpcCloseMemHandle(dev_ptr); }
 
+int rc_peer_barrier(void *stream, void *const *peer_flags, void *epoch, uint32_t rank, uint32_t world)
+{
+    if (world == 0 || world > RC_MAX_PEERS || rank >= world) return RC_ERR_BAD_ARGUMENT;
+    if (!peer_flags || !epoch) return RC_ERR_NULL_POINTER;
+    for (uint32_t r = 0; r < world; r++) {
+        if (!peer_flags[r]) return RC_ERR_NULL_POINTER;
+        if ((uintptr_t)peer_flags[r] & 7u) return RC_ERR_MISALIGNED;
+    }
+    // the gather kernel with an empty shard: epoch publication and the bounded wait only
+    return launch_allgather_push(S(stream), nullptr, 0, peer_flags, peer_flags, epoch, rank, world);
+}
+
+int rc_allgather_push_logical(void *stream, const void *const *srcs, size_t bytes, void *const *dsts, void *const *flags,
+                              void *const *epochs, uint32_t world)
+{
+    if (world == 0 || world > RC_MAX_PEERS) return RC_ERR_BAD_ARGUMENT;
+    if (bytes % 16 || bytes / 16 > 0xFFFFFFFFull) return RC_ERR_BAD_SHAPE;
+    if (!srcs || !dsts || !flags || !epochs) return RC_ERR_NULL_POINTER;
+    for (uint32_t r = 0; r < world; r++) {
+        if (!srcs[r] || !dsts[r] || !flags[r] || !epochs[r]) return RC_ERR_NULL_POINTER;
+        if (((uintptr_t)srcs[r] & 15u) || ((uintptr_t)dsts[r] & 15u) || ((uintptr_t)flags[r] & 7u) || ((uintptr_t)epochs[r] & 7u))
+            return RC_ERR_MISALIGNED;
+    }
+    return launch_allgather_push_logical(S(stream), srcs, bytes, dsts, flags, epochs, world);
+}
+
+int rc_matmul_gather(void *stream, int type, const void *w, const float *x, float *const *y_peers, uint32_t world,
+                     uint32_t out_total, uint32_t row_begin, uint32_t in_dim, uint32_t out_dim, uint32_t n_rows, void *scratch,
+                     size_t scratch_bytes)
+{
+    if (n_rows == 0) return RC_OK;
+    if (world == 0 || world > RC_MAX_PEERS) return RC_ERR_BAD_ARGUMENT;
+    if (!x || !y_peers) return RC_ERR_NULL_POINTER;
+    for (uint32_t g = 0; g < world; g++)
+        if (!y_peers[g]) return RC_ERR_NULL_POINTER;
+    int rc = check_weight_args(type, w, scratch, y_peers[0], in_dim, out_dim);
+    if (rc) return rc;
+    if (!mmq_x_supports(type)) return RC_ERR_BAD_TYPE;
+    if ((uint64_t)row_begin + out_dim > out_total) return RC_ERR_BAD_SHAPE;
+    if (((uintptr_t)scratch & 15u)) return RC_ERR_MISALIGNED;
+    if (scratch_bytes < mmq_x_scratch_bytes(in_dim, n_rows)) return RC_ERR_SCRATCH_TOO_SMALL;
+    rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_mmq_x_f32(S(stream), type, w, x, nullptr, in_dim, out_dim, n_rows, scratch, nullptr, y_peers, world, out_total,
+                            row_begin);
+}
+
 int rc_allgather_push(void *stream, const void *src, size_t bytes, void *const *peer_dst,
                       void *const *peer_flags, void *epoch, uint32_t rank, uint32_t world)
 {

@@ -32,13 +32,11 @@ __device__ __forceinline__ unsigned long long gather_ns()
     return t;
 }
 
-// One CTA.  Shard i of the gathered buffer belongs to rank i.
-__global__ void __launch_bounds__(512)
-allgather_push_kernel(const uint4 *__restrict__ src, uint32_t n16, GatherPeers peers,
-                      unsigned long long *epoch_ctr, uint32_t rank, uint32_t world)
+// The work of one rank, by one CTA: store the shard into every rank's gathered buffer (shard i of a buffer
+// belongs to rank i), publish this call's epoch in every rank's flag array, wait (bounded) for every rank's.
+__device__ __forceinline__ void gather_body(const uint4 *__restrict__ src, uint32_t n16, const GatherPeers &peers,
+                                            unsigned long long *epoch_ctr, uint32_t rank, uint32_t world)
 {
-    pdl_launch_dependents(); // the consumer may start fetching its weights during the handshake
-    pdl_wait();              // the shard comes from the preceding kernel
     for (uint32_t r = 0; r < world; r++) {
         uint4 *dst = peers.dst[r] + (size_t)rank * n16;
         for (uint32_t i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
@@ -68,6 +66,28 @@ allgather_push_kernel(const uint4 *__restrict__ src, uint32_t n16, GatherPeers p
     __syncthreads();
 }
 
+__global__ void __launch_bounds__(512)
+allgather_push_kernel(const uint4 *__restrict__ src, uint32_t n16, GatherPeers peers,
+                      unsigned long long *epoch_ctr, uint32_t rank, uint32_t world)
+{
+    pdl_launch_dependents(); // the consumer may start fetching its weights during the handshake
+    pdl_wait();              // the shard comes from the preceding kernel; a peer's stores into this rank's
+                             // memory (a fused producer) are complete when its own handshake kernel starts
+    gather_body(src, n16, peers, epoch_ctr, rank, world);
+}
+
+// `world` logical ranks on ONE device, one CTA each, launched cooperatively so that they are co-resident
+// (separate launches that wait on one another are not guaranteed to run at the same time).
+struct LogicalRanks {
+    const uint4 *src[RC_MAX_PEERS];
+    unsigned long long *epoch[RC_MAX_PEERS];
+};
+__global__ void __launch_bounds__(512)
+allgather_push_logical_kernel(LogicalRanks ranks, uint32_t n16, GatherPeers peers, uint32_t world)
+{
+    gather_body(ranks.src[blockIdx.x], n16, peers, ranks.epoch[blockIdx.x], blockIdx.x, world);
+}
+
 } // namespace
 
 int gather_device_error(unsigned int *out, bool clear)
@@ -95,6 +115,22 @@ int launch_allgather_push(cudaStream_t s, const void *src, size_t bytes, void *c
     }
     return (int)launch_pdl(allgather_push_kernel, dim3(1), dim3(512), 0, s, static_cast<const uint4 *>(src),
                            (uint32_t)(bytes / 16), p, static_cast<unsigned long long *>(epoch), rank, world);
+}
+
+int launch_allgather_push_logical(cudaStream_t s, const void *const *srcs, size_t bytes, void *const *dsts, void *const *flags,
+                                  void *const *epochs, uint32_t world)
+{
+    GatherPeers p;
+    LogicalRanks lr;
+    for (uint32_t r = 0; r < RC_MAX_PEERS; r++) {
+        p.dst[r] = r < world ? static_cast<uint4 *>(dsts[r]) : nullptr;
+        p.flags[r] = r < world ? static_cast<unsigned long long *>(flags[r]) : nullptr;
+        lr.src[r] = r < world ? static_cast<const uint4 *>(srcs[r]) : nullptr;
+        lr.epoch[r] = r < world ? static_cast<unsigned long long *>(epochs[r]) : nullptr;
+    }
+    uint32_t n16 = (uint32_t)(bytes / 16);
+    void *args[] = {&lr, &n16, &p, &world};
+    return (int)cudaLaunchCooperativeKernel((const void *)allgather_push_logical_kernel, dim3(world), dim3(512), args, 0, s);
 }
 
 } // namespace rc

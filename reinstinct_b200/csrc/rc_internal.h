@@ -59,8 +59,11 @@ void mmq_x_set_debug(int mask);
 int mmq_x_read_prof(void *out, size_t bytes);
 int mmq_x_device_error(unsigned int *out, bool clear);
 size_t mmq_x_scratch_bytes(uint32_t in_dim, uint32_t n_tok);
+// y_peers != nullptr: the result is rows [col_off, col_off + out_dim) of a [n_tok][ld_out] matrix and is stored
+// into each of the n_peers copies of it (this rank's own and its peers' mapped ones); y is then unused
 int launch_mmq_x_f32(cudaStream_t s, int type, const void *w, const float *x, float *y, uint32_t in_dim, uint32_t out_dim,
-                     uint32_t n_tok, void *scratch, int32_t *dump);
+                     uint32_t n_tok, void *scratch, int32_t *dump, float *const *y_peers = nullptr, uint32_t n_peers = 0,
+                     uint32_t ld_out = 0, uint32_t col_off = 0);
 uint32_t mmq_grouped_bn();
 uint32_t matvec_grouped_bn();
 void mmq_force_dp4a(int on);
@@ -78,6 +81,8 @@ int launch_moe_scatter_rows(cudaStream_t s, const float *src, const int32_t *per
 int launch_allgather_push(cudaStream_t s, const void *src, size_t bytes, void *const *peer_dst,
                           void *const *peer_flags, void *epoch, uint32_t rank, uint32_t world);
 int gather_device_error(unsigned int *out, bool clear);
+int launch_allgather_push_logical(cudaStream_t s, const void *const *srcs, size_t bytes, void *const *dsts, void *const *flags,
+                                  void *const *epochs, uint32_t world);
 
 int launch_rmsnorm_q8(cudaStream_t s, const float *x, const float *add, const float *w, float *hidden_io, float *y, void *out,
                       uint32_t n, uint32_t n_vec, float eps);

@@ -645,7 +645,8 @@ __global__ void __launch_bounds__(kActWarps * 32) activations_to_f16_kernel(cons
     {   // pass 1: warp -> (token, quarter of the row)
         const uint32_t t = warp >> 2, qk = warp & 3u, tok = tok0 + t;
         float amax = 0.0f;
-        if (tok < n_tok) {
+        // an entry the sort dropped (perm = -1: an expert id outside the table) is a row of zeros, never a load
+        if (tok < n_tok && !(src.index && src.index[tok] < 0)) {
             const float *row = src.x + (size_t)(src.index ? (uint32_t)src.index[tok] / src.div : tok) * src.row_stride;
             const uint32_t per = in_dim / 4u, lo = qk * per, hi = lo + per; // in_dim is a multiple of 32
             if (src.act >= 0) {
@@ -684,17 +685,20 @@ __global__ void __launch_bounds__(kActWarps * 32) activations_to_f16_kernel(cons
     const uint32_t tl = lane >> 2, pair = lane & 3u; // store role: token tl, halves 2*pair, 2*pair + 1 of a chunk
     const float s_mine = s_scale[lane & 7u];         // lane t < 8 also does token t's divides and xsum
     const float *rows[kActTokens];
+    uint32_t live = 0u; // bit t: token t of the group has a source row
 #pragma unroll
     for (int t = 0; t < kActTokens; t++) {
         const uint32_t tok = min(tok0 + t, n_tok - 1u);
-        rows[t] = src.x + (size_t)(src.index ? (uint32_t)src.index[tok] / src.div : tok) * src.row_stride;
+        const bool dropped = src.index && src.index[tok] < 0;
+        rows[t] = src.x + (size_t)(src.index ? (dropped ? 0u : (uint32_t)src.index[tok] / src.div) : tok) * src.row_stride;
+        if (tok0 + t < n_tok && !dropped) live |= 1u << t;
     }
     for (uint32_t sb = warp + 32u * blockIdx.y; sb < n_sub; sb += 32u * gridDim.y) {
         float v[kActTokens], sum[kActTokens];
         uint32_t bmax[kActTokens]; // |v| as bits: non-negative floats order like unsigned integers
 #pragma unroll
         for (int t = 0; t < kActTokens; t++) {
-            v[t] = (tok0 + t < n_tok) ? act_value(rows[t], sb * 32u + lane, in_dim, src.act) : 0.0f;
+            v[t] = ((live >> t) & 1u) ? act_value(rows[t], sb * 32u + lane, in_dim, src.act) : 0.0f;
             const float a = fabsf(v[t]);
             bmax[t] = __reduce_max_sync(0xFFFFFFFFu, a == a ? __float_as_uint(a) : 0u); // fmaxf skips a NaN: so does this
             sum[t] = v[t];

@@ -235,7 +235,8 @@ template <int FMT> struct SmemX {
 
 struct XParams {
     const uint8_t *w;
-    float *y;
+    float *y[RC_MAX_PEERS]; // the output matrix on this device and, for a row shard that gathers itself, its peers' copies
+    uint32_t n_y, ld_out, col_off; // copies; row pitch of the output; first column (weight row) this launch owns
     int32_t *dump;   // debug variant: the integer tile of every (token, row, sub-block)
     uint32_t in_dim, out_dim, n_tok, tok_ld;
     uint32_t y_vec4; // y rows may be written with 16-byte stores
@@ -683,18 +684,23 @@ mmqx_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CU
                 const XTile t = x_tile(P, id, tiles_t);
                 if (tlane >= t.n_valid) return;
                 const uint32_t rowc = t.m0 + c * 32u;
-                float *dst = P.y + (size_t)(t.tok0 + tlane) * P.out_dim + rowc;
-                if (P.y_vec4 && rowc + 32u <= P.out_dim) {
+                const size_t off = (size_t)(t.tok0 + tlane) * P.ld_out + P.col_off + rowc;
+                // every copy of the output (one, or this GPU's and its peers': plain stores over NVLink, 128
+                // contiguous bytes per thread and chunk, issued as the tile finishes while other tiles compute)
+                for (uint32_t g = 0; g < P.n_y; g++) {
+                    float *dst = P.y[g] + off;
+                    if (P.y_vec4 && rowc + 32u <= P.out_dim) {
 #pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        *reinterpret_cast<uint4 *>(dst + 4 * k) = make_uint4(v0[4 * k], v0[4 * k + 1], v0[4 * k + 2], v0[4 * k + 3]);
-                        *reinterpret_cast<uint4 *>(dst + 16 + 4 * k) = make_uint4(v1[4 * k], v1[4 * k + 1], v1[4 * k + 2], v1[4 * k + 3]);
-                    }
-                } else {
+                        for (int k = 0; k < 4; k++) {
+                            *reinterpret_cast<uint4 *>(dst + 4 * k) = make_uint4(v0[4 * k], v0[4 * k + 1], v0[4 * k + 2], v0[4 * k + 3]);
+                            *reinterpret_cast<uint4 *>(dst + 16 + 4 * k) = make_uint4(v1[4 * k], v1[4 * k + 1], v1[4 * k + 2], v1[4 * k + 3]);
+                        }
+                    } else {
 #pragma unroll
-                    for (int k = 0; k < 16; k++) {
-                        if (rowc + k < P.out_dim) dst[k] = __uint_as_float(v0[k]);
-                        if (rowc + 16u + k < P.out_dim) dst[16 + k] = __uint_as_float(v1[k]);
+                        for (int k = 0; k < 16; k++) {
+                            if (rowc + k < P.out_dim) dst[k] = __uint_as_float(v0[k]);
+                            if (rowc + 16u + k < P.out_dim) dst[16 + k] = __uint_as_float(v1[k]);
+                        }
                     }
                 }
             };
@@ -1098,7 +1104,8 @@ size_t mmq_x_scratch_bytes(uint32_t in_dim, uint32_t n_tok)
 // x f32 [n_tok][in_dim] -> y f32 [n_tok][out_dim]; scratch 16-byte aligned, mmq_x_scratch_bytes large.
 // dump != nullptr: also the integer tiles, int32 [n_tok][out_dim][in_dim / 32].
 int launch_mmq_x_f32(cudaStream_t s, int type, const void *w, const float *x, float *y, uint32_t in_dim, uint32_t out_dim,
-                     uint32_t n_tok, void *scratch, int32_t *dump)
+                     uint32_t n_tok, void *scratch, int32_t *dump, float *const *y_peers, uint32_t n_peers, uint32_t ld_out,
+                     uint32_t col_off)
 {
     const uint32_t ld = x_tok_ld(n_tok);
     // 8 tokens per CTA; a second CTA shares their sub-blocks while that still adds SMs
@@ -1108,13 +1115,30 @@ int launch_mmq_x_f32(cudaStream_t s, int type, const void *w, const float *x, fl
     if (e != cudaSuccess) return (int)e;
     XParams P;
     P.w = (const uint8_t *)w;
-    P.y = y;
+    bool aligned = true;
+    for (uint32_t g = 0; g < RC_MAX_PEERS; g++) P.y[g] = nullptr;
+    if (y_peers) {
+        P.n_y = n_peers;
+        P.ld_out = ld_out;
+        P.col_off = col_off;
+        for (uint32_t g = 0; g < n_peers; g++) {
+            P.y[g] = y_peers[g];
+            aligned = aligned && ((uintptr_t)y_peers[g] & 15u) == 0;
+        }
+        aligned = aligned && (ld_out & 3u) == 0 && (col_off & 3u) == 0;
+    } else {
+        P.n_y = 1;
+        P.ld_out = out_dim;
+        P.col_off = 0;
+        P.y[0] = y;
+        aligned = ((uintptr_t)y & 15u) == 0 && (out_dim & 3u) == 0;
+    }
     P.dump = dump;
     P.in_dim = in_dim;
     P.out_dim = out_dim;
     P.n_tok = n_tok;
     P.tok_ld = ld;
-    P.y_vec4 = (((uintptr_t)y & 15u) == 0 && (out_dim & 3u) == 0) ? 1u : 0u;
+    P.y_vec4 = aligned ? 1u : 0u;
     P.debug = (uint32_t)g_x_debug;
     return dump ? launch_x_type<true>(s, type, P, scratch) : launch_x_type<false>(s, type, P, scratch);
 }

@@ -22,7 +22,7 @@ __all__ = [
     "launch_quantize_q8", "launch_matvec", "launch_matvec_xq8", "launch_matvec_batched",
     "matvec_block_dots", "launch_mmq_gemm", "launch_moe_sort", "launch_moe_gather_xq",
     "launch_moe_grouped_gemm", "launch_moe_scatter_rows", "repacked_len", "init", "PeerAllGather",
-    "MoeGroupedGemm", "launch_rmsnorm_q8", "launch_add_rmsnorm_q8", "launch_swiglu_q8",
+    "PeerBuffers", "GatheredPrefillGemm", "MoeGroupedGemm", "launch_rmsnorm_q8", "launch_add_rmsnorm_q8", "launch_swiglu_q8",
     "launch_moe_expert_matvec", "launch_moe_gate_up_swiglu", "launch_moe_topk", "launch_moe_act_q8", "launch_moe_combine", "ACT_GEGLU", "ACT_SWIGLU",
 ]
 
@@ -408,21 +408,19 @@ def launch_moe_combine(experts: torch.Tensor, ids: torch.Tensor, weights: torch.
                                      _ptr(out), hidden, n_used, n_tok), "rc_moe_combine")
 
 
-class PeerAllGather:
-    """All-gather of one small shard per rank by direct stores into the peers' memory
-    (rc_allgather_push): one process per GPU on one box, buffers exported with CUDA IPC.  The
-    gathered buffer (`world * bytes_per_rank` bytes at `buffer_ptr`, rank r's shard at offset
-    r * bytes_per_rank) is written by all ranks; a call returns, on the stream, once every
-    rank's shard of this call has arrived.  Safe to capture in a CUDA graph."""
+class PeerBuffers:
+    """`n_buffers` equal device buffers per rank plus the handshake words, allocated with rc_malloc and mapped
+    into every rank of the group with CUDA IPC (one process per GPU on one box).  ptrs[k] is a ctypes array of
+    every rank's k-th buffer (own one included), as the gather entry points take them."""
 
-    def __init__(self, bytes_per_rank: int, group=None):
+    def __init__(self, bytes_per_buffer: int, n_buffers: int = 2, group=None):
         import torch.distributed as dist
 
-        assert bytes_per_rank % 16 == 0, "shards are copied in 16-byte units"
         lib = _lib.load()
-        self.lib, self.bytes = lib, bytes_per_rank
+        self.lib, self.bytes, self.n_buffers, self.group = lib, bytes_per_buffer, n_buffers, group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
-        data = (self.world * bytes_per_rank + 255) // 256 * 256
+        self._stride = (bytes_per_buffer + 255) // 256 * 256
+        data = self._stride * n_buffers
         flags = (self.world * 8 + 255) // 256 * 256
         base = C.c_void_p()
         check(lib.rc_malloc(C.byref(base), data + flags + 256), "rc_malloc")
@@ -444,26 +442,103 @@ class PeerAllGather:
             check(lib.rc_ipc_open_handle(hb, C.byref(p)), "rc_ipc_open_handle")
             self._opened.append(p.value)
             bases.append(p.value)
-        self._dst = (C.c_void_p * self.world)(*bases)
-        self._flags = (C.c_void_p * self.world)(*[b + data for b in bases])
-        self._epoch = self._base + data + flags
-        self.buffer_ptr = self._base
+        self.ptrs = [(C.c_void_p * self.world)(*[b + k * self._stride for b in bases]) for k in range(n_buffers)]
+        self.own = [self._base + k * self._stride for k in range(n_buffers)]
+        self.flags = (C.c_void_p * self.world)(*[b + data for b in bases])
+        self.epoch = self._base + data + flags
         dist.barrier(group=group)
 
-    def gather(self, src) -> None:
-        check(self.lib.rc_allgather_push(_stream(), _ptr(src), self.bytes, self._dst, self._flags, self._epoch,
-                                         self.rank, self.world), "rc_allgather_push")
+    def barrier(self) -> None:
+        """rc_peer_barrier on the current stream: returns once every rank's barrier of this call has run, i.e.
+        once every store a peer issued before its barrier has landed here."""
+        check(self.lib.rc_peer_barrier(_stream(), self.flags, self.epoch, self.rank, self.world), "rc_peer_barrier")
 
-    def copy_out(self, dst: torch.Tensor) -> None:
-        """Gathered bytes -> a torch tensor (device or pinned host), on the current stream."""
+    def read(self, k: int, dst: torch.Tensor, n_bytes: int | None = None) -> None:
+        """This rank's k-th buffer -> a torch tensor (device or pinned host), on the current stream."""
         kind = 3 if dst.is_cuda else 2
-        check(self.lib.rc_memcpy_async(dst.data_ptr(), self.buffer_ptr, self.world * self.bytes, kind, _stream()),
+        check(self.lib.rc_memcpy_async(dst.data_ptr(), self.own[k], self.bytes if n_bytes is None else n_bytes, kind, _stream()),
               "rc_memcpy_async")
 
     def close(self) -> None:
+        import torch.distributed as dist
+
+        torch.cuda.current_stream().synchronize()
+        dist.barrier(group=self.group)  # nobody unmaps while a peer may still store
         for p in self._opened:
             self.lib.rc_ipc_close_handle(p)
         self._opened = []
         if self._base:
             self.lib.rc_free(self._base)
             self._base = 0
+
+
+class PeerAllGather:
+    """All-gather of one small shard per rank by direct stores into the peers' memory
+    (rc_allgather_push).  A call returns, on the stream, once every rank's shard of this call has arrived in
+    the gathered buffer at `buffer_ptr` (`world * bytes_per_rank` bytes, rank r's shard at offset
+    r * bytes_per_rank).  Consecutive calls ALTERNATE between two gathered buffers, so a fast rank's next
+    push can never land under a slower rank's consumer of the previous call; read `buffer_ptr` after each
+    call.  Safe to capture in a CUDA graph if the graph holds an even number of calls per object (a replay
+    then starts on the same buffer as the capture did)."""
+
+    def __init__(self, bytes_per_rank: int, group=None):
+        assert bytes_per_rank % 16 == 0, "shards are copied in 16-byte units"
+        self.bytes = bytes_per_rank
+        self.peers = PeerBuffers(bytes_per_rank * _world(group), 2, group)
+        self.rank, self.world = self.peers.rank, self.peers.world
+        self.calls = 0
+        self.buffer_ptr = self.peers.own[0]
+
+    def gather(self, src) -> None:
+        k = self.calls & 1
+        p = self.peers
+        check(p.lib.rc_allgather_push(_stream(), _ptr(src), self.bytes, p.ptrs[k], p.flags, p.epoch, self.rank, self.world),
+              "rc_allgather_push")
+        self.buffer_ptr = p.own[k]
+        self.calls += 1
+
+    def copy_out(self, dst: torch.Tensor) -> None:
+        """The buffer of the latest call -> a torch tensor (device or pinned host), on the current stream."""
+        self.peers.read((self.calls - 1) & 1 if self.calls else 0, dst, self.world * self.bytes)
+
+    def close(self) -> None:
+        self.peers.close()
+
+
+def _world(group) -> int:
+    import torch.distributed as dist
+
+    return dist.get_world_size(group)
+
+
+class GatheredPrefillGemm:
+    """Row-sharded PrefillGemm whose kernel gathers its own output (rc_matmul_gather + rc_peer_barrier): every
+    rank holds rows [row_begin, row_begin + w.out_dim) of an [out_total, in_dim] matrix, and after a call every
+    rank's output buffer holds the whole [n_rows][out_total] f32 product, bit-identical to the unsharded
+    rc_matmul.  Two output buffers alternate between calls (see PeerAllGather)."""
+
+    def __init__(self, max_rows: int, out_total: int, in_dim: int, group=None, device="cuda"):
+        self.out_total, self.max_rows = out_total, max_rows
+        self.peers = PeerBuffers(max_rows * out_total * 4, 2, group)
+        lib = _lib.load()
+        self.scratch = torch.empty(lib.rc_matmul_scratch_bytes(in_dim, max(max_rows, MATVEC_MAX_ROWS + 1)), dtype=torch.uint8,
+                                   device=device)
+        self.calls = 0
+
+    def matmul(self, w: GpuMatvecTensor, x: torch.Tensor, n_rows: int, row_begin: int, barrier: bool = True) -> int:
+        """Returns the index of the output buffer this call fills."""
+        assert w.repacked and n_rows <= self.max_rows
+        k = self.calls & 1
+        p = self.peers
+        check(p.lib.rc_matmul_gather(_stream(), w.dtype, _ptr(w.data), _ptr(x), p.ptrs[k], p.world, self.out_total, row_begin,
+                                     w.in_dim, w.out_dim, n_rows, _ptr(self.scratch), self.scratch.numel()), "rc_matmul_gather")
+        if barrier:
+            p.barrier()
+        self.calls += 1
+        return k
+
+    def read(self, k: int, dst: torch.Tensor, n_rows: int) -> None:
+        self.peers.read(k, dst, n_rows * self.out_total * 4)
+
+    def close(self) -> None:
+        self.peers.close()

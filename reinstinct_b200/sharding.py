@@ -126,3 +126,33 @@ def combine_rows(rows: torch.Tensor, plan: DispatchPlan, group=None) -> torch.Te
     out = torch.empty_like(back)
     out[plan.order] = back
     return out
+
+
+# ---- failure detection on the host --------------------------------------------------------------
+#
+# A rank may only leave between steps, with none of its kernels or collectives in flight.  The others
+# must learn of it on the host before their next launch: a device-side wait on a peer that is gone would
+# merely run out (rc_device_status bit 16) after the step's outputs are already lost.
+
+
+class RankLeft(RuntimeError):
+    def __init__(self, ranks):
+        super().__init__(f"ranks {sorted(ranks)} left the job")
+        self.ranks = sorted(ranks)
+
+
+def announce_leave(store, rank: int) -> None:
+    """Called by a rank that is about to leave (between steps)."""
+    store.set(f"reinstinct/left/{rank}", b"1")
+
+
+def departed_ranks(store, world: int) -> list[int]:
+    """Ranks that have announced their leave (a non-blocking look at the rendezvous store)."""
+    return [r for r in range(world) if store.check([f"reinstinct/left/{r}"])]
+
+
+def check_peers_alive(store, world: int) -> None:
+    """Raises RankLeft if any rank has announced its leave; call before every sharded launch."""
+    gone = departed_ranks(store, world)
+    if gone:
+        raise RankLeft(gone)

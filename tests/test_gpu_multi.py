@@ -44,20 +44,39 @@ def _worker(rank: int, world: int, port: int, q):
         rt.launch_quantize_q8(torch.from_numpy(x).cuda(), xq, in_dim, 1)
         y = torch.empty(rows, device="cuda")
         ga = rt.PeerAllGather(rows * 4)
-        for _ in range(3):  # several rounds over the same buffers and counters
-            rt.launch_matvec_xq8(w, xq, y)
-            ga.gather(y)
-        got = torch.empty(out_dim, device="cuda")
-        ga.copy_out(got)
-        torch.cuda.synchronize()
-        full32, _, _ = ro.matvec_q8(t, ro.repack(t, raw, in_dim, out_dim), ro.quantize_q8(x), in_dim, out_dim, 1)
-        # same kernel, same rows, same arithmetic as the unsharded launch
         w_full = rt.GpuMatvecTensor.from_bytes_matvec(raw, t, in_dim, out_dim)
         y_full = torch.empty(out_dim, device="cuda")
-        rt.launch_matvec_xq8(w_full, xq, y_full)
-        torch.cuda.synchronize()
-        assert torch.equal(got, y_full), "gathered shards differ from the single-GPU launch"
+        got = torch.empty(out_dim, device="cuda")
+        lib = rt._lib.load()
+        for rnd in range(5):  # new activations every round over the same (alternating) buffers and counters
+            x = cases.synth_case(t, in_dim, out_dim, 1, seed=50 + rnd)[1]
+            rt.launch_quantize_q8(torch.from_numpy(x).cuda(), xq, in_dim, 1)
+            rt.launch_matvec_xq8(w, xq, y)
+            ga.gather(y)
+            ga.copy_out(got)
+            # same kernel, same rows, same arithmetic as the unsharded launch
+            rt.launch_matvec_xq8(w_full, xq, y_full)
+            torch.cuda.synchronize()
+            assert torch.equal(got, y_full), f"round {rnd}: gathered shards differ from the single-GPU launch"
+        st = __import__("ctypes").c_uint(0)
+        assert lib.rc_device_status(__import__("ctypes").byref(st)) == 0 and st.value == 0
+        full32, _, _ = ro.matvec_q8(t, ro.repack(t, raw, in_dim, out_dim), ro.quantize_q8(x), in_dim, out_dim, 1)
         assert ro.rel_l2(got.cpu().numpy(), full32.astype(np.float64)) < 1e-3
+        # the row-sharded prefill GEMM that gathers its own output: every rank ends with the whole product,
+        # bit-identical to the unsharded call, on both of its alternating buffers
+        P = 200
+        xs = torch.from_numpy(cases.synth_case(t, in_dim, out_dim, P, seed=77)[1]).cuda()
+        y_ref, _ = rt.PrefillGemm().matmul_block_dots(w_full, xs, P)
+        gg = rt.GatheredPrefillGemm(P, out_dim, in_dim)
+        b0, _ = sh.row_shard_range(out_dim, rank, world)
+        y_all = torch.empty(P, out_dim, device="cuda")
+        for rnd in range(3):
+            k = gg.matmul(w, xs, P, b0)
+            gg.read(k, y_all, P)
+            torch.cuda.synchronize()
+            assert torch.equal(y_all, y_ref), f"gathered GEMM round {rnd} differs from the unsharded product"
+        assert lib.rc_device_status(__import__("ctypes").byref(st)) == 0 and st.value == 0
+        gg.close()
         ga.close()
         q.put((rank, "ok"))
     except Exception as e:  # report instead of leaving the peer waiting

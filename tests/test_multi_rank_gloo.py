@@ -22,9 +22,12 @@ def _free_port() -> int:
 
 
 def _worker(rank: int, world: int, port: int, fn_name: str, q):
+    import datetime
+
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    # a short collective timeout: a peer that is gone ends the next collective with an error, not a hang
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
     try:
         globals()[fn_name](rank, world)
         q.put((rank, "ok"))
@@ -82,6 +85,42 @@ def _expert_parallel_case(rank: int, world: int):
     assert torch.equal(back, want)
 
 
+def _rank_leaves_announced_case(rank: int, world: int):
+    """A rank leaves between steps and says so in the rendezvous store: the other learns of it on the host
+    before its next launch."""
+    store = dist.distributed_c10d._get_default_store()
+    t = torch.ones(4) * (rank + 1)
+    dist.all_reduce(t)  # step 1: everybody is there
+    assert float(t[0]) == sum(range(1, world + 1))
+    if rank == world - 1:
+        sh.announce_leave(store, rank)
+        return  # leaves: no collective in flight
+    import time
+    for _ in range(200):  # the survivors poll the store before their next step
+        if sh.departed_ranks(store, world):
+            break
+        time.sleep(0.02)
+    with pytest.raises(sh.RankLeft) as e:
+        sh.check_peers_alive(store, world)
+    assert e.value.ranks == [world - 1]
+
+
+def _rank_leaves_silently_case(rank: int, world: int):
+    """A rank leaves between steps without a word: the survivor's next collective ends with an error within
+    the process group's timeout."""
+    t = torch.ones(4)
+    dist.all_reduce(t)
+    if rank == world - 1:
+        return
+    import time
+    t0 = time.time()
+    with pytest.raises(Exception):
+        for _ in range(3):  # the peer's sockets may outlive it by one call
+            dist.all_reduce(t)
+            time.sleep(0.5)
+    assert time.time() - t0 < 60
+
+
 def test_row_shard_ranges_cover_everything():
     for out_dim in (17408, 5120, 259, 40, 31, 64):
         for world in (1, 2, 3, 4, 8):
@@ -101,3 +140,11 @@ def test_row_sharded_matvec_two_ranks():
 
 def test_expert_parallel_dispatch_two_ranks():
     _run("_expert_parallel_case")
+
+
+def test_rank_that_leaves_is_seen_in_the_store():
+    _run("_rank_leaves_announced_case")
+
+
+def test_rank_that_leaves_silently_ends_the_next_collective_with_an_error():
+    _run("_rank_leaves_silently_case")
