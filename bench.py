@@ -9,8 +9,11 @@ distinct copies of the layer's weights so that no launch finds its weights in L2
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
+The K steps are replayed from CUDA graphs and timed as one round; the round is repeated until the
+timed region lasts at least 50 ms, and `ms_per_step` is the median round (min and max beside it).
+
 With N > 1 (launched by torch.distributed.run, one rank per GPU) every matrix is split by
-output rows, each rank streams its shard, and the shards' outputs are all-gathered.
+output rows, each rank streams its shard, and the shards' outputs are gathered by peer stores.
 `--impl reference` times the reference's CPU path (dequantize to f32 + sequential-f32 row
 dots, row-parallel over the host cores) on a bounded sample of the same workload.
 """
@@ -91,104 +94,6 @@ class ClockSampler:
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(smax) if smax else None,
                 "samples": len(sm), "reasons": sorted(reasons)}
-
-
-def moe_layer(rt, synth, torch, dev, timed):
-    """Config 5: 256 experts, top-8 of 512 tokens, hidden 2048, expert FFN 512: router top-k, sort,
-    gather, grouped gate+up GEMM (Q4_K [1024, 2048] per expert), SwiGLU + quantize, grouped down
-    GEMM (Q6_K [2048, 512]), scatter, weighted combine; every step a launch of the library.
-    HBM-bound: the figure of merit is expert-weight bytes / s."""
-    E, H, F, NT, K = 256, 2048, 512, 512, 8
-    lib_tile = 8  # experts' worth of distinct blocks, tiled to 256 experts (bytes are what matter)
-
-    def slab(t, in_dim, out_dim, seed):
-        one = synth.synth_blocks(t, in_dim, out_dim * lib_tile, seed)
-        return rt.GpuExpertTensor.from_bytes(np.tile(one, E // lib_tile), t, in_dim, out_dim, E, device=dev)
-
-    gu, dn = slab(Q4_K, H, 2 * F, 91), slab(Q6_K, F, H, 92)
-    logits = torch.from_numpy(synth.synth_router_logits(NT, E, 93)).to(dev)
-    NE = NT * K
-    ids = torch.empty(NT, K, dtype=torch.int32, device=dev)
-    wts = torch.empty(NT, K, device=dev)
-    x = torch.from_numpy(synth.synth_activations(NT, H, 94)).to(dev)
-    moe = rt.MoeGroupedScratch.new(E, NE, device=dev)
-    u8 = dict(dtype=torch.uint8, device=dev)
-    xq, xg = torch.empty(NT * (H // 32) * 40, **u8), torch.empty(NE * (H // 32) * 40, **u8)
-    hq = torch.empty(NE * (F // 32) * 40, **u8)
-    y1 = torch.empty(NE, 2 * F, device=dev)
-    y2, per_entry = torch.empty(NE, H, device=dev), torch.empty(NE, H, device=dev)
-    out = torch.empty(NT, H, device=dev)
-
-    def step(i):
-        rt.launch_moe_topk(logits, ids, wts, E, K, NT)
-        rt.launch_quantize_q8(x, xq, H, NT)
-        rt.launch_moe_sort(moe, ids, NE)
-        rt.launch_moe_gather_xq(moe, xq, xg, H // 32, K, NE)
-        rt.launch_moe_grouped_gemm(moe, gu, xg, y1, H, 2 * F, NE)
-        rt.launch_moe_act_q8(y1, hq, F, NE, rt.ACT_SWIGLU)
-        rt.launch_moe_grouped_gemm(moe, dn, hq, y2, F, H, NE)
-        rt.launch_moe_scatter_rows(moe, y2, per_entry, H, NE)
-        rt.launch_moe_combine(per_entry, ids, wts, None, out, H, K, NT)
-
-    # The same layer through the grouped GEMM that takes f32 activations (f16 operands, whole-K
-    # accumulation): the gather, the activation and both quantizations happen inside its prologue.
-    gg = rt.MoeGroupedGemm(device=dev)
-
-    def step_f32(i):
-        rt.launch_moe_topk(logits, ids, wts, E, K, NT)
-        rt.launch_moe_sort(moe, ids, NE)
-        gg.gate_up(moe, gu, x, K, y1, NE)
-        gg.down(moe, dn, y1, rt.ACT_SWIGLU, y2, NE)
-        rt.launch_moe_scatter_rows(moe, y2, per_entry, H, NE)
-        rt.launch_moe_combine(per_entry, ids, wts, None, out, H, K, NT)
-
-    reps = 10
-    us_i8 = timed(step, reps, 3) / reps * 1e3
-    out_i8 = out.clone()
-    us_f32 = timed(step_f32, reps, 3) / reps * 1e3
-    rel = float((out - out_i8).norm() / out_i8.norm())
-    us = min(us_i8, us_f32)
-    us_gu = timed(lambda i: rt.launch_moe_grouped_gemm(moe, gu, xg, y1, H, 2 * F, NE), reps, 3) / reps * 1e3
-    us_dn = timed(lambda i: rt.launch_moe_grouped_gemm(moe, dn, hq, y2, F, H, NE), reps, 3) / reps * 1e3
-    us_gu32 = timed(lambda i: gg.gate_up(moe, gu, x, K, y1, NE), reps, 3) / reps * 1e3
-    us_dn32 = timed(lambda i: gg.down(moe, dn, y1, rt.ACT_SWIGLU, y2, NE), reps, 3) / reps * 1e3
-    wbytes = gu.data.numel() + dn.data.numel()
-    peak, _ = measured_peaks()
-
-    # decode side of the same layer: one token, its 8 routed experts through the expert-indexed matvec
-    # (gate+up then down).  Each call takes the next 8 experts of the slab, so every weight byte comes
-    # from HBM (549 MB of experts > 4x L2).
-    ids_dec = torch.arange(E, dtype=torch.int32, device=dev).reshape(E // K, K)
-    xq1 = torch.empty((H // 32) * 40, **u8)
-    hq1 = torch.empty(K * (F // 32) * 40, **u8)
-    g1, d1 = torch.empty(1, K, 2 * F, device=dev), torch.empty(1, K, H, device=dev)
-    rt.launch_quantize_q8(x[:1], xq1, H, 1)
-
-    def decode_step(i):
-        sel = ids_dec[i % (E // K)]
-        rt.launch_moe_expert_matvec(gu, sel, xq1, g1, K, 1, H // 32, 0)
-        rt.launch_moe_act_q8(g1, hq1, F, K, rt.ACT_SWIGLU)
-        rt.launch_moe_expert_matvec(dn, sel, hq1, d1, K, 1, K * (F // 32), F // 32)
-
-    # replayed from a CUDA graph of one pass over all 32 expert groups, as a decode loop would be
-    for i in range(3):
-        decode_step(i)
-    torch.cuda.synchronize()
-    g_dec = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g_dec):
-        for i in range(E // K):
-            decode_step(i)
-    us_dec = timed(lambda i: g_dec.replay(), 4, 2) / (4 * (E // K)) * 1e3
-    dec_bytes = (gu.bytes_per_expert + dn.bytes_per_expert) * K
-    return {"workload": "config 5: 256 experts top-8, 512 tokens, hidden 2048, ffn 512 (548.9 MB of expert weights, 25.8 GOP)",
-            "us_layer": us, "tok_per_s_per_layer": NT / (us * 1e-6), "tops": 2.0 * NE * (H * 2 * F + F * H) / us / 1e6,
-            "us_layer_blockq8_route": us_i8, "us_layer_f32_route": us_f32, "rel_l2_between_routes": rel,
-            "us_gate_up": us_gu, "us_down": us_dn, "us_gate_up_f32_route": us_gu32, "us_down_f32_route": us_dn32,
-            "decode_1_token": {"us": us_dec, "expert_bytes": dec_bytes, "gbs": dec_bytes / us_dec / 1e3,
-                               "frac_of_hbm_peak": dec_bytes / us_dec / 1e3 / peak,
-                               "launches": "expert matvec (gate+up), SwiGLU+quantize, expert matvec (down)"},
-            "roofline": {"bound": "hbm", "achieved": wbytes / us / 1e3, "peak": peak, "unit": "GB/s",
-                         "frac": wbytes / us / 1e3 / peak, "note": "expert-weight bytes over the whole layer time"}}
 
 
 # ------------------------------------------------------------------------------------- CPU arm
@@ -280,18 +185,28 @@ def workload_config(n_gpus: int) -> dict:
     return {
         "workload": "config 2: dense-27B decode FFN, batch 1 (quantize x; Q4_K gate, up 5120->17408; SwiGLU+quantize; Q6_K down 17408->5120)",
         "bytes_per_step": 176168960,
-        "l2": "weights rotate over 3 distinct layer copies (528 MB > 4x L2); every launch reads cold HBM",
+        "l2": "weights rotate over 4 distinct layer copies (705 MB > 5x L2); every launch reads cold HBM",
         "parallelism": (f"row-shard x{n_gpus}; all-gather of the quantized intermediate and of down's output "
-                        "(peer-memory push over NVLink, or NCCL with --nccl-gather)" if n_gpus > 1 else "single GPU"),
+                        "(peer-memory push over NVLink, two alternating buffers)" if n_gpus > 1 else "single GPU"),
     }
 
 
 # ------------------------------------------------------------------------------------- GPU arm
 
-# DRAM bytes of one Q4_K 5120->17408 matvec launch, from the ncu capture summarised in
-# profiles/matvec_q4k_5120x17408.md (algorithmic bytes: 51,527,680).
-Q4K_DRAM_TRAFFIC_BYTES = 51_566_000
-INT8_DENSE_PEAK_TOPS = 4500.0  # nominal B200 dense int8; no measured int8 figure is supplied
+INT8_DENSE_PEAK_TOPS = 4500.0  # nominal B200 dense int8
+
+
+def q4k_dram_traffic() -> tuple[int | None, str]:
+    """DRAM bytes of one Q4_K 5120->17408 matvec launch, as the ncu summary kept beside the other
+    profile summaries records it (dram__bytes_read.sum + dram__bytes_write.sum of one launch)."""
+    import re
+
+    f = ROOT / "profiles" / "matvec_q4k_5120x17408.md"
+    try:
+        m = re.search(r"dram bytes per launch \(read \+ write\)[^:]*:\s*([0-9,]+)", f.read_text())
+        return int(m.group(1).replace(",", "")), "ncu summary of this kernel: dram__bytes_read.sum + dram__bytes_write.sum, one launch"
+    except Exception:
+        return None, "no ncu summary found"
 
 
 def measured_tensor_peak() -> tuple[float, str]:
@@ -303,6 +218,143 @@ def measured_tensor_peak() -> tuple[float, str]:
         except Exception:
             pass
     return 1590.0, "fallback"
+
+
+def moe_layer(rt, synth, torch, dev, timed):
+    """Config 5: 256 experts, top-8 of 512 tokens, hidden 2048, expert FFN 512: router top-k, sort,
+    gather, grouped gate+up GEMM (Q4_K [1024, 2048] per expert), SwiGLU + quantize, grouped down
+    GEMM (Q6_K [2048, 512]), scatter, weighted combine; every step a launch of the library.
+    HBM-bound: the figure of merit is expert-weight bytes / s.  The reported layer is the exact-integer
+    route (BlockQ8 records into the per-sub-block tensor-core kernels); the f16-dequantized route, an
+    approximation, rides beside it."""
+    E, H, F, NT, K = 256, 2048, 512, 512, 8
+    lib_tile = 8  # experts' worth of distinct blocks, tiled to 256 experts (bytes are what matter)
+
+    def slab(t, in_dim, out_dim, seed):
+        one = synth.synth_blocks(t, in_dim, out_dim * lib_tile, seed)
+        return rt.GpuExpertTensor.from_bytes(np.tile(one, E // lib_tile), t, in_dim, out_dim, E, device=dev)
+
+    gu, dn = slab(Q4_K, H, 2 * F, 91), slab(Q6_K, F, H, 92)
+    logits = torch.from_numpy(synth.synth_router_logits(NT, E, 93)).to(dev)
+    NE = NT * K
+    ids = torch.empty(NT, K, dtype=torch.int32, device=dev)
+    wts = torch.empty(NT, K, device=dev)
+    x = torch.from_numpy(synth.synth_activations(NT, H, 94)).to(dev)
+    moe = rt.MoeGroupedScratch.new(E, NE, device=dev)
+    u8 = dict(dtype=torch.uint8, device=dev)
+    xq, xg = torch.empty(NT * (H // 32) * 40, **u8), torch.empty(NE * (H // 32) * 40, **u8)
+    hq = torch.empty(NE * (F // 32) * 40, **u8)
+    y1 = torch.empty(NE, 2 * F, device=dev)
+    y2, per_entry = torch.empty(NE, H, device=dev), torch.empty(NE, H, device=dev)
+    out = torch.empty(NT, H, device=dev)
+
+    def step(i):
+        rt.launch_moe_topk(logits, ids, wts, E, K, NT)
+        rt.launch_quantize_q8(x, xq, H, NT)
+        rt.launch_moe_sort(moe, ids, NE)
+        rt.launch_moe_gather_xq(moe, xq, xg, H // 32, K, NE)
+        rt.launch_moe_grouped_gemm(moe, gu, xg, y1, H, 2 * F, NE)
+        rt.launch_moe_act_q8(y1, hq, F, NE, rt.ACT_SWIGLU)
+        rt.launch_moe_grouped_gemm(moe, dn, hq, y2, F, H, NE)
+        rt.launch_moe_scatter_rows(moe, y2, per_entry, H, NE)
+        rt.launch_moe_combine(per_entry, ids, wts, None, out, H, K, NT)
+
+    gg = rt.MoeGroupedGemm(device=dev)
+
+    def step_f16(i):
+        rt.launch_moe_topk(logits, ids, wts, E, K, NT)
+        rt.launch_moe_sort(moe, ids, NE)
+        gg.gate_up(moe, gu, x, K, y1, NE)
+        gg.down(moe, dn, y1, rt.ACT_SWIGLU, y2, NE)
+        rt.launch_moe_scatter_rows(moe, y2, per_entry, H, NE)
+        rt.launch_moe_combine(per_entry, ids, wts, None, out, H, K, NT)
+
+    reps = 10
+    us = timed(step, reps, 3) / reps * 1e3
+    out_exact = out.clone()
+    us_f16 = timed(step_f16, reps, 3) / reps * 1e3
+    rel = float((out - out_exact).norm() / out_exact.norm())
+    us_gu = timed(lambda i: rt.launch_moe_grouped_gemm(moe, gu, xg, y1, H, 2 * F, NE), reps, 3) / reps * 1e3
+    us_dn = timed(lambda i: rt.launch_moe_grouped_gemm(moe, dn, hq, y2, F, H, NE), reps, 3) / reps * 1e3
+    us_gu16 = timed(lambda i: gg.gate_up(moe, gu, x, K, y1, NE), reps, 3) / reps * 1e3
+    us_dn16 = timed(lambda i: gg.down(moe, dn, y1, rt.ACT_SWIGLU, y2, NE), reps, 3) / reps * 1e3
+    wbytes = gu.data.numel() + dn.data.numel()
+    peak, _ = measured_peaks()
+
+    # decode side of the same layer: one token, its 8 routed experts through the expert-indexed matvec
+    # (gate+up then down).  Each call takes the next 8 experts of the slab, so every weight byte comes
+    # from HBM (549 MB of experts > 4x L2).
+    ids_dec = torch.arange(E, dtype=torch.int32, device=dev).reshape(E // K, K)
+    xq1 = torch.empty((H // 32) * 40, **u8)
+    hq1 = torch.empty(K * (F // 32) * 40, **u8)
+    g1, d1 = torch.empty(1, K, 2 * F, device=dev), torch.empty(1, K, H, device=dev)
+    rt.launch_quantize_q8(x[:1], xq1, H, 1)
+
+    def decode_step(i):
+        sel = ids_dec[i % (E // K)]
+        rt.launch_moe_expert_matvec(gu, sel, xq1, g1, K, 1, H // 32, 0)
+        rt.launch_moe_act_q8(g1, hq1, F, K, rt.ACT_SWIGLU)
+        rt.launch_moe_expert_matvec(dn, sel, hq1, d1, K, 1, K * (F // 32), F // 32)
+
+    for i in range(3):
+        decode_step(i)
+    torch.cuda.synchronize()
+    g_dec = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g_dec):
+        for i in range(E // K):
+            decode_step(i)
+    us_dec = timed(lambda i: g_dec.replay(), 4, 2) / (4 * (E // K)) * 1e3
+    dec_bytes = (gu.bytes_per_expert + dn.bytes_per_expert) * K
+    return {"workload": "config 5: 256 experts top-8, 512 tokens, hidden 2048, ffn 512 (548.9 MB of expert weights, 25.8 GOP)",
+            "route": "exact integer block dots: quantize, sort, gather, grouped int8 / integer-f16 tensor-core GEMMs",
+            "us_layer": us, "tok_per_s_per_layer": NT / (us * 1e-6), "tops": 2.0 * NE * (H * 2 * F + F * H) / us / 1e6,
+            "us_gate_up": us_gu, "us_down": us_dn,
+            "f16_dequantized_route": {"us_layer": us_f16, "us_gate_up": us_gu16, "us_down": us_dn16, "rel_l2_vs_exact_route": rel,
+                                      "note": "opt-in approximation (rc_mmq_gemm_grouped_f32); not the reported figure"},
+            "decode_1_token": {"us": us_dec, "expert_bytes": dec_bytes, "gbs": dec_bytes / us_dec / 1e3,
+                               "frac_of_hbm_peak": dec_bytes / us_dec / 1e3 / peak,
+                               "launches": "expert matvec (gate+up), SwiGLU+quantize, expert matvec (down)"},
+            "roofline": {"bound": "hbm", "achieved": wbytes / us / 1e3, "peak": peak, "unit": "GB/s",
+                         "frac": wbytes / us / 1e3 / peak, "note": "expert-weight bytes over the whole exact-route layer time"}}
+
+
+def small_matvecs(rt, synth, torch, dev, timed):
+    """Config 1 (Q8_0 4096 x 4096, batch 1) and config 3 (batch-4 verify matvec, 5120 x 5120, five formats):
+    each over rotating weight copies larger than L2, replayed from a CUDA graph; GB/s of repacked weights."""
+    peak, _ = measured_peaks()
+    out = {}
+
+    def one(t, in_dim, out_dim, n_rows, seed):
+        w1 = rt.GpuMatvecTensor.from_bytes_matvec(synth.synth_blocks(t, in_dim, out_dim, seed), t, in_dim, out_dim, device=dev)
+        n_copies = max(2, int(np.ceil(300e6 / w1.data.numel())))
+        ws = [w1] + [rt.GpuMatvecTensor.from_repacked(w1.data.clone(), t, in_dim, out_dim, device=dev) for _ in range(n_copies - 1)]
+        x = torch.from_numpy(synth.synth_activations(n_rows, in_dim, seed + 1)).to(dev)
+        xq = torch.empty(n_rows * (in_dim // 32) * 40, dtype=torch.uint8, device=dev)
+        rt.launch_quantize_q8(x, xq, in_dim, n_rows)
+        y = torch.empty(n_rows, out_dim, device=dev)
+
+        def sweep(i):
+            for w in ws:
+                if n_rows == 1:
+                    rt.launch_matvec_xq8(w, xq, y)
+                else:
+                    rt.launch_matvec_batched(w, xq, y, n_rows)
+        sweep(0)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            sweep(0)
+        reps = 20
+        us = timed(lambda i: g.replay(), reps, 3) * 1e3 / (reps * n_copies)
+        nbytes = w1.data.numel()
+        return {"us": us, "bytes": nbytes, "gbs": nbytes / us / 1e3, "frac_of_hbm_peak": nbytes / us / 1e3 / peak, "copies": n_copies}
+
+    out["config1_q8_0"] = dict(workload="config 1: Q8_0 4096x4096 matvec, batch 1", **one(8, 4096, 4096, 1, 301))
+    c3 = {}
+    for name, t in (("Q4_0", 2), ("Q5_K", 13), ("Q6_K", 14), ("Q8_0", 8), ("IQ4_XS", 23)):
+        c3[name] = one(t, 5120, 5120, 4, 310 + t)
+    out["config3_batch4"] = {"workload": "config 3: batch-4 verify matvec, 5120x5120, five formats", "formats": c3}
+    return out
 
 
 def moe_expert_parallel(rt, synth, torch, dist, dev, timed, rank, world):
@@ -323,20 +375,26 @@ def moe_expert_parallel(rt, synth, torch, dist, dev, timed, rank, world):
     x = torch.from_numpy(synth.synth_activations(NT, H, 94)[rank * nt:(rank + 1) * nt].copy()).to(dev)
     ids = torch.empty(nt, K, dtype=torch.int32, device=dev)
     wts = torch.empty(nt, K, device=dev)
-    gg = rt.MoeGroupedGemm(device=dev)
+    u8 = dict(dtype=torch.uint8, device=dev)
+    xq = torch.empty(nt * (H // 32) * 40, **u8)
     state = {}
 
     def step(i):
+        # exact route: the routed rows travel as BlockQ8 records (2.56 KB instead of 8 KB of f32 per entry)
         rt.launch_moe_topk(logits, ids, wts, E, K, nt)
+        rt.launch_quantize_q8(x, xq, H, nt)
         flat = ids.reshape(-1)
         plan = sh.plan_dispatch(flat, E)
-        rows_in = sh.dispatch_rows(x.repeat_interleave(K, dim=0).contiguous(), plan)
+        rows = xq.reshape(nt, (H // 32) * 40).repeat_interleave(K, dim=0).contiguous()
+        rows_in = sh.dispatch_rows(rows, plan)
         ids_in = (sh.dispatch_rows(flat.to(torch.float32).reshape(-1, 1), plan).reshape(-1).to(torch.int32) - e0).contiguous()
         n_in = rows_in.shape[0]
         moe = rt.MoeGroupedScratch.new(n_local, n_in, device=dev)
         rt.launch_moe_sort(moe, ids_in, n_in)
+        xg = torch.empty(n_in * (H // 32) * 40, **u8)
+        rt.launch_moe_gather_xq(moe, rows_in.reshape(-1), xg, H // 32, 1, n_in)
         y_sorted = torch.empty(n_in, 2 * F, device=dev)
-        gg.gate_up(moe, gu, rows_in, 1, y_sorted, n_in)
+        rt.launch_moe_grouped_gemm(moe, gu, xg, y_sorted, H, 2 * F, n_in)
         y_in = torch.empty(n_in, 2 * F, device=dev)
         rt.launch_moe_scatter_rows(moe, y_sorted, y_in, 2 * F, n_in)
         state["y"] = sh.combine_rows(y_in, plan)
@@ -346,49 +404,60 @@ def moe_expert_parallel(rt, synth, torch, dist, dev, timed, rank, world):
     us = timed(step, reps, 3) / reps * 1e3
     return {"workload": f"config 5 gate+up stage, {E} experts over {world} ranks, {nt} tokens per rank, top-{K}",
             "us_step": us, "tok_per_s": NT / (us * 1e-6), "rows_received_rank0": state.get("n_in"),
-            "collectives": "NCCL all_to_all_single: counts, rows, expert ids, results (eager, host-driven)"}
+            "collectives": "NCCL all_to_all_single: counts, BlockQ8 rows, expert ids, f32 results (eager, host-driven)"}
 
 
 def mmq_prefill_row_sharded(rt, synth, torch, dist, dev, timed, rank, world):
     """Config 4 sharded by output rows (N > 1): every rank holds rows [b, e) of the Q4_K 5120->17408 matrix
-    (multiples of 32 rows), runs the prefill GEMM of all 512 tokens against them, and the [512, e - b]
-    outputs are all-gathered (NCCL all_gather_into_tensor, eager) into [N, 512, widest shard]; no other
-    exchange.  Timed as the whole step, max over ranks; TOPS counts the whole 91.3 GOP."""
+    (multiples of 32 rows) and runs the exact prefill GEMM of all 512 tokens against them; the kernel stores
+    every finished tile into all ranks' [512, 17408] outputs (peer stores over NVLink, overlapped with the
+    tiles still computing), and one handshake kernel ends the step.  Timed as the whole step, max over ranks;
+    TOPS counts the whole 91.3 GOP.  The gathered result is checked against the unsharded call on rank 0."""
     from reinstinct_b200 import sharding as sh
 
     P = 512
     raw = synth.synth_blocks(Q4_K, HIDDEN, FFN, seed=77)
     shard, n_rows = sh.shard_raw_rows(raw, Q4_K, HIDDEN, FFN, rank, world)
+    b0, _ = sh.row_shard_range(FFN, rank, world)
     w = rt.GpuMatvecTensor.from_bytes_matvec(shard.copy(), Q4_K, HIDDEN, n_rows, device=dev)
     x = torch.from_numpy(synth.synth_activations(P, HIDDEN, 78)).to(dev)
+    gg = rt.GatheredPrefillGemm(P, FFN, HIDDEN, device=dev)
     gemm = rt.PrefillGemm(max_x=P * HIDDEN, device=dev)
-    widest = max(e - b for b, e in (sh.row_shard_range(FFN, r, world) for r in range(world)))
-    y = torch.zeros((P, widest), dtype=torch.float32, device=dev)
-    y_local = y if n_rows == widest else torch.empty((P, n_rows), dtype=torch.float32, device=dev)
-    gathered = torch.empty((world * P, widest), dtype=torch.float32, device=dev)
+    y_local = torch.empty((P, n_rows), dtype=torch.float32, device=dev)
 
-    def step(i):
-        gemm.matmul_into(y_local, w, x, P)
-        if y_local is not y:
-            y[:, :n_rows] = y_local
-        dist.all_gather_into_tensor(gathered, y)
-
-    def gemm_only(i):
-        gemm.matmul_into(y_local, w, x, P)
+    # one checked step
+    k = gg.matmul(w, x, P, b0)
+    got = torch.empty((P, FFN), dtype=torch.float32, device=dev)
+    gg.read(k, got, P)
+    torch.cuda.synchronize()
+    same = None
+    if rank == 0:
+        w_full = rt.GpuMatvecTensor.from_bytes_matvec(raw, Q4_K, HIDDEN, FFN, device=dev)
+        y_full = torch.empty((P, FFN), dtype=torch.float32, device=dev)
+        gemm.matmul_into(y_full, w_full, x, P)
+        torch.cuda.synchronize()
+        same = bool(torch.equal(got, y_full))
+        del w_full, y_full
+    dist.barrier()
 
     reps = 10
-    us = timed(step, reps, 3) / reps * 1e3
-    us_gemm = timed(gemm_only, reps, 3) / reps * 1e3
+    us = timed(lambda i: gg.matmul(w, x, P, b0), reps, 4) / reps * 1e3
+    us_gemm = timed(lambda i: gemm.matmul_into(y_local, w, x, P), reps, 3) / reps * 1e3
     ops = 2.0 * P * HIDDEN * FFN
-    return {"workload": f"config 4 row-sharded: 512 tokens x Q4_K 5120->17408, {n_rows} rows on rank 0 of {world}",
-            "us_step": us, "us_gemm_only": us_gemm, "tops": ops / (us * 1e-6) / 1e12,
-            "gather": f"NCCL all_gather_into_tensor of {P * widest * 4} bytes per rank (eager)"}
+    out = {"workload": f"config 4 row-sharded: 512 tokens x Q4_K 5120->17408, {n_rows} rows on rank 0 of {world}",
+           "us_step": us, "us_gemm_only": us_gemm, "tops": ops / (us * 1e-6) / 1e12,
+           "gathered_equals_unsharded_bit_for_bit": same,
+           "gather": f"tile stores into all {world} outputs from the GEMM's drain ({P * n_rows * 4 * (world - 1)} bytes outbound per rank) + rc_peer_barrier"}
+    gg.close()
+    return out
 
 
 def mmq_prefill(rt, synth, torch, dev, timed):
-    """Config 4: dense prefill GEMM, 512 tokens x Q4_K 5120->17408, through PrefillGemm (f32
-    activations in: f16 image + tcgen05 kind::f16 GEMM) and through the int8 entry point given
-    BlockQ8 records (exact integer dots).  TOPS = 2*P*K*N / t."""
+    """Config 4: dense prefill GEMM, 512 tokens x Q4_K 5120->17408, through PrefillGemm (rc_matmul: exact
+    integer block dots on tcgen05, integer-valued f16 operands, one accumulator tile per sub-block).
+    TOPS = 2*P*K*N / t.  Beside it: the BlockQ8-input entry rc_mmq_gemm (kind::i8 kernel), the opt-in
+    f16-dequantized approximation, and a scale-free int8 GEMM of the same shape by the vendor library as the
+    attainable int8 rate of this box."""
     P = 512
     raw = synth.synth_blocks(Q4_K, HIDDEN, FFN, seed=77)
     w = rt.GpuMatvecTensor.from_bytes_matvec(raw, Q4_K, HIDDEN, FFN, device=dev)
@@ -399,21 +468,35 @@ def mmq_prefill(rt, synth, torch, dev, timed):
     rt.launch_quantize_q8(x, xq, HIDDEN, P)
     ops = 2.0 * P * HIDDEN * FFN
     reps = 10
-    ms_k = timed(lambda i: rt.launch_mmq_gemm(w, xq, y, P), reps, 3) / reps
     ms_q = timed(lambda i: gemm.matmul_into(y, w, x, P), reps, 3) / reps
+    y_exact = y.clone()
+    ms_k = timed(lambda i: rt.launch_mmq_gemm(w, xq, y, P), reps, 3) / reps
+    ms_f = timed(lambda i: gemm.matmul_f16_into(y, w, x, P), reps, 3) / reps
+    rel_f16 = float((y - y_exact).norm() / y_exact.norm())
+    attainable = None
+    try:
+        a8 = torch.randint(-127, 128, (P, HIDDEN), dtype=torch.int8, device=dev)
+        b8 = torch.randint(-8, 8, (HIDDEN, FFN), dtype=torch.int8, device=dev)
+        ms_i = timed(lambda i: torch._int_mm(a8, b8), reps, 3) / reps
+        attainable = {"tops": ops / (ms_i * 1e-3) / 1e12, "us": ms_i * 1e3,
+                      "how": "torch._int_mm (vendor int8 GEMM, int32 accumulation over the whole K, no block scales) on the same shape"}
+        del a8, b8
+    except Exception as e:  # a measurement aid only
+        attainable = {"error": f"{type(e).__name__}: {e}"}
     tops_q = ops / (ms_q * 1e-3) / 1e12
     peak, peak_kind = measured_tensor_peak()
     return {"workload": "config 4: 512 tokens x Q4_K 5120->17408 (91.3 GOP)",
-            "kernel": "activations_to_f16_kernel + mmqd_kernel<Q4_K,512> (tcgen05 kind::f16, f32 accumulator in tensor "
-                      "memory over the whole K; TMA-fed raw weights, bulk-copied activation image)",
+            "kernel": "activations_to_q16_kernel + mmqx_kernel<Q4_K> (tcgen05 kind::f16 on integer-valued operands: the f32 "
+                      "accumulator tile of every 32-wide sub-block is the exact integer block dot; drained and scaled per sub-block)",
             "us_matmul_f32_in": ms_q * 1e3, "tops_matmul_f32_in": tops_q,
             "us_mmq_blockq8_in": ms_k * 1e3, "tops_mmq_blockq8_in": ops / (ms_k * 1e-3) / 1e12,
-            "note": "matmul_f32_in = PrefillGemm (two launches, both timed); mmq_blockq8_in = mmq_kernel<Q4_K,128,16,2> "
-                    "(tcgen05 kind::i8, exact integer dots, one accumulator drain per 32-wide sub-block)",
+            "f16_dequantized_opt_in": {"us": ms_f * 1e3, "tops": ops / (ms_f * 1e-3) / 1e12, "rel_l2_vs_exact_route": rel_f16,
+                                       "note": "rc_matmul_f16: an approximation without integer block dots; not the reported figure"},
             "roofline": {"bound": "tensor", "achieved": tops_q, "peak": peak, "unit": "TFLOP/s",
                          "frac": tops_q / peak, "peak_kind": peak_kind,
                          "frac_of_nominal_int8": tops_q / INT8_DENSE_PEAK_TOPS,
-                         "timed": "PrefillGemm call, activation-image launch included"},
+                         "attainable_int8": attainable,
+                         "timed": "PrefillGemm call (rc_matmul), activation-image launch included"},
             "tok_per_s_per_layer_gate_only": P / (ms_q * 1e-3)}
 
 
@@ -435,7 +518,7 @@ def run_gpu_arm(args):
         dist.init_process_group("nccl", device_id=dev)
     rt.init(local)
 
-    n_copies = 3
+    n_copies = 4  # even: the two gathered buffers of a peer all-gather alternate, a replayed graph must hold an even number of gathers
     # Row shards: rank r owns rows [r*out/world, (r+1)*out/world) of every matrix; shard sizes
     # are multiples of 32 so quantize-then-gather equals gather-then-quantize.
     shards = []
@@ -443,7 +526,6 @@ def run_gpu_arm(args):
         assert out_dim % (32 * world) == 0
         shards.append((name, t, in_dim, out_dim // world))
     copies = []
-    layer_bytes_local = 0
     for c in range(n_copies):
         ws = []
         for i, (name, t, in_dim, out_local) in enumerate(shards):
@@ -460,71 +542,63 @@ def run_gpu_arm(args):
     x_dev.copy_(in_host)
     xq = torch.empty((HIDDEN // 32) * 40, dtype=torch.uint8, device=dev)
     hq = torch.empty((FFN // 32) * 40, dtype=torch.uint8, device=dev)
-    # gate | up outputs side by side (this rank's rows)
     y_gu = torch.empty(2 * (FFN // world), device=dev)
     y_gate, y_up = y_gu[:FFN // world], y_gu[FFN // world:]
     y_down = torch.empty(HIDDEN // world, device=dev)
     g_gate = torch.empty(FFN, device=dev) if world > 1 else y_gate
     g_up = torch.empty(FFN, device=dev) if world > 1 else y_up
-    g_down = torch.empty(HIDDEN, device=dev) if world > 1 else y_down
     yd_host = torch.empty(HIDDEN, dtype=torch.float32).pin_memory()
-    launches_per_step = 5
+    launches_per_step = 5 + (2 if world > 1 else 0)
 
-    # The intermediate h = silu(gate) * up is made and quantized in one launch (rc_swiglu_q8), so the
-    # step is the decode FFN as the engine runs it: quantize x, gate, up, SwiGLU+quantize, down.
-    # N > 1: gate and up stay sharded (the activation between them and down is elementwise); each
-    # rank produces its 1/N of the quantized intermediate and the BlockQ8 shards are all-gathered (21.7 KB
-    # instead of 2 x 68 KB of f32); down's output rows are all-gathered for the next layer.  The
-    # gathers are rc_allgather_push (stores into peer memory over NVLink + a counter handshake),
-    # so the whole sharded step replays from one CUDA graph; --nccl-gather uses NCCL instead.
+    # The step is the decode FFN as the engine runs it (step_swiglu_ffn): quantize x, gate, up, SwiGLU+quantize,
+    # down.  N > 1: gate and up stay sharded (the activation between them and down is elementwise); each rank
+    # produces its 1/N of the quantized intermediate and the BlockQ8 shards are all-gathered (21.7 KB instead
+    # of 2 x 68 KB of f32); down's output rows are all-gathered for the next layer.  The gathers are
+    # rc_allgather_push (stores into peer memory over NVLink + a counter handshake, two alternating buffers),
+    # so the whole sharded step replays from CUDA graphs.
     h_local = FFN // world
     hq_local = torch.empty((h_local // 32) * 40, dtype=torch.uint8, device=dev) if world > 1 else hq
-    push = world > 1 and not args.nccl_gather
-    if push:
+    if world > 1:
         ga_h = rt.PeerAllGather(hq_local.numel())
         ga_y = rt.PeerAllGather(y_down.numel() * 4)
-        hq_in, y_full = ga_h.buffer_ptr, ga_y
-    else:
-        hq_in = hq
 
     def step(c: int):
         ws = copies[c % n_copies]
+        if world == 1:
+            rt.launch_ffn_decode(ws[0], ws[1], ws[2], x_dev, xq, y_gate, y_up, hq, y_down)
+            return
         rt.launch_quantize_q8(x_dev, xq, HIDDEN, 1)
         rt.launch_matvec_xq8(ws[0], xq, y_gate)
         rt.launch_matvec_xq8(ws[1], xq, y_up)
         rt.launch_swiglu_q8(y_gate, y_up, None, hq_local, h_local)
-        if world > 1:
-            if push:
-                ga_h.gather(hq_local)
-            else:
-                dist.all_gather_into_tensor(hq, hq_local)
-        rt.launch_matvec_xq8(ws[2], hq_in, y_down)
-        if world > 1:
-            if push:
-                ga_y.gather(y_down)
-            else:
-                dist.all_gather_into_tensor(g_down, y_down)
+        ga_h.gather(hq_local)
+        rt.launch_matvec_xq8(ws[2], ga_h.buffer_ptr, y_down)
+        ga_y.gather(y_down)
 
-    if push:
-        # one checked step: the gathered BlockQ8 must equal SwiGLU+quantize of the whole gathered vectors
-        step(0)
-        got = torch.empty_like(hq)
-        ga_h.copy_out(got)
-        dist.all_gather_into_tensor(g_gate, y_gate)
-        dist.all_gather_into_tensor(g_up, y_up)
-        rt.launch_swiglu_q8(g_gate, g_up, None, hq, FFN)
-        torch.cuda.synchronize()
-        assert torch.equal(got, hq), "peer gather of the quantized intermediate differs from the local quantization"
+    if world > 1:
+        # one checked step (two, so that both of the alternating buffers are used): the gathered BlockQ8 must
+        # equal SwiGLU+quantize of the whole gathered vectors
+        for c in range(2):
+            step(c)
+            got = torch.empty_like(hq)
+            ga_h.copy_out(got)
+            dist.all_gather_into_tensor(g_gate, y_gate)
+            dist.all_gather_into_tensor(g_up, y_up)
+            rt.launch_swiglu_q8(g_gate, g_up, None, hq, FFN)
+            torch.cuda.synchronize()
+            assert torch.equal(got, hq), "peer gather of the quantized intermediate differs from the local quantization"
 
-    # End-to-end step: the layer's input comes from pinned host memory and its output goes back there,
-    # both inside the step.
+    # End-to-end step through the host-side API with HOST buffers.  One GPU: rt.launch_ffn_decode given the pinned
+    # host input and output themselves (the first kernel reads x, the last writes y across PCIe; no copy launches).
+    # N > 1: x is uploaded by a copy node and the gathered output downloaded by another.
     def step_e2e(c: int):
-        x_dev.copy_(in_host, non_blocking=True)
-        step(c)
-        if push:
-            ga_y.copy_out(yd_host)
+        ws = copies[c % n_copies]
+        if world == 1:
+            rt.launch_ffn_decode(ws[0], ws[1], ws[2], in_host, xq, y_gate, y_up, hq, yd_host)
         else:
-            yd_host.copy_(g_down, non_blocking=True)
+            x_dev.copy_(in_host, non_blocking=True)
+            step(c)
+            ga_y.copy_out(yd_host)
 
     def barrier():
         if world > 1:
@@ -547,84 +621,99 @@ def run_gpu_arm(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    # The decode loop is launch-bound from Python (8 us kernels), so the steps are replayed
-    # from a CUDA graph, as the reference's engine replays its forward (graph of n_copies steps).
-    # (Replaying NCCL collectives captured together with these launches hung on 2 GPUs, so with
-    # --nccl-gather the steps are launched eagerly and are bound by host launch latency.)
-    use_graph = (world == 1 or push) and not args.no_graph
-    if use_graph:
+    def timed_rounds(round_fn, rounds: int, warm_rounds: int):
+        """Per-round device times in ms (max over ranks per round): one event between consecutive rounds."""
+        for i in range(warm_rounds):
+            round_fn()
+        barrier()
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(rounds + 1)]
+        evs[0].record()
+        for i in range(rounds):
+            round_fn()
+            evs[i + 1].record()
+        barrier()
+        ms = torch.tensor([evs[i].elapsed_time(evs[i + 1]) for i in range(rounds)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.cpu().numpy()
+
+    # The decode loop is launch-bound from Python (8 us kernels), so the steps are replayed from CUDA graphs, as
+    # the reference's engine replays its forward.  A round is EXACTLY --steps steps: graphs of L steps each, L the
+    # largest of 4, 2, 1 that divides --steps (N > 1 needs an even L or a pair of graphs per parity; with L = 1 the
+    # four graphs alternate parity by construction), replayed in cyclic order.
+    K = max(1, args.steps)
+    L = 4 if K % 4 == 0 else 2 if K % 2 == 0 else 1
+
+    def build_graphs(step_fn):
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            for i in range(3):
-                step(i)
+            for i in range(n_copies):  # warm-up outside capture (an even number of steps: parity is kept)
+                step_fn(i)
         torch.cuda.current_stream().wait_stream(side)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            for c in range(n_copies):
-                step(c)
+        torch.cuda.synchronize()
+        graphs = []
+        for g0 in range(0, n_copies, L):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for c in range(g0, g0 + L):
+                    step_fn(c)
+            graphs.append(g)
+        return graphs
 
-        def run_steps(i):
-            graph.replay()
-        steps_per_call = n_copies
+    def make_round(graphs):
+        cursor = [0]
+
+        def one_round():
+            for _ in range(K // L):
+                graphs[cursor[0] % len(graphs)].replay()
+                cursor[0] += 1
+        return one_round
+
+    use_graph = not args.no_graph
+    if use_graph:
+        round_fn = make_round(build_graphs(step))
     else:
-        run_steps = step
-        steps_per_call = 1
+        cur = [0]
+
+        def round_fn():
+            for _ in range(K):
+                step(cur[0])
+                cur[0] += 1
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    calls = max(1, (args.steps + steps_per_call - 1) // steps_per_call)
-    steps_timed = calls * steps_per_call
-    ms = timed(run_steps, calls, max(3, (args.warmup + steps_per_call - 1) // steps_per_call))
-    ms_per_step = ms / steps_timed
+    # rounds: until the timed region lasts >= 50 ms (estimated from a probe round), at least 20
+    probe = timed_rounds(round_fn, 3, max(1, (max(3, args.warmup) + K - 1) // K))
+    est = float(np.median(probe))
+    rounds = int(min(5000, max(20, np.ceil(50.0 / max(est, 1e-3)))))
+    ms_rounds = timed_rounds(round_fn, rounds, 1)
+    ms_per_step = float(np.median(ms_rounds)) / K
     value = layer_bytes_total / (ms_per_step * 1e-3) / 1e9
 
-    # end to end: host buffers in, host buffers out, copies inside the timed region.  Like the
-    # device-resident steps, a user replays this from a CUDA graph (pinned-memory copies are
-    # ordinary graph nodes): n_copies steps per graph, every one with its own uploads and downloads.
     if use_graph:
-        for i in range(2):
-            step_e2e(i)
-        torch.cuda.synchronize()
-        graph_e2e = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph_e2e):
-            for c in range(n_copies):
-                step_e2e(c)
-        e2e_calls = max(1, (args.steps + n_copies - 1) // n_copies)
-        ms_e2e = timed(lambda i: graph_e2e.replay(), e2e_calls, 3)
-        e2e_steps = e2e_calls * n_copies
+        round_e2e = make_round(build_graphs(step_e2e))
     else:
-        ms_e2e = timed(step_e2e, args.steps, max(3, args.warmup))
-        e2e_steps = args.steps
-    e2e_value = layer_bytes_total / (ms_e2e / e2e_steps * 1e-3) / 1e9
+        cur_e = [0]
 
-    # The same step with no copy nodes: pinned host memory is addressable from the device, so the first
-    # kernel reads x and the last one writes y straight across PCIe (single GPU; reported beside e2e).
-    zero_copy = None
-    if world == 1 and use_graph:
-        def step_zc(c: int):
-            ws = copies[c % n_copies]
-            rt.launch_quantize_q8(in_host, xq, HIDDEN, 1)
-            rt.launch_matvec_xq8(ws[0], xq, y_gate)
-            rt.launch_matvec_xq8(ws[1], xq, y_up)
-            rt.launch_swiglu_q8(y_gate, y_up, None, hq, FFN)
-            rt.launch_matvec_xq8(ws[2], hq, yd_host)
-        yd_host.zero_()
+        def round_e2e():
+            for _ in range(K):
+                step_e2e(cur_e[0])
+                cur_e[0] += 1
+    ms_e2e_rounds = timed_rounds(round_e2e, max(20, rounds // 2), 2)
+    ms_e2e = float(np.median(ms_e2e_rounds)) / K
+    e2e_value = layer_bytes_total / (ms_e2e * 1e-3) / 1e9
+    e2e_check = None
+    if world == 1:
+        # the end-to-end call writes the same numbers the device-resident step does
         step(0)
         torch.cuda.synchronize()
         want = y_down.cpu()
-        step_zc(0)
+        yd_host.zero_()
+        step_e2e(0)
         torch.cuda.synchronize()
-        if torch.equal(yd_host.reshape(-1), want.reshape(-1)):
-            graph_zc = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph_zc):
-                for c in range(n_copies):
-                    step_zc(c)
-            calls = max(1, (args.steps + n_copies - 1) // n_copies)
-            ms_zc = timed(lambda i: graph_zc.replay(), calls, 3) / (calls * n_copies)
-            zero_copy = {"value": layer_bytes_total / (ms_zc * 1e-3) / 1e9, "ms_per_step": ms_zc,
-                         "note": "x read and y written in pinned host memory by the kernels themselves"}
+        e2e_check = bool(torch.equal(yd_host.reshape(-1), want.reshape(-1)))
 
     # dominant kernel alone: the Q4_K matvec over rotating copies, CUDA events on its stream
     q4k_bytes = copies[0][0].data.numel()
@@ -640,69 +729,76 @@ def run_gpu_arm(args):
         with torch.cuda.graph(gq):
             q4k_only(0)
 
-        def q4k_call(i):
+        def q4k_call():
             gq.replay()
     else:
-        q4k_call = q4k_only
-    reps = max(20, args.steps // 2)
-    ms_q = timed(q4k_call, reps, 5)
-    q4k_us = ms_q * 1e3 / (reps * len(mats))
+        def q4k_call():
+            q4k_only(0)
+    q_rounds = timed_rounds(q4k_call, 200, 5)
+    q4k_us = float(np.median(q_rounds)) * 1e3 / len(mats)
     clocks = sampler.stop() if rank == 0 else None
 
-    clocks = clocks  # sampled over the layer, e2e and Q4_K regions above
     # Q6_K down alone, for the per-format report
     q6_bytes = copies[0][2].data.numel()
     downs = [copies[c][2] for c in range(n_copies)]
+    hq_src = hq if world == 1 else ga_h.buffer_ptr
 
-    def q6_only(i):
+    def q6_only():
         for w in downs:
-            rt.launch_matvec_xq8(w, hq, y_down)
-    ms_6 = timed(q6_only, reps, 5)
-    q6_us = ms_6 * 1e3 / (reps * len(downs))
+            rt.launch_matvec_xq8(w, hq_src, y_down)
+    q6_rounds = timed_rounds(q6_only, 100, 5)
+    q6_us = float(np.median(q6_rounds)) * 1e3 / len(downs)
 
-    mmq = moe = None
+    mmq = moe = small = None
     if world == 1 and not args.skip_mmq:
+        small = small_matvecs(rt, synth, torch, dev, timed)
         mmq = mmq_prefill(rt, synth, torch, dev, timed)
         moe = moe_layer(rt, synth, torch, dev, timed)
 
-    moe_ep = None
-    if world > 1 and not args.skip_mmq:
-        try:
-            moe_ep = moe_expert_parallel(rt, synth, torch, dist, dev, timed, rank, world)
-        except Exception as e:  # the headline line must not depend on this extra
-            moe_ep = {"error": f"{type(e).__name__}: {e}"}
-
-    mmq_rs = None
+    moe_ep = mmq_rs = None
     if world > 1 and not args.skip_mmq:
         try:
             mmq_rs = mmq_prefill_row_sharded(rt, synth, torch, dist, dev, timed, rank, world)
-        except Exception as e:
+        except Exception as e:  # the headline line must not depend on this extra
             mmq_rs = {"error": f"{type(e).__name__}: {e}"}
+        try:
+            moe_ep = moe_expert_parallel(rt, synth, torch, dist, dev, timed, rank, world)
+        except Exception as e:
+            moe_ep = {"error": f"{type(e).__name__}: {e}"}
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
         achieved = q4k_bytes / (q4k_us * 1e-6) / 1e9
+        traffic, traffic_src = q4k_dram_traffic()
         line = {
             "metric": "q4k_decode_matvec_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
-            "steps": steps_timed, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "steps": K, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "rounds": rounds, "timed_region_ms": float(ms_rounds.sum()),
+            "ms_per_step_min": float(ms_rounds.min()) / K, "ms_per_step_max": float(ms_rounds.max()) / K,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 dp4a, f32 accumulate",
             "data": "synthetic", "config": workload_config(world),
             "e2e": {"value": e2e_value, "unit": "GB/s",
                     "h2d_bytes_per_step": HIDDEN * 4, "d2h_bytes_per_step": HIDDEN * 4,
-                    "ms_per_step": ms_e2e / e2e_steps, "graph_replay": use_graph, "zero_copy": zero_copy},
-            "gpu_launches": (launches_per_step + (2 if push else 0)) * steps_timed,
-            "gather": ("peer-push" if push else "nccl") if world > 1 else None,
+                    "ms_per_step": ms_e2e, "ms_per_step_min": float(ms_e2e_rounds.min()) / K,
+                    "ms_per_step_max": float(ms_e2e_rounds.max()) / K, "graph_replay": use_graph,
+                    "how": ("runtime.launch_ffn_decode with the pinned host input and output as its x and y: the first kernel reads "
+                            "x and the last writes y across PCIe" if world == 1 else
+                            "copy node in, sharded step, copy node out of the gathered output"),
+                    "equals_device_resident_step": e2e_check},
+            "gpu_launches": launches_per_step * K * rounds,
+            "gather": "peer-push, alternating buffers" if world > 1 else None,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "matvec_rows_kernel<Q4_K,1,5> 5120->%d" % (FFN // world),
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "us_per_launch": q4k_us, "bytes_per_launch": q4k_bytes,
-                         "traffic": Q4K_DRAM_TRAFFIC_BYTES if world == 1 else None,
-                         "traffic_source": "profiles/matvec_q4k_5120x17408.md (ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch)"},
+                         "traffic": traffic if world == 1 else None, "traffic_source": traffic_src},
             "per_kernel": {"q4k_gate_up_gbs": achieved, "q6k_down_gbs": q6_bytes / (q6_us * 1e-6) / 1e9,
                            "q6k_us": q6_us},
             "tok_per_s_per_layer": 1e3 / ms_per_step,
-            "graph_replay": use_graph,
+            "graph_replay": use_graph, "graph_steps": L if use_graph else 0,
         }
+        if small is not None:
+            line.update(small)
         if mmq is not None:
             line["mmq_prefill"] = mmq
         if moe is not None:
@@ -717,6 +813,8 @@ def run_gpu_arm(args):
                                     "sample": sample}
         print(json.dumps(line), flush=True)
     if world > 1:
+        ga_h.close()
+        ga_y.close()
         dist.destroy_process_group()
 
 
@@ -728,8 +826,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--nccl-gather", action="store_true", help="N > 1: gather with NCCL instead of rc_allgather_push")
-    ap.add_argument("--skip-mmq", action="store_true", help="leave the config-4 prefill GEMM section out")
+    ap.add_argument("--skip-mmq", action="store_true", help="leave the prefill GEMM, MoE and small-matvec sections out")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -22,7 +22,7 @@ __all__ = [
     "launch_quantize_q8", "launch_matvec", "launch_matvec_xq8", "launch_matvec_batched",
     "matvec_block_dots", "launch_mmq_gemm", "launch_moe_sort", "launch_moe_gather_xq",
     "launch_moe_grouped_gemm", "launch_moe_scatter_rows", "repacked_len", "init", "PeerAllGather",
-    "PeerBuffers", "GatheredPrefillGemm", "MoeGroupedGemm", "launch_rmsnorm_q8", "launch_add_rmsnorm_q8", "launch_swiglu_q8",
+    "PeerBuffers", "GatheredPrefillGemm", "launch_ffn_decode", "MoeGroupedGemm", "launch_rmsnorm_q8", "launch_add_rmsnorm_q8", "launch_swiglu_q8",
     "launch_moe_expert_matvec", "launch_moe_gate_up_swiglu", "launch_moe_topk", "launch_moe_act_q8", "launch_moe_combine", "ACT_GEGLU", "ACT_SWIGLU",
 ]
 
@@ -406,6 +406,19 @@ def launch_moe_combine(experts: torch.Tensor, ids: torch.Tensor, weights: torch.
     """launch_moe_combine (src/runtime/gemma4.rs:1804-1823)."""
     check(_lib.load().rc_moe_combine(_stream(), _ptr(experts), _ptr(ids), _ptr(weights), _ptr(expert_scale),
                                      _ptr(out), hidden, n_used, n_tok), "rc_moe_combine")
+
+
+def launch_ffn_decode(gate: GpuMatvecTensor, up: GpuMatvecTensor, down: GpuMatvecTensor, x, xq8: torch.Tensor,
+                      y_gate: torch.Tensor, y_up: torch.Tensor, hq8: torch.Tensor, y) -> None:
+    """step_swiglu_ffn (src/runtime/qwen35.rs:2694-2707): quantize x -> gate and up matvecs on the shared
+    BlockQ8 -> SwiGLU + quantize in one launch -> down matvec; five launches on the current stream.  x and y
+    may be PINNED HOST tensors: pinned memory is addressable from the device, so the first kernel reads the
+    20 KB input and the last one writes the output across PCIe themselves and the step has no copy launches."""
+    launch_quantize_q8(x, xq8, gate.in_dim, 1)
+    launch_matvec_xq8(gate, xq8, y_gate)
+    launch_matvec_xq8(up, xq8, y_up)
+    launch_swiglu_q8(y_gate, y_up, None, hq8, gate.out_dim)
+    launch_matvec_xq8(down, hq8, y)
 
 
 class PeerBuffers:
