@@ -861,20 +861,36 @@ int launch_one(cudaStream_t s, const void *w, const void *xq, float *y, int32_t 
     }
     if (DUMP) ks = 1;
     if constexpr (!DUMP && NB >= 2) {
-        // several activation rows on a matrix with enough weight rows to give every warp slot R of them
-        constexpr int R = MultiRows<NB>::v;
-        if (n_sub % 32u == 0 && !g_tune.no_rows_kernel && (uint64_t)out_dim >= (uint64_t)sm_count() * kWarpsPerCta * R) {
+        // Several activation rows: a warp owns R consecutive weight rows (each activation block is read from
+        // shared memory once for all R).  R as large as still leaves two CTAs of work per SM: on a 5120-row
+        // matrix four rows per warp would leave most warp slots empty (measured: batch 4, 5120 x 5120 Q5_K,
+        // 24 us with R = 4).
+        constexpr int RMAX = MultiRows<NB>::v;
+        if (n_sub % 32u == 0 && !g_tune.no_rows_kernel && (uint64_t)out_dim >= (uint64_t)sm_count() * kWarpsPerCta) {
             const uint32_t capacity = (uint32_t)sm_count() * min(resident, (uint32_t)kMultiMinBlocks);
-            const uint32_t n_cta_rows = (out_dim + kWarpsPerCta * R - 1u) / (kWarpsPerCta * R);
-            const uint32_t grid = min(n_cta_rows, capacity);
+            int r_pick = RMAX;
+            while (r_pick > 1 && (uint64_t)out_dim < 2ull * (uint64_t)sm_count() * kWarpsPerCta * r_pick) r_pick >>= 1;
+            if (kCodebook<FMT> && r_pick < RMAX) r_pick = 1; // the codebook lookups hold more registers per row (measured: 11.4 us against 18.4)
+            if (g_tune.ks > 0 && g_tune.ks <= RMAX) r_pick = g_tune.ks; // measurement override
             const size_t xsm = (((size_t)n_rows * n_sub * FmtTraits<FMT>::x_bytes) + 15u) & ~(size_t)15u;
-            if (g_tune.no_pdl) {
-                matvec_multi_kernel<FMT, NB, R><<<grid, kWarpsPerCta * 32, xsm, s>>>((const uint8_t *)w, (const uint8_t *)xq, y, in_dim,
-                                                                                    out_dim, n_rows);
-                return (int)cudaGetLastError();
+            auto go = [&](auto rtag) -> int {
+                constexpr int R = decltype(rtag)::value;
+                const uint32_t n_cta_rows = (out_dim + kWarpsPerCta * R - 1u) / (kWarpsPerCta * R);
+                const uint32_t grid = min(n_cta_rows, capacity * (n_cta_rows >= 3u * capacity ? 2u : 1u));
+                if (g_tune.no_pdl) {
+                    matvec_multi_kernel<FMT, NB, R><<<grid, kWarpsPerCta * 32, xsm, s>>>((const uint8_t *)w, (const uint8_t *)xq, y, in_dim,
+                                                                                        out_dim, n_rows);
+                    return (int)cudaGetLastError();
+                }
+                return (int)launch_pdl(matvec_multi_kernel<FMT, NB, R>, dim3(grid), dim3(kWarpsPerCta * 32), xsm, s, (const uint8_t *)w,
+                                       (const uint8_t *)xq, y, in_dim, out_dim, n_rows);
+            };
+            if constexpr (RMAX >= 4) {
+                if (r_pick >= 4) return go(std::integral_constant<int, 4>{});
             }
-            return (int)launch_pdl(matvec_multi_kernel<FMT, NB, R>, dim3(grid), dim3(kWarpsPerCta * 32), xsm, s, (const uint8_t *)w,
-                                   (const uint8_t *)xq, y, in_dim, out_dim, n_rows);
+            if (r_pick >= 2) return go(std::integral_constant<int, 2>{});
+            if constexpr (NB <= 4) return go(std::integral_constant<int, 1>{});
+            else return go(std::integral_constant<int, 2>{});
         }
     }
     if constexpr (!DUMP && NB <= 4) {
@@ -957,9 +973,12 @@ constexpr int kGroupedBN = 16;
 template <int FMT, int NB> int set_attr_rows()
 {
     int rc = 0;
-    if constexpr (NB >= 2)
+    if constexpr (NB >= 2) {
         rc |= (int)cudaFuncSetAttribute(matvec_multi_kernel<FMT, NB, MultiRows<NB>::v>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)kMaxStageBytesHost);
+        rc |= (int)cudaFuncSetAttribute(matvec_multi_kernel<FMT, NB, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
+        rc |= (int)cudaFuncSetAttribute(matvec_multi_kernel<FMT, NB, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
+    }
     rc |= (int)cudaFuncSetAttribute(matvec_rows_kernel<FMT, NB, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
     rc |= (int)cudaFuncSetAttribute(matvec_rows_kernel<FMT, NB, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
     rc |= (int)cudaFuncSetAttribute(matvec_rows_kernel<FMT, NB, 5>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
