@@ -548,7 +548,8 @@ def run_gpu_arm(args):
     g_gate = torch.empty(FFN, device=dev) if world > 1 else y_gate
     g_up = torch.empty(FFN, device=dev) if world > 1 else y_up
     yd_host = torch.empty(HIDDEN, dtype=torch.float32).pin_memory()
-    launches_per_step = 5 + (2 if world > 1 else 0)
+    use_fused = world > 1  # one GPU: the launch chain is the faster step; N > 1: one cooperative launch per GPU
+    launches_per_step = 1 if use_fused else 5
 
     # The step is the decode FFN as the engine runs it (step_swiglu_ffn): quantize x, gate, up, SwiGLU+quantize,
     # down.  N > 1: gate and up stay sharded (the activation between them and down is elementwise); each rank
@@ -562,7 +563,17 @@ def run_gpu_arm(args):
         ga_h = rt.PeerAllGather(hq_local.numel())
         ga_y = rt.PeerAllGather(y_down.numel() * 4)
 
-    def step(c: int):
+    # The step as ONE cooperative launch per GPU (rc_ffn_decode): quantize, gate and up rows, SwiGLU + quantize with the
+    # records stored into every rank's intermediate buffer, the down rows stored into every rank's output; bounded
+    # counter waits instead of launches between the phases.  One object per weight copy.
+    fused = [rt.FusedFfnDecode(ws[0], ws[1], ws[2], FFN, HIDDEN, rank * h_local, rank * (HIDDEN // world), device=dev)
+             for ws in copies]
+
+    def step_fused(c: int):
+        fused[c % n_copies].run(x_dev)
+
+    def step_chain(c: int):
+        """The same step as separate launches (five on one GPU, seven with the two peer gathers)."""
         ws = copies[c % n_copies]
         if world == 1:
             rt.launch_ffn_decode(ws[0], ws[1], ws[2], x_dev, xq, y_gate, y_up, hq, y_down)
@@ -575,30 +586,41 @@ def run_gpu_arm(args):
         rt.launch_matvec_xq8(ws[2], ga_h.buffer_ptr, y_down)
         ga_y.gather(y_down)
 
-    if world > 1:
-        # one checked step (two, so that both of the alternating buffers are used): the gathered BlockQ8 must
-        # equal SwiGLU+quantize of the whole gathered vectors
-        for c in range(2):
-            step(c)
+    # checked steps: the fused launch against the launch chain (and, N > 1, the gathered records against
+    # SwiGLU + quantize of the whole gathered vectors), on two copies so that both alternating buffers are used
+    y_fused, y_chain = torch.empty(HIDDEN, device=dev), torch.empty(HIDDEN, device=dev)
+    fused_rel = 0.0
+    for c in range(2):
+        step_chain(c)
+        if world > 1:
             got = torch.empty_like(hq)
             ga_h.copy_out(got)
+            ga_y.copy_out(y_chain)
             dist.all_gather_into_tensor(g_gate, y_gate)
             dist.all_gather_into_tensor(g_up, y_up)
             rt.launch_swiglu_q8(g_gate, g_up, None, hq, FFN)
             torch.cuda.synchronize()
             assert torch.equal(got, hq), "peer gather of the quantized intermediate differs from the local quantization"
+        else:
+            y_chain.copy_(y_down)
+        step_fused(c)
+        fused[c].read_y(y_fused)
+        torch.cuda.synchronize()
+        fused_rel = max(fused_rel, float((y_fused - y_chain).norm() / y_chain.norm()))
+    assert fused_rel < 1e-3, f"fused FFN launch differs from the launch chain: {fused_rel}"
+    step, step_other = (step_fused, step_chain) if use_fused else (step_chain, step_fused)
 
-    # End-to-end step through the host-side API with HOST buffers.  One GPU: rt.launch_ffn_decode given the pinned
-    # host input and output themselves (the first kernel reads x, the last writes y across PCIe; no copy launches).
+    # End-to-end step through the host-side API with HOST buffers.  One GPU: runtime.launch_ffn_decode given the pinned
+    # host input and output themselves (the quantizer reads x, the down matvec writes y across PCIe; no copy launches).
     # N > 1: x is uploaded by a copy node and the gathered output downloaded by another.
     def step_e2e(c: int):
-        ws = copies[c % n_copies]
         if world == 1:
+            ws = copies[c % n_copies]
             rt.launch_ffn_decode(ws[0], ws[1], ws[2], in_host, xq, y_gate, y_up, hq, yd_host)
         else:
             x_dev.copy_(in_host, non_blocking=True)
-            step(c)
-            ga_y.copy_out(yd_host)
+            fused[c % n_copies].run(x_dev)
+            fused[c % n_copies].read_y(yd_host)
 
     def barrier():
         if world > 1:
@@ -691,6 +713,18 @@ def run_gpu_arm(args):
     ms_rounds = timed_rounds(round_fn, rounds, 1)
     ms_per_step = float(np.median(ms_rounds)) / K
     value = layer_bytes_total / (ms_per_step * 1e-3) / 1e9
+    # the same step the other way (one GPU: the single cooperative launch; N > 1: separate launches), for comparison
+    if use_graph:
+        other_round = make_round(build_graphs(step_other))
+    else:
+        cur_c = [0]
+
+        def other_round():
+            for _ in range(K):
+                step_other(cur_c[0])
+                cur_c[0] += 1
+    ms_other = float(np.median(timed_rounds(other_round, max(20, rounds // 4), 2))) / K
+    ms_chain, ms_fused = (ms_other, ms_per_step) if use_fused else (ms_per_step, ms_other)
 
     if use_graph:
         round_e2e = make_round(build_graphs(step_e2e))
@@ -781,17 +815,23 @@ def run_gpu_arm(args):
                     "h2d_bytes_per_step": HIDDEN * 4, "d2h_bytes_per_step": HIDDEN * 4,
                     "ms_per_step": ms_e2e, "ms_per_step_min": float(ms_e2e_rounds.min()) / K,
                     "ms_per_step_max": float(ms_e2e_rounds.max()) / K, "graph_replay": use_graph,
-                    "how": ("runtime.launch_ffn_decode with the pinned host input and output as its x and y: the first kernel reads "
-                            "x and the last writes y across PCIe" if world == 1 else
-                            "copy node in, sharded step, copy node out of the gathered output"),
+                    "how": ("runtime.launch_ffn_decode with the pinned host input and output as its x and y: the quantizer reads x "
+                            "and the down matvec writes y across PCIe" if world == 1 else
+                            "copy node in, fused sharded launch, copy node out of the gathered output"),
                     "equals_device_resident_step": e2e_check},
             "gpu_launches": launches_per_step * K * rounds,
-            "gather": "peer-push, alternating buffers" if world > 1 else None,
+            "step": ("one cooperative launch per GPU (rc_ffn_decode)" if use_fused else
+                     "five launches (quantize, gate, up, SwiGLU + quantize, down) with programmatic dependent launch"),
+            "ms_per_step_launch_chain": ms_chain, "ms_per_step_one_launch": ms_fused, "fused_vs_chain_rel_l2": fused_rel,
+            "gather": "peer stores from inside the fused launch, monotone arrival counters" if world > 1 else None,
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": "matvec_rows_kernel<Q4_K,1,5> 5120->%d" % (FFN // world),
+            "roofline": {"bound": "hbm", "kernel": "matvec_rows_kernel<Q4_K,1,5> 5120->%d (the Q4_K decode matvec, timed alone)" % (FFN // world),
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "us_per_launch": q4k_us, "bytes_per_launch": q4k_bytes,
-                         "traffic": traffic if world == 1 else None, "traffic_source": traffic_src},
+                         "traffic": traffic if world == 1 else None, "traffic_source": traffic_src,
+                         "fused_step": {"kernel": "ffn_decode_kernel<Q4_K,Q6_K>", "bytes_per_launch": layer_bytes_local,
+                                        "us_per_launch": ms_fused * 1e3, "achieved": layer_bytes_local / (ms_fused * 1e-3) / 1e9,
+                                        "frac": layer_bytes_local / (ms_fused * 1e-3) / 1e9 / peak}},
             "per_kernel": {"q4k_gate_up_gbs": achieved, "q6k_down_gbs": q6_bytes / (q6_us * 1e-6) / 1e9,
                            "q6k_us": q6_us},
             "tok_per_s_per_layer": 1e3 / ms_per_step,
@@ -812,6 +852,8 @@ def run_gpu_arm(args):
             line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port",
                                     "sample": sample}
         print(json.dumps(line), flush=True)
+    for f in fused:
+        f.close()
     if world > 1:
         ga_h.close()
         ga_y.close()

@@ -179,7 +179,8 @@ void rc_tune_matvec(int ks, int grid_mult, int no_pdl);
 void rc_tune_mmq(int force_dp4a, int kind);
 /* Reads (synchronously) the device-side status word: 0, or the codes of the bounded waits that
  * gave up: bits 0-7 the int8 GEMM, 8-11 the BlockQ8-input f16 GEMM, 12-15 the dense exact GEMM of
- * rc_matmul, 16-23 the peer gather, 24-31 the f16-dequantized GEMM.  A nonzero value means the
+ * rc_matmul, 16-19 the peer gather / barrier, 20-23 the fused decode FFN (1 its grid barrier, 2 the wait for
+ * the peers' intermediate records, 3 the wait for the peers' output rows), 24-31 the f16-dequantized GEMM.  A nonzero value means the
  * affected outputs are invalid; the context stays usable.  The words are sticky: they keep the
  * last code until rc_device_status_clear.  hipDeviceSynchronize + error check in the
  * reference's tests (src/runtime/kernels.rs) is the nearest counterpart. */
@@ -197,6 +198,10 @@ int rc_debug_read_trace(void *out, size_t bytes);
  * uint64, six counters for each of: token producer, MMA issuer, the two expander groups, the first
  * and the last epilogue warp.  No counterpart in the reference. */
 int rc_debug_read_prof(void *out, size_t bytes);
+/* Measurement aid: the phase timestamps (globaltimer ns) CTA 0 of the latest rc_ffn_decode launch recorded:
+ * start, x quantized, gate/up rows done, grid barrier passed, records pushed, records arrived, intermediate
+ * staged, down rows done, end.  16 uint64.  No counterpart in the reference. */
+int rc_debug_read_ffn_trace(void *out, size_t bytes);
 
 /* ---- int8 MMQ GEMM --------------------------------------------------------------------- */
 
@@ -405,6 +410,30 @@ int rc_peer_barrier(void *stream, void *const *peer_flags, void *epoch, uint32_t
  * two-stage pipeline on one device the same way (tests/qwen35_pipeline.rs:8-10). */
 int rc_allgather_push_logical(void *stream, const void *const *srcs, size_t bytes, void *const *dsts,
                               void *const *flags, void *const *epochs, uint32_t world);
+/* The decode FFN of one GPU as ONE cooperative launch: step_swiglu_ffn (src/runtime/qwen35.rs:2694-2707:
+ * quantize x, gate and up matvecs, silu(gate) * up, quantize, down matvec), row-sharded over `world` GPUs.
+ * This rank holds rows [ffn_begin, ffn_begin + ffn_local) of gate_w and up_w ([ffn_total, in_dim], both of
+ * gate_type) and rows [out_begin, out_begin + out_local) of down_w ([out_total, ffn_total], down_type).  It
+ * stores its ffn_local values of the intermediate silu(gate) * up, as f32, into every rank's h vector (f32
+ * [ffn_total]; every rank then quantizes the whole vector itself, block by block as rc_quantize_q8 does) and
+ * its out_local output rows into every rank's y (f32 [out_total]); the launch ends when all out_total rows of
+ * this call have arrived in this rank's y.  h_peers, y_peers, ctr_peers: host arrays of `world` device
+ * pointers (own buffers included, peers' mapped with rc_ipc_open_handle; h 16-byte aligned); ctr_peers[r]: two
+ * 64-bit counters in rank r's memory; work: rc_ffn_decode_work_bytes(ffn_local) bytes of this rank's memory.
+ * Counters and work are zeroed ONCE and then belong to this shape: the counters grow by a fixed amount per
+ * call.  Same per-block arithmetic as rc_quantize_q8 / rc_matvec / rc_swiglu_q8; a row's partial sums are
+ * added in a fixed order that depends on the shapes only, so results repeat bit for bit, and differ from the
+ * launch chain's in the last bits where the two split a row differently.  x (16-byte aligned) may be pinned
+ * host memory.  in_dim and ffn_total multiples of 1024; format pairs (gate, down): (Q4_K, Q6_K), (Q4_K, Q4_K),
+ * (Q5_K, Q6_K), (Q6_K, Q6_K), (Q8_0, Q8_0), (Q4_0, Q4_0), else RC_ERR_BAD_TYPE.  A cooperative launch of one
+ * CTA per SM; may be captured in a CUDA graph.  A wait that runs out (a peer that never launched) sets bits
+ * 20-23 of rc_device_status and the launch ends. */
+size_t rc_ffn_decode_work_bytes(uint32_t ffn_local);
+int rc_ffn_decode(void *stream, int gate_type, int down_type, const void *gate_w, const void *up_w,
+                  const void *down_w, const float *x, uint32_t in_dim, uint32_t ffn_local, uint32_t ffn_total,
+                  uint32_t ffn_begin, uint32_t out_local, uint32_t out_total, uint32_t out_begin,
+                  uint32_t world, uint32_t rank, void *const *h_peers, void *const *y_peers,
+                  void *const *ctr_peers, void *work);
 /* Row-sharded PrefillGemm::matmul_into_raw that gathers its own output: this rank holds weight rows
  * [row_begin, row_begin + out_dim) of an [out_total, in_dim] matrix; the kernel's finished tiles are stored
  * into columns row_begin.. of EVERY rank's [n_rows][out_total] f32 output (y_peers: host array of `world`

@@ -68,6 +68,7 @@ _SIGNATURES = {
     "rc_kernel_type": (_i, [_i]),
     "rc_debug_read_trace": (_i, [_vp, C.c_size_t]),
     "rc_debug_read_prof": (_i, [_vp, C.c_size_t]),
+    "rc_debug_read_ffn_trace": (_i, [_vp, C.c_size_t]),
     "rc_mmq_gemm_grouped_scratch_bytes": (_sz, [_u32, _u32]),
     "rc_mmq_gemm_grouped_f32": (_i, [_vp, _i, _vp, _sz, _vp, _vp, _u32, _vp, _vp, _u32, _sz, _i, _vp, _u32, _u32, _u32, _vp, _sz]),
     "rc_moe_gate_up_swiglu": (_i, [_vp, _i, _vp, _vp, _sz, _vp, _u32, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32]),
@@ -79,6 +80,9 @@ _SIGNATURES = {
     "rc_ipc_open_handle": (_i, [_vp, C.POINTER(_vp)]),
     "rc_ipc_close_handle": (_i, [_vp]),
     "rc_allgather_push": (_i, [_vp, _vp, _sz, C.POINTER(_vp), C.POINTER(_vp), _vp, _u32, _u32]),
+    "rc_ffn_decode_work_bytes": (_sz, [_u32]),
+    "rc_ffn_decode": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _u32,
+                           C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _vp]),
     "rc_peer_barrier": (_i, [_vp, C.POINTER(_vp), _vp, _u32, _u32]),
     "rc_allgather_push_logical": (_i, [_vp, C.POINTER(_vp), _sz, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _u32]),
     "rc_matmul_gather": (_i, [_vp, _i, _vp, _vp, C.POINTER(_vp), _u32, _u32, _u32, _u32, _u32, _u32, _vp, _sz]),

@@ -28,6 +28,14 @@ int launch_matvec_grouped(cudaStream_t s, int type, const void *slab, size_t byt
                           const void *xq, float *y, uint32_t in_dim, uint32_t out_dim,
                           uint32_t n_entries);
 int moe_set_attributes();
+// the decode FFN of one GPU in one cooperative launch (rc_matvec.cu)
+size_t ffn_decode_work_bytes(uint32_t ffn_local);
+int ffn_device_error(unsigned int *out, bool clear);
+int ffn_read_trace(void *out, size_t bytes);
+int launch_ffn_decode(cudaStream_t s, int gate_type, int down_type, const void *gate, const void *up, const void *down, const float *x,
+                      uint32_t in_dim, uint32_t ffn_local, uint32_t ffn_total, uint32_t ffn_begin, uint32_t out_local,
+                      uint32_t out_total, uint32_t out_begin, uint32_t world, uint32_t rank, void *const *h_peers,
+                      void *const *y_peers, void *const *ctr_peers, void *work);
 
 int launch_mmq_gemm(cudaStream_t s, int type, const void *w, const void *xq, float *y,
                     uint32_t in_dim, uint32_t out_dim, uint32_t p_rows);

@@ -30,6 +30,8 @@
 // A shared-memory ring filled by cp.async.bulk with a producer warp was built and measured
 // first: 12.3 us on the 5120->17408 Q4_K matrix against 9.9 us for this form (a plain read of
 // the same bytes takes 8.7 us), so the ring is not used.
+#include <algorithm>
+#include <cstring>
 #include <type_traits>
 
 #include "rc_common.cuh"
@@ -77,27 +79,30 @@ __device__ __forceinline__ XStage carve_stage(uint8_t *smem, uint32_t n_blocks)
 //   Q6_K        is = (32*sum(lo half), 32*sum(hi half));   Q4_0  is.x = 128*sum(all)
 //   IQ4_XS, IQ3_S  quants permuted into iq4_lookup8 order
 template <int FMT>
+__device__ __forceinline__ void stage_block(const XStage &st, uint32_t i, XBlock x)
+{
+    if (kCodebook<FMT>) {
+        int4 a, b;
+        xperm_iq4(x.lo.x, x.hi.x, a.x, a.y);
+        xperm_iq4(x.lo.y, x.hi.y, a.z, a.w);
+        xperm_iq4(x.lo.z, x.hi.z, b.x, b.y);
+        xperm_iq4(x.lo.w, x.hi.w, b.z, b.w);
+        x.lo = a;
+        x.hi = b;
+    }
+    st.lo[i] = x.lo;
+    st.hi[i] = x.hi;
+    const float dscale = (FMT == Q4_K || FMT == Q4_0) ? 0.0625f : 1.0f;
+    const float ssign = (FMT == Q4_K || FMT == Q5_K) ? -1.0f : 1.0f;
+    st.ds[i] = make_float2(x.d * dscale, x.xsum * ssign);
+    if (FMT == Q6_K) st.is[i] = make_int2(32 * x.s_lo, 32 * x.s_hi);
+    if (FMT == Q4_0) st.is[i] = make_int2(128 * (x.s_lo + x.s_hi), 0);
+}
+
+template <int FMT>
 __device__ __forceinline__ void stage_x(const XStage &st, const uint8_t *__restrict__ xq, uint32_t n_blocks)
 {
-    for (uint32_t i = threadIdx.x; i < n_blocks; i += blockDim.x) {
-        XBlock x = load_blockq8(xq + (size_t)i * RC_BLOCKQ8_BYTES);
-        if (kCodebook<FMT>) {
-            int4 a, b;
-            xperm_iq4(x.lo.x, x.hi.x, a.x, a.y);
-            xperm_iq4(x.lo.y, x.hi.y, a.z, a.w);
-            xperm_iq4(x.lo.z, x.hi.z, b.x, b.y);
-            xperm_iq4(x.lo.w, x.hi.w, b.z, b.w);
-            x.lo = a;
-            x.hi = b;
-        }
-        st.lo[i] = x.lo;
-        st.hi[i] = x.hi;
-        const float dscale = (FMT == Q4_K || FMT == Q4_0) ? 0.0625f : 1.0f;
-        const float ssign = (FMT == Q4_K || FMT == Q5_K) ? -1.0f : 1.0f;
-        st.ds[i] = make_float2(x.d * dscale, x.xsum * ssign);
-        if (FMT == Q6_K) st.is[i] = make_int2(32 * x.s_lo, 32 * x.s_hi);
-        if (FMT == Q4_0) st.is[i] = make_int2(128 * (x.s_lo + x.s_hi), 0);
-    }
+    for (uint32_t i = threadIdx.x; i < n_blocks; i += blockDim.x) stage_block<FMT>(st, i, load_blockq8(xq + (size_t)i * RC_BLOCKQ8_BYTES));
 }
 
 // ---- raw weight registers of one (row, sub-block) ---------------------------------------------
@@ -813,6 +818,466 @@ moe_gate_up_swiglu_kernel(const uint8_t *__restrict__ gate_slab, const uint8_t *
     }
 }
 
+// --------------------------------------------------------------------------------------------
+// The whole decode FFN of one GPU in ONE cooperative launch (step_swiglu_ffn, src/runtime/qwen35.rs:2694-2707:
+// quantize x -> gate, up -> silu(gate) * up -> quantize -> down), row-sharded over `world` GPUs; the phases are listed
+// at ffn_decode_kernel.  Seven launches of 3 to 9 us each become one, with no barrier inside the grid: a gate row and its
+// up row are walked by warps of one CTA.  A wait that runs out records a code (rc_device_status) and the launch ends.
+constexpr unsigned long long kFfnWaitNs = 200ull * 1000 * 1000;
+__device__ unsigned int g_ffn_error;
+// measurement aid, off until the first ffn_read_trace(): phase timestamps (globaltimer ns) of CTA 0, and the latest time any
+// CTA passed each mark
+__device__ unsigned long long g_ffn_trace[16];
+__device__ unsigned long long g_ffn_trace_max[16];
+static uint32_t g_ffn_trace_on = 0;
+
+struct FfnPeers {
+    float *h[RC_MAX_PEERS];                 // rank r's intermediate vector: f32 [ffn_total]
+    float *y[RC_MAX_PEERS];                 // rank r's output: f32 [out_total]
+    unsigned long long *ctr[RC_MAX_PEERS];  // rank r's counters: [0] intermediate values arrived, [1] output rows arrived
+};
+struct FfnParams {
+    const uint8_t *gate, *up, *down;
+    const float *x;
+    unsigned long long *sync;  // work: [0] calls done
+    uint32_t in_dim, ffn_local, ffn_total, ffn_begin, out_local, out_total, out_begin, world, rank;
+    uint32_t ks, ks_gu;        // warps that share a down row / a gate or up row
+    uint32_t trace;            // record phase times (debug)
+};
+
+__device__ __forceinline__ unsigned long long ffn_ld_acquire(const unsigned long long *p)
+{
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void ffn_red_release(unsigned long long *p, unsigned long long v)
+{
+    asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+// Adds n to counter `which` of every rank: this GPU's own first (its waiters are CTAs of this launch: device scope), then
+// one system-scope fence for all the peers' (their waiters read this CTA's stores across NVLink).
+__device__ __forceinline__ void ffn_post(unsigned long long *const *ctr, uint32_t which, unsigned long long n, uint32_t rank, uint32_t world)
+{
+    asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(ctr[rank] + which), "l"(n) : "memory");
+    if (world > 1u) {
+        asm volatile("fence.acq_rel.sys;" ::: "memory");
+        for (uint32_t r = 0; r < world; r++)
+            if (r != rank) asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(ctr[r] + which), "l"(n) : "memory");
+    }
+}
+__device__ __forceinline__ unsigned long long ffn_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// thread 0 of every CTA waits until *p >= target; false (and a recorded code) when the limit runs out
+__device__ __forceinline__ bool ffn_wait_ge(const unsigned long long *p, unsigned long long target, unsigned int code)
+{
+    const unsigned long long t0 = ffn_ns();
+    while (ffn_ld_acquire(p) < target) {
+        if (ffn_ns() - t0 > kFfnWaitNs) {
+            atomicExch(&g_ffn_error, code);
+            return false;
+        }
+        __nanosleep(40);
+    }
+    return true;
+}
+__device__ __forceinline__ float ffn_ld_cg(const float *p)
+{
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+// a 40-byte record written during this launch (by this or another GPU): read through L2, never through the
+// non-coherent path
+__device__ __forceinline__ XBlock load_blockq8_cg(const uint8_t *p)
+{
+    uint2 w[5];
+#pragma unroll
+    for (int i = 0; i < 5; i++)
+        asm volatile("ld.global.cg.v2.u32 {%0, %1}, [%2];" : "=r"(w[i].x), "=r"(w[i].y) : "l"(p + 8 * i));
+    XBlock x;
+    x.d = __uint_as_float(w[0].x);
+    x.xsum = __uint_as_float(w[0].y);
+    x.lo = make_int4((int)w[1].x, (int)w[1].y, (int)w[2].x, (int)w[2].y);
+    x.hi = make_int4((int)w[3].x, (int)w[3].y, (int)w[4].x, (int)w[4].y);
+    const int ones = 0x01010101;
+    x.s_lo = __dp4a(x.lo.x, ones, __dp4a(x.lo.y, ones, __dp4a(x.lo.z, ones, __dp4a(x.lo.w, ones, 0))));
+    x.s_hi = __dp4a(x.hi.x, ones, __dp4a(x.hi.y, ones, __dp4a(x.hi.z, ones, __dp4a(x.hi.w, ones, 0))));
+    return x;
+}
+
+// The BlockQ8 of 32 values held one per lane, as ten words: every lane returns word (lane < 10 ? lane : 0).
+__device__ __forceinline__ uint32_t q8_words(float v, uint32_t lane)
+{
+    float amax = fabsf(v), sum = v;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+        sum = __fadd_rn(sum, __shfl_xor_sync(0xFFFFFFFFu, sum, o));
+    }
+    const float d = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    int q = __float2int_rn(__fmul_rn(v, inv));
+    q = max(-127, min(127, q));
+    uint32_t b = (uint32_t)(q & 0xFF) << (8 * (lane & 3u));
+    b |= __shfl_xor_sync(0xFFFFFFFFu, b, 1);
+    b |= __shfl_xor_sync(0xFFFFFFFFu, b, 2);
+    const uint32_t word = __shfl_sync(0xFFFFFFFFu, b, ((lane >= 2u ? lane - 2u : 0u) & 7u) * 4u);
+    return lane == 0 ? __float_as_uint(d) : lane == 1 ? __float_as_uint(sum) : word;
+}
+
+// One warp's walk over rows of one tensor against staged activations.  A CTA's warps are split into teams of `vwarps`
+// (the caller gives each warp its place `vwarp` in its team and the team's tensor); `ks` warps of a team share a row, each
+// with a balanced slice of the row's 1024-wide iterations, loaded LEN iterations at a time.  prime() sends the first
+// loads, which depend on no activation, so that they can fly while the activations are still being produced; run() keeps
+// the next chunk (of this row, else of the warp's next row) in flight while the current one is multiplied.
+template <int FMT> struct RowWalk {
+    static constexpr int LEN = FmtTraits<FMT>::rows_max_len;
+    Planes p;
+    uint32_t lane, n_rows, i0, i1, row, row_stride, rows_per_cta;
+    bool a4;
+    Raw<FMT> cur[LEN];
+
+    __device__ __forceinline__ void init(const Planes &planes, uint32_t n_sub, uint32_t rows, uint32_t ks, uint32_t vwarp, uint32_t vwarps)
+    {
+        p = planes;
+        lane = threadIdx.x & 31u;
+        n_rows = rows;
+        const uint32_t slice = vwarp % ks, n_iters = n_sub >> 5;
+        i0 = slice * n_iters / ks;
+        i1 = (slice + 1u) * n_iters / ks;
+        rows_per_cta = vwarps / ks;
+        row = blockIdx.x * rows_per_cta + vwarp / ks;
+        row_stride = gridDim.x * rows_per_cta;
+        a4 = (reinterpret_cast<uintptr_t>(p.sup) & 3u) == 0;
+    }
+    __device__ __forceinline__ void fetch(uint32_t r, uint32_t it)
+    {
+        const GroupPtrs gp = group_ptrs<FMT>(p, r, it * 32u + lane);
+        if (it + LEN <= i1) { // the common, unguarded chunk: its loads issue back to back
+#pragma unroll
+            for (int i = 0; i < LEN; i++) {
+                if (a4) fetch_off<FMT, true>(cur[i], gp, i);
+                else fetch_off<FMT, false>(cur[i], gp, i);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < LEN; i++) {
+                if (it + i < i1) {
+                    if (a4) fetch_off<FMT, true>(cur[i], gp, i);
+                    else fetch_off<FMT, false>(cur[i], gp, i);
+                }
+            }
+        }
+    }
+    __device__ __forceinline__ void prime()
+    {
+        if (row < n_rows && i0 < i1) fetch(row, i0);
+    }
+    // Asks L2 for the 4-bit and high-bit planes of this warp's slices of its next `n_ahead` rows beyond the one in flight.
+    __device__ __forceinline__ void prefetch_l2(uint32_t n_ahead) const
+    {
+        constexpr uint32_t aux_w = (FMT == Q8_0) ? 16u : (FMT == Q6_K) ? 8u : (FMT == Q5_K || FMT == Q5_1) ? 4u : 0u;
+        uint32_t r = row;
+        for (uint32_t k = 0; k <= n_ahead && r < n_rows; k++, r += row_stride) {
+            const uint8_t *b0 = p.nib + ((size_t)r * p.nsp + (size_t)i0 * 32u) * 16u;
+            const uint32_t len = (i1 - i0) * 32u * 16u;
+            for (uint32_t o = lane * 128u; o < len; o += 32u * 128u) asm volatile("prefetch.global.L2 [%0];" ::"l"(b0 + o));
+            if (aux_w) {
+                const uint8_t *b1 = p.aux + ((size_t)r * p.nsp + (size_t)i0 * 32u) * aux_w;
+                const uint32_t len1 = (i1 - i0) * 32u * aux_w;
+                for (uint32_t o = lane * 128u; o < len1; o += 32u * 128u) asm volatile("prefetch.global.L2 [%0];" ::"l"(b1 + o));
+            }
+        }
+    }
+    // finish(row, live, sum) runs on every lane of every warp once per round of the CTA (sum = the warp's slice of the
+    // row's dot product, the same in all lanes); a round is uniform over the CTA, so finish may synchronize warps.
+    template <typename Finish> __device__ __forceinline__ void run(const XStage &st, Finish finish)
+    {
+        for (uint32_t r0 = blockIdx.x * rows_per_cta; r0 < n_rows; r0 += row_stride, row += row_stride) {
+            const bool live = row < n_rows && i0 < i1;
+            float acc = 0.0f;
+            if (live) {
+                for (uint32_t it = i0; it < i1; it += LEN) {
+                    if (it + LEN <= i1) {
+#pragma unroll
+                        for (int i = 0; i < LEN; i++) {
+                            const uint32_t xi = (it + i) * 32u + lane;
+                            const int4 xl = st.lo[xi], xh = st.hi[xi];
+                            const float2 ds = st.ds[xi];
+                            const int2 is = FmtTraits<FMT>::needs_is ? st.is[xi] : make_int2(0, 0);
+                            int d0, d1;
+                            acc += term<FMT>(cur[i], xl, xh, ds, is, d0, d1);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < LEN; i++) {
+                            if (it + i < i1) {
+                                const uint32_t xi = (it + i) * 32u + lane;
+                                const int4 xl = st.lo[xi], xh = st.hi[xi];
+                                const float2 ds = st.ds[xi];
+                                const int2 is = FmtTraits<FMT>::needs_is ? st.is[xi] : make_int2(0, 0);
+                                int d0, d1;
+                                acc += term<FMT>(cur[i], xl, xh, ds, is, d0, d1);
+                            }
+                        }
+                    }
+                    if (it + LEN < i1) fetch(row, it + LEN);
+                    else if (row + row_stride < n_rows) fetch(row + row_stride, i0);
+                }
+            }
+            finish(row, live, warp_sum(acc));
+        }
+    }
+};
+
+// Quantizes n_blocks blocks of 32 f32 values (16-byte aligned) into staged activations for format FMT, the whole CTA at
+// work: a warp loads four blocks per instruction (one float4 per lane, eight lanes per block) and all of a warp's loads go
+// out before the first is used.  The sum follows the warp quantizer's butterfly (element i adds v[i] + v[i ^ 16], then
+// ^ 8, 4, 2, 1: lanes ^ 4, 2, 1 of the block's eight, then the lane's own elements ^ 2, ^ 1), so a record equals
+// quantize_q8's bit for bit.  through_l2: the values were written during this launch (by this or another GPU).
+template <int FMT> __device__ __forceinline__ void quantize_stage(const XStage &st, uint32_t n_blocks, const float *src, bool through_l2)
+{
+    constexpr int kAhead = 6;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const uint32_t n_quads = (n_blocks + 3u) >> 2;
+    for (uint32_t q0 = warp; q0 < n_quads; q0 += n_warps * kAhead) {
+        float4 f[kAhead];
+#pragma unroll
+        for (int a = 0; a < kAhead; a++) {
+            const uint32_t q = q0 + a * n_warps, b = q * 4u + (lane >> 3);
+            f[a] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (q < n_quads && b < n_blocks) {
+                const float *p = src + (size_t)b * 32u + (lane & 7u) * 4u;
+                if (through_l2)
+                    asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(f[a].x), "=f"(f[a].y), "=f"(f[a].z), "=f"(f[a].w) : "l"(p));
+                else
+                    f[a] = *reinterpret_cast<const float4 *>(p);
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < kAhead; a++) {
+            const uint32_t q = q0 + a * n_warps, b = q * 4u + (lane >> 3);
+            if (q >= n_quads) break; // uniform over the warp
+            const float4 v = f[a];
+            float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+            float s0 = v.x, s1 = v.y, s2 = v.z, s3 = v.w;
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) {
+                amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+                s0 = __fadd_rn(s0, __shfl_xor_sync(0xFFFFFFFFu, s0, o));
+                s1 = __fadd_rn(s1, __shfl_xor_sync(0xFFFFFFFFu, s1, o));
+                s2 = __fadd_rn(s2, __shfl_xor_sync(0xFFFFFFFFu, s2, o));
+                s3 = __fadd_rn(s3, __shfl_xor_sync(0xFFFFFFFFu, s3, o));
+            }
+            XBlock xb;
+            xb.xsum = __fadd_rn(__fadd_rn(s0, s2), __fadd_rn(s1, s3));
+            xb.d = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+            const float inv = amax > 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+            const int q0i = max(-127, min(127, __float2int_rn(__fmul_rn(v.x, inv))));
+            const int q1i = max(-127, min(127, __float2int_rn(__fmul_rn(v.y, inv))));
+            const int q2i = max(-127, min(127, __float2int_rn(__fmul_rn(v.z, inv))));
+            const int q3i = max(-127, min(127, __float2int_rn(__fmul_rn(v.w, inv))));
+            const int word = (q0i & 0xFF) | ((q1i & 0xFF) << 8) | ((q2i & 0xFF) << 16) | ((q3i & 0xFF) << 24);
+            const uint32_t base = lane & 24u;
+            xb.lo.x = __shfl_sync(0xFFFFFFFFu, word, base + 0);
+            xb.lo.y = __shfl_sync(0xFFFFFFFFu, word, base + 1);
+            xb.lo.z = __shfl_sync(0xFFFFFFFFu, word, base + 2);
+            xb.lo.w = __shfl_sync(0xFFFFFFFFu, word, base + 3);
+            xb.hi.x = __shfl_sync(0xFFFFFFFFu, word, base + 4);
+            xb.hi.y = __shfl_sync(0xFFFFFFFFu, word, base + 5);
+            xb.hi.z = __shfl_sync(0xFFFFFFFFu, word, base + 6);
+            xb.hi.w = __shfl_sync(0xFFFFFFFFu, word, base + 7);
+            if ((lane & 7u) == 0 && b < n_blocks) {
+                const int ones = 0x01010101;
+                xb.s_lo = __dp4a(xb.lo.x, ones, __dp4a(xb.lo.y, ones, __dp4a(xb.lo.z, ones, __dp4a(xb.lo.w, ones, 0))));
+                xb.s_hi = __dp4a(xb.hi.x, ones, __dp4a(xb.hi.y, ones, __dp4a(xb.hi.z, ones, __dp4a(xb.hi.w, ones, 0))));
+                stage_block<FMT>(st, b, xb);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void ffn_group_sync(uint32_t id, uint32_t n_threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n_threads) : "memory");
+}
+
+// The decode feed-forward of one shard in one launch, one CTA of 24 warps per SM (a cooperative launch: every CTA is
+// resident, so CTAs may wait for data that other CTAs and other GPUs produce):
+//   1. every CTA quantizes x into shared memory while its first weights are in flight; warps 0-11 walk gate rows and warps
+//      12-23 the same up rows, so silu(g) * u of a row is formed inside the CTA and stored, as f32, into every rank's
+//      intermediate vector; the CTA then adds its row count to every rank's arrival counter (release, system scope);
+//   2. every CTA waits until its own rank's counter shows all ffn_total values of this call, quantizes the intermediate into
+//      shared memory (records equal to quantize_q8's), and walks its down rows, storing each into every rank's output;
+//   3. CTA 0 waits until all out_total rows of this rank's output have arrived and publishes the call number.
+// Counters only grow: call c waits for c * total, so nothing is reset between launches and a launch's data cannot be
+// mistaken for the next one's.  Every wait gives up after kFfnWaitNs, records a code and lets the kernel run out.
+constexpr int kFfnWarps = 24;
+constexpr uint32_t kFfnTeam = kFfnWarps / 2;
+
+template <int FG, int FD>
+__global__ void __launch_bounds__(kFfnWarps * 32, 1) ffn_decode_kernel(const FfnParams P, const FfnPeers peers)
+{
+    extern __shared__ __align__(16) uint8_t smem[];
+    __shared__ float s_part[2][kFfnWarps];
+    __shared__ uint32_t s_count[kFfnWarps];
+    __shared__ unsigned long long s_call;
+    __shared__ int s_ok;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t n_sub_x = P.in_dim >> 5, n_sub_h = P.ffn_total >> 5;
+    auto mark = [&](int k) {
+        if (P.trace && threadIdx.x == 0) {
+            const unsigned long long t = ffn_ns();
+            if (blockIdx.x == 0) g_ffn_trace[k] = t;
+            atomicMax(&g_ffn_trace_max[k], t);
+        }
+    };
+    mark(0);
+    if (threadIdx.x == 0) {
+        s_call = *reinterpret_cast<volatile unsigned long long *>(P.sync) + 1ull; // written only by the previous launch
+        s_ok = 1;
+    }
+    // ---- phase 1
+    const XStage stx = carve_stage<FG>(smem, n_sub_x);
+    uint32_t rows_done = 0;
+    {
+        RowWalk<FG> w1;
+        const bool is_up = warp >= kFfnTeam;
+        const uint32_t vwarp = warp % kFfnTeam, ks = P.ks_gu;
+        w1.init(planes_of<FG>(is_up ? P.up : P.gate, P.in_dim, P.ffn_local), n_sub_x, P.ffn_local, ks, vwarp, kFfnTeam);
+        w1.prime();
+        quantize_stage<FG>(stx, n_sub_x, P.x, false);
+        __syncthreads();
+        mark(1);
+        // the 2 * ks warps that hold slices of gate row i and up row i meet at a barrier of their own; the first of them
+        // sums the slices in slice order and forms the row's intermediate value
+        uint32_t buf = 0;
+        const uint32_t group = vwarp / ks, slice = vwarp % ks;
+        w1.run(stx, [&](uint32_t r, bool live, float sum) {
+            if (lane == 0) s_part[buf][warp] = sum;
+            ffn_group_sync(1u + group, 64u * ks);
+            if (!is_up && slice == 0 && lane == 0 && live) {
+                float g = s_part[buf][warp], u = s_part[buf][warp + kFfnTeam];
+                for (uint32_t k = 1; k < ks; k++) {
+                    g += s_part[buf][warp + k];
+                    u += s_part[buf][warp + kFfnTeam + k];
+                }
+                const float h = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u); // swiglu_q8_kernel's expression
+                for (uint32_t k = 0; k < P.world; k++) peers.h[k][P.ffn_begin + r] = h;
+                rows_done++;
+            }
+            buf ^= 1u;
+        });
+    }
+    const unsigned long long call = s_call;
+    if (lane == 0) s_count[warp] = rows_done;
+    __syncthreads(); // every store of this CTA's intermediate values is ordered before thread 0's releases
+    mark(2);
+    if (threadIdx.x == 0) {
+        unsigned long long n = 0;
+        for (int k = 0; k < (int)kFfnTeam; k++) n += s_count[k];
+        if (n) ffn_post(peers.ctr, 0, n, P.rank, P.world);
+    }
+    // the down rows' first weights fly, and the following ones are called into L2, across the exchange of the intermediate
+    RowWalk<FD> w3;
+    w3.init(planes_of<FD>(P.down, P.ffn_total, P.out_local), n_sub_h, P.out_local, P.ks, warp, kFfnWarps);
+    w3.prime();
+    w3.prefetch_l2(2);
+    mark(3);
+    if (threadIdx.x == 0) {
+        if (!ffn_wait_ge(peers.ctr[P.rank], call * (unsigned long long)P.ffn_total, 2u)) s_ok = 0;
+    }
+    __syncthreads();
+    mark(4);
+    // ---- phase 2: the whole intermediate, quantized per CTA (read through L2: it was written during this launch)
+    const XStage sth = carve_stage<FD>(smem, n_sub_h);
+    if (s_ok) quantize_stage<FD>(sth, n_sub_h, peers.h[P.rank], true);
+    __syncthreads();
+    mark(5);
+    rows_done = 0;
+    if (s_ok) {
+        uint32_t buf = 0;
+        const uint32_t ks = P.ks, slice = warp % ks;
+        w3.run(sth, [&](uint32_t r, bool live, float sum) {
+            float v = sum;
+            if (ks > 1u) {
+                if (lane == 0) s_part[buf][warp] = sum;
+                ffn_group_sync(1u + warp / ks, 32u * ks);
+                if (slice == 0 && lane == 0) {
+                    v = s_part[buf][warp];
+                    for (uint32_t k = 1; k < ks; k++) v += s_part[buf][warp + k]; // slice order: reproducible
+                }
+                buf ^= 1u;
+            }
+            if (slice == 0 && lane == 0 && live) {
+                for (uint32_t k = 0; k < P.world; k++) peers.y[k][P.out_begin + r] = v;
+                rows_done++;
+            }
+        });
+    }
+    // one arrival per CTA: the rows its warps wrote
+    if (lane == 0) s_count[warp] = rows_done;
+    __syncthreads();
+    mark(6);
+    if (threadIdx.x == 0) {
+        unsigned long long n = 0;
+        for (int k = 0; k < kFfnWarps; k++) n += s_count[k];
+        if (n) ffn_post(peers.ctr, 1, n, P.rank, P.world);
+        if (blockIdx.x == 0) {
+            if (s_ok) ffn_wait_ge(peers.ctr[P.rank] + 1, call * (unsigned long long)P.out_total, 3u);
+            *reinterpret_cast<volatile unsigned long long *>(P.sync) = call; // the next launch's call number follows
+            mark(7);
+        }
+    }
+}
+
+// Warps that share a row: the count, among the powers of two up to the team size, with the least (rounds of the grid) x
+// (dependent load round trips + multiply time per round), the shared-row reduction counted per round.
+static uint32_t ffn_pick_ks(uint32_t rows, uint32_t n_iters, uint32_t len, uint32_t grid, uint32_t team)
+{
+    uint32_t best = 1;
+    float best_cost = 1e30f;
+    for (uint32_t ks = 1; ks <= team; ks *= 2u) {
+        if (ks > n_iters) break;
+        if (team % ks) continue;
+        const uint32_t per_round = grid * (team / ks), rounds = (rows + per_round - 1u) / per_round;
+        const uint32_t per = (n_iters + ks - 1u) / ks, trips = (per + len - 1u) / len;
+        const float cost = (float)rounds * ((float)trips + 0.15f * (float)per + (ks > 1u ? 0.3f : 0.0f));
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = ks;
+        }
+    }
+    return best;
+}
+
+template <int FG, int FD>
+int launch_ffn(cudaStream_t s, const FfnParams &P, const FfnPeers &peers)
+{
+    const uint32_t nx = P.in_dim >> 5, nh = P.ffn_total >> 5;
+    const size_t smem = (std::max((size_t)nx * FmtTraits<FG>::x_bytes, (size_t)nh * FmtTraits<FD>::x_bytes) + 15u) & ~(size_t)15u;
+    if (smem > kMaxStageBytesHost) return RC_ERR_BAD_SHAPE;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(ffn_decode_kernel<FG, FD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    FfnParams Q = P;
+    const uint32_t grid = (uint32_t)sm_count(); // one CTA per SM: 24 warps, the whole register file
+    Q.ks = ffn_pick_ks(P.out_local, nh >> 5, (uint32_t)FmtTraits<FD>::rows_max_len, grid, (uint32_t)kFfnWarps);
+    Q.ks_gu = ffn_pick_ks(P.ffn_local, nx >> 5, (uint32_t)FmtTraits<FG>::rows_max_len, grid, kFfnTeam);
+    Q.trace = g_ffn_trace_on;
+    FfnPeers pp = peers;
+    void *args[] = {&Q, &pp};
+    return (int)cudaLaunchCooperativeKernel((const void *)ffn_decode_kernel<FG, FD>, dim3(grid), dim3(kFfnWarps * 32), args, smem, s);
+}
+
 struct Tuning {
     int ks = 0;          // 0 = heuristic
     int grid_mult = 0;   // CTAs launched per resident CTA slot; 0 = heuristic
@@ -1190,6 +1655,73 @@ int launch_matvec(cudaStream_t s, int type, const void *w, const void *xq, float
         if (rc) return rc;
     }
     return RC_OK;
+}
+
+size_t ffn_decode_work_bytes(uint32_t) { return 64; }
+
+// Copies out CTA 0's marks [0, 16) and the per-mark maxima over CTAs [16, 32), clears the maxima and switches the marks on.
+int ffn_read_trace(void *out, size_t bytes)
+{
+    unsigned long long buf[32] = {0};
+    cudaError_t e = cudaMemcpyFromSymbol(buf, g_ffn_trace, sizeof(g_ffn_trace));
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(buf + 16, g_ffn_trace_max, sizeof(g_ffn_trace_max));
+    if (e != cudaSuccess) return (int)e;
+    const unsigned long long zeros[16] = {0};
+    e = cudaMemcpyToSymbol(g_ffn_trace_max, zeros, sizeof(zeros));
+    g_ffn_trace_on = 1;
+    memcpy(out, buf, bytes < sizeof(buf) ? bytes : sizeof(buf));
+    return (int)e;
+}
+
+int ffn_device_error(unsigned int *out, bool clear)
+{
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_ffn_error, sizeof(unsigned int));
+    if (e == cudaSuccess && clear && *out) {
+        const unsigned int zero = 0;
+        e = cudaMemcpyToSymbol(g_ffn_error, &zero, sizeof(unsigned int));
+    }
+    return (int)e;
+}
+
+int launch_ffn_decode(cudaStream_t s, int gate_type, int down_type, const void *gate, const void *up, const void *down, const float *x,
+                      uint32_t in_dim, uint32_t ffn_local, uint32_t ffn_total, uint32_t ffn_begin, uint32_t out_local,
+                      uint32_t out_total, uint32_t out_begin, uint32_t world, uint32_t rank, void *const *h_peers,
+                      void *const *y_peers, void *const *ctr_peers, void *work)
+{
+    FfnParams P;
+    P.gate = (const uint8_t *)gate;
+    P.up = (const uint8_t *)up;
+    P.down = (const uint8_t *)down;
+    P.x = x;
+    P.sync = reinterpret_cast<unsigned long long *>(work);
+    P.in_dim = in_dim;
+    P.ffn_local = ffn_local;
+    P.ffn_total = ffn_total;
+    P.ffn_begin = ffn_begin;
+    P.out_local = out_local;
+    P.out_total = out_total;
+    P.out_begin = out_begin;
+    P.world = world;
+    P.rank = rank;
+    P.ks = 1;
+    P.ks_gu = 1;
+    P.trace = 0;
+    FfnPeers peers;
+    for (uint32_t r = 0; r < RC_MAX_PEERS; r++) {
+        peers.h[r] = r < world ? (float *)h_peers[r] : nullptr;
+        peers.y[r] = r < world ? (float *)y_peers[r] : nullptr;
+        peers.ctr[r] = r < world ? (unsigned long long *)ctr_peers[r] : nullptr;
+    }
+#define RC_FFN(G, D) \
+    if (gate_type == G && down_type == D) return launch_ffn<G, D>(s, P, peers);
+    RC_FFN(Q4_K, Q6_K)
+    RC_FFN(Q4_K, Q4_K)
+    RC_FFN(Q5_K, Q6_K)
+    RC_FFN(Q6_K, Q6_K)
+    RC_FFN(Q8_0, Q8_0)
+    RC_FFN(Q4_0, Q4_0)
+#undef RC_FFN
+    return RC_ERR_BAD_TYPE;
 }
 
 } // namespace rc

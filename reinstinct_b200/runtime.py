@@ -22,7 +22,7 @@ __all__ = [
     "launch_quantize_q8", "launch_matvec", "launch_matvec_xq8", "launch_matvec_batched",
     "matvec_block_dots", "launch_mmq_gemm", "launch_moe_sort", "launch_moe_gather_xq",
     "launch_moe_grouped_gemm", "launch_moe_scatter_rows", "repacked_len", "init", "PeerAllGather",
-    "PeerBuffers", "GatheredPrefillGemm", "launch_ffn_decode", "MoeGroupedGemm", "launch_rmsnorm_q8", "launch_add_rmsnorm_q8", "launch_swiglu_q8",
+    "PeerBuffers", "GatheredPrefillGemm", "launch_ffn_decode", "FusedFfnDecode", "MoeGroupedGemm", "launch_rmsnorm_q8", "launch_add_rmsnorm_q8", "launch_swiglu_q8",
     "launch_moe_expert_matvec", "launch_moe_gate_up_swiglu", "launch_moe_topk", "launch_moe_act_q8", "launch_moe_combine", "ACT_GEGLU", "ACT_SWIGLU",
 ]
 
@@ -483,6 +483,66 @@ class PeerBuffers:
         if self._base:
             self.lib.rc_free(self._base)
             self._base = 0
+
+
+class FusedFfnDecode:
+    """step_swiglu_ffn (src/runtime/qwen35.rs:2694-2707) as ONE cooperative launch per GPU (rc_ffn_decode), row-sharded
+    over the ranks of `group` (or a single GPU when torch.distributed is not initialised): this rank's `gate` and `up`
+    hold rows [ffn_begin, ffn_begin + gate.out_dim) of the [ffn_total, in_dim] projections, `down` rows
+    [out_begin, out_begin + down.out_dim) of [out_total, ffn_total].  After run(x) — on the stream — this rank's
+    `y_ptr` holds all out_total outputs and `h_ptr` the whole f32 intermediate silu(gate) * up.  Buffers, counters and the
+    work area belong to this object (one per layer shape)."""
+
+    def __init__(self, gate: GpuMatvecTensor, up: GpuMatvecTensor, down: GpuMatvecTensor, ffn_total: int, out_total: int,
+                 ffn_begin: int = 0, out_begin: int = 0, group=None, device="cuda"):
+        import torch.distributed as dist
+
+        lib = _lib.load()
+        self.lib, self.gate, self.up, self.down = lib, gate, up, down
+        self.ffn_total, self.out_total, self.ffn_begin, self.out_begin = ffn_total, out_total, ffn_begin, out_begin
+        h_bytes = (ffn_total * 4 + 255) // 256 * 256
+        y_bytes = (out_total * 4 + 255) // 256 * 256
+        self._h_off, self._y_off, self._ctr_off = 0, h_bytes, h_bytes + y_bytes
+        total = h_bytes + y_bytes + 256
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            self.peers = PeerBuffers(total, 1, group)
+            self.rank, self.world = self.peers.rank, self.peers.world
+            bases = [self.peers.ptrs[0][r] for r in range(self.world)]
+            self._local = None
+        else:
+            self.peers, self.rank, self.world = None, 0, 1
+            self._local = torch.zeros(total, dtype=torch.uint8, device=device)
+            bases = [self._local.data_ptr()]
+        self._h = (C.c_void_p * self.world)(*[b + self._h_off for b in bases])
+        self._y = (C.c_void_p * self.world)(*[b + self._y_off for b in bases])
+        self._ctr = (C.c_void_p * self.world)(*[b + self._ctr_off for b in bases])
+        own = bases[self.rank]
+        self.h_ptr, self.y_ptr = own + self._h_off, own + self._y_off
+        self.work = torch.zeros(lib.rc_ffn_decode_work_bytes(gate.out_dim), dtype=torch.uint8, device=device)
+
+    def run(self, x, y=None) -> None:
+        """x: f32 [in_dim] on the device or in pinned host memory.  y (single GPU only): a pinned host tensor that
+        receives the output instead of this object's device buffer: the last phase then writes across PCIe itself."""
+        g, d = self.gate, self.down
+        y_arr = self._y
+        if y is not None:
+            assert self.world == 1, "an output override is for the single-GPU call"
+            y_arr = (C.c_void_p * 1)(_ptr(y))
+        check(self.lib.rc_ffn_decode(_stream(), g.dtype, d.dtype, _ptr(g.data), _ptr(self.up.data), _ptr(d.data), _ptr(x), g.in_dim,
+                                     g.out_dim, self.ffn_total, self.ffn_begin, d.out_dim, self.out_total, self.out_begin,
+                                     self.world, self.rank, self._h, y_arr, self._ctr, _ptr(self.work)), "rc_ffn_decode")
+
+    def read_y(self, dst: torch.Tensor) -> None:
+        kind = 3 if dst.is_cuda else 2
+        check(self.lib.rc_memcpy_async(dst.data_ptr(), self.y_ptr, self.out_total * 4, kind, _stream()), "rc_memcpy_async")
+
+    def read_h(self, dst: torch.Tensor) -> None:
+        kind = 3 if dst.is_cuda else 2
+        check(self.lib.rc_memcpy_async(dst.data_ptr(), self.h_ptr, self.ffn_total * 4, kind, _stream()), "rc_memcpy_async")
+
+    def close(self) -> None:
+        if self.peers is not None:
+            self.peers.close()
 
 
 class PeerAllGather:

@@ -1,0 +1,133 @@
+"""The decode FFN as one cooperative launch (rc_ffn_decode) against the five-launch chain it replaces
+(step_swiglu_ffn, src/runtime/qwen35.rs:2694-2707: quantize, gate, up, swiglu_q8, down): the intermediate quantizes to
+the chain's BlockQ8 records (up to the last bit of a row sum, where the two split a row over warps differently), the
+outputs agree within f32 association and with the CPU oracle's exact integer dots, and repeat bit for bit.  A rank
+whose peer never arrives runs into its bounded wait."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+import oracle as ro
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-3
+
+
+def _status(lib, clear=False) -> int:
+    st = C.c_uint(0)
+    fn = lib.rc_device_status_clear if clear else lib.rc_device_status
+    assert fn(C.byref(st)) == 0
+    return st.value
+
+
+def _records_close(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """BlockQ8 streams equal up to what a last-bit difference of the f32 inputs can do: d and xsum within 1e-5
+    relative, quants off by at most one step in at most 1 % of the places."""
+    ra, rb = a.cpu().numpy().reshape(-1, 40), b.cpu().numpy().reshape(-1, 40)
+    fa, fb = ra[:, :8].copy().view(np.float32), rb[:, :8].copy().view(np.float32)
+    if not np.allclose(fa, fb, rtol=1e-5, atol=1e-6):
+        return False
+    dq = np.abs(ra[:, 8:].view(np.int8).astype(np.int32) - rb[:, 8:].view(np.int8).astype(np.int32))
+    return int(dq.max()) <= 1 and float((dq != 0).mean()) < 0.01
+
+
+def _chain(rt, gate, up, down, xd, ffn, out):
+    u8 = dict(dtype=torch.uint8, device="cuda")
+    xq = torch.empty((gate.in_dim // 32) * 40, **u8)
+    hq = torch.empty((ffn // 32) * 40, **u8)
+    yg, yu, y = torch.empty(ffn, device="cuda"), torch.empty(ffn, device="cuda"), torch.empty(out, device="cuda")
+    rt.launch_ffn_decode(gate, up, down, xd, xq, yg, yu, hq, y)
+    return hq, y
+
+
+@pytest.mark.parametrize("tg,td,hidden,ffn,out", [
+    (ro.Q4_K, ro.Q6_K, 5120, 17408, 5120),   # config 2: one warp per down row
+    (ro.Q4_K, ro.Q6_K, 1024, 2048, 640),     # a small shard-like shape: eight warps share a down row
+    (ro.Q8_0, ro.Q8_0, 2048, 1024, 300),
+    (ro.Q6_K, ro.Q6_K, 1024, 3072, 96),
+    (ro.Q4_0, ro.Q4_0, 1024, 1024, 2000),
+])
+def test_fused_ffn_equals_the_launch_chain(rt, tg, td, hidden, ffn, out):
+    lib = rt._lib.load()
+    _status(lib, clear=True)
+    gate = rt.GpuMatvecTensor.from_bytes_matvec(cases.synth_case(tg, hidden, ffn, 1, seed=1)[0], tg, hidden, ffn)
+    up = rt.GpuMatvecTensor.from_bytes_matvec(cases.synth_case(tg, hidden, ffn, 1, seed=2)[0], tg, hidden, ffn)
+    raw_d = cases.synth_case(td, ffn, out, 1, seed=3)[0]
+    down = rt.GpuMatvecTensor.from_bytes_matvec(raw_d, td, ffn, out)
+    fused = rt.FusedFfnDecode(gate, up, down, ffn, out)
+    for rnd in range(3):  # the counters grow call by call
+        x = cases.synth_case(tg, hidden, 8, 1, seed=10 + rnd)[1]
+        xd = torch.from_numpy(x).cuda().reshape(-1)
+        hq_ref, y_ref = _chain(rt, gate, up, down, xd, ffn, out)
+        fused.run(xd)
+        h = torch.empty(ffn, device="cuda")
+        y = torch.empty_like(y_ref)
+        fused.read_h(h)
+        fused.read_y(y)
+        hq = torch.empty_like(hq_ref)
+        rt.launch_quantize_q8(h, hq, ffn, 1)   # the records the kernel formed from h in shared memory
+        torch.cuda.synchronize()
+        assert _status(lib) == 0
+        # (the two may split a row over warps differently: a sum then differs in the last bit, and a quant may land
+        # on the other side of a rounding boundary)
+        assert _records_close(hq, hq_ref), f"round {rnd}: intermediate records differ"
+        a, b = y.cpu().numpy(), y_ref.cpu().numpy().astype(np.float64)
+        assert ro.rel_l2(a, b) < F32_TOL, rnd
+        # the down projection against the CPU oracle on the fused kernel's OWN records: exact integer dots
+        _, y64, _ = ro.matvec_q8(td, ro.repack(td, raw_d, ffn, out), hq.cpu().numpy(), ffn, out, 1)
+        assert ro.rel_l2(a, y64) < 1e-5, rnd
+
+
+def test_fused_ffn_config2_repeats_bit_for_bit(rt):
+    """The order of additions depends on the shapes only: two objects, two calls each, one set of bits."""
+    tg, td, hidden, ffn, out = ro.Q4_K, ro.Q6_K, 5120, 17408, 5120
+    gate = rt.GpuMatvecTensor.from_bytes_matvec(cases.synth_case(tg, hidden, ffn, 1, seed=4)[0], tg, hidden, ffn)
+    up = rt.GpuMatvecTensor.from_bytes_matvec(cases.synth_case(tg, hidden, ffn, 1, seed=5)[0], tg, hidden, ffn)
+    down = rt.GpuMatvecTensor.from_bytes_matvec(cases.synth_case(td, ffn, out, 1, seed=6)[0], td, ffn, out)
+    xd = torch.from_numpy(cases.synth_case(tg, hidden, 8, 1, seed=7)[1]).cuda().reshape(-1)
+    _, y_ref = _chain(rt, gate, up, down, xd, ffn, out)
+    outs = []
+    for _ in range(2):
+        fused = rt.FusedFfnDecode(gate, up, down, ffn, out)
+        for _ in range(2):
+            fused.run(xd)
+            y = torch.empty_like(y_ref)
+            fused.read_y(y)
+            torch.cuda.synchronize()
+            outs.append(y)
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+    assert ro.rel_l2(outs[0].cpu().numpy(), y_ref.cpu().numpy().astype(np.float64)) < 1e-5
+
+
+def test_fused_ffn_absent_peer_runs_into_the_bounded_wait(rt):
+    """Rank 0 of two whose peer never runs: its own half of the records arrives, the wait for the rest gives up
+    after its limit, the status word says which wait, and the device stays usable."""
+    lib = rt._lib.load()
+    _status(lib, clear=True)
+    tg, td, hidden, ffn, out = ro.Q4_K, ro.Q6_K, 1024, 2048, 256
+    half = ffn // 2
+    gate = rt.GpuMatvecTensor.from_bytes_matvec(cases.synth_case(tg, hidden, half, 1, seed=1)[0], tg, hidden, half)
+    up = rt.GpuMatvecTensor.from_bytes_matvec(cases.synth_case(tg, hidden, half, 1, seed=2)[0], tg, hidden, half)
+    down = rt.GpuMatvecTensor.from_bytes_matvec(cases.synth_case(td, ffn, out // 2, 1, seed=3)[0], td, ffn, out // 2)
+    xd = torch.from_numpy(cases.synth_case(tg, hidden, 8, 1, seed=9)[1]).cuda().reshape(-1)
+    mine = torch.zeros(ffn * 4 + out * 4 + 64, dtype=torch.uint8, device="cuda")
+    absent = torch.zeros_like(mine)  # stands in for the peer's mapped buffers
+    hq_off, y_off, c_off = 0, ffn * 4, ffn * 4 + out * 4
+    arr = lambda off: (C.c_void_p * 2)(mine.data_ptr() + off, absent.data_ptr() + off)
+    work = torch.zeros(lib.rc_ffn_decode_work_bytes(half), dtype=torch.uint8, device="cuda")
+    rc = lib.rc_ffn_decode(torch.cuda.current_stream().cuda_stream, tg, td, gate.data.data_ptr(), up.data.data_ptr(),
+                           down.data.data_ptr(), xd.data_ptr(), hidden, half, ffn, 0, out // 2, out, 0, 2, 0,
+                           arr(hq_off), arr(y_off), arr(c_off), work.data_ptr())
+    assert rc == 0, lib.rc_error_string(rc)
+    torch.cuda.synchronize()
+    st = _status(lib, clear=True)
+    assert (st >> 20) & 0xF == 2, hex(st)      # the wait for the peers' share of the intermediate
+    assert _status(lib) == 0
+    ctr = mine[c_off:c_off + 16].view(torch.int64)
+    assert int(ctr[0]) == half                 # its own values did arrive, here and at the "peer"
+    assert int(absent[c_off:c_off + 16].view(torch.int64)[0]) == half
+    assert float((torch.ones(4, device="cuda") * 3).sum()) == 12.0

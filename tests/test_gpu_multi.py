@@ -78,6 +78,38 @@ def _worker(rank: int, world: int, port: int, q):
         assert lib.rc_device_status(__import__("ctypes").byref(st)) == 0 and st.value == 0
         gg.close()
         ga.close()
+        # the decode FFN as one cooperative launch per GPU: gate/up rows and down rows sharded, the f32 intermediate
+        # and the output rows stored straight into the peer's memory; every rank ends with the whole output, the two
+        # ranks' copies bit-equal, and equal to the one-GPU launch chain within f32 association
+        tg, td, hidden, ffn, out = ro.Q4_K, ro.Q6_K, 1024, 2048, 640
+        raw_g, raw_u = (cases.synth_case(tg, hidden, ffn, 1, seed=s)[0] for s in (61, 62))
+        raw_d = cases.synth_case(td, ffn, out, 1, seed=63)[0]
+        full = [rt.GpuMatvecTensor.from_bytes_matvec(r, ty, i, o) for r, ty, i, o in
+                ((raw_g, tg, hidden, ffn), (raw_u, tg, hidden, ffn), (raw_d, td, ffn, out))]
+        pg, ng = sh.shard_raw_rows(raw_g, tg, hidden, ffn, rank, world)
+        pu, _ = sh.shard_raw_rows(raw_u, tg, hidden, ffn, rank, world)
+        pd, nd = sh.shard_raw_rows(raw_d, td, ffn, out, rank, world)
+        f0, _ = sh.row_shard_range(ffn, rank, world)
+        o0, _ = sh.row_shard_range(out, rank, world)
+        fused = rt.FusedFfnDecode(rt.GpuMatvecTensor.from_bytes_matvec(pg, tg, hidden, ng),
+                                  rt.GpuMatvecTensor.from_bytes_matvec(pu, tg, hidden, ng),
+                                  rt.GpuMatvecTensor.from_bytes_matvec(pd, td, ffn, nd), ffn, out, f0, o0)
+        u8 = dict(dtype=torch.uint8, device="cuda")
+        xq2, hq2 = torch.empty((hidden // 32) * 40, **u8), torch.empty((ffn // 32) * 40, **u8)
+        yg, yu, y_chain = (torch.empty(n, device="cuda") for n in (ffn, ffn, out))
+        y_f = torch.empty(out, device="cuda")
+        for rnd in range(4):
+            xd = torch.from_numpy(cases.synth_case(tg, hidden, 8, 1, seed=70 + rnd)[1]).cuda().reshape(-1)
+            rt.launch_ffn_decode(full[0], full[1], full[2], xd, xq2, yg, yu, hq2, y_chain)
+            fused.run(xd)
+            fused.read_y(y_f)
+            torch.cuda.synchronize()
+            assert lib.rc_device_status(__import__("ctypes").byref(st)) == 0 and st.value == 0, hex(st.value)
+            assert ro.rel_l2(y_f.cpu().numpy(), y_chain.cpu().numpy().astype(np.float64)) < 1e-3, rnd
+            both = [torch.empty_like(y_f) for _ in range(world)]
+            dist.all_gather(both, y_f)
+            assert all(torch.equal(both[0], b) for b in both[1:]), f"fused FFN round {rnd}: the ranks' outputs differ"
+        fused.close()
         q.put((rank, "ok"))
     except Exception as e:  # report instead of leaving the peer waiting
         q.put((rank, f"{type(e).__name__}: {e}"))
