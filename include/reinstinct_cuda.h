@@ -414,26 +414,29 @@ int rc_allgather_push_logical(void *stream, const void *const *srcs, size_t byte
  * quantize x, gate and up matvecs, silu(gate) * up, quantize, down matvec), row-sharded over `world` GPUs.
  * This rank holds rows [ffn_begin, ffn_begin + ffn_local) of gate_w and up_w ([ffn_total, in_dim], both of
  * gate_type) and rows [out_begin, out_begin + out_local) of down_w ([out_total, ffn_total], down_type).  It
- * stores its ffn_local values of the intermediate silu(gate) * up, as f32, into every rank's h vector (f32
- * [ffn_total]; every rank then quantizes the whole vector itself, block by block as rc_quantize_q8 does) and
- * its out_local output rows into every rank's y (f32 [out_total]); the launch ends when all out_total rows of
- * this call have arrived in this rank's y.  h_peers, y_peers, ctr_peers: host arrays of `world` device
- * pointers (own buffers included, peers' mapped with rc_ipc_open_handle; h 16-byte aligned); ctr_peers[r]: two
- * 64-bit counters in rank r's memory; work: rc_ffn_decode_work_bytes(ffn_local) bytes of this rank's memory.
- * Counters and work are zeroed ONCE and then belong to this shape: the counters grow by a fixed amount per
- * call.  Same per-block arithmetic as rc_quantize_q8 / rc_matvec / rc_swiglu_q8; a row's partial sums are
- * added in a fixed order that depends on the shapes only, so results repeat bit for bit, and differ from the
- * launch chain's in the last bits where the two split a row differently.  x (16-byte aligned) may be pinned
- * host memory.  in_dim and ffn_total multiples of 1024; format pairs (gate, down): (Q4_K, Q6_K), (Q4_K, Q4_K),
- * (Q5_K, Q6_K), (Q6_K, Q6_K), (Q8_0, Q8_0), (Q4_0, Q4_0), else RC_ERR_BAD_TYPE.  A cooperative launch of one
- * CTA per SM; may be captured in a CUDA graph.  A wait that runs out (a peer that never launched) sets bits
- * 20-23 of rc_device_status and the launch ends. */
+ * stores its ffn_local values of the intermediate silu(gate) * up, as f32, into every rank's intermediate
+ * vector (every rank then quantizes the whole vector itself, block by block as rc_quantize_q8 does) and its
+ * out_local output rows into every rank's arrival vector; the launch ends when all out_total rows of this call
+ * have arrived at this rank and have been copied to y (f32 [out_total]; may be pinned host memory, as may x,
+ * 16-byte aligned).  h_peers, y_peers: host arrays of `world` device pointers (own buffers included, peers'
+ * mapped with rc_ipc_open_handle): h_peers[r] = rank r's f32 [3][ffn_total] (16-byte aligned), y_peers[r] =
+ * rank r's f32 [3][out_total]; work: rc_ffn_decode_work_bytes(ffn_local) bytes of this rank's memory.  Before
+ * the first call, once, every byte of the h and y buffers is set to 0xFF ("not arrived": arrival is read off
+ * the values themselves, no flags or fences; the three copies take turns call by call and a launch refills
+ * the one that the call after the next uses) and work to zero; they then belong to this shape, and every rank makes the same
+ * sequence of calls.  Same per-block arithmetic as rc_quantize_q8 / rc_matvec / rc_swiglu_q8; a row's partial
+ * sums are added in a fixed order that depends on the shapes only, so results repeat bit for bit, and differ
+ * from the launch chain's in the last bits where the two split a row differently.  in_dim and ffn_total
+ * multiples of 1024; format pairs (gate, down): (Q4_K, Q6_K), (Q4_K, Q4_K), (Q5_K, Q6_K), (Q6_K, Q6_K),
+ * (Q8_0, Q8_0), (Q4_0, Q4_0), else RC_ERR_BAD_TYPE.  A cooperative launch of one CTA per SM; may be captured
+ * in a CUDA graph.  A wait that runs out (a peer that never launched) sets bits 20-23 of rc_device_status (2:
+ * the intermediate, 3: the output rows) and the launch ends. */
 size_t rc_ffn_decode_work_bytes(uint32_t ffn_local);
 int rc_ffn_decode(void *stream, int gate_type, int down_type, const void *gate_w, const void *up_w,
-                  const void *down_w, const float *x, uint32_t in_dim, uint32_t ffn_local, uint32_t ffn_total,
-                  uint32_t ffn_begin, uint32_t out_local, uint32_t out_total, uint32_t out_begin,
-                  uint32_t world, uint32_t rank, void *const *h_peers, void *const *y_peers,
-                  void *const *ctr_peers, void *work);
+                  const void *down_w, const float *x, float *y, uint32_t in_dim, uint32_t ffn_local,
+                  uint32_t ffn_total, uint32_t ffn_begin, uint32_t out_local, uint32_t out_total,
+                  uint32_t out_begin, uint32_t world, uint32_t rank, void *const *h_peers,
+                  void *const *y_peers, void *work);
 /* Row-sharded PrefillGemm::matmul_into_raw that gathers its own output: this rank holds weight rows
  * [row_begin, row_begin + out_dim) of an [out_total, in_dim] matrix; the kernel's finished tiles are stored
  * into columns row_begin.. of EVERY rank's [n_rows][out_total] f32 output (y_peers: host array of `world`

@@ -81,8 +81,8 @@ _SIGNATURES = {
     "rc_ipc_close_handle": (_i, [_vp]),
     "rc_allgather_push": (_i, [_vp, _vp, _sz, C.POINTER(_vp), C.POINTER(_vp), _vp, _u32, _u32]),
     "rc_ffn_decode_work_bytes": (_sz, [_u32]),
-    "rc_ffn_decode": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _u32,
-                           C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _vp]),
+    "rc_ffn_decode": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _u32,
+                           C.POINTER(_vp), C.POINTER(_vp), _vp]),
     "rc_peer_barrier": (_i, [_vp, C.POINTER(_vp), _vp, _u32, _u32]),
     "rc_allgather_push_logical": (_i, [_vp, C.POINTER(_vp), _sz, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _u32]),
     "rc_matmul_gather": (_i, [_vp, _i, _vp, _vp, C.POINTER(_vp), _u32, _u32, _u32, _u32, _u32, _u32, _vp, _sz]),

@@ -587,27 +587,28 @@ int rc_matmul_gather(void *stream, int type, const void *w, const float *x, floa
 size_t rc_ffn_decode_work_bytes(uint32_t ffn_local) { return ffn_decode_work_bytes(ffn_local); }
 
 int rc_ffn_decode(void *stream, int gate_type, int down_type, const void *gate_w, const void *up_w, const void *down_w,
-                  const float *x, uint32_t in_dim, uint32_t ffn_local, uint32_t ffn_total, uint32_t ffn_begin,
+                  const float *x, float *y, uint32_t in_dim, uint32_t ffn_local, uint32_t ffn_total, uint32_t ffn_begin,
                   uint32_t out_local, uint32_t out_total, uint32_t out_begin, uint32_t world, uint32_t rank,
-                  void *const *h_peers, void *const *y_peers, void *const *ctr_peers, void *work)
+                  void *const *h_peers, void *const *y_peers, void *work)
 {
     if (world == 0 || world > RC_MAX_PEERS || rank >= world) return RC_ERR_BAD_ARGUMENT;
     if (!fmt_known(gate_type) || !fmt_known(down_type)) return RC_ERR_BAD_TYPE;
-    // whole 1024-wide iterations on both contractions, shard boundaries on BlockQ8 records
-    if (in_dim == 0 || in_dim % 1024u || ffn_total == 0 || ffn_total % 1024u || ffn_local == 0 || ffn_local % 32u || ffn_begin % 32u ||
-        out_local == 0 || (uint64_t)ffn_begin + ffn_local > ffn_total || (uint64_t)out_begin + out_local > out_total)
+    // whole 1024-wide iterations on both contractions
+    if (in_dim == 0 || in_dim % 1024u || ffn_total == 0 || ffn_total % 1024u || ffn_local == 0 || out_local == 0 ||
+        (uint64_t)ffn_begin + ffn_local > ffn_total || (uint64_t)out_begin + out_local > out_total)
         return RC_ERR_BAD_SHAPE;
-    if (!gate_w || !up_w || !down_w || !x || !h_peers || !y_peers || !ctr_peers || !work) return RC_ERR_NULL_POINTER;
-    if (((uintptr_t)gate_w & 15u) || ((uintptr_t)up_w & 15u) || ((uintptr_t)down_w & 15u) || ((uintptr_t)x & 15u) || ((uintptr_t)work & 15u))
+    if (!gate_w || !up_w || !down_w || !x || !y || !h_peers || !y_peers || !work) return RC_ERR_NULL_POINTER;
+    if (((uintptr_t)gate_w & 15u) || ((uintptr_t)up_w & 15u) || ((uintptr_t)down_w & 15u) || ((uintptr_t)x & 15u) || ((uintptr_t)y & 3u) ||
+        ((uintptr_t)work & 15u))
         return RC_ERR_MISALIGNED;
     for (uint32_t r = 0; r < world; r++) {
-        if (!h_peers[r] || !y_peers[r] || !ctr_peers[r]) return RC_ERR_NULL_POINTER;
-        if (((uintptr_t)h_peers[r] & 15u) || ((uintptr_t)y_peers[r] & 3u) || ((uintptr_t)ctr_peers[r] & 7u)) return RC_ERR_MISALIGNED;
+        if (!h_peers[r] || !y_peers[r]) return RC_ERR_NULL_POINTER;
+        if (((uintptr_t)h_peers[r] & 15u) || ((uintptr_t)y_peers[r] & 3u)) return RC_ERR_MISALIGNED;
     }
     int rc = ensure_device_ready();
     if (rc) return rc;
     return launch_ffn_decode(S(stream), gate_type, down_type, gate_w, up_w, down_w, x, in_dim, ffn_local, ffn_total, ffn_begin,
-                             out_local, out_total, out_begin, world, rank, h_peers, y_peers, ctr_peers, work);
+                             out_local, out_total, out_begin, world, rank, h_peers, y_peers, y, work);
 }
 
 int rc_allgather_push(void *stream, const void *src, size_t bytes, void *const *peer_dst,

@@ -35,7 +35,7 @@ int ffn_read_trace(void *out, size_t bytes);
 int launch_ffn_decode(cudaStream_t s, int gate_type, int down_type, const void *gate, const void *up, const void *down, const float *x,
                       uint32_t in_dim, uint32_t ffn_local, uint32_t ffn_total, uint32_t ffn_begin, uint32_t out_local,
                       uint32_t out_total, uint32_t out_begin, uint32_t world, uint32_t rank, void *const *h_peers,
-                      void *const *y_peers, void *const *ctr_peers, void *work);
+                      void *const *y_peers, float *y, void *work);
 
 int launch_mmq_gemm(cudaStream_t s, int type, const void *w, const void *xq, float *y,
                     uint32_t in_dim, uint32_t out_dim, uint32_t p_rows);

@@ -824,71 +824,39 @@ moe_gate_up_swiglu_kernel(const uint8_t *__restrict__ gate_slab, const uint8_t *
 // at ffn_decode_kernel.  Seven launches of 3 to 9 us each become one, with no barrier inside the grid: a gate row and its
 // up row are walked by warps of one CTA.  A wait that runs out records a code (rc_device_status) and the launch ends.
 constexpr unsigned long long kFfnWaitNs = 200ull * 1000 * 1000;
+constexpr uint32_t kFfnEmpty = 0xFFFFFFFFu; // "not arrived yet" in the intermediate and output vectors
 __device__ unsigned int g_ffn_error;
 // measurement aid, off until the first ffn_read_trace(): phase timestamps (globaltimer ns) of CTA 0, and the latest time any
 // CTA passed each mark
 __device__ unsigned long long g_ffn_trace[16];
 __device__ unsigned long long g_ffn_trace_max[16];
+__device__ unsigned long long g_ffn_cta[8][160];
 static uint32_t g_ffn_trace_on = 0;
 
 struct FfnPeers {
-    float *h[RC_MAX_PEERS];                 // rank r's intermediate vector: f32 [ffn_total]
-    float *y[RC_MAX_PEERS];                 // rank r's output: f32 [out_total]
-    unsigned long long *ctr[RC_MAX_PEERS];  // rank r's counters: [0] intermediate values arrived, [1] output rows arrived
+    float *h[RC_MAX_PEERS];  // rank r's intermediate vector, three copies: f32 [3][ffn_total]
+    float *y[RC_MAX_PEERS];  // rank r's arriving output rows, three copies: f32 [3][out_total]
 };
 struct FfnParams {
     const uint8_t *gate, *up, *down;
     const float *x;
-    unsigned long long *sync;  // work: [0] calls done
+    float *y;                  // f32 [out_total]: the finished output of this call (device or pinned host memory)
+    unsigned long long *sync;  // work: [0] calls done, [1] CTAs past their gate and up rows, [2] gate/up rows drawn, over all calls
     uint32_t in_dim, ffn_local, ffn_total, ffn_begin, out_local, out_total, out_begin, world, rank;
     uint32_t ks, ks_gu;        // warps that share a down row / a gate or up row
     uint32_t trace;            // record phase times (debug)
 };
 
-__device__ __forceinline__ unsigned long long ffn_ld_acquire(const unsigned long long *p)
-{
-    unsigned long long v;
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void ffn_red_release(unsigned long long *p, unsigned long long v)
-{
-    asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-// Adds n to counter `which` of every rank: this GPU's own first (its waiters are CTAs of this launch: device scope), then
-// one system-scope fence for all the peers' (their waiters read this CTA's stores across NVLink).
-__device__ __forceinline__ void ffn_post(unsigned long long *const *ctr, uint32_t which, unsigned long long n, uint32_t rank, uint32_t world)
-{
-    asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(ctr[rank] + which), "l"(n) : "memory");
-    if (world > 1u) {
-        asm volatile("fence.acq_rel.sys;" ::: "memory");
-        for (uint32_t r = 0; r < world; r++)
-            if (r != rank) asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(ctr[r] + which), "l"(n) : "memory");
-    }
-}
 __device__ __forceinline__ unsigned long long ffn_ns()
 {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-// thread 0 of every CTA waits until *p >= target; false (and a recorded code) when the limit runs out
-__device__ __forceinline__ bool ffn_wait_ge(const unsigned long long *p, unsigned long long target, unsigned int code)
-{
-    const unsigned long long t0 = ffn_ns();
-    while (ffn_ld_acquire(p) < target) {
-        if (ffn_ns() - t0 > kFfnWaitNs) {
-            atomicExch(&g_ffn_error, code);
-            return false;
-        }
-        __nanosleep(40);
-    }
-    return true;
-}
 __device__ __forceinline__ float ffn_ld_cg(const float *p)
 {
     float v;
-    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
     return v;
 }
 // a 40-byte record written during this launch (by this or another GPU): read through L2, never through the
@@ -978,59 +946,65 @@ template <int FMT> struct RowWalk {
     {
         if (row < n_rows && i0 < i1) fetch(row, i0);
     }
-    // Asks L2 for the 4-bit and high-bit planes of this warp's slices of its next `n_ahead` rows beyond the one in flight.
-    __device__ __forceinline__ void prefetch_l2(uint32_t n_ahead) const
+    // Asks L2 for the 4-bit and high-bit planes of the rows that this CTA walks (whole rows: all their slices are this CTA's;
+    // the rows of one round are consecutive), round by round, up to `budget` bytes, shared by n_pf warps.
+    __device__ __forceinline__ void prefetch_cta_rows(uint32_t pf, uint32_t n_pf, uint32_t budget) const
     {
         constexpr uint32_t aux_w = (FMT == Q8_0) ? 16u : (FMT == Q6_K) ? 8u : (FMT == Q5_K || FMT == Q5_1) ? 4u : 0u;
-        uint32_t r = row;
-        for (uint32_t k = 0; k <= n_ahead && r < n_rows; k++, r += row_stride) {
-            const uint8_t *b0 = p.nib + ((size_t)r * p.nsp + (size_t)i0 * 32u) * 16u;
-            const uint32_t len = (i1 - i0) * 32u * 16u;
-            for (uint32_t o = lane * 128u; o < len; o += 32u * 128u) asm volatile("prefetch.global.L2 [%0];" ::"l"(b0 + o));
+        uint32_t spent = 0;
+        for (uint32_t r0 = blockIdx.x * rows_per_cta; r0 < n_rows && spent < budget; r0 += row_stride) {
+            const uint32_t n = min(rows_per_cta, n_rows - r0);
+            const uint32_t len = n * p.nsp * 16u, len1 = n * p.nsp * aux_w;
+            const uint8_t *b0 = p.nib + (size_t)r0 * p.nsp * 16u;
+            for (uint32_t o = (pf * 32u + lane) * 128u; o < len; o += n_pf * 32u * 128u) asm volatile("prefetch.global.L2 [%0];" ::"l"(b0 + o));
             if (aux_w) {
-                const uint8_t *b1 = p.aux + ((size_t)r * p.nsp + (size_t)i0 * 32u) * aux_w;
-                const uint32_t len1 = (i1 - i0) * 32u * aux_w;
-                for (uint32_t o = lane * 128u; o < len1; o += 32u * 128u) asm volatile("prefetch.global.L2 [%0];" ::"l"(b1 + o));
+                const uint8_t *b1 = p.aux + (size_t)r0 * p.nsp * aux_w;
+                for (uint32_t o = (pf * 32u + lane) * 128u; o < len1; o += n_pf * 32u * 128u) asm volatile("prefetch.global.L2 [%0];" ::"l"(b1 + o));
             }
+            spent += len + len1;
         }
     }
-    // finish(row, live, sum) runs on every lane of every warp once per round of the CTA (sum = the warp's slice of the
-    // row's dot product, the same in all lanes); a round is uniform over the CTA, so finish may synchronize warps.
+    // This warp's slice of row r (its first chunk in flight already) against the staged activations; while the last chunk is
+    // multiplied, the first chunk of row r_next (if r_next < n_rows) goes out.  The same sum in all lanes.
+    __device__ __forceinline__ float walk_row(const XStage &st, uint32_t r, uint32_t r_next)
+    {
+        float acc = 0.0f;
+        for (uint32_t it = i0; it < i1; it += LEN) {
+            if (it + LEN <= i1) {
+#pragma unroll
+                for (int i = 0; i < LEN; i++) {
+                    const uint32_t xi = (it + i) * 32u + lane;
+                    const int4 xl = st.lo[xi], xh = st.hi[xi];
+                    const float2 ds = st.ds[xi];
+                    const int2 is = FmtTraits<FMT>::needs_is ? st.is[xi] : make_int2(0, 0);
+                    int d0, d1;
+                    acc += term<FMT>(cur[i], xl, xh, ds, is, d0, d1);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < LEN; i++) {
+                    if (it + i < i1) {
+                        const uint32_t xi = (it + i) * 32u + lane;
+                        const int4 xl = st.lo[xi], xh = st.hi[xi];
+                        const float2 ds = st.ds[xi];
+                        const int2 is = FmtTraits<FMT>::needs_is ? st.is[xi] : make_int2(0, 0);
+                        int d0, d1;
+                        acc += term<FMT>(cur[i], xl, xh, ds, is, d0, d1);
+                    }
+                }
+            }
+            if (it + LEN < i1) fetch(r, it + LEN);
+            else if (r_next < n_rows) fetch(r_next, i0);
+        }
+        return warp_sum(acc);
+    }
+    // Rows dealt out in fixed order (row, row + row_stride, ...).  finish(row, live, sum) runs on every lane of every warp
+    // once per round of the CTA; a round is uniform over the CTA, so finish may synchronize warps.
     template <typename Finish> __device__ __forceinline__ void run(const XStage &st, Finish finish)
     {
         for (uint32_t r0 = blockIdx.x * rows_per_cta; r0 < n_rows; r0 += row_stride, row += row_stride) {
             const bool live = row < n_rows && i0 < i1;
-            float acc = 0.0f;
-            if (live) {
-                for (uint32_t it = i0; it < i1; it += LEN) {
-                    if (it + LEN <= i1) {
-#pragma unroll
-                        for (int i = 0; i < LEN; i++) {
-                            const uint32_t xi = (it + i) * 32u + lane;
-                            const int4 xl = st.lo[xi], xh = st.hi[xi];
-                            const float2 ds = st.ds[xi];
-                            const int2 is = FmtTraits<FMT>::needs_is ? st.is[xi] : make_int2(0, 0);
-                            int d0, d1;
-                            acc += term<FMT>(cur[i], xl, xh, ds, is, d0, d1);
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < LEN; i++) {
-                            if (it + i < i1) {
-                                const uint32_t xi = (it + i) * 32u + lane;
-                                const int4 xl = st.lo[xi], xh = st.hi[xi];
-                                const float2 ds = st.ds[xi];
-                                const int2 is = FmtTraits<FMT>::needs_is ? st.is[xi] : make_int2(0, 0);
-                                int d0, d1;
-                                acc += term<FMT>(cur[i], xl, xh, ds, is, d0, d1);
-                            }
-                        }
-                    }
-                    if (it + LEN < i1) fetch(row, it + LEN);
-                    else if (row + row_stride < n_rows) fetch(row + row_stride, i0);
-                }
-            }
-            finish(row, live, warp_sum(acc));
+            finish(row, live, live ? walk_row(st, row, row + row_stride) : 0.0f);
         }
     }
 };
@@ -1039,11 +1013,41 @@ template <int FMT> struct RowWalk {
 // work: a warp loads four blocks per instruction (one float4 per lane, eight lanes per block) and all of a warp's loads go
 // out before the first is used.  The sum follows the warp quantizer's butterfly (element i adds v[i] + v[i ^ 16], then
 // ^ 8, 4, 2, 1: lanes ^ 4, 2, 1 of the block's eight, then the lane's own elements ^ 2, ^ 1), so a record equals
-// quantize_q8's bit for bit.  through_l2: the values were written during this launch (by this or another GPU).
-template <int FMT> __device__ __forceinline__ void quantize_stage(const XStage &st, uint32_t n_blocks, const float *src, bool through_l2)
+// quantize_q8's bit for bit.  through_l2: the values are written during this launch (by this or another GPU): they are read
+// with relaxed system-scope loads, which observe them (a polling loop of ld.global.cg was seen to spin on a stale line).
+__device__ __forceinline__ bool ffn_any_empty(const float4 &v)
+{
+    return __float_as_uint(v.x) == kFfnEmpty || __float_as_uint(v.y) == kFfnEmpty || __float_as_uint(v.z) == kFfnEmpty ||
+           __float_as_uint(v.w) == kFfnEmpty;
+}
+// The slow path of a polled read, kept out of line so that the callers' unrolled loops stay in registers.
+__device__ __noinline__ float4 ffn_wait_quad(const float *p, volatile int *ok)
+{
+    const unsigned long long t0 = ffn_ns();
+    uint32_t spins = 0;
+    float4 v;
+    do {
+        __nanosleep(40);
+        asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+        if ((++spins & 15u) == 0 && (!*ok || ffn_ns() - t0 > kFfnWaitNs)) {
+            if (*ok) {
+                atomicExch(&g_ffn_error, 2u);
+                *ok = 0;
+            }
+            break;
+        }
+    } while (ffn_any_empty(v));
+    return v;
+}
+//   warp, n_warps: the calling warp's place among the warps that share the work.
+//   poll: a value that still reads as kFfnEmpty has not arrived: it is read again, until *ok drops or the limit runs out
+//   (then the code is recorded, *ok cleared and whatever is there is used: the caller discards the result).
+template <int FMT>
+__device__ __forceinline__ void quantize_stage(const XStage &st, uint32_t n_blocks, const float *src, bool through_l2, uint32_t warp,
+                                               uint32_t n_warps, bool poll = false, volatile int *ok = nullptr)
 {
     constexpr int kAhead = 6;
-    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const uint32_t lane = threadIdx.x & 31u;
     const uint32_t n_quads = (n_blocks + 3u) >> 2;
     for (uint32_t q0 = warp; q0 < n_quads; q0 += n_warps * kAhead) {
         float4 f[kAhead];
@@ -1054,7 +1058,7 @@ template <int FMT> __device__ __forceinline__ void quantize_stage(const XStage &
             if (q < n_quads && b < n_blocks) {
                 const float *p = src + (size_t)b * 32u + (lane & 7u) * 4u;
                 if (through_l2)
-                    asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(f[a].x), "=f"(f[a].y), "=f"(f[a].z), "=f"(f[a].w) : "l"(p));
+                    asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(f[a].x), "=f"(f[a].y), "=f"(f[a].z), "=f"(f[a].w) : "l"(p));
                 else
                     f[a] = *reinterpret_cast<const float4 *>(p);
             }
@@ -1062,8 +1066,9 @@ template <int FMT> __device__ __forceinline__ void quantize_stage(const XStage &
 #pragma unroll
         for (int a = 0; a < kAhead; a++) {
             const uint32_t q = q0 + a * n_warps, b = q * 4u + (lane >> 3);
-            if (q >= n_quads) break; // uniform over the warp
-            const float4 v = f[a];
+            if (q >= n_quads) continue; // uniform over the warp
+            float4 v = f[a];
+            if (poll && b < n_blocks && ffn_any_empty(v)) v = ffn_wait_quad(src + (size_t)b * 32u + (lane & 7u) * 4u, ok);
             float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
             float s0 = v.x, s1 = v.y, s2 = v.z, s3 = v.w;
 #pragma unroll
@@ -1111,21 +1116,31 @@ __device__ __forceinline__ void ffn_group_sync(uint32_t id, uint32_t n_threads)
 // resident, so CTAs may wait for data that other CTAs and other GPUs produce):
 //   1. every CTA quantizes x into shared memory while its first weights are in flight; warps 0-11 walk gate rows and warps
 //      12-23 the same up rows, so silu(g) * u of a row is formed inside the CTA and stored, as f32, into every rank's
-//      intermediate vector; the CTA then adds its row count to every rank's arrival counter (release, system scope);
-//   2. every CTA waits until its own rank's counter shows all ffn_total values of this call, quantizes the intermediate into
-//      shared memory (records equal to quantize_q8's), and walks its down rows, storing each into every rank's output;
-//   3. CTA 0 waits until all out_total rows of this rank's output have arrived and publishes the call number.
-// Counters only grow: call c waits for c * total, so nothing is reset between launches and a launch's data cannot be
-// mistaken for the next one's.  Every wait gives up after kFfnWaitNs, records a code and lets the kernel run out.
+//      intermediate vector;
+//   2. every CTA reads this rank's whole intermediate vector, reading again what has not arrived, quantizes it into shared
+//      memory (records equal to quantize_q8's), and walks its down rows, storing each into every rank's output vector;
+//   3. CTA 0 reads this rank's whole output vector the same way, copies it to y and publishes the call number.
+// Arrival needs no flag, fence or counter: a vector is filled with kFfnEmpty (a NaN pattern that arithmetic never
+// produces; a producer that meets it stores the canonical NaN) before its values are stored, and a 4-byte store arrives
+// whole.  Each vector exists three times; call c uses copy c % 3 and refills copy (c + 2) % 3, which this rank's CTAs
+// finished reading in call c - 1 and which a peer stores into in its call c + 2, i.e. after it has seen all of this rank's
+// output rows of call c + 1: the end of this launch lies between the refill and those rows, so no fence is needed (with two
+// copies the refill would have to be fenced against this launch's own output rows: a system-scope fence here costs 8 us).
+// Every wait gives up after kFfnWaitNs, records a code and lets the kernel run out.
 constexpr int kFfnWarps = 24;
 constexpr uint32_t kFfnTeam = kFfnWarps / 2;
+
+__device__ __forceinline__ float ffn_boxed(float v)
+{
+    return __float_as_uint(v) == kFfnEmpty ? __uint_as_float(0x7FFFFFFFu) : v;
+}
 
 template <int FG, int FD>
 __global__ void __launch_bounds__(kFfnWarps * 32, 1) ffn_decode_kernel(const FfnParams P, const FfnPeers peers)
 {
     extern __shared__ __align__(16) uint8_t smem[];
     __shared__ float s_part[2][kFfnWarps];
-    __shared__ uint32_t s_count[kFfnWarps];
+    __shared__ uint32_t s_next[2][kFfnTeam];
     __shared__ unsigned long long s_call;
     __shared__ int s_ok;
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
@@ -1135,74 +1150,102 @@ __global__ void __launch_bounds__(kFfnWarps * 32, 1) ffn_decode_kernel(const Ffn
             const unsigned long long t = ffn_ns();
             if (blockIdx.x == 0) g_ffn_trace[k] = t;
             atomicMax(&g_ffn_trace_max[k], t);
+            if (k < 8 && blockIdx.x < 160) g_ffn_cta[k][blockIdx.x] = t;
         }
     };
     mark(0);
+    const unsigned long long call = *reinterpret_cast<volatile unsigned long long *>(P.sync) + 1ull; // written only by the previous launch
+    const uint32_t cur = (uint32_t)(call % 3ull);
     if (threadIdx.x == 0) {
-        s_call = *reinterpret_cast<volatile unsigned long long *>(P.sync) + 1ull; // written only by the previous launch
+        s_call = call;
         s_ok = 1;
     }
     // ---- phase 1
     const XStage stx = carve_stage<FG>(smem, n_sub_x);
-    uint32_t rows_done = 0;
     {
         RowWalk<FG> w1;
         const bool is_up = warp >= kFfnTeam;
         const uint32_t vwarp = warp % kFfnTeam, ks = P.ks_gu;
         w1.init(planes_of<FG>(is_up ? P.up : P.gate, P.in_dim, P.ffn_local), n_sub_x, P.ffn_local, ks, vwarp, kFfnTeam);
         w1.prime();
-        quantize_stage<FG>(stx, n_sub_x, P.x, false);
+        {
+            // refill the copies that the call after the next will use (this rank's CTAs read them last in the previous call)
+            float *const h_fill = peers.h[P.rank] + (size_t)((cur + 2u) % 3u) * P.ffn_total;
+            float *const y_fill = peers.y[P.rank] + (size_t)((cur + 2u) % 3u) * P.out_total;
+            for (uint32_t k = blockIdx.x * blockDim.x + threadIdx.x; k < P.ffn_total; k += gridDim.x * blockDim.x) h_fill[k] = __uint_as_float(kFfnEmpty);
+            for (uint32_t k = blockIdx.x * blockDim.x + threadIdx.x; k < P.out_total; k += gridDim.x * blockDim.x) y_fill[k] = __uint_as_float(kFfnEmpty);
+        }
+        quantize_stage<FG>(stx, n_sub_x, P.x, false, warp, kFfnWarps);
         __syncthreads();
         mark(1);
-        // the 2 * ks warps that hold slices of gate row i and up row i meet at a barrier of their own; the first of them
-        // sums the slices in slice order and forms the row's intermediate value
-        uint32_t buf = 0;
+        // The 2 * ks warps that hold slices of gate row i and up row i meet at a barrier of their own; the first of them
+        // sums the slices in slice order and forms the row's intermediate value.  Rows are dealt out on demand: a group's
+        // first two rows are fixed, every further one is the next of a counter that the group's first lane draws from at the
+        // start of a round and hands to the group at the round's barrier, one round before its first loads go out (SMs do
+        // not all stream equally fast: with fixed shares a tenth of the CTAs ended 5 us after the rest, and every rank
+        // waits for the last value).  A call draws exactly ffn_local numbers, so the counter is never reset.
         const uint32_t group = vwarp / ks, slice = vwarp % ks;
-        w1.run(stx, [&](uint32_t r, bool live, float sum) {
+        const bool leader = !is_up && slice == 0 && lane == 0;
+        const size_t h_off = (size_t)cur * P.ffn_total + P.ffn_begin;
+        const unsigned long long base = (call - 1ull) * (unsigned long long)P.ffn_local;
+        const uint32_t first_drawn = 2u * w1.row_stride;
+        uint32_t buf = 0, r_cur = w1.row, r_next = w1.row + w1.row_stride;
+        while (r_cur < P.ffn_local) {
+            unsigned long long drawn = 0;
+            if (leader) drawn = atomicAdd(P.sync + 2, 1ull);
+            const float sum = w1.walk_row(stx, r_cur, r_next);
             if (lane == 0) s_part[buf][warp] = sum;
+            if (leader) s_next[buf][group] = first_drawn + (uint32_t)(drawn - base);
             ffn_group_sync(1u + group, 64u * ks);
-            if (!is_up && slice == 0 && lane == 0 && live) {
+            if (leader) {
                 float g = s_part[buf][warp], u = s_part[buf][warp + kFfnTeam];
                 for (uint32_t k = 1; k < ks; k++) {
                     g += s_part[buf][warp + k];
                     u += s_part[buf][warp + kFfnTeam + k];
                 }
-                const float h = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u); // swiglu_q8_kernel's expression
-                for (uint32_t k = 0; k < P.world; k++) peers.h[k][P.ffn_begin + r] = h;
-                rows_done++;
+                const float h = ffn_boxed(__fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u)); // swiglu_q8_kernel's expression
+                for (uint32_t k = 0; k < P.world; k++) peers.h[k][h_off + r_cur] = h;
             }
+            r_cur = r_next;
+            r_next = s_next[buf][group];
             buf ^= 1u;
-        });
+        }
     }
-    const unsigned long long call = s_call;
-    if (lane == 0) s_count[warp] = rows_done;
-    __syncthreads(); // every store of this CTA's intermediate values is ordered before thread 0's releases
     mark(2);
-    if (threadIdx.x == 0) {
-        unsigned long long n = 0;
-        for (int k = 0; k < (int)kFfnTeam; k++) n += s_count[k];
-        if (n) ffn_post(peers.ctr, 0, n, P.rank, P.world);
-    }
-    // the down rows' first weights fly, and the following ones are called into L2, across the exchange of the intermediate
+    // the down rows' first weights fly across the exchange of the intermediate
     RowWalk<FD> w3;
     w3.init(planes_of<FD>(P.down, P.ffn_total, P.out_local), n_sub_h, P.out_local, P.ks, warp, kFfnWarps);
     w3.prime();
-    w3.prefetch_l2(2);
+    __syncthreads(); // the shared memory of phase 1 is free
+    if (threadIdx.x == 0) atomicAdd(P.sync + 1, 1ull); // this CTA's gate and up rows are done (monotone: call x CTAs when all are)
     mark(3);
-    if (threadIdx.x == 0) {
-        if (!ffn_wait_ge(peers.ctr[P.rank], call * (unsigned long long)P.ffn_total, 2u)) s_ok = 0;
+    // ---- phase 2: the whole intermediate, quantized per CTA.  Two warps meanwhile call the CTA's down rows into L2 (HBM is
+    // idle during the exchange): a prefetch blocks its warp once the request queues are full, hence warps of their own, and
+    // no more bytes than the exchange gives time for.
+    const XStage sth = carve_stage<FD>(smem, n_sub_h);
+    constexpr uint32_t kPfWarps = 2, kStageWarps = kFfnWarps - kPfWarps;
+    if (warp < kStageWarps) quantize_stage<FD>(sth, n_sub_h, peers.h[P.rank] + (size_t)cur * P.ffn_total, true, warp, kStageWarps, true, &s_ok);
+    else {
+        // (not before every CTA of this GPU has finished its gate and up rows: the prefetch of 148 CTAs fills the memory
+        // system's queues for microseconds, and a CTA still loading weights behind it would hold up every rank)
+        const unsigned long long t0 = ffn_ns(), want = call * (unsigned long long)gridDim.x;
+        bool go = true;
+        while (*reinterpret_cast<volatile unsigned long long *>(P.sync + 1) < want) {
+            if (ffn_ns() - t0 > kFfnWaitNs) {
+                go = false;
+                break;
+            }
+            __nanosleep(100);
+        }
+        if (go) w3.prefetch_cta_rows(warp - kStageWarps, kPfWarps, 224u * 1024u);
     }
     __syncthreads();
     mark(4);
-    // ---- phase 2: the whole intermediate, quantized per CTA (read through L2: it was written during this launch)
-    const XStage sth = carve_stage<FD>(smem, n_sub_h);
-    if (s_ok) quantize_stage<FD>(sth, n_sub_h, peers.h[P.rank], true);
-    __syncthreads();
-    mark(5);
-    rows_done = 0;
-    if (s_ok) {
+    const bool ok = s_ok != 0;
+    if (ok) {
         uint32_t buf = 0;
         const uint32_t ks = P.ks, slice = warp % ks;
+        const size_t y_off = (size_t)cur * P.out_total + P.out_begin;
         w3.run(sth, [&](uint32_t r, bool live, float sum) {
             float v = sum;
             if (ks > 1u) {
@@ -1215,23 +1258,39 @@ __global__ void __launch_bounds__(kFfnWarps * 32, 1) ffn_decode_kernel(const Ffn
                 buf ^= 1u;
             }
             if (slice == 0 && lane == 0 && live) {
-                for (uint32_t k = 0; k < P.world; k++) peers.y[k][P.out_begin + r] = v;
-                rows_done++;
+                v = ffn_boxed(v);
+                for (uint32_t k = 0; k < P.world; k++) peers.y[k][y_off + r] = v;
             }
         });
     }
-    // one arrival per CTA: the rows its warps wrote
-    if (lane == 0) s_count[warp] = rows_done;
-    __syncthreads();
-    mark(6);
-    if (threadIdx.x == 0) {
-        unsigned long long n = 0;
-        for (int k = 0; k < kFfnWarps; k++) n += s_count[k];
-        if (n) ffn_post(peers.ctr, 1, n, P.rank, P.world);
-        if (blockIdx.x == 0) {
-            if (s_ok) ffn_wait_ge(peers.ctr[P.rank] + 1, call * (unsigned long long)P.out_total, 3u);
+    mark(5);
+    // ---- phase 3
+    if (blockIdx.x == 0) {
+        __syncthreads();
+        if (ok) {
+            const float *src = peers.y[P.rank] + (size_t)cur * P.out_total;
+            const unsigned long long t0 = ffn_ns();
+            for (uint32_t i = threadIdx.x; i < P.out_total; i += blockDim.x) {
+                float v = ffn_ld_cg(src + i);
+                uint32_t spins = 0;
+                while (__float_as_uint(v) == kFfnEmpty) {
+                    if ((++spins & 15u) == 0 && (!*(volatile int *)&s_ok || ffn_ns() - t0 > kFfnWaitNs)) {
+                        if (*(volatile int *)&s_ok) {
+                            atomicExch(&g_ffn_error, 3u);
+                            s_ok = 0;
+                        }
+                        break;
+                    }
+                    __nanosleep(100);
+                    v = ffn_ld_cg(src + i);
+                }
+                P.y[i] = v;
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
             *reinterpret_cast<volatile unsigned long long *>(P.sync) = call; // the next launch's call number follows
-            mark(7);
+            mark(6);
         }
     }
 }
@@ -1256,6 +1315,8 @@ static uint32_t ffn_pick_ks(uint32_t rows, uint32_t n_iters, uint32_t len, uint3
     return best;
 }
 
+int g_ffn_plain_launch = 0; // measurement: the fused decode FFN as an ordinary launch
+
 template <int FG, int FD>
 int launch_ffn(cudaStream_t s, const FfnParams &P, const FfnPeers &peers)
 {
@@ -1275,6 +1336,10 @@ int launch_ffn(cudaStream_t s, const FfnParams &P, const FfnPeers &peers)
     Q.trace = g_ffn_trace_on;
     FfnPeers pp = peers;
     void *args[] = {&Q, &pp};
+    if (g_ffn_plain_launch) {
+        ffn_decode_kernel<FG, FD><<<grid, kFfnWarps * 32, smem, s>>>(Q, pp);
+        return (int)cudaGetLastError();
+    }
     return (int)cudaLaunchCooperativeKernel((const void *)ffn_decode_kernel<FG, FD>, dim3(grid), dim3(kFfnWarps * 32), args, smem, s);
 }
 
@@ -1629,6 +1694,7 @@ void matvec_set_tuning(int ks, int grid_mult, int no_pdl)
     g_tune.grid_mult = grid_mult;
     g_tune.no_pdl = no_pdl & 1;
     g_tune.no_rows_kernel = (no_pdl >> 1) & 1;
+    g_ffn_plain_launch = (no_pdl >> 2) & 1;
 }
 bool matvec_pdl_enabled() { return !g_tune.no_pdl; }
 
@@ -1668,6 +1734,7 @@ int ffn_read_trace(void *out, size_t bytes)
     if (e != cudaSuccess) return (int)e;
     const unsigned long long zeros[16] = {0};
     e = cudaMemcpyToSymbol(g_ffn_trace_max, zeros, sizeof(zeros));
+    if (bytes >= sizeof(buf) + sizeof(g_ffn_cta)) cudaMemcpyFromSymbol((char *)out + sizeof(buf), g_ffn_cta, sizeof(g_ffn_cta));
     g_ffn_trace_on = 1;
     memcpy(out, buf, bytes < sizeof(buf) ? bytes : sizeof(buf));
     return (int)e;
@@ -1686,13 +1753,14 @@ int ffn_device_error(unsigned int *out, bool clear)
 int launch_ffn_decode(cudaStream_t s, int gate_type, int down_type, const void *gate, const void *up, const void *down, const float *x,
                       uint32_t in_dim, uint32_t ffn_local, uint32_t ffn_total, uint32_t ffn_begin, uint32_t out_local,
                       uint32_t out_total, uint32_t out_begin, uint32_t world, uint32_t rank, void *const *h_peers,
-                      void *const *y_peers, void *const *ctr_peers, void *work)
+                      void *const *y_peers, float *y, void *work)
 {
     FfnParams P;
     P.gate = (const uint8_t *)gate;
     P.up = (const uint8_t *)up;
     P.down = (const uint8_t *)down;
     P.x = x;
+    P.y = y;
     P.sync = reinterpret_cast<unsigned long long *>(work);
     P.in_dim = in_dim;
     P.ffn_local = ffn_local;
@@ -1710,7 +1778,6 @@ int launch_ffn_decode(cudaStream_t s, int gate_type, int down_type, const void *
     for (uint32_t r = 0; r < RC_MAX_PEERS; r++) {
         peers.h[r] = r < world ? (float *)h_peers[r] : nullptr;
         peers.y[r] = r < world ? (float *)y_peers[r] : nullptr;
-        peers.ctr[r] = r < world ? (unsigned long long *)ctr_peers[r] : nullptr;
     }
 #define RC_FFN(G, D) \
     if (gate_type == G && down_type == D) return launch_ffn<G, D>(s, P, peers);

@@ -489,56 +489,60 @@ class FusedFfnDecode:
     """step_swiglu_ffn (src/runtime/qwen35.rs:2694-2707) as ONE cooperative launch per GPU (rc_ffn_decode), row-sharded
     over the ranks of `group` (or a single GPU when torch.distributed is not initialised): this rank's `gate` and `up`
     hold rows [ffn_begin, ffn_begin + gate.out_dim) of the [ffn_total, in_dim] projections, `down` rows
-    [out_begin, out_begin + down.out_dim) of [out_total, ffn_total].  After run(x) — on the stream — this rank's
-    `y_ptr` holds all out_total outputs and `h_ptr` the whole f32 intermediate silu(gate) * up.  Buffers, counters and the
-    work area belong to this object (one per layer shape)."""
+    [out_begin, out_begin + down.out_dim) of [out_total, ffn_total].  After run(x) — on the stream — `self.y` (or the
+    tensor given to run) holds all out_total outputs.  The exchange buffers and the work area belong to this object
+    (one per layer shape); every rank makes the same sequence of run() calls."""
 
     def __init__(self, gate: GpuMatvecTensor, up: GpuMatvecTensor, down: GpuMatvecTensor, ffn_total: int, out_total: int,
                  ffn_begin: int = 0, out_begin: int = 0, group=None, device="cuda"):
         import torch.distributed as dist
 
         lib = _lib.load()
-        self.lib, self.gate, self.up, self.down = lib, gate, up, down
+        self.lib, self.gate, self.up, self.down, self.group = lib, gate, up, down, group
         self.ffn_total, self.out_total, self.ffn_begin, self.out_begin = ffn_total, out_total, ffn_begin, out_begin
-        h_bytes = (ffn_total * 4 + 255) // 256 * 256
-        y_bytes = (out_total * 4 + 255) // 256 * 256
-        self._h_off, self._y_off, self._ctr_off = 0, h_bytes, h_bytes + y_bytes
-        total = h_bytes + y_bytes + 256
-        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        h_bytes = (3 * ffn_total * 4 + 255) // 256 * 256
+        total = h_bytes + (3 * out_total * 4 + 255) // 256 * 256
+        self._h_off, self._y_off = 0, h_bytes
+        multi = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        if multi:
             self.peers = PeerBuffers(total, 1, group)
             self.rank, self.world = self.peers.rank, self.peers.world
             bases = [self.peers.ptrs[0][r] for r in range(self.world)]
             self._local = None
         else:
             self.peers, self.rank, self.world = None, 0, 1
-            self._local = torch.zeros(total, dtype=torch.uint8, device=device)
+            self._local = torch.empty(total, dtype=torch.uint8, device=device)
             bases = [self._local.data_ptr()]
-        self._h = (C.c_void_p * self.world)(*[b + self._h_off for b in bases])
-        self._y = (C.c_void_p * self.world)(*[b + self._y_off for b in bases])
-        self._ctr = (C.c_void_p * self.world)(*[b + self._ctr_off for b in bases])
         own = bases[self.rank]
-        self.h_ptr, self.y_ptr = own + self._h_off, own + self._y_off
+        check(lib.rc_memset_async(own, 0xFF, total, _stream()), "rc_memset_async")  # "not arrived" everywhere
+        torch.cuda.current_stream().synchronize()
+        if multi:
+            dist.barrier(group=group)  # no peer stores before every rank's fill is done
+        self._h = (C.c_void_p * self.world)(*[b + self._h_off for b in bases])
+        self._yp = (C.c_void_p * self.world)(*[b + self._y_off for b in bases])
+        self._own_h = own + self._h_off
+        self.y = torch.empty(out_total, dtype=torch.float32, device=device)
         self.work = torch.zeros(lib.rc_ffn_decode_work_bytes(gate.out_dim), dtype=torch.uint8, device=device)
+        self.calls = 0
 
     def run(self, x, y=None) -> None:
-        """x: f32 [in_dim] on the device or in pinned host memory.  y (single GPU only): a pinned host tensor that
-        receives the output instead of this object's device buffer: the last phase then writes across PCIe itself."""
+        """x: f32 [in_dim] on the device or in pinned host memory.  y: where the finished output goes instead of self.y
+        (a device tensor or a pinned host tensor: the last phase then writes across PCIe itself)."""
         g, d = self.gate, self.down
-        y_arr = self._y
-        if y is not None:
-            assert self.world == 1, "an output override is for the single-GPU call"
-            y_arr = (C.c_void_p * 1)(_ptr(y))
-        check(self.lib.rc_ffn_decode(_stream(), g.dtype, d.dtype, _ptr(g.data), _ptr(self.up.data), _ptr(d.data), _ptr(x), g.in_dim,
-                                     g.out_dim, self.ffn_total, self.ffn_begin, d.out_dim, self.out_total, self.out_begin,
-                                     self.world, self.rank, self._h, y_arr, self._ctr, _ptr(self.work)), "rc_ffn_decode")
+        out = self.y if y is None else y
+        check(self.lib.rc_ffn_decode(_stream(), g.dtype, d.dtype, _ptr(g.data), _ptr(self.up.data), _ptr(d.data), _ptr(x), _ptr(out),
+                                     g.in_dim, g.out_dim, self.ffn_total, self.ffn_begin, d.out_dim, self.out_total, self.out_begin,
+                                     self.world, self.rank, self._h, self._yp, _ptr(self.work)), "rc_ffn_decode")
+        self.calls += 1
 
     def read_y(self, dst: torch.Tensor) -> None:
-        kind = 3 if dst.is_cuda else 2
-        check(self.lib.rc_memcpy_async(dst.data_ptr(), self.y_ptr, self.out_total * 4, kind, _stream()), "rc_memcpy_async")
+        dst.copy_(self.y.reshape(dst.shape), non_blocking=True)
 
     def read_h(self, dst: torch.Tensor) -> None:
+        """The f32 intermediate silu(gate) * up of the last run() (all ffn_total values), on the current stream."""
         kind = 3 if dst.is_cuda else 2
-        check(self.lib.rc_memcpy_async(dst.data_ptr(), self.h_ptr, self.ffn_total * 4, kind, _stream()), "rc_memcpy_async")
+        src = self._own_h + (self.calls % 3) * self.ffn_total * 4
+        check(self.lib.rc_memcpy_async(dst.data_ptr(), src, self.ffn_total * 4, kind, _stream()), "rc_memcpy_async")
 
     def close(self) -> None:
         if self.peers is not None:

@@ -114,20 +114,22 @@ def test_fused_ffn_absent_peer_runs_into_the_bounded_wait(rt):
     up = rt.GpuMatvecTensor.from_bytes_matvec(cases.synth_case(tg, hidden, half, 1, seed=2)[0], tg, hidden, half)
     down = rt.GpuMatvecTensor.from_bytes_matvec(cases.synth_case(td, ffn, out // 2, 1, seed=3)[0], td, ffn, out // 2)
     xd = torch.from_numpy(cases.synth_case(tg, hidden, 8, 1, seed=9)[1]).cuda().reshape(-1)
-    mine = torch.zeros(ffn * 4 + out * 4 + 64, dtype=torch.uint8, device="cuda")
-    absent = torch.zeros_like(mine)  # stands in for the peer's mapped buffers
-    hq_off, y_off, c_off = 0, ffn * 4, ffn * 4 + out * 4
+    mine = torch.full((3 * ffn * 4 + 3 * out * 4,), 0xFF, dtype=torch.uint8, device="cuda")
+    absent = mine.clone()  # stands in for the peer's mapped buffers
+    h_off, y_off = 0, 3 * ffn * 4
     arr = lambda off: (C.c_void_p * 2)(mine.data_ptr() + off, absent.data_ptr() + off)
     work = torch.zeros(lib.rc_ffn_decode_work_bytes(half), dtype=torch.uint8, device="cuda")
+    y = torch.zeros(out, device="cuda")
     rc = lib.rc_ffn_decode(torch.cuda.current_stream().cuda_stream, tg, td, gate.data.data_ptr(), up.data.data_ptr(),
-                           down.data.data_ptr(), xd.data_ptr(), hidden, half, ffn, 0, out // 2, out, 0, 2, 0,
-                           arr(hq_off), arr(y_off), arr(c_off), work.data_ptr())
+                           down.data.data_ptr(), xd.data_ptr(), y.data_ptr(), hidden, half, ffn, 0, out // 2, out, 0, 2, 0,
+                           arr(h_off), arr(y_off), work.data_ptr())
     assert rc == 0, lib.rc_error_string(rc)
     torch.cuda.synchronize()
     st = _status(lib, clear=True)
     assert (st >> 20) & 0xF == 2, hex(st)      # the wait for the peers' share of the intermediate
     assert _status(lib) == 0
-    ctr = mine[c_off:c_off + 16].view(torch.int64)
-    assert int(ctr[0]) == half                 # its own values did arrive, here and at the "peer"
-    assert int(absent[c_off:c_off + 16].view(torch.int64)[0]) == half
+    # its own half of the intermediate did arrive, here and at the "peer" (the first call uses copy 1), the rest did not
+    for buf in (mine, absent):
+        h = buf[h_off:h_off + 3 * ffn * 4].view(torch.int32).reshape(3, ffn)
+        assert bool((h[1, :half] != -1).all()) and bool((h[1, half:] == -1).all())
     assert float((torch.ones(4, device="cuda") * 3).sum()) == 12.0
