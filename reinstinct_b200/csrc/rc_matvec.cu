@@ -1027,7 +1027,7 @@ __device__ __noinline__ float4 ffn_wait_quad(const float *p, volatile int *ok)
     uint32_t spins = 0;
     float4 v;
     do {
-        __nanosleep(40);
+        __nanosleep(100);
         asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
         if ((++spins & 15u) == 0 && (!*ok || ffn_ns() - t0 > kFfnWaitNs)) {
             if (*ok) {
@@ -1217,7 +1217,22 @@ __global__ void __launch_bounds__(kFfnWarps * 32, 1) ffn_decode_kernel(const Ffn
     w3.init(planes_of<FD>(P.down, P.ffn_total, P.out_local), n_sub_h, P.out_local, P.ks, warp, kFfnWarps);
     w3.prime();
     __syncthreads(); // the shared memory of phase 1 is free
-    if (threadIdx.x == 0) atomicAdd(P.sync + 1, 1ull); // this CTA's gate and up rows are done (monotone: call x CTAs when all are)
+    // This CTA's gate and up rows are done; thread 0 waits until those of every CTA of this GPU are (a monotone count: call x
+    // CTAs), which is about when the other ranks' are.  Only then does the CTA poll the intermediate and prefetch: 148 CTAs
+    // polling or prefetching crowd the loads of a CTA that still walks its rows, and every rank waits for the last value.
+    if (threadIdx.x == 0) {
+        atomicAdd(P.sync + 1, 1ull);
+        const unsigned long long t0 = ffn_ns(), want = call * (unsigned long long)gridDim.x;
+        while (*reinterpret_cast<volatile unsigned long long *>(P.sync + 1) < want) {
+            if (ffn_ns() - t0 > kFfnWaitNs) {
+                atomicExch(&g_ffn_error, 1u);
+                s_ok = 0;
+                break;
+            }
+            __nanosleep(100);
+        }
+    }
+    __syncthreads();
     mark(3);
     // ---- phase 2: the whole intermediate, quantized per CTA.  Two warps meanwhile call the CTA's down rows into L2 (HBM is
     // idle during the exchange): a prefetch blocks its warp once the request queues are full, hence warps of their own, and
@@ -1225,20 +1240,7 @@ __global__ void __launch_bounds__(kFfnWarps * 32, 1) ffn_decode_kernel(const Ffn
     const XStage sth = carve_stage<FD>(smem, n_sub_h);
     constexpr uint32_t kPfWarps = 2, kStageWarps = kFfnWarps - kPfWarps;
     if (warp < kStageWarps) quantize_stage<FD>(sth, n_sub_h, peers.h[P.rank] + (size_t)cur * P.ffn_total, true, warp, kStageWarps, true, &s_ok);
-    else {
-        // (not before every CTA of this GPU has finished its gate and up rows: the prefetch of 148 CTAs fills the memory
-        // system's queues for microseconds, and a CTA still loading weights behind it would hold up every rank)
-        const unsigned long long t0 = ffn_ns(), want = call * (unsigned long long)gridDim.x;
-        bool go = true;
-        while (*reinterpret_cast<volatile unsigned long long *>(P.sync + 1) < want) {
-            if (ffn_ns() - t0 > kFfnWaitNs) {
-                go = false;
-                break;
-            }
-            __nanosleep(100);
-        }
-        if (go) w3.prefetch_cta_rows(warp - kStageWarps, kPfWarps, 224u * 1024u);
-    }
+    else w3.prefetch_cta_rows(warp - kStageWarps, kPfWarps, 224u * 1024u);
     __syncthreads();
     mark(4);
     const bool ok = s_ok != 0;
