@@ -181,6 +181,14 @@ __device__ __forceinline__ unsigned long long xfma2(unsigned long long a, unsign
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
     return d;
 }
+__device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void lds_v4(uint32_t addr, uint4 &q)
+{
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "r"(addr) : "memory");
+}
 __device__ __forceinline__ void sts_f32(uint32_t addr, float v)
 {
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
@@ -230,7 +238,12 @@ template <int FMT> struct SmemX {
     // op_full[S] op_empty[S] raw_full[R] raw_empty[R] tm_full[NB] tm_empty[NB] sup_full[kSupSlots] acc_ready acc_free
     static constexpr uint32_t n_bars = 2 * T::S + 2 * T::R + 2 * T::NB + kSupSlots + 2;
     static constexpr uint32_t misc_off = bar_off + n_bars * 8;
-    static constexpr uint32_t total = misc_off + 16 + 1024; // misc: tmem base, abort flag, the two issuers' progress words
+    // per epilogue warp: 32 tokens x 32 finished columns, rows 144 bytes apart (16-byte accesses without bank conflicts both
+    // ways), for the transposed stores into the peers' outputs
+    static constexpr uint32_t xpose_row = 144, xpose_warp = 32 * xpose_row;
+    static constexpr uint32_t xpose_off = (misc_off + 16 + 15) & ~15u;
+    static constexpr uint32_t total = xpose_off + 4 * xpose_warp + 1024; // misc: tmem base, abort flag, the two issuers' progress words
+    static_assert(total <= 227u * 1024u, "shared memory budget");
 };
 
 struct XParams {
@@ -682,11 +695,36 @@ mmqx_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CU
             // from the tile id, so that nothing but the id stays live through the K loop
             auto store32 = [&](const uint32_t (&v0)[16], const uint32_t (&v1)[16], uint32_t c) {
                 const XTile t = x_tile(P, id, tiles_t);
-                if (tlane >= t.n_valid) return;
                 const uint32_t rowc = t.m0 + c * 32u;
+                if (P.n_y > 1u && P.y_vec4 && rowc + 32u <= P.out_dim) {
+                    // This GPU's output and its peers' (plain stores over NVLink, issued as the tile finishes while other
+                    // tiles compute).  A thread holds 128 contiguous bytes of ITS token, so a warp's store instruction
+                    // would touch 32 rows with 16 bytes each: 16-byte packets on the links.  The warp turns the 32 x 32
+                    // block through shared memory instead: eight lanes then write the 128 bytes of one token, four
+                    // tokens per instruction.
+                    const uint32_t xs = sbase + L::xpose_off + quarter * L::xpose_warp;
+                    __syncwarp();
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        sts_v4(xs + lane * L::xpose_row + 16u * k, v0[4 * k], v0[4 * k + 1], v0[4 * k + 2], v0[4 * k + 3]);
+                        sts_v4(xs + lane * L::xpose_row + 64u + 16u * k, v1[4 * k], v1[4 * k + 1], v1[4 * k + 2], v1[4 * k + 3]);
+                    }
+                    __syncwarp();
+                    const uint32_t piece = lane & 7u;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const uint32_t trow = 4u * j + (lane >> 3), tok = quarter * 32u + trow;
+                        uint4 q;
+                        lds_v4(xs + trow * L::xpose_row + 16u * piece, q);
+                        if (tok < t.n_valid) {
+                            const size_t o = (size_t)(t.tok0 + tok) * P.ld_out + P.col_off + rowc + 4u * piece;
+                            for (uint32_t g = 0; g < P.n_y; g++) *reinterpret_cast<uint4 *>(P.y[g] + o) = q;
+                        }
+                    }
+                    return;
+                }
+                if (tlane >= t.n_valid) return;
                 const size_t off = (size_t)(t.tok0 + tlane) * P.ld_out + P.col_off + rowc;
-                // every copy of the output (one, or this GPU's and its peers': plain stores over NVLink, 128
-                // contiguous bytes per thread and chunk, issued as the tile finishes while other tiles compute)
                 for (uint32_t g = 0; g < P.n_y; g++) {
                     float *dst = P.y[g] + off;
                     if (P.y_vec4 && rowc + 32u <= P.out_dim) {
