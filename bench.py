@@ -500,6 +500,46 @@ def mmq_prefill(rt, synth, torch, dev, timed):
             "tok_per_s_per_layer_gate_only": P / (ms_q * 1e-3)}
 
 
+def run_profile_case(args):
+    """A few launches of ONE kernel on a workload small enough for a multi-pass ncu capture (the launches before the
+    captured one run slowly under ncu, and multi-pass captures save and restore the device memory the kernel writes):
+      mmqx  the exact prefill GEMM: 512 tokens x Q4_K 5120 -> 4736 rows (one wave of 148 tiles; K as in config 4)
+      ffn   the decode FFN of config 2 as one cooperative launch (176 MB of weights per launch, two copies in turn)
+    Prints a short JSON line; no timing claims are made from this mode."""
+    import torch
+
+    from reinstinct_b200 import runtime as rt
+    from reinstinct_b200 import synth
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    rt.init(0)
+    n = 0
+    if args.profile_case == "mmqx":
+        P, rows = 512, 4736
+        w = rt.GpuMatvecTensor.from_bytes_matvec(synth.synth_blocks(Q4_K, HIDDEN, rows, seed=77), Q4_K, HIDDEN, rows, device=dev)
+        x = torch.from_numpy(synth.synth_activations(P, HIDDEN, 78)).to(dev)
+        gemm = rt.PrefillGemm(max_x=P * HIDDEN, device=dev)
+        y = torch.empty((P, rows), dtype=torch.float32, device=dev)
+        for _ in range(3):
+            gemm.matmul_into(y, w, x, P)
+            n += 1
+    else:
+        copies = [[rt.GpuMatvecTensor.from_bytes_matvec(synth.synth_blocks(t, i, o, seed=10 * c + k), t, i, o, device=dev)
+                   for k, (_, t, i, o) in enumerate(LAYER)] for c in range(2)]
+        x = torch.from_numpy(synth.synth_activations(1, HIDDEN, 5)).to(dev).reshape(-1)
+        fused = [rt.FusedFfnDecode(ws[0], ws[1], ws[2], FFN, HIDDEN, device=dev) for ws in copies]
+        for c in range(4):
+            fused[c % 2].run(x)
+            n += 1
+    torch.cuda.synchronize()
+    import ctypes
+
+    st = ctypes.c_uint(0)
+    rt._lib.load().rc_device_status(ctypes.byref(st))
+    print(json.dumps({"profile_case": args.profile_case, "launches": n, "device_status": st.value}), flush=True)
+
+
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -880,9 +920,12 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-mmq", action="store_true", help="leave the prefill GEMM, MoE and small-matvec sections out")
+    ap.add_argument("--profile-case", choices=["mmqx", "ffn"], help="run a few launches of one kernel on a small case (for ncu) and exit")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.profile_case:
+        run_profile_case(args)
     else:
         run_gpu_arm(args)
 
