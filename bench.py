@@ -358,11 +358,11 @@ def small_matvecs(rt, synth, torch, dev, timed):
 
 
 def moe_expert_parallel(rt, synth, torch, dist, dev, timed, rank, world):
-    """Config 5 sharded by experts over the ranks (N > 1): 256 experts split evenly, every rank routes its
-    own 512 / N tokens (top-8), the routed activation rows go to the owner of their expert by NCCL
-    all-to-all (counts first), through the grouped gate+up GEMM there, and the results travel back.  The
-    collectives are host-driven (eager NCCL), so the step is timed eagerly; value = tokens of all ranks per
-    second through this gate+up stage."""
+    """Config 5 sharded by experts over the ranks (N > 1): 256 experts split evenly, every rank routes its own 512 / N
+    tokens (top-8); the routed BlockQ8 rows go to the owner of their expert, through the grouped gate+up GEMM there, and
+    the results travel back.  Reported: the exchange done by the GPUs themselves (runtime.ExpertParallel: peer stores and
+    two peer barriers per step, the whole step replayed from a CUDA graph of two steps).  Beside it: the same step with
+    host-driven NCCL all-to-alls (eager).  value = tokens of all ranks per second through this gate+up stage."""
     from reinstinct_b200 import sharding as sh
 
     E, H, F, NT, K = 256, 2048, 512, 512, 8
@@ -379,8 +379,8 @@ def moe_expert_parallel(rt, synth, torch, dist, dev, timed, rank, world):
     xq = torch.empty(nt * (H // 32) * 40, **u8)
     state = {}
 
-    def step(i):
-        # exact route: the routed rows travel as BlockQ8 records (2.56 KB instead of 8 KB of f32 per entry)
+    def step_host(i):
+        # the routed rows travel as BlockQ8 records (2.56 KB instead of 8 KB of f32 per entry)
         rt.launch_moe_topk(logits, ids, wts, E, K, nt)
         rt.launch_quantize_q8(x, xq, H, nt)
         flat = ids.reshape(-1)
@@ -400,11 +400,44 @@ def moe_expert_parallel(rt, synth, torch, dist, dev, timed, rank, world):
         state["y"] = sh.combine_rows(y_in, plan)
         state["n_in"] = n_in
 
-    reps = 5
-    us = timed(step, reps, 3) / reps * 1e3
+    n_ent = nt * K
+    ep = rt.ExpertParallel(gu, H, 2 * F, cap=n_ent, device=dev)
+    out = torch.empty(n_ent, 2 * F, device=dev)
+
+    def step_dev(i):
+        rt.launch_moe_topk(logits, ids, wts, E, K, nt)
+        rt.launch_quantize_q8(x, xq, H, nt)
+        ep.step(ids.reshape(-1), xq, n_ent, K, out)
+
+    # checked steps: both receive buffers against the host-driven result
+    step_host(0)
+    torch.cuda.synchronize()
+    same = True
+    for i in range(2):
+        step_dev(i)
+        torch.cuda.synchronize()
+        same = same and bool(torch.equal(out, state["y"]))
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i in range(2):
+            step_dev(i)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(2):
+            step_dev(i)
+    reps = 10
+    us = timed(lambda i: g.replay(), reps, 3) / (2 * reps) * 1e3
+    us_host = timed(step_host, 5, 3) / 5 * 1e3
+    ep.close()
     return {"workload": f"config 5 gate+up stage, {E} experts over {world} ranks, {nt} tokens per rank, top-{K}",
             "us_step": us, "tok_per_s": NT / (us * 1e-6), "rows_received_rank0": state.get("n_in"),
-            "collectives": "NCCL all_to_all_single: counts, BlockQ8 rows, expert ids, f32 results (eager, host-driven)"}
+            "exchange": "rc_ep_plan / rc_ep_dispatch / rc_ep_return / rc_ep_collect: BlockQ8 rows and f32 results stored straight "
+                        "into the owner's / the source's memory, two rc_peer_barrier per step, graph replay of two steps",
+            "equals_host_driven_result": same,
+            "us_step_host_driven_nccl": us_host}
 
 
 def mmq_prefill_row_sharded(rt, synth, torch, dist, dev, timed, rank, world):

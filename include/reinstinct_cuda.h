@@ -366,7 +366,8 @@ int rc_moe_act_q8(void *stream, const float *gu, void *out, uint32_t ff, uint32_
 
 /* launch_moe_combine (src/runtime/gemma4.rs:1804-1823); kernel moe_combine_f32
  * (kernels/moe_combine.cpp:16-37): out[t][i] = sum_j weights[t][j] * expert_scale[ids[t][j]] *
- * experts[t][j][i], accumulated in slot order.  expert_scale may be NULL (all ones). */
+ * experts[t][j][i], accumulated in slot order.  expert_scale may be NULL (all ones).  A slot whose id is
+ * negative (a dropped entry: rc_moe_topk writes -1 when no logit of a token is a number) adds nothing. */
 int rc_moe_combine(void *stream, const float *experts, const int32_t *ids, const float *weights,
                    const float *expert_scale, float *out, uint32_t hidden, uint32_t n_used, uint32_t n_tok);
 
@@ -437,6 +438,36 @@ int rc_ffn_decode(void *stream, int gate_type, int down_type, const void *gate_w
                   uint32_t ffn_total, uint32_t ffn_begin, uint32_t out_local, uint32_t out_total,
                   uint32_t out_begin, uint32_t world, uint32_t rank, void *const *h_peers,
                   void *const *y_peers, void *work);
+/* Expert parallelism without the host (no counterpart in the reference, which pipelines layers): the routed rows
+ * of this rank's tokens travel to the rank that owns their expert and the results travel back by plain stores
+ * into peer memory; between the two exchanges the owner runs the reference's own sequence on what it received
+ * (rc_moe_sort, rc_moe_gather_xq with n_used = 1, rc_mmq_gemm_grouped, rc_moe_scatter_rows; launch wrappers at
+ * src/runtime/qwen35.rs:2892-3064).  Shapes are static: every (source, owner) pair has `cap` slots (cap >= the
+ * entries one rank can route, n_tok * n_used), unused slots carry expert id -1, which those kernels skip; so a
+ * step is a fixed launch sequence and can be captured in a CUDA graph.  Expert e belongs to rank e /
+ * experts_per_rank.  Buffers per rank (mapped into every rank with rc_ipc_open_handle; *_peers are host arrays
+ * of `world` device pointers, own buffers included):
+ *   rows  BlockQ8 [2][world * cap][in_dim / 32]   ids  int32 [2][world * cap], every entry -1 before the first step
+ *   ret   f32 [world * cap][dim]
+ * One step on every rank, `buf` alternating 0, 1 from step to step:
+ *   rc_ep_plan      back[e] = owner * cap + (count of earlier entries with that owner), -1 for a dropped id
+ *   rc_ep_dispatch  stores each entry's row and local expert index into slot (this rank, slot) of its owner's
+ *                   buffers `buf`, and marks this rank's OTHER ids buffer unused for the next step
+ *   rc_peer_barrier
+ *   the owner's sort / gather / grouped GEMM / scatter over its world * cap slots of buffer `buf`
+ *   rc_ep_return    stores the result row of every used slot into slot (this rank, slot) of its source's ret
+ *   rc_peer_barrier
+ *   rc_ep_collect   out[e] = ret[back[e]] (zeros for a dropped entry)
+ * The placement depends on the ids only; an entry's result does not depend on where it was placed. */
+int rc_ep_plan(void *stream, const int32_t *ids, uint32_t n_entries, uint32_t experts_per_rank, uint32_t cap,
+               uint32_t world, int32_t *back);
+int rc_ep_dispatch(void *stream, const int32_t *ids, const int32_t *back, const void *xq, uint32_t n_entries,
+                   uint32_t n_used, uint32_t in_dim, uint32_t experts_per_rank, uint32_t cap, uint32_t rank,
+                   uint32_t world, uint32_t buf, void *const *rows_peers, void *const *ids_peers);
+int rc_ep_return(void *stream, const int32_t *ids_in, const float *y_in, uint32_t dim, uint32_t cap,
+                 uint32_t rank, uint32_t world, void *const *ret_peers);
+int rc_ep_collect(void *stream, const int32_t *back, const float *ret, float *out, uint32_t dim,
+                  uint32_t n_entries);
 /* Row-sharded PrefillGemm::matmul_into_raw that gathers its own output: this rank holds weight rows
  * [row_begin, row_begin + out_dim) of an [out_total, in_dim] matrix; the kernel's finished tiles are stored
  * into columns row_begin.. of EVERY rank's [n_rows][out_total] f32 output (y_peers: host array of `world`

@@ -84,6 +84,10 @@ _SIGNATURES = {
     "rc_ffn_decode": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _u32,
                            C.POINTER(_vp), C.POINTER(_vp), _vp]),
     "rc_peer_barrier": (_i, [_vp, C.POINTER(_vp), _vp, _u32, _u32]),
+    "rc_ep_plan": (_i, [_vp, _vp, _u32, _u32, _u32, _u32, _vp]),
+    "rc_ep_dispatch": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _u32, C.POINTER(_vp), C.POINTER(_vp)]),
+    "rc_ep_return": (_i, [_vp, _vp, _vp, _u32, _u32, _u32, _u32, C.POINTER(_vp)]),
+    "rc_ep_collect": (_i, [_vp, _vp, _vp, _vp, _u32, _u32]),
     "rc_allgather_push_logical": (_i, [_vp, C.POINTER(_vp), _sz, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _u32]),
     "rc_matmul_gather": (_i, [_vp, _i, _vp, _vp, C.POINTER(_vp), _u32, _u32, _u32, _u32, _u32, _u32, _vp, _sz]),
     "rc_get_device_count": (_i, [C.POINTER(_i)]),

@@ -611,6 +611,54 @@ int rc_ffn_decode(void *stream, int gate_type, int down_type, const void *gate_w
                              out_local, out_total, out_begin, world, rank, h_peers, y_peers, y, work);
 }
 
+int rc_ep_plan(void *stream, const int32_t *ids, uint32_t n_entries, uint32_t experts_per_rank, uint32_t cap, uint32_t world,
+               int32_t *back)
+{
+    if (world == 0 || world > RC_MAX_PEERS || experts_per_rank == 0 || cap == 0) return RC_ERR_BAD_ARGUMENT;
+    if (n_entries == 0) return RC_OK;
+    if (!ids || !back) return RC_ERR_NULL_POINTER;
+    return launch_ep_plan(S(stream), ids, n_entries, experts_per_rank, cap, world, back);
+}
+
+int rc_ep_dispatch(void *stream, const int32_t *ids, const int32_t *back, const void *xq, uint32_t n_entries, uint32_t n_used,
+                   uint32_t in_dim, uint32_t experts_per_rank, uint32_t cap, uint32_t rank, uint32_t world, uint32_t buf,
+                   void *const *rows_peers, void *const *ids_peers)
+{
+    if (world == 0 || world > RC_MAX_PEERS || rank >= world || experts_per_rank == 0 || cap == 0 || n_used == 0) return RC_ERR_BAD_ARGUMENT;
+    if (in_dim == 0 || in_dim % 32u) return RC_ERR_BAD_SHAPE;
+    if (!rows_peers || !ids_peers || (n_entries && (!ids || !back || !xq))) return RC_ERR_NULL_POINTER;
+    if ((uintptr_t)xq & 7u) return RC_ERR_MISALIGNED;
+    for (uint32_t r = 0; r < world; r++) {
+        if (!rows_peers[r] || !ids_peers[r]) return RC_ERR_NULL_POINTER;
+        if (((uintptr_t)rows_peers[r] & 7u) || ((uintptr_t)ids_peers[r] & 3u)) return RC_ERR_MISALIGNED;
+    }
+    return launch_ep_dispatch(S(stream), ids, back, xq, n_entries, n_used, in_dim / 32u, experts_per_rank, cap, rank, world, buf, rows_peers,
+                              ids_peers);
+}
+
+int rc_ep_return(void *stream, const int32_t *ids_in, const float *y_in, uint32_t dim, uint32_t cap, uint32_t rank, uint32_t world,
+                 void *const *ret_peers)
+{
+    if (world == 0 || world > RC_MAX_PEERS || rank >= world || cap == 0) return RC_ERR_BAD_ARGUMENT;
+    if (dim == 0 || dim % 4u) return RC_ERR_BAD_SHAPE;
+    if (!ids_in || !y_in || !ret_peers) return RC_ERR_NULL_POINTER;
+    if ((uintptr_t)y_in & 15u) return RC_ERR_MISALIGNED;
+    for (uint32_t r = 0; r < world; r++) {
+        if (!ret_peers[r]) return RC_ERR_NULL_POINTER;
+        if ((uintptr_t)ret_peers[r] & 15u) return RC_ERR_MISALIGNED;
+    }
+    return launch_ep_return(S(stream), ids_in, y_in, dim, cap, rank, world, ret_peers);
+}
+
+int rc_ep_collect(void *stream, const int32_t *back, const float *ret, float *out, uint32_t dim, uint32_t n_entries)
+{
+    if (dim == 0 || dim % 4u) return RC_ERR_BAD_SHAPE;
+    if (n_entries == 0) return RC_OK;
+    if (!back || !ret || !out) return RC_ERR_NULL_POINTER;
+    if (((uintptr_t)ret & 15u) || ((uintptr_t)out & 15u)) return RC_ERR_MISALIGNED;
+    return launch_ep_collect(S(stream), back, ret, out, dim, n_entries);
+}
+
 int rc_allgather_push(void *stream, const void *src, size_t bytes, void *const *peer_dst,
                       void *const *peer_flags, void *epoch, uint32_t rank, uint32_t world)
 {

@@ -136,6 +136,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float *__restric
     weights += tok * n_used;
     float acc = 0.0f;
     for (uint32_t j = 0; j < n_used; j++) {
+        if (ids[j] < 0) continue; // a dropped slot (no expert row was ever written for it) adds nothing
         const float s = expert_scale ? __fmul_rn(weights[j], expert_scale[ids[j]]) : weights[j];
         acc = __fmaf_rn(s, experts[(size_t)j * hidden + i], acc);
     }

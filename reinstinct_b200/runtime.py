@@ -549,6 +549,81 @@ class FusedFfnDecode:
             self.peers.close()
 
 
+class ExpertParallel:
+    """Expert parallelism without the host (rc_ep_plan / rc_ep_dispatch / rc_ep_return / rc_ep_collect around the
+    reference's own sort, gather, grouped GEMM and scatter launches, src/runtime/qwen35.rs:2892-3064): this rank owns
+    the `experts.n_expert` experts [rank * n, (rank + 1) * n) of the layer, routes its own tokens, sends each routed
+    BlockQ8 row to the owner of its expert by stores into peer memory and gets the result rows back the same way.
+    `cap` >= the entries one rank routes per step (tokens x n_used).  step() is a fixed sequence of launches on the
+    current stream (two peer barriers inside, no host involvement); the receive buffers alternate, so a captured graph
+    must hold an even number of steps.  Without an initialised process group it runs as a world of one."""
+
+    def __init__(self, experts: "GpuExpertTensor", in_dim: int, out_dim: int, cap: int, group=None, device="cuda"):
+        import torch.distributed as dist
+
+        lib = _lib.load()
+        self.lib, self.experts, self.in_dim, self.out_dim, self.cap, self.group = lib, experts, in_dim, out_dim, cap, group
+        multi = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        self.world = dist.get_world_size(group) if multi else 1
+        self.rank = dist.get_rank(group) if multi else 0
+        self.slots = self.world * cap
+        self.row_bytes = in_dim // 32 * BLOCKQ8_BYTES
+        al = lambda n: (n + 255) // 256 * 256
+        rows_b, ids_b, ret_b = al(2 * self.slots * self.row_bytes), al(2 * self.slots * 4), al(self.slots * out_dim * 4)
+        total = rows_b + ids_b + ret_b
+        if multi:
+            self.peers = PeerBuffers(total, 1, group)
+            bases = [self.peers.ptrs[0][r] for r in range(self.world)]
+            self._local = None
+        else:
+            self.peers = None
+            self._local = torch.empty(total, dtype=torch.uint8, device=device)
+            bases = [self._local.data_ptr()]
+        own = bases[self.rank]
+        check(lib.rc_memset_async(own + rows_b, 0xFF, ids_b, _stream()), "rc_memset_async")  # every slot unused
+        torch.cuda.current_stream().synchronize()
+        if multi:
+            dist.barrier(group=group)
+        arr = lambda off: (C.c_void_p * self.world)(*[b + off for b in bases])
+        self._rows, self._ids, self._ret = arr(0), arr(rows_b), arr(rows_b + ids_b)
+        self._own_rows, self._own_ids, self._own_ret = own, own + rows_b, own + rows_b + ids_b
+        self.moe = MoeGroupedScratch.new(experts.n_expert, self.slots, device=device)
+        self.xg = torch.empty(self.slots * self.row_bytes, dtype=torch.uint8, device=device)
+        self.y_sorted = torch.empty(self.slots, out_dim, dtype=torch.float32, device=device)
+        self.y_in = torch.empty(self.slots, out_dim, dtype=torch.float32, device=device)
+        self.back = torch.empty(cap, dtype=torch.int32, device=device)
+        self.buf = 0
+
+    def step(self, ids: torch.Tensor, xq: torch.Tensor, n_entries: int, n_used: int, out: torch.Tensor) -> None:
+        """ids: int32 [n_entries] global expert ids (entry e belongs to token e // n_used); xq: the tokens' BlockQ8 rows;
+        out: f32 [n_entries, out_dim], entry order."""
+        assert ids.dtype == torch.int32 and n_entries <= self.cap
+        lib, st, b = self.lib, _stream(), self.buf
+        n_local = self.experts.n_expert
+        check(lib.rc_ep_plan(st, _ptr(ids), n_entries, n_local, self.cap, self.world, _ptr(self.back)), "rc_ep_plan")
+        check(lib.rc_ep_dispatch(st, _ptr(ids), _ptr(self.back), _ptr(xq), n_entries, n_used, self.in_dim, n_local, self.cap,
+                                 self.rank, self.world, b, self._rows, self._ids), "rc_ep_dispatch")
+        if self.peers is not None:
+            self.peers.barrier()
+        ids_in = self._own_ids + b * self.slots * 4
+        rows_in = self._own_rows + b * self.slots * self.row_bytes
+        moe = self.moe
+        check(lib.rc_moe_sort(st, ids_in, self.slots, n_local, moe_tile_bn(), _ptr(moe.count), _ptr(moe.cursor), _ptr(moe.expert_off),
+                              _ptr(moe.tile_off), _ptr(moe.perm)), "rc_moe_sort")
+        check(lib.rc_moe_gather_xq(st, rows_in, _ptr(moe.perm), _ptr(self.xg), self.in_dim // 32, 1, self.slots), "rc_moe_gather_xq")
+        launch_moe_grouped_gemm(moe, self.experts, self.xg, self.y_sorted, self.in_dim, self.out_dim, self.slots)
+        launch_moe_scatter_rows(moe, self.y_sorted, self.y_in, self.out_dim, self.slots)
+        check(lib.rc_ep_return(st, ids_in, _ptr(self.y_in), self.out_dim, self.cap, self.rank, self.world, self._ret), "rc_ep_return")
+        if self.peers is not None:
+            self.peers.barrier()
+        check(lib.rc_ep_collect(st, _ptr(self.back), self._own_ret, _ptr(out), self.out_dim, n_entries), "rc_ep_collect")
+        self.buf ^= 1
+
+    def close(self) -> None:
+        if self.peers is not None:
+            self.peers.close()
+
+
 class PeerAllGather:
     """All-gather of one small shard per rank by direct stores into the peers' memory
     (rc_allgather_push).  A call returns, on the stream, once every rank's shard of this call has arrived in

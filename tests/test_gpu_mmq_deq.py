@@ -50,6 +50,35 @@ def test_deq_gemm_matches_oracle(rt, t, bn, in_dim, out_dim, p):
     assert err < EXPECTED < F32_TOL
 
 
+@pytest.mark.parametrize("t,in_dim,out_dim,p", [
+    (ro.Q4_K, 4096, 130, 513),    # 4 ranges of K steps (minima steps included in the last one)
+    (ro.Q6_K, 4096, 130, 513),
+    (ro.Q4_K, 3072, 1300, 512),   # 11 row tiles: 3 ranges, uneven (99 steps over 3)
+    (ro.Q8_0, 3072, 1300, 300),
+])
+def test_deq_gemm_k_split_three_and_four_ways(rt, t, in_dim, out_dim, p):
+    """Few tiles, long K: the opt-in f16 route splits K into up to four ranges and adds the partial sums atomically
+    (y zeroed first).  Parity with the oracle, and with the same call forced to one range (debug bit 64)."""
+    lib = rt._lib.load()
+    raw, x = cases.synth_case(t, in_dim, out_dim, p, seed=11 * t + p)
+    w = rt.GpuMatvecTensor.from_bytes_matvec(raw, t, in_dim, out_dim)
+    xd = torch.from_numpy(x).cuda()
+    want = _oracle(t, raw, x, in_dim, out_dim, p)
+    got = {}
+    for name, kind in (("split", 32), ("one range", 32 | (64 << 20))):
+        lib.rc_tune_mmq(0, kind)
+        try:
+            y = torch.full((p, out_dim), float("nan"), device="cuda")
+            rt.PrefillGemm().matmul_into(y, w, xd, p)
+            torch.cuda.synchronize()
+        finally:
+            lib.rc_tune_mmq(0, 0)
+        assert _status(lib) == 0
+        got[name] = y.cpu().numpy()
+        assert ro.rel_l2(got[name], want) < EXPECTED, name
+    assert ro.rel_l2(got["split"], got["one range"].astype(np.float64)) < 1e-5
+
+
 @pytest.mark.parametrize("t", ro.ALL_TYPES)
 def test_deq_gemm_many_tiles_per_cta(rt, t):
     """More tiles than SMs at the narrow width: the accumulator buffers and both rings wrap many times."""

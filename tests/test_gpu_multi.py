@@ -198,6 +198,30 @@ def _moe_worker(rank: int, world: int, port: int, q):
         got = sh.combine_rows(y_in, plan)
         torch.cuda.synchronize()
         assert torch.equal(got, want), f"expert-parallel result differs: rel {float((got - want).norm() / want.norm()):.3e}"
+
+        # the same layer with the exchange done by the GPUs themselves (peer stores, two peer barriers per step, no
+        # host in the loop), from BlockQ8 rows: equal to the reference's launch sequence on one GPU with all experts,
+        # over both receive buffers
+        xq = torch.empty(n_tok * (hidden // 32) * 40, dtype=torch.uint8, device="cuda")
+        ep = rt.ExpertParallel(et_local, hidden, out_dim, cap=n_ent)
+        for rnd in range(4):
+            x2 = torch.from_numpy(np.random.default_rng(70 + 10 * rnd + rank).standard_normal((n_tok, hidden)).astype(np.float32)).cuda()
+            rt.launch_quantize_q8(x2, xq, hidden, n_tok)
+            moe2 = rt.MoeGroupedScratch.new(n_expert, n_ent)
+            rt.launch_moe_sort(moe2, flat_ids.contiguous(), n_ent)
+            xg = torch.empty(n_ent * (hidden // 32) * 40, dtype=torch.uint8, device="cuda")
+            rt.launch_moe_gather_xq(moe2, xq, xg, hidden // 32, n_used, n_ent)
+            ys = torch.zeros(n_ent, out_dim, device="cuda")
+            rt.launch_moe_grouped_gemm(moe2, et_all, xg, ys, hidden, out_dim, n_ent)
+            want2 = torch.zeros(n_ent, out_dim, device="cuda")
+            rt.launch_moe_scatter_rows(moe2, ys, want2, out_dim, n_ent)
+            got2 = torch.empty(n_ent, out_dim, device="cuda")
+            ep.step(flat_ids.contiguous(), xq, n_ent, n_used, got2)
+            torch.cuda.synchronize()
+            assert torch.equal(got2, want2), f"device-driven expert parallelism, round {rnd}: differs from the one-GPU layer"
+        st = __import__("ctypes").c_uint(0)
+        assert rt._lib.load().rc_device_status(__import__("ctypes").byref(st)) == 0 and st.value == 0, hex(st.value)
+        ep.close()
         q.put((rank, "ok"))
     except Exception as e:  # report instead of leaving the peer waiting
         q.put((rank, f"{type(e).__name__}: {e}"))
