@@ -409,6 +409,34 @@ def moe_expert_parallel(rt, synth, torch, dist, dev, timed, rank, world):
         rt.launch_quantize_q8(x, xq, H, nt)
         ep.step(ids.reshape(-1), xq, n_ent, K, out)
 
+    # the whole layer: the owner also runs SwiGLU + quantize and the down GEMM, rows of the model width come back and
+    # are combined with the routing weights at the source
+    one_d = synth.synth_blocks(Q6_K, F, H * 8, 92)
+    dn = rt.GpuExpertTensor.from_bytes(np.tile(one_d, (n_local + 7) // 8)[: (n_local * one_d.size) // 8], Q6_K, F, H, n_local, device=dev)
+    ep_l = rt.ExpertParallel(gu, H, 2 * F, cap=n_ent, device=dev, down=dn, act=rt.ACT_SWIGLU)
+    per_entry = torch.empty(n_ent, H, device=dev)
+    y_layer = torch.empty(nt, H, device=dev)
+
+    def step_layer(i):
+        rt.launch_moe_topk(logits, ids, wts, E, K, nt)
+        rt.launch_quantize_q8(x, xq, H, nt)
+        ep_l.step(ids.reshape(-1), xq, n_ent, K, per_entry)
+        rt.launch_moe_combine(per_entry, ids, wts, None, y_layer, H, K, nt)
+
+    def graph_of_two(fn):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(2):
+                fn(i)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(2):
+                fn(i)
+        return g
+
     # checked steps: both receive buffers against the host-driven result
     step_host(0)
     torch.cuda.synchronize()
@@ -417,23 +445,19 @@ def moe_expert_parallel(rt, synth, torch, dist, dev, timed, rank, world):
         step_dev(i)
         torch.cuda.synchronize()
         same = same and bool(torch.equal(out, state["y"]))
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        for i in range(2):
-            step_dev(i)
-    torch.cuda.current_stream().wait_stream(side)
-    torch.cuda.synchronize()
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
-        for i in range(2):
-            step_dev(i)
     reps = 10
+    g = graph_of_two(step_dev)
     us = timed(lambda i: g.replay(), reps, 3) / (2 * reps) * 1e3
+    gl = graph_of_two(step_layer)
+    us_layer = timed(lambda i: gl.replay(), reps, 3) / (2 * reps) * 1e3
     us_host = timed(step_host, 5, 3) / 5 * 1e3
     ep.close()
-    return {"workload": f"config 5 gate+up stage, {E} experts over {world} ranks, {nt} tokens per rank, top-{K}",
+    ep_l.close()
+    return {"workload": f"config 5, {E} experts over {world} ranks, {nt} tokens per rank, top-{K}",
+            "us_layer": us_layer, "tok_per_s_layer": NT / (us_layer * 1e-6),
+            "layer": "top-k, quantize, dispatch, [owner: sort, gather, gate_up GEMM, SwiGLU + quantize, down GEMM, scatter], return, combine",
             "us_step": us, "tok_per_s": NT / (us * 1e-6), "rows_received_rank0": state.get("n_in"),
+            "step": "the gate_up stage alone (what the host-driven figure beside it covers)",
             "exchange": "rc_ep_plan / rc_ep_dispatch / rc_ep_return / rc_ep_collect: BlockQ8 rows and f32 results stored straight "
                         "into the owner's / the source's memory, two rc_peer_barrier per step, graph replay of two steps",
             "equals_host_driven_result": same,

@@ -1042,11 +1042,10 @@ __device__ __noinline__ float4 ffn_wait_quad(const float *p, volatile int *ok)
 //   warp, n_warps: the calling warp's place among the warps that share the work.
 //   poll: a value that still reads as kFfnEmpty has not arrived: it is read again, until *ok drops or the limit runs out
 //   (then the code is recorded, *ok cleared and whatever is there is used: the caller discards the result).
-template <int FMT>
+template <int FMT, int kAhead = 6>
 __device__ __forceinline__ void quantize_stage(const XStage &st, uint32_t n_blocks, const float *src, bool through_l2, uint32_t warp,
                                                uint32_t n_warps, bool poll = false, volatile int *ok = nullptr)
 {
-    constexpr int kAhead = 6;
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t n_quads = (n_blocks + 3u) >> 2;
     for (uint32_t q0 = warp; q0 < n_quads; q0 += n_warps * kAhead) {
@@ -1239,7 +1238,8 @@ __global__ void __launch_bounds__(kFfnWarps * 32, 1) ffn_decode_kernel(const Ffn
     // no more bytes than the exchange gives time for.
     const XStage sth = carve_stage<FD>(smem, n_sub_h);
     constexpr uint32_t kPfWarps = 2, kStageWarps = kFfnWarps - kPfWarps;
-    if (warp < kStageWarps) quantize_stage<FD>(sth, n_sub_h, peers.h[P.rank] + (size_t)cur * P.ffn_total, true, warp, kStageWarps, true, &s_ok);
+    // (seven quads in flight per warp: the 136 quads of config 2's intermediate are then one batch for each of the 22 warps)
+    if (warp < kStageWarps) quantize_stage<FD, 7>(sth, n_sub_h, peers.h[P.rank] + (size_t)cur * P.ffn_total, true, warp, kStageWarps, true, &s_ok);
     else w3.prefetch_cta_rows(warp - kStageWarps, kPfWarps, 224u * 1024u);
     __syncthreads();
     mark(4);

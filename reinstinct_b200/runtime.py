@@ -556,13 +556,20 @@ class ExpertParallel:
     BlockQ8 row to the owner of its expert by stores into peer memory and gets the result rows back the same way.
     `cap` >= the entries one rank routes per step (tokens x n_used).  step() is a fixed sequence of launches on the
     current stream (two peer barriers inside, no host involvement); the receive buffers alternate, so a captured graph
-    must hold an even number of steps.  Without an initialised process group it runs as a world of one."""
+    must hold an even number of steps.  Without an initialised process group it runs as a world of one.
+    With `down` (the owner's down-projection experts, [out_dim / 2 -> down.out_dim]) the owner runs the whole expert FFN
+    on what it received — gate_up GEMM, gated activation + quantize, down GEMM (the sequence of the reference's MoE
+    prefill, src/runtime/qwen35.rs:3036-3064 around moe_geglu_q8 / swiglu) — and rows of down.out_dim come back."""
 
-    def __init__(self, experts: "GpuExpertTensor", in_dim: int, out_dim: int, cap: int, group=None, device="cuda"):
+    def __init__(self, experts: "GpuExpertTensor", in_dim: int, out_dim: int, cap: int, group=None, device="cuda",
+                 down: "GpuExpertTensor | None" = None, act: int = ACT_SWIGLU):
         import torch.distributed as dist
 
         lib = _lib.load()
-        self.lib, self.experts, self.in_dim, self.out_dim, self.cap, self.group = lib, experts, in_dim, out_dim, cap, group
+        self.lib, self.experts, self.in_dim, self.cap, self.group = lib, experts, in_dim, cap, group
+        self.down, self.act, self.mid_dim = down, act, out_dim
+        out_dim = down.out_dim if down is not None else out_dim
+        self.out_dim = out_dim
         multi = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
         self.world = dist.get_world_size(group) if multi else 1
         self.rank = dist.get_rank(group) if multi else 0
@@ -589,7 +596,10 @@ class ExpertParallel:
         self._own_rows, self._own_ids, self._own_ret = own, own + rows_b, own + rows_b + ids_b
         self.moe = MoeGroupedScratch.new(experts.n_expert, self.slots, device=device)
         self.xg = torch.empty(self.slots * self.row_bytes, dtype=torch.uint8, device=device)
-        self.y_sorted = torch.empty(self.slots, out_dim, dtype=torch.float32, device=device)
+        self.y_sorted = torch.empty(self.slots, self.mid_dim, dtype=torch.float32, device=device)
+        if down is not None:
+            self.hq = torch.empty(self.slots * (self.mid_dim // 2 // 32) * BLOCKQ8_BYTES, dtype=torch.uint8, device=device)
+            self.y2_sorted = torch.empty(self.slots, out_dim, dtype=torch.float32, device=device)
         self.y_in = torch.empty(self.slots, out_dim, dtype=torch.float32, device=device)
         self.back = torch.empty(cap, dtype=torch.int32, device=device)
         self.buf = 0
@@ -611,8 +621,14 @@ class ExpertParallel:
         check(lib.rc_moe_sort(st, ids_in, self.slots, n_local, moe_tile_bn(), _ptr(moe.count), _ptr(moe.cursor), _ptr(moe.expert_off),
                               _ptr(moe.tile_off), _ptr(moe.perm)), "rc_moe_sort")
         check(lib.rc_moe_gather_xq(st, rows_in, _ptr(moe.perm), _ptr(self.xg), self.in_dim // 32, 1, self.slots), "rc_moe_gather_xq")
-        launch_moe_grouped_gemm(moe, self.experts, self.xg, self.y_sorted, self.in_dim, self.out_dim, self.slots)
-        launch_moe_scatter_rows(moe, self.y_sorted, self.y_in, self.out_dim, self.slots)
+        launch_moe_grouped_gemm(moe, self.experts, self.xg, self.y_sorted, self.in_dim, self.mid_dim, self.slots)
+        if self.down is not None:
+            ff = self.mid_dim // 2
+            launch_moe_act_q8(self.y_sorted, self.hq, ff, self.slots, self.act)
+            launch_moe_grouped_gemm(moe, self.down, self.hq, self.y2_sorted, ff, self.out_dim, self.slots)
+            launch_moe_scatter_rows(moe, self.y2_sorted, self.y_in, self.out_dim, self.slots)
+        else:
+            launch_moe_scatter_rows(moe, self.y_sorted, self.y_in, self.out_dim, self.slots)
         check(lib.rc_ep_return(st, ids_in, _ptr(self.y_in), self.out_dim, self.cap, self.rank, self.world, self._ret), "rc_ep_return")
         if self.peers is not None:
             self.peers.barrier()

@@ -91,3 +91,36 @@ def test_two_steps_replay_from_a_graph(rt):
         torch.cuda.synchronize()
         assert torch.equal(outs[0], want) and torch.equal(outs[1], want), rep
     ep.close()
+
+
+def test_whole_expert_ffn_at_the_owner(rt):
+    """With a down projection the owner runs gate_up GEMM, SwiGLU + quantize and the down GEMM on what it received;
+    rows of the model width come back.  Equal to the same launches on one GPU, bit for bit."""
+    t, td, hidden, ff, n_expert, n_used, n_tok = ro.Q4_K, ro.Q6_K, 512, 256, 8, 2, 40
+    gu = _layer(rt, t, hidden, 2 * ff, n_expert, 700)
+    dn = _layer(rt, td, ff, hidden, n_expert, 800)
+    n_ent = n_tok * n_used
+    ep = rt.ExpertParallel(gu, hidden, 2 * ff, cap=n_ent, down=dn, act=rt.ACT_SWIGLU)
+    rng = np.random.default_rng(5)
+    for rnd in range(2):
+        x = torch.from_numpy(rng.standard_normal((n_tok, hidden)).astype(np.float32)).cuda()
+        xq = torch.empty(n_tok * (hidden // 32) * 40, dtype=torch.uint8, device="cuda")
+        rt.launch_quantize_q8(x, xq, hidden, n_tok)
+        ids = torch.from_numpy(rng.integers(0, n_expert, size=n_ent).astype(np.int32)).cuda()
+        out = torch.empty(n_ent, hidden, device="cuda")
+        ep.step(ids, xq, n_ent, n_used, out)
+        moe = rt.MoeGroupedScratch.new(n_expert, n_ent)
+        rt.launch_moe_sort(moe, ids, n_ent)
+        xg = torch.empty(n_ent * (hidden // 32) * 40, dtype=torch.uint8, device="cuda")
+        rt.launch_moe_gather_xq(moe, xq, xg, hidden // 32, n_used, n_ent)
+        y1 = torch.zeros(n_ent, 2 * ff, device="cuda")
+        rt.launch_moe_grouped_gemm(moe, gu, xg, y1, hidden, 2 * ff, n_ent)
+        hq = torch.empty(n_ent * (ff // 32) * 40, dtype=torch.uint8, device="cuda")
+        rt.launch_moe_act_q8(y1, hq, ff, n_ent, rt.ACT_SWIGLU)
+        y2 = torch.zeros(n_ent, hidden, device="cuda")
+        rt.launch_moe_grouped_gemm(moe, dn, hq, y2, ff, hidden, n_ent)
+        want = torch.zeros(n_ent, hidden, device="cuda")
+        rt.launch_moe_scatter_rows(moe, y2, want, hidden, n_ent)
+        torch.cuda.synchronize()
+        assert torch.equal(out, want), rnd
+    ep.close()
