@@ -720,15 +720,14 @@ def run_gpu_arm(args):
 
     # End-to-end step through the host-side API with HOST buffers.  One GPU: runtime.launch_ffn_decode given the pinned
     # host input and output themselves (the quantizer reads x, the down matvec writes y across PCIe; no copy launches).
-    # N > 1: x is uploaded by a copy node and the gathered output downloaded by another.
+    # N > 1: x is uploaded by a copy node (every CTA reads it) and the launch writes the gathered output into the pinned host y.
     def step_e2e(c: int):
         if world == 1:
             ws = copies[c % n_copies]
             rt.launch_ffn_decode(ws[0], ws[1], ws[2], in_host, xq, y_gate, y_up, hq, yd_host)
         else:
             x_dev.copy_(in_host, non_blocking=True)
-            fused[c % n_copies].run(x_dev)
-            fused[c % n_copies].read_y(yd_host)
+            fused[c % n_copies].run(x_dev, yd_host)  # the last phase writes the gathered output to the host itself
 
     def barrier():
         if world > 1:
@@ -925,7 +924,7 @@ def run_gpu_arm(args):
                     "ms_per_step_max": float(ms_e2e_rounds.max()) / K, "graph_replay": use_graph,
                     "how": ("runtime.launch_ffn_decode with the pinned host input and output as its x and y: the quantizer reads x "
                             "and the down matvec writes y across PCIe" if world == 1 else
-                            "copy node in, fused sharded launch, copy node out of the gathered output"),
+                            "copy node in, fused sharded launch whose last phase writes the gathered output into the pinned host y"),
                     "equals_device_resident_step": e2e_check},
             "gpu_launches": launches_per_step * K * rounds,
             "step": ("one cooperative launch per GPU (rc_ffn_decode)" if use_fused else

@@ -242,8 +242,9 @@ template <int FMT> struct SmemX {
     // ways), for the transposed stores into the peers' outputs
     static constexpr uint32_t xpose_row = 144, xpose_warp = 32 * xpose_row;
     static constexpr uint32_t xpose_off = (misc_off + 16 + 15) & ~15u;
-    static constexpr uint32_t total = xpose_off + 4 * xpose_warp + 1024; // misc: tmem base, abort flag, the two issuers' progress words
-    static_assert(total <= 227u * 1024u, "shared memory budget");
+    static constexpr uint32_t total = misc_off + 16 + 1024; // misc: tmem base, abort flag, the two issuers' progress words
+    static constexpr uint32_t total_gather = xpose_off + 4 * xpose_warp + 1024; // the instantiation that stores into peers
+    static_assert(total_gather <= 227u * 1024u, "shared memory budget");
 };
 
 struct XParams {
@@ -272,7 +273,7 @@ __device__ __forceinline__ XTile x_tile(const XParams &P, uint32_t id, uint32_t 
 __device__ __forceinline__ uint32_t bf16_bits(float v) { return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v)); }
 __device__ __forceinline__ float bf16_val(uint32_t b) { return __uint_as_float(b << 16); }
 
-template <int FMT, bool DUMP, bool PROF = false>
+template <int FMT, bool DUMP, bool PROF = false, bool GATHER = false>
 __global__ void __launch_bounds__(kXThreads, 1)
 mmqx_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap tokmap,
             const __grid_constant__ CUtensorMap dxmap, const XParams P)
@@ -696,7 +697,27 @@ mmqx_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CU
             auto store32 = [&](const uint32_t (&v0)[16], const uint32_t (&v1)[16], uint32_t c) {
                 const XTile t = x_tile(P, id, tiles_t);
                 const uint32_t rowc = t.m0 + c * 32u;
-                if (P.n_y > 1u && P.y_vec4 && rowc + 32u <= P.out_dim) {
+                if constexpr (!GATHER) {
+                    // one output matrix, rows out_dim apart (the instantiation that every plain call runs: the copies
+                    // and the transposed stores below cost the steady-state loop registers and time even when unused)
+                    if (tlane >= t.n_valid) return;
+                    float *dst = P.y[0] + (size_t)(t.tok0 + tlane) * P.out_dim + rowc;
+                    if (P.y_vec4 && rowc + 32u <= P.out_dim) {
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            *reinterpret_cast<uint4 *>(dst + 4 * k) = make_uint4(v0[4 * k], v0[4 * k + 1], v0[4 * k + 2], v0[4 * k + 3]);
+                            *reinterpret_cast<uint4 *>(dst + 16 + 4 * k) = make_uint4(v1[4 * k], v1[4 * k + 1], v1[4 * k + 2], v1[4 * k + 3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 16; k++) {
+                            if (rowc + k < P.out_dim) dst[k] = __uint_as_float(v0[k]);
+                            if (rowc + 16u + k < P.out_dim) dst[16 + k] = __uint_as_float(v1[k]);
+                        }
+                    }
+                    return;
+                }
+                if (P.y_vec4 && rowc + 32u <= P.out_dim) {
                     // This GPU's output and its peers' (plain stores over NVLink, issued as the tile finishes while other
                     // tiles compute).  A thread holds 128 contiguous bytes of ITS token, so a warp's store instruction
                     // would touch 32 rows with 16 bytes each: 16-byte packets on the links.  The warp turns the 32 x 32
@@ -727,18 +748,10 @@ mmqx_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CU
                 const size_t off = (size_t)(t.tok0 + tlane) * P.ld_out + P.col_off + rowc;
                 for (uint32_t g = 0; g < P.n_y; g++) {
                     float *dst = P.y[g] + off;
-                    if (P.y_vec4 && rowc + 32u <= P.out_dim) {
 #pragma unroll
-                        for (int k = 0; k < 4; k++) {
-                            *reinterpret_cast<uint4 *>(dst + 4 * k) = make_uint4(v0[4 * k], v0[4 * k + 1], v0[4 * k + 2], v0[4 * k + 3]);
-                            *reinterpret_cast<uint4 *>(dst + 16 + 4 * k) = make_uint4(v1[4 * k], v1[4 * k + 1], v1[4 * k + 2], v1[4 * k + 3]);
-                        }
-                    } else {
-#pragma unroll
-                        for (int k = 0; k < 16; k++) {
-                            if (rowc + k < P.out_dim) dst[k] = __uint_as_float(v0[k]);
-                            if (rowc + 16u + k < P.out_dim) dst[16 + k] = __uint_as_float(v1[k]);
-                        }
+                    for (int k = 0; k < 16; k++) {
+                        if (rowc + k < P.out_dim) dst[k] = __uint_as_float(v0[k]);
+                        if (rowc + 16u + k < P.out_dim) dst[16 + k] = __uint_as_float(v1[k]);
                     }
                 }
             };
@@ -1078,6 +1091,8 @@ int launch_x(cudaStream_t s, const XParams &P, const void *image)
         if (g_x_prof)
             return (int)launch_pdl(mmqx_kernel<FMT, false, true>, dim3(grid), dim3(kXThreads), SmemX<FMT>::total, s, wmap, tokmap, dxmap, P);
     }
+    if (!DUMP && (P.n_y > 1u || P.ld_out != P.out_dim || P.col_off != 0u))
+        return (int)launch_pdl(mmqx_kernel<FMT, false, false, true>, dim3(grid), dim3(kXThreads), SmemX<FMT>::total_gather, s, wmap, tokmap, dxmap, P);
     return (int)launch_pdl(mmqx_kernel<FMT, DUMP>, dim3(grid), dim3(kXThreads), SmemX<FMT>::total, s, wmap, tokmap, dxmap, P);
 }
 
@@ -1085,6 +1100,7 @@ template <int FMT> int set_attr_x()
 {
     int rc = (int)cudaFuncSetAttribute(mmqx_kernel<FMT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemX<FMT>::total);
     rc |= (int)cudaFuncSetAttribute(mmqx_kernel<FMT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemX<FMT>::total);
+    rc |= (int)cudaFuncSetAttribute(mmqx_kernel<FMT, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemX<FMT>::total_gather);
     if constexpr (FMT == Q4_K || FMT == Q8_0)
         rc |= (int)cudaFuncSetAttribute(mmqx_kernel<FMT, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SmemX<FMT>::total);
     return rc;
