@@ -198,9 +198,12 @@ int rc_debug_read_trace(void *out, size_t bytes);
  * uint64, six counters for each of: token producer, MMA issuer, the two expander groups, the first
  * and the last epilogue warp.  No counterpart in the reference. */
 int rc_debug_read_prof(void *out, size_t bytes);
-/* Measurement aid: the phase timestamps (globaltimer ns) CTA 0 of the latest rc_ffn_decode launch recorded:
- * start, x quantized, gate/up rows done, grid barrier passed, records pushed, records arrived, intermediate
- * staged, down rows done, end.  16 uint64.  No counterpart in the reference. */
+/* Measurement aid: phase timestamps (globaltimer ns) of rc_ffn_decode launches.  The first call switches the
+ * recording on; every call copies out and then clears the maxima.  Layout, uint64: [0, 16) the marks of CTA 0
+ * of the latest launch (0 start, 1 x quantized, 2 first warp past its gate/up rows, 3 every CTA of the GPU
+ * past them, 4 intermediate staged, 5 down rows done, 6 output complete), [16, 32) for each mark the latest
+ * time any CTA passed it since the previous call, then, if `bytes` has room, [32, 32 + 8 * 160) marks 0..7
+ * of every CTA (CTA index fastest).  No counterpart in the reference. */
 int rc_debug_read_ffn_trace(void *out, size_t bytes);
 
 /* ---- int8 MMQ GEMM --------------------------------------------------------------------- */
