@@ -441,6 +441,24 @@ int rc_ffn_decode(void *stream, int gate_type, int down_type, const void *gate_w
                   uint32_t ffn_total, uint32_t ffn_begin, uint32_t out_local, uint32_t out_total,
                   uint32_t out_begin, uint32_t world, uint32_t rank, void *const *h_peers,
                   void *const *y_peers, void *work);
+/* The same step (step_swiglu_ffn, src/runtime/qwen35.rs:2694-2707) as one cooperative launch per GPU with the
+ * down projection sharded along its CONTRACTION: this rank holds rows [b, b + ffn_local) of gate_w and up_w
+ * ([ffn_total, in_dim]) and the matching columns of down_w as a tensor of its own, [out_total][ffn_local]
+ * (ffn_local a whole number of the down format's blocks, so a row's blocks [b / 256, ...) are taken as they
+ * are).  A rank's slice of the intermediate never leaves it; every rank stores its out_total partial sums into
+ * slot `rank` of every rank's partial buffer and adds the `world` slots in rank order into y (f32 [out_total],
+ * may be pinned host memory, as may x, 16-byte aligned).  part_peers: host array of `world` device pointers,
+ * part_peers[r] = rank r's f32 [3][world][out_total], every byte 0xFF before the first call; work:
+ * rc_ffn_decode_tp_work_bytes(ffn_local) bytes of this rank's memory, zeroed once.  One exchange per step
+ * instead of rc_ffn_decode's two, and ffn_local / 32 instead of ffn_total / 32 blocks to quantize per CTA; the
+ * sum over ranks replaces part of a row sum, so results differ from the one-GPU step in the last bits (and
+ * repeat bit for bit).  in_dim a multiple of 1024; format pairs as rc_ffn_decode.  Every rank makes the same
+ * sequence of calls; a wait that runs out sets bits 20-23 of rc_device_status (1: this GPU's own CTAs, 3: the
+ * peers' partial sums) and the launch ends. */
+size_t rc_ffn_decode_tp_work_bytes(uint32_t ffn_local);
+int rc_ffn_decode_tp(void *stream, int gate_type, int down_type, const void *gate_w, const void *up_w,
+                     const void *down_w, const float *x, float *y, uint32_t in_dim, uint32_t ffn_local,
+                     uint32_t out_total, uint32_t world, uint32_t rank, void *const *part_peers, void *work);
 /* Expert parallelism without the host (no counterpart in the reference, which pipelines layers): the routed rows
  * of this rank's tokens travel to the rank that owns their expert and the results travel back by plain stores
  * into peer memory; between the two exchanges the owner runs the reference's own sequence on what it received

@@ -84,6 +84,8 @@ _SIGNATURES = {
     "rc_ffn_decode": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _u32,
                            C.POINTER(_vp), C.POINTER(_vp), _vp]),
     "rc_peer_barrier": (_i, [_vp, C.POINTER(_vp), _vp, _u32, _u32]),
+    "rc_ffn_decode_tp_work_bytes": (_sz, [_u32]),
+    "rc_ffn_decode_tp": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, C.POINTER(_vp), _vp]),
     "rc_ep_plan": (_i, [_vp, _vp, _u32, _u32, _u32, _u32, _vp]),
     "rc_ep_dispatch": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _u32, C.POINTER(_vp), C.POINTER(_vp)]),
     "rc_ep_return": (_i, [_vp, _vp, _vp, _u32, _u32, _u32, _u32, C.POINTER(_vp)]),

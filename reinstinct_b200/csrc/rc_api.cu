@@ -611,6 +611,31 @@ int rc_ffn_decode(void *stream, int gate_type, int down_type, const void *gate_w
                              out_local, out_total, out_begin, world, rank, h_peers, y_peers, y, work);
 }
 
+size_t rc_ffn_decode_tp_work_bytes(uint32_t ffn_local) { return ffn_decode_tp_work_bytes(ffn_local); }
+
+int rc_ffn_decode_tp(void *stream, int gate_type, int down_type, const void *gate_w, const void *up_w, const void *down_w,
+                     const float *x, float *y, uint32_t in_dim, uint32_t ffn_local, uint32_t out_total, uint32_t world,
+                     uint32_t rank, void *const *part_peers, void *work)
+{
+    if (world == 0 || world > RC_MAX_PEERS || rank >= world) return RC_ERR_BAD_ARGUMENT;
+    if (!fmt_known(gate_type) || !fmt_known(down_type)) return RC_ERR_BAD_TYPE;
+    // whole 1024-wide iterations on the first contraction; the slice of the second one in whole blocks of the down format
+    if (in_dim == 0 || in_dim % 1024u || ffn_local == 0 || ffn_local % fmt_block_weights(down_type) || ffn_local % 32u || out_total == 0)
+        return RC_ERR_BAD_SHAPE;
+    if (!gate_w || !up_w || !down_w || !x || !y || !part_peers || !work) return RC_ERR_NULL_POINTER;
+    if (((uintptr_t)gate_w & 15u) || ((uintptr_t)up_w & 15u) || ((uintptr_t)down_w & 15u) || ((uintptr_t)x & 15u) || ((uintptr_t)y & 3u) ||
+        ((uintptr_t)work & 15u))
+        return RC_ERR_MISALIGNED;
+    for (uint32_t r = 0; r < world; r++) {
+        if (!part_peers[r]) return RC_ERR_NULL_POINTER;
+        if ((uintptr_t)part_peers[r] & 3u) return RC_ERR_MISALIGNED;
+    }
+    int rc = ensure_device_ready();
+    if (rc) return rc;
+    return launch_ffn_decode_tp(S(stream), gate_type, down_type, gate_w, up_w, down_w, x, y, in_dim, ffn_local, out_total, world, rank,
+                                part_peers, work);
+}
+
 int rc_ep_plan(void *stream, const int32_t *ids, uint32_t n_entries, uint32_t experts_per_rank, uint32_t cap, uint32_t world,
                int32_t *back)
 {

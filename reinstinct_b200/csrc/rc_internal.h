@@ -32,6 +32,10 @@ int moe_set_attributes();
 size_t ffn_decode_work_bytes(uint32_t ffn_local);
 int ffn_device_error(unsigned int *out, bool clear);
 int ffn_read_trace(void *out, size_t bytes);
+int launch_ffn_decode_tp(cudaStream_t s, int gate_type, int down_type, const void *gate, const void *up, const void *down, const float *x,
+                         float *y, uint32_t in_dim, uint32_t ffn_local, uint32_t out_total, uint32_t world, uint32_t rank,
+                         void *const *part_peers, void *work);
+size_t ffn_decode_tp_work_bytes(uint32_t ffn_local);
 int launch_ep_plan(cudaStream_t s, const int32_t *ids, uint32_t n_entries, uint32_t experts_per_rank, uint32_t cap, uint32_t world,
                    int32_t *back);
 int launch_ep_dispatch(cudaStream_t s, const int32_t *ids, const int32_t *back, const void *xq, uint32_t n_entries, uint32_t n_used,

@@ -906,16 +906,19 @@ __device__ __forceinline__ uint32_t q8_words(float v, uint32_t lane)
 template <int FMT> struct RowWalk {
     static constexpr int LEN = FmtTraits<FMT>::rows_max_len;
     Planes p;
-    uint32_t lane, n_rows, i0, i1, row, row_stride, rows_per_cta;
+    uint32_t lane, n_rows, n_sub, i0, i1, row, row_stride, rows_per_cta;
     bool a4;
     Raw<FMT> cur[LEN];
 
-    __device__ __forceinline__ void init(const Planes &planes, uint32_t n_sub, uint32_t rows, uint32_t ks, uint32_t vwarp, uint32_t vwarps)
+    // n_sub_ need not be a multiple of 32: the last iteration's lanes beyond the row read its last sub-block again, against
+    // staged activations that are zero there (the caller stages zero blocks up to the next multiple of 32).
+    __device__ __forceinline__ void init(const Planes &planes, uint32_t n_sub_, uint32_t rows, uint32_t ks, uint32_t vwarp, uint32_t vwarps)
     {
         p = planes;
         lane = threadIdx.x & 31u;
         n_rows = rows;
-        const uint32_t slice = vwarp % ks, n_iters = n_sub >> 5;
+        n_sub = n_sub_;
+        const uint32_t slice = vwarp % ks, n_iters = (n_sub + 31u) >> 5;
         i0 = slice * n_iters / ks;
         i1 = (slice + 1u) * n_iters / ks;
         rows_per_cta = vwarps / ks;
@@ -925,8 +928,8 @@ template <int FMT> struct RowWalk {
     }
     __device__ __forceinline__ void fetch(uint32_t r, uint32_t it)
     {
-        const GroupPtrs gp = group_ptrs<FMT>(p, r, it * 32u + lane);
-        if (it + LEN <= i1) { // the common, unguarded chunk: its loads issue back to back
+        if (it + LEN <= i1 && (it + LEN) * 32u <= n_sub) { // the common, unguarded chunk: its loads issue back to back
+            const GroupPtrs gp = group_ptrs<FMT>(p, r, it * 32u + lane);
 #pragma unroll
             for (int i = 0; i < LEN; i++) {
                 if (a4) fetch_off<FMT, true>(cur[i], gp, i);
@@ -936,8 +939,9 @@ template <int FMT> struct RowWalk {
 #pragma unroll
             for (int i = 0; i < LEN; i++) {
                 if (it + i < i1) {
-                    if (a4) fetch_off<FMT, true>(cur[i], gp, i);
-                    else fetch_off<FMT, false>(cur[i], gp, i);
+                    const GroupPtrs gp = group_ptrs<FMT>(p, r, min((it + i) * 32u + lane, n_sub - 1u));
+                    if (a4) fetch_off<FMT, true>(cur[i], gp, 0);
+                    else fetch_off<FMT, false>(cur[i], gp, 0);
                 }
             }
         }
@@ -1104,6 +1108,18 @@ __device__ __forceinline__ void quantize_stage(const XStage &st, uint32_t n_bloc
             }
         }
     }
+}
+
+// Zero blocks [n_blocks, next multiple of 32) of staged activations: what RowWalk's lanes beyond a ragged row multiply by.
+template <int FMT> __device__ __forceinline__ void stage_zero_tail(const XStage &st, uint32_t n_blocks)
+{
+    const uint32_t padded = (n_blocks + 31u) & ~31u;
+    XBlock z;
+    z.d = 0.0f;
+    z.xsum = 0.0f;
+    z.lo = z.hi = make_int4(0, 0, 0, 0);
+    z.s_lo = z.s_hi = 0;
+    for (uint32_t b = n_blocks + threadIdx.x; b < padded; b += blockDim.x) stage_block<FMT>(st, b, z);
 }
 
 __device__ __forceinline__ void ffn_group_sync(uint32_t id, uint32_t n_threads)
@@ -1297,6 +1313,195 @@ __global__ void __launch_bounds__(kFfnWarps * 32, 1) ffn_decode_kernel(const Ffn
     }
 }
 
+// The same step with the down projection sharded along its CONTRACTION (the usual tensor-parallel feed-forward: gate and up
+// split by rows, down by the matching columns): a rank's slice of the intermediate never leaves it, and the only exchange
+// is the sum of the ranks' partial outputs.  One CTA of 24 warps per SM, cooperative launch:
+//   1. as in ffn_decode_kernel, but silu(g) * u goes to this GPU's own h vector (work memory);
+//   2. when every CTA of the GPU is past step 1 (a release/acquire count), every CTA quantizes the rank's slice of h into
+//      shared memory (ffn_local / 32 blocks: an eighth of the vector at eight GPUs) and walks ALL out_total rows of its
+//      down slice [out_total][ffn_local]; the rows of a round are consecutive, so one warp per destination stores the
+//      CTA's partial sums of the round into slot (this rank) of that rank's partial buffer in one instruction;
+//   3. every CTA takes a share of the output rows, reads the `world` partial sums of each (reading again what has not
+//      arrived: the buffers carry the "empty" pattern of ffn_decode_kernel and rotate over three copies the same way),
+//      adds them in rank order and writes y.
+// The sum over ranks replaces a single row sum, so results differ from the one-GPU step in the last bits and repeat bit
+// for bit; the BlockQ8 blocks of the intermediate are the one-GPU step's (shards end on block boundaries).
+struct FfnTpPeers {
+    float *part[RC_MAX_PEERS]; // rank r's partial sums: f32 [3][world][out_total]
+};
+struct FfnTpParams {
+    const uint8_t *gate, *up, *down;
+    const float *x;
+    float *y;                  // f32 [out_total]
+    float *h;                  // work: f32 [ffn_local]
+    unsigned long long *sync;  // work: [0] calls done, [1] CTAs past their gate and up rows, [2] gate/up rows drawn, over all calls
+    uint32_t in_dim, ffn_local, out_total, world, rank, ks, ks_gu, trace;
+};
+
+template <int FG, int FD>
+__global__ void __launch_bounds__(kFfnWarps * 32, 1) ffn_tp_kernel(const FfnTpParams P, const FfnTpPeers peers)
+{
+    extern __shared__ __align__(16) uint8_t smem[];
+    __shared__ float s_part[2][kFfnWarps];
+    __shared__ float s_out[2][kFfnWarps];
+    __shared__ float s_sum[kFfnWarps * 32];
+    __shared__ uint32_t s_next[2][kFfnTeam];
+    __shared__ int s_ok;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t n_sub_x = P.in_dim >> 5, n_sub_h = P.ffn_local >> 5;
+    auto mark = [&](int k) {
+        if (P.trace && threadIdx.x == 0) {
+            const unsigned long long t = ffn_ns();
+            if (blockIdx.x == 0) g_ffn_trace[k] = t;
+            atomicMax(&g_ffn_trace_max[k], t);
+            if (k < 8 && blockIdx.x < 160) g_ffn_cta[k][blockIdx.x] = t;
+        }
+    };
+    mark(0);
+    const unsigned long long call = *reinterpret_cast<volatile unsigned long long *>(P.sync) + 1ull; // written only by the previous launch
+    const uint32_t cur = (uint32_t)(call % 3ull);
+    if (threadIdx.x == 0) s_ok = 1;
+    // ---- phase 1
+    const XStage stx = carve_stage<FG>(smem, n_sub_x);
+    {
+        RowWalk<FG> w1;
+        const bool is_up = warp >= kFfnTeam;
+        const uint32_t vwarp = warp % kFfnTeam, ks = P.ks_gu;
+        w1.init(planes_of<FG>(is_up ? P.up : P.gate, P.in_dim, P.ffn_local), n_sub_x, P.ffn_local, ks, vwarp, kFfnTeam);
+        w1.prime();
+        {
+            // refill the copy of the partial buffer that the call after the next will use
+            float *const fill = peers.part[P.rank] + (size_t)((cur + 2u) % 3u) * P.world * P.out_total;
+            const uint32_t n = P.world * P.out_total;
+            for (uint32_t k = blockIdx.x * blockDim.x + threadIdx.x; k < n; k += gridDim.x * blockDim.x) fill[k] = __uint_as_float(kFfnEmpty);
+        }
+        quantize_stage<FG>(stx, n_sub_x, P.x, false, warp, kFfnWarps);
+        __syncthreads();
+        mark(1);
+        const uint32_t group = vwarp / ks, slice = vwarp % ks;
+        const bool leader = !is_up && slice == 0 && lane == 0;
+        const unsigned long long base = (call - 1ull) * (unsigned long long)P.ffn_local;
+        const uint32_t first_drawn = 2u * w1.row_stride;
+        uint32_t buf = 0, r_cur = w1.row, r_next = w1.row + w1.row_stride;
+        while (r_cur < P.ffn_local) {
+            unsigned long long drawn = 0;
+            if (leader) drawn = atomicAdd(P.sync + 2, 1ull);
+            const float sum = w1.walk_row(stx, r_cur, r_next);
+            if (lane == 0) s_part[buf][warp] = sum;
+            if (leader) s_next[buf][group] = first_drawn + (uint32_t)(drawn - base);
+            ffn_group_sync(1u + group, 64u * ks);
+            if (leader) {
+                float g = s_part[buf][warp], u = s_part[buf][warp + kFfnTeam];
+                for (uint32_t k = 1; k < ks; k++) {
+                    g += s_part[buf][warp + k];
+                    u += s_part[buf][warp + kFfnTeam + k];
+                }
+                P.h[r_cur] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u); // swiglu_q8_kernel's expression
+            }
+            r_cur = r_next;
+            r_next = s_next[buf][group];
+            buf ^= 1u;
+        }
+    }
+    mark(2);
+    RowWalk<FD> w3;
+    w3.init(planes_of<FD>(P.down, P.ffn_local, P.out_total), n_sub_h, P.out_total, P.ks, warp, kFfnWarps);
+    w3.prime();
+    __syncthreads(); // this CTA's values of h are written; the shared memory of phase 1 is free
+    if (threadIdx.x == 0) {
+        __threadfence(); // release: the CTA's stores to h (ordered before this thread by the barrier) before the count
+        atomicAdd(P.sync + 1, 1ull);
+        const unsigned long long t0 = ffn_ns(), want = call * (unsigned long long)gridDim.x;
+        while (*reinterpret_cast<volatile unsigned long long *>(P.sync + 1) < want) {
+            if (ffn_ns() - t0 > kFfnWaitNs) {
+                atomicExch(&g_ffn_error, 1u);
+                s_ok = 0;
+                break;
+            }
+            __nanosleep(100);
+        }
+        __threadfence(); // acquire
+    }
+    __syncthreads();
+    mark(3);
+    // ---- phase 2
+    const XStage sth = carve_stage<FD>(smem, (n_sub_h + 31u) & ~31u);
+    constexpr uint32_t kPfWarps = 2, kStageWarps = kFfnWarps - kPfWarps;
+    if (warp < kStageWarps) quantize_stage<FD, 7>(sth, n_sub_h, P.h, true, warp, kStageWarps);
+    else w3.prefetch_cta_rows(warp - kStageWarps, kPfWarps, 224u * 1024u);
+    stage_zero_tail<FD>(sth, n_sub_h);
+    __syncthreads();
+    mark(4);
+    const bool ok = s_ok != 0;
+    if (ok) {
+        uint32_t buf = 0;
+        const uint32_t ks = P.ks, slice = warp % ks, rows_per_cta = kFfnWarps / ks;
+        const size_t slot = ((size_t)cur * P.world + P.rank) * P.out_total;
+        w3.run(sth, [&](uint32_t r, bool live, float sum) {
+            float v = sum;
+            if (ks > 1u) {
+                if (lane == 0) s_part[buf][warp] = sum;
+                ffn_group_sync(1u + warp / ks, 32u * ks);
+                if (slice == 0 && lane == 0) {
+                    v = s_part[buf][warp];
+                    for (uint32_t k = 1; k < ks; k++) v += s_part[buf][warp + k]; // slice order: reproducible
+                }
+            }
+            if (slice == 0 && lane == 0) s_out[buf][warp / ks] = ffn_boxed(v);
+            __syncthreads(); // the round's partial sums are in shared memory (a round is uniform over the CTA)
+            // warp k stores the round's consecutive rows into rank k's buffer: one instruction, one packet on the link
+            const uint32_t r0 = r - warp / ks;
+            for (uint32_t k = warp; k < P.world; k += kFfnWarps)
+                if (lane < rows_per_cta && r0 + lane < P.out_total) peers.part[k][slot + r0 + lane] = s_out[buf][lane];
+            buf ^= 1u;
+        });
+    }
+    mark(5);
+    // ---- phase 3: this CTA's share of the output rows, summed over the ranks in rank order
+    if (ok) {
+        const uint32_t per = (P.out_total + gridDim.x - 1u) / gridDim.x;
+        const uint32_t r_begin = min(blockIdx.x * per, P.out_total), r_end = min(r_begin + per, P.out_total);
+        const uint32_t chunk = (kFfnWarps * 32u) / P.world; // rows whose partial sums fit the staging array
+        const float *src = peers.part[P.rank] + (size_t)cur * P.world * P.out_total;
+        const unsigned long long t0 = ffn_ns();
+        for (uint32_t c0 = r_begin; c0 < r_end; c0 += chunk) {
+            const uint32_t n = min(chunk, r_end - c0);
+            __syncthreads();
+            for (uint32_t i = threadIdx.x; i < n * P.world; i += blockDim.x) {
+                const uint32_t k = i / n, j = i % n;
+                const float *a = src + (size_t)k * P.out_total + c0 + j;
+                float v = ffn_ld_cg(a);
+                uint32_t spins = 0;
+                while (__float_as_uint(v) == kFfnEmpty) {
+                    if ((++spins & 15u) == 0 && (!*(volatile int *)&s_ok || ffn_ns() - t0 > kFfnWaitNs)) {
+                        if (*(volatile int *)&s_ok) {
+                            atomicExch(&g_ffn_error, 3u);
+                            s_ok = 0;
+                        }
+                        break;
+                    }
+                    __nanosleep(100);
+                    v = ffn_ld_cg(a);
+                }
+                s_sum[k * n + j] = v;
+            }
+            __syncthreads();
+            for (uint32_t j = threadIdx.x; j < n; j += blockDim.x) {
+                float v = s_sum[j];
+                for (uint32_t k = 1; k < P.world; k++) v = __fadd_rn(v, s_sum[k * n + j]);
+                P.y[c0 + j] = v;
+            }
+        }
+    }
+    if (blockIdx.x == 0) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            *reinterpret_cast<volatile unsigned long long *>(P.sync) = call; // the next launch's call number follows
+            mark(6);
+        }
+    }
+}
+
 // Warps that share a row: the count, among the powers of two up to the team size, with the least (rounds of the grid) x
 // (dependent load round trips + multiply time per round), the shared-row reduction counted per round.
 static uint32_t ffn_pick_ks(uint32_t rows, uint32_t n_iters, uint32_t len, uint32_t grid, uint32_t team)
@@ -1343,6 +1548,28 @@ int launch_ffn(cudaStream_t s, const FfnParams &P, const FfnPeers &peers)
         return (int)cudaGetLastError();
     }
     return (int)cudaLaunchCooperativeKernel((const void *)ffn_decode_kernel<FG, FD>, dim3(grid), dim3(kFfnWarps * 32), args, smem, s);
+}
+
+template <int FG, int FD>
+int launch_ffn_tp(cudaStream_t s, const FfnTpParams &P, const FfnTpPeers &peers)
+{
+    const uint32_t nx = P.in_dim >> 5, nh = ((P.ffn_local >> 5) + 31u) & ~31u;
+    const size_t smem = (std::max((size_t)nx * FmtTraits<FG>::x_bytes, (size_t)nh * FmtTraits<FD>::x_bytes) + 15u) & ~(size_t)15u;
+    if (smem > kMaxStageBytesHost) return RC_ERR_BAD_SHAPE;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(ffn_tp_kernel<FG, FD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    FfnTpParams Q = P;
+    const uint32_t grid = (uint32_t)sm_count();
+    Q.ks = ffn_pick_ks(P.out_total, nh >> 5, (uint32_t)FmtTraits<FD>::rows_max_len, grid, (uint32_t)kFfnWarps);
+    Q.ks_gu = ffn_pick_ks(P.ffn_local, nx >> 5, (uint32_t)FmtTraits<FG>::rows_max_len, grid, kFfnTeam);
+    Q.trace = g_ffn_trace_on;
+    FfnTpPeers pp = peers;
+    void *args[] = {&Q, &pp};
+    return (int)cudaLaunchCooperativeKernel((const void *)ffn_tp_kernel<FG, FD>, dim3(grid), dim3(kFfnWarps * 32), args, smem, s);
 }
 
 struct Tuning {
@@ -1792,5 +2019,41 @@ int launch_ffn_decode(cudaStream_t s, int gate_type, int down_type, const void *
 #undef RC_FFN
     return RC_ERR_BAD_TYPE;
 }
+
+int launch_ffn_decode_tp(cudaStream_t s, int gate_type, int down_type, const void *gate, const void *up, const void *down, const float *x,
+                         float *y, uint32_t in_dim, uint32_t ffn_local, uint32_t out_total, uint32_t world, uint32_t rank,
+                         void *const *part_peers, void *work)
+{
+    FfnTpParams P;
+    P.gate = (const uint8_t *)gate;
+    P.up = (const uint8_t *)up;
+    P.down = (const uint8_t *)down;
+    P.x = x;
+    P.y = y;
+    P.sync = reinterpret_cast<unsigned long long *>(work);
+    P.h = reinterpret_cast<float *>((uint8_t *)work + 64);
+    P.in_dim = in_dim;
+    P.ffn_local = ffn_local;
+    P.out_total = out_total;
+    P.world = world;
+    P.rank = rank;
+    P.ks = 1;
+    P.ks_gu = 1;
+    P.trace = 0;
+    FfnTpPeers peers;
+    for (uint32_t r = 0; r < RC_MAX_PEERS; r++) peers.part[r] = r < world ? (float *)part_peers[r] : nullptr;
+#define RC_FFN(G, D) \
+    if (gate_type == G && down_type == D) return launch_ffn_tp<G, D>(s, P, peers);
+    RC_FFN(Q4_K, Q6_K)
+    RC_FFN(Q4_K, Q4_K)
+    RC_FFN(Q5_K, Q6_K)
+    RC_FFN(Q6_K, Q6_K)
+    RC_FFN(Q8_0, Q8_0)
+    RC_FFN(Q4_0, Q4_0)
+#undef RC_FFN
+    return RC_ERR_BAD_TYPE;
+}
+
+size_t ffn_decode_tp_work_bytes(uint32_t ffn_local) { return 64 + (size_t)ffn_local * sizeof(float); }
 
 } // namespace rc

@@ -549,6 +549,57 @@ class FusedFfnDecode:
             self.peers.close()
 
 
+class TensorParallelFfnDecode:
+    """step_swiglu_ffn (src/runtime/qwen35.rs:2694-2707) as ONE cooperative launch per GPU with the usual tensor-parallel
+    split (rc_ffn_decode_tp): this rank's `gate` and `up` hold rows [b, b + n) of the [ffn_total, in_dim] projections and
+    `down` the matching COLUMNS of the down projection as a tensor [out_total, n] of its own (sharding.shard_raw_cols).
+    The intermediate stays on the rank; the ranks' partial outputs are summed in rank order.  After run(x) — on the
+    stream — `self.y` (or the tensor given to run) holds all out_total outputs.  The exchange buffer and the work area
+    belong to this object; every rank makes the same sequence of run() calls."""
+
+    def __init__(self, gate: GpuMatvecTensor, up: GpuMatvecTensor, down: GpuMatvecTensor, group=None, device="cuda"):
+        import torch.distributed as dist
+
+        lib = _lib.load()
+        assert down.in_dim == gate.out_dim == up.out_dim, "down must hold the columns that match this rank's gate/up rows"
+        self.lib, self.gate, self.up, self.down, self.group = lib, gate, up, down, group
+        self.out_total = down.out_dim
+        multi = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        world = dist.get_world_size(group) if multi else 1
+        total = (3 * world * self.out_total * 4 + 255) // 256 * 256
+        if multi:
+            self.peers = PeerBuffers(total, 1, group)
+            self.rank, self.world = self.peers.rank, self.peers.world
+            bases = [self.peers.ptrs[0][r] for r in range(self.world)]
+            self._local = None
+        else:
+            self.peers, self.rank, self.world = None, 0, 1
+            self._local = torch.empty(total, dtype=torch.uint8, device=device)
+            bases = [self._local.data_ptr()]
+        check(lib.rc_memset_async(bases[self.rank], 0xFF, total, _stream()), "rc_memset_async")  # "not arrived" everywhere
+        torch.cuda.current_stream().synchronize()
+        if multi:
+            dist.barrier(group=group)  # no peer stores before every rank's fill is done
+        self._part = (C.c_void_p * self.world)(*bases)
+        self.y = torch.empty(self.out_total, dtype=torch.float32, device=device)
+        self.work = torch.zeros(lib.rc_ffn_decode_tp_work_bytes(gate.out_dim), dtype=torch.uint8, device=device)
+
+    def run(self, x, y=None) -> None:
+        """x: f32 [in_dim] on the device or in pinned host memory; y: where the output goes instead of self.y."""
+        g, d = self.gate, self.down
+        out = self.y if y is None else y
+        check(self.lib.rc_ffn_decode_tp(_stream(), g.dtype, d.dtype, _ptr(g.data), _ptr(self.up.data), _ptr(d.data), _ptr(x), _ptr(out),
+                                        g.in_dim, g.out_dim, self.out_total, self.world, self.rank, self._part, _ptr(self.work)),
+              "rc_ffn_decode_tp")
+
+    def read_y(self, dst: torch.Tensor) -> None:
+        dst.copy_(self.y.reshape(dst.shape), non_blocking=True)
+
+    def close(self) -> None:
+        if self.peers is not None:
+            self.peers.close()
+
+
 class ExpertParallel:
     """Expert parallelism without the host (rc_ep_plan / rc_ep_dispatch / rc_ep_return / rc_ep_collect around the
     reference's own sort, gather, grouped GEMM and scatter launches, src/runtime/qwen35.rs:2892-3064): this rank owns

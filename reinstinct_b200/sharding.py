@@ -52,6 +52,31 @@ def shard_raw_rows(raw, dtype: int, in_dim: int, out_dim: int, rank: int, world:
     return raw[b * row_bytes:e * row_bytes], e - b
 
 
+def col_shard_range(in_dim: int, rank: int, world: int, block: int) -> tuple[int, int]:
+    """Columns [begin, end) of rank `rank` when a contraction of in_dim columns is dealt out in whole blocks of `block`
+    columns (the weight format's block: 256 for the K-quants, 32 otherwise), as evenly as possible, the ranks with the
+    larger share last."""
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside world {world}")
+    if in_dim % block:
+        raise ValueError("in_dim is not a whole number of blocks")
+    units = in_dim // block
+    base, extra = divmod(units, world)
+    first_big = world - extra
+    begin = (rank * base + max(0, rank - first_big)) * block
+    end = begin + (base + (1 if rank >= first_big else 0)) * block
+    return begin, end
+
+
+def shard_raw_cols(raw, dtype: int, in_dim: int, out_dim: int, begin: int, end: int) -> np.ndarray:
+    """The on-disk bytes of columns [begin, end) of every row (whole blocks), as a tensor [out_dim][end - begin] of its own."""
+    bw, bb = BLOCK_WEIGHTS[dtype], BLOCK_BYTES[dtype]
+    if begin % bw or end % bw or not 0 <= begin < end <= in_dim:
+        raise ValueError("column range must be whole blocks inside the row")
+    rows = np.asarray(raw, dtype=np.uint8).reshape(-1)[: out_dim * (in_dim // bw) * bb].reshape(out_dim, in_dim // bw, bb)
+    return np.ascontiguousarray(rows[:, begin // bw:end // bw, :]).reshape(-1)
+
+
 def all_gather_rows(y_local: torch.Tensor, out_dim: int, group=None) -> torch.Tensor:
     """[n_rows, out_local] shards (any sizes) -> [n_rows, out_dim] on every rank."""
     world = dist.get_world_size(group)

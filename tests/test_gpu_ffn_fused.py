@@ -133,3 +133,40 @@ def test_fused_ffn_absent_peer_runs_into_the_bounded_wait(rt):
         h = buf[h_off:h_off + 3 * ffn * 4].view(torch.int32).reshape(3, ffn)
         assert bool((h[1, :half] != -1).all()) and bool((h[1, half:] == -1).all())
     assert float((torch.ones(4, device="cuda") * 3).sum()) == 12.0
+
+
+@pytest.mark.parametrize("tg,td,hidden,ffn,out", [
+    (ro.Q4_K, ro.Q6_K, 5120, 17408, 5120),   # config 2
+    (ro.Q4_K, ro.Q6_K, 1024, 2304, 640),     # 72 sub-blocks: the last 1024-wide iteration of a down row is a quarter full
+    (ro.Q4_K, ro.Q6_K, 1024, 2048, 300),
+    (ro.Q8_0, ro.Q8_0, 2048, 1056, 300),     # 33 sub-blocks
+    (ro.Q6_K, ro.Q6_K, 1024, 256, 2000),     # one superblock per down row
+    (ro.Q4_0, ro.Q4_0, 1024, 1024, 96),
+])
+def test_tensor_parallel_ffn_world_of_one_equals_the_launch_chain(rt, tg, td, hidden, ffn, out):
+    """rc_ffn_decode_tp with one rank: the slice of the contraction is the whole of it.  Against the launch chain (f32
+    association) and against the CPU oracle's exact integer dots on the chain's own records."""
+    lib = rt._lib.load()
+    _status(lib, clear=True)
+    gate = rt.GpuMatvecTensor.from_bytes_matvec(cases.synth_case(tg, hidden, ffn, 1, seed=1)[0], tg, hidden, ffn)
+    up = rt.GpuMatvecTensor.from_bytes_matvec(cases.synth_case(tg, hidden, ffn, 1, seed=2)[0], tg, hidden, ffn)
+    raw_d = cases.synth_case(td, ffn, out, 1, seed=3)[0]
+    down = rt.GpuMatvecTensor.from_bytes_matvec(raw_d, td, ffn, out)
+    tp = rt.TensorParallelFfnDecode(gate, up, down)
+    outs = []
+    for rnd in range(4):  # the three copies of the partial buffer take turns
+        x = cases.synth_case(tg, hidden, 8, 1, seed=10 + rnd % 2)[1]
+        xd = torch.from_numpy(x).cuda().reshape(-1)
+        hq_ref, y_ref = _chain(rt, gate, up, down, xd, ffn, out)
+        tp.run(xd)
+        y = torch.empty_like(y_ref)
+        tp.read_y(y)
+        torch.cuda.synchronize()
+        assert _status(lib) == 0, rnd
+        a = y.cpu().numpy()
+        assert ro.rel_l2(a, y_ref.cpu().numpy().astype(np.float64)) < 1e-5, rnd
+        _, y64, _ = ro.matvec_q8(td, ro.repack(td, raw_d, ffn, out), hq_ref.cpu().numpy(), ffn, out, 1)
+        assert ro.rel_l2(a, y64) < 1e-4, rnd
+        outs.append(y)
+    assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[3])  # same input, same bits
+    tp.close()

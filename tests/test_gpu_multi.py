@@ -110,6 +110,35 @@ def _worker(rank: int, world: int, port: int, q):
             dist.all_gather(both, y_f)
             assert all(torch.equal(both[0], b) for b in both[1:]), f"fused FFN round {rnd}: the ranks' outputs differ"
         fused.close()
+        # the tensor-parallel form (gate/up by rows, down by the matching columns, partial outputs summed in rank order):
+        # uneven column shards in whole superblocks
+        ffn2 = 2304
+        raw_g2, raw_u2 = (cases.synth_case(tg, hidden, ffn2, 1, seed=s)[0] for s in (64, 65))
+        raw_d2 = cases.synth_case(td, ffn2, out, 1, seed=66)[0]
+        full2 = [rt.GpuMatvecTensor.from_bytes_matvec(r, ty, i, o) for r, ty, i, o in
+                 ((raw_g2, tg, hidden, ffn2), (raw_u2, tg, hidden, ffn2), (raw_d2, td, ffn2, out))]
+        c0, c1 = sh.col_shard_range(ffn2, rank, world, 256)
+        row_bytes = (hidden // 256) * 144
+        g_part = np.asarray(raw_g2, dtype=np.uint8)[c0 * row_bytes:c1 * row_bytes]
+        u_part = np.asarray(raw_u2, dtype=np.uint8)[c0 * row_bytes:c1 * row_bytes]
+        d_part = sh.shard_raw_cols(raw_d2, td, ffn2, out, c0, c1)
+        tp = rt.TensorParallelFfnDecode(rt.GpuMatvecTensor.from_bytes_matvec(g_part, tg, hidden, c1 - c0),
+                                        rt.GpuMatvecTensor.from_bytes_matvec(u_part, tg, hidden, c1 - c0),
+                                        rt.GpuMatvecTensor.from_bytes_matvec(d_part, td, c1 - c0, out))
+        hq3 = torch.empty((ffn2 // 32) * 40, **u8)
+        yg3, yu3 = torch.empty(ffn2, device="cuda"), torch.empty(ffn2, device="cuda")
+        for rnd in range(4):
+            xd = torch.from_numpy(cases.synth_case(tg, hidden, 8, 1, seed=80 + rnd)[1]).cuda().reshape(-1)
+            rt.launch_ffn_decode(full2[0], full2[1], full2[2], xd, xq2, yg3, yu3, hq3, y_chain)
+            tp.run(xd)
+            tp.read_y(y_f)
+            torch.cuda.synchronize()
+            assert lib.rc_device_status(__import__("ctypes").byref(st)) == 0 and st.value == 0, hex(st.value)
+            assert ro.rel_l2(y_f.cpu().numpy(), y_chain.cpu().numpy().astype(np.float64)) < 1e-5, rnd
+            both = [torch.empty_like(y_f) for _ in range(world)]
+            dist.all_gather(both, y_f)
+            assert all(torch.equal(both[0], b) for b in both[1:]), f"tensor-parallel FFN round {rnd}: the ranks' outputs differ"
+        tp.close()
         q.put((rank, "ok"))
     except Exception as e:  # report instead of leaving the peer waiting
         q.put((rank, f"{type(e).__name__}: {e}"))

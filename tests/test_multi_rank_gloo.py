@@ -134,6 +134,32 @@ def test_row_shard_ranges_cover_everything():
         assert bool((owners[lo:hi] == r).all())
 
 
+def test_column_shards_partition_the_contraction_and_sum_to_the_whole():
+    """The tensor-parallel split of the down projection: whole blocks of the format per rank, uneven shares last; the
+    ranks' partial products (CPU oracle, exact integer dots per block) add up to the unsharded row products."""
+    t, in_dim, out_dim = ro.Q6_K, 2304, 24
+    for world in (1, 2, 4, 8):
+        ranges = [sh.col_shard_range(in_dim, r, world, 256) for r in range(world)]
+        assert ranges[0][0] == 0 and ranges[-1][1] == in_dim
+        assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+        sizes = [e - b for b, e in ranges]
+        assert all(s % 256 == 0 for s in sizes) and max(sizes) - min(sizes) <= 256 and sizes == sorted(sizes)
+    raw, x = cases.synth_case(t, in_dim, out_dim, 1, seed=21)
+    xq = ro.quantize_q8(x)
+    _, want, _ = ro.matvec_q8(t, ro.repack(t, raw, in_dim, out_dim), xq, in_dim, out_dim, 1)
+    world = 4
+    total = np.zeros(out_dim, dtype=np.float64)
+    for r in range(world):
+        b, e = sh.col_shard_range(in_dim, r, world, 256)
+        part = sh.shard_raw_cols(raw, t, in_dim, out_dim, b, e)
+        xq_part = np.asarray(xq).reshape(-1, 40)[b // 32:e // 32].reshape(-1)
+        _, y, _ = ro.matvec_q8(t, ro.repack(t, part, e - b, out_dim), xq_part, e - b, out_dim, 1)
+        total += np.asarray(y, dtype=np.float64).reshape(-1)
+    assert ro.rel_l2(total, np.asarray(want, dtype=np.float64).reshape(-1)) < 1e-6
+    with pytest.raises(ValueError):
+        sh.shard_raw_cols(raw, t, in_dim, out_dim, 32, 288)
+
+
 def test_row_sharded_matvec_two_ranks():
     _run("_row_shard_case")
 
