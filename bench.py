@@ -718,6 +718,47 @@ def run_gpu_arm(args):
     assert fused_rel < 1e-3, f"fused FFN launch differs from the launch chain: {fused_rel}"
     step, step_other = (step_fused, step_chain) if use_fused else (step_chain, step_fused)
 
+    # N > 1, the reported step: the tensor-parallel form (rc_ffn_decode_tp).  Gate and up by rows, down by the matching
+    # COLUMNS in whole superblocks (17408 / 256 = 68 superblocks dealt out as evenly as they go), so the intermediate stays
+    # on its rank and the one exchange is the sum of the partial outputs.  Its own weight shards (the same total bytes).
+    tp = tp_rel = ms_rows = None
+    if world > 1:
+        from reinstinct_b200 import sharding as sh
+
+        c0, c1 = sh.col_shard_range(FFN, rank, world, 256)
+        n_loc = c1 - c0
+        copies_tp = []
+        for c in range(n_copies):
+            shapes = ((Q4_K, HIDDEN, n_loc), (Q4_K, HIDDEN, n_loc), (Q6_K, n_loc, HIDDEN))
+            copies_tp.append([rt.GpuMatvecTensor.from_bytes_matvec(synth.synth_blocks(t, i, o, seed=2000 * c + 10 * k + rank + 1), t, i, o, device=dev)
+                              for k, (t, i, o) in enumerate(shapes)])
+        tp = [rt.TensorParallelFfnDecode(ws[0], ws[1], ws[2], device=dev) for ws in copies_tp]
+        tp_bytes = torch.tensor([float(sum(w.data.numel() for w in copies_tp[0]))], device=dev)
+        dist.all_reduce(tp_bytes)
+        layer_bytes_total = int(tp_bytes.item())
+
+        def step_tp(c: int):
+            tp[c % n_copies].run(x_dev)
+
+        # checked steps: against the same shards through separate launches, partial outputs summed by NCCL
+        yg_l, yu_l = torch.empty(n_loc, device=dev), torch.empty(n_loc, device=dev)
+        hq_l = torch.empty((n_loc // 32) * 40, dtype=torch.uint8, device=dev)
+        y_part, y_tp = torch.empty(HIDDEN, device=dev), torch.empty(HIDDEN, device=dev)
+        tp_rel = 0.0
+        for c in range(3):
+            ws = copies_tp[c]
+            rt.launch_ffn_decode(ws[0], ws[1], ws[2], x_dev, xq, yg_l, yu_l, hq_l, y_part)
+            dist.all_reduce(y_part)
+            step_tp(c)
+            tp[c].read_y(y_tp)
+            torch.cuda.synchronize()
+            tp_rel = max(tp_rel, float((y_tp - y_part).norm() / y_part.norm()))
+        # (a last-bit difference between the two forms' gate/up row sums moves a few quants of the intermediate across a
+        # rounding boundary: the bar is the f32 tolerance of the reference's own kernel tests)
+        assert tp_rel < 1e-3, f"tensor-parallel FFN launch differs from the launch chain + all-reduce: {tp_rel}"
+        step_rows = step
+        step = step_tp
+
     # End-to-end step through the host-side API with HOST buffers.  One GPU: runtime.launch_ffn_decode given the pinned
     # host input and output themselves (the quantizer reads x, the down matvec writes y across PCIe; no copy launches).
     # N > 1: x is uploaded by a copy node (every CTA reads it) and the launch writes the gathered output into the pinned host y.
@@ -727,7 +768,7 @@ def run_gpu_arm(args):
             rt.launch_ffn_decode(ws[0], ws[1], ws[2], in_host, xq, y_gate, y_up, hq, yd_host)
         else:
             x_dev.copy_(in_host, non_blocking=True)
-            fused[c % n_copies].run(x_dev, yd_host)  # the last phase writes the gathered output to the host itself
+            tp[c % n_copies].run(x_dev, yd_host)  # the last phase writes the summed output to the host itself
 
     def barrier():
         if world > 1:
@@ -832,6 +873,10 @@ def run_gpu_arm(args):
                 cur_c[0] += 1
     ms_other = float(np.median(timed_rounds(other_round, max(20, rounds // 4), 2))) / K
     ms_chain, ms_fused = (ms_other, ms_per_step) if use_fused else (ms_per_step, ms_other)
+    if world > 1:
+        rows_round = make_round(build_graphs(step_rows)) if use_graph else None
+        if rows_round is not None:
+            ms_rows = float(np.median(timed_rounds(rows_round, max(20, rounds // 4), 2))) / K
 
     if use_graph:
         round_e2e = make_round(build_graphs(step_e2e))
@@ -924,19 +969,21 @@ def run_gpu_arm(args):
                     "ms_per_step_max": float(ms_e2e_rounds.max()) / K, "graph_replay": use_graph,
                     "how": ("runtime.launch_ffn_decode with the pinned host input and output as its x and y: the quantizer reads x "
                             "and the down matvec writes y across PCIe" if world == 1 else
-                            "copy node in, fused sharded launch whose last phase writes the gathered output into the pinned host y"),
+                            "copy node in, the sharded launch whose last phase writes the summed output into the pinned host y"),
                     "equals_device_resident_step": e2e_check},
             "gpu_launches": launches_per_step * K * rounds,
-            "step": ("one cooperative launch per GPU (rc_ffn_decode)" if use_fused else
+            "step": ("one cooperative launch per GPU, tensor-parallel (rc_ffn_decode_tp: gate/up by rows, down by columns, partial "
+                     "outputs summed in rank order)" if use_fused else
                      "five launches (quantize, gate, up, SwiGLU + quantize, down) with programmatic dependent launch"),
             "ms_per_step_launch_chain": ms_chain, "ms_per_step_one_launch": ms_fused, "fused_vs_chain_rel_l2": fused_rel,
-            "gather": "peer stores from inside the fused launch, monotone arrival counters" if world > 1 else None,
+            "ms_per_step_one_launch_row_sharded": ms_rows, "tp_vs_chain_allreduce_rel_l2": tp_rel,
+            "gather": "peer stores from inside the launch; arrival is read off the values" if world > 1 else None,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "matvec_rows_kernel<Q4_K,1,5> 5120->%d (the Q4_K decode matvec, timed alone)" % (FFN // world),
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "us_per_launch": q4k_us, "bytes_per_launch": q4k_bytes,
                          "traffic": traffic if world == 1 else None, "traffic_source": traffic_src,
-                         "fused_step": {"kernel": "ffn_decode_kernel<Q4_K,Q6_K>", "bytes_per_launch": layer_bytes_local,
+                         "fused_step": {"kernel": "ffn_tp_kernel<Q4_K,Q6_K>" if world > 1 else "ffn_decode_kernel<Q4_K,Q6_K>", "bytes_per_launch": layer_bytes_local,
                                         "us_per_launch": ms_fused * 1e3, "achieved": layer_bytes_local / (ms_fused * 1e-3) / 1e9,
                                         "frac": layer_bytes_local / (ms_fused * 1e-3) / 1e9 / peak}},
             "per_kernel": {"q4k_gate_up_gbs": achieved, "q6k_down_gbs": q6_bytes / (q6_us * 1e-6) / 1e9,
@@ -959,7 +1006,7 @@ def run_gpu_arm(args):
             line["cpu_baseline"] = {"value": v, "unit": "GB/s", "cores": os.cpu_count() or 1, "kind": "port",
                                     "sample": sample}
         print(json.dumps(line), flush=True)
-    for f in fused:
+    for f in fused + (tp or []):
         f.close()
     if world > 1:
         ga_h.close()

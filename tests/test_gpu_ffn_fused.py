@@ -164,9 +164,11 @@ def test_tensor_parallel_ffn_world_of_one_equals_the_launch_chain(rt, tg, td, hi
         torch.cuda.synchronize()
         assert _status(lib) == 0, rnd
         a = y.cpu().numpy()
-        assert ro.rel_l2(a, y_ref.cpu().numpy().astype(np.float64)) < 1e-5, rnd
+        # (a last-bit difference between the two forms' gate/up row sums may move a quant of the intermediate across a
+        # rounding boundary: 5e-4 allows a few such, a wrong block or scale would be 1e-2 and more)
+        assert ro.rel_l2(a, y_ref.cpu().numpy().astype(np.float64)) < 5e-4, rnd
         _, y64, _ = ro.matvec_q8(td, ro.repack(td, raw_d, ffn, out), hq_ref.cpu().numpy(), ffn, out, 1)
-        assert ro.rel_l2(a, y64) < 1e-4, rnd
+        assert ro.rel_l2(a, y64) < 5e-4, rnd
         outs.append(y)
     assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[3])  # same input, same bits
     tp.close()

@@ -134,7 +134,7 @@ def _worker(rank: int, world: int, port: int, q):
             tp.read_y(y_f)
             torch.cuda.synchronize()
             assert lib.rc_device_status(__import__("ctypes").byref(st)) == 0 and st.value == 0, hex(st.value)
-            assert ro.rel_l2(y_f.cpu().numpy(), y_chain.cpu().numpy().astype(np.float64)) < 1e-5, rnd
+            assert ro.rel_l2(y_f.cpu().numpy(), y_chain.cpu().numpy().astype(np.float64)) < 5e-4, rnd
             both = [torch.empty_like(y_f) for _ in range(world)]
             dist.all_gather(both, y_f)
             assert all(torch.equal(both[0], b) for b in both[1:]), f"tensor-parallel FFN round {rnd}: the ranks' outputs differ"
