@@ -1409,18 +1409,20 @@ __global__ void __launch_bounds__(kFfnWarps * 32, 1) ffn_tp_kernel(const FfnTpPa
     w3.prime();
     __syncthreads(); // this CTA's values of h are written; the shared memory of phase 1 is free
     if (threadIdx.x == 0) {
-        __threadfence(); // release: the CTA's stores to h (ordered before this thread by the barrier) before the count
-        atomicAdd(P.sync + 1, 1ull);
+        // release: the CTA's stores to h (ordered before this thread by the barrier) before the count; acquire on the way out
+        asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(P.sync + 1), "l"(1ull) : "memory");
         const unsigned long long t0 = ffn_ns(), want = call * (unsigned long long)gridDim.x;
-        while (*reinterpret_cast<volatile unsigned long long *>(P.sync + 1) < want) {
-            if (ffn_ns() - t0 > kFfnWaitNs) {
+        unsigned long long seen = 0;
+        uint32_t spins = 0;
+        for (;;) {
+            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(P.sync + 1) : "memory");
+            if (seen >= want) break;
+            if ((++spins & 63u) == 0 && ffn_ns() - t0 > kFfnWaitNs) {
                 atomicExch(&g_ffn_error, 1u);
                 s_ok = 0;
                 break;
             }
-            __nanosleep(100);
         }
-        __threadfence(); // acquire
     }
     __syncthreads();
     mark(3);
