@@ -172,3 +172,32 @@ def test_tensor_parallel_ffn_world_of_one_equals_the_launch_chain(rt, tg, td, hi
         outs.append(y)
     assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[3])  # same input, same bits
     tp.close()
+
+
+def test_tensor_parallel_ffn_absent_peer_runs_into_the_bounded_wait(rt):
+    """Rank 0 of two whose peer never runs: its own partial sums arrive in both partial buffers, the peer's never do,
+    the read of the output rows gives up after its limit, the status word says which wait, the device stays usable."""
+    lib = rt._lib.load()
+    _status(lib, clear=True)
+    tg, td, hidden, ffn, out = ro.Q4_K, ro.Q6_K, 1024, 2048, 256
+    half = ffn // 2
+    gate = rt.GpuMatvecTensor.from_bytes_matvec(cases.synth_case(tg, hidden, half, 1, seed=1)[0], tg, hidden, half)
+    up = rt.GpuMatvecTensor.from_bytes_matvec(cases.synth_case(tg, hidden, half, 1, seed=2)[0], tg, hidden, half)
+    down = rt.GpuMatvecTensor.from_bytes_matvec(cases.synth_case(td, half, out, 1, seed=3)[0], td, half, out)
+    xd = torch.from_numpy(cases.synth_case(tg, hidden, 8, 1, seed=9)[1]).cuda().reshape(-1)
+    mine = torch.full((3 * 2 * out * 4,), 0xFF, dtype=torch.uint8, device="cuda")
+    absent = mine.clone()  # stands in for the peer's mapped buffer
+    parts = (C.c_void_p * 2)(mine.data_ptr(), absent.data_ptr())
+    work = torch.zeros(lib.rc_ffn_decode_tp_work_bytes(half), dtype=torch.uint8, device="cuda")
+    y = torch.zeros(out, device="cuda")
+    rc = lib.rc_ffn_decode_tp(torch.cuda.current_stream().cuda_stream, tg, td, gate.data.data_ptr(), up.data.data_ptr(),
+                              down.data.data_ptr(), xd.data_ptr(), y.data_ptr(), hidden, half, out, 2, 0, parts, work.data_ptr())
+    assert rc == 0, lib.rc_error_string(rc)
+    torch.cuda.synchronize()
+    st = _status(lib, clear=True)
+    assert (st >> 20) & 0xF == 3, hex(st)      # the wait for the peers' partial sums
+    assert _status(lib) == 0
+    for buf in (mine, absent):                 # the first call uses copy 1: slot 0 (this rank) filled, slot 1 still empty
+        p = buf.view(torch.int32).reshape(3, 2, out)
+        assert bool((p[1, 0] != -1).all()) and bool((p[1, 1] == -1).all())
+    assert float((torch.ones(4, device="cuda") * 3).sum()) == 12.0
