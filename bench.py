@@ -767,7 +767,7 @@ def run_gpu_arm(args):
             ws = copies[c % n_copies]
             rt.launch_ffn_decode(ws[0], ws[1], ws[2], in_host, xq, y_gate, y_up, hq, yd_host)
         else:
-            x_dev.copy_(in_host, non_blocking=True)
+            rt.copy_small(x_dev, in_host, HIDDEN * 4)  # every CTA reads x: one upload by a kernel (a memcpy node costs 9 us here)
             tp[c % n_copies].run(x_dev, yd_host)  # the last phase writes the summed output to the host itself
 
     def barrier():
@@ -969,7 +969,7 @@ def run_gpu_arm(args):
                     "ms_per_step_max": float(ms_e2e_rounds.max()) / K, "graph_replay": use_graph,
                     "how": ("runtime.launch_ffn_decode with the pinned host input and output as its x and y: the quantizer reads x "
                             "and the down matvec writes y across PCIe" if world == 1 else
-                            "copy node in, the sharded launch whose last phase writes the summed output into the pinned host y"),
+                            "x uploaded by a copy kernel (rc_copy_small), the sharded launch whose last phase writes the summed output into the pinned host y"),
                     "equals_device_resident_step": e2e_check},
             "gpu_launches": launches_per_step * K * rounds,
             "step": ("one cooperative launch per GPU, tensor-parallel (rc_ffn_decode_tp: gate/up by rows, down by columns, partial "

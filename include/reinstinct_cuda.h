@@ -524,6 +524,11 @@ int rc_malloc(void **ptr, size_t bytes);
 int rc_free(void *ptr);
 int rc_memcpy(void *dst, const void *src, size_t bytes, int kind);
 int rc_memcpy_async(void *dst, const void *src, size_t bytes, int kind, void *stream);
+/* A small copy (up to 16 MiB, 16-byte aligned, a multiple of 16 bytes) done by a kernel instead of the copy
+ * engine: either side may be pinned host memory.  For steps replayed from a CUDA graph whose few-KB input or
+ * output sits in host memory: a memcpy node costs 8-10 us of such a step here, this launch 3.  No counterpart
+ * in the reference (its uploads are hipMemcpyAsync, src/hip/sys.rs:64). */
+int rc_copy_small(void *stream, void *dst, const void *src, size_t bytes);
 int rc_memcpy_peer_async(void *dst, int dst_device, const void *src, int src_device,
                          size_t bytes, void *stream);
 int rc_memset_async(void *dst, int value, size_t bytes, void *stream);

@@ -84,6 +84,7 @@ _SIGNATURES = {
     "rc_ffn_decode": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _u32, _u32,
                            C.POINTER(_vp), C.POINTER(_vp), _vp]),
     "rc_peer_barrier": (_i, [_vp, C.POINTER(_vp), _vp, _u32, _u32]),
+    "rc_copy_small": (_i, [_vp, _vp, _vp, _sz]),
     "rc_ffn_decode_tp_work_bytes": (_sz, [_u32]),
     "rc_ffn_decode_tp": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, C.POINTER(_vp), _vp]),
     "rc_ep_plan": (_i, [_vp, _vp, _u32, _u32, _u32, _u32, _vp]),

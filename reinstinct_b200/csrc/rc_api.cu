@@ -759,6 +759,23 @@ int rc_memcpy_async(void *dst, const void *src, size_t bytes, int kind, void *st
 {
     return (int)cudaMemcpyAsync(dst, src, bytes, (cudaMemcpyKind)kind, S(stream));
 }
+// A small copy done by the SMs: 16-byte words, one CTA per 16 KB.
+static __global__ void __launch_bounds__(1024) rc_copy_small_kernel(uint4 *__restrict__ dst, const uint4 *__restrict__ src, uint32_t n16)
+{
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+int rc_copy_small(void *stream, void *dst, const void *src, size_t bytes)
+{
+    if (bytes == 0) return RC_OK;
+    if (!dst || !src) return RC_ERR_NULL_POINTER;
+    if (bytes % 16 || bytes > (1u << 24)) return RC_ERR_BAD_SHAPE;
+    if (((uintptr_t)dst & 15u) || ((uintptr_t)src & 15u)) return RC_ERR_MISALIGNED;
+    const uint32_t n16 = (uint32_t)(bytes / 16);
+    rc_copy_small_kernel<<<std::min<uint32_t>((n16 + 1023u) / 1024u, 64u), 1024, 0, S(stream)>>>((uint4 *)dst, (const uint4 *)src, n16);
+    return (int)cudaGetLastError();
+}
+
 int rc_memcpy_peer_async(void *dst, int dst_device, const void *src, int src_device, size_t bytes,
                          void *stream)
 {

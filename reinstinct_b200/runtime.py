@@ -485,6 +485,12 @@ class PeerBuffers:
             self._base = 0
 
 
+def copy_small(dst, src, n_bytes: int) -> None:
+    """rc_copy_small on the current stream: a few KB between pinned host and device memory (either way) by a kernel;
+    in a replayed graph a memcpy node of that size costs three times as much."""
+    check(_lib.load().rc_copy_small(_stream(), _ptr(dst), _ptr(src), n_bytes), "rc_copy_small")
+
+
 class FusedFfnDecode:
     """step_swiglu_ffn (src/runtime/qwen35.rs:2694-2707) as ONE cooperative launch per GPU (rc_ffn_decode), row-sharded
     over the ranks of `group` (or a single GPU when torch.distributed is not initialised): this rank's `gate` and `up`

@@ -201,3 +201,27 @@ def test_tensor_parallel_ffn_absent_peer_runs_into_the_bounded_wait(rt):
         p = buf.view(torch.int32).reshape(3, 2, out)
         assert bool((p[1, 0] != -1).all()) and bool((p[1, 1] == -1).all())
     assert float((torch.ones(4, device="cuda") * 3).sum()) == 12.0
+
+
+def test_copy_small_moves_bytes_between_pinned_host_and_device(rt):
+    """rc_copy_small: the kernel-side upload / download of a step's few KB (a memcpy node costs more in a replayed graph)."""
+    lib = rt._lib.load()
+    host = torch.arange(5120, dtype=torch.float32).pin_memory()
+    dev = torch.zeros(5120, device="cuda")
+    back = torch.zeros(5120, dtype=torch.float32).pin_memory()
+    rt.copy_small(dev, host, 5120 * 4)
+    rt.copy_small(back, dev, 5120 * 4)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        rt.copy_small(dev, host, 5120 * 4)
+        rt.copy_small(back, dev, 5120 * 4)
+    torch.cuda.synchronize()
+    assert torch.equal(back, host) and torch.equal(dev.cpu(), host)
+    host.mul_(2.0)
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(back, host)
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.rc_copy_small(st, dev.data_ptr(), host.data_ptr(), 20) == -2          # not a multiple of 16 bytes: RC_ERR_BAD_SHAPE
+    assert lib.rc_copy_small(st, dev.data_ptr() + 4, host.data_ptr(), 16) == -4      # RC_ERR_MISALIGNED
+    assert lib.rc_copy_small(st, 0, host.data_ptr(), 16) == -3                       # RC_ERR_NULL_POINTER
