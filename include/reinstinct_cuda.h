@@ -434,7 +434,8 @@ int rc_allgather_push_logical(void *stream, const void *const *srcs, size_t byte
  * multiples of 1024; format pairs (gate, down): (Q4_K, Q6_K), (Q4_K, Q4_K), (Q5_K, Q6_K), (Q6_K, Q6_K),
  * (Q8_0, Q8_0), (Q4_0, Q4_0), else RC_ERR_BAD_TYPE.  A cooperative launch of one CTA per SM; may be captured
  * in a CUDA graph.  A wait that runs out (a peer that never launched) sets bits 20-23 of rc_device_status (2:
- * the intermediate, 3: the output rows) and the launch ends. */
+ * the intermediate, 3: the output rows) and the launch ends; the buffers and counters of the shape are then
+ * out of step with the peers' and must be set up again (fill, zero) on every rank before the next call. */
 size_t rc_ffn_decode_work_bytes(uint32_t ffn_local);
 int rc_ffn_decode(void *stream, int gate_type, int down_type, const void *gate_w, const void *up_w,
                   const void *down_w, const float *x, float *y, uint32_t in_dim, uint32_t ffn_local,
@@ -454,7 +455,7 @@ int rc_ffn_decode(void *stream, int gate_type, int down_type, const void *gate_w
  * sum over ranks replaces part of a row sum, so results differ from the one-GPU step in the last bits (and
  * repeat bit for bit).  in_dim a multiple of 1024; format pairs as rc_ffn_decode.  Every rank makes the same
  * sequence of calls; a wait that runs out sets bits 20-23 of rc_device_status (1: this GPU's own CTAs, 3: the
- * peers' partial sums) and the launch ends. */
+ * peers' partial sums) and the launch ends; buffers and work must then be set up again on every rank. */
 size_t rc_ffn_decode_tp_work_bytes(uint32_t ffn_local);
 int rc_ffn_decode_tp(void *stream, int gate_type, int down_type, const void *gate_w, const void *up_w,
                      const void *down_w, const float *x, float *y, uint32_t in_dim, uint32_t ffn_local,
