@@ -1504,14 +1504,13 @@ __global__ void __launch_bounds__(kFfnWarps * 32, 1) ffn_tp_kernel(const FfnTpPa
     }
 }
 
-// Warps that share a row: the count, among the powers of two up to the team size, with the least (rounds of the grid) x
+// Warps that share a row: the count, among the powers of two that divide the team size, with the least (rounds of the grid) x
 // (dependent load round trips + multiply time per round), the shared-row reduction counted per round.
 static uint32_t ffn_pick_ks(uint32_t rows, uint32_t n_iters, uint32_t len, uint32_t grid, uint32_t team)
 {
     uint32_t best = 1;
     float best_cost = 1e30f;
-    for (uint32_t ks = 1; ks <= team; ks *= 2u) {
-        if (ks > n_iters) break;
+    for (uint32_t ks = 1; ks <= team && ks <= n_iters; ks *= 2u) { // (3 and 6 warps per row were measured: never better)
         if (team % ks) continue;
         const uint32_t per_round = grid * (team / ks), rounds = (rows + per_round - 1u) / per_round;
         const uint32_t per = (n_iters + ks - 1u) / ks, trips = (per + len - 1u) / len;
@@ -1525,6 +1524,7 @@ static uint32_t ffn_pick_ks(uint32_t rows, uint32_t n_iters, uint32_t len, uint3
 }
 
 int g_ffn_plain_launch = 0; // measurement: the fused decode FFN as an ordinary launch
+int g_ffn_ks_override = 0;   // measurement: warps that share a down row in the tensor-parallel launch (rc_tune_matvec's ks)
 
 template <int FG, int FD>
 int launch_ffn(cudaStream_t s, const FfnParams &P, const FfnPeers &peers)
@@ -1567,6 +1567,7 @@ int launch_ffn_tp(cudaStream_t s, const FfnTpParams &P, const FfnTpPeers &peers)
     FfnTpParams Q = P;
     const uint32_t grid = (uint32_t)sm_count();
     Q.ks = ffn_pick_ks(P.out_total, nh >> 5, (uint32_t)FmtTraits<FD>::rows_max_len, grid, (uint32_t)kFfnWarps);
+    if (g_ffn_ks_override > 0 && kFfnWarps % g_ffn_ks_override == 0 && (uint32_t)g_ffn_ks_override <= (nh >> 5)) Q.ks = (uint32_t)g_ffn_ks_override;
     Q.ks_gu = ffn_pick_ks(P.ffn_local, nx >> 5, (uint32_t)FmtTraits<FG>::rows_max_len, grid, kFfnTeam);
     Q.trace = g_ffn_trace_on;
     FfnTpPeers pp = peers;
@@ -1926,6 +1927,7 @@ void matvec_set_tuning(int ks, int grid_mult, int no_pdl)
     g_tune.no_pdl = no_pdl & 1;
     g_tune.no_rows_kernel = (no_pdl >> 1) & 1;
     g_ffn_plain_launch = (no_pdl >> 2) & 1;
+    g_ffn_ks_override = ks;
 }
 bool matvec_pdl_enabled() { return !g_tune.no_pdl; }
 
