@@ -755,9 +755,19 @@ def run_gpu_arm(args):
             tp_rel = max(tp_rel, float((y_tp - y_part).norm() / y_part.norm()))
         # (a last-bit difference between the two forms' gate/up row sums moves a few quants of the intermediate across a
         # rounding boundary: the bar is the f32 tolerance of the reference's own kernel tests)
-        assert tp_rel < 1e-3, f"tensor-parallel FFN launch differs from the launch chain + all-reduce: {tp_rel}"
+        worst = torch.tensor([tp_rel], device=dev)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)  # one decision for all ranks
+        tp_rel = float(worst.item())
         step_rows = step
-        step = step_tp
+        if tp_rel < 1e-3:
+            step = step_tp
+        else:  # keep the row-sharded launch as the step and say so in the line
+            print(f"bench: tensor-parallel launch differs from the launch chain + all-reduce by {tp_rel}; reporting the row-sharded launch",
+                  file=sys.stderr, flush=True)
+            for f in tp:
+                f.close()
+            tp = None
+            layer_bytes_total = layer_bytes_local * world
 
     # End-to-end step through the host-side API with HOST buffers.  One GPU: runtime.launch_ffn_decode given the pinned
     # host input and output themselves (the quantizer reads x, the down matvec writes y across PCIe; no copy launches).
@@ -768,7 +778,7 @@ def run_gpu_arm(args):
             rt.launch_ffn_decode(ws[0], ws[1], ws[2], in_host, xq, y_gate, y_up, hq, yd_host)
         else:
             rt.copy_small(x_dev, in_host, HIDDEN * 4)  # every CTA reads x: one upload by a kernel (a memcpy node costs 9 us here)
-            tp[c % n_copies].run(x_dev, yd_host)  # the last phase writes the summed output to the host itself
+            (tp or fused)[c % n_copies].run(x_dev, yd_host)  # the last phase writes the output to the host itself
 
     def barrier():
         if world > 1:
@@ -973,7 +983,8 @@ def run_gpu_arm(args):
                     "equals_device_resident_step": e2e_check},
             "gpu_launches": launches_per_step * K * rounds,
             "step": ("one cooperative launch per GPU, tensor-parallel (rc_ffn_decode_tp: gate/up by rows, down by columns, partial "
-                     "outputs summed in rank order)" if use_fused else
+                     "outputs summed in rank order)" if use_fused and tp is not None else
+                     "one cooperative launch per GPU, all three projections by rows (rc_ffn_decode)" if use_fused else
                      "five launches (quantize, gate, up, SwiGLU + quantize, down) with programmatic dependent launch"),
             "ms_per_step_launch_chain": ms_chain, "ms_per_step_one_launch": ms_fused, "fused_vs_chain_rel_l2": fused_rel,
             "ms_per_step_one_launch_row_sharded": ms_rows, "tp_vs_chain_allreduce_rel_l2": tp_rel,
@@ -983,7 +994,7 @@ def run_gpu_arm(args):
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "us_per_launch": q4k_us, "bytes_per_launch": q4k_bytes,
                          "traffic": traffic if world == 1 else None, "traffic_source": traffic_src,
-                         "fused_step": {"kernel": "ffn_tp_kernel<Q4_K,Q6_K>" if world > 1 else "ffn_decode_kernel<Q4_K,Q6_K>", "bytes_per_launch": layer_bytes_local,
+                         "fused_step": {"kernel": "ffn_tp_kernel<Q4_K,Q6_K>" if tp is not None else "ffn_decode_kernel<Q4_K,Q6_K>", "bytes_per_launch": layer_bytes_local,
                                         "us_per_launch": ms_fused * 1e3, "achieved": layer_bytes_local / (ms_fused * 1e-3) / 1e9,
                                         "frac": layer_bytes_local / (ms_fused * 1e-3) / 1e9 / peak}},
             "per_kernel": {"q4k_gate_up_gbs": achieved, "q6k_down_gbs": q6_bytes / (q6_us * 1e-6) / 1e9,
