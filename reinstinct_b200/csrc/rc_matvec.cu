@@ -1369,15 +1369,16 @@ __global__ void __launch_bounds__(kFfnWarps * 32, 1) ffn_tp_kernel(const FfnTpPa
         const uint32_t vwarp = warp % kFfnTeam, ks = P.ks_gu;
         w1.init(planes_of<FG>(is_up ? P.up : P.gate, P.in_dim, P.ffn_local), n_sub_x, P.ffn_local, ks, vwarp, kFfnTeam);
         w1.prime();
+        quantize_stage<FG>(stx, n_sub_x, P.x, false, warp, kFfnWarps);
+        __syncthreads();
+        mark(1);
         {
-            // refill the copy of the partial buffer that the call after the next will use
+            // refill the copy of the partial buffer that the call after the next will use (here, not at the top: the call
+            // number is the kernel's first load, and nothing before this point has to wait for it)
             float *const fill = peers.part[P.rank] + (size_t)((cur + 2u) % 3u) * P.world * P.out_total;
             const uint32_t n = P.world * P.out_total;
             for (uint32_t k = blockIdx.x * blockDim.x + threadIdx.x; k < n; k += gridDim.x * blockDim.x) fill[k] = __uint_as_float(kFfnEmpty);
         }
-        quantize_stage<FG>(stx, n_sub_x, P.x, false, warp, kFfnWarps);
-        __syncthreads();
-        mark(1);
         const uint32_t group = vwarp / ks, slice = vwarp % ks;
         const bool leader = !is_up && slice == 0 && lane == 0;
         const unsigned long long base = (call - 1ull) * (unsigned long long)P.ffn_local;
