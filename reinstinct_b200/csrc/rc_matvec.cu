@@ -520,7 +520,15 @@ constexpr int kMultiMinBlocks = 2; // 128 registers: R weight rows in flight twi
 // LEN iterations plus at most one shorter group.  Same loads, same term(), same order of additions per
 // lane as stream_body; it only sheds that kernel's bookkeeping, which is a third of its
 // instructions on a 5-iteration row.
-template <int FMT, int NB, int LEN>
+// Rows of a last, mostly empty round that the CTAs share (see matvec_rows_kernel): the leftover of the rounds of
+// row_stride rows when it is at most a quarter of a round, there is a full round before it and a row has several groups.
+__host__ __device__ inline uint32_t rows_shared_tail(uint32_t out_dim, uint32_t row_stride, uint32_t n_units)
+{
+    const uint32_t full_rounds = out_dim / row_stride, left = out_dim - full_rounds * row_stride;
+    return (n_units >= 2u && full_rounds >= 1u && left * 4u <= row_stride) ? left : 0u;
+}
+
+template <int FMT, int NB, int LEN, bool TAIL = false>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, MinBlocks<NB>::v)
 matvec_rows_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq, float *__restrict__ y,
                    uint32_t in_dim, uint32_t out_dim, uint32_t n_rows)
@@ -580,29 +588,61 @@ matvec_rows_kernel(const uint8_t *__restrict__ w, const uint8_t *__restrict__ xq
 
     uint32_t row = blockIdx.x * kWarpsPerCta + warp;
     const uint32_t first_group = n_groups ? 0u : n_groups; // rows shorter than LEN are one short group
-    if (row < out_dim) fetch_group(row, first_group);       // weights do not wait for x
+    // A last round that is mostly empty would cost a whole row time for a few rows (5120 rows on 4736 resident warps: 384
+    // warps walk a second row while the others idle).  When the leftover is at most a quarter of a round and a row has
+    // several groups, those rows are dealt one per CTA instead and the CTA's warps share each: a group per warp, the
+    // partial sums added in group order.
+    // (TAIL: the instantiation the host picks when that applies; the plain one keeps the original code exactly.)
+    const uint32_t n_units = n_groups + (tail ? 1u : 0u);
+    const uint32_t shared_rows = TAIL ? rows_shared_tail(out_dim, row_stride, n_units) : 0u;
+    const uint32_t main_end = out_dim - shared_rows;
+    if (row < main_end) fetch_group(row, first_group);      // weights do not wait for x
     pdl_launch_dependents();
     pdl_wait();
     stage_x<FMT>(st, xq, n_rows * n_sub);
     __syncthreads();
 
-    for (; row < out_dim; row += row_stride) {
+    for (; row < main_end; row += row_stride) {
 #pragma unroll
         for (int b = 0; b < NB; b++) acc[b] = 0.0f;
         for (uint32_t g = 0; g < n_groups; g++) {
             compute(g, LEN);
             // the next group's loads go out before this row is reduced
             if (g + 1 < n_groups || tail) fetch_group(row, g + 1);
-            else if (row + row_stride < out_dim) fetch_group(row + row_stride, first_group);
+            else if (row + row_stride < main_end) fetch_group(row + row_stride, first_group);
         }
         if (tail) {
             compute(n_groups, tail);
-            if (row + row_stride < out_dim) fetch_group(row + row_stride, first_group);
+            if (row + row_stride < main_end) fetch_group(row + row_stride, first_group);
         }
 #pragma unroll
         for (int b = 0; b < NB; b++) {
             const float v = warp_sum(acc[b]);
             if (lane == 0 && b < (int)n_rows) y[(size_t)b * out_dim + row] = v;
+        }
+    }
+    if constexpr (TAIL) {
+        __shared__ float s_shared[NB][kWarpsPerCta];
+        for (uint32_t t = blockIdx.x; t < shared_rows; t += gridDim.x) {
+            const uint32_t r = main_end + t;
+#pragma unroll
+            for (int b = 0; b < NB; b++) acc[b] = 0.0f;
+            for (uint32_t g = warp; g < n_units; g += kWarpsPerCta) {
+                fetch_group(r, g);
+                compute(g, g < n_groups ? (uint32_t)LEN : tail);
+            }
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                const float v = warp_sum(acc[b]);
+                if (lane == 0) s_shared[b][warp] = v;
+            }
+            __syncthreads();
+            if (warp == 0 && lane < n_rows) {
+                float v = s_shared[lane][0];
+                for (uint32_t w = 1; w < min((uint32_t)kWarpsPerCta, n_units); w++) v += s_shared[lane][w]; // warp order: reproducible
+                y[(size_t)lane * out_dim + r] = v;
+            }
+            __syncthreads();
         }
     }
 }
@@ -1594,13 +1634,17 @@ template <int FMT, int NB, int LEN>
 int launch_rows(cudaStream_t s, const void *w, const void *xq, float *y, uint32_t in_dim, uint32_t out_dim,
                 uint32_t n_rows, uint32_t grid, size_t smem)
 {
-    if (g_tune.no_pdl) {
-        matvec_rows_kernel<FMT, NB, LEN><<<grid, kWarpsPerCta * 32, smem, s>>>((const uint8_t *)w, (const uint8_t *)xq, y,
-                                                                            in_dim, out_dim, n_rows);
-        return (int)cudaGetLastError();
-    }
-    return (int)launch_pdl(matvec_rows_kernel<FMT, NB, LEN>, dim3(grid), dim3(kWarpsPerCta * 32), smem, s,
-                           (const uint8_t *)w, (const uint8_t *)xq, y, in_dim, out_dim, n_rows);
+    const uint32_t n_iters = in_dim >> 10, n_units = n_iters / LEN + (n_iters % LEN ? 1u : 0u);
+    const bool tail = rows_shared_tail(out_dim, grid * kWarpsPerCta, n_units) != 0u;
+    auto launch = [&](auto kernel) {
+        if (g_tune.no_pdl) {
+            kernel<<<grid, kWarpsPerCta * 32, smem, s>>>((const uint8_t *)w, (const uint8_t *)xq, y, in_dim, out_dim, n_rows);
+            return (int)cudaGetLastError();
+        }
+        return (int)launch_pdl(kernel, dim3(grid), dim3(kWarpsPerCta * 32), smem, s, (const uint8_t *)w, (const uint8_t *)xq, y, in_dim,
+                               out_dim, n_rows);
+    };
+    return tail ? launch(matvec_rows_kernel<FMT, NB, LEN, true>) : launch(matvec_rows_kernel<FMT, NB, LEN, false>);
 }
 
 template <int FMT, int NB, bool DUMP>
@@ -1745,6 +1789,9 @@ template <int FMT, int NB> int set_attr_rows()
     rc |= (int)cudaFuncSetAttribute(matvec_rows_kernel<FMT, NB, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
     rc |= (int)cudaFuncSetAttribute(matvec_rows_kernel<FMT, NB, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
     rc |= (int)cudaFuncSetAttribute(matvec_rows_kernel<FMT, NB, 5>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
+    rc |= (int)cudaFuncSetAttribute(matvec_rows_kernel<FMT, NB, 3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
+    rc |= (int)cudaFuncSetAttribute(matvec_rows_kernel<FMT, NB, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
+    rc |= (int)cudaFuncSetAttribute(matvec_rows_kernel<FMT, NB, 5, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxStageBytesHost);
     return rc;
 }
 
