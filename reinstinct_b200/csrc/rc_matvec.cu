@@ -946,23 +946,26 @@ __device__ __forceinline__ uint32_t q8_words(float v, uint32_t lane)
 template <int FMT> struct RowWalk {
     static constexpr int LEN = FmtTraits<FMT>::rows_max_len;
     Planes p;
-    uint32_t lane, n_rows, n_sub, i0, i1, row, row_stride, rows_per_cta;
+    uint32_t lane, n_rows, n_sub, i0, i1, row, row_base, row_stride, rows_per_cta; // n_rows: one past the walk's last row
     bool a4;
     Raw<FMT> cur[LEN];
 
     // n_sub_ need not be a multiple of 32: the last iteration's lanes beyond the row read its last sub-block again, against
     // staged activations that are zero there (the caller stages zero blocks up to the next multiple of 32).
-    __device__ __forceinline__ void init(const Planes &planes, uint32_t n_sub_, uint32_t rows, uint32_t ks, uint32_t vwarp, uint32_t vwarps)
+    // The walk covers rows [first, first + rows) of the tensor.
+    __device__ __forceinline__ void init(const Planes &planes, uint32_t n_sub_, uint32_t rows, uint32_t ks, uint32_t vwarp, uint32_t vwarps,
+                                         uint32_t first = 0)
     {
         p = planes;
         lane = threadIdx.x & 31u;
-        n_rows = rows;
+        n_rows = first + rows;
         n_sub = n_sub_;
         const uint32_t slice = vwarp % ks, n_iters = (n_sub + 31u) >> 5;
         i0 = slice * n_iters / ks;
         i1 = (slice + 1u) * n_iters / ks;
         rows_per_cta = vwarps / ks;
-        row = blockIdx.x * rows_per_cta + vwarp / ks;
+        row_base = first + blockIdx.x * rows_per_cta;
+        row = row_base + vwarp / ks;
         row_stride = gridDim.x * rows_per_cta;
         a4 = (reinterpret_cast<uintptr_t>(p.sup) & 3u) == 0;
     }
@@ -996,7 +999,7 @@ template <int FMT> struct RowWalk {
     {
         constexpr uint32_t aux_w = (FMT == Q8_0) ? 16u : (FMT == Q6_K) ? 8u : (FMT == Q5_K || FMT == Q5_1) ? 4u : 0u;
         uint32_t spent = 0;
-        for (uint32_t r0 = blockIdx.x * rows_per_cta; r0 < n_rows && spent < budget; r0 += row_stride) {
+        for (uint32_t r0 = row_base; r0 < n_rows && spent < budget; r0 += row_stride) {
             const uint32_t n = min(rows_per_cta, n_rows - r0);
             const uint32_t len = n * p.nsp * 16u, len1 = n * p.nsp * aux_w;
             const uint8_t *b0 = p.nib + (size_t)r0 * p.nsp * 16u;
@@ -1046,7 +1049,7 @@ template <int FMT> struct RowWalk {
     // once per round of the CTA; a round is uniform over the CTA, so finish may synchronize warps.
     template <typename Finish> __device__ __forceinline__ void run(const XStage &st, Finish finish)
     {
-        for (uint32_t r0 = blockIdx.x * rows_per_cta; r0 < n_rows; r0 += row_stride, row += row_stride) {
+        for (uint32_t r0 = row_base; r0 < n_rows; r0 += row_stride, row += row_stride) {
             const bool live = row < n_rows && i0 < i1;
             finish(row, live, live ? walk_row(st, row, row + row_stride) : 0.0f);
         }
@@ -1376,6 +1379,7 @@ struct FfnTpParams {
     float *h;                  // work: f32 [ffn_local]
     unsigned long long *sync;  // work: [0] calls done, [1] CTAs past their gate and up rows, [2] gate/up rows drawn, over all calls
     uint32_t in_dim, ffn_local, out_total, world, rank, ks, ks_gu, trace;
+    uint32_t tail_rows, ks_tail; // the down rows of a last, mostly empty round and the warps that share each of them
 };
 
 template <int FG, int FD>
@@ -1445,8 +1449,12 @@ __global__ void __launch_bounds__(kFfnWarps * 32, 1) ffn_tp_kernel(const FfnTpPa
         }
     }
     mark(2);
+    // The down rows in two walks: whole rounds of the grid with P.ks warps per row, then the leftover rows of a last,
+    // mostly empty round (P.tail_rows of them, none when that does not pay) with more warps per row, so that the whole GPU
+    // works on them instead of a fraction of its warps walking one more full row.
+    const uint32_t main_rows = P.out_total - P.tail_rows;
     RowWalk<FD> w3;
-    w3.init(planes_of<FD>(P.down, P.ffn_local, P.out_total), n_sub_h, P.out_total, P.ks, warp, kFfnWarps);
+    w3.init(planes_of<FD>(P.down, P.ffn_local, P.out_total), n_sub_h, main_rows, P.ks, warp, kFfnWarps);
     w3.prime();
     __syncthreads(); // this CTA's values of h are written; the shared memory of phase 1 is free
     if (threadIdx.x == 0) {
@@ -1478,26 +1486,35 @@ __global__ void __launch_bounds__(kFfnWarps * 32, 1) ffn_tp_kernel(const FfnTpPa
     const bool ok = s_ok != 0;
     if (ok) {
         uint32_t buf = 0;
-        const uint32_t ks = P.ks, slice = warp % ks, rows_per_cta = kFfnWarps / ks;
         const size_t slot = ((size_t)cur * P.world + P.rank) * P.out_total;
-        w3.run(sth, [&](uint32_t r, bool live, float sum) {
-            float v = sum;
-            if (ks > 1u) {
-                if (lane == 0) s_part[buf][warp] = sum;
-                ffn_group_sync(1u + warp / ks, 32u * ks);
-                if (slice == 0 && lane == 0) {
-                    v = s_part[buf][warp];
-                    for (uint32_t k = 1; k < ks; k++) v += s_part[buf][warp + k]; // slice order: reproducible
+        auto walk = [&](RowWalk<FD> &w, const uint32_t ks) {
+            const uint32_t slice = warp % ks, rows_per_cta = kFfnWarps / ks;
+            w.run(sth, [&](uint32_t r, bool live, float sum) {
+                float v = sum;
+                if (ks > 1u) {
+                    if (lane == 0) s_part[buf][warp] = sum;
+                    ffn_group_sync(1u + warp / ks, 32u * ks);
+                    if (slice == 0 && lane == 0) {
+                        v = s_part[buf][warp];
+                        for (uint32_t k = 1; k < ks; k++) v += s_part[buf][warp + k]; // slice order: reproducible
+                    }
                 }
-            }
-            if (slice == 0 && lane == 0) s_out[buf][warp / ks] = ffn_boxed(v);
-            __syncthreads(); // the round's partial sums are in shared memory (a round is uniform over the CTA)
-            // warp k stores the round's consecutive rows into rank k's buffer: one instruction, one packet on the link
-            const uint32_t r0 = r - warp / ks;
-            for (uint32_t k = warp; k < P.world; k += kFfnWarps)
-                if (lane < rows_per_cta && r0 + lane < P.out_total) peers.part[k][slot + r0 + lane] = s_out[buf][lane];
-            buf ^= 1u;
-        });
+                if (slice == 0 && lane == 0) s_out[buf][warp / ks] = ffn_boxed(v);
+                __syncthreads(); // the round's partial sums are in shared memory (a round is uniform over the CTA)
+                // warp k stores the round's consecutive rows into rank k's buffer: one instruction, one packet on the link
+                const uint32_t r0 = r - warp / ks;
+                for (uint32_t k = warp; k < P.world; k += kFfnWarps)
+                    if (lane < rows_per_cta && r0 + lane < w.n_rows) peers.part[k][slot + r0 + lane] = s_out[buf][lane];
+                buf ^= 1u;
+            });
+        };
+        walk(w3, P.ks);
+        if (P.tail_rows) {
+            RowWalk<FD> w4;
+            w4.init(planes_of<FD>(P.down, P.ffn_local, P.out_total), n_sub_h, P.tail_rows, P.ks_tail, warp, kFfnWarps, main_rows);
+            w4.prime();
+            walk(w4, P.ks_tail);
+        }
     }
     mark(5);
     // ---- phase 3: this CTA's share of the output rows, summed over the ranks in rank order
@@ -1609,6 +1626,19 @@ int launch_ffn_tp(cudaStream_t s, const FfnTpParams &P, const FfnTpPeers &peers)
     const uint32_t grid = (uint32_t)sm_count();
     Q.ks = ffn_pick_ks(P.out_total, nh >> 5, (uint32_t)FmtTraits<FD>::rows_max_len, grid, (uint32_t)kFfnWarps);
     if (g_ffn_ks_override > 0 && kFfnWarps % g_ffn_ks_override == 0 && (uint32_t)g_ffn_ks_override <= (nh >> 5)) Q.ks = (uint32_t)g_ffn_ks_override;
+    {
+        // leftover rows of the last round: their own, larger number of warps per row when the round is at most half full
+        const uint32_t per_round = grid * ((uint32_t)kFfnWarps / Q.ks), full = P.out_total / per_round, left = P.out_total - full * per_round;
+        Q.tail_rows = 0;
+        Q.ks_tail = Q.ks;
+        if (full >= 1u && left > 0u && left * 2u <= per_round && g_ffn_ks_override >= 0) {
+            const uint32_t kt = ffn_pick_ks(left, nh >> 5, (uint32_t)FmtTraits<FD>::rows_max_len, grid, (uint32_t)kFfnWarps);
+            if (kt > Q.ks) {
+                Q.tail_rows = left;
+                Q.ks_tail = kt;
+            }
+        }
+    }
     Q.ks_gu = ffn_pick_ks(P.ffn_local, nx >> 5, (uint32_t)FmtTraits<FG>::rows_max_len, grid, kFfnTeam);
     Q.trace = g_ffn_trace_on;
     FfnTpPeers pp = peers;
@@ -2092,6 +2122,8 @@ int launch_ffn_decode_tp(cudaStream_t s, int gate_type, int down_type, const voi
     P.ks = 1;
     P.ks_gu = 1;
     P.trace = 0;
+    P.tail_rows = 0;
+    P.ks_tail = 1;
     FfnTpPeers peers;
     for (uint32_t r = 0; r < RC_MAX_PEERS; r++) peers.part[r] = r < world ? (float *)part_peers[r] : nullptr;
 #define RC_FFN(G, D) \

@@ -138,6 +138,7 @@ def test_fused_ffn_absent_peer_runs_into_the_bounded_wait(rt):
 @pytest.mark.parametrize("tg,td,hidden,ffn,out", [
     (ro.Q4_K, ro.Q6_K, 5120, 17408, 5120),   # config 2
     (ro.Q4_K, ro.Q6_K, 1024, 2304, 640),     # 72 sub-blocks: the last 1024-wide iteration of a down row is a quarter full
+    (ro.Q4_K, ro.Q6_K, 1024, 6144, 4000),    # two full rounds of down rows, then 448 leftover rows walked by four warps each
     (ro.Q4_K, ro.Q6_K, 1024, 2048, 300),
     (ro.Q8_0, ro.Q8_0, 2048, 1056, 300),     # 33 sub-blocks
     (ro.Q6_K, ro.Q6_K, 1024, 256, 2000),     # one superblock per down row
