@@ -143,3 +143,30 @@ def test_argument_errors_leave_context_usable(rt):
         rt.launch_matvec_xq8(bad, xq, y)
     rt.launch_matvec_xq8(w, xq, y)  # still works afterwards
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("t", ro.ALL_TYPES)
+def test_leftover_rows_of_a_mostly_empty_last_round(rt, t):
+    """More rows than one-row-per-warp slots of the whole GPU, by a few: the leftover rows are dealt one per CTA and the
+    CTA's warps take a group of the row each (matvec_rows_kernel's TAIL instantiation).  6144 columns are two groups in
+    every format.  Against the oracle, row by row: the shared rows are the last ones."""
+    props = torch.cuda.get_device_properties(0)
+    slots = props.multi_processor_count * 4 * 8        # one-row warps resident at four CTAs of eight warps per SM
+    in_dim, out_dim = 6144, slots + 164
+    raw, x = cases.synth_case(t, in_dim, out_dim, 1, seed=900 + t)
+    w = rt.GpuMatvecTensor.from_bytes_matvec(raw, t, in_dim, out_dim)
+    xq_ref = ro.quantize_q8(x)
+    xq = torch.from_numpy(xq_ref).cuda()
+    y = torch.full((1, out_dim), float("nan"), device="cuda")
+    rt.launch_matvec_xq8(w, xq, y)
+    torch.cuda.synchronize()
+    _, y64, _ = ro.matvec_q8(t, ro.repack(t, raw, in_dim, out_dim), xq_ref, in_dim, out_dim, 1)
+    got = y.cpu().numpy().reshape(-1)
+    want = np.asarray(y64, dtype=np.float64).reshape(-1)
+    assert np.isfinite(got).all()
+    assert ro.rel_l2(got[:slots], want[:slots]) < 1e-5
+    assert ro.rel_l2(got[slots:], want[slots:]) < 1e-5   # the shared rows
+    y2 = torch.empty_like(y)
+    rt.launch_matvec_xq8(w, xq, y2)
+    torch.cuda.synchronize()
+    assert torch.equal(y, y2)
