@@ -12,8 +12,13 @@ distinct copies of the layer's weights so that no launch finds its weights in L2
 The K steps are replayed from CUDA graphs and timed as one round; the round is repeated until the
 timed region lasts at least 50 ms, and `ms_per_step` is the median round (min and max beside it).
 
-With N > 1 (launched by torch.distributed.run, one rank per GPU) every matrix is split by
-output rows, each rank streams its shard, and the shards' outputs are gathered by peer stores.
+One GPU: the step is five launches with programmatic dependent launch.  With N > 1 (launched by
+torch.distributed.run, one rank per GPU) the step is ONE cooperative launch per GPU (rc_ffn_decode_tp):
+gate and up split by output rows, down by the matching columns, each rank streams its shard and the
+ranks' partial outputs are summed through stores into peer memory; the row-sharded one-launch form and
+the launch chain with peer gathers are timed beside it.  At N > 1 the line also carries the row-sharded
+prefill GEMM that gathers its own output and the MoE layer with the experts spread over the ranks.
+`--profile-case {mmqx,ffn}` runs a few launches of one kernel for a small ncu capture.
 `--impl reference` times the reference's CPU path (dequantize to f32 + sequential-f32 row
 dots, row-parallel over the host cores) on a bounded sample of the same workload.
 """
