@@ -79,3 +79,35 @@ def test_grouped_many_tiles_per_cta(rt):
     _, y64 = ro.grouped_q8(t, slab, et.bytes_per_expert, moe.expert_off.cpu().numpy(), ro.quantize_q8(x[perm // n_used]),
                            in_dim, out_dim)
     assert ro.rel_l2(y.cpu().numpy(), y64) < EXPECTED
+
+
+@pytest.mark.parametrize("t", [ro.Q4_K, ro.Q6_K])
+def test_grouped_gate_up_with_dropped_entries(rt, t):
+    """Ids outside the experts (and -1, which rc_moe_topk writes when no logit of a token is a number) are dropped by the
+    sort: perm carries -1 for the slots past the routed total, and the f32 prologue must treat those as zero rows instead
+    of reading a row at index 0xFFFFFFFF / n_used.  The kept entries equal the oracle's, nothing else is touched."""
+    in_dim, out_dim, n_expert, n_tok, n_used = 512, 256, 8, 40, 2
+    rng = np.random.default_rng(50 + t)
+    n_entries = n_tok * n_used
+    ids = rng.integers(0, n_expert, n_entries, dtype=np.int32)
+    ids[::9] = -1
+    ids[4::13] = n_expert + 3
+    n_kept = int(((ids >= 0) & (ids < n_expert)).sum())
+    raws = [cases.synth_case(t, in_dim, out_dim, 1, seed=200 * t + e)[0] for e in range(n_expert)]
+    et = rt.GpuExpertTensor.from_bytes(np.concatenate(raws), t, in_dim, out_dim, n_expert)
+    slab = np.concatenate([ro.repack(t, r, in_dim, out_dim) for r in raws])
+    moe = rt.MoeGroupedScratch.new(n_expert, n_entries)
+    rt.launch_moe_sort(moe, torch.from_numpy(ids).cuda(), n_entries)
+    x = rng.standard_normal((n_tok, in_dim)).astype(np.float32)
+    y = torch.full((n_entries, out_dim), float("nan"), device="cuda")
+    rt.MoeGroupedGemm().gate_up(moe, et, torch.from_numpy(x).cuda(), n_used, y, n_entries)
+    torch.cuda.synchronize()
+    assert _status(rt._lib.load()) == 0
+    expert_off = moe.expert_off.cpu().numpy()
+    perm = moe.perm.cpu().numpy()[:n_entries]
+    assert int(expert_off[n_expert]) == n_kept and (perm[:n_kept] >= 0).all() and (perm[n_kept:] == -1).all()
+    _, y64 = ro.grouped_q8(t, slab, et.bytes_per_expert, expert_off, ro.quantize_q8(x[perm[:n_kept] // n_used]), in_dim, out_dim)
+    got = y.cpu().numpy()
+    assert np.isfinite(got[:n_kept]).all()
+    assert ro.rel_l2(got[:n_kept], y64) < EXPECTED
+    assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0   # the context is alive
