@@ -370,7 +370,7 @@ int rc_moe_act_q8(void *stream, const float *gu, void *out, uint32_t ff, uint32_
 /* launch_moe_combine (src/runtime/gemma4.rs:1804-1823); kernel moe_combine_f32
  * (kernels/moe_combine.cpp:16-37): out[t][i] = sum_j weights[t][j] * expert_scale[ids[t][j]] *
  * experts[t][j][i], accumulated in slot order.  expert_scale may be NULL (all ones).  A slot whose id is
- * negative (a dropped entry: rc_moe_topk writes -1 when no logit of a token is a number) adds nothing. */
+ * negative (a dropped entry) adds nothing. */
 int rc_moe_combine(void *stream, const float *experts, const int32_t *ids, const float *weights,
                    const float *expert_scale, float *out, uint32_t hidden, uint32_t n_used, uint32_t n_tok);
 

@@ -67,6 +67,9 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float *__restrict__
             const uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
             if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
         }
+        // no probability of the row is a number (all logits NaN): the reference's scan leaves its index at 0
+        // (kernels/moe_topk.cpp: `float bv = -1.0f; int bi = 0;`)
+        if (bi == 0xFFFFFFFFu) bi = 0u;
         if (lane == 0) out_ids[(size_t)tok * n_used + r] = (int32_t)bi;
         if ((r & 31u) == lane) mine = bv; // n_used <= 32 (checked on the host)
         wsum += bv;

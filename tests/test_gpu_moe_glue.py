@@ -55,6 +55,20 @@ def test_topk_ties_nan_and_floor(rt):
     np.testing.assert_allclose(wts, 0.125, rtol=1e-6)
 
 
+def test_topk_row_without_a_number_follows_the_reference(rt):
+    """All logits of a token NaN: no probability is a number and no candidate ever wins.  The reference's scan then
+    leaves its index at 0 (kernels/moe_topk.cpp: `float bv = -1.0f; int bi = 0;`), and so do the oracle and the kernel:
+    ids stay inside the experts, the neighbouring rows are untouched."""
+    logits = np.zeros((3, 64), dtype=np.float32)
+    logits[1] = np.nan
+    ids, wts = _topk(rt, logits, 4)
+    rids, rwts = ro.router_topk(logits, 4)
+    np.testing.assert_array_equal(ids, rids)
+    np.testing.assert_array_equal(ids[1], 0)
+    np.testing.assert_array_equal(wts[1], rwts[1])
+    np.testing.assert_allclose(wts[[0, 2]], 0.25, rtol=1e-6)
+
+
 def _unpack_q8(b: np.ndarray):
     b = np.ascontiguousarray(b).reshape(-1, 40)
     d = b[:, 0:4].copy().view(np.float32).reshape(-1)
