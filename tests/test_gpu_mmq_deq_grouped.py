@@ -83,7 +83,7 @@ def test_grouped_many_tiles_per_cta(rt):
 
 @pytest.mark.parametrize("t", [ro.Q4_K, ro.Q6_K])
 def test_grouped_gate_up_with_dropped_entries(rt, t):
-    """Ids outside the experts (and -1, which rc_moe_topk writes when no logit of a token is a number) are dropped by the
+    """Ids outside the experts (and -1, the mark of an unused slot) are dropped by the
     sort: perm carries -1 for the slots past the routed total, and the f32 prologue must treat those as zero rows instead
     of reading a row at index 0xFFFFFFFF / n_used.  The kept entries equal the oracle's, nothing else is touched."""
     in_dim, out_dim, n_expert, n_tok, n_used = 512, 256, 8, 40, 2
